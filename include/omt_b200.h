@@ -1,0 +1,239 @@
+/* omt_b200.h -- C ABI of libomt_b200.so: the B200 (sm_100a) runtime and kernels under the
+ * "omarchy_mac_torch" PyTorch device.
+ *
+ * This is the boundary the reference's op layer sits on. In the reference the op files (csrc/conv.cpp, nn.cpp,
+ * fused.cpp, plans.cpp, optim.cpp) call a wgpu runtime through csrc/omt.h:48-106 (alloc_buf / launch / uniform /
+ * sync_all ...) with kernel *names*; here they call these entry points instead. Every function:
+ *   - takes plain device pointers, sizes and a stream handle (a cudaStream_t cast to omt_stream_t; NULL = the
+ *     legacy default stream); no torch or C++ types cross this boundary;
+ *   - returns 0 on success or a negative OMT_E* code; the message is read with omt_last_error();
+ *   - never throws, never falls back to the host: there is no CPU path in this library.
+ * All tensors are float32 unless stated. Activations are addressed through OmtAct (pointer + element strides), so
+ * the same entry point serves NCHW-contiguous tensors (the reference's only layout, csrc/device.cpp:60-66 base0)
+ * and channels-last (NHWC) tensors, which is what the tensor-core kernels prefer.
+ */
+#ifndef OMT_B200_H
+#define OMT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* omt_stream_t; /* cudaStream_t */
+typedef void* omt_event_t;  /* cudaEvent_t  */
+
+enum {
+  OMT_OK = 0,
+  OMT_EINVAL = -1,      /* argument outside what the kernels cover (the op layer's NEED() cases) */
+  OMT_ECUDA = -2,       /* a CUDA runtime call failed; omt_last_error() has cudaGetErrorString */
+  OMT_ENOMEM = -3,      /* device allocation failed even after releasing the cache */
+  OMT_EWORKSPACE = -4,  /* caller-provided workspace too small */
+  OMT_ETOOBIG = -5      /* beyond the fixed capacity of a no-allocation entry point */
+};
+
+/* ---- geometry ------------------------------------------------------------------------------------------------ */
+
+/* Convolution geometry. Mirrors the reference's `Geo` (csrc/omt.h:224-226) and `conv_geo` (csrc/conv.cpp:19-21):
+ * square kernel ks, one stride and one padding for both axes, no dilation. groups is 1 (dense) or ci (depthwise). */
+typedef struct OmtConvGeo {
+  int32_t n, ci, co, ih, iw, oh, ow, ks, stride, pad, groups;
+} OmtConvGeo;
+
+/* An activation tensor [n, c, h, w] given by its base pointer and element strides. */
+typedef struct OmtAct {
+  float* p;
+  int64_t sn, sc, sh, sw;
+} OmtAct;
+
+/* epilogue / behaviour flags of the conv entry points */
+enum {
+  OMT_EPI_BIAS = 1,        /* y += bias[co]          (reference hb bit 0, omarchy_mac_torch/gemm.py:37) */
+  OMT_EPI_RELU = 2,        /* y = max(y, 0)          (reference hb bit 1, omarchy_mac_torch/gemm.py:38) */
+  OMT_EPI_BNSTATS = 4,     /* also accumulate per-channel sum / sum of squares of y into stats[2*co] (must be zeroed) */
+  OMT_FORCE_SIMT = 0x100,  /* skip the tcgen05 path (used by tests to cross-check the two paths) */
+  OMT_FORCE_TC = 0x200     /* fail with OMT_EINVAL instead of taking the SIMT path */
+};
+
+/* ---- runtime: replaces csrc/runtime.cpp + the allocator/guard half of csrc/device.cpp -------------------------- */
+
+/* Select and initialise a device (creates the context lazily like init_ctx, csrc/runtime.cpp:83-127). */
+int omt_init(int device_ordinal);
+int omt_device(void);
+/* Copies the last error message of the calling thread into buf; returns its length. */
+int omt_last_error(char* buf, size_t n);
+/* Sticky asynchronous error check (reference check_errors, csrc/runtime.cpp:73-81): returns OMT_ECUDA once a
+ * kernel or copy has failed. */
+int omt_check_errors(void);
+/* Waits for all work on the device (reference sync_all, csrc/runtime.cpp). */
+int omt_sync(void);
+
+/* Caching allocator (reference alloc_buf/free_buf/empty_cache, csrc/runtime.cpp:183-240; c10 allocator
+ * csrc/device.cpp:18-30). Blocks are rounded to size classes and reused; a block freed while streams other than its
+ * allocation stream still use it (omt_record_stream) is parked until their recorded events complete. On
+ * cudaErrorMemoryAllocation the cache is released and the allocation retried once (csrc/runtime.cpp:219-225). */
+void* omt_malloc(size_t bytes, omt_stream_t stream);
+void omt_free(void* p);
+int omt_record_stream(void* p, omt_stream_t stream);
+void omt_empty_cache(void);
+size_t omt_memory_allocated(void);
+size_t omt_memory_reserved(void);
+
+/* Streams and events (reference Guard, csrc/device.cpp:120-162, had one in-order queue; here: real streams). */
+omt_stream_t omt_stream_create(int high_priority);
+int omt_stream_destroy(omt_stream_t s);
+int omt_stream_sync(omt_stream_t s);
+int omt_stream_query(omt_stream_t s); /* 1 = idle, 0 = busy, <0 error */
+omt_event_t omt_event_create(int timing);
+int omt_event_destroy(omt_event_t e);
+int omt_event_record(omt_event_t e, omt_stream_t s);
+int omt_event_query(omt_event_t e); /* 1 = complete */
+int omt_event_sync(omt_event_t e);
+int omt_stream_wait_event(omt_stream_t s, omt_event_t e);
+int omt_event_elapsed_ms(omt_event_t a, omt_event_t b, float* ms);
+
+/* Transfers (reference upload_bytes/download_bytes/record_copy, csrc/runtime.cpp). d2h waits for the copy. */
+int omt_memcpy_h2d(void* dst, const void* src, size_t bytes, omt_stream_t s);
+int omt_memcpy_d2h(void* dst, const void* src, size_t bytes, omt_stream_t s);
+int omt_memcpy_d2d(void* dst, const void* src, size_t bytes, omt_stream_t s);
+int omt_memset(void* dst, int byte, size_t bytes, omt_stream_t s);
+
+/* Launch accounting (reference stats().kcount, csrc/runtime.cpp:598-610, bound as kernel_counts in
+ * csrc/module.cpp:30-33). omt_launch_count is the number of kernels of this library launched so far. */
+uint64_t omt_launch_count(void);
+/* Writes "name=count\n" lines for every kernel launched since the last reset; returns bytes needed. */
+size_t omt_kernel_counts(char* buf, size_t n, int reset);
+
+/* ---- dense convolution: reference gemm_forward / gemm_grad_input / gemm_grad_weight + csum_nchw ---------------- */
+
+/* Scratch bytes omt_conv_* needs for this geometry (kind: 0 fwd, 1 dgrad, 2 wgrad). When the caller passes
+ * workspace == NULL the library takes the scratch from its own caching allocator on `stream`. */
+size_t omt_conv_workspace_bytes(int kind, const OmtConvGeo* g, uint32_t flags);
+
+/* y[n,co,oh,ow] = conv(x, w) (+bias)(ReLU). w is [co, ci, ks, ks] contiguous. Replaces gemm_forward
+ * (csrc/conv.cpp:70-77) and the kind-0 generated kernel (omarchy_mac_torch/gemm.py:25-42).
+ * With OMT_EPI_BNSTATS, stats[0..co) += sum_y, stats[co..2co) += sum_y^2 of the stored values. */
+int omt_conv_fwd(const OmtConvGeo* g, const OmtAct* x, const float* w, const float* bias, const OmtAct* y,
+                 float* stats, uint32_t flags, void* workspace, size_t workspace_bytes, omt_stream_t stream);
+
+/* dx[n,ci,ih,iw] = conv^T(gy, w). Any stride 1..4: strided convs are split into stride^2 phases, each a dense
+ * GEMM over the taps that land on it, batched in one launch. Replaces gemm_grad_input (csrc/conv.cpp:78-100) and
+ * kinds 1 and 5 (omarchy_mac_torch/gemm.py:43-80). */
+int omt_conv_dgrad(const OmtConvGeo* g, const OmtAct* gy, const float* w, const OmtAct* dx, uint32_t flags,
+                   void* workspace, size_t workspace_bytes, omt_stream_t stream);
+
+/* dw[co,ci,ks,ks] = sum over (n,oy,ox) of gy * im2col(x); split-K partial slabs in the workspace, then a
+ * deterministic slab sum. Replaces gemm_grad_weight (csrc/conv.cpp:102-114), kind 2 (omarchy_mac_torch/gemm.py:81-91)
+ * and csrc/kernels/gemm_reduce.wgsl. `scale` multiplies the result (1/world_size pre-scaling for data parallel). */
+int omt_conv_wgrad(const OmtConvGeo* g, const OmtAct* x, const OmtAct* gy, float* dw, float scale, uint32_t flags,
+                   void* workspace, size_t workspace_bytes, omt_stream_t stream);
+
+/* db[c] = sum over (n,h,w) of gy. Replaces csrc/kernels/csum_nchw.wgsl (csrc/conv.cpp:232-235). */
+int omt_conv_bias_grad(const OmtAct* gy, int32_t n, int32_t c, int32_t h, int32_t w, float* db, float scale,
+                       omt_stream_t stream);
+
+/* ---- depthwise convolution: reference dw_fwd/dw_gin/dw_gwt and dwg_* (csrc/conv.cpp:194-229) ------------------- */
+
+int omt_dw_fwd(const OmtConvGeo* g, const OmtAct* x, const float* w, const float* bias, const OmtAct* y,
+               uint32_t flags, omt_stream_t stream);
+int omt_dw_dgrad(const OmtConvGeo* g, const OmtAct* gy, const float* w, const OmtAct* dx, omt_stream_t stream);
+int omt_dw_wgrad(const OmtConvGeo* g, const OmtAct* x, const OmtAct* gy, float* dw, float scale,
+                 omt_stream_t stream);
+
+/* ---- batch norm: reference batch_norm_ / batch_norm_backward_ (csrc/nn.cpp:25-78), bn_relu_* (csrc/fused.cpp) --- */
+
+enum { OMT_BN_RELU = 1 /* apply / mask ReLU */, OMT_BN_FUNCTIONAL = 2 /* running stats go to new_rm/new_rv */ };
+
+/* Per-channel batch statistics. mean[c], var[c] (biased), from shifted sums like bn_stats_part/fin
+ * (csrc/kernels/bn_stats_part.wgsl:22-31, bn_stats_fin.wgsl:15-21). Also updates the running statistics:
+ * rm += momentum*(mean-rm), rv += momentum*(var*count/(count-1) - rv); with OMT_BN_FUNCTIONAL the updated values
+ * are written to new_rm/new_rv instead and rm/rv are left alone (bn_stats_fin_functional.wgsl). rm may be NULL.
+ * invstd[c] = rsqrt(var+eps) is written as well. */
+int omt_bn_stats(const OmtAct* x, int32_t n, int32_t c, int32_t h, int32_t w, float* mean, float* var,
+                 float* invstd, float* rm, float* rv, float* new_rm, float* new_rv, float momentum, float eps,
+                 uint32_t flags, omt_stream_t stream);
+/* Same, from sums the conv epilogue accumulated (OMT_EPI_BNSTATS): sums[0..c)=sum y, sums[c..2c)=sum y^2. */
+int omt_bn_stats_from_sums(const float* sums, int64_t count, int32_t c, float* mean, float* var, float* invstd,
+                           float* rm, float* rv, float momentum, float eps, omt_stream_t stream);
+/* y = (x-mean)*invstd*gamma+beta, ReLU with OMT_BN_RELU (bn_apply.wgsl:17-18, bn_relu.wgsl:17-18). */
+int omt_bn_apply(const OmtAct* x, const OmtAct* y, int32_t n, int32_t c, int32_t h, int32_t w, const float* mean,
+                 const float* invstd, const float* gamma, const float* beta, uint32_t flags, omt_stream_t stream);
+/* Eval mode: invstd = rsqrt(rv+eps) computed on the fly (bn_eval_inv.wgsl, bn_relu_rv.wgsl). */
+int omt_bn_eval(const OmtAct* x, const OmtAct* y, int32_t n, int32_t c, int32_t h, int32_t w, const float* rm,
+                const float* rv, const float* gamma, const float* beta, float eps, uint32_t flags,
+                omt_stream_t stream);
+/* Backward (training). dgamma=sum g*xhat, dbeta=sum g, dx=gamma*invstd/m*(m*g-dbeta-xhat*dgamma)
+ * (bnb_reduce.wgsl:25-37, bnb_apply.wgsl:19-21). With OMT_BN_RELU, g is first masked by y>0
+ * (bn_bwd_part.wgsl:25-38, bn_bwd_apply.wgsl:19-23); y is then required. dx->p may be NULL (mask[0] false).
+ * dgb is [2*c]: row 0 dgamma, row 1 dbeta (the layout csrc/nn.cpp:70 uses). scale multiplies dgamma/dbeta only. */
+int omt_bn_backward(const OmtAct* gy, const OmtAct* x, const OmtAct* y, const OmtAct* dx, int32_t n, int32_t c,
+                    int32_t h, int32_t w, const float* mean, const float* invstd, const float* gamma, float* dgb,
+                    float scale, uint32_t flags, omt_stream_t stream);
+
+/* ---- pooling: plan kernels (pool_fwd/bwd, avgpool_fwd/bwd, gap_fwd/bwd) and general ops (csrc/nn.cpp:137-222) --- */
+
+/* 2x2 stride-2 max pool; idx[n,c,oh,ow] in {0..3} = (dy*2+dx) of the first maximum (strict >), pool_fwd.wgsl:15-21.
+ * idx has the strides of y. */
+int omt_pool2_fwd(const OmtAct* x, const OmtAct* y, uint8_t* idx, int32_t n, int32_t c, int32_t h, int32_t w,
+                  omt_stream_t stream);
+int omt_pool2_bwd(const OmtAct* gy, const uint8_t* idx, const OmtAct* gx, int32_t n, int32_t c, int32_t h,
+                  int32_t w, omt_stream_t stream);
+int omt_avgpool2_fwd(const OmtAct* x, const OmtAct* y, int32_t n, int32_t c, int32_t h, int32_t w,
+                     omt_stream_t stream);
+int omt_avgpool2_bwd(const OmtAct* gy, const OmtAct* gx, int32_t n, int32_t c, int32_t h, int32_t w,
+                     omt_stream_t stream);
+/* General max pool with aten semantics: int64 indices = flat iy*iw+ix, NaN propagates
+ * (maxpool_gen_fwd.wgsl:16-28). idx has the strides of y. */
+typedef struct OmtPool {
+  int32_t kh, kw, sh, sw, ph, pw, dh, dw;
+} OmtPool;
+int omt_maxpool_fwd(const OmtAct* x, const OmtAct* y, int64_t* idx, int32_t n, int32_t c, int32_t ih, int32_t iw,
+                    int32_t oh, int32_t ow, const OmtPool* p, omt_stream_t stream);
+int omt_maxpool_bwd(const OmtAct* gy, const int64_t* idx, const OmtAct* gx, int32_t n, int32_t c, int32_t ih,
+                    int32_t iw, int32_t oh, int32_t ow, const OmtPool* p, omt_stream_t stream);
+/* avg pool with aten divisor rules (avgpool_gen_fwd.wgsl); divisor 0 = none. */
+int omt_avgpool_fwd(const OmtAct* x, const OmtAct* y, int32_t n, int32_t c, int32_t ih, int32_t iw, int32_t oh,
+                    int32_t ow, const OmtPool* p, int32_t count_include_pad, int32_t divisor, omt_stream_t stream);
+int omt_avgpool_bwd(const OmtAct* gy, const OmtAct* gx, int32_t n, int32_t c, int32_t ih, int32_t iw, int32_t oh,
+                    int32_t ow, const OmtPool* p, int32_t count_include_pad, int32_t divisor, omt_stream_t stream);
+/* adaptive average pool (adapool_fwd/bwd.wgsl; gap_fwd/bwd.wgsl are the 1x1 case). */
+int omt_adaptive_avgpool_fwd(const OmtAct* x, const OmtAct* y, int32_t n, int32_t c, int32_t ih, int32_t iw,
+                             int32_t oh, int32_t ow, omt_stream_t stream);
+int omt_adaptive_avgpool_bwd(const OmtAct* gy, const OmtAct* gx, int32_t n, int32_t c, int32_t ih, int32_t iw,
+                             int32_t oh, int32_t ow, omt_stream_t stream);
+
+/* ---- fused optimizers: reference fused_sgd_ / adam_impl (csrc/optim.cpp:12-61), sgd.wgsl, adam.wgsl ------------- */
+
+/* One entry per parameter tensor. The reference issues one dispatch per parameter (csrc/optim.cpp:20-25); here one
+ * launch walks the whole table. `step` is the device float32 step counter of that parameter (Adam only). */
+typedef struct OmtParam {
+  float* p;
+  const float* g;
+  float* m;          /* SGD momentum buffer (may be NULL) / Adam exp_avg */
+  float* v;          /* Adam exp_avg_sq */
+  const float* step; /* Adam: device scalar holding the (already incremented) step count */
+  int64_t numel;
+} OmtParam;
+
+/* g=+-g+wd*p; v=first?g:mom*m+(1-damp)*g; d=nesterov?g+mom*v:v; p-=lr*d  (sgd.wgsl:9-24).
+ * `table` is a HOST array of `count` entries; it is copied to the device by this call (pinned staging). */
+int omt_sgd(const OmtParam* table, int32_t count, float lr, float momentum, float dampening, float weight_decay,
+            int32_t nesterov, int32_t first_step, int32_t maximize, omt_stream_t stream);
+/* Adam / AdamW (decoupled=1), adam.wgsl:13-27: bias corrections from the device step counter. */
+int omt_adam(const OmtParam* table, int32_t count, float lr, float beta1, float beta2, float eps,
+             float weight_decay, int32_t decoupled, int32_t maximize, omt_stream_t stream);
+
+/* ---- small helpers used by plans and data parallel ---------------------------------------------------------------- */
+
+/* dst = src * scale over n floats (bucket averaging after all-reduce; icopy.wgsl when scale == 1). */
+int omt_scale_copy(float* dst, const float* src, int64_t n, float scale, omt_stream_t stream);
+/* strided copy between two activation views (layout change NCHW <-> NHWC). */
+int omt_act_copy(const OmtAct* src, const OmtAct* dst, int32_t n, int32_t c, int32_t h, int32_t w,
+                 omt_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OMT_B200_H */

@@ -1,0 +1,394 @@
+// BatchNorm2d kernels: batch statistics, normalise(+ReLU), eval, backward(+ReLU mask). All are HBM-bound: every
+// kernel reads its activations once with 128-bit accesses where the layout allows and reduces with warp shuffles.
+//
+// Behaviour follows the reference's BN shaders: shifted one-pass statistics (bn_stats_part.wgsl:22-31,
+// bn_stats_fin.wgsl:15-21), running-stat update with the unbiased correction count/(count-1) (csrc/nn.cpp:44),
+// apply/ReLU (bn_apply.wgsl, bn_relu.wgsl, bn_relu_rv.wgsl), backward (bnb_reduce.wgsl, bnb_apply.wgsl) and the
+// ReLU-masked backward (bn_bwd_part.wgsl:25-38, bn_bwd_apply.wgsl:19-23). Two layouts: NCHW-contiguous (the
+// reference's) and channels-last.
+#include <algorithm>
+
+#include "common.cuh"
+
+namespace omt {
+
+// ---------------------------------------------------------------------------------------------------------------
+// partial sums. part layout: [c][S][2]
+// ---------------------------------------------------------------------------------------------------------------
+
+// NCHW: block (channel, slice); slice sl takes images sl, sl+S, ...
+// MODE 0: stats of x (shifted by x[0,ch,0,0]); MODE 1: backward sums (sum g, sum g*xhat), g masked by y>0 if RELU.
+template <int MODE, bool RELU>
+__global__ void __launch_bounds__(256) bn_part_nchw(const float* __restrict__ x, const float* __restrict__ g,
+                                                    const float* __restrict__ y, const float* __restrict__ mean,
+                                                    const float* __restrict__ invstd, int n, int c, int hw, int S,
+                                                    float* __restrict__ part) {
+  __shared__ float red[32];
+  const int ch = blockIdx.x, sl = blockIdx.y;
+  float a0, a1;
+  if (MODE == 0) { a0 = __ldg(x + (int64_t)ch * hw); a1 = 0.f; }
+  else { a0 = __ldg(mean + ch); a1 = __ldg(invstd + ch); }
+  float s1 = 0.f, s2 = 0.f;
+  const bool vec = (hw & 3) == 0;
+  for (int img = sl; img < n; img += S) {
+    const int64_t base = ((int64_t)img * c + ch) * hw;
+    if (vec) {
+      const float4* x4 = reinterpret_cast<const float4*>(x + base);
+      const float4* g4 = reinterpret_cast<const float4*>(g + base);
+      const float4* y4 = reinterpret_cast<const float4*>(y + base);
+      for (int e = threadIdx.x; e < hw / 4; e += blockDim.x) {
+        float4 xv = __ldg(x4 + e);
+        if (MODE == 0) {
+          float d0 = xv.x - a0, d1 = xv.y - a0, d2 = xv.z - a0, d3 = xv.w - a0;
+          s1 += (d0 + d1) + (d2 + d3);
+          s2 += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
+        } else {
+          float4 gv = __ldg(g4 + e);
+          if (RELU) {
+            float4 yv = __ldg(y4 + e);
+            gv.x = yv.x > 0.f ? gv.x : 0.f; gv.y = yv.y > 0.f ? gv.y : 0.f;
+            gv.z = yv.z > 0.f ? gv.z : 0.f; gv.w = yv.w > 0.f ? gv.w : 0.f;
+          }
+          s1 += (gv.x + gv.y) + (gv.z + gv.w);
+          s2 += (gv.x * (xv.x - a0) + gv.y * (xv.y - a0) + gv.z * (xv.z - a0) + gv.w * (xv.w - a0)) * a1;
+        }
+      }
+    } else {
+      for (int e = threadIdx.x; e < hw; e += blockDim.x) {
+        float xv = __ldg(x + base + e);
+        if (MODE == 0) {
+          float d = xv - a0;
+          s1 += d; s2 += d * d;
+        } else {
+          float gv = __ldg(g + base + e);
+          if (RELU) gv = __ldg(y + base + e) > 0.f ? gv : 0.f;
+          s1 += gv; s2 += gv * (xv - a0) * a1;
+        }
+      }
+    }
+  }
+  s1 = block_sum(s1, red);
+  s2 = block_sum(s2, red);
+  if (threadIdx.x == 0) {
+    part[((int64_t)ch * S + sl) * 2] = s1;
+    part[((int64_t)ch * S + sl) * 2 + 1] = s2;
+  }
+}
+
+// NHWC: x is [P pixels][c]. Block = CX channel groups of 4 x PY pixel lanes; slice sl takes pixels sl*PY+py, +S*PY ...
+template <int MODE, bool RELU>
+__global__ void __launch_bounds__(256) bn_part_nhwc(const float* __restrict__ x, const float* __restrict__ g,
+                                                    const float* __restrict__ y, const float* __restrict__ mean,
+                                                    const float* __restrict__ invstd, int64_t P, int c, int S, int CX,
+                                                    float* __restrict__ part) {
+  __shared__ float4 sh1[256], sh2[256];
+  const int cx = threadIdx.x % CX, py = threadIdx.x / CX, PY = blockDim.x / CX;
+  const int c4 = (blockIdx.x * CX + cx) * 4, sl = blockIdx.y;
+  float4 s1 = make_float4(0, 0, 0, 0), s2 = s1;
+  if (c4 < c) {
+    float4 a0, a1 = make_float4(0, 0, 0, 0);
+    if (MODE == 0) a0 = __ldg(reinterpret_cast<const float4*>(x + c4));
+    else { a0 = __ldg(reinterpret_cast<const float4*>(mean + c4)); a1 = __ldg(reinterpret_cast<const float4*>(invstd + c4)); }
+    for (int64_t p = (int64_t)sl * PY + py; p < P; p += (int64_t)S * PY) {
+      float4 xv = __ldg(reinterpret_cast<const float4*>(x + p * c + c4));
+      if (MODE == 0) {
+        float d0 = xv.x - a0.x, d1 = xv.y - a0.y, d2 = xv.z - a0.z, d3 = xv.w - a0.w;
+        s1.x += d0; s1.y += d1; s1.z += d2; s1.w += d3;
+        s2.x += d0 * d0; s2.y += d1 * d1; s2.z += d2 * d2; s2.w += d3 * d3;
+      } else {
+        float4 gv = __ldg(reinterpret_cast<const float4*>(g + p * c + c4));
+        if (RELU) {
+          float4 yv = __ldg(reinterpret_cast<const float4*>(y + p * c + c4));
+          gv.x = yv.x > 0.f ? gv.x : 0.f; gv.y = yv.y > 0.f ? gv.y : 0.f;
+          gv.z = yv.z > 0.f ? gv.z : 0.f; gv.w = yv.w > 0.f ? gv.w : 0.f;
+        }
+        s1.x += gv.x; s1.y += gv.y; s1.z += gv.z; s1.w += gv.w;
+        s2.x += gv.x * (xv.x - a0.x) * a1.x; s2.y += gv.y * (xv.y - a0.y) * a1.y;
+        s2.z += gv.z * (xv.z - a0.z) * a1.z; s2.w += gv.w * (xv.w - a0.w) * a1.w;
+      }
+    }
+  }
+  sh1[threadIdx.x] = s1; sh2[threadIdx.x] = s2;
+  __syncthreads();
+  if (py == 0 && c4 < c) {
+    for (int q = 1; q < PY; q++) {
+      float4 u = sh1[q * CX + cx], v = sh2[q * CX + cx];
+      s1.x += u.x; s1.y += u.y; s1.z += u.z; s1.w += u.w;
+      s2.x += v.x; s2.y += v.y; s2.z += v.z; s2.w += v.w;
+    }
+    const float a[4] = {s1.x, s1.y, s1.z, s1.w}, b[4] = {s2.x, s2.y, s2.z, s2.w};
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      part[((int64_t)(c4 + j) * S + sl) * 2] = a[j];
+      part[((int64_t)(c4 + j) * S + sl) * 2 + 1] = b[j];
+    }
+  }
+}
+
+// finalise statistics: one thread per channel. shift_stride = distance between channels' first elements.
+__global__ void bn_stats_fin(const float* __restrict__ x, int64_t shift_stride, const float* __restrict__ part, int c, int S,
+                             float count, float corr, float momentum, float eps, float* mean, float* var, float* invstd,
+                             const float* rm_in, const float* rv_in, float* rm_out, float* rv_out) {
+  int ch = blockIdx.x * blockDim.x + threadIdx.x;
+  if (ch >= c) return;
+  float s1 = 0.f, s2 = 0.f;
+  for (int k = 0; k < S; k++) { s1 += part[((int64_t)ch * S + k) * 2]; s2 += part[((int64_t)ch * S + k) * 2 + 1]; }
+  float a = s1 / count, shift = x ? x[ch * shift_stride] : 0.f;
+  float m = shift + a, v = fmaxf(s2 / count - a * a, 0.f);
+  if (mean) mean[ch] = m;
+  if (var) var[ch] = v;
+  if (invstd) invstd[ch] = rsqrtf(v + eps);
+  if (rm_out) {
+    float r0 = rm_in[ch], r1 = rv_in[ch];
+    rm_out[ch] = r0 + momentum * (m - r0);
+    rv_out[ch] = r1 + momentum * (v * corr - r1);
+  }
+}
+// finalise backward sums: dgb[0][c] = dgamma (s2), dgb[1][c] = dbeta (s1)   (bn_bwd_fin.wgsl)
+__global__ void bn_bwd_fin(const float* __restrict__ part, int c, int S, float scale, float* dgb, float* raw) {
+  int ch = blockIdx.x * blockDim.x + threadIdx.x;
+  if (ch >= c) return;
+  float s1 = 0.f, s2 = 0.f;
+  for (int k = 0; k < S; k++) { s1 += part[((int64_t)ch * S + k) * 2]; s2 += part[((int64_t)ch * S + k) * 2 + 1]; }
+  raw[ch] = s2; raw[c + ch] = s1;  // unscaled, for the dx formula
+  dgb[ch] = s2 * scale; dgb[c + ch] = s1 * scale;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// elementwise passes. KIND 0: y = (x-mean)*inv*gamma+beta (train; inv given) ; 1: eval (inv = rsqrt(rv+eps))
+//                     KIND 2: dx = gamma*inv/m*(m*g - dbeta - xhat*dgamma)
+// ---------------------------------------------------------------------------------------------------------------
+struct BnEw {
+  const float* x; const float* g; const float* y; float* out;
+  const float* mean; const float* inv; const float* gamma; const float* beta; const float* dgb;
+  float eps, m;
+  int c, hw;
+  int64_t total;
+};
+
+template <int KIND, bool RELU>
+__device__ __forceinline__ float bn_ew_one(const BnEw& a, float xv, float gv, float yv, float mean, float inv, float ga, float be,
+                                           float dg, float db) {
+  if (KIND <= 1) {
+    float r = (xv - mean) * inv * ga + be;
+    return RELU ? fmaxf(r, 0.f) : r;
+  } else {
+    float gz = RELU ? (yv > 0.f ? gv : 0.f) : gv;
+    float xhat = (xv - mean) * inv;
+    return ga * inv / a.m * (a.m * gz - db - xhat * dg);
+  }
+}
+
+template <int KIND, bool RELU, bool NHWC>
+__global__ void __launch_bounds__(256) bn_ew_vec4(BnEw a) {
+  int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i >= a.total) return;
+  float4 xv = __ldg(reinterpret_cast<const float4*>(a.x + i)), gv = xv, yv = xv, o;
+  if (KIND == 2) {
+    gv = __ldg(reinterpret_cast<const float4*>(a.g + i));
+    if (RELU) yv = __ldg(reinterpret_cast<const float4*>(a.y + i));
+  }
+  if (NHWC) {
+    int ch = (int)(i % a.c);
+    float4 mean = __ldg(reinterpret_cast<const float4*>(a.mean + ch)), inv = __ldg(reinterpret_cast<const float4*>(a.inv + ch));
+    float4 ga = __ldg(reinterpret_cast<const float4*>(a.gamma + ch));
+    float4 be = ga, dg = ga, db = ga;
+    if (KIND <= 1) be = __ldg(reinterpret_cast<const float4*>(a.beta + ch));
+    if (KIND == 1) { inv.x = rsqrtf(inv.x + a.eps); inv.y = rsqrtf(inv.y + a.eps); inv.z = rsqrtf(inv.z + a.eps); inv.w = rsqrtf(inv.w + a.eps); }
+    if (KIND == 2) { dg = __ldg(reinterpret_cast<const float4*>(a.dgb + ch)); db = __ldg(reinterpret_cast<const float4*>(a.dgb + a.c + ch)); }
+    o.x = bn_ew_one<KIND, RELU>(a, xv.x, gv.x, yv.x, mean.x, inv.x, ga.x, be.x, dg.x, db.x);
+    o.y = bn_ew_one<KIND, RELU>(a, xv.y, gv.y, yv.y, mean.y, inv.y, ga.y, be.y, dg.y, db.y);
+    o.z = bn_ew_one<KIND, RELU>(a, xv.z, gv.z, yv.z, mean.z, inv.z, ga.z, be.z, dg.z, db.z);
+    o.w = bn_ew_one<KIND, RELU>(a, xv.w, gv.w, yv.w, mean.w, inv.w, ga.w, be.w, dg.w, db.w);
+  } else {
+    int ch = (int)((i / a.hw) % a.c);
+    float mean = __ldg(a.mean + ch), inv = __ldg(a.inv + ch), ga = __ldg(a.gamma + ch), be = 0.f, dg = 0.f, db = 0.f;
+    if (KIND <= 1) be = __ldg(a.beta + ch);
+    if (KIND == 1) inv = rsqrtf(inv + a.eps);
+    if (KIND == 2) { dg = __ldg(a.dgb + ch); db = __ldg(a.dgb + a.c + ch); }
+    o.x = bn_ew_one<KIND, RELU>(a, xv.x, gv.x, yv.x, mean, inv, ga, be, dg, db);
+    o.y = bn_ew_one<KIND, RELU>(a, xv.y, gv.y, yv.y, mean, inv, ga, be, dg, db);
+    o.z = bn_ew_one<KIND, RELU>(a, xv.z, gv.z, yv.z, mean, inv, ga, be, dg, db);
+    o.w = bn_ew_one<KIND, RELU>(a, xv.w, gv.w, yv.w, mean, inv, ga, be, dg, db);
+  }
+  *reinterpret_cast<float4*>(a.out + i) = o;
+}
+
+template <int KIND, bool RELU>
+__global__ void __launch_bounds__(256) bn_ew_scalar(BnEw a, bool nhwc) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= a.total) return;
+  int ch = nhwc ? (int)(i % a.c) : (int)((i / a.hw) % a.c);
+  float xv = __ldg(a.x + i), gv = KIND == 2 ? __ldg(a.g + i) : 0.f, yv = (KIND == 2 && RELU) ? __ldg(a.y + i) : 0.f;
+  float inv = __ldg(a.inv + ch);
+  if (KIND == 1) inv = rsqrtf(inv + a.eps);
+  a.out[i] = bn_ew_one<KIND, RELU>(a, xv, gv, yv, __ldg(a.mean + ch), inv, __ldg(a.gamma + ch), KIND <= 1 ? __ldg(a.beta + ch) : 0.f,
+                                   KIND == 2 ? __ldg(a.dgb + ch) : 0.f, KIND == 2 ? __ldg(a.dgb + a.c + ch) : 0.f);
+}
+
+template <int KIND>
+static int launch_ew(const BnEw& a, bool relu, bool nhwc, cudaStream_t s, const char* name) {
+  bool vec = nhwc ? (a.c % 4 == 0) : (a.hw % 4 == 0);
+  vec = vec && ((reinterpret_cast<uintptr_t>(a.x) | reinterpret_cast<uintptr_t>(a.out) | reinterpret_cast<uintptr_t>(a.g) |
+                 reinterpret_cast<uintptr_t>(a.y)) & 15) == 0;
+  if (nhwc)  // per-channel tables are read as float4 too
+    vec = vec && ((reinterpret_cast<uintptr_t>(a.mean) | reinterpret_cast<uintptr_t>(a.inv) | reinterpret_cast<uintptr_t>(a.gamma) |
+                   reinterpret_cast<uintptr_t>(a.beta) | reinterpret_cast<uintptr_t>(a.dgb)) & 15) == 0;
+  if (vec) {
+    unsigned blocks = (unsigned)cdiv(a.total / 4, 256);
+    if (nhwc) {
+      if (relu) bn_ew_vec4<KIND, true, true><<<blocks, 256, 0, s>>>(a);
+      else bn_ew_vec4<KIND, false, true><<<blocks, 256, 0, s>>>(a);
+    } else {
+      if (relu) bn_ew_vec4<KIND, true, false><<<blocks, 256, 0, s>>>(a);
+      else bn_ew_vec4<KIND, false, false><<<blocks, 256, 0, s>>>(a);
+    }
+  } else {
+    unsigned blocks = (unsigned)cdiv(a.total, 256);
+    if (relu) bn_ew_scalar<KIND, true><<<blocks, 256, 0, s>>>(a, nhwc);
+    else bn_ew_scalar<KIND, false><<<blocks, 256, 0, s>>>(a, nhwc);
+  }
+  return check_launch(name);
+}
+
+// layout of an activation: 0 NCHW contiguous, 1 NHWC contiguous, -1 neither
+static int layout_of(const OmtAct* a, int c, int h, int w) {
+  if (is_nchw(a, c, h, w)) return 0;
+  if (is_nhwc(a, c, h, w)) return 1;
+  return -1;
+}
+
+// partial-sum launch shared by forward statistics (MODE 0) and backward (MODE 1)
+template <int MODE>
+static int launch_part(int lay, const float* x, const float* g, const float* y, const float* mean, const float* invstd, bool relu,
+                       int n, int c, int h, int w, int* S_out, float* part, cudaStream_t s) {
+  const int hw = h * w;
+  if (lay == 1 && c % 4 == 0) {
+    int64_t P = (int64_t)n * hw;
+    int CX = std::min(c / 4, 64);
+    while (256 % CX) CX--;  // CX must divide the block
+    int PY = 256 / CX, gx = (int)cdiv(c / 4, CX);
+    int S = (int)std::max<int64_t>(1, std::min<int64_t>(cdiv(P, PY * 4), cdiv(4 * sm_count(), gx)));
+    *S_out = S;
+    dim3 grid(gx, S);
+    if (relu) bn_part_nhwc<MODE, true><<<grid, 256, 0, s>>>(x, g, y, mean, invstd, P, c, S, CX, part);
+    else bn_part_nhwc<MODE, false><<<grid, 256, 0, s>>>(x, g, y, mean, invstd, P, c, S, CX, part);
+    return check_launch(MODE == 0 ? "bn_stats_part_nhwc" : "bn_bwd_part_nhwc");
+  }
+  // NCHW (also used for channels-last with c % 4 != 0 through the caller's layout check)
+  int S = (int)std::max<int64_t>(1, std::min<int64_t>(n, cdiv(4 * sm_count(), c)));
+  *S_out = S;
+  dim3 grid(c, S);
+  if (relu) bn_part_nchw<MODE, true><<<grid, 256, 0, s>>>(x, g, y, mean, invstd, n, c, hw, S, part);
+  else bn_part_nchw<MODE, false><<<grid, 256, 0, s>>>(x, g, y, mean, invstd, n, c, hw, S, part);
+  return check_launch(MODE == 0 ? "bn_stats_part_nchw" : "bn_bwd_part_nchw");
+}
+
+// statistics from raw sums [2][c] accumulated by a conv epilogue
+__global__ void bn_from_sums_kernel(const float* sums, int c, float count, float corr, float momentum, float eps, float* mean,
+                                    float* var, float* invstd, float* rm, float* rv) {
+  int ch = blockIdx.x * blockDim.x + threadIdx.x;
+  if (ch >= c) return;
+  float m = sums[ch] / count, v = fmaxf(sums[c + ch] / count - m * m, 0.f);
+  if (mean) mean[ch] = m;
+  if (var) var[ch] = v;
+  if (invstd) invstd[ch] = rsqrtf(v + eps);
+  if (rm) {
+    rm[ch] += momentum * (m - rm[ch]);
+    rv[ch] += momentum * (v * corr - rv[ch]);
+  }
+}
+
+static size_t part_floats(int c) { return (size_t)c * (size_t)std::max(8, 4 * sm_count()) * 2 + 64; }
+
+}  // namespace omt
+
+using namespace omt;
+
+extern "C" {
+
+int omt_bn_stats(const OmtAct* x, int32_t n, int32_t c, int32_t h, int32_t w, float* mean, float* var, float* invstd,
+                 float* rm, float* rv, float* new_rm, float* new_rv, float momentum, float eps, uint32_t flags,
+                 omt_stream_t stream) {
+  OMT_REQUIRE(x && x->p && n > 0 && c > 0 && h > 0 && w > 0, "omt_bn_stats: bad arguments");
+  int lay = layout_of(x, c, h, w);
+  OMT_REQUIRE(lay == 0 || (lay == 1 && c % 4 == 0), "omt_bn_stats: activation must be NCHW- or NHWC-contiguous (c %% 4 == 0)");
+  OMT_REQUIRE(!(flags & OMT_BN_FUNCTIONAL) || (rm && rv && new_rm && new_rv), "omt_bn_stats: functional mode needs rm, rv, new_rm, new_rv");
+  cudaStream_t s = st(stream);
+  Scratch sc;
+  int r = sc.get(nullptr, 0, part_floats(c) * sizeof(float), stream);
+  if (r) return r;
+  float* part = (float*)sc.p;
+  int S = 1;
+  r = launch_part<0>(lay, x->p, nullptr, nullptr, nullptr, nullptr, false, n, c, h, w, &S, part, s);
+  if (r) return r;
+  float count = (float)((int64_t)n * h * w);
+  float corr = count / std::max(count - 1.f, 1.f);
+  bool fn = flags & OMT_BN_FUNCTIONAL;
+  bn_stats_fin<<<(unsigned)cdiv(c, 128), 128, 0, s>>>(x->p, lay == 0 ? (int64_t)h * w : 1, part, c, S, count, corr, momentum, eps,
+                                                      mean, var, invstd, rm, rv, rm ? (fn ? new_rm : rm) : nullptr,
+                                                      rm ? (fn ? new_rv : rv) : nullptr);
+  return check_launch("bn_stats_fin");
+}
+
+int omt_bn_stats_from_sums(const float* sums, int64_t count, int32_t c, float* mean, float* var, float* invstd, float* rm,
+                           float* rv, float momentum, float eps, omt_stream_t stream) {
+  OMT_REQUIRE(sums && c > 0 && count > 0, "omt_bn_stats_from_sums: bad arguments");
+  float cnt = (float)count;
+  bn_from_sums_kernel<<<(unsigned)cdiv(c, 128), 128, 0, st(stream)>>>(sums, c, cnt, cnt / std::max(cnt - 1.f, 1.f), momentum, eps, mean, var,
+                                                         invstd, rm, rv);
+  return check_launch("bn_stats_from_sums");
+}
+
+int omt_bn_apply(const OmtAct* x, const OmtAct* y, int32_t n, int32_t c, int32_t h, int32_t w, const float* mean,
+                 const float* invstd, const float* gamma, const float* beta, uint32_t flags, omt_stream_t stream) {
+  OMT_REQUIRE(x && y && x->p && y->p && mean && invstd && gamma && beta, "omt_bn_apply: bad arguments");
+  int lay = layout_of(x, c, h, w);
+  OMT_REQUIRE(lay >= 0 && layout_of(y, c, h, w) == lay, "omt_bn_apply: x and y must share an NCHW or NHWC contiguous layout");
+  BnEw a{};
+  a.x = x->p; a.g = x->p; a.y = x->p; a.out = y->p; a.mean = mean; a.inv = invstd; a.gamma = gamma; a.beta = beta;
+  a.c = c; a.hw = h * w; a.total = (int64_t)n * c * h * w;
+  return launch_ew<0>(a, flags & OMT_BN_RELU, lay == 1, st(stream), "bn_apply");
+}
+
+int omt_bn_eval(const OmtAct* x, const OmtAct* y, int32_t n, int32_t c, int32_t h, int32_t w, const float* rm,
+                const float* rv, const float* gamma, const float* beta, float eps, uint32_t flags, omt_stream_t stream) {
+  OMT_REQUIRE(x && y && x->p && y->p && rm && rv && gamma && beta, "omt_bn_eval: bad arguments");
+  int lay = layout_of(x, c, h, w);
+  OMT_REQUIRE(lay >= 0 && layout_of(y, c, h, w) == lay, "omt_bn_eval: x and y must share an NCHW or NHWC contiguous layout");
+  BnEw a{};
+  a.x = x->p; a.g = x->p; a.y = x->p; a.out = y->p; a.mean = rm; a.inv = rv; a.gamma = gamma; a.beta = beta; a.eps = eps;
+  a.c = c; a.hw = h * w; a.total = (int64_t)n * c * h * w;
+  return launch_ew<1>(a, flags & OMT_BN_RELU, lay == 1, st(stream), "bn_eval");
+}
+
+int omt_bn_backward(const OmtAct* gy, const OmtAct* x, const OmtAct* y, const OmtAct* dx, int32_t n, int32_t c, int32_t h,
+                    int32_t w, const float* mean, const float* invstd, const float* gamma, float* dgb, float scale,
+                    uint32_t flags, omt_stream_t stream) {
+  bool relu = flags & OMT_BN_RELU;
+  OMT_REQUIRE(gy && x && gy->p && x->p && mean && invstd && gamma && dgb, "omt_bn_backward: bad arguments");
+  OMT_REQUIRE(!relu || (y && y->p), "omt_bn_backward: the ReLU mask needs y");
+  int lay = layout_of(x, c, h, w);
+  OMT_REQUIRE(lay == 0 || (lay == 1 && c % 4 == 0), "omt_bn_backward: activation must be NCHW- or NHWC-contiguous (c %% 4 == 0)");
+  OMT_REQUIRE(layout_of(gy, c, h, w) == lay && (!relu || layout_of(y, c, h, w) == lay) &&
+                  (!dx || !dx->p || layout_of(dx, c, h, w) == lay),
+              "omt_bn_backward: gy, x, y, dx must share one layout");
+  cudaStream_t s = st(stream);
+  Scratch sc;
+  int r = sc.get(nullptr, 0, (part_floats(c) + 2 * (size_t)c) * sizeof(float), stream);
+  if (r) return r;
+  float* part = (float*)sc.p;
+  float* raw = part + part_floats(c);
+  int S = 1;
+  r = launch_part<1>(lay, x->p, gy->p, relu ? y->p : x->p, mean, invstd, relu, n, c, h, w, &S, part, s);
+  if (r) return r;
+  bn_bwd_fin<<<(unsigned)cdiv(c, 128), 128, 0, s>>>(part, c, S, scale, dgb, raw);
+  r = check_launch("bn_bwd_fin");
+  if (r || !dx || !dx->p) return r;
+  BnEw a{};
+  a.x = x->p; a.g = gy->p; a.y = relu ? y->p : x->p; a.out = dx->p; a.mean = mean; a.inv = invstd; a.gamma = gamma; a.dgb = raw;
+  a.m = (float)((int64_t)n * h * w); a.c = c; a.hw = h * w; a.total = (int64_t)n * c * h * w;
+  return launch_ew<2>(a, relu, lay == 1, st(stream), "bn_bwd_apply");
+}
+
+}  // extern "C"

@@ -1,0 +1,97 @@
+// Shared internals of libomt_b200.so: error reporting, launch accounting, small device helpers.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include "../../include/omt_b200.h"
+
+namespace omt {
+
+// ---- errors (thread-local message, sticky async flag) ----
+void set_error(const char* fmt, ...);
+int cuda_fail(cudaError_t e, const char* what);  // records the message, returns OMT_ECUDA
+void note_launch(const char* kernel);             // bumps the launch counter and the per-kernel count
+int check_launch(const char* kernel);             // note_launch + cudaGetLastError
+
+#define OMT_CUDA(call)                                          \
+  do {                                                          \
+    cudaError_t e_ = (call);                                    \
+    if (e_ != cudaSuccess) return ::omt::cuda_fail(e_, #call);  \
+  } while (0)
+
+#define OMT_REQUIRE(cond, ...)       \
+  do {                               \
+    if (!(cond)) {                   \
+      ::omt::set_error(__VA_ARGS__); \
+      return OMT_EINVAL;             \
+    }                                \
+  } while (0)
+
+inline cudaStream_t st(omt_stream_t s) { return (cudaStream_t)s; }
+inline int64_t cdiv(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+int sm_count();  // SMs of the current device (148 on B200)
+
+// Scratch from the library's own caching allocator, returned to the pool when the guard dies. The pool is
+// stream-ordered: a block freed right after the launch is only handed to later work on the same stream.
+struct Scratch {
+  void* p = nullptr;
+  bool owned = false;
+  int get(void* user, size_t user_bytes, size_t need, omt_stream_t s) {
+    if (need == 0) return OMT_OK;
+    if (user) {
+      if (user_bytes < need) {
+        set_error("workspace too small: %zu < %zu bytes", user_bytes, need);
+        return OMT_EWORKSPACE;
+      }
+      p = user;
+      return OMT_OK;
+    }
+    p = omt_malloc(need, s);
+    if (!p) return OMT_ENOMEM;
+    owned = true;
+    return OMT_OK;
+  }
+  ~Scratch() {
+    if (owned) omt_free(p);
+  }
+};
+
+// ---- device helpers ----
+struct ActView {  // OmtAct by value for kernels
+  float* p;
+  int64_t sn, sc, sh, sw;
+  __host__ __device__ int64_t off(int n, int c, int h, int w) const { return n * sn + c * sc + h * sh + w * sw; }
+};
+inline ActView view(const OmtAct* a) { return ActView{a->p, a->sn, a->sc, a->sh, a->sw}; }
+inline bool is_nchw(const OmtAct* a, int c, int h, int w) {
+  return a->sw == 1 && a->sh == w && a->sc == (int64_t)h * w && a->sn == (int64_t)c * h * w;
+}
+inline bool is_nhwc(const OmtAct* a, int c, int h, int w) {
+  return a->sc == 1 && a->sw == c && a->sh == (int64_t)w * c && a->sn == (int64_t)h * w * c;
+}
+
+#ifdef __CUDACC__
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+// Sum over a block of up to 1024 threads; result valid in every thread. `red` holds 32 floats of shared memory.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (lane == 0) red[wid] = v;
+  __syncthreads();
+  float r = lane < nw ? red[lane] : 0.f;
+  r = warp_sum(r);
+  return r;
+}
+#endif
+
+}  // namespace omt

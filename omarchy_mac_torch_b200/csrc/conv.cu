@@ -1,0 +1,175 @@
+// Dense convolution entry points: argument checks (the reference's conv_kind / NEED rules, csrc/conv.cpp:167-183),
+// path selection (tcgen05 tensor-core kernels when the geometry and layout allow, exact-fp32 CUDA-core kernels
+// otherwise), workspace handling, and two small copy helpers.
+#include <algorithm>
+
+#include "common.cuh"
+
+namespace omt {
+
+// conv_simt.cu
+int simt_conv_fwd(const OmtConvGeo* g, const OmtAct* x, const float* w, const float* bias, const OmtAct* y, uint32_t flags,
+                  cudaStream_t s);
+int simt_conv_dgrad(const OmtConvGeo* g, const OmtAct* gy, const float* w, const OmtAct* dx, cudaStream_t s);
+int simt_conv_wgrad(const OmtConvGeo* g, const OmtAct* x, const OmtAct* gy, float* dw, float scale, float* part, cudaStream_t s);
+size_t simt_wgrad_workspace(const OmtConvGeo* g);
+// conv_tc.cu
+bool tc_supported(int kind, const OmtConvGeo* g, const OmtAct* a, const OmtAct* b);
+size_t tc_workspace(int kind, const OmtConvGeo* g);
+int tc_conv_fwd(const OmtConvGeo* g, const OmtAct* x, const float* w, const float* bias, const OmtAct* y, float* stats,
+                uint32_t flags, void* ws, cudaStream_t s);
+int tc_conv_dgrad(const OmtConvGeo* g, const OmtAct* gy, const float* w, const OmtAct* dx, void* ws, cudaStream_t s);
+int tc_conv_wgrad(const OmtConvGeo* g, const OmtAct* x, const OmtAct* gy, float* dw, float scale, void* ws, cudaStream_t s);
+
+static int check_dense(const OmtConvGeo* g, const char* who) {
+  OMT_REQUIRE(g != nullptr, "%s: null geometry", who);
+  OMT_REQUIRE(g->groups == 1, "%s: groups must be 1 (use omt_dw_* for depthwise)", who);
+  OMT_REQUIRE(g->n > 0 && g->ci > 0 && g->co > 0 && g->ih > 0 && g->iw > 0, "%s: empty tensor", who);
+  OMT_REQUIRE(g->ks >= 1 && g->ks <= 11 && g->stride >= 1 && g->stride <= 4 && g->pad >= 0 && g->pad <= g->ks,
+              "%s: needs ks<=11, stride 1..4, pad<=ks (got ks=%d stride=%d pad=%d)", who, g->ks, g->stride, g->pad);
+  OMT_REQUIRE(g->oh == (g->ih + 2 * g->pad - g->ks) / g->stride + 1 && g->ow == (g->iw + 2 * g->pad - g->ks) / g->stride + 1 &&
+                  g->oh > 0 && g->ow > 0,
+              "%s: output size does not match the geometry", who);
+  OMT_REQUIRE((int64_t)g->n * g->oh * g->ow < (1ll << 31) && (int64_t)g->n * g->ih * g->iw < (1ll << 31) &&
+                  (int64_t)g->co * g->ci * g->ks * g->ks < (1ll << 31),
+              "%s: GEMM extent exceeds 2^31", who);
+  return OMT_OK;
+}
+
+__global__ void __launch_bounds__(256) scale_copy_kernel(float* __restrict__ dst, const float* __restrict__ src, int64_t n, float scale) {
+  int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i + 3 < n) {
+    float4 v = __ldg(reinterpret_cast<const float4*>(src + i));
+    *reinterpret_cast<float4*>(dst + i) = make_float4(v.x * scale, v.y * scale, v.z * scale, v.w * scale);
+  } else {
+    for (; i < n; i++) dst[i] = src[i] * scale;
+  }
+}
+__global__ void __launch_bounds__(256) scale_copy_scalar_kernel(float* __restrict__ dst, const float* __restrict__ src, int64_t n, float scale) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) dst[i] = src[i] * scale;
+}
+
+// Layout change through a 32x32 shared tile: reads coalesced along the source's fast axis, writes along the
+// destination's. View both tensors as [n][c][hw]; one of (c, hw) is contiguous in each.
+__global__ void __launch_bounds__(256) transpose_kernel(const float* __restrict__ src, float* __restrict__ dst, int c, int hw,
+                                                        bool src_c_fast) {
+  __shared__ float tile[32][33];
+  const int img = blockIdx.z;
+  const int c0 = blockIdx.y * 32, p0 = blockIdx.x * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+  const int64_t base = (int64_t)img * c * hw;
+  if (src_c_fast) {  // src [hw][c] -> dst [c][hw]
+    for (int j = ty; j < 32; j += 8) {
+      int p = p0 + j, ch = c0 + tx;
+      if (p < hw && ch < c) tile[j][tx] = __ldg(src + base + (int64_t)p * c + ch);
+    }
+    __syncthreads();
+    for (int j = ty; j < 32; j += 8) {
+      int ch = c0 + j, p = p0 + tx;
+      if (p < hw && ch < c) dst[base + (int64_t)ch * hw + p] = tile[tx][j];
+    }
+  } else {  // src [c][hw] -> dst [hw][c]
+    for (int j = ty; j < 32; j += 8) {
+      int ch = c0 + j, p = p0 + tx;
+      if (p < hw && ch < c) tile[j][tx] = __ldg(src + base + (int64_t)ch * hw + p);
+    }
+    __syncthreads();
+    for (int j = ty; j < 32; j += 8) {
+      int p = p0 + j, ch = c0 + tx;
+      if (p < hw && ch < c) dst[base + (int64_t)p * c + ch] = tile[tx][j];
+    }
+  }
+}
+__global__ void __launch_bounds__(256) strided_copy_kernel(ActView src, ActView dst, int n, int c, int h, int w) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (int64_t)n * c * h * w) return;
+  int x = (int)(i % w); i /= w;
+  int y = (int)(i % h); i /= h;
+  int ch = (int)(i % c), img = (int)(i / c);
+  dst.p[dst.off(img, ch, y, x)] = __ldg(src.p + src.off(img, ch, y, x));
+}
+
+}  // namespace omt
+
+using namespace omt;
+
+extern "C" {
+
+size_t omt_conv_workspace_bytes(int kind, const OmtConvGeo* g, uint32_t flags) {
+  if (!g || g->groups != 1) return 0;
+  size_t simt = kind == 2 ? simt_wgrad_workspace(g) : 0;
+  if (flags & OMT_FORCE_SIMT) return simt;
+  return std::max(simt, tc_workspace(kind, g));
+}
+
+int omt_conv_fwd(const OmtConvGeo* g, const OmtAct* x, const float* w, const float* bias, const OmtAct* y, float* stats,
+                 uint32_t flags, void* workspace, size_t workspace_bytes, omt_stream_t stream) {
+  int r = check_dense(g, "omt_conv_fwd");
+  if (r) return r;
+  OMT_REQUIRE(x && y && x->p && y->p && w, "omt_conv_fwd: null pointer");
+  OMT_REQUIRE(!(flags & OMT_EPI_BIAS) || bias, "omt_conv_fwd: OMT_EPI_BIAS without a bias pointer");
+  OMT_REQUIRE(!(flags & OMT_EPI_BNSTATS) || stats, "omt_conv_fwd: OMT_EPI_BNSTATS without a stats pointer");
+  bool tc = !(flags & OMT_FORCE_SIMT) && tc_supported(0, g, x, y);
+  OMT_REQUIRE(tc || !(flags & OMT_FORCE_TC), "omt_conv_fwd: geometry/layout not covered by the tensor-core path");
+  OMT_REQUIRE(tc || !(flags & OMT_EPI_BNSTATS), "omt_conv_fwd: OMT_EPI_BNSTATS needs the tensor-core path");
+  if (!tc) return simt_conv_fwd(g, x, w, bias, y, flags, st(stream));
+  Scratch sc;
+  r = sc.get(workspace, workspace_bytes, tc_workspace(0, g), stream);
+  if (r) return r;
+  return tc_conv_fwd(g, x, w, bias, y, stats, flags, sc.p, st(stream));
+}
+
+int omt_conv_dgrad(const OmtConvGeo* g, const OmtAct* gy, const float* w, const OmtAct* dx, uint32_t flags, void* workspace,
+                   size_t workspace_bytes, omt_stream_t stream) {
+  int r = check_dense(g, "omt_conv_dgrad");
+  if (r) return r;
+  OMT_REQUIRE(gy && dx && gy->p && dx->p && w, "omt_conv_dgrad: null pointer");
+  bool tc = !(flags & OMT_FORCE_SIMT) && tc_supported(1, g, gy, dx);
+  OMT_REQUIRE(tc || !(flags & OMT_FORCE_TC), "omt_conv_dgrad: geometry/layout not covered by the tensor-core path");
+  if (!tc) return simt_conv_dgrad(g, gy, w, dx, st(stream));
+  Scratch sc;
+  r = sc.get(workspace, workspace_bytes, tc_workspace(1, g), stream);
+  if (r) return r;
+  return tc_conv_dgrad(g, gy, w, dx, sc.p, st(stream));
+}
+
+int omt_conv_wgrad(const OmtConvGeo* g, const OmtAct* x, const OmtAct* gy, float* dw, float scale, uint32_t flags, void* workspace,
+                   size_t workspace_bytes, omt_stream_t stream) {
+  int r = check_dense(g, "omt_conv_wgrad");
+  if (r) return r;
+  OMT_REQUIRE(x && gy && x->p && gy->p && dw, "omt_conv_wgrad: null pointer");
+  bool tc = !(flags & OMT_FORCE_SIMT) && tc_supported(2, g, x, gy);
+  OMT_REQUIRE(tc || !(flags & OMT_FORCE_TC), "omt_conv_wgrad: geometry/layout not covered by the tensor-core path");
+  Scratch sc;
+  r = sc.get(workspace, workspace_bytes, tc ? tc_workspace(2, g) : simt_wgrad_workspace(g), stream);
+  if (r) return r;
+  if (tc) return tc_conv_wgrad(g, x, gy, dw, scale, sc.p, st(stream));
+  return simt_conv_wgrad(g, x, gy, dw, scale, (float*)sc.p, st(stream));
+}
+
+int omt_scale_copy(float* dst, const float* src, int64_t n, float scale, omt_stream_t stream) {
+  OMT_REQUIRE(dst && src && n >= 0, "omt_scale_copy: bad arguments");
+  if (n == 0) return OMT_OK;
+  if (((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src)) & 15) == 0)
+    scale_copy_kernel<<<(unsigned)cdiv(cdiv(n, 4), 256), 256, 0, st(stream)>>>(dst, src, n, scale);
+  else
+    scale_copy_scalar_kernel<<<(unsigned)cdiv(n, 256), 256, 0, st(stream)>>>(dst, src, n, scale);
+  return check_launch("scale_copy");
+}
+
+int omt_act_copy(const OmtAct* src, const OmtAct* dst, int32_t n, int32_t c, int32_t h, int32_t w, omt_stream_t stream) {
+  OMT_REQUIRE(src && dst && src->p && dst->p && n > 0 && c > 0 && h > 0 && w > 0, "omt_act_copy: bad arguments");
+  bool s_nchw = is_nchw(src, c, h, w), s_nhwc = is_nhwc(src, c, h, w), d_nchw = is_nchw(dst, c, h, w), d_nhwc = is_nhwc(dst, c, h, w);
+  int64_t total = (int64_t)n * c * h * w;
+  if ((s_nchw && d_nchw) || (s_nhwc && d_nhwc)) return omt_memcpy_d2d(dst->p, src->p, total * sizeof(float), stream);
+  if (((s_nchw && d_nhwc) || (s_nhwc && d_nchw)) && n <= 65535) {
+    dim3 grid((unsigned)cdiv(h * w, 32), (unsigned)cdiv(c, 32), n);
+    transpose_kernel<<<grid, 256, 0, st(stream)>>>(src->p, dst->p, c, h * w, s_nhwc);
+    return check_launch("act_transpose");
+  }
+  strided_copy_kernel<<<(unsigned)cdiv(total, 256), 256, 0, st(stream)>>>(view(src), view(dst), n, c, h, w);
+  return check_launch("act_strided_copy");
+}
+
+}  // extern "C"

@@ -1,0 +1,335 @@
+// Pooling kernels: the plan's 2x2 max / average pools and global average pool, and the general aten pools.
+// All HBM-bound, one thread per output (forward) or per input (backward gather), indexed in memory order of the
+// written tensor so stores coalesce for both NCHW and channels-last.
+//
+// Semantics: pool_fwd.wgsl:15-21 / pool_bwd.wgsl:14-21 (index 0..3, first maximum wins), avgpool_fwd/bwd.wgsl,
+// gap_fwd/bwd.wgsl, maxpool_gen_fwd.wgsl:16-28 (int64 flat index, NaN propagates) / maxpool_gen_bwd.wgsl,
+// avgpool_gen_fwd/bwd.wgsl (aten divisor rules), adapool_fwd/bwd.wgsl; host side csrc/nn.cpp:137-222 and
+// csrc/plans.cpp:188-213.
+#include "common.cuh"
+
+namespace omt {
+
+template <bool NHWC>
+__device__ __forceinline__ void decode4(int64_t i, int c, int h, int w, int& img, int& ch, int& y, int& x) {
+  if (NHWC) {
+    ch = (int)(i % c); i /= c;
+    x = (int)(i % w); i /= w;
+    y = (int)(i % h); img = (int)(i / h);
+  } else {
+    x = (int)(i % w); i /= w;
+    y = (int)(i % h); i /= h;
+    ch = (int)(i % c); img = (int)(i / c);
+  }
+}
+
+// ---- 2x2 stride-2 max pool with 2-bit argmax ----
+template <bool NHWC>
+__global__ void __launch_bounds__(256) pool2_fwd_kernel(ActView x, ActView y, uint8_t* idx, int n, int c, int oh, int ow) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (int64_t)n * c * oh * ow) return;
+  int img, ch, oy, ox;
+  decode4<NHWC>(i, c, oh, ow, img, ch, oy, ox);
+  const float* p = x.p + x.off(img, ch, 2 * oy, 2 * ox);
+  float best = __ldg(p);
+  int bi = 0;
+  float v1 = __ldg(p + x.sw); if (v1 > best) { best = v1; bi = 1; }
+  float v2 = __ldg(p + x.sh); if (v2 > best) { best = v2; bi = 2; }
+  float v3 = __ldg(p + x.sh + x.sw); if (v3 > best) { best = v3; bi = 3; }
+  int64_t o = y.off(img, ch, oy, ox);
+  y.p[o] = best;
+  idx[o] = (uint8_t)bi;
+}
+template <bool NHWC>
+__global__ void __launch_bounds__(256) pool2_bwd_kernel(ActView g, const uint8_t* idx, ActView gx, int n, int c, int h, int w,
+                                                        int oh, int ow) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (int64_t)n * c * h * w) return;
+  int img, ch, yy, xx;
+  decode4<NHWC>(i, c, h, w, img, ch, yy, xx);
+  int oy = yy >> 1, ox = xx >> 1;
+  float v = 0.f;
+  if (oy < oh && ox < ow) {
+    int64_t o = g.off(img, ch, oy, ox);
+    if (idx[o] == (uint8_t)((yy & 1) * 2 + (xx & 1))) v = __ldg(g.p + o);
+  }
+  gx.p[gx.off(img, ch, yy, xx)] = v;
+}
+template <bool NHWC>
+__global__ void __launch_bounds__(256) avgpool2_fwd_kernel(ActView x, ActView y, int n, int c, int oh, int ow) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (int64_t)n * c * oh * ow) return;
+  int img, ch, oy, ox;
+  decode4<NHWC>(i, c, oh, ow, img, ch, oy, ox);
+  const float* p = x.p + x.off(img, ch, 2 * oy, 2 * ox);
+  y.p[y.off(img, ch, oy, ox)] = (__ldg(p) + __ldg(p + x.sw) + __ldg(p + x.sh) + __ldg(p + x.sh + x.sw)) * 0.25f;
+}
+template <bool NHWC>
+__global__ void __launch_bounds__(256) avgpool2_bwd_kernel(ActView g, ActView gx, int n, int c, int h, int w, int oh, int ow) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (int64_t)n * c * h * w) return;
+  int img, ch, yy, xx;
+  decode4<NHWC>(i, c, h, w, img, ch, yy, xx);
+  int oy = yy >> 1, ox = xx >> 1;
+  gx.p[gx.off(img, ch, yy, xx)] = (oy < oh && ox < ow) ? __ldg(g.p + g.off(img, ch, oy, ox)) * 0.25f : 0.f;
+}
+
+// ---- general max pool ----
+struct PoolArgs {
+  ActView x, y;
+  int n, c, ih, iw, oh, ow;
+  OmtPool p;
+  int include_pad, divisor;
+};
+__device__ __forceinline__ bool isnan_bits(float v) { return (__float_as_uint(v) & 0x7fffffffu) > 0x7f800000u; }
+
+template <bool NHWC>
+__global__ void __launch_bounds__(256) maxpool_fwd_kernel(PoolArgs a, int64_t* idx) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (int64_t)a.n * a.c * a.oh * a.ow) return;
+  int img, ch, oy, ox;
+  decode4<NHWC>(i, a.c, a.oh, a.ow, img, ch, oy, ox);
+  const float* xp = a.x.p + img * a.x.sn + ch * a.x.sc;
+  float best = -INFINITY;
+  int bi = -1;
+  bool done = false;
+  for (int ky = 0; ky < a.p.kh && !done; ky++) {
+    int y = oy * a.p.sh + ky * a.p.dh - a.p.ph;
+    if (y < 0 || y >= a.ih) continue;
+    for (int kx = 0; kx < a.p.kw; kx++) {
+      int xx = ox * a.p.sw + kx * a.p.dw - a.p.pw;
+      if (xx < 0 || xx >= a.iw) continue;
+      float v = __ldg(xp + y * a.x.sh + xx * a.x.sw);
+      bool nan = isnan_bits(v);
+      if (bi < 0 || nan || v > best) {
+        best = v; bi = y * a.iw + xx;
+        if (nan) { done = true; break; }
+      }
+    }
+  }
+  int64_t o = a.y.off(img, ch, oy, ox);
+  a.y.p[o] = best;
+  idx[o] = bi;
+}
+template <bool NHWC>
+__global__ void __launch_bounds__(256) maxpool_bwd_kernel(PoolArgs a, const int64_t* idx) {
+  // a.x = gy (strides of the forward output), a.y = gx
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (int64_t)a.n * a.c * a.ih * a.iw) return;
+  int img, ch, y, xx;
+  decode4<NHWC>(i, a.c, a.ih, a.iw, img, ch, y, xx);
+  // outputs whose window can contain (y, xx)
+  int ylo = max(0, (y + a.p.ph - (a.p.kh - 1) * a.p.dh + a.p.sh - 1) / a.p.sh), yhi = min(a.oh - 1, (y + a.p.ph) / a.p.sh);
+  int xlo = max(0, (xx + a.p.pw - (a.p.kw - 1) * a.p.dw + a.p.sw - 1) / a.p.sw), xhi = min(a.ow - 1, (xx + a.p.pw) / a.p.sw);
+  int64_t me = (int64_t)y * a.iw + xx;
+  float acc = 0.f;
+  for (int oy = ylo; oy <= yhi; oy++)
+    for (int ox = xlo; ox <= xhi; ox++) {
+      int64_t o = a.x.off(img, ch, oy, ox);
+      if (idx[o] == me) acc += __ldg(a.x.p + o);
+    }
+  a.y.p[a.y.off(img, ch, y, xx)] = acc;
+}
+
+// ---- general average pool (aten divisor rules) ----
+__device__ __forceinline__ float avg_div(const PoolArgs& a, int oy, int ox) {
+  if (a.divisor) return (float)a.divisor;
+  int hs = oy * a.p.sh - a.p.ph, ws = ox * a.p.sw - a.p.pw;
+  int he = min(hs + a.p.kh, a.ih + a.p.ph), we = min(ws + a.p.kw, a.iw + a.p.pw);
+  int pool = (he - hs) * (we - ws);
+  if (a.include_pad) return (float)pool;
+  hs = max(hs, 0); ws = max(ws, 0);
+  he = min(he, a.ih); we = min(we, a.iw);
+  return (float)((he - hs) * (we - ws));
+}
+template <bool NHWC>
+__global__ void __launch_bounds__(256) avgpool_fwd_kernel(PoolArgs a) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (int64_t)a.n * a.c * a.oh * a.ow) return;
+  int img, ch, oy, ox;
+  decode4<NHWC>(i, a.c, a.oh, a.ow, img, ch, oy, ox);
+  const float* xp = a.x.p + img * a.x.sn + ch * a.x.sc;
+  float s = 0.f;
+  for (int ky = 0; ky < a.p.kh; ky++) {
+    int y = oy * a.p.sh + ky - a.p.ph;
+    if (y < 0 || y >= a.ih) continue;
+    for (int kx = 0; kx < a.p.kw; kx++) {
+      int xx = ox * a.p.sw + kx - a.p.pw;
+      if (xx < 0 || xx >= a.iw) continue;
+      s += __ldg(xp + y * a.x.sh + xx * a.x.sw);
+    }
+  }
+  a.y.p[a.y.off(img, ch, oy, ox)] = s / avg_div(a, oy, ox);
+}
+template <bool NHWC>
+__global__ void __launch_bounds__(256) avgpool_bwd_kernel(PoolArgs a) {  // a.x = gy, a.y = gx
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (int64_t)a.n * a.c * a.ih * a.iw) return;
+  int img, ch, y, xx;
+  decode4<NHWC>(i, a.c, a.ih, a.iw, img, ch, y, xx);
+  int ylo = max(0, (y + a.p.ph - (a.p.kh - 1) + a.p.sh - 1) / a.p.sh), yhi = min(a.oh - 1, (y + a.p.ph) / a.p.sh);
+  int xlo = max(0, (xx + a.p.pw - (a.p.kw - 1) + a.p.sw - 1) / a.p.sw), xhi = min(a.ow - 1, (xx + a.p.pw) / a.p.sw);
+  float acc = 0.f;
+  for (int oy = ylo; oy <= yhi; oy++)
+    for (int ox = xlo; ox <= xhi; ox++) acc += __ldg(a.x.p + a.x.off(img, ch, oy, ox)) / avg_div(a, oy, ox);
+  a.y.p[a.y.off(img, ch, y, xx)] = acc;
+}
+
+// ---- adaptive average pool: window [floor(o*I/O), ceil((o+1)*I/O)) ----
+__device__ __forceinline__ int ad_start(int o, int I, int O) { return (int)(((int64_t)o * I) / O); }
+__device__ __forceinline__ int ad_end(int o, int I, int O) { return (int)((((int64_t)o + 1) * I + O - 1) / O); }
+template <bool NHWC>
+__global__ void __launch_bounds__(256) adapool_fwd_kernel(PoolArgs a) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (int64_t)a.n * a.c * a.oh * a.ow) return;
+  int img, ch, oy, ox;
+  decode4<NHWC>(i, a.c, a.oh, a.ow, img, ch, oy, ox);
+  int y0 = ad_start(oy, a.ih, a.oh), y1 = ad_end(oy, a.ih, a.oh), x0 = ad_start(ox, a.iw, a.ow), x1 = ad_end(ox, a.iw, a.ow);
+  const float* xp = a.x.p + img * a.x.sn + ch * a.x.sc;
+  float s = 0.f;
+  for (int y = y0; y < y1; y++)
+    for (int xx = x0; xx < x1; xx++) s += __ldg(xp + y * a.x.sh + xx * a.x.sw);
+  a.y.p[a.y.off(img, ch, oy, ox)] = s / (float)((y1 - y0) * (x1 - x0));
+}
+// global average pool over an NCHW plane: one warp per (n, c) plane, coalesced, shuffle-reduced
+__global__ void __launch_bounds__(256) gap_nchw_kernel(const float* __restrict__ x, float* __restrict__ y, int64_t planes, int hw) {
+  int64_t pl = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  int lane = threadIdx.x & 31;
+  if (pl >= planes) return;
+  const float* p = x + pl * hw;
+  float s = 0.f;
+  for (int e = lane; e < hw; e += 32) s += __ldg(p + e);
+  s = warp_sum(s);
+  if (lane == 0) y[pl] = s / (float)hw;
+}
+template <bool NHWC>
+__global__ void __launch_bounds__(256) adapool_bwd_kernel(PoolArgs a) {  // a.x = gy, a.y = gx
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (int64_t)a.n * a.c * a.ih * a.iw) return;
+  int img, ch, y, xx;
+  decode4<NHWC>(i, a.c, a.ih, a.iw, img, ch, y, xx);
+  // outputs o with start(o) <= y < end(o)
+  int oy0 = (int)(((int64_t)y * a.oh) / a.ih), ox0 = (int)(((int64_t)xx * a.ow) / a.iw);
+  float acc = 0.f;
+  for (int oy = max(0, oy0 - 1); oy < a.oh && ad_start(oy, a.ih, a.oh) <= y; oy++) {
+    if (ad_end(oy, a.ih, a.oh) <= y) continue;
+    int hy = ad_end(oy, a.ih, a.oh) - ad_start(oy, a.ih, a.oh);
+    for (int ox = max(0, ox0 - 1); ox < a.ow && ad_start(ox, a.iw, a.ow) <= xx; ox++) {
+      if (ad_end(ox, a.iw, a.ow) <= xx) continue;
+      int wx = ad_end(ox, a.iw, a.ow) - ad_start(ox, a.iw, a.ow);
+      acc += __ldg(a.x.p + a.x.off(img, ch, oy, ox)) / (float)(hy * wx);
+    }
+  }
+  a.y.p[a.y.off(img, ch, y, xx)] = acc;
+}
+
+static bool chan_last(const OmtAct* a) { return a->sc == 1 && a->sw != 1; }
+static int pool_check(const OmtPool* p, const char* who) {
+  OMT_REQUIRE(p && p->kh > 0 && p->kw > 0 && p->sh > 0 && p->sw > 0 && p->ph >= 0 && p->pw >= 0 && p->ph <= p->kh / 2 &&
+                  p->pw <= p->kw / 2 && p->dh >= 1 && p->dw >= 1,
+              "%s: window/stride must be positive and padding <= kernel/2", who);
+  return OMT_OK;
+}
+
+#define LAUNCH_BY_LAYOUT(kern, nhwc, total, s, ...)                                      \
+  do {                                                                                   \
+    unsigned blocks_ = (unsigned)cdiv((total), 256);                                     \
+    if (nhwc) kern<true><<<blocks_, 256, 0, (s)>>>(__VA_ARGS__);                          \
+    else kern<false><<<blocks_, 256, 0, (s)>>>(__VA_ARGS__);                              \
+  } while (0)
+
+}  // namespace omt
+
+using namespace omt;
+
+extern "C" {
+
+int omt_pool2_fwd(const OmtAct* x, const OmtAct* y, uint8_t* idx, int32_t n, int32_t c, int32_t h, int32_t w, omt_stream_t stream) {
+  OMT_REQUIRE(x && y && x->p && y->p && idx && n > 0 && c > 0 && h >= 2 && w >= 2, "omt_pool2_fwd: bad arguments");
+  int oh = h / 2, ow = w / 2;
+  LAUNCH_BY_LAYOUT(pool2_fwd_kernel, chan_last(y), (int64_t)n * c * oh * ow, st(stream), view(x), view(y), idx, n, c, oh, ow);
+  return check_launch("pool2_fwd");
+}
+int omt_pool2_bwd(const OmtAct* gy, const uint8_t* idx, const OmtAct* gx, int32_t n, int32_t c, int32_t h, int32_t w,
+                  omt_stream_t stream) {
+  OMT_REQUIRE(gy && gx && gy->p && gx->p && idx && n > 0 && c > 0 && h >= 2 && w >= 2, "omt_pool2_bwd: bad arguments");
+  LAUNCH_BY_LAYOUT(pool2_bwd_kernel, chan_last(gx), (int64_t)n * c * h * w, st(stream), view(gy), idx, view(gx), n, c, h, w, h / 2,
+                   w / 2);
+  return check_launch("pool2_bwd");
+}
+int omt_avgpool2_fwd(const OmtAct* x, const OmtAct* y, int32_t n, int32_t c, int32_t h, int32_t w, omt_stream_t stream) {
+  OMT_REQUIRE(x && y && x->p && y->p && n > 0 && c > 0 && h >= 2 && w >= 2, "omt_avgpool2_fwd: bad arguments");
+  LAUNCH_BY_LAYOUT(avgpool2_fwd_kernel, chan_last(y), (int64_t)n * c * (h / 2) * (w / 2), st(stream), view(x), view(y), n, c, h / 2,
+                   w / 2);
+  return check_launch("avgpool2_fwd");
+}
+int omt_avgpool2_bwd(const OmtAct* gy, const OmtAct* gx, int32_t n, int32_t c, int32_t h, int32_t w, omt_stream_t stream) {
+  OMT_REQUIRE(gy && gx && gy->p && gx->p && n > 0 && c > 0 && h >= 2 && w >= 2, "omt_avgpool2_bwd: bad arguments");
+  LAUNCH_BY_LAYOUT(avgpool2_bwd_kernel, chan_last(gx), (int64_t)n * c * h * w, st(stream), view(gy), view(gx), n, c, h, w, h / 2,
+                   w / 2);
+  return check_launch("avgpool2_bwd");
+}
+
+static PoolArgs pa(const OmtAct* x, const OmtAct* y, int n, int c, int ih, int iw, int oh, int ow, const OmtPool* p, int inc, int div) {
+  PoolArgs a{};
+  a.x = view(x); a.y = view(y); a.n = n; a.c = c; a.ih = ih; a.iw = iw; a.oh = oh; a.ow = ow;
+  if (p) a.p = *p;
+  a.include_pad = inc; a.divisor = div;
+  return a;
+}
+
+int omt_maxpool_fwd(const OmtAct* x, const OmtAct* y, int64_t* idx, int32_t n, int32_t c, int32_t ih, int32_t iw, int32_t oh,
+                    int32_t ow, const OmtPool* p, omt_stream_t stream) {
+  int r = pool_check(p, "omt_maxpool_fwd");
+  if (r) return r;
+  OMT_REQUIRE(x && y && x->p && y->p && idx && n > 0 && c > 0 && oh > 0 && ow > 0, "omt_maxpool_fwd: bad arguments");
+  LAUNCH_BY_LAYOUT(maxpool_fwd_kernel, chan_last(y), (int64_t)n * c * oh * ow, st(stream), pa(x, y, n, c, ih, iw, oh, ow, p, 0, 0), idx);
+  return check_launch("maxpool_fwd");
+}
+int omt_maxpool_bwd(const OmtAct* gy, const int64_t* idx, const OmtAct* gx, int32_t n, int32_t c, int32_t ih, int32_t iw,
+                    int32_t oh, int32_t ow, const OmtPool* p, omt_stream_t stream) {
+  int r = pool_check(p, "omt_maxpool_bwd");
+  if (r) return r;
+  OMT_REQUIRE(gy && gx && gy->p && gx->p && idx && n > 0 && c > 0 && oh > 0 && ow > 0, "omt_maxpool_bwd: bad arguments");
+  LAUNCH_BY_LAYOUT(maxpool_bwd_kernel, chan_last(gx), (int64_t)n * c * ih * iw, st(stream), pa(gy, gx, n, c, ih, iw, oh, ow, p, 0, 0),
+                   idx);
+  return check_launch("maxpool_bwd");
+}
+int omt_avgpool_fwd(const OmtAct* x, const OmtAct* y, int32_t n, int32_t c, int32_t ih, int32_t iw, int32_t oh, int32_t ow,
+                    const OmtPool* p, int32_t count_include_pad, int32_t divisor, omt_stream_t stream) {
+  int r = pool_check(p, "omt_avgpool_fwd");
+  if (r) return r;
+  OMT_REQUIRE(x && y && x->p && y->p && n > 0 && c > 0 && oh > 0 && ow > 0 && divisor >= 0, "omt_avgpool_fwd: bad arguments");
+  LAUNCH_BY_LAYOUT(avgpool_fwd_kernel, chan_last(y), (int64_t)n * c * oh * ow, st(stream),
+                   pa(x, y, n, c, ih, iw, oh, ow, p, count_include_pad, divisor));
+  return check_launch("avgpool_fwd");
+}
+int omt_avgpool_bwd(const OmtAct* gy, const OmtAct* gx, int32_t n, int32_t c, int32_t ih, int32_t iw, int32_t oh, int32_t ow,
+                    const OmtPool* p, int32_t count_include_pad, int32_t divisor, omt_stream_t stream) {
+  int r = pool_check(p, "omt_avgpool_bwd");
+  if (r) return r;
+  OMT_REQUIRE(gy && gx && gy->p && gx->p && n > 0 && c > 0 && oh > 0 && ow > 0 && divisor >= 0, "omt_avgpool_bwd: bad arguments");
+  LAUNCH_BY_LAYOUT(avgpool_bwd_kernel, chan_last(gx), (int64_t)n * c * ih * iw, st(stream),
+                   pa(gy, gx, n, c, ih, iw, oh, ow, p, count_include_pad, divisor));
+  return check_launch("avgpool_bwd");
+}
+int omt_adaptive_avgpool_fwd(const OmtAct* x, const OmtAct* y, int32_t n, int32_t c, int32_t ih, int32_t iw, int32_t oh,
+                             int32_t ow, omt_stream_t stream) {
+  OMT_REQUIRE(x && y && x->p && y->p && n > 0 && c > 0 && ih > 0 && iw > 0 && oh > 0 && ow > 0, "omt_adaptive_avgpool_fwd: bad arguments");
+  if (oh == 1 && ow == 1 && is_nchw(x, c, ih, iw) && y->sc == 1 && y->sn == c) {
+    int64_t planes = (int64_t)n * c;
+    gap_nchw_kernel<<<(unsigned)cdiv(planes * 32, 256), 256, 0, st(stream)>>>(x->p, y->p, planes, ih * iw);
+    return check_launch("gap_fwd_nchw");
+  }
+  LAUNCH_BY_LAYOUT(adapool_fwd_kernel, chan_last(y) || (oh == 1 && ow == 1 && chan_last(x)), (int64_t)n * c * oh * ow, st(stream),
+                   pa(x, y, n, c, ih, iw, oh, ow, nullptr, 0, 0));
+  return check_launch("adaptive_avgpool_fwd");
+}
+int omt_adaptive_avgpool_bwd(const OmtAct* gy, const OmtAct* gx, int32_t n, int32_t c, int32_t ih, int32_t iw, int32_t oh,
+                             int32_t ow, omt_stream_t stream) {
+  OMT_REQUIRE(gy && gx && gy->p && gx->p && n > 0 && c > 0 && ih > 0 && iw > 0 && oh > 0 && ow > 0, "omt_adaptive_avgpool_bwd: bad arguments");
+  LAUNCH_BY_LAYOUT(adapool_bwd_kernel, chan_last(gx), (int64_t)n * c * ih * iw, st(stream), pa(gy, gx, n, c, ih, iw, oh, ow, nullptr, 0, 0));
+  return check_launch("adaptive_avgpool_bwd");
+}
+
+}  // extern "C"

@@ -1,0 +1,36 @@
+import json
+import pathlib
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = pathlib.Path(__file__).resolve().parent.parent
+for p in (ROOT, ROOT / "tests" / "golden"):
+    if str(p) not in sys.path:
+        sys.path.insert(0, str(p))
+
+TOL = 1e-4  # max|err| / max|ref| per tensor (the bound BASELINE.json's north_star states)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
+
+
+@pytest.fixture(scope="session")
+def golden():
+    return np.load(ROOT / "tests" / "golden" / "ops.npz")
+
+
+@pytest.fixture(scope="session")
+def golden_losses():
+    return json.loads((ROOT / "tests" / "golden" / "losses.json").read_text())
+
+
+def rel_err(a, ref):
+    a = np.asarray(a, dtype=np.float64)
+    ref = np.asarray(ref, dtype=np.float64)
+    assert a.shape == ref.shape, (a.shape, ref.shape)
+    if ref.size == 0:
+        return 0.0
+    return float(np.abs(a - ref).max() / max(np.abs(ref).max(), 1e-30))

@@ -1,0 +1,312 @@
+"""Parity of the CUDA kernels, called through the C ABI (libomt_b200.so via ctypes), against the golden fixtures
+(aten-CPU outputs on the reference's shape lists) and the CPU oracle. Needs a B200: run with -m gpu."""
+import numpy as np
+import pytest
+import torch
+
+import cases
+import oracle
+from conftest import TOL, rel_err
+
+pytestmark = pytest.mark.gpu
+
+CONV = cases.conv_cases()
+
+
+@pytest.fixture(scope="module")
+def capi():
+    from omarchy_mac_torch_b200 import capi as m
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    m.lib()
+    return m
+
+
+def dev(t, cl=False):
+    if t is None:
+        return None
+    t = torch.as_tensor(t).cuda()
+    return t.contiguous(memory_format=torch.channels_last) if cl else t
+
+
+def host(t):
+    return t.detach().cpu().numpy()
+
+
+@pytest.mark.parametrize("cl", [False, True], ids=["nchw", "nhwc"])
+@pytest.mark.parametrize("name", sorted(CONV))
+def test_conv_golden(capi, golden, name, cl):
+    """Every conv fixture (dense: notes/scripts/conv_kinds_check.py, alexnet_ops_check.py; depthwise incl. general
+    stride/pad) in both layouts, exact-fp32 path."""
+    seed, n, ci, co, ks, s, p, hw, groups, bias = CONV[name]
+    x, w, b, gy = cases.conv_inputs(*CONV[name])
+    xd, wd, bd, gd = dev(x, cl), dev(w), dev(b), dev(gy, cl)
+    if groups == 1:
+        y = capi.conv_fwd(xd, wd, bd, s, p, flags=capi.FORCE_SIMT, cl=cl)
+        dx = capi.conv_dgrad(gd, wd, (hw, hw), s, p, flags=capi.FORCE_SIMT, cl=cl)
+        dw = capi.conv_wgrad(xd, gd, ks, s, p, flags=capi.FORCE_SIMT)
+    else:
+        y = capi.dw_fwd(xd, wd, bd, s, p, cl=cl)
+        dx = capi.dw_dgrad(gd, wd, (hw, hw), s, p, cl=cl)
+        dw = capi.dw_wgrad(xd, gd, ks, s, p)
+    assert rel_err(host(y), golden[f"{name}_y"]) <= TOL
+    assert rel_err(host(dx), golden[f"{name}_dx"]) <= TOL
+    assert rel_err(host(dw), golden[f"{name}_dw"]) <= TOL
+    if bias:
+        assert rel_err(host(capi.conv_bias_grad(gd)), golden[f"{name}_db"]) <= TOL
+
+
+def test_conv_default_path_matches_golden(capi, golden):
+    """Without OMT_FORCE_SIMT the library picks its own path (tensor cores where supported); results must still hold."""
+    for name in sorted(CONV):
+        seed, n, ci, co, ks, s, p, hw, groups, bias = CONV[name]
+        if groups != 1:
+            continue
+        x, w, b, gy = cases.conv_inputs(*CONV[name])
+        for cl in (False, True):
+            xd, wd, bd, gd = dev(x, cl), dev(w), dev(b), dev(gy, cl)
+            assert rel_err(host(capi.conv_fwd(xd, wd, bd, s, p, cl=cl)), golden[f"{name}_y"]) <= TOL
+            assert rel_err(host(capi.conv_dgrad(gd, wd, (hw, hw), s, p, cl=cl)), golden[f"{name}_dx"]) <= TOL
+            assert rel_err(host(capi.conv_wgrad(xd, gd, ks, s, p)), golden[f"{name}_dw"]) <= TOL
+
+
+def test_conv_epilogues_and_scale(capi):
+    rng = np.random.default_rng(11)
+    x = rng.standard_normal((2, 5, 10, 9)).astype(np.float32)
+    w = rng.standard_normal((7, 5, 3, 3)).astype(np.float32)
+    b = rng.standard_normal(7).astype(np.float32)
+    y = capi.conv_fwd(dev(x), dev(w), dev(b), 1, 1, flags=capi.EPI_RELU | capi.FORCE_SIMT)
+    assert rel_err(host(y), oracle.c.conv_fwd(x, w, b, 1, 1, relu=True)) <= TOL
+    gy = rng.standard_normal((2, 7, 10, 9)).astype(np.float32)
+    dw = capi.conv_wgrad(dev(x), dev(gy), 3, 1, 1, flags=capi.FORCE_SIMT, scale=0.25)
+    assert rel_err(host(dw), 0.25 * oracle.c.conv_wgrad(x, gy, 3, 1, 1)) <= TOL
+    # K = 0 stride phases: ks=1 stride=2 leaves three of four phases without taps -> zeros
+    w1 = rng.standard_normal((7, 5, 1, 1)).astype(np.float32)
+    g1 = rng.standard_normal((2, 7, 5, 5)).astype(np.float32)
+    dx = host(capi.conv_dgrad(dev(g1), dev(w1), (10, 9), 2, 0, flags=capi.FORCE_SIMT))
+    ref = oracle.c.conv_dgrad(g1, w1, (10, 9), 2, 0)
+    assert rel_err(dx, ref) <= TOL and np.all(dx[:, :, 1::2, :] == 0)
+
+
+@pytest.mark.parametrize("shape", [(16, 3, 64, 11, 4, 2, 63), (8, 64, 192, 5, 1, 2, 27), (32, 128, 128, 3, 1, 1, 16), (4, 32, 48, 3, 2, 1, 30),
+                                   (2, 256, 64, 1, 1, 0, 14), (3, 16, 300, 3, 1, 1, 7)])
+def test_conv_larger_shapes_vs_aten(capi, shape):
+    """AlexNet / ResNet style shapes (tools/gemm_bench.py:8-9, scaled to keep the CPU side quick) against aten CPU."""
+    n, ci, co, ks, s, p, hw = shape
+    torch.manual_seed(0)
+    x, w = torch.randn(n, ci, hw, hw), torch.randn(co, ci, ks, ks) * 0.05
+    b = torch.randn(co)
+    oh = (hw + 2 * p - ks) // s + 1
+    gy = torch.randn(n, co, oh, oh)
+    y, dx, dw, db = oracle.aten_conv(x, w, b, s, p, gy)
+    for cl in (False, True):
+        xd, gd = dev(x, cl), dev(gy, cl)
+        assert rel_err(host(capi.conv_fwd(xd, dev(w), dev(b), s, p, cl=cl)), y.numpy()) <= TOL
+        assert rel_err(host(capi.conv_dgrad(gd, dev(w), (hw, hw), s, p, cl=cl)), dx.numpy()) <= TOL
+        assert rel_err(host(capi.conv_wgrad(xd, gd, ks, s, p)), dw.numpy()) <= TOL
+        assert rel_err(host(capi.conv_bias_grad(gd)), db.numpy()) <= TOL
+
+
+def test_alexnet_conv1_full_size_properties(capi):
+    """BASELINE config 1 at full size through size-independent properties: linearity of each pass in its activation
+    argument and the adjoint identity <conv(x), gy> == <x, dgrad(gy)> == <w, wgrad(x, gy)>."""
+    torch.manual_seed(0)
+    x = torch.randn(16, 3, 224, 224, device="cuda")
+    conv = torch.nn.Conv2d(3, 64, 11, stride=4, padding=2)
+    w, b = conv.weight.detach().cuda(), conv.bias.detach().cuda()
+    gy = torch.randn(16, 64, 55, 55, device="cuda")
+    y = capi.conv_fwd(x, w, None, 4, 2)
+    dx = capi.conv_dgrad(gy, w, (224, 224), 4, 2)
+    dw = capi.conv_wgrad(x, gy, 11, 4, 2)
+    a = (y.double() * gy.double()).sum().item()
+    assert abs(a - (x.double() * dx.double()).sum().item()) <= 1e-4 * abs(a)
+    assert abs(a - (w.double() * dw.double()).sum().item()) <= 1e-4 * abs(a)
+    y2 = capi.conv_fwd(2.0 * x, w, None, 4, 2)
+    assert rel_err(host(y2), 2.0 * host(y)) <= 1e-6
+    yb = capi.conv_fwd(x, w, b, 4, 2)
+    assert rel_err(host(yb - y), np.broadcast_to(host(b)[None, :, None, None], yb.shape)) <= 1e-4
+    # and a slice of the result against the CPU oracle
+    ys = oracle.c.conv_fwd(host(x[:1]), host(w), host(b), 4, 2)
+    assert rel_err(host(yb[:1]), ys) <= TOL
+
+
+@pytest.mark.parametrize("cl", [False, True], ids=["nchw", "nhwc"])
+@pytest.mark.parametrize("i", range(len(cases.BN)))
+def test_bn_golden(capi, golden, i, cl):
+    n, c, h, w = cases.BN[i]
+    if cl and c % 4:
+        pytest.skip("channels-last BN kernels need c % 4 == 0")
+    G = lambda k: golden[f"bn{i}_{k}"]
+    x = dev(cases.rnd(900 + i, n, c, h, w) * 2 + 3, cl)
+    gamma, beta = dev(cases.rnd(910 + i, c)), dev(cases.rnd(920 + i, c))
+    rm, rv = dev(cases.rnd(930 + i, c)), dev(cases.rnd(940 + i, c).abs() + 0.5)
+    g = dev(cases.rnd(950 + i, n, c, h, w), cl)
+    ye = capi.bn_eval(x, gamma, beta, rm, rv)
+    assert rel_err(host(ye), G("yeval")) <= TOL
+    rm0 = rm.clone()
+    y, mean, invstd, nrm, nrv = capi.bn_train(x, gamma, beta, rm, rv, functional=True)
+    assert torch.equal(rm, rm0)  # functional mode leaves the running stats alone
+    assert rel_err(host(nrm), G("rm")) <= TOL and rel_err(host(nrv), G("rv")) <= TOL
+    y, mean, invstd = capi.bn_train(x, gamma, beta, rm, rv)
+    for got, key in ((y, "y"), (mean, "mean"), (invstd, "invstd"), (rm, "rm"), (rv, "rv")):
+        assert rel_err(host(got), G(key)) <= TOL, key
+    dx, dg, db = capi.bn_backward(g, x, None, mean, invstd, gamma)
+    assert rel_err(host(dx), G("dx")) <= TOL and rel_err(host(dg), G("dgamma")) <= TOL and rel_err(host(db), G("dbeta")) <= TOL
+    yr, _, _, _, _ = capi.bn_train(x, gamma, beta, rm, rv, relu=True, functional=True)
+    assert rel_err(host(yr), np.maximum(G("y"), 0)) <= TOL
+    dx, dg, db = capi.bn_backward(g, x, yr, mean, invstd, gamma, relu=True)
+    assert rel_err(host(dx), G("relu_dx")) <= TOL and rel_err(host(dg), G("relu_dgamma")) <= TOL and rel_err(host(db), G("relu_dbeta")) <= TOL
+
+
+@pytest.mark.parametrize("cl", [False, True], ids=["nchw", "nhwc"])
+def test_bn_large_mean_is_stable(capi, cl):
+    """Shifted sums keep the variance accurate when |mean| >> std (bn_stats_part.wgsl:22-31)."""
+    torch.manual_seed(1)
+    x = torch.randn(32, 64, 28, 28) * 0.1 + 100.0
+    xd = dev(x, cl)
+    gamma, beta = torch.ones(64, device="cuda"), torch.zeros(64, device="cuda")
+    rm, rv = torch.zeros(64, device="cuda"), torch.ones(64, device="cuda")
+    y, mean, invstd = capi.bn_train(xd, gamma, beta, rm, rv)
+    ref_var = x.double().var(dim=(0, 2, 3), unbiased=False)
+    assert rel_err(host(invstd), (1 / torch.sqrt(ref_var + 1e-5)).float().numpy()) <= 1e-3
+    assert rel_err(host(mean), x.double().mean(dim=(0, 2, 3)).float().numpy()) <= 1e-6
+
+
+@pytest.mark.parametrize("cl", [False, True], ids=["nchw", "nhwc"])
+@pytest.mark.parametrize("i", range(len(cases.MAXPOOL)))
+def test_maxpool_golden(capi, golden, i, cl):
+    k, s, p, hw = cases.MAXPOOL[i]
+    x = dev(cases.rnd(700 + i, 2, 4, hw, hw), cl)
+    y, idx = capi.maxpool_fwd(x, k, s, p)
+    assert np.array_equal(host(y), golden[f"maxpool{i}_y"]) and np.array_equal(host(idx), golden[f"maxpool{i}_idx"])
+    g = dev(cases.rnd(720 + i, *y.shape), cl)
+    gx = capi.maxpool_bwd(g, idx, (hw, hw), k, s, p)
+    assert rel_err(host(gx), golden[f"maxpool{i}_gx"]) <= TOL
+
+
+def test_pool_edge_cases(capi):
+    x = torch.zeros(1, 1, 4, 4)
+    x[0, 0, 0, 1] = float("nan")
+    y, idx = capi.maxpool_fwd(dev(x), 2, 2, 0)
+    assert torch.isnan(y[0, 0, 0, 0]).item() and idx[0, 0, 0, 0].item() == 1
+    ones = np.ones((1, 2, 4, 6), np.float32)
+    y2, i2 = capi.pool2_fwd(dev(ones))
+    ry, ri = oracle.c.pool2_fwd(ones)
+    assert np.array_equal(host(i2), ri) and np.array_equal(host(y2), ry)
+    xr = np.random.default_rng(3).standard_normal((3, 8, 6, 10)).astype(np.float32)
+    for cl in (False, True):
+        yr, ir = capi.pool2_fwd(dev(xr, cl))
+        oy, oi = oracle.c.pool2_fwd(xr)
+        assert np.array_equal(host(yr), oy) and np.array_equal(host(ir), oi)
+        g = np.random.default_rng(4).standard_normal(oy.shape).astype(np.float32)
+        assert np.array_equal(host(capi.pool2_bwd(dev(g, cl), ir, (6, 10))), oracle.c.pool2_bwd(g, oi, (6, 10)))
+
+
+@pytest.mark.parametrize("i", range(len(cases.ADAPOOL)))
+def test_adapool_golden(capi, golden, i):
+    hw, o = cases.ADAPOOL[i]
+    for cl in (False, True):
+        x = dev(cases.rnd(800 + i, 2, 5, hw, hw), cl)
+        y = capi.adaptive_avgpool_fwd(x, o)
+        assert rel_err(host(y), golden[f"adapool{i}_y"]) <= TOL
+        g = dev(cases.rnd(820 + i, *y.shape))
+        assert rel_err(host(capi.adaptive_avgpool_bwd(g, (hw, hw))), golden[f"adapool{i}_gx"]) <= TOL
+
+
+def test_avgpool_general_vs_aten(capi):
+    torch.manual_seed(2)
+    x = torch.randn(2, 6, 13, 11)
+    for k, s, p, inc, div in [(2, 2, 0, True, 0), (3, 2, 1, True, 0), (3, 2, 1, False, 0), (3, 1, 1, True, 5)]:
+        ref = torch.nn.functional.avg_pool2d(x, k, s, p, count_include_pad=inc, divisor_override=div or None)
+        xr = x.clone().requires_grad_()
+        r2 = torch.nn.functional.avg_pool2d(xr, k, s, p, count_include_pad=inc, divisor_override=div or None)
+        g = torch.randn_like(r2)
+        r2.backward(g)
+        n, c, ih, iw = x.shape
+        oh, ow = ref.shape[2:]
+        xd = dev(x)
+        y = torch.empty(n, c, oh, ow, device="cuda")
+        pl = capi.Pool(k, k, s, s, p, p, 1, 1)
+        capi.call("omt_avgpool_fwd", capi.act(xd), capi.act(y), n, c, ih, iw, oh, ow, pl, int(inc), div, capi.stream_handle())
+        assert rel_err(host(y), ref.numpy()) <= TOL
+        gx = torch.empty_like(xd)
+        capi.call("omt_avgpool_bwd", capi.act(dev(g)), capi.act(gx), n, c, ih, iw, oh, ow, pl, int(inc), div, capi.stream_handle())
+        assert rel_err(host(gx), xr.grad.numpy()) <= TOL
+
+
+OPT = {"sgd_nesterov_wd": ("sgd", dict(lr=0.1, momentum=0.9, nesterov=True, weight_decay=1e-4)), "sgd_plain": ("sgd", dict(lr=0.05)),
+       "sgd_damp_max": ("sgd", dict(lr=0.05, momentum=0.8, dampening=0.3, maximize=True)),
+       "adam_wd": ("adam", dict(lr=1e-3, weight_decay=0.01)), "adamw": ("adam", dict(lr=1e-3, weight_decay=0.01, decoupled=True))}
+
+
+@pytest.mark.parametrize("name", sorted(OPT))
+def test_optimizers_golden(capi, golden, name):
+    kind, kw = OPT[name]
+    p = dev(cases.rnd(1000, 37, 11))
+    m, v = torch.zeros_like(p), torch.zeros_like(p)
+    step = torch.zeros((), device="cuda")
+    for it in range(3):
+        g = dev(cases.rnd(1001 + it, 37, 11))
+        if kind == "sgd":
+            capi.sgd([p], [g], [m if kw.get("momentum") else None], first=(it == 0), **kw)
+        else:
+            step += 1
+            capi.adam([p], [g], [m], [v], [step], **kw)
+        assert rel_err(host(p), golden[f"optim_{name}_p{it}"]) <= 1e-5
+
+
+def test_multi_tensor_optimizer_ragged_table(capi):
+    """Many tensors of ragged sizes (incl. size 1, unaligned views and an empty one) in one launch vs the oracle."""
+    rng = np.random.default_rng(7)
+    sizes = [1, 3, 4096, 4097, 0, 12289, 64, 5]
+    slab = torch.zeros(sum(sizes) + 64, device="cuda")
+    ps, gs, ms, hp, hm, hg = [], [], [], [], [], []
+    off = 1  # deliberately not 16-byte aligned
+    for s in sizes:
+        a, g, m = (rng.standard_normal(s).astype(np.float32) for _ in range(3))
+        view = slab[off:off + s]
+        view.copy_(torch.from_numpy(a))
+        off += s
+        ps.append(view); gs.append(dev(g)); ms.append(dev(m)); hp.append(a.copy()); hg.append(g); hm.append(m.copy())
+    capi.sgd(ps, gs, ms, lr=0.1, momentum=0.9, weight_decay=1e-4, nesterov=True)
+    for a, g, m, pd, md in zip(hp, hg, hm, ps, ms):
+        if a.size == 0:
+            continue
+        oracle.c.sgd(a, g, m, 0.1, 0.9, 0.0, 1e-4, nesterov=True)
+        assert rel_err(host(pd), a) <= 1e-6 and rel_err(host(md), m) <= 1e-6
+
+
+def test_allocator_and_streams(capi):
+    l = capi.lib()
+    base_alloc, base_res = l.omt_memory_allocated(), l.omt_memory_reserved()
+    s = l.omt_stream_create(1)
+    p = l.omt_malloc(3 << 20, s)
+    assert p and l.omt_memory_allocated() - base_alloc >= 3 << 20
+    l.omt_free(p)
+    assert l.omt_memory_allocated() == base_alloc and l.omt_memory_reserved() > base_res  # cached, not returned
+    q = l.omt_malloc(3 << 20, s)
+    assert q == p  # same size class on the same stream reuses the cached block
+    src = np.arange(1000, dtype=np.float32)
+    dst = np.zeros_like(src)
+    capi.call("omt_memcpy_h2d", q, src.ctypes.data, src.nbytes, s)
+    capi.call("omt_memcpy_d2h", dst.ctypes.data, q, src.nbytes, s)
+    assert np.array_equal(src, dst)
+    e = l.omt_event_create(0)
+    capi.call("omt_event_record", e, s)
+    capi.call("omt_event_sync", e)
+    assert l.omt_event_query(e) == 1 and l.omt_stream_query(s) == 1
+    l.omt_free(q)
+    l.omt_empty_cache()
+    assert l.omt_memory_reserved() <= base_res
+    capi.call("omt_event_destroy", e)
+    capi.call("omt_stream_destroy", s)
+    assert l.omt_check_errors() == 0 and l.omt_launch_count() > 0
+
+
+def test_act_copy_layout_change(capi):
+    x = torch.randn(3, 10, 7, 5, device="cuda")
+    y = torch.empty_like(x).contiguous(memory_format=torch.channels_last)
+    capi.call("omt_act_copy", capi.act(x), capi.act(y), 3, 10, 7, 5, capi.stream_handle())
+    assert torch.equal(x, y)
+    z = torch.empty_like(x)
+    capi.call("omt_act_copy", capi.act(y), capi.act(z), 3, 10, 7, 5, capi.stream_handle())
+    assert torch.equal(x, z)
