@@ -59,39 +59,63 @@ def build_lib(verbose=False):
     out = LIB / "libomt_b200.so"
     newest = max(o.stat().st_mtime for o in objs)
     if not out.exists() or out.stat().st_mtime < newest:
-        cmd = [NVCC, "-shared", "-o", str(out)] + [str(o) for o in objs] + ["-lcudart", "-Xlinker", "-z,defs"] if False else \
-              [NVCC, "-shared", "-o", str(out)] + [str(o) for o in objs] + ["-lcudart"]
+        cmd = [NVCC, "-shared", "-o", str(out)] + [str(o) for o in objs] + ["-lcudart"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
     return out
 
 
+def _compile_cpp(src, flags, verbose):
+    bdir = OBJ / "ext"
+    bdir.mkdir(parents=True, exist_ok=True)
+    obj = bdir / (src.stem + ".o")
+    stamp_file = bdir / (src.stem + ".stamp")
+    h = hashlib.sha1(" ".join(flags).encode())
+    for p in [src] + sorted(src.parent.glob("*.h")) + sorted((HERE.parent / "include").glob("*.h")):
+        h.update(p.read_bytes())
+    stamp = h.hexdigest()
+    if obj.exists() and stamp_file.exists() and stamp_file.read_text() == stamp:
+        return obj
+    cmd = [os.environ.get("CXX", "g++")] + flags + ["-c", str(src), "-o", str(obj)]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"g++ failed for {src.name}:\n{r.stdout}\n{r.stderr}")
+    if verbose and r.stderr:
+        print(r.stderr)
+    stamp_file.write_text(stamp)
+    return obj
+
+
 def build_ext(verbose=False):
-    """Build the PrivateUse1 torch extension _native in-tree (ninja via torch.utils.cpp_extension)."""
+    """Build the PrivateUse1 torch extension omarchy_mac_torch_b200/_native.so in-tree (g++, linked against the
+    installed torch and lib/libomt_b200.so; found at run time through an $ORIGIN rpath)."""
     ext_dir = CSRC / "ext"
-    srcs = sorted(str(p) for p in ext_dir.glob("*.cpp"))
+    srcs = sorted(ext_dir.glob("*.cpp"))
     if not srcs:
         return None
+    import sysconfig
+
     import torch
     from torch.utils import cpp_extension
 
-    lib = build_lib(verbose)
-    bdir = OBJ / "ext"
-    bdir.mkdir(parents=True, exist_ok=True)
-    os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0a")
-    os.environ.setdefault("MAX_JOBS", "8")
-    mod = cpp_extension.load(
-        name="_native", sources=srcs, build_directory=str(bdir), verbose=verbose, is_python_module=False,
-        extra_include_paths=[str(HERE.parent / "include"), str(CSRC)] + cpp_extension.include_paths("cuda"),
-        extra_cflags=["-O2", "-std=c++17", "-DOMT_TORCH_VERSION=\"%s\"" % torch.__version__],
-        extra_ldflags=[f"-L{LIB}", "-lomt_b200", "-Wl,-rpath,$ORIGIN/lib", "-L/usr/local/cuda/lib64", "-lcudart",
-                       "-lc10_cuda", "-ltorch_cuda"],
-        with_cuda=True)
-    built = bdir / "_native.so"
+    build_lib(verbose)
+    incs = [str(HERE.parent / "include"), str(CSRC)] + cpp_extension.include_paths("cuda") + [sysconfig.get_paths()["include"]]
+    flags = ["-O2", "-std=c++17", "-fPIC", "-DTORCH_EXTENSION_NAME=_native", "-DTORCH_API_INCLUDE_EXTENSION_H",
+             f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}", "-Wno-deprecated-declarations"]
+    flags += [f"-I{i}" for i in incs]
+    with concurrent.futures.ThreadPoolExecutor(max_workers=8) as ex:
+        objs = list(ex.map(lambda s: _compile_cpp(s, flags, verbose), srcs))
     dst = HERE / "_native.so"
-    if not dst.exists() or dst.stat().st_mtime < built.stat().st_mtime:
-        shutil.copy2(built, dst)
+    newest = max(max(o.stat().st_mtime for o in objs), (LIB / "libomt_b200.so").stat().st_mtime)
+    if not dst.exists() or dst.stat().st_mtime < newest:
+        tlib = str(pathlib.Path(torch.__file__).parent / "lib")
+        cmd = [os.environ.get("CXX", "g++"), "-shared", "-o", str(dst)] + [str(o) for o in objs] + [
+            f"-L{LIB}", "-lomt_b200", f"-L{tlib}", "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-ltorch_python",
+            "-L/usr/local/cuda/lib64", "-lcudart", "-Wl,-rpath,$ORIGIN/lib", f"-Wl,-rpath,{tlib}"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
     (HERE / "_build_info.json").write_text(json.dumps({"torch": torch.__version__}))
     return dst
 

@@ -1,0 +1,176 @@
+"""torch.compile backend: `torch.compile(model, backend="omarchy_mac_torch")`.
+
+Dynamo captures the model and AOTAutograd lowers it to aten graphs for forward and backward. Three FX passes then rewrite
+those graphs to the fused `omt::` ops, and the graph runs op by op on the device:
+
+  1. training BatchNorm2d followed by ReLU            -> omt.bn_relu_train
+  2. threshold_backward -> native_batch_norm_backward -> omt.bn_relu_backward (ReLU mask folded into the BN backward)
+  3. conv -> [eval BatchNorm] -> [ReLU]               -> omt.conv_act / omt.conv_bn_act_eval
+
+These are passes 1-3 of the reference's omarchy_mac_torch/compile.py:69-161. Its pass 4 (pointwise chains compiled to
+generated shader source) is not part of this build. Every fused op has a composite definition in plain aten ops, so a
+rewritten graph is always correct, on any device. OMARCHY_MAC_TORCH_COMPILE_DEBUG=1 prints what each pass did."""
+
+import operator
+import os
+
+import torch
+from torch._dynamo import register_backend
+from torch._dynamo.backends.common import aot_autograd
+from torch.fx import Node
+
+from omarchy_mac_torch_b200.native import DEVICE
+
+aten = torch.ops.aten
+omt = torch.ops.omt
+_DEBUG = os.environ.get("OMARCHY_MAC_TORCH_COMPILE_DEBUG", "0") == "1"
+_ANY_DEVICE = False  # tests flip this to exercise the passes on CPU graphs through the composite implementations
+
+
+def _meta(n):
+    return n.meta.get("val") if isinstance(n, Node) else None
+
+
+def _f32_4d(n):
+    v = _meta(n)
+    return (isinstance(v, torch.Tensor) and v.dtype == torch.float32 and v.dim() == 4 and (_ANY_DEVICE or v.device.type == DEVICE))
+
+
+def _is(n, target):
+    return isinstance(n, Node) and n.op == "call_function" and n.target is target
+
+
+def _items(n):
+    """index -> getitem node, for a node with tuple output"""
+    return {u.args[1]: u for u in n.users if _is(u, operator.getitem)}
+
+
+def _sole_user(n):
+    users = list(n.users)
+    return users[0] if len(users) == 1 else None
+
+
+def _getitem_after(graph, anchor, src, index, meta):
+    with graph.inserting_before(anchor):
+        node = graph.call_function(operator.getitem, (src, index))
+    node.meta = dict(meta)
+    return node
+
+
+def _swap_tuple_node(graph, old, new):
+    """Re-point every getitem of `old` at `new` (same indices) and drop `old`."""
+    for idx, gi in _items(old).items():
+        gi.replace_all_uses_with(_getitem_after(graph, gi, new, idx, gi.meta))
+        graph.erase_node(gi)
+    graph.erase_node(old)
+
+
+def fuse_bn_relu(graph):
+    done = 0
+    for bn in list(graph.nodes):
+        if not _is(bn, aten._native_batch_norm_legit_functional.default):
+            continue
+        x, w, b, rm, rv, training, momentum, eps = bn.args[:8]
+        if not training or None in (w, b, rm, rv) or not _f32_4d(x):
+            continue
+        y = _items(bn).get(0)
+        relu = _sole_user(y) if y is not None else None
+        if not _is(relu, aten.relu.default):
+            continue
+        with graph.inserting_before(bn):
+            fused = graph.call_function(omt.bn_relu_train.default, (x, w, b, rm, rv, momentum, eps))
+        relu.replace_all_uses_with(_getitem_after(graph, relu, fused, 0, relu.meta))
+        graph.erase_node(relu)
+        graph.erase_node(y)
+        _swap_tuple_node(graph, bn, fused)
+        done += 1
+    return done
+
+
+def fuse_bn_relu_backward(graph):
+    done = 0
+    for bw in list(graph.nodes):
+        if not _is(bw, aten.native_batch_norm_backward.default):
+            continue
+        g, x, w, _rm, _rv, mean, invstd, train, _eps, mask = bw.args[:10]
+        if not train or w is None or not _f32_4d(x):
+            continue
+        if not (_is(g, aten.threshold_backward.default) and g.args[2] == 0 and len(g.users) == 1):
+            continue
+        gout, y = g.args[0], g.args[1]
+        with graph.inserting_before(bw):
+            fused = graph.call_function(omt.bn_relu_backward.default, (gout, x, y, w, mean, invstd, list(mask)))
+        _swap_tuple_node(graph, bw, fused)
+        graph.erase_node(g)
+        done += 1
+    return done
+
+
+def _dense_conv(n):
+    if not _is(n, aten.convolution.default):
+        return False
+    x, w, _b, stride, padding, dilation, transposed, _outpad, groups = n.args[:9]
+    wv = _meta(w)
+    return (_f32_4d(x) and not transposed and groups == 1 and list(dilation) == [1, 1] and wv is not None and wv.shape[2] == wv.shape[3]
+            and len(set(stride)) == 1 and len(set(padding)) == 1)
+
+
+def fuse_conv_epilogues(graph):
+    done = 0
+    for conv in list(graph.nodes):
+        if not _dense_conv(conv):
+            continue
+        x, w, b, stride, padding = conv.args[:5]
+        nxt = _sole_user(conv)
+        if nxt is None:
+            continue
+        if _is(nxt, aten._native_batch_norm_legit_no_training.default) and nxt.args[0] is conv:
+            _, bw, bb, rm, rv, _mom, eps = nxt.args[:7]
+            outs = _items(nxt)
+            if None in (bw, bb, rm, rv) or set(outs) != {0}:
+                continue
+            y = outs[0]
+            relu = _sole_user(y)
+            act = 1 if _is(relu, aten.relu.default) else 0
+            last = relu if act else y
+            with graph.inserting_before(conv):
+                fused = graph.call_function(omt.conv_bn_act_eval.default, (x, w, b, bw, bb, rm, rv, eps, list(stride), list(padding), act))
+            fused.meta = dict(last.meta)
+            last.replace_all_uses_with(fused)
+            for dead in ([relu] if act else []) + [y, nxt, conv]:
+                graph.erase_node(dead)
+            done += 1
+        elif _is(nxt, aten.relu.default):
+            with graph.inserting_before(conv):
+                fused = graph.call_function(omt.conv_act.default, (x, w, b, list(stride), list(padding), 1))
+            fused.meta = dict(nxt.meta)
+            nxt.replace_all_uses_with(fused)
+            graph.erase_node(nxt)
+            graph.erase_node(conv)
+            done += 1
+    return done
+
+
+def rewrite(gm):
+    """Apply the three passes to a GraphModule in place; returns {pass: rewrites}."""
+    g = gm.graph
+    stats = {"bn_relu": fuse_bn_relu(g), "bn_relu_backward": fuse_bn_relu_backward(g), "conv_epilogue": fuse_conv_epilogues(g)}
+    g.eliminate_dead_code()
+    g.lint()
+    gm.recompile()
+    return stats
+
+
+def _compile(gm, example_inputs):
+    stats = rewrite(gm)
+    if _DEBUG:
+        print("[omarchy-mac-torch compile]", stats)
+    from functorch.compile import make_boxed_func
+    return make_boxed_func(gm.forward)
+
+
+backend = aot_autograd(fw_compiler=_compile, bw_compiler=_compile, inference_compiler=_compile)
+try:
+    register_backend(name=DEVICE)(backend)
+except Exception:  # already registered (module re-import)
+    pass

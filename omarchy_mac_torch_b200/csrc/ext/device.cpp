@@ -1,0 +1,428 @@
+// Allocator, device guard (with events), hooks and generator, memory/copy/view ops, and the bridge that serves ops
+// outside the hot path with ATen's CUDA kernels on the same memory.
+//
+// Registration surface = the reference's csrc/device.cpp:238-256 (empty.memory_format, empty_strided, _copy_from,
+// _copy_from_and_resize, _local_scalar_dense, set_ variants, view ops, the boxed fallback); what sits underneath is
+// different: storages are CUDA memory from the caching allocator of libomt_b200.so, and the fallback does not leave
+// the GPU.
+#include "omt.h"
+
+#include <ATen/CPUGeneratorImpl.h>
+#include <ATen/EmptyTensor.h>
+#include <ATen/detail/PrivateUse1HooksInterface.h>
+#include <ATen/native/Resize.h>
+#include <c10/core/impl/DeviceGuardImplInterface.h>
+#include <c10/cuda/CUDAFunctions.h>
+#include <cuda_runtime.h>
+
+#include <cstdlib>
+
+namespace omt {
+
+std::recursive_mutex& big_lock() {
+  static std::recursive_mutex m;
+  return m;
+}
+Stats& stats() {
+  static Stats s;
+  return s;
+}
+
+// ------------------------------------------------------------------------------------------------
+// runtime glue
+// ------------------------------------------------------------------------------------------------
+
+static int g_index = -1;
+
+static int pick_device() {
+  for (const char* name : {"OMARCHY_MAC_TORCH_CUDA_DEVICE", "LOCAL_RANK"}) {
+    const char* e = std::getenv(name);
+    if (e && *e) {
+      int v = std::atoi(e);
+      if (v >= 0 && v < c10::cuda::device_count()) return v;
+    }
+  }
+  return 0;
+}
+
+void ensure_init() {
+  if (g_index >= 0) {
+    if (c10::cuda::current_device() != g_index) c10::cuda::set_device((c10::DeviceIndex)g_index);
+    return;
+  }
+  OMT_LOCK;
+  if (g_index >= 0) return;
+  TORCH_CHECK(c10::cuda::device_count() > 0,
+              "omarchy-mac-torch: no CUDA device is visible; this backend has no CPU path and needs a B200");
+  int idx = pick_device();
+  c10::cuda::set_device((c10::DeviceIndex)idx);
+  int r = omt_init(idx);
+  if (r != OMT_OK) {
+    char buf[512];
+    omt_last_error(buf, sizeof(buf));
+    TORCH_CHECK(false, "omarchy-mac-torch: cannot initialise CUDA device ", idx, ": ", buf);
+  }
+  g_index = idx;
+}
+int device_index() {
+  ensure_init();
+  return g_index;
+}
+omt_stream_t cur_stream() { return (omt_stream_t)c10::cuda::getCurrentCUDAStream((c10::DeviceIndex)device_index()).stream(); }
+
+void check(int status, const char* what) {
+  if (status == OMT_OK) return;
+  char buf[512];
+  omt_last_error(buf, sizeof(buf));
+  if (status == OMT_ENOMEM) TORCH_CHECK_WITH(OutOfMemoryError, false, "omarchy-mac-torch: ", what, ": ", buf);
+  TORCH_CHECK(false, "omarchy-mac-torch: ", what, " failed (", status, "): ", buf);
+}
+void check_errors() {
+  if (g_index < 0) return;
+  if (omt_check_errors() != OMT_OK) {
+    char buf[512];
+    omt_last_error(buf, sizeof(buf));
+    TORCH_CHECK(false, "omarchy-mac-torch: ", buf);
+  }
+}
+void debug_end(const char* op) {  // OMARCHY_MAC_TORCH_DEBUG=1: surface asynchronous failures at the op that caused them
+  cudaError_t e = cudaStreamSynchronize((cudaStream_t)cur_stream());
+  if (e == cudaSuccess) e = cudaGetLastError();
+  TORCH_CHECK(e == cudaSuccess, "omarchy-mac-torch: CUDA error after ", op, ": ", cudaGetErrorString(e));
+}
+
+// ------------------------------------------------------------------------------------------------
+// allocator
+// ------------------------------------------------------------------------------------------------
+
+static void free_block(void* p) { omt_free(p); }
+
+struct Allocator final : c10::Allocator {
+  c10::DataPtr allocate(size_t n) override {
+    ensure_init();
+    void* p = omt_malloc(std::max<size_t>(n, 4), cur_stream());
+    if (!p) {
+      char buf[512];
+      omt_last_error(buf, sizeof(buf));
+      TORCH_CHECK_WITH(OutOfMemoryError, false, "omarchy-mac-torch: ", buf);
+    }
+    return {p, p, &free_block, c10::Device(kDev, 0)};
+  }
+  void copy_data(void* dst, const void* src, std::size_t count) const override {
+    ensure_init();
+    check(omt_memcpy_d2d(dst, src, count, cur_stream()), "storage copy");
+  }
+  c10::DeleterFnPtr raw_deleter() const override { return &free_block; }
+};
+static Allocator g_alloc;
+REGISTER_ALLOCATOR(c10::DeviceType::PrivateUse1, &g_alloc);
+
+Tensor empty_dev(IntArrayRef size, c10::ScalarType dt, bool channels_last) {
+  c10::DispatchKeySet ks(c10::DispatchKey::PrivateUse1);
+  return at::detail::empty_generic(size, &g_alloc, ks, dt,
+                                   channels_last && size.size() == 4 ? std::optional<at::MemoryFormat>(at::MemoryFormat::ChannelsLast)
+                                                                     : std::nullopt);
+}
+
+// ------------------------------------------------------------------------------------------------
+// CUDA aliases of device tensors and back
+// ------------------------------------------------------------------------------------------------
+
+Tensor cuda_alias(const Tensor& t) {
+  auto opts = t.options().device(at::Device(at::kCUDA, (c10::DeviceIndex)device_index()));
+  if (t.numel() == 0) return at::empty_strided(t.sizes(), t.strides(), opts);
+  Tensor keep = t;  // the alias keeps the device storage alive
+  return at::from_blob(t.data_ptr(), t.sizes(), t.strides(), [keep](void*) {}, opts);
+}
+
+Tensor wrap_cuda(const Tensor& c) {
+  auto* keep = new Tensor(c);
+  c10::DataPtr dp(c.storage().mutable_data(), keep, [](void* p) { delete static_cast<Tensor*>(p); }, c10::Device(kDev, 0));
+  c10::Storage st(c10::Storage::use_byte_size_t(), c.storage().nbytes(), std::move(dp), &g_alloc, /*resizable=*/true);
+  Tensor out = at::detail::make_tensor<c10::TensorImpl>(std::move(st), c10::DispatchKeySet(c10::DispatchKey::PrivateUse1), c.dtype());
+  out.unsafeGetTensorImpl()->set_sizes_and_strides(c.sizes(), c.strides(), c.storage_offset());
+  return out;
+}
+
+int layout4(const Tensor& t) {
+  if (t.dim() != 4) return -1;
+  if (t.is_contiguous()) return 0;
+  if (t.is_contiguous(at::MemoryFormat::ChannelsLast)) return 1;
+  return -1;
+}
+Tensor contig(const Tensor& t) {
+  if (t.is_contiguous()) return t;
+  Tensor out = empty_dev(t.sizes(), t.scalar_type());
+  cuda_alias(out).copy_(cuda_alias(t));
+  return out;
+}
+// strides as the kernels expect them for a given layout (size-1 dimensions make PyTorch's strides ambiguous)
+static Tensor canon(const Tensor& t, int layout) {
+  int64_t c = t.size(1), h = t.size(2), w = t.size(3);
+  std::vector<int64_t> st = layout == 0 ? std::vector<int64_t>{c * h * w, h * w, w, 1} : std::vector<int64_t>{h * w * c, 1, w * c, c};
+  if (t.strides() == IntArrayRef(st)) return t;
+  return t.as_strided(t.sizes(), st);
+}
+Tensor dense4(const Tensor& t) {
+  int l = layout4(t);
+  if (l >= 0) return canon(t, l);
+  return canon(contig(t), 0);
+}
+Tensor to_layout(const Tensor& t_, int layout) {
+  Tensor t = dense4(t_);
+  int have = layout4(t);
+  if (have == layout || (t.is_contiguous() && t.is_contiguous(at::MemoryFormat::ChannelsLast))) return canon(t, layout);
+  Tensor out = canon(empty_dev(t.sizes(), at::kFloat, layout == 1), layout);
+  OmtAct a = act(t), b = act(out);
+  check(omt_act_copy(&a, &b, (int)t.size(0), (int)t.size(1), (int)t.size(2), (int)t.size(3), cur_stream()), "layout change");
+  return out;
+}
+
+// ------------------------------------------------------------------------------------------------
+// memory / copy ops
+// ------------------------------------------------------------------------------------------------
+
+static Tensor empty_memory_format_impl(IntArrayRef size, std::optional<at::ScalarType> dtype, std::optional<at::Layout>,
+                                       std::optional<at::Device>, std::optional<bool>, std::optional<at::MemoryFormat> mf) {
+  c10::DispatchKeySet ks(c10::DispatchKey::PrivateUse1);
+  return at::detail::empty_generic(size, &g_alloc, ks, dtype.value_or(at::kFloat), mf);
+}
+static Tensor empty_strided_impl(IntArrayRef size, IntArrayRef stride, std::optional<at::ScalarType> dtype, std::optional<at::Layout>,
+                                 std::optional<at::Device>, std::optional<bool>) {
+  c10::DispatchKeySet ks(c10::DispatchKey::PrivateUse1);
+  return at::detail::empty_strided_generic(size, stride, &g_alloc, ks, dtype.value_or(at::kFloat));
+}
+
+// copy self -> dst in any direction; ATen's CUDA copy does dtype conversion, strides and broadcasting
+static Tensor copy_from_impl(const Tensor& self, const Tensor& dst, bool non_blocking) {
+  ensure_init();
+  Tensor a = is_dev(self) ? cuda_alias(self) : self;
+  Tensor b = is_dev(dst) ? cuda_alias(dst) : dst;
+  b.copy_(a, non_blocking);
+  return dst;
+}
+static Tensor copy_from_and_resize_impl(const Tensor& self, const Tensor& dst) {
+  at::native::resize_(dst, self.sizes(), std::nullopt);
+  return copy_from_impl(self, dst, false);
+}
+static c10::Scalar local_scalar(const Tensor& self) {
+  ensure_init();
+  return cuda_alias(self).item();
+}
+static Tensor& set_storage(Tensor& self, c10::Storage src, int64_t off, IntArrayRef size, IntArrayRef stride) {
+  return at::native::set_storage_cpu_(self, src, off, size, stride);  // metadata only
+}
+
+// ------------------------------------------------------------------------------------------------
+// device guard with events. One logical stream per device: PyTorch's current CUDA stream.
+// ------------------------------------------------------------------------------------------------
+
+struct Guard final : c10::impl::DeviceGuardImplInterface {
+  c10::DeviceType type() const override { return kDev; }
+  c10::Device exchangeDevice(c10::Device) const override {
+    if (g_index >= 0) ensure_init();
+    return {kDev, 0};
+  }
+  c10::Device getDevice() const override { return {kDev, 0}; }
+  void setDevice(c10::Device) const override {
+    if (g_index >= 0) ensure_init();  // worker threads (autograd) start on CUDA device 0: move them to ours
+  }
+  void uncheckedSetDevice(c10::Device) const noexcept override {
+    if (g_index >= 0) cudaSetDevice(g_index);
+  }
+  c10::Stream getStream(c10::Device d) const noexcept override { return c10::Stream(c10::Stream::DEFAULT, d); }
+  c10::Stream getDefaultStream(c10::Device d) const override { return c10::Stream(c10::Stream::DEFAULT, d); }
+  c10::Stream getNewStream(c10::Device d, int) const override { return c10::Stream(c10::Stream::DEFAULT, d); }
+  c10::Stream exchangeStream(c10::Stream s) const noexcept override { return s; }
+  c10::DeviceIndex deviceCount() const noexcept override { return 1; }
+  void record(void** event, const c10::Stream&, const c10::DeviceIndex, const c10::EventFlag) const override {
+    ensure_init();
+    if (!*event) *event = omt_event_create(0);
+    check(omt_event_record((omt_event_t)*event, cur_stream()), "event record");
+  }
+  void block(void* event, const c10::Stream&) const override {
+    if (event) check(omt_stream_wait_event(cur_stream(), (omt_event_t)event), "stream wait event");
+  }
+  bool queryEvent(void* event) const override { return !event || omt_event_query((omt_event_t)event) == 1; }
+  void destroyEvent(void* event, const c10::DeviceIndex) const noexcept override {
+    if (event) omt_event_destroy((omt_event_t)event);
+  }
+  void synchronizeEvent(void* event) const override {
+    if (event) check(omt_event_sync((omt_event_t)event), "event synchronize");
+  }
+  bool queryStream(const c10::Stream&) const override { return omt_stream_query(cur_stream()) == 1; }
+  void synchronizeStream(const c10::Stream&) const override { check(omt_stream_sync(cur_stream()), "stream synchronize"); }
+  void synchronizeDevice(const c10::DeviceIndex) const override {
+    ensure_init();
+    check(omt_sync(), "device synchronize");
+  }
+  void recordDataPtrOnStream(const c10::DataPtr& p, const c10::Stream&) const override { omt_record_stream(p.get(), cur_stream()); }
+};
+C10_REGISTER_GUARD_IMPL(PrivateUse1, Guard);
+
+// ------------------------------------------------------------------------------------------------
+// hooks and generator (random fills are drawn on the host with this device's own generator, then uploaded)
+// ------------------------------------------------------------------------------------------------
+
+struct Generator : at::CPUGeneratorImpl {
+  explicit Generator(c10::DeviceIndex i) {
+    device_ = c10::Device(kDev, i);
+    key_set_ = c10::DispatchKeySet(c10::DispatchKey::PrivateUse1);
+  }
+};
+static const at::Generator& default_generator() {
+  static at::Generator g = at::make_generator<Generator>(0);
+  return g;
+}
+
+struct Hooks final : at::PrivateUse1HooksInterface {
+  bool isBuilt() const override { return true; }
+  bool isAvailable() const override { return true; }
+  bool hasPrimaryContext(c10::DeviceIndex) const override { return true; }
+  c10::DeviceIndex deviceCount() const override { return 1; }
+  c10::DeviceIndex getCurrentDevice() const override { return 0; }
+  void setCurrentDevice(c10::DeviceIndex) const override {}
+  c10::DeviceIndex exchangeDevice(c10::DeviceIndex) const override { return 0; }
+  c10::DeviceIndex maybeExchangeDevice(c10::DeviceIndex) const override { return 0; }
+  const at::Generator& getDefaultGenerator(c10::DeviceIndex) const override { return default_generator(); }
+  at::Generator getNewGenerator(c10::DeviceIndex i) const override { return at::make_generator<Generator>(i < 0 ? 0 : i); }
+  at::Device getDeviceFromPtr(void*) const override { return {kDev, 0}; }
+  void resizePrivateUse1Bytes(const c10::Storage& storage, size_t newsize) const override {
+    ensure_init();
+    c10::DataPtr fresh = newsize ? g_alloc.allocate(newsize) : c10::DataPtr(nullptr, c10::Device(kDev, 0));
+    size_t keep = std::min(newsize, storage.nbytes());
+    if (keep && storage.data()) check(omt_memcpy_d2d(fresh.get(), storage.data(), keep, cur_stream()), "storage resize");
+    storage.unsafeGetStorageImpl()->set_data_ptr_noswap(std::move(fresh));
+    storage.unsafeGetStorageImpl()->set_nbytes(newsize);
+  }
+};
+static struct HooksRegistrar {
+  HooksRegistrar() {
+    static Hooks hooks;
+    at::RegisterPrivateUse1HooksInterface(&hooks);
+  }
+} g_hooks_registrar;
+
+at::CPUGeneratorImpl* generator(const std::optional<at::Generator>& gen) {
+  const at::Generator& g = (gen && gen->defined()) ? *gen : default_generator();
+  TORCH_CHECK(g.device().type() == kDev, "omarchy-mac-torch: expected a generator for this device, got one for ", g.device());
+  return static_cast<at::CPUGeneratorImpl*>(g.unsafeGetGeneratorImpl());
+}
+
+// ------------------------------------------------------------------------------------------------
+// the bridge: ops without a kernel in this library run ATen's CUDA kernel on aliases of the same memory
+// ------------------------------------------------------------------------------------------------
+
+std::map<std::string, int64_t>& fallback_counts() {
+  static std::map<std::string, int64_t> m;
+  return m;
+}
+void note_fallback(const std::string& op, const std::string& why) { fallback_counts()[op + " (" + why + ")"]++; }
+bool strict_mode() {
+  static bool s = [] {
+    const char* e = std::getenv("OMARCHY_MAC_TORCH_STRICT");
+    return e && e[0] == '1';
+  }();
+  return s;
+}
+
+namespace {
+struct AliasMap {
+  std::vector<Tensor> dev, cuda;
+  Tensor to_cuda(const Tensor& t) {
+    if (!is_dev(t)) return t;
+    for (size_t i = 0; i < dev.size(); i++)
+      if (dev[i].unsafeGetTensorImpl() == t.unsafeGetTensorImpl()) return cuda[i];
+    dev.push_back(t);
+    cuda.push_back(cuda_alias(t));
+    return cuda.back();
+  }
+  Tensor to_dev(const Tensor& c) {
+    if (!c.defined() || !c.is_cuda()) return c;
+    for (size_t i = 0; i < cuda.size(); i++)
+      if (cuda[i].unsafeGetTensorImpl() == c.unsafeGetTensorImpl()) return dev[i];  // in-place / out= result
+    for (size_t i = 0; i < cuda.size(); i++)
+      if (c.is_alias_of(cuda[i])) {  // a view of an input: rebuild it over the input's device storage
+        Tensor v = at::detail::make_tensor<c10::TensorImpl>(c10::Storage(dev[i].storage()), dev[i].key_set(), c.dtype());
+        v.unsafeGetTensorImpl()->set_sizes_and_strides(c.sizes(), c.strides(),
+                                                       dev[i].storage_offset() * (int64_t)dev[i].element_size() / (int64_t)c.element_size() +
+                                                           c.storage_offset());
+        return v;
+      }
+    return wrap_cuda(c);
+  }
+};
+}  // namespace
+
+static void bridge_impl(const c10::OperatorHandle& op, torch::jit::Stack* stack, bool count) {
+  ensure_init();
+  const auto& schema = op.schema();
+  const std::string key = schema.name().substr(6) + (schema.overload_name().empty() ? "" : "." + schema.overload_name());
+  if (!op.hasKernelForDispatchKey(c10::DispatchKey::CUDA)) {  // nothing on the GPU for it anywhere: host fallback, recorded
+    TORCH_CHECK(!strict_mode(), "omarchy-mac-torch (strict): ", key, " has no GPU kernel");
+    {
+      OMT_LOCK;
+      if (count) fallback_counts()[key]++;
+    }
+    at::native::cpu_fallback(op, stack);
+    return;
+  }
+  OMT_LOCK;
+  if (count) stats().bridge[key]++;
+  const size_t nargs = schema.arguments().size(), begin = stack->size() - nargs;
+  const c10::Device cuda_dev(at::kCUDA, (c10::DeviceIndex)device_index());
+  AliasMap map;
+  for (size_t i = 0; i < nargs; i++) {
+    c10::IValue& v = (*stack)[begin + i];
+    if (v.isTensor()) {
+      v = map.to_cuda(v.toTensor());
+    } else if (v.isTensorList()) {
+      c10::List<Tensor> out;
+      for (const Tensor& t : v.toTensorVector()) out.push_back(map.to_cuda(t));
+      v = out;
+    } else if (v.isOptionalTensorList()) {
+      c10::List<std::optional<Tensor>> out;
+      for (const std::optional<Tensor>& t : v.toOptionalTensorVector())
+        out.push_back(t && t->defined() ? std::optional<Tensor>(map.to_cuda(*t)) : t);
+      v = out;
+    } else if (v.isDevice() && v.toDevice().type() == kDev) {
+      v = cuda_dev;
+    }
+  }
+  op.redispatchBoxed(c10::DispatchKeySet(c10::DispatchKey::CUDA), stack);
+  const size_t nret = schema.returns().size(), rbegin = stack->size() - nret;
+  for (size_t i = 0; i < nret; i++) {
+    c10::IValue& v = (*stack)[rbegin + i];
+    if (v.isTensor()) {
+      v = map.to_dev(v.toTensor());
+    } else if (v.isTensorList()) {
+      c10::List<Tensor> out;
+      for (const Tensor& t : v.toTensorVector()) out.push_back(map.to_dev(t));
+      v = out;
+    }
+  }
+}
+void bridge_boxed(const c10::OperatorHandle& op, torch::jit::Stack* stack) { bridge_impl(op, stack, true); }
+void bridge_quiet(const c10::OperatorHandle& op, torch::jit::Stack* stack) { bridge_impl(op, stack, false); }
+
+TORCH_LIBRARY_IMPL(_, PrivateUse1, m) { m.fallback(torch::CppFunction::makeFromBoxedFunction<&bridge_boxed>()); }
+
+TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
+  OMT_IMPL(m, empty_memory_format, empty_memory_format_impl);
+  OMT_IMPL(m, empty_strided, empty_strided_impl);
+  OMT_IMPL(m, _copy_from, copy_from_impl);
+  OMT_IMPL(m, _copy_from_and_resize, copy_from_and_resize_impl);
+  OMT_IMPL(m, _local_scalar_dense, local_scalar);
+  OMT_IMPL(m, set__source_Storage_storage_offset, set_storage);
+  m.impl("view", &at::native::view);
+  m.impl("_unsafe_view", &at::native::_unsafe_view);
+  m.impl("as_strided", &at::native::as_strided_tensorimpl);
+  m.impl("_reshape_alias", &at::native::_reshape_alias);
+  m.impl("resize_", &at::native::resize_);
+  m.impl("unfold", &at::native::unfold);  // views cannot go through the bridge's alias rebuild safely: explicit impls
+  m.impl("view_as_real", &at::native::view_as_real);
+  m.impl("view_as_complex", &at::native::view_as_complex);
+  m.impl("set_.source_Storage", &at::native::set_);
+}
+
+}  // namespace omt

@@ -1,0 +1,142 @@
+"""Loads the C++ device extension and registers the "omarchy_mac_torch" PrivateUse1 device with PyTorch (the public
+out-of-tree backend route: rename_privateuse1_backend + generated tensor/module methods + a device module).
+
+Same Python surface as the reference's omarchy_mac_torch/native.py (DEVICE, FALLBACKS, synchronize, empty_cache,
+memory_*, set_queue_depth, validate_kernels, the torch.omarchy_mac_torch device module); the WGSL kernel generator
+hand-off and the on-disk tuning cache of the reference have no counterpart because the CUDA kernels are prebuilt."""
+
+import ctypes
+import json
+import os
+import pathlib
+import types
+
+import torch
+
+_HERE = pathlib.Path(__file__).resolve().parent
+DEVICE = "omarchy_mac_torch"
+
+
+def _require_build():
+    so, lib, info = _HERE / "_native.so", _HERE / "lib" / "libomt_b200.so", _HERE / "_build_info.json"
+    if not (so.exists() and lib.exists() and info.exists()):
+        raise ImportError("omarchy-mac-torch: the native backend is not built; run `python -m omarchy_mac_torch_b200.build`")
+    built = json.loads(info.read_text())["torch"].split("+")[0]
+    if built != torch.__version__.split("+")[0]:
+        raise ImportError(f"omarchy-mac-torch was built against torch {built} but torch {torch.__version__} is installed; rebuild")
+    return lib
+
+
+ctypes.CDLL(str(_require_build()), mode=ctypes.RTLD_GLOBAL)
+from omarchy_mac_torch_b200 import _native as core  # noqa: E402
+
+torch.utils.rename_privateuse1_backend(DEVICE)
+torch.utils.generate_methods_for_privateuse1_backend(for_tensor=True, for_module=True, for_packed_sequence=True, for_storage=True)
+
+core.set_fold(int(os.environ.get("OMARCHY_MAC_TORCH_FOLD", "1")))
+core.set_tuning(os.environ.get("OMARCHY_MAC_TORCH_TUNE", "1") != "0", 0)
+core.set_debug(os.environ.get("OMARCHY_MAC_TORCH_DEBUG", "0") == "1")
+core.set_channels_last(int(os.environ.get("OMARCHY_MAC_TORCH_CHANNELS_LAST", "0")))
+
+
+def synchronize():
+    """Wait for all queued device work; raises if a kernel failed asynchronously."""
+    core.sync()
+
+
+def empty_cache():
+    core.empty_cache()
+
+
+def memory_allocated():
+    return core.memory_allocated()
+
+
+def memory_reserved():
+    return core.memory_reserved()
+
+
+def set_queue_depth(depth=3, chunk=64):
+    """Kept for API parity. The reference bounded its wgpu queue so a desktop compositor sharing the GPU stayed
+    responsive; CUDA streams on a compute-only B200 need no such throttle, so this records nothing."""
+    core.set_queue(chunk, depth)
+
+
+def validate_kernels():
+    """Kernels are compiled ahead of time for sm_100a, so there is nothing to compile at run time: no failures."""
+    return core.validate_kernels()
+
+
+class _DeviceContext:
+    def __init__(self, device=None):
+        self.device = device
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
+def _device_module():
+    m = types.ModuleType("torch." + DEVICE)
+    const = lambda v: (lambda *a, **k: v)
+    m.is_available, m.is_initialized, m._is_in_bad_fork = const(True), const(True), const(False)
+    m._lazy_init, m.set_device = const(None), const(None)
+    m.device_count, m.current_device = const(1), const(0)
+    m.get_amp_supported_dtype = const([torch.float32])
+    m.synchronize = lambda device=None: core.sync()
+    m.empty_cache = core.empty_cache
+    m.memory_allocated = lambda device=None: core.memory_allocated()
+    m.memory_reserved = lambda device=None: core.memory_reserved()
+    m.manual_seed = m.manual_seed_all = lambda seed: core.manual_seed(int(seed) & 0xFFFFFFFFFFFFFFFF)
+    m.seed = m.seed_all = core.seed
+    m.initial_seed = core.initial_seed
+    m.get_rng_state = lambda device=None: core.get_rng_state()
+    m.set_rng_state = lambda state, device=None: core.set_rng_state(state)
+    m.device = _DeviceContext
+    return m
+
+
+torch._register_device_module(DEVICE, _device_module())
+
+
+class _Fallbacks:
+    """Read-only view of the ops that did not run on this library's kernels, with why: {"op (reason)": count}.
+    An entry means the call was served by ATen's CUDA kernel (or, if ATen has none, on the host)."""
+
+    def _d(self):
+        return core.fallback_counts()
+
+    def keys(self):
+        return self._d().keys()
+
+    def items(self):
+        return self._d().items()
+
+    def values(self):
+        return self._d().values()
+
+    def __getitem__(self, k):
+        return self._d()[k]
+
+    def __contains__(self, k):
+        return k in self._d()
+
+    def __iter__(self):
+        return iter(self._d())
+
+    def __len__(self):
+        return len(self._d())
+
+    def __bool__(self):
+        return bool(self._d())
+
+    def clear(self):
+        core.reset_fallbacks()
+
+    def __repr__(self):
+        return repr(self._d())
+
+
+FALLBACKS = _Fallbacks()

@@ -1,0 +1,277 @@
+"""The "omarchy_mac_torch" PyTorch device end to end on a B200: storage semantics, the aten overrides through autograd,
+fused stacks, fused optimizers, whole-model training against the golden loss curves (the reference's acceptance test,
+tools/acceptance.py) and the torch.compile backend. Run with -m gpu."""
+import copy
+import io
+
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+import cases
+from conftest import TOL, rel_err
+
+pytestmark = pytest.mark.gpu
+D = "omarchy_mac_torch"
+
+
+@pytest.fixture(scope="module")
+def omt():
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    import omarchy_mac_torch_b200 as m
+    m.DEVICE  # registers the device
+    return m
+
+
+def e(a, b):
+    return rel_err(a.detach().cpu().numpy(), b.detach().cpu().numpy())
+
+
+def test_storage_semantics(omt):
+    """notes/scripts/storage_check.py: save/load, deepcopy, dtype views, generator determinism, events."""
+    x = torch.randn(7, 5)
+    xd = x.to(D)
+    assert xd.device.type == D and torch.equal(xd.cpu(), x)
+    assert torch.equal(copy.deepcopy(xd).cpu(), x)
+    buf = io.BytesIO()
+    torch.save({"t": xd}, buf)
+    buf.seek(0)
+    assert torch.equal(torch.load(buf, map_location="cpu")["t"], x)
+    buf.seek(0)
+    back = torch.load(buf)["t"]
+    assert back.device.type == D and torch.equal(back.cpu(), x)
+    assert torch.equal(xd.view(torch.int32).cpu(), x.view(torch.int32))
+    assert torch.equal(xd.t()[1:3].contiguous().cpu(), x.t()[1:3].contiguous())
+    assert xd.sum().item() == pytest.approx(x.sum().item(), rel=1e-5)
+    y = torch.arange(10, device=D)
+    assert y.dtype == torch.int64 and y.cpu().tolist() == list(range(10))
+    torch.manual_seed(3)
+    a = torch.empty(64, device=D).normal_()
+    torch.manual_seed(3)
+    b = torch.empty(64, device=D).normal_()
+    assert torch.equal(a.cpu(), b.cpu()) and a.cpu().std() > 0.5
+    ev = torch.Event(D)
+    ev.record()
+    ev.synchronize()
+    assert ev.query()
+    z = torch.zeros(3, device=D)
+    z.resize_(6)
+    assert z.shape == (6,)
+    before = omt.memory_allocated()
+    big = torch.empty(1 << 20, device=D)
+    assert omt.memory_allocated() >= before + (4 << 20)
+    del big
+    omt.empty_cache()
+    omt.synchronize()
+
+
+CONV = {k: v for k, v in cases.conv_cases().items()}
+
+
+@pytest.mark.parametrize("name", sorted(CONV))
+def test_conv_modules_through_autograd(omt, golden, name):
+    """notes/scripts/conv_kinds_check.py and alexnet_ops_check.py: nn.Conv2d forward + backward on the device."""
+    seed, n, ci, co, ks, s, p, hw, groups, bias = CONV[name]
+    x, w, b, gy = cases.conv_inputs(*CONV[name])
+    omt.FALLBACKS.clear()
+    conv = nn.Conv2d(ci, co, ks, stride=s, padding=p, groups=groups, bias=bias)
+    with torch.no_grad():
+        conv.weight.copy_(w)
+        if bias:
+            conv.bias.copy_(b)
+    conv = conv.to(D)
+    xd = x.to(D).requires_grad_()
+    y = conv(xd)
+    y.backward(gy.to(D))
+    assert rel_err(y.detach().cpu().numpy(), golden[f"{name}_y"]) <= TOL
+    assert rel_err(xd.grad.cpu().numpy(), golden[f"{name}_dx"]) <= TOL
+    assert rel_err(conv.weight.grad.cpu().numpy(), golden[f"{name}_dw"]) <= TOL
+    if bias:
+        assert rel_err(conv.bias.grad.cpu().numpy(), golden[f"{name}_db"]) <= TOL
+    assert not omt.FALLBACKS, dict(omt.FALLBACKS)
+    # channels-last input keeps working and stays channels-last
+    ycl = conv(x.to(D).contiguous(memory_format=torch.channels_last))
+    assert rel_err(ycl.detach().cpu().numpy(), golden[f"{name}_y"]) <= TOL
+
+
+def test_unsupported_conv_is_recorded_and_still_correct(omt):
+    omt.FALLBACKS.clear()
+    x, w = torch.randn(2, 4, 9, 9), torch.randn(6, 4, 3, 3)
+    y = F.conv2d(x.to(D), w.to(D), dilation=2)
+    assert e(y, F.conv2d(x, w, dilation=2)) <= TOL
+    assert any(k.startswith("convolution (") for k in omt.FALLBACKS.keys())
+    omt.FALLBACKS.clear()
+
+
+@pytest.mark.parametrize("i", range(len(cases.BN)))
+def test_batchnorm_module(omt, golden, i):
+    n, c, h, w = cases.BN[i]
+    G = lambda k: golden[f"bn{i}_{k}"]
+    bn = nn.BatchNorm2d(c)
+    with torch.no_grad():
+        bn.weight.copy_(cases.rnd(910 + i, c)); bn.bias.copy_(cases.rnd(920 + i, c))
+        bn.running_mean.copy_(cases.rnd(930 + i, c)); bn.running_var.copy_(cases.rnd(940 + i, c).abs() + 0.5)
+    bn = bn.to(D)
+    x = (cases.rnd(900 + i, n, c, h, w) * 2 + 3).to(D).requires_grad_()
+    bn.eval()
+    assert rel_err(bn(x).detach().cpu().numpy(), G("yeval")) <= TOL
+    bn.train()
+    y = bn(x)
+    y.backward(cases.rnd(950 + i, n, c, h, w).to(D))
+    for got, key in ((y, "y"), (x.grad, "dx"), (bn.weight.grad, "dgamma"), (bn.bias.grad, "dbeta"), (bn.running_mean, "rm"), (bn.running_var, "rv")):
+        assert rel_err(got.detach().cpu().numpy(), G(key)) <= TOL, key
+    assert not omt.FALLBACKS, dict(omt.FALLBACKS)
+
+
+def test_pools_through_autograd(omt, golden):
+    for i, (k, s, p, hw) in enumerate(cases.MAXPOOL):
+        x = cases.rnd(700 + i, 2, 4, hw, hw).to(D).requires_grad_()
+        y = F.max_pool2d(x, k, s, p)
+        y.backward(cases.rnd(720 + i, *y.shape).to(D))
+        assert np.array_equal(y.detach().cpu().numpy(), golden[f"maxpool{i}_y"])
+        assert rel_err(x.grad.cpu().numpy(), golden[f"maxpool{i}_gx"]) <= TOL
+    for i, (hw, o) in enumerate(cases.ADAPOOL):
+        x = cases.rnd(800 + i, 2, 5, hw, hw).to(D).requires_grad_()
+        y = F.adaptive_avg_pool2d(x, o)
+        y.backward(cases.rnd(820 + i, *y.shape).to(D))
+        assert rel_err(y.detach().cpu().numpy(), golden[f"adapool{i}_y"]) <= TOL
+        assert rel_err(x.grad.cpu().numpy(), golden[f"adapool{i}_gx"]) <= TOL
+    assert not omt.FALLBACKS, dict(omt.FALLBACKS)
+
+
+OPT = {"sgd_nesterov_wd": lambda p: torch.optim.SGD(p, lr=0.1, momentum=0.9, nesterov=True, weight_decay=1e-4),
+       "sgd_plain": lambda p: torch.optim.SGD(p, lr=0.05),
+       "sgd_damp_max": lambda p: torch.optim.SGD(p, lr=0.05, momentum=0.8, dampening=0.3, maximize=True),
+       "adam_wd": lambda p: torch.optim.Adam(p, lr=1e-3, weight_decay=0.01),
+       "adamw": lambda p: torch.optim.AdamW(p, lr=1e-3, weight_decay=0.01)}
+
+
+@pytest.mark.parametrize("name", sorted(OPT))
+def test_torch_optim_takes_the_fused_kernels(omt, golden, name):
+    from omarchy_mac_torch_b200.native import core
+    p = nn.Parameter(cases.rnd(1000, 37, 11).to(D))
+    opt = OPT[name]([p])
+    assert opt.defaults.get("fused") is True  # optim.py wrapped the constructor
+    core.kernel_counts(True)
+    for it in range(3):
+        p.grad = cases.rnd(1001 + it, 37, 11).to(D)
+        opt.step()
+        assert rel_err(p.detach().cpu().numpy(), golden[f"optim_{name}_p{it}"]) <= 1e-5
+    kc = core.kernel_counts(False)
+    assert kc.get("sgd_multi", 0) + kc.get("adam_multi", 0) == 3
+    assert not omt.FALLBACKS, dict(omt.FALLBACKS)
+
+
+def _train(model, x, y, kind, steps=5):
+    opt = {"sgd": lambda p: torch.optim.SGD(p, lr=0.01, momentum=0.9), "adam": lambda p: torch.optim.Adam(p, lr=1e-3)}[kind](model.parameters())
+    out = []
+    for _ in range(steps + 1):
+        loss = F.cross_entropy(model(x), y)
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+        out.append(loss.item())
+    return out
+
+
+@pytest.mark.parametrize("name,tol", [("plaincnn", 1e-3), ("separablecnn", 1e-3), ("mobilenetv3", 1e-3), ("resnet18", 1e-2)])
+def test_training_matches_reference_loss_curves(omt, golden_losses, name, tol):
+    """tools/acceptance.py: 1 warm-up + 5 steps from the same seed; loss curves must match the CPU curves of the
+    reference's own model classes (tests/golden/losses.json) with no op off the device kernels. ResNet-18's loss falls
+    to 0.04 within 5 steps at lr 0.01, which amplifies rounding differences: the reference itself records 1.6e-3 there
+    (results/acceptance.json) and accepts < 1e-2 (tools/acceptance.py:103)."""
+    from omarchy_mac_torch_b200 import models
+    cls = {"plaincnn": models.PlainCNN, "separablecnn": models.SeparableCNN, "mobilenetv3": models.MobileNetV3Small, "resnet18": models.ResNet18}[name]
+    g = golden_losses[name]
+    torch.manual_seed(0)
+    model = cls()
+    for m in model.modules():
+        if isinstance(m, nn.Dropout):
+            m.p = 0.0
+    assert sum(p.numel() for p in model.parameters()) == g["params"]
+    x, y = torch.randn(*g["shape"]), torch.randint(0, g["classes"], (g["shape"][0],))
+    omt.FALLBACKS.clear()
+    losses = _train(model.to(D), x.to(D), y.to(D), g["optimizer"])
+    diff = max(abs(a - b) / max(abs(b), 1e-6) for a, b in zip(losses, g["losses"]))
+    assert diff <= tol, (diff, losses, g["losses"])
+    assert max(abs(a - b) / max(abs(b), 1e-6) for a, b in zip(losses[:3], g["losses"][:3])) <= 1e-3
+    assert not omt.FALLBACKS, dict(omt.FALLBACKS)
+
+
+def test_fused_stacks_train_eval_and_accumulate(omt):
+    """notes/scripts/native_final_check.py: fused stacks in training, eval with folded BN, gradient accumulation."""
+    from omarchy_mac_torch_b200 import models, stacks
+    for cls, bias in ((models.SeparableCNN, None), (models.PlainCNN, None), (models.PlainCNN3, True), (models.PlainCNN3, False)):
+        torch.manual_seed(0)
+        ref = cls() if bias is None else cls(bias=bias)
+        mod = copy.deepcopy(ref).to(D)
+        o1, o2 = torch.optim.Adam(ref.parameters(), 1e-3), torch.optim.Adam(mod.parameters(), 1e-3)
+        shape = (64, 3, 32, 32) if cls is models.PlainCNN3 else (64, 1, 28, 28)
+        X, y = torch.rand(*shape), torch.randint(0, 10, (64,))
+        for _ in range(3):
+            l1 = F.cross_entropy(ref(X), y, label_smoothing=0.1); o1.zero_grad(); l1.backward(); o1.step()
+            l2 = F.cross_entropy(mod(X.to(D)), y.to(D), label_smoothing=0.1); o2.zero_grad(); l2.backward(); o2.step()
+            assert abs(l1.item() - l2.item()) <= 1e-3 * abs(l1.item())
+        assert type(mod.features) is stacks.FusedSequential
+        for a, b in zip(ref.parameters(), mod.parameters()):
+            assert e(b, a) <= 1e-3
+        for a, b in zip(ref.buffers(), mod.buffers()):
+            assert e(b.float(), a.float()) <= 1e-3  # running stats and num_batches_tracked
+        ref.eval(); mod.eval()
+        Xe = torch.rand(50, *shape[1:])
+        with torch.no_grad():
+            assert e(mod(Xe.to(D)), ref(Xe)) <= 1e-3  # eval plan: BN folded into the conv weights
+    # two backward passes accumulate into .grad (the plan must not overwrite gradients that are still alive)
+    torch.manual_seed(0)
+    ref = models.SeparableCNN(); mod = copy.deepcopy(ref).to(D)
+    for seed in (1, 2):
+        g = torch.Generator().manual_seed(seed)
+        xb, yb = torch.rand(64, 1, 28, 28, generator=g), torch.randint(0, 10, (64,), generator=g)
+        F.cross_entropy(ref(xb), yb).backward()
+        F.cross_entropy(mod(xb.to(D)), yb.to(D)).backward()
+    assert max(e(b.grad, a.grad) for a, b in zip(ref.parameters(), mod.parameters())) <= 1e-3
+    assert not omt.FALLBACKS, dict(omt.FALLBACKS)
+
+
+def test_omt_ops_device_vs_composite(omt):
+    """The omt:: custom ops: device implementation against their composite definition run on the CPU."""
+    omt_ops = torch.ops.omt
+    x = torch.randn(8, 6, 5, 7) * 2 + 1
+    w, b, rm, rv = torch.randn(6), torch.randn(6), torch.randn(6), torch.rand(6) + 0.5
+    ref = omt_ops.bn_relu_train(x, w, b, rm, rv, 0.1, 1e-5)
+    dev = omt_ops.bn_relu_train(*(t.to(D) for t in (x, w, b, rm, rv)), 0.1, 1e-5)
+    for r, d in zip(ref, dev):
+        assert e(d, r) <= TOL
+    assert dev[1].untyped_storage().data_ptr() == dev[2].untyped_storage().data_ptr()  # mean | invstd share one buffer
+    g = torch.randn_like(x)
+    rb = omt_ops.bn_relu_backward(g, x, ref[0], w, ref[1], ref[2], [True, True, True])
+    db = omt_ops.bn_relu_backward(g.to(D), x.to(D), dev[0], w.to(D), dev[1], dev[2], [True, True, True])
+    for r, d in zip(rb, db):
+        assert e(d, r) <= TOL
+    cw, cb = torch.randn(5, 6, 3, 3) * 0.2, torch.randn(5)
+    assert e(omt_ops.conv_act(x.to(D), cw.to(D), cb.to(D), [1, 1], [1, 1], 1), omt_ops.conv_act(x, cw, cb, [1, 1], [1, 1], 1)) <= TOL
+    w5, b5, rm5, rv5 = torch.randn(5), torch.randn(5), torch.randn(5), torch.rand(5) + 0.5
+    r = omt_ops.conv_bn_act_eval(x, cw, cb, w5, b5, rm5, rv5, 1e-5, [2, 2], [1, 1], 1)
+    d = omt_ops.conv_bn_act_eval(*(t.to(D) for t in (x, cw, cb, w5, b5, rm5, rv5)), 1e-5, [2, 2], [1, 1], 1)
+    assert e(d, r) <= TOL
+    assert not omt.FALLBACKS, dict(omt.FALLBACKS)
+
+
+def test_compile_backend(omt):
+    """notes/scripts/compile_check.py: torch.compile(backend="omarchy_mac_torch") gradients and eval output vs CPU."""
+    from omarchy_mac_torch_b200 import models
+    from omarchy_mac_torch_b200.native import core
+    torch.manual_seed(0)
+    ref = models.PlainCNN3(bias=False)
+    mod = copy.deepcopy(ref).to(D)
+    cmod = torch.compile(mod, backend="omarchy_mac_torch")
+    x, y = torch.randn(16, 3, 32, 32), torch.randint(0, 10, (16,))
+    core.kernel_counts(True)
+    F.cross_entropy(ref(x), y).backward()
+    F.cross_entropy(cmod(x.to(D)), y.to(D)).backward()
+    assert max(e(b.grad, a.grad) for a, b in zip(ref.parameters(), mod.parameters())) <= 1e-3
+    ref.eval(); mod.eval()
+    with torch.no_grad():
+        assert e(torch.compile(mod, backend="omarchy_mac_torch")(x.to(D)), ref(x)) <= 1e-3

@@ -1,0 +1,115 @@
+"""Host-side logic that needs no GPU: stack eligibility rules and layer specs (omarchy_mac_torch/stacks.py:41-94), the
+fused-optimizer constructor rule (optim.py:15-31), the FX rewrite passes (compile.py:69-161) exercised on CPU graphs
+through the ops' composite definitions, and the workload model definitions against the golden loss curves."""
+import copy
+
+import pytest
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+
+@pytest.fixture(scope="module")
+def pkg():
+    import omarchy_mac_torch_b200 as m
+    m.DEVICE  # loads the extension and registers the device (no CUDA call happens until a tensor is allocated)
+    return m
+
+
+def test_device_is_registered_and_fails_loudly_without_a_gpu(pkg):
+    assert pkg.DEVICE == "omarchy_mac_torch" and hasattr(torch, "omarchy_mac_torch") and torch.omarchy_mac_torch.device_count() == 1
+    import omarchy_mac_torch  # the reference's import name resolves to this package
+    assert omarchy_mac_torch is pkg
+    if not torch.cuda.is_available():
+        with pytest.raises(RuntimeError, match="no CUDA device"):
+            torch.empty(2, device=pkg.DEVICE)
+    assert pkg.validate_kernels() == [] and pkg.tune_cpu() is None and len(pkg.FALLBACKS) == 0
+
+
+def test_fusable_rules(pkg):
+    from omarchy_mac_torch_b200 import models, stacks
+    cbr = lambda ci, co, **kw: [nn.Conv2d(ci, co, 3, padding=1, bias=False, **kw), nn.BatchNorm2d(co), nn.ReLU()]
+    assert stacks.fusable(nn.Sequential(*cbr(3, 8), nn.MaxPool2d(2)))
+    assert stacks.fusable(nn.Sequential(*cbr(3, 8), *cbr(8, 8, groups=8), nn.AvgPool2d(2), nn.AdaptiveAvgPool2d(1)))
+    assert stacks.fusable(nn.Sequential(nn.Conv2d(3, 8, 3, padding=1, bias=True), nn.BatchNorm2d(8), nn.ReLU()))  # bias accepted here
+    assert not stacks.fusable(nn.Sequential())
+    assert not stacks.fusable(nn.Sequential(nn.BatchNorm2d(3), nn.ReLU()))                                # must start with a conv
+    assert not stacks.fusable(nn.Sequential(nn.Conv2d(3, 8, 3, padding=1), nn.BatchNorm2d(8)))             # BN without ReLU
+    assert not stacks.fusable(nn.Sequential(nn.Conv2d(3, 8, 3, padding=1), nn.BatchNorm2d(8, eps=1e-3), nn.ReLU()))
+    assert not stacks.fusable(nn.Sequential(nn.Conv2d(3, 8, 3, stride=2, padding=1)))                      # strided
+    assert not stacks.fusable(nn.Sequential(nn.Conv2d(3, 8, 7, padding=3)))                                # dense 7x7 not in a plan
+    assert not stacks.fusable(nn.Sequential(nn.Conv2d(3, 8, 3, padding=1), nn.MaxPool2d(3, 2)))
+    assert not stacks.fusable(nn.Sequential(nn.Conv2d(3, 8, 3, padding=1), nn.AdaptiveAvgPool2d(2)))
+    assert not stacks.fusable(nn.Sequential(nn.Conv2d(4, 8, 3, padding=1, groups=2)))                      # grouped, not depthwise
+    assert not stacks.fusable(nn.Sequential(nn.Conv2d(3, 8, 3, padding=1), nn.Hardswish()))
+    m = models.PlainCNN3()
+    assert stacks.layer_specs(m.features)[:3] == [("convb", 3, 32, 3, 0.0), ("bn", 32, 32, 0, 0.1), ("pool", 0, 0, 0, 0.0)]
+    assert [tuple(p.shape) for p in stacks._params(m.features)][:4] == [(32, 3, 3, 3), (32,), (32,), (32,)]
+    sep = models.SeparableCNN()
+    kinds = [s[0] for s in stacks.layer_specs(sep.features)]
+    assert kinds.count("dw") == 4 and kinds[-1] == "gap" and kinds.count("pool") == 2
+    assert not stacks.fusable(models.ResNet18().stem)  # 7x7 stride-2 stem stays eager
+
+
+def test_optimizer_constructor_rule(pkg):
+    from omarchy_mac_torch_b200 import optim
+
+    class P:  # stands in for a parameter on the device
+        def __init__(self, dev):
+            self.device = torch.device(dev)
+    on, off = [P("omarchy_mac_torch:0")], [P("cpu")]
+    assert optim.wants_fused(on, {})
+    assert optim.wants_fused([{"params": on}], {"lr": 0.1})
+    assert not optim.wants_fused(off, {}) and not optim.wants_fused(on + off, {}) and not optim.wants_fused([], {})
+    assert not optim.wants_fused(on, {"fused": False}) and not optim.wants_fused(on, {"foreach": True})
+    assert not optim.wants_fused(on, {"differentiable": True}) and not optim.wants_fused(on, {"lr": torch.tensor(0.1)})
+    assert torch.optim.SGD([nn.Parameter(torch.zeros(2))], lr=0.1).defaults.get("fused") in (None, False)  # CPU params untouched
+
+
+def test_fx_passes_rewrite_and_preserve_results(pkg, monkeypatch):
+    """Passes 1-3 on CPU graphs (the omt:: ops' composite definitions run anywhere), compared with the unrewritten graph."""
+    from torch._dynamo.backends.common import aot_autograd
+    from functorch.compile import make_boxed_func
+    from omarchy_mac_torch_b200 import compile as C, models
+    monkeypatch.setattr(C, "_ANY_DEVICE", True)
+    seen = []
+
+    def compiler(gm, _inputs):
+        seen.append(C.rewrite(gm))
+        return make_boxed_func(gm.forward)
+
+    backend = aot_autograd(fw_compiler=compiler, bw_compiler=compiler, inference_compiler=compiler)
+    torch.manual_seed(0)
+    ref = models.PlainCNN3(bias=False)
+    mod = copy.deepcopy(ref)
+    x, y = torch.randn(8, 3, 32, 32), torch.randint(0, 10, (8,))
+    F.cross_entropy(ref(x), y).backward()
+    F.cross_entropy(torch.compile(mod, backend=backend)(x), y).backward()
+    assert sum(s["bn_relu"] for s in seen) == 3 and sum(s["bn_relu_backward"] for s in seen) == 3
+    for a, b in zip(ref.parameters(), mod.parameters()):
+        assert torch.allclose(a.grad, b.grad, rtol=1e-4, atol=1e-6)
+    for a, b in zip(ref.buffers(), mod.buffers()):
+        assert torch.allclose(a.float(), b.float(), rtol=1e-5, atol=1e-6)
+    seen.clear()
+    ref.eval(); mod.eval()
+    torch._dynamo.reset()
+    with torch.no_grad():
+        out = torch.compile(mod, backend=backend)(x)
+        assert torch.allclose(out, ref(x), rtol=1e-4, atol=1e-5)
+    assert sum(s["conv_epilogue"] for s in seen) == 3  # conv -> eval BN -> ReLU folded three times
+
+
+def test_model_definitions_reproduce_reference_curves(pkg, golden_losses):
+    """This package's PlainCNN / SeparableCNN register parameters in the reference's order: same seed, same CPU loss curve."""
+    from omarchy_mac_torch_b200 import models
+    for name, cls in (("plaincnn", models.PlainCNN), ("separablecnn", models.SeparableCNN)):
+        g = golden_losses[name]
+        torch.manual_seed(0)
+        m = cls()
+        x, y = torch.randn(*g["shape"]), torch.randint(0, g["classes"], (g["shape"][0],))
+        opt = torch.optim.SGD(m.parameters(), lr=0.01, momentum=0.9)
+        out = []
+        for _ in range(3):
+            loss = F.cross_entropy(m(x), y); opt.zero_grad(); loss.backward(); opt.step(); out.append(loss.item())
+        assert max(abs(a - b) / abs(b) for a, b in zip(out, g["losses"][:3])) < 1e-5
+    assert sum(p.numel() for p in models.ResNet50().parameters()) == 25557032
