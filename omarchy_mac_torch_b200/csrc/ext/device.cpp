@@ -201,8 +201,22 @@ static Tensor copy_from_impl(const Tensor& self, const Tensor& dst, bool non_blo
   b.copy_(a, non_blocking);
   return dst;
 }
+static void grow_storage(const c10::Storage& storage, size_t newsize);  // below, with the hooks
+
+// resize_ for device tensors. ATen's generic implementation grows the storage with a host memcpy, which cannot touch
+// device memory, so the growth goes through the allocator and a device copy here.
+static const Tensor& resize_impl(const Tensor& self, IntArrayRef size, std::optional<at::MemoryFormat> mf) {
+  auto* impl = self.unsafeGetTensorImpl();
+  int64_t numel = 1;
+  for (int64_t d : size) numel *= d;
+  size_t need = (size_t)(impl->storage_offset() + numel) * impl->dtype().itemsize();
+  if (numel > 0 && need > impl->unsafe_storage().nbytes()) grow_storage(impl->unsafe_storage(), need);
+  impl->set_sizes_contiguous(size);
+  if (mf && *mf != at::MemoryFormat::Preserve && *mf != at::MemoryFormat::Contiguous) impl->empty_tensor_restride(*mf);
+  return self;
+}
 static Tensor copy_from_and_resize_impl(const Tensor& self, const Tensor& dst) {
-  at::native::resize_(dst, self.sizes(), std::nullopt);
+  resize_impl(dst, self.sizes(), std::nullopt);
   return copy_from_impl(self, dst, false);
 }
 static c10::Scalar local_scalar(const Tensor& self) {
@@ -287,15 +301,16 @@ struct Hooks final : at::PrivateUse1HooksInterface {
   const at::Generator& getDefaultGenerator(c10::DeviceIndex) const override { return default_generator(); }
   at::Generator getNewGenerator(c10::DeviceIndex i) const override { return at::make_generator<Generator>(i < 0 ? 0 : i); }
   at::Device getDeviceFromPtr(void*) const override { return {kDev, 0}; }
-  void resizePrivateUse1Bytes(const c10::Storage& storage, size_t newsize) const override {
-    ensure_init();
-    c10::DataPtr fresh = newsize ? g_alloc.allocate(newsize) : c10::DataPtr(nullptr, c10::Device(kDev, 0));
-    size_t keep = std::min(newsize, storage.nbytes());
-    if (keep && storage.data()) check(omt_memcpy_d2d(fresh.get(), storage.data(), keep, cur_stream()), "storage resize");
-    storage.unsafeGetStorageImpl()->set_data_ptr_noswap(std::move(fresh));
-    storage.unsafeGetStorageImpl()->set_nbytes(newsize);
-  }
+  void resizePrivateUse1Bytes(const c10::Storage& storage, size_t newsize) const override { grow_storage(storage, newsize); }
 };
+static void grow_storage(const c10::Storage& storage, size_t newsize) {
+  ensure_init();
+  c10::DataPtr fresh = newsize ? g_alloc.allocate(newsize) : c10::DataPtr(nullptr, c10::Device(kDev, 0));
+  size_t keep = std::min(newsize, storage.nbytes());
+  if (keep && storage.data()) check(omt_memcpy_d2d(fresh.get(), storage.data(), keep, cur_stream()), "storage resize");
+  storage.unsafeGetStorageImpl()->set_data_ptr_noswap(std::move(fresh));
+  storage.unsafeGetStorageImpl()->set_nbytes(newsize);
+}
 static struct HooksRegistrar {
   HooksRegistrar() {
     static Hooks hooks;
@@ -336,6 +351,16 @@ struct AliasMap {
     dev.push_back(t);
     cuda.push_back(cuda_alias(t));
     return cuda.back();
+  }
+  // out= arguments that arrive empty are resized by the ATen kernel: give the device tensor the new storage and shape
+  void adopt_resized() {
+    for (size_t i = 0; i < dev.size(); i++) {
+      if (dev[i].numel() != 0 || cuda[i].numel() == 0) continue;
+      Tensor w = wrap_cuda(cuda[i]);
+      auto* impl = dev[i].unsafeGetTensorImpl();
+      impl->set_storage_keep_dtype(w.storage());
+      impl->set_sizes_and_strides(cuda[i].sizes(), cuda[i].strides(), cuda[i].storage_offset());
+    }
   }
   Tensor to_dev(const Tensor& c) {
     if (!c.defined() || !c.is_cuda()) return c;
@@ -390,6 +415,7 @@ static void bridge_impl(const c10::OperatorHandle& op, torch::jit::Stack* stack,
     }
   }
   op.redispatchBoxed(c10::DispatchKeySet(c10::DispatchKey::CUDA), stack);
+  map.adopt_resized();
   const size_t nret = schema.returns().size(), rbegin = stack->size() - nret;
   for (size_t i = 0; i < nret; i++) {
     c10::IValue& v = (*stack)[rbegin + i];
@@ -418,7 +444,7 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
   m.impl("_unsafe_view", &at::native::_unsafe_view);
   m.impl("as_strided", &at::native::as_strided_tensorimpl);
   m.impl("_reshape_alias", &at::native::_reshape_alias);
-  m.impl("resize_", &at::native::resize_);
+  m.impl("resize_", &resize_impl);
   m.impl("unfold", &at::native::unfold);  // views cannot go through the bridge's alias rebuild safely: explicit impls
   m.impl("view_as_real", &at::native::view_as_real);
   m.impl("view_as_complex", &at::native::view_as_complex);
