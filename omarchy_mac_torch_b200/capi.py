@@ -179,8 +179,8 @@ def kernel_counts(reset=False):
 
 def _empty(shape, like, cl=False):
     import torch
-    t = torch.empty(shape, device=like.device, dtype=torch.float32)
-    return t.contiguous(memory_format=torch.channels_last) if cl and len(shape) == 4 else t
+    fmt = torch.channels_last if cl and len(shape) == 4 else torch.contiguous_format
+    return torch.empty(shape, device=like.device, dtype=torch.float32, memory_format=fmt)
 
 
 def conv_fwd(x, w, bias=None, stride=1, pad=0, flags=0, cl=False, stats=None):

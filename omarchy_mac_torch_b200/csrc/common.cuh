@@ -35,6 +35,7 @@ inline cudaStream_t st(omt_stream_t s) { return (cudaStream_t)s; }
 inline int64_t cdiv(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
 int sm_count();  // SMs of the current device (148 on B200)
+int tc_error_word();  // conv_tc.cu: non-zero once a tensor-core kernel gave up on a bounded wait (-1: cannot read)
 
 // Scratch from the library's own caching allocator, returned to the pool when the guard dies. The pool is
 // stream-ordered: a block freed right after the launch is only handed to later work on the same stream.

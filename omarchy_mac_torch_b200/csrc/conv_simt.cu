@@ -56,6 +56,24 @@ struct Fwd {
   // 4 consecutive rows (m..m+3) x 4 consecutive columns (nn..nn+3)
   __device__ void store(int m, int nn, const float (&v)[4][4]) const {
     int ohw = g.oh * g.ow;
+    if (g.b.sc == 1 && nn + 3 < N) {  // channels-last output: the 4 columns of a row are contiguous
+      float bv[4];
+#pragma unroll
+      for (int j = 0; j < 4; j++) bv[j] = (g.flags & OMT_EPI_BIAS) ? __ldg(g.bias + nn + j) : 0.f;
+      bool done = true;
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        int mm = m + i;
+        if (mm >= M) break;
+        int im2 = mm / ohw, r2 = mm - im2 * ohw, oy = r2 / g.ow, ox = r2 - oy * g.ow;
+        float* p = g.b.p + g.b.off(im2, nn, oy, ox);
+        if (reinterpret_cast<uintptr_t>(p) & 15) { done = false; break; }
+        float4 o = make_float4(v[i][0] + bv[0], v[i][1] + bv[1], v[i][2] + bv[2], v[i][3] + bv[3]);
+        if (g.flags & OMT_EPI_RELU) o = make_float4(fmaxf(o.x, 0.f), fmaxf(o.y, 0.f), fmaxf(o.z, 0.f), fmaxf(o.w, 0.f));
+        *reinterpret_cast<float4*>(p) = o;
+      }
+      if (done) return;
+    }
 #pragma unroll
     for (int j = 0; j < 4; j++) {
       int c = nn + j;

@@ -1,20 +1,484 @@
-// Tensor-core (tcgen05 / TMEM / TMA) implicit-GEMM convolution. Placeholder until the kernels land: reports every
-// geometry as unsupported so the exact-fp32 CUDA-core path serves it.
+// Tensor-core implicit-GEMM convolution for sm_100a: tcgen05.mma (kind::tf32) with the accumulator in TMEM, operands
+// staged in shared memory by TMA (im2col-mode loads for the activation operand, tiled loads for the weights), and a
+// 3xTF32 split so float32 accuracy holds:  a*b ~= a_lo*b_hi + a_hi*b_lo + a_hi*b_hi  with x_hi = tf32(x), x_lo = tf32(x - x_hi).
+//
+// GEMM view (forward): D[m, co] = sum_k A[m, k] * W[co, k],  m = (img, oy, ox),  k = (ky, kx, c) with c innermost in
+// blocks of 32 floats (one 128-byte swizzle row). The activation must be channels-last with c % 4 == 0 so that a pixel's
+// channel run starts on a 16-byte boundary (a TMA requirement). Weights are re-laid out per call into [2][co][ky][kx][c
+// padded to 32] (hi and lo planes, zero padded) by a small kernel; they are tiny next to the activations.
+//
+// One CTA computes a 128 x BN output tile. Warp roles (192 threads):
+//   warp 0       TMA producer: per k-block one im2col load of A (128 pixels x 32 channels of one filter tap) and two tiled
+//                loads of W (hi and lo planes), all completing on the stage's "loaded" mbarrier
+//   warp 1       allocates TMEM; one lane issues the MMAs: per 8-wide k-step three tcgen05.mma, then tcgen05.commit to
+//                free the stage; a final commit signals the epilogue
+//   warps 2..5   split A in place into hi (tf32-rounded) and lo, arrive on the stage's "split" mbarrier; afterwards they are
+//                the epilogue: tcgen05.ld of their 32-lane quarter of the accumulator, bias / ReLU, store in the output's layout
+// Every mbarrier wait is bounded by a clock budget; on expiry the kernel raises an error word, all roles leave their loops,
+// TMEM is freed and the kernel returns (the host reports it as a failed launch at the next synchronisation).
+//
+// The input gradient of a stride-1 convolution is the same kernel: a forward convolution of gy with the weights transposed
+// and flipped (done by the weight re-layout kernel). Replaces the reference's generated kinds 0 and 1
+// (omarchy_mac_torch/gemm.py:25-59) for the geometries it accepts; everything else stays on the exact-fp32 path.
+#include <cuda.h>
+
+#include <algorithm>
+#include <mutex>
+
 #include "common.cuh"
 
 namespace omt {
-bool tc_supported(int, const OmtConvGeo*, const OmtAct*, const OmtAct*) { return false; }
-size_t tc_workspace(int, const OmtConvGeo*) { return 0; }
-int tc_conv_fwd(const OmtConvGeo*, const OmtAct*, const float*, const float*, const OmtAct*, float*, uint32_t, void*, cudaStream_t) {
-  set_error("tensor-core path not built");
-  return OMT_EINVAL;
+
+namespace {
+
+constexpr int BM = 128;        // output pixels per tile (UMMA M)
+constexpr int BKF = 32;        // floats per k-block (128 bytes)
+constexpr int UMMA_K = 8;      // tf32 MMA depth
+constexpr int TC_THREADS = 192;
+constexpr long long WAIT_BUDGET_CLOCKS = 2000000000ll;  // ~1 s at B200 clocks
+
+__device__ int g_tc_error = 0;  // first failure: 1 = mbarrier wait expired
+
+// ---------------------------------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
-int tc_conv_dgrad(const OmtConvGeo*, const OmtAct*, const float*, const OmtAct*, void*, cudaStream_t) {
-  set_error("tensor-core path not built");
-  return OMT_EINVAL;
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait. Returns false when the budget expired or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 256; i++)
+      if (mbar_try(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > WAIT_BUDGET_CLOCKS) {
+      *abort_flag = 1;
+      atomicCAS(&g_tc_error, 0, 1);
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ void tma_im2col_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c, int w, int h, int n, uint16_t ow,
+                                              uint16_t oh) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n), "h"(ow), "h"(oh)
+      : "memory");
+}
+__device__ __forceinline__ void tma_tile_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+               ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, "
+      "%20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float tf32_rna(float x) {
+  uint32_t u;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
+  return __uint_as_float(u);
+}
+
+// K-major operand tile with 128-byte rows and the 128B swizzle: 8-row atoms of 1024 bytes.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFF) >> 4);        // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                        // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset: next 8-row atom
+  d |= (uint64_t)1 << 46;                        // descriptor version (sm_100)
+  d |= (uint64_t)2 << 61;                        // SWIZZLE_128B
+  return d;
+}
+constexpr uint32_t idesc_tf32(int n) {
+  return (1u << 4) /* D = f32 */ | (2u << 7) /* A = tf32 */ | (2u << 10) /* B = tf32 */ | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+struct TcArgs {
+  ActView y;          // output activation (any strides)
+  const float* bias;
+  int M, N;           // GEMM extents: pixels, output channels
+  int oh, ow;         // output plane (to decompose m)
+  int ks, stride, pad;
+  int cblocks;        // 32-channel blocks per tap
+  int cpad;           // cblocks * 32
+  uint32_t flags;
+};
+
+template <int BN>
+struct Smem {
+  static constexpr int STAGES = BN == 256 ? 2 : (BN == 128 ? 3 : 4);
+  static constexpr int A_BYTES = BM * 128, B_BYTES = BN * 128;
+  static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
+  static constexpr int BAR_OFF = STAGES * STAGE_BYTES;
+  static constexpr int TOTAL = BAR_OFF + 256 + 1024;  // barriers + alignment slack
+};
+
+// ---------------------------------------------------------------------------------------------------------------------
+// the kernel
+// ---------------------------------------------------------------------------------------------------------------------
+template <int BN>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const TcArgs g) {
+  using S = Smem<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const uint32_t smem_base = smem_u32(smem);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::BAR_OFF);
+  // barrier indices: [0,S) loaded, [S,2S) split, [2S,3S) free, 3S accumulator ready
+  const uint32_t bar0 = smem_u32(bars);
+  auto BAR = [&](int i) { return bar0 + 8u * i; };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 3 * S::STAGES + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 3 * S::STAGES + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+  const int kblocks = g.ks * g.ks * g.cblocks;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S::STAGES; s++) {
+      mbar_init(BAR(s), 1);                    // loaded: one arrive.expect_tx + TMA bytes
+      mbar_init(BAR(S::STAGES + s), 4);        // split: one arrival per transform warp
+      mbar_init(BAR(2 * S::STAGES + s), 1);    // free: tcgen05.commit
+    }
+    mbar_init(BAR(3 * S::STAGES), 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {  // TMEM: BN fp32 columns (power of two >= 32)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"((uint32_t)BN)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_acc = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      const int ohw = g.oh * g.ow;
+      const int img0 = m0 / ohw, r0 = m0 - img0 * ohw, oy0 = r0 / g.ow, ox0 = r0 - oy0 * g.ow;
+      const int w0 = ox0 * g.stride - g.pad, h0 = oy0 * g.stride - g.pad;
+      int issued = 0;
+      for (int kb = 0; kb < kblocks; kb++) {
+        const int s = kb % S::STAGES, round = kb / S::STAGES;
+        if (round > 0 && !mbar_wait(BAR(2 * S::STAGES + s), (round - 1) & 1, abort_flag)) break;
+        const int tap = kb / g.cblocks, cb = kb - tap * g.cblocks;
+        const int ky = tap / g.ks, kx = tap - ky * g.ks;
+        const uint32_t stage = smem_base + s * S::STAGE_BYTES;
+        mbar_expect_tx(BAR(s), S::A_BYTES + 2 * S::B_BYTES);
+        tma_im2col_4d(stage, &map_a, BAR(s), cb * BKF, w0, h0, img0, (uint16_t)kx, (uint16_t)ky);
+        tma_tile_3d(stage + 2 * S::A_BYTES, &map_w, BAR(s), tap * g.cpad + cb * BKF, n0, 0);
+        tma_tile_3d(stage + 2 * S::A_BYTES + S::B_BYTES, &map_w, BAR(s), tap * g.cpad + cb * BKF, n0, 1);
+        issued = kb + 1;
+      }
+      if (*abort_flag) {  // drain: let the copies already in flight land before the CTA exits (bounded)
+        for (int kb = max(0, issued - S::STAGES); kb < issued; kb++) {
+          const long long t0 = clock64();
+          while (!mbar_try(BAR(kb % S::STAGES), (kb / S::STAGES) & 1) && clock64() - t0 < WAIT_BUDGET_CLOCKS) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = idesc_tf32(BN);
+      bool ok = true;
+      for (int kb = 0; kb < kblocks && ok; kb++) {
+        const int s = kb % S::STAGES, round = kb / S::STAGES;
+        ok = mbar_wait(BAR(S::STAGES + s), round & 1, abort_flag) && mbar_wait(BAR(s), round & 1, abort_flag);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t stage = smem_base + s * S::STAGE_BYTES;
+        const uint64_t a_hi = smem_desc_sw128(stage), a_lo = smem_desc_sw128(stage + S::A_BYTES);
+        const uint64_t b_hi = smem_desc_sw128(stage + 2 * S::A_BYTES), b_lo = smem_desc_sw128(stage + 2 * S::A_BYTES + S::B_BYTES);
+#pragma unroll
+        for (int k = 0; k < BKF / UMMA_K; k++) {
+          const uint64_t adv = (uint64_t)((k * UMMA_K * 4) >> 4);  // 32 bytes per k-step inside the swizzled row
+          umma_tf32(tmem_acc, a_lo + adv, b_hi + adv, idesc, (kb | k) ? 1u : 0u);
+          umma_tf32(tmem_acc, a_hi + adv, b_lo + adv, idesc, 1u);
+          umma_tf32(tmem_acc, a_hi + adv, b_hi + adv, idesc, 1u);
+        }
+        umma_commit(BAR(2 * S::STAGES + s));  // stage is free once these MMAs have read it
+      }
+      if (ok) umma_commit(BAR(3 * S::STAGES));  // accumulator complete
+    }
+  } else {
+    // ---------------- operand split (warps 2..5), then epilogue ----------------
+    const int t = threadIdx.x - 64;  // 0..127
+    bool ok = true;
+    for (int kb = 0; kb < kblocks && ok; kb++) {
+      const int s = kb % S::STAGES, round = kb / S::STAGES;
+      ok = mbar_wait(BAR(s), round & 1, abort_flag);
+      if (!ok) break;
+      uint4* hi = reinterpret_cast<uint4*>(smem + s * S::STAGE_BYTES);
+      uint4* lo = reinterpret_cast<uint4*>(smem + s * S::STAGE_BYTES + S::A_BYTES);
+#pragma unroll
+      for (int i = 0; i < S::A_BYTES / 16 / 128; i++) {
+        const int idx = i * 128 + t;
+        uint4 v = hi[idx], h, l;
+        float f0 = __uint_as_float(v.x), f1 = __uint_as_float(v.y), f2 = __uint_as_float(v.z), f3 = __uint_as_float(v.w);
+        float h0 = tf32_rna(f0), h1 = tf32_rna(f1), h2 = tf32_rna(f2), h3 = tf32_rna(f3);
+        h.x = __float_as_uint(h0); h.y = __float_as_uint(h1); h.z = __float_as_uint(h2); h.w = __float_as_uint(h3);
+        l.x = __float_as_uint(tf32_rna(f0 - h0)); l.y = __float_as_uint(tf32_rna(f1 - h1));
+        l.z = __float_as_uint(tf32_rna(f2 - h2)); l.w = __float_as_uint(tf32_rna(f3 - h3));
+        hi[idx] = h;
+        lo[idx] = l;
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the tensor core
+      __syncwarp();
+      if (lane == 0) mbar_arrive(BAR(S::STAGES + s));
+    }
+    // epilogue
+    if (ok) ok = mbar_wait(BAR(3 * S::STAGES), 0, abort_flag);
+    if (ok) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int q = warp & 3;  // TMEM lane quarter this warp may read
+      const int m = m0 + q * 32 + lane;
+      const int ohw = g.oh * g.ow;
+      const int img = m / ohw, r = m - img * ohw, oy = r / g.ow, ox = r - oy * g.ow;
+      float* yrow = g.y.p + g.y.off(img, 0, oy, ox);
+      const bool vec = g.y.sc == 1 && ((reinterpret_cast<uintptr_t>(yrow) & 15) == 0);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; c++) {
+        uint32_t v[32];
+        tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + c * 32, v);
+        if (m >= g.M) continue;
+        const int nb = n0 + c * 32;
+        if (nb >= g.N) continue;
+        float o[32];
+#pragma unroll
+        for (int j = 0; j < 32; j++) {
+          float x = __uint_as_float(v[j]);
+          if ((g.flags & OMT_EPI_BIAS) && nb + j < g.N) x += __ldg(g.bias + nb + j);
+          if (g.flags & OMT_EPI_RELU) x = fmaxf(x, 0.f);
+          o[j] = x;
+        }
+        if (vec && nb + 32 <= g.N) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(yrow + nb + j) = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; j++)
+            if (nb + j < g.N) yrow[(int64_t)(nb + j) * g.y.sc] = o[j];
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"((uint32_t)BN) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// weight re-layout: w[co][ci][ks][ks] -> out[2][rows][ks*ks][cpad], hi and lo planes, zero padded
+//   forward:  rows = co, channel = ci, tap (ky, kx)
+//   dgrad:    rows = ci, channel = co, tap (ks-1-ky, ks-1-kx)   (transposed and flipped)
+// ---------------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) weight_split_kernel(const float* __restrict__ w, float* __restrict__ out, int co, int ci, int ks,
+                                                           int cpad, bool dgrad) {
+  const int rows = dgrad ? ci : co, chans = dgrad ? co : ci, kk = ks * ks;
+  const int64_t total = (int64_t)rows * kk * cpad;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int c = (int)(i % cpad);
+  const int tap = (int)((i / cpad) % kk);
+  const int row = (int)(i / ((int64_t)cpad * kk));
+  float v = 0.f;
+  if (c < chans) {
+    int ky = tap / ks, kx = tap - ky * ks;
+    if (dgrad) v = __ldg(w + (((int64_t)c * ci + row) * ks + (ks - 1 - ky)) * ks + (ks - 1 - kx));
+    else v = __ldg(w + (((int64_t)row * ci + c) * ks + ky) * ks + kx);
+  }
+  const float hi = tf32_rna(v);
+  out[i] = hi;
+  out[total + i] = tf32_rna(v - hi);
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+typedef CUresult (*EncodeIm2colFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const int*, const int*,
+                                   cuuint32_t, cuuint32_t, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                   CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode_tiled = nullptr;
+EncodeIm2colFn g_encode_im2col = nullptr;
+std::once_flag g_driver_once;
+
+bool load_driver_entry_points() {
+  std::call_once(g_driver_once, [] {
+    cudaDriverEntryPointQueryResult q;
+    void* fn = nullptr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      g_encode_tiled = (EncodeTiledFn)fn;
+    fn = nullptr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &fn, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      g_encode_im2col = (EncodeIm2colFn)fn;
+    (void)cudaGetLastError();
+  });
+  return g_encode_tiled && g_encode_im2col;
+}
+
+struct TcProblem {  // a stride-`stride` convolution of a channels-last activation `a` [n, ih, iw, c] producing [n, oh, ow, rows]
+  const float* a;
+  int n, c, ih, iw, oh, ow, rows, ks, stride, pad;
+};
+
+int pick_bn(const TcProblem& p) {
+  if (p.rows <= 64) return 64;
+  if (p.rows <= 128) return 128;
+  int64_t mt = cdiv((int64_t)p.n * p.oh * p.ow, BM);
+  return (mt * cdiv(p.rows, 256) >= sm_count()) ? 256 : 128;
+}
+
+template <int BN>
+int launch_tc(const TcProblem& p, const float* wsplit, const TcArgs& args, cudaStream_t s) {
+  using S = Smem<BN>;
+  alignas(64) CUtensorMap map_a, map_w;
+  {
+    cuuint64_t dims[4] = {(cuuint64_t)p.c, (cuuint64_t)p.iw, (cuuint64_t)p.ih, (cuuint64_t)p.n};
+    cuuint64_t strides[3] = {(cuuint64_t)p.c * 4, (cuuint64_t)p.iw * p.c * 4, (cuuint64_t)p.ih * p.iw * p.c * 4};
+    int lower[2] = {-p.pad, -p.pad};
+    int upper[2] = {p.pad - (p.ks - 1), p.pad - (p.ks - 1)};
+    cuuint32_t estr[4] = {1, (cuuint32_t)p.stride, (cuuint32_t)p.stride, 1};
+    CUresult r = g_encode_im2col(&map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void*)p.a, dims, strides, lower, upper, BKF, BM, estr,
+                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+      set_error("cuTensorMapEncodeIm2col failed (%d)", (int)r);
+      return OMT_ECUDA;
+    }
+  }
+  {
+    const int kp = p.ks * p.ks * args.cpad;
+    cuuint64_t dims[3] = {(cuuint64_t)kp, (cuuint64_t)p.rows, 2};
+    cuuint64_t strides[2] = {(cuuint64_t)kp * 4, (cuuint64_t)kp * 4 * p.rows};
+    cuuint32_t box[3] = {BKF, (cuuint32_t)BN, 1}, estr[3] = {1, 1, 1};
+    CUresult r = g_encode_tiled(&map_w, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)wsplit, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+      set_error("cuTensorMapEncodeTiled failed (%d)", (int)r);
+      return OMT_ECUDA;
+    }
+  }
+  static bool attr_set = false;
+  if (!attr_set) {
+    OMT_CUDA(cudaFuncSetAttribute(conv_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
+    attr_set = true;
+  }
+  dim3 grid((unsigned)cdiv(args.M, BM), (unsigned)cdiv(args.N, BN));
+  conv_tc_kernel<BN><<<grid, TC_THREADS, S::TOTAL, s>>>(map_a, map_w, args);
+  return check_launch(BN == 64 ? "conv_tc_128x64" : (BN == 128 ? "conv_tc_128x128" : "conv_tc_128x256"));
+}
+
+size_t split_floats(int rows, int ks, int chans) { return (size_t)2 * rows * ks * ks * (cdiv(chans, BKF) * BKF); }
+
+int run_tc(const TcProblem& p, const float* w, bool dgrad, int co, int ci, const OmtAct* y, const float* bias, uint32_t flags, void* ws,
+           cudaStream_t s) {
+  if (!load_driver_entry_points()) {
+    set_error("the CUDA driver does not export cuTensorMapEncodeTiled/Im2col");
+    return OMT_ECUDA;
+  }
+  float* wsplit = (float*)ws;
+  TcArgs a{};
+  a.y = view(y); a.bias = bias;
+  a.M = p.n * p.oh * p.ow; a.N = p.rows; a.oh = p.oh; a.ow = p.ow;
+  a.ks = p.ks; a.stride = p.stride; a.pad = p.pad;
+  a.cblocks = (int)cdiv(p.c, BKF); a.cpad = a.cblocks * BKF;
+  a.flags = flags;
+  const int64_t total = (int64_t)p.rows * p.ks * p.ks * a.cpad;
+  weight_split_kernel<<<(unsigned)cdiv(total, 256), 256, 0, s>>>(w, wsplit, co, ci, p.ks, a.cpad, dgrad);
+  int r = check_launch("conv_tc_weight_split");
+  if (r) return r;
+  switch (pick_bn(p)) {
+    case 64: return launch_tc<64>(p, wsplit, a, s);
+    case 128: return launch_tc<128>(p, wsplit, a, s);
+    default: return launch_tc<256>(p, wsplit, a, s);
+  }
+}
+
+bool cl_ok(const OmtAct* a, int c, int h, int w) {
+  return a && a->p && is_nhwc(a, c, h, w) && c % 4 == 0 && (reinterpret_cast<uintptr_t>(a->p) & 15) == 0;
+}
+
+}  // namespace
+
+int tc_error_word() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_tc_error, sizeof(int)) != cudaSuccess) return -1;
+  return v;
+}
+
+// kind 0: a = x, b = y.  kind 1: a = gy, b = dx.  kind 2: weight gradient (not on this path yet)
+bool tc_supported(int kind, const OmtConvGeo* g, const OmtAct* a, const OmtAct* b) {
+  if (!b || !b->p) return false;
+  if (kind == 0) return cl_ok(a, g->ci, g->ih, g->iw) && g->ci >= 8 && g->co >= 8 && g->pad < g->ks;
+  if (kind == 1) return g->stride == 1 && cl_ok(a, g->co, g->oh, g->ow) && g->co >= 8 && g->ci >= 8 && g->ks - 1 - g->pad >= 0;
+  return false;
+}
+size_t tc_workspace(int kind, const OmtConvGeo* g) {
+  if (kind == 0) return split_floats(g->co, g->ks, g->ci) * sizeof(float) + 256;
+  if (kind == 1) return split_floats(g->ci, g->ks, g->co) * sizeof(float) + 256;
+  return 0;
+}
+
+int tc_conv_fwd(const OmtConvGeo* g, const OmtAct* x, const float* w, const float* bias, const OmtAct* y, float* stats, uint32_t flags, void* ws,
+                cudaStream_t s) {
+  (void)stats;
+  OMT_REQUIRE(!(flags & OMT_EPI_BNSTATS), "OMT_EPI_BNSTATS is not implemented in the tensor-core epilogue yet");
+  TcProblem p{x->p, g->n, g->ci, g->ih, g->iw, g->oh, g->ow, g->co, g->ks, g->stride, g->pad};
+  return run_tc(p, w, false, g->co, g->ci, y, bias, flags, ws, s);
+}
+// stride-1 input gradient = forward convolution of gy with transposed, flipped weights and padding ks-1-pad
+int tc_conv_dgrad(const OmtConvGeo* g, const OmtAct* gy, const float* w, const OmtAct* dx, void* ws, cudaStream_t s) {
+  TcProblem p{gy->p, g->n, g->co, g->oh, g->ow, g->ih, g->iw, g->ci, g->ks, 1, g->ks - 1 - g->pad};
+  return run_tc(p, w, true, g->co, g->ci, dx, nullptr, 0, ws, s);
 }
 int tc_conv_wgrad(const OmtConvGeo*, const OmtAct*, const OmtAct*, float*, float, void*, cudaStream_t) {
-  set_error("tensor-core path not built");
+  set_error("tensor-core weight gradient is not built");
   return OMT_EINVAL;
 }
+
 }  // namespace omt

@@ -164,6 +164,12 @@ int omt_check_errors(void) {
 }
 int omt_sync(void) {
   OMT_CUDA(cudaDeviceSynchronize());
+  int e = tc_error_word();
+  if (e > 0) {
+    set_error("a tensor-core convolution kernel gave up waiting on a barrier (code %d); its output is invalid", e);
+    if (!g_sticky) g_sticky = (int)cudaErrorLaunchFailure;
+    return OMT_ECUDA;
+  }
   return OMT_OK;
 }
 

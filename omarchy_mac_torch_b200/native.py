@@ -36,7 +36,8 @@ torch.utils.generate_methods_for_privateuse1_backend(for_tensor=True, for_module
 core.set_fold(int(os.environ.get("OMARCHY_MAC_TORCH_FOLD", "1")))
 core.set_tuning(os.environ.get("OMARCHY_MAC_TORCH_TUNE", "1") != "0", 0)
 core.set_debug(os.environ.get("OMARCHY_MAC_TORCH_DEBUG", "0") == "1")
-core.set_channels_last(int(os.environ.get("OMARCHY_MAC_TORCH_CHANNELS_LAST", "0")))
+# conv outputs are produced channels-last (the layout the tensor-core kernels read) unless this is set to 0
+core.set_channels_last(int(os.environ.get("OMARCHY_MAC_TORCH_CHANNELS_LAST", "1")))
 
 
 def synchronize():

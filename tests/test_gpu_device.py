@@ -215,10 +215,10 @@ def test_fused_stacks_train_eval_and_accumulate(omt):
             l2 = F.cross_entropy(mod(X.to(D)), y.to(D), label_smoothing=0.1); o2.zero_grad(); l2.backward(); o2.step()
             assert abs(l1.item() - l2.item()) <= 1e-3 * abs(l1.item())
         assert type(mod.features) is stacks.FusedSequential
-        # Adam divides by sqrt(v): parameters whose gradient is rounding noise (e.g. a bias feeding a BatchNorm) move by
-        # +-lr per step with a noise-determined sign, so parameters are compared with an absolute slack of a step
+        # (SGD rather than the reference script's Adam: Adam turns rounding-noise gradients into +-lr steps, which makes
+        # parameter comparisons meaningless; the Adam kernels are compared step by step in the optimizer tests)
         for a, b in zip(ref.parameters(), mod.parameters()):
-            assert torch.allclose(b.detach().cpu(), a.detach(), rtol=1e-2, atol=2.5e-3)
+            assert e(b, a) <= 1e-3
         for a, b in zip(ref.buffers(), mod.buffers()):
             assert e(b.float(), a.float()) <= 1e-3  # running stats and num_batches_tracked
         ref.eval(); mod.eval()
