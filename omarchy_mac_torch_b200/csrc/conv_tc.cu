@@ -17,6 +17,12 @@
 // Every mbarrier wait is bounded by a clock budget; on expiry the kernel raises an error word, all roles leave their loops,
 // TMEM is freed and the kernel returns (the host reports it as a failed launch at the next synchronisation).
 //
+// The weight gradient is a second kernel with the same machinery and both operands "MN-major": D[co, (tap, c)] = sum over
+// pixels of gy[pix, co] * im2col(x)[pix, (tap, c)]. The reduction runs over pixels, which is the row index of both
+// channels-last operands, so each 32-pixel x 32-channel TMA box is one column of swizzle atoms of an MN-major UMMA operand.
+// Pixels are split over blockIdx.z; partial tiles go to slabs that a second kernel sums in a fixed order (deterministic),
+// re-laying [co][tap][c] out as [co][ci][ky][kx]. Both operands are activations, so both are split hi/lo in shared memory.
+//
 // The input gradient of a stride-1 convolution is the same kernel: a forward convolution of gy with the weights transposed
 // and flipped (done by the weight re-layout kernel). Replaces the reference's generated kinds 0 and 1
 // (omarchy_mac_torch/gemm.py:25-59) for the geometries it accepts; everything else stays on the exact-fp32 path.
@@ -125,8 +131,28 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
   d |= (uint64_t)2 << 61;                        // SWIZZLE_128B
   return d;
 }
-constexpr uint32_t idesc_tf32(int n) {
-  return (1u << 4) /* D = f32 */ | (2u << 7) /* A = tf32 */ | (2u << 10) /* B = tf32 */ | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+constexpr uint32_t idesc_tf32(int n, bool mn_major = false) {
+  return (1u << 4) /* D = f32 */ | (2u << 7) /* A = tf32 */ | (2u << 10) /* B = tf32 */ | (mn_major ? (3u << 15) : 0u) /* A, B majors */ |
+         ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+// MN-major tf32 operand. The only shared-memory layout the tensor core accepts for it is "128B swizzle with 32-byte
+// atomicity": 128-byte rows (32 floats along M/N) for consecutive k, 32-byte granules XOR-ed with the row index modulo 4, so
+// the swizzle atom is 4 k-rows x 128 bytes. `chunk_bytes` separates consecutive 32-float runs along M/N (leading byte
+// offset); groups of 4 k-rows follow each other every 512 bytes (stride byte offset). TMA writes this layout with
+// CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B.
+__device__ __forceinline__ uint64_t smem_desc_mn_sw128(uint32_t addr, uint32_t chunk_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)(chunk_bytes >> 4) << 16;
+  d |= (uint64_t)(512 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)1 << 61;  // SWIZZLE_128B_BASE32B
+  return d;
+}
+__device__ __forceinline__ void tma_tile_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+               ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+               : "memory");
 }
 
 struct TcArgs {
@@ -439,6 +465,260 @@ int run_tc(const TcProblem& p, const float* w, bool dgrad, int co, int ci, const
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------------
+// weight gradient kernel
+// ---------------------------------------------------------------------------------------------------------------------
+constexpr int PB = 32;            // pixels (reduction depth) per stage
+constexpr int WG_THREADS = 320;   // producer warp, MMA warp, 8 split/epilogue warps
+
+struct WgArgs {
+  float* part;       // [slices][co][kcols] partial tiles
+  int P;             // pixels = n * oh * ow
+  int co;
+  int oh, ow, ks, stride, pad;
+  int cblocks, cpad; // 32-channel blocks per tap
+  int chunks;        // ks * ks * cblocks: 32-wide column chunks of the output
+  int blocks_per_slice;  // 32-pixel blocks per blockIdx.z
+};
+
+template <int BN>
+struct WgSmem {
+  static constexpr int STAGES = BN == 256 ? 2 : (BN == 128 ? 3 : 4);
+  static constexpr int CH = PB * 128;                 // one 32-pixel x 32-float box
+  static constexpr int A_BYTES = 4 * CH, B_BYTES = (BN / 32) * CH;
+  static constexpr int HALF = A_BYTES + B_BYTES;      // hi region; the lo region follows at +HALF
+  static constexpr int STAGE_BYTES = 2 * HALF;
+  static constexpr int BAR_OFF = STAGES * STAGE_BYTES;
+  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(WG_THREADS, 1)
+wgrad_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_g, const WgArgs g) {
+  using S = WgSmem<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const uint32_t smem_base = smem_u32(smem);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::BAR_OFF);
+  const uint32_t bar0 = smem_u32(bars);
+  auto BAR = [&](int i) { return bar0 + 8u * i; };  // [0,S) loaded, [S,2S) split, [2S,3S) free, 3S accumulator ready
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 3 * S::STAGES + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 3 * S::STAGES + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int co0 = blockIdx.x * BM;
+  const int chunk0 = blockIdx.y * (BN / 32);
+  const int nchunks = min(BN / 32, g.chunks - chunk0);
+  const int total_blocks = (g.P + PB - 1) / PB;
+  const int blk_begin = blockIdx.z * g.blocks_per_slice;
+  const int kblocks = max(0, min(g.blocks_per_slice, total_blocks - blk_begin));
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S::STAGES; s++) {
+      mbar_init(BAR(s), 1);
+      mbar_init(BAR(S::STAGES + s), 8);
+      mbar_init(BAR(2 * S::STAGES + s), 1);
+    }
+    mbar_init(BAR(3 * S::STAGES), 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"((uint32_t)BN)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_acc = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const int ohw = g.oh * g.ow;
+      int issued = 0;
+      for (int kb = 0; kb < kblocks; kb++) {
+        const int s = kb % S::STAGES, round = kb / S::STAGES;
+        if (round > 0 && !mbar_wait(BAR(2 * S::STAGES + s), (round - 1) & 1, abort_flag)) break;
+        const int p0 = (blk_begin + kb) * PB;
+        const int img = p0 / ohw, r = p0 - img * ohw, oy = r / g.ow, ox = r - oy * g.ow;
+        const int w0 = ox * g.stride - g.pad, h0 = oy * g.stride - g.pad;
+        const uint32_t stage = smem_base + s * S::STAGE_BYTES;
+        mbar_expect_tx(BAR(s), S::A_BYTES + nchunks * S::CH);
+#pragma unroll
+        for (int i = 0; i < 4; i++) tma_tile_2d(stage + i * S::CH, &map_g, BAR(s), co0 + 32 * i, p0);
+        for (int j = 0; j < nchunks; j++) {
+          const int chunk = chunk0 + j, tap = chunk / g.cblocks, cb = chunk - tap * g.cblocks;
+          const int ky = tap / g.ks, kx = tap - ky * g.ks;
+          tma_im2col_4d(stage + S::A_BYTES + j * S::CH, &map_x, BAR(s), cb * BKF, w0, h0, img, (uint16_t)kx, (uint16_t)ky);
+        }
+        issued = kb + 1;
+      }
+      if (*abort_flag) {
+        for (int kb = max(0, issued - S::STAGES); kb < issued; kb++) {
+          const long long t0 = clock64();
+          while (!mbar_try(BAR(kb % S::STAGES), (kb / S::STAGES) & 1) && clock64() - t0 < WAIT_BUDGET_CLOCKS) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = idesc_tf32(BN, true);
+      bool ok = true;
+      for (int kb = 0; kb < kblocks && ok; kb++) {
+        const int s = kb % S::STAGES, round = kb / S::STAGES;
+        ok = mbar_wait(BAR(S::STAGES + s), round & 1, abort_flag) && mbar_wait(BAR(s), round & 1, abort_flag);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t stage = smem_base + s * S::STAGE_BYTES;
+#pragma unroll
+        for (int k = 0; k < PB / UMMA_K; k++) {
+          const uint32_t koff = k * 1024;  // next group of 8 pixel rows
+          const uint64_t a_hi = smem_desc_mn_sw128(stage + koff, S::CH), a_lo = smem_desc_mn_sw128(stage + S::HALF + koff, S::CH);
+          const uint64_t b_hi = smem_desc_mn_sw128(stage + S::A_BYTES + koff, S::CH);
+          const uint64_t b_lo = smem_desc_mn_sw128(stage + S::HALF + S::A_BYTES + koff, S::CH);
+          umma_tf32(tmem_acc, a_lo, b_hi, idesc, (kb | k) ? 1u : 0u);
+          umma_tf32(tmem_acc, a_hi, b_lo, idesc, 1u);
+          umma_tf32(tmem_acc, a_hi, b_hi, idesc, 1u);
+        }
+        umma_commit(BAR(2 * S::STAGES + s));
+      }
+      if (ok) umma_commit(BAR(3 * S::STAGES));
+    }
+  } else {
+    const int t = threadIdx.x - 64;  // 0..255
+    bool ok = true;
+    const int n16 = (S::A_BYTES + nchunks * S::CH) / 16;  // 16-byte words that were loaded this stage
+    for (int kb = 0; kb < kblocks && ok; kb++) {
+      const int s = kb % S::STAGES, round = kb / S::STAGES;
+      ok = mbar_wait(BAR(s), round & 1, abort_flag);
+      if (!ok) break;
+      uint4* hi = reinterpret_cast<uint4*>(smem + s * S::STAGE_BYTES);
+      uint4* lo = reinterpret_cast<uint4*>(smem + s * S::STAGE_BYTES + S::HALF);
+      for (int idx = t; idx < n16; idx += 256) {
+        uint4 v = hi[idx], h, l;
+        float f0 = __uint_as_float(v.x), f1 = __uint_as_float(v.y), f2 = __uint_as_float(v.z), f3 = __uint_as_float(v.w);
+        float h0 = tf32_rna(f0), h1 = tf32_rna(f1), h2 = tf32_rna(f2), h3 = tf32_rna(f3);
+        h.x = __float_as_uint(h0); h.y = __float_as_uint(h1); h.z = __float_as_uint(h2); h.w = __float_as_uint(h3);
+        l.x = __float_as_uint(tf32_rna(f0 - h0)); l.y = __float_as_uint(tf32_rna(f1 - h1));
+        l.z = __float_as_uint(tf32_rna(f2 - h2)); l.w = __float_as_uint(tf32_rna(f3 - h3));
+        hi[idx] = h;
+        lo[idx] = l;
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(BAR(S::STAGES + s));
+    }
+    // epilogue: warps 2..9; quarter = warp & 3, column half = (warp - 2) / 4
+    if (ok && kblocks > 0) ok = mbar_wait(BAR(3 * S::STAGES), 0, abort_flag);
+    if (ok) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int q = warp & 3, half = (warp - 2) >> 2;
+      const int row = co0 + q * 32 + lane;
+      const int kcols = g.chunks * 32;
+      float* prow = g.part + ((int64_t)blockIdx.z * g.co + row) * kcols;
+#pragma unroll 1
+      for (int c = half; c < BN / 32; c += 2) {
+        uint32_t v[32];
+        if (kblocks > 0) {
+          tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + c * 32, v);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; j++) v[j] = 0u;  // a slice with no pixels contributes zeros
+        }
+        if (row >= g.co || c >= nchunks) continue;
+        float4* dst = reinterpret_cast<float4*>(prow + (chunk0 + c) * 32);
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          dst[j / 4] = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"((uint32_t)BN) : "memory");
+  }
+}
+
+// dw[o][c][ky][kx] = scale * sum_z part[z][o][tap*cpad + c]
+__global__ void __launch_bounds__(256) wgrad_tc_reduce_kernel(const float* __restrict__ part, float* __restrict__ dw, int co, int ci, int kk,
+                                                              int cpad, int slices, float scale) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t total = (int64_t)co * ci * kk;
+  if (i >= total) return;
+  const int tap = (int)(i % kk);
+  const int c = (int)((i / kk) % ci);
+  const int o = (int)(i / ((int64_t)kk * ci));
+  const int64_t kcols = (int64_t)kk * cpad, slab = (int64_t)co * kcols;
+  const float* p = part + (int64_t)o * kcols + (int64_t)tap * cpad + c;
+  float s = 0.f;
+  for (int z = 0; z < slices; z++) s += __ldg(p + z * slab);
+  dw[i] = s * scale;
+}
+
+struct WgPlan {
+  int bn, slices, blocks_per_slice, cblocks, cpad, chunks;
+  size_t part_floats;
+};
+WgPlan plan_wgrad(const OmtConvGeo* g) {
+  WgPlan w{};
+  w.cblocks = (int)cdiv(g->ci, BKF); w.cpad = w.cblocks * BKF; w.chunks = g->ks * g->ks * w.cblocks;
+  w.bn = w.chunks >= 6 ? 256 : (w.chunks >= 3 ? 128 : 64);
+  int64_t tiles = cdiv(g->co, BM) * cdiv(w.chunks, w.bn / 32);
+  int64_t total_blocks = cdiv((int64_t)g->n * g->oh * g->ow, PB);
+  int64_t want = std::max<int64_t>(1, (3 * sm_count()) / tiles);
+  int64_t slices = std::max<int64_t>(1, std::min<int64_t>(want, total_blocks / 8));
+  w.blocks_per_slice = (int)cdiv(total_blocks, slices);
+  w.slices = (int)cdiv(total_blocks, w.blocks_per_slice);
+  w.part_floats = (size_t)w.slices * g->co * w.chunks * 32;
+  return w;
+}
+
+template <int BN>
+int launch_wgrad(const OmtConvGeo* g, const WgPlan& w, const float* x, const float* gy, float* part, cudaStream_t s) {
+  using S = WgSmem<BN>;
+  alignas(64) CUtensorMap map_x, map_g;
+  {
+    cuuint64_t dims[4] = {(cuuint64_t)g->ci, (cuuint64_t)g->iw, (cuuint64_t)g->ih, (cuuint64_t)g->n};
+    cuuint64_t strides[3] = {(cuuint64_t)g->ci * 4, (cuuint64_t)g->iw * g->ci * 4, (cuuint64_t)g->ih * g->iw * g->ci * 4};
+    int lower[2] = {-g->pad, -g->pad}, upper[2] = {g->pad - (g->ks - 1), g->pad - (g->ks - 1)};
+    cuuint32_t estr[4] = {1, (cuuint32_t)g->stride, (cuuint32_t)g->stride, 1};
+    CUresult r = g_encode_im2col(&map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void*)x, dims, strides, lower, upper, BKF, PB, estr,
+                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+      set_error("cuTensorMapEncodeIm2col failed (%d)", (int)r);
+      return OMT_ECUDA;
+    }
+  }
+  {
+    const int64_t P = (int64_t)g->n * g->oh * g->ow;
+    cuuint64_t dims[2] = {(cuuint64_t)g->co, (cuuint64_t)P};
+    cuuint64_t strides[1] = {(cuuint64_t)g->co * 4};
+    cuuint32_t box[2] = {BKF, PB}, estr[2] = {1, 1};
+    CUresult r = g_encode_tiled(&map_g, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)gy, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+      set_error("cuTensorMapEncodeTiled failed (%d)", (int)r);
+      return OMT_ECUDA;
+    }
+  }
+  static bool attr_set = false;
+  if (!attr_set) {
+    OMT_CUDA(cudaFuncSetAttribute(wgrad_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
+    attr_set = true;
+  }
+  WgArgs a{};
+  a.part = part; a.P = g->n * g->oh * g->ow; a.co = g->co; a.oh = g->oh; a.ow = g->ow; a.ks = g->ks; a.stride = g->stride; a.pad = g->pad;
+  a.cblocks = w.cblocks; a.cpad = w.cpad; a.chunks = w.chunks; a.blocks_per_slice = w.blocks_per_slice;
+  dim3 grid((unsigned)cdiv(g->co, BM), (unsigned)cdiv(w.chunks, BN / 32), (unsigned)w.slices);
+  wgrad_tc_kernel<BN><<<grid, WG_THREADS, S::TOTAL, s>>>(map_x, map_g, a);
+  return check_launch(BN == 64 ? "wgrad_tc_128x64" : (BN == 128 ? "wgrad_tc_128x128" : "wgrad_tc_128x256"));
+}
+
 bool cl_ok(const OmtAct* a, int c, int h, int w) {
   return a && a->p && is_nhwc(a, c, h, w) && c % 4 == 0 && (reinterpret_cast<uintptr_t>(a->p) & 15) == 0;
 }
@@ -456,12 +736,13 @@ bool tc_supported(int kind, const OmtConvGeo* g, const OmtAct* a, const OmtAct* 
   if (!b || !b->p) return false;
   if (kind == 0) return cl_ok(a, g->ci, g->ih, g->iw) && g->ci >= 8 && g->co >= 8 && g->pad < g->ks;
   if (kind == 1) return g->stride == 1 && cl_ok(a, g->co, g->oh, g->ow) && g->co >= 8 && g->ci >= 8 && g->ks - 1 - g->pad >= 0;
-  return false;
+  // kind 2: a = x, b = gy
+  return cl_ok(a, g->ci, g->ih, g->iw) && cl_ok(b, g->co, g->oh, g->ow) && g->ci >= 8 && g->co >= 8 && g->pad < g->ks;
 }
 size_t tc_workspace(int kind, const OmtConvGeo* g) {
   if (kind == 0) return split_floats(g->co, g->ks, g->ci) * sizeof(float) + 256;
   if (kind == 1) return split_floats(g->ci, g->ks, g->co) * sizeof(float) + 256;
-  return 0;
+  return plan_wgrad(g).part_floats * sizeof(float) + 256;
 }
 
 int tc_conv_fwd(const OmtConvGeo* g, const OmtAct* x, const float* w, const float* bias, const OmtAct* y, float* stats, uint32_t flags, void* ws,
@@ -476,9 +757,23 @@ int tc_conv_dgrad(const OmtConvGeo* g, const OmtAct* gy, const float* w, const O
   TcProblem p{gy->p, g->n, g->co, g->oh, g->ow, g->ih, g->iw, g->ci, g->ks, 1, g->ks - 1 - g->pad};
   return run_tc(p, w, true, g->co, g->ci, dx, nullptr, 0, ws, s);
 }
-int tc_conv_wgrad(const OmtConvGeo*, const OmtAct*, const OmtAct*, float*, float, void*, cudaStream_t) {
-  set_error("tensor-core weight gradient is not built");
-  return OMT_EINVAL;
+int tc_conv_wgrad(const OmtConvGeo* g, const OmtAct* x, const OmtAct* gy, float* dw, float scale, void* ws, cudaStream_t s) {
+  if (!load_driver_entry_points()) {
+    set_error("the CUDA driver does not export cuTensorMapEncodeTiled/Im2col");
+    return OMT_ECUDA;
+  }
+  const WgPlan w = plan_wgrad(g);
+  float* part = (float*)ws;
+  int r;
+  switch (w.bn) {
+    case 64: r = launch_wgrad<64>(g, w, x->p, gy->p, part, s); break;
+    case 128: r = launch_wgrad<128>(g, w, x->p, gy->p, part, s); break;
+    default: r = launch_wgrad<256>(g, w, x->p, gy->p, part, s); break;
+  }
+  if (r) return r;
+  const int64_t total = (int64_t)g->co * g->ci * g->ks * g->ks;
+  wgrad_tc_reduce_kernel<<<(unsigned)cdiv(total, 256), 256, 0, s>>>(part, dw, g->co, g->ci, g->ks * g->ks, w.cpad, w.slices, scale);
+  return check_launch("wgrad_tc_reduce");
 }
 
 }  // namespace omt
