@@ -5,10 +5,13 @@
 Prints ONE JSON line. A "step" is one pass of the hot path over one batch of synthetic input (seeded; the reference
 benchmarks on random tensors too). Workloads:
 
+  resnet50  (default) BASELINE config 5: ResNet-50 training step, batch 256 per GPU, 224x224, SGD nesterov, on the
+            "omarchy_mac_torch" device; with --gpus N each rank takes its own batch (weak scaling) and gradients are
+            averaged by the bucketed all-reduce of omarchy_mac_torch_b200.dp. This is the configuration the metric
+            "train ms/step at 1/2/4/8 B200" is quoted on, and it fits one GPU.
+  plaincnn / resnet18 / mobilenetv3   BASELINE configs 2-4, training step on the device.
   conv1     BASELINE config 1: AlexNet conv1 fwd + dgrad + wgrad, x[16,3,224,224], w[64,3,11,11], stride 4, pad 2
             (tools/gemm_bench.py "alex1"), called through the C ABI.
-  plaincnn  BASELINE config 2: PlainCNN b128 training step (fwd+bwd+SGD) on the "omarchy_mac_torch" device.
-  resnet18 / mobilenetv3 / resnet50   BASELINE configs 3-5, training step on the device; resnet50 is the multi-GPU one.
 
 Timing: W >= 3 untimed warm-up steps, then K steps timed with CUDA events on the launching stream, a barrier and a
 device synchronize on both sides, max over ranks; L2 is flushed between timed iterations whenever the step's working
@@ -96,7 +99,13 @@ class Conv1:
         gy = torch.randn(16, 64, 55, 55)
         return x, conv.weight.detach().clone(), conv.bias.detach().clone(), gy
 
-    def setup_gpu(self, seed):
+    def cpu_setup(self):
+        return self.host_inputs(0)
+
+    def cpu_scale(self):
+        return 1.0
+
+    def setup_gpu(self, seed, world=1):
         from omarchy_mac_torch_b200 import capi
         self.capi = capi
         capi.lib()
@@ -139,7 +148,132 @@ class Conv1:
                 "peak_source": f"{peaks['source']} bf16 burst / 2 (tf32) / 3 (3xTF32)"}
 
 
-WORKLOADS = {"conv1": Conv1}
+
+# ---------------------------------------------------------------------------------------------------------------------
+# training workloads on the "omarchy_mac_torch" device
+# ---------------------------------------------------------------------------------------------------------------------
+
+class Train:
+    metric, unit, higher = "train_ms_per_step", "ms/step", False
+
+    def __init__(self, name, make_model, shape, classes, make_opt, cpu_batch, note):
+        self.name, self.make_model, self.in_shape, self.classes, self.make_opt = name, make_model, shape, classes, make_opt
+        self.cpu_batch = min(cpu_batch, shape[0])
+        self.shape = {"batch_per_gpu": shape[0], "input": list(shape[1:]), "classes": classes, "optimizer": note}
+
+    def host_inputs(self, seed, batch=None):
+        g = torch.Generator().manual_seed(1000 + seed)
+        b = batch or self.in_shape[0]
+        return torch.randn(b, *self.in_shape[1:], generator=g), torch.randint(0, self.classes, (b,), generator=g)
+
+    def build_model(self):
+        torch.manual_seed(0)  # identical initial weights on every rank
+        m = self.make_model()
+        for mod in m.modules():
+            if isinstance(mod, torch.nn.Dropout):
+                mod.p = 0.0
+        return m
+
+    def setup_gpu(self, seed, world=1):
+        import omarchy_mac_torch_b200 as omt
+        from omarchy_mac_torch_b200 import capi
+        from omarchy_mac_torch_b200.native import core
+        self.capi, self.core, self.dev = capi, core, omt.DEVICE
+        capi.lib()
+        self.model = self.build_model().to(self.dev)
+        self.dp = None
+        if world > 1:
+            from omarchy_mac_torch_b200.dp import DataParallel
+            self.dp = DataParallel(self.model, bucket_mb=25.0)
+        self.opt = self.make_opt(self.model.parameters())
+        xh, yh = self.host_inputs(seed)
+        self.xh, self.yh = xh.pin_memory(), yh.pin_memory()
+        self.x, self.y = self.xh.to(self.dev), self.yh.to(self.dev)
+        self.xs, self.ys = torch.empty_like(self.x), torch.empty_like(self.y)
+        self.bytes_resident = 1 << 40  # activations of a training step are far larger than L2: no flush needed
+        self.h2d_bytes = self.xh.numel() * 4 + self.yh.numel() * 8
+        self.d2h_bytes = 4
+
+    def _step(self, x, y):
+        if self.dp is not None:
+            self.dp.zero_grad()
+        else:
+            self.opt.zero_grad(set_to_none=True)
+        loss = torch.nn.functional.cross_entropy(self.model(x), y)
+        loss.backward()
+        if self.dp is not None:
+            self.dp.finish()
+        self.opt.step()
+        return loss
+
+    def step(self):
+        return self._step(self.x, self.y)
+
+    def e2e_step(self):
+        self.xs.copy_(self.xh, non_blocking=True)
+        self.ys.copy_(self.yh, non_blocking=True)
+        return self._step(self.xs, self.ys).item()  # device->host read of the loss
+
+    def value(self, ms):
+        return ms
+
+    def cpu_setup(self):
+        self.cpu_model = self.build_model()
+        self.cpu_opt = self.make_opt(self.cpu_model.parameters())
+        return self.host_inputs(0, self.cpu_batch)
+
+    def cpu_step(self, ins):
+        x, y = ins
+        self.cpu_opt.zero_grad()
+        loss = torch.nn.functional.cross_entropy(self.cpu_model(x), y)
+        loss.backward()
+        self.cpu_opt.step()
+        return loss
+
+    def cpu_scale(self):  # CPU sample batch -> full per-GPU batch
+        return self.in_shape[0] / self.cpu_batch
+
+    def roofline(self, ms, peaks):
+        # conv GEMMs measured live: two extra steps with the library's per-call CUDA-event timing switched on
+        self.capi.conv_timing(True)
+        for _ in range(2):
+            self.step()
+        torch.cuda.synchronize()
+        t = self.capi.conv_timing_read(reset=True)
+        self.capi.conv_timing(False)
+        flops = sum(v[0] for v in t.values()) / 2
+        conv_ms = sum(v[1] for v in t.values()) / 2
+        sustained = peaks.get("bf16_tflops_sustained") or peaks["bf16_tflops"]
+        peak = sustained / 2 / 3
+        ach = flops / (conv_ms * 1e-3) / 1e12 if conv_ms else 0.0
+        return {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak, "traffic": None,
+                "peak_source": f"{peaks['source']} bf16 sustained / 2 (tf32) / 3 (3xTF32)",
+                "kernel": "dense conv fwd + dgrad + wgrad (all conv calls of one step)",
+                "conv_flops_per_step": flops, "conv_ms_per_step": conv_ms, "conv_share_of_step": conv_ms / ms if ms else None,
+                "per_pass": {k: {"tflops": (v[0] / (v[1] * 1e-3) / 1e12 if v[1] else None), "ms": v[1] / 2, "calls": v[2] // 2} for k, v in t.items()}}
+
+
+def _models():
+    from omarchy_mac_torch_b200 import models
+    return models
+
+
+def _sgd(lr, **kw):
+    return lambda p: torch.optim.SGD(p, lr=lr, **kw)
+
+
+TRAIN = {
+    "plaincnn": lambda: Train("plaincnn_b128_train", lambda: _models().PlainCNN3(), (128, 3, 32, 32), 10, _sgd(0.05, momentum=0.9), 128,
+                              "SGD lr .05 momentum .9"),
+    "resnet18": lambda: Train("resnet18_b32_train", lambda: _models().kaiming_normal_convs(_models().ResNet18(num_classes=1000)),
+                              (32, 3, 64, 64), 1000, _sgd(0.1, momentum=0.9, weight_decay=1e-4), 32, "SGD lr .1 momentum .9 wd 1e-4"),
+    "mobilenetv3": lambda: Train("mobilenetv3_small_b32_train", lambda: _models().MobileNetV3SE(), (32, 3, 224, 224), 1000,
+                                 lambda p: torch.optim.AdamW(p, lr=1e-3, weight_decay=0.01), 32, "AdamW lr 1e-3 wd .01"),
+    "resnet50": lambda: Train("resnet50_b256_train", lambda: _models().ResNet50(), (256, 3, 224, 224), 1000,
+                              _sgd(0.1, momentum=0.9, nesterov=True, weight_decay=1e-4), 16, "SGD lr .1 momentum .9 nesterov wd 1e-4"),
+}
+
+WORKLOADS = {"conv1": Conv1, **TRAIN}
 
 
 def dist_setup(n):
@@ -192,19 +326,24 @@ def run_reference(args, wl):
         return
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    ins = wl.host_inputs(0)
-    for _ in range(max(1, args.warmup)):
+    ins = wl.cpu_setup()
+    budget, t_start = 150.0, time.perf_counter()  # keep the whole arm within a few minutes
+    wl.cpu_step(ins)
+    for _ in range(max(0, min(args.warmup, 2) - 1)):
+        if time.perf_counter() - t_start < budget / 3:
+            wl.cpu_step(ins)
+    done, t0 = 0, time.perf_counter()
+    while done < args.steps and (done == 0 or time.perf_counter() - t_start < budget):
         wl.cpu_step(ins)
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        wl.cpu_step(ins)
-    ms = (time.perf_counter() - t0) / args.steps * 1e3
+        done += 1
+    ms = (time.perf_counter() - t0) / done * 1e3 * wl.cpu_scale()
     v = wl.value(ms)
     line = {"impl": "reference", "metric": wl.metric, "value": v, "unit": wl.unit, "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": wl.higher, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic", "config": {"workload": wl.name, **wl.shape},
             "cpu_baseline": {"value": v, "unit": wl.unit, "cores": cores, "kind": "reference",
-                             "sample": f"{args.steps} full steps of PyTorch CPU aten ({torch.__version__}), {cores} threads"},
+                             "sample": f"{done} steps of PyTorch CPU aten ({torch.__version__}) on {cores} threads"
+                                       + (f", batch {wl.cpu_batch} scaled x{wl.cpu_scale():g} to the full batch" if wl.cpu_scale() != 1 else "")},
             "e2e": {"value": v, "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
 
@@ -214,17 +353,17 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="conv1", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="resnet50", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
-    wl = WORKLOADS[args.workload]()
+    wl = WORKLOADS[args.workload]() if args.workload != "conv1" else Conv1()
     if args.impl == "reference":
         return run_reference(args, wl)
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
     rank, world = dist_setup(args.gpus)
-    wl.setup_gpu(seed=rank)
+    wl.setup_gpu(seed=rank, world=world)
     capi = wl.capi
     peaks = measured_peaks()
     flush = wl.bytes_resident < 2 * L2_BYTES
@@ -238,26 +377,31 @@ def main():
     clocks = sampler.stop() if rank == 0 else None
     if rank != 0:
         return
-    line = {"metric": wl.metric, "value": wl.value(ms) * world, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
+    agg = world if wl.higher else 1  # throughput metrics aggregate over ranks; a step time does not
+    line = {"metric": wl.metric, "value": wl.value(ms) * agg, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": wl.higher, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
             "config": {"workload": wl.name, **wl.shape, "l2": "flushed between timed iterations" if flush else "working set > L2"},
             "roofline": wl.roofline(ms, peaks),
-            "e2e": {"value": wl.value(ms_e2e) * world, "unit": wl.unit, "ms_per_step": ms_e2e, "h2d_bytes_per_step": wl.h2d_bytes,
+            "e2e": {"value": wl.value(ms_e2e) * agg, "unit": wl.unit, "ms_per_step": ms_e2e, "h2d_bytes_per_step": wl.h2d_bytes,
                     "d2h_bytes_per_step": wl.d2h_bytes},
             "gpu_launches": int(launches) * args.steps, "clocks": clocks}
+    if not wl.higher:
+        line["images_per_s"] = wl.in_shape[0] * world / (ms * 1e-3)
+        line["config"]["parallelism"] = f"dp{world}"
     if not args.no_cpu_baseline:
         cores = os.cpu_count() or 1
         torch.set_num_threads(cores)
-        ins = wl.host_inputs(0)
+        ins = wl.cpu_setup()
         wl.cpu_step(ins)
         reps, t0 = 0, time.perf_counter()
-        while reps < 3 or (time.perf_counter() - t0 < 10 and reps < 200):
+        while reps < 1 or (time.perf_counter() - t0 < 12 and reps < 200):
             wl.cpu_step(ins)
             reps += 1
-        cms = (time.perf_counter() - t0) / reps * 1e3
+        cms = (time.perf_counter() - t0) / reps * 1e3 * wl.cpu_scale()
         line["cpu_baseline"] = {"value": wl.value(cms), "unit": wl.unit, "cores": cores, "kind": "reference", "ms_per_step": cms,
-                                "sample": f"{reps} full steps of the same workload on PyTorch CPU aten, {cores} threads"}
+                                "sample": f"{reps} steps of the same workload on PyTorch CPU aten (the reference's CPU arm), {cores} threads"
+                                          + (f", batch {wl.cpu_batch} scaled x{wl.cpu_scale():g} to the full batch" if wl.cpu_scale() != 1 else "")}
     print(json.dumps(line))
 
 

@@ -134,6 +134,14 @@ int omt_conv_wgrad(const OmtConvGeo* g, const OmtAct* x, const OmtAct* gy, float
 int omt_conv_bias_grad(const OmtAct* gy, int32_t n, int32_t c, int32_t h, int32_t w, float* db, float scale,
                        omt_stream_t stream);
 
+/* Per-call device timing of the dense-conv entry points (reference debug_time_kernels / kernel_times,
+ * csrc/runtime.cpp:598-610, csrc/module.cpp:30-33). While enabled, omt_conv_fwd/dgrad/wgrad bracket their launches with
+ * CUDA events on the caller's stream. omt_conv_timing_read synchronises those events and returns, per pass (index 0 fwd,
+ * 1 dgrad, 2 wgrad), the summed algorithmic FLOPs (2*n*co*oh*ow*ci*ks*ks per call, tools/gemm_bench.py:29), the summed
+ * milliseconds and the number of calls; `reset` clears the records. */
+int omt_conv_timing(int enable);
+int omt_conv_timing_read(double flops[3], double ms[3], int64_t calls[3], int reset);
+
 /* ---- depthwise convolution: reference dw_fwd/dw_gin/dw_gwt and dwg_* (csrc/conv.cpp:194-229) ------------------- */
 
 int omt_dw_fwd(const OmtConvGeo* g, const OmtAct* x, const float* w, const float* bias, const OmtAct* y,

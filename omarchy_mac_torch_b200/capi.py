@@ -75,6 +75,8 @@ SIGNATURES = {
     "omt_conv_dgrad": (_I, [_G, _A, _P, _A, _U, _P, _SZ, _P]),
     "omt_conv_wgrad": (_I, [_G, _A, _A, _P, _F, _U, _P, _SZ, _P]),
     "omt_conv_bias_grad": (_I, [_A, _I, _I, _I, _I, _P, _F, _P]),
+    "omt_conv_timing": (_I, [_I]),
+    "omt_conv_timing_read": (_I, [C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_int64), _I]),
     "omt_dw_fwd": (_I, [_G, _A, _P, _P, _A, _U, _P]),
     "omt_dw_dgrad": (_I, [_G, _A, _P, _A, _P]),
     "omt_dw_wgrad": (_I, [_G, _A, _A, _P, _F, _P]),
@@ -160,6 +162,17 @@ def stream_handle(stream=None):
     import torch
     s = stream if stream is not None else torch.cuda.current_stream()
     return C.c_void_p(s.cuda_stream)
+
+
+def conv_timing(enable):
+    call("omt_conv_timing", int(enable))
+
+
+def conv_timing_read(reset=True):
+    """{pass: (flops, ms, calls)} for fwd / dgrad / wgrad since the last reset."""
+    f, m, c = (C.c_double * 3)(), (C.c_double * 3)(), (C.c_int64 * 3)()
+    call("omt_conv_timing_read", f, m, c, int(reset))
+    return {k: (f[i], m[i], c[i]) for i, k in enumerate(("fwd", "dgrad", "wgrad"))}
 
 
 def kernel_counts(reset=False):

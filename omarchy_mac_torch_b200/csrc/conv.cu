@@ -2,6 +2,8 @@
 // path selection (tcgen05 tensor-core kernels when the geometry and layout allow, exact-fp32 CUDA-core kernels
 // otherwise), workspace handling, and two small copy helpers.
 #include <algorithm>
+#include <mutex>
+#include <vector>
 
 #include "common.cuh"
 
@@ -20,6 +22,34 @@ int tc_conv_fwd(const OmtConvGeo* g, const OmtAct* x, const float* w, const floa
                 uint32_t flags, void* ws, cudaStream_t s);
 int tc_conv_dgrad(const OmtConvGeo* g, const OmtAct* gy, const float* w, const OmtAct* dx, void* ws, cudaStream_t s);
 int tc_conv_wgrad(const OmtConvGeo* g, const OmtAct* x, const OmtAct* gy, float* dw, float scale, void* ws, cudaStream_t s);
+
+// ---- optional per-call timing of the three passes ----
+static bool g_timing = false;
+struct TimedCall {
+  cudaEvent_t a, b;
+  int kind;
+  double flops;
+};
+static std::vector<TimedCall> g_timed;
+static std::mutex g_timed_mu;
+struct CallTimer {
+  bool on;
+  TimedCall c{};
+  cudaStream_t s;
+  CallTimer(int kind, const OmtConvGeo* g, cudaStream_t s_) : on(g_timing), s(s_) {
+    if (!on) return;
+    c.kind = kind;
+    c.flops = 2.0 * g->n * g->co * g->oh * g->ow * (double)g->ci * g->ks * g->ks;
+    if (cudaEventCreate(&c.a) != cudaSuccess || cudaEventCreate(&c.b) != cudaSuccess) { on = false; return; }
+    cudaEventRecord(c.a, s);
+  }
+  ~CallTimer() {
+    if (!on) return;
+    cudaEventRecord(c.b, s);
+    std::lock_guard<std::mutex> l(g_timed_mu);
+    g_timed.push_back(c);
+  }
+};
 
 static int check_dense(const OmtConvGeo* g, const char* who) {
   OMT_REQUIRE(g != nullptr, "%s: null geometry", who);
@@ -112,6 +142,7 @@ int omt_conv_fwd(const OmtConvGeo* g, const OmtAct* x, const float* w, const flo
   OMT_REQUIRE(!(flags & OMT_EPI_BNSTATS) || stats, "omt_conv_fwd: OMT_EPI_BNSTATS without a stats pointer");
   bool tc = !(flags & OMT_FORCE_SIMT) && tc_supported(0, g, x, y);
   OMT_REQUIRE(tc || !(flags & OMT_FORCE_TC), "omt_conv_fwd: geometry/layout not covered by the tensor-core path");
+  CallTimer timer(0, g, st(stream));
   OMT_REQUIRE(tc || !(flags & OMT_EPI_BNSTATS), "omt_conv_fwd: OMT_EPI_BNSTATS needs the tensor-core path");
   if (!tc) return simt_conv_fwd(g, x, w, bias, y, flags, st(stream));
   Scratch sc;
@@ -127,6 +158,7 @@ int omt_conv_dgrad(const OmtConvGeo* g, const OmtAct* gy, const float* w, const 
   OMT_REQUIRE(gy && dx && gy->p && dx->p && w, "omt_conv_dgrad: null pointer");
   bool tc = !(flags & OMT_FORCE_SIMT) && tc_supported(1, g, gy, dx);
   OMT_REQUIRE(tc || !(flags & OMT_FORCE_TC), "omt_conv_dgrad: geometry/layout not covered by the tensor-core path");
+  CallTimer timer(1, g, st(stream));
   if (!tc) return simt_conv_dgrad(g, gy, w, dx, st(stream));
   Scratch sc;
   r = sc.get(workspace, workspace_bytes, tc_workspace(1, g), stream);
@@ -141,11 +173,32 @@ int omt_conv_wgrad(const OmtConvGeo* g, const OmtAct* x, const OmtAct* gy, float
   OMT_REQUIRE(x && gy && x->p && gy->p && dw, "omt_conv_wgrad: null pointer");
   bool tc = !(flags & OMT_FORCE_SIMT) && tc_supported(2, g, x, gy);
   OMT_REQUIRE(tc || !(flags & OMT_FORCE_TC), "omt_conv_wgrad: geometry/layout not covered by the tensor-core path");
+  CallTimer timer(2, g, st(stream));
   Scratch sc;
   r = sc.get(workspace, workspace_bytes, tc ? tc_workspace(2, g) : simt_wgrad_workspace(g), stream);
   if (r) return r;
   if (tc) return tc_conv_wgrad(g, x, gy, dw, scale, sc.p, st(stream));
   return simt_conv_wgrad(g, x, gy, dw, scale, (float*)sc.p, st(stream));
+}
+
+int omt_conv_timing(int enable) {
+  g_timing = enable != 0;
+  return OMT_OK;
+}
+int omt_conv_timing_read(double flops[3], double ms[3], int64_t calls[3], int reset) {
+  std::lock_guard<std::mutex> l(g_timed_mu);
+  for (int k = 0; k < 3; k++) { flops[k] = 0; ms[k] = 0; calls[k] = 0; }
+  for (auto& c : g_timed) {
+    OMT_CUDA(cudaEventSynchronize(c.b));
+    float t = 0.f;
+    OMT_CUDA(cudaEventElapsedTime(&t, c.a, c.b));
+    flops[c.kind] += c.flops; ms[c.kind] += t; calls[c.kind]++;
+  }
+  if (reset) {
+    for (auto& c : g_timed) { cudaEventDestroy(c.a); cudaEventDestroy(c.b); }
+    g_timed.clear();
+  }
+  return OMT_OK;
 }
 
 int omt_scale_copy(float* dst, const float* src, int64_t n, float scale, omt_stream_t stream) {

@@ -159,8 +159,11 @@ struct TcArgs {
   ActView y;          // output activation (any strides)
   const float* bias;
   int M, N;           // GEMM extents: pixels, output channels
-  int oh, ow;         // output plane (to decompose m)
-  int ks, stride, pad;
+  int oh, ow;         // pixel grid of the GEMM rows (to decompose m)
+  int kh, kw;         // filter taps of this (sub-)convolution
+  int stride;         // traversal stride over the input
+  int low_h, low_w;   // input coordinate of tap (0,0) for output pixel (0,0): -pad for a forward convolution
+  int out_step, out_y0, out_x0;  // GEMM row (oy, ox) is stored at (oy*out_step + out_y0, ox*out_step + out_x0)
   int cblocks;        // 32-channel blocks per tap
   int cpad;           // cblocks * 32
   uint32_t flags;
@@ -194,7 +197,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
-  const int kblocks = g.ks * g.ks * g.cblocks;
+  const int kblocks = g.kh * g.kw * g.cblocks;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S::STAGES; s++) {
@@ -221,13 +224,13 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (lane == 0) {
       const int ohw = g.oh * g.ow;
       const int img0 = m0 / ohw, r0 = m0 - img0 * ohw, oy0 = r0 / g.ow, ox0 = r0 - oy0 * g.ow;
-      const int w0 = ox0 * g.stride - g.pad, h0 = oy0 * g.stride - g.pad;
+      const int w0 = ox0 * g.stride + g.low_w, h0 = oy0 * g.stride + g.low_h;
       int issued = 0;
       for (int kb = 0; kb < kblocks; kb++) {
         const int s = kb % S::STAGES, round = kb / S::STAGES;
         if (round > 0 && !mbar_wait(BAR(2 * S::STAGES + s), (round - 1) & 1, abort_flag)) break;
         const int tap = kb / g.cblocks, cb = kb - tap * g.cblocks;
-        const int ky = tap / g.ks, kx = tap - ky * g.ks;
+        const int ky = tap / g.kw, kx = tap - ky * g.kw;
         const uint32_t stage = smem_base + s * S::STAGE_BYTES;
         mbar_expect_tx(BAR(s), S::A_BYTES + 2 * S::B_BYTES);
         tma_im2col_4d(stage, &map_a, BAR(s), cb * BKF, w0, h0, img0, (uint16_t)kx, (uint16_t)ky);
@@ -300,7 +303,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const int m = m0 + q * 32 + lane;
       const int ohw = g.oh * g.ow;
       const int img = m / ohw, r = m - img * ohw, oy = r / g.ow, ox = r - oy * g.ow;
-      float* yrow = g.y.p + g.y.off(img, 0, oy, ox);
+      float* yrow = g.y.p + g.y.off(img, 0, oy * g.out_step + g.out_y0, ox * g.out_step + g.out_x0);
       const bool vec = g.y.sc == 1 && ((reinterpret_cast<uintptr_t>(yrow) & 15) == 0);
 #pragma unroll 1
       for (int c = 0; c < BN / 32; c++) {
@@ -337,24 +340,31 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-// weight re-layout: w[co][ci][ks][ks] -> out[2][rows][ks*ks][cpad], hi and lo planes, zero padded
-//   forward:  rows = co, channel = ci, tap (ky, kx)
-//   dgrad:    rows = ci, channel = co, tap (ks-1-ky, ks-1-kx)   (transposed and flipped)
+// weight re-layout: w[co][ci][ks][ks] -> out[2][rows][kh*kw][cpad], hi and lo planes, zero padded
+//   forward:  rows = co, channel = ci, tap (ty, tx) reads w[.., ty, tx]                       (kh = kw = ks)
+//   dgrad:    rows = ci, channel = co, tap (ty, tx) reads w[.., ky0 + step*(kh-1-ty), kx0 + step*(kw-1-tx)]
+//             (transposed and flipped; for a strided convolution one call per stride phase with that phase's taps)
 // ---------------------------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) weight_split_kernel(const float* __restrict__ w, float* __restrict__ out, int co, int ci, int ks,
-                                                           int cpad, bool dgrad) {
-  const int rows = dgrad ? ci : co, chans = dgrad ? co : ci, kk = ks * ks;
-  const int64_t total = (int64_t)rows * kk * cpad;
+struct SplitArgs {
+  int co, ci, ks, kh, kw, cpad, dgrad, ky0, kx0, step;
+};
+__global__ void __launch_bounds__(256) weight_split_kernel(const float* __restrict__ w, float* __restrict__ out, SplitArgs a) {
+  const int rows = a.dgrad ? a.ci : a.co, chans = a.dgrad ? a.co : a.ci, kk = a.kh * a.kw;
+  const int64_t total = (int64_t)rows * kk * a.cpad;
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
-  const int c = (int)(i % cpad);
-  const int tap = (int)((i / cpad) % kk);
-  const int row = (int)(i / ((int64_t)cpad * kk));
+  const int c = (int)(i % a.cpad);
+  const int tap = (int)((i / a.cpad) % kk);
+  const int row = (int)(i / ((int64_t)a.cpad * kk));
   float v = 0.f;
   if (c < chans) {
-    int ky = tap / ks, kx = tap - ky * ks;
-    if (dgrad) v = __ldg(w + (((int64_t)c * ci + row) * ks + (ks - 1 - ky)) * ks + (ks - 1 - kx));
-    else v = __ldg(w + (((int64_t)row * ci + c) * ks + ky) * ks + kx);
+    int ty = tap / a.kw, tx = tap - ty * a.kw;
+    if (a.dgrad) {
+      int ky = a.ky0 + a.step * (a.kh - 1 - ty), kx = a.kx0 + a.step * (a.kw - 1 - tx);
+      v = __ldg(w + (((int64_t)c * a.ci + row) * a.ks + ky) * a.ks + kx);
+    } else {
+      v = __ldg(w + (((int64_t)row * a.ci + c) * a.ks + ty) * a.ks + tx);
+    }
   }
   const float hi = tf32_rna(v);
   out[i] = hi;
@@ -387,9 +397,12 @@ bool load_driver_entry_points() {
   return g_encode_tiled && g_encode_im2col;
 }
 
-struct TcProblem {  // a stride-`stride` convolution of a channels-last activation `a` [n, ih, iw, c] producing [n, oh, ow, rows]
+struct TcProblem {  // a convolution of a channels-last activation `a` [n, ih, iw, c] producing a [n, oh, ow, rows] pixel grid
   const float* a;
-  int n, c, ih, iw, oh, ow, rows, ks, stride, pad;
+  int n, c, ih, iw, oh, ow, rows;
+  int kh, kw, stride;
+  int low_h, low_w;              // input coordinate of tap (0,0) at output pixel (0,0)
+  int out_step, out_y0, out_x0;  // where GEMM row (oy, ox) lands in the output tensor
 };
 
 int pick_bn(const TcProblem& p) {
@@ -406,19 +419,20 @@ int launch_tc(const TcProblem& p, const float* wsplit, const TcArgs& args, cudaS
   {
     cuuint64_t dims[4] = {(cuuint64_t)p.c, (cuuint64_t)p.iw, (cuuint64_t)p.ih, (cuuint64_t)p.n};
     cuuint64_t strides[3] = {(cuuint64_t)p.c * 4, (cuuint64_t)p.iw * p.c * 4, (cuuint64_t)p.ih * p.iw * p.c * 4};
-    int lower[2] = {-p.pad, -p.pad};
-    int upper[2] = {p.pad - (p.ks - 1), p.pad - (p.ks - 1)};
+    // base pixels run over [low, dim - 1 + upper] in steps of `stride`; their count must equal the output extent
+    int lower[2] = {p.low_w, p.low_h};
+    int upper[2] = {(p.ow - 1) * p.stride + p.low_w - (p.iw - 1), (p.oh - 1) * p.stride + p.low_h - (p.ih - 1)};
     cuuint32_t estr[4] = {1, (cuuint32_t)p.stride, (cuuint32_t)p.stride, 1};
     CUresult r = g_encode_im2col(&map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void*)p.a, dims, strides, lower, upper, BKF, BM, estr,
                                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
-      set_error("cuTensorMapEncodeIm2col failed (%d)", (int)r);
+      set_error("cuTensorMapEncodeIm2col failed (%d) for corners (%d,%d)/(%d,%d)", (int)r, lower[0], lower[1], upper[0], upper[1]);
       return OMT_ECUDA;
     }
   }
   {
-    const int kp = p.ks * p.ks * args.cpad;
+    const int kp = p.kh * p.kw * args.cpad;
     cuuint64_t dims[3] = {(cuuint64_t)kp, (cuuint64_t)p.rows, 2};
     cuuint64_t strides[2] = {(cuuint64_t)kp * 4, (cuuint64_t)kp * 4 * p.rows};
     cuuint32_t box[3] = {BKF, (cuuint32_t)BN, 1}, estr[3] = {1, 1, 1};
@@ -441,21 +455,18 @@ int launch_tc(const TcProblem& p, const float* wsplit, const TcArgs& args, cudaS
 
 size_t split_floats(int rows, int ks, int chans) { return (size_t)2 * rows * ks * ks * (cdiv(chans, BKF) * BKF); }
 
-int run_tc(const TcProblem& p, const float* w, bool dgrad, int co, int ci, const OmtAct* y, const float* bias, uint32_t flags, void* ws,
-           cudaStream_t s) {
-  if (!load_driver_entry_points()) {
-    set_error("the CUDA driver does not export cuTensorMapEncodeTiled/Im2col");
-    return OMT_ECUDA;
-  }
-  float* wsplit = (float*)ws;
+// one (sub-)convolution: re-lay the weights it needs into `wsplit`, then run the GEMM
+int run_tc(const TcProblem& p, const float* w, SplitArgs sp, float* wsplit, const OmtAct* y, const float* bias, uint32_t flags, cudaStream_t s) {
   TcArgs a{};
   a.y = view(y); a.bias = bias;
   a.M = p.n * p.oh * p.ow; a.N = p.rows; a.oh = p.oh; a.ow = p.ow;
-  a.ks = p.ks; a.stride = p.stride; a.pad = p.pad;
+  a.kh = p.kh; a.kw = p.kw; a.stride = p.stride; a.low_h = p.low_h; a.low_w = p.low_w;
+  a.out_step = p.out_step; a.out_y0 = p.out_y0; a.out_x0 = p.out_x0;
   a.cblocks = (int)cdiv(p.c, BKF); a.cpad = a.cblocks * BKF;
   a.flags = flags;
-  const int64_t total = (int64_t)p.rows * p.ks * p.ks * a.cpad;
-  weight_split_kernel<<<(unsigned)cdiv(total, 256), 256, 0, s>>>(w, wsplit, co, ci, p.ks, a.cpad, dgrad);
+  sp.kh = p.kh; sp.kw = p.kw; sp.cpad = a.cpad;
+  const int64_t total = (int64_t)p.rows * p.kh * p.kw * a.cpad;
+  weight_split_kernel<<<(unsigned)cdiv(total, 256), 256, 0, s>>>(w, wsplit, sp);
   int r = check_launch("conv_tc_weight_split");
   if (r) return r;
   switch (pick_bn(p)) {
@@ -464,7 +475,6 @@ int run_tc(const TcProblem& p, const float* w, bool dgrad, int co, int ci, const
     default: return launch_tc<256>(p, wsplit, a, s);
   }
 }
-
 
 // ---------------------------------------------------------------------------------------------------------------------
 // weight gradient kernel
@@ -735,7 +745,7 @@ int tc_error_word() {
 bool tc_supported(int kind, const OmtConvGeo* g, const OmtAct* a, const OmtAct* b) {
   if (!b || !b->p) return false;
   if (kind == 0) return cl_ok(a, g->ci, g->ih, g->iw) && g->ci >= 8 && g->co >= 8 && g->pad < g->ks;
-  if (kind == 1) return g->stride == 1 && cl_ok(a, g->co, g->oh, g->ow) && g->co >= 8 && g->ci >= 8 && g->ks - 1 - g->pad >= 0;
+  if (kind == 1) return cl_ok(a, g->co, g->oh, g->ow) && g->co >= 8 && g->ci >= 8 && g->pad < g->ks;
   // kind 2: a = x, b = gy
   return cl_ok(a, g->ci, g->ih, g->iw) && cl_ok(b, g->co, g->oh, g->ow) && g->ci >= 8 && g->co >= 8 && g->pad < g->ks;
 }
@@ -749,13 +759,58 @@ int tc_conv_fwd(const OmtConvGeo* g, const OmtAct* x, const float* w, const floa
                 cudaStream_t s) {
   (void)stats;
   OMT_REQUIRE(!(flags & OMT_EPI_BNSTATS), "OMT_EPI_BNSTATS is not implemented in the tensor-core epilogue yet");
-  TcProblem p{x->p, g->n, g->ci, g->ih, g->iw, g->oh, g->ow, g->co, g->ks, g->stride, g->pad};
-  return run_tc(p, w, false, g->co, g->ci, y, bias, flags, ws, s);
+  if (!load_driver_entry_points()) {
+    set_error("the CUDA driver does not export cuTensorMapEncodeTiled/Im2col");
+    return OMT_ECUDA;
+  }
+  TcProblem p{x->p, g->n, g->ci, g->ih, g->iw, g->oh, g->ow, g->co, g->ks, g->ks, g->stride, -g->pad, -g->pad, 1, 0, 0};
+  SplitArgs sp{g->co, g->ci, g->ks, 0, 0, 0, 0, 0, 0, 1};
+  return run_tc(p, w, sp, (float*)ws, y, bias, flags, s);
 }
-// stride-1 input gradient = forward convolution of gy with transposed, flipped weights and padding ks-1-pad
-int tc_conv_dgrad(const OmtConvGeo* g, const OmtAct* gy, const float* w, const OmtAct* dx, void* ws, cudaStream_t s) {
-  TcProblem p{gy->p, g->n, g->co, g->oh, g->ow, g->ih, g->iw, g->ci, g->ks, 1, g->ks - 1 - g->pad};
-  return run_tc(p, w, true, g->co, g->ci, dx, nullptr, 0, ws, s);
+
+// Input gradient as forward convolutions of gy. Stride 1: one convolution with the weights transposed and flipped and
+// padding ks-1-pad. Stride s: one stride-1 convolution per phase (py, px) of the input grid, over the taps ky = ky0 + s*ty
+// that reach that phase (the index algebra of the reference's host loop, csrc/conv.cpp:78-95), written to every s-th pixel;
+// phases no tap reaches stay zero.
+int tc_conv_dgrad(const OmtConvGeo* g, const OmtAct* gy, const float* w, const OmtAct* dx, void* ws, cudaStream_t st_) {
+  if (!load_driver_entry_points()) {
+    set_error("the CUDA driver does not export cuTensorMapEncodeTiled/Im2col");
+    return OMT_ECUDA;
+  }
+  const int s = g->stride;
+  float* wsplit = (float*)ws;
+  bool zeroed = false;
+  for (int py = 0; py < s; py++)
+    for (int px = 0; px < s; px++) {
+      const int hi = (int)cdiv(g->ih - py, s), wi = (int)cdiv(g->iw - px, s);
+      if (hi <= 0 || wi <= 0) continue;
+      const int ky0 = (py + g->pad) % s, kx0 = (px + g->pad) % s;
+      const int jy = ky0 < g->ks ? (int)cdiv(g->ks - ky0, s) : 0, jx = kx0 < g->ks ? (int)cdiv(g->ks - kx0, s) : 0;
+      if (jy == 0 || jx == 0) {  // no tap lands on this phase: its pixels are zero
+        if (!zeroed) {
+          OMT_REQUIRE(is_nhwc(dx, g->ci, g->ih, g->iw) || is_nchw(dx, g->ci, g->ih, g->iw), "strided input gradient needs a dense dx");
+          OMT_CUDA(cudaMemsetAsync(dx->p, 0, (size_t)g->n * g->ci * g->ih * g->iw * sizeof(float), st_));
+          zeroed = true;
+        }
+        continue;
+      }
+    }
+  for (int py = 0; py < s; py++)
+    for (int px = 0; px < s; px++) {
+      const int hi = (int)cdiv(g->ih - py, s), wi = (int)cdiv(g->iw - px, s);
+      if (hi <= 0 || wi <= 0) continue;
+      const int ky0 = (py + g->pad) % s, kx0 = (px + g->pad) % s;
+      const int jy = ky0 < g->ks ? (int)cdiv(g->ks - ky0, s) : 0, jx = kx0 < g->ks ? (int)cdiv(g->ks - kx0, s) : 0;
+      if (jy == 0 || jx == 0) continue;
+      const int qy = (py + g->pad - ky0) / s, qx = (px + g->pad - kx0) / s;
+      // output (i, j) of the phase reads gy[i + qy - ty, j + qx - tx]; with flipped taps ty' = jy-1-ty the first tap sits at qy-(jy-1)
+      TcProblem p{gy->p, g->n, g->co, g->oh, g->ow, hi, wi, g->ci, jy, jx, 1, qy - (jy - 1), qx - (jx - 1), s, py, px};
+      SplitArgs sp{g->co, g->ci, g->ks, 0, 0, 0, 1, ky0, kx0, s};
+      int r = run_tc(p, w, sp, wsplit, dx, nullptr, 0, st_);
+      if (r) return r;
+      wsplit += 2 * (size_t)g->ci * jy * jx * (cdiv(g->co, BKF) * BKF);
+    }
+  return OMT_OK;
 }
 int tc_conv_wgrad(const OmtConvGeo* g, const OmtAct* x, const OmtAct* gy, float* dw, float scale, void* ws, cudaStream_t s) {
   if (!load_driver_entry_points()) {

@@ -9,6 +9,7 @@
 
 #include <ATen/CPUGeneratorImpl.h>
 #include <ATen/EmptyTensor.h>
+#include <ATen/detail/CUDAHooksInterface.h>
 #include <ATen/detail/PrivateUse1HooksInterface.h>
 #include <ATen/native/Resize.h>
 #include <c10/core/impl/DeviceGuardImplInterface.h>
@@ -301,6 +302,9 @@ struct Hooks final : at::PrivateUse1HooksInterface {
   const at::Generator& getDefaultGenerator(c10::DeviceIndex) const override { return default_generator(); }
   at::Generator getNewGenerator(c10::DeviceIndex i) const override { return at::make_generator<Generator>(i < 0 ? 0 : i); }
   at::Device getDeviceFromPtr(void*) const override { return {kDev, 0}; }
+  // pinned host memory is CUDA's: tensor.pin_memory() keeps working with this device registered
+  bool isPinnedPtr(const void* data) const override { return at::detail::getCUDAHooks().isPinnedPtr(data); }
+  c10::Allocator* getPinnedMemoryAllocator() const override { return at::detail::getCUDAHooks().getPinnedMemoryAllocator(); }
   void resizePrivateUse1Bytes(const c10::Storage& storage, size_t newsize) const override { grow_storage(storage, newsize); }
 };
 static void grow_storage(const c10::Storage& storage, size_t newsize) {
