@@ -356,6 +356,8 @@ def main():
     ap.add_argument("--workload", default="resnet50", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile-step", action="store_true",
+                    help="for ncu --profile-from-start off: after the warm-up run ONE step between cudaProfilerStart/Stop and exit")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     wl = WORKLOADS[args.workload]() if args.workload != "conv1" else Conv1()
@@ -370,6 +372,16 @@ def main():
     sampler = ClockSampler(torch.cuda.current_device())
     if rank == 0:
         sampler.start()
+    if args.profile_step:
+        for _ in range(args.warmup):
+            wl.step()
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        wl.step()
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        print(json.dumps({"profiled": wl.name, "kernel_counts": capi.kernel_counts()}))
+        return
     l0 = capi.lib().omt_launch_count()
     ms = time_steps(wl.step, args.steps, args.warmup, world, flush)
     launches = (capi.lib().omt_launch_count() - l0) // (args.steps + args.warmup)

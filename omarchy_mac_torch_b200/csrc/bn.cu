@@ -125,14 +125,21 @@ __global__ void __launch_bounds__(256) bn_part_nhwc(const float* __restrict__ x,
   }
 }
 
-// finalise statistics: one thread per channel. shift_stride = distance between channels' first elements.
-__global__ void bn_stats_fin(const float* __restrict__ x, int64_t shift_stride, const float* __restrict__ part, int c, int S,
-                             float count, float corr, float momentum, float eps, float* mean, float* var, float* invstd,
-                             const float* rm_in, const float* rv_in, float* rm_out, float* rv_out) {
-  int ch = blockIdx.x * blockDim.x + threadIdx.x;
+// finalise statistics: one warp per channel sums the S partial pairs (contiguous in memory), lane 0 writes.
+// shift_stride = distance between channels' first elements.
+__global__ void __launch_bounds__(256) bn_stats_fin(const float* __restrict__ x, int64_t shift_stride, const float* __restrict__ part, int c, int S,
+                                                    float count, float corr, float momentum, float eps, float* mean, float* var, float* invstd,
+                                                    const float* rm_in, const float* rv_in, float* rm_out, float* rv_out) {
+  const int ch = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (ch >= c) return;
   float s1 = 0.f, s2 = 0.f;
-  for (int k = 0; k < S; k++) { s1 += part[((int64_t)ch * S + k) * 2]; s2 += part[((int64_t)ch * S + k) * 2 + 1]; }
+  const float2* p = reinterpret_cast<const float2*>(part) + (int64_t)ch * S;
+  for (int k = lane; k < S; k += 32) {
+    float2 v = __ldg(p + k);
+    s1 += v.x; s2 += v.y;
+  }
+  s1 = warp_sum(s1); s2 = warp_sum(s2);
+  if (lane) return;
   float a = s1 / count, shift = x ? x[ch * shift_stride] : 0.f;
   float m = shift + a, v = fmaxf(s2 / count - a * a, 0.f);
   if (mean) mean[ch] = m;
@@ -145,11 +152,17 @@ __global__ void bn_stats_fin(const float* __restrict__ x, int64_t shift_stride, 
   }
 }
 // finalise backward sums: dgb[0][c] = dgamma (s2), dgb[1][c] = dbeta (s1)   (bn_bwd_fin.wgsl)
-__global__ void bn_bwd_fin(const float* __restrict__ part, int c, int S, float scale, float* dgb, float* raw) {
-  int ch = blockIdx.x * blockDim.x + threadIdx.x;
+__global__ void __launch_bounds__(256) bn_bwd_fin(const float* __restrict__ part, int c, int S, float scale, float* dgb, float* raw) {
+  const int ch = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (ch >= c) return;
   float s1 = 0.f, s2 = 0.f;
-  for (int k = 0; k < S; k++) { s1 += part[((int64_t)ch * S + k) * 2]; s2 += part[((int64_t)ch * S + k) * 2 + 1]; }
+  const float2* p = reinterpret_cast<const float2*>(part) + (int64_t)ch * S;
+  for (int k = lane; k < S; k += 32) {
+    float2 v = __ldg(p + k);
+    s1 += v.x; s2 += v.y;
+  }
+  s1 = warp_sum(s1); s2 = warp_sum(s2);
+  if (lane) return;
   raw[ch] = s2; raw[c + ch] = s1;  // unscaled, for the dx formula
   dgb[ch] = s2 * scale; dgb[c + ch] = s1 * scale;
 }
@@ -189,7 +202,7 @@ __global__ void __launch_bounds__(256) bn_ew_vec4(BnEw a) {
     if (RELU) yv = __ldg(reinterpret_cast<const float4*>(a.y + i));
   }
   if (NHWC) {
-    int ch = (int)(i % a.c);
+    int ch = a.total < 0x7fffffffll ? (int)((uint32_t)i % (uint32_t)a.c) : (int)(i % a.c);
     float4 mean = __ldg(reinterpret_cast<const float4*>(a.mean + ch)), inv = __ldg(reinterpret_cast<const float4*>(a.inv + ch));
     float4 ga = __ldg(reinterpret_cast<const float4*>(a.gamma + ch));
     float4 be = ga, dg = ga, db = ga;
@@ -201,7 +214,7 @@ __global__ void __launch_bounds__(256) bn_ew_vec4(BnEw a) {
     o.z = bn_ew_one<KIND, RELU>(a, xv.z, gv.z, yv.z, mean.z, inv.z, ga.z, be.z, dg.z, db.z);
     o.w = bn_ew_one<KIND, RELU>(a, xv.w, gv.w, yv.w, mean.w, inv.w, ga.w, be.w, dg.w, db.w);
   } else {
-    int ch = (int)((i / a.hw) % a.c);
+    int ch = a.total < 0x7fffffffll ? (int)(((uint32_t)i / (uint32_t)a.hw) % (uint32_t)a.c) : (int)((i / a.hw) % a.c);
     float mean = __ldg(a.mean + ch), inv = __ldg(a.inv + ch), ga = __ldg(a.gamma + ch), be = 0.f, dg = 0.f, db = 0.f;
     if (KIND <= 1) be = __ldg(a.beta + ch);
     if (KIND == 1) inv = rsqrtf(inv + a.eps);
@@ -325,7 +338,7 @@ int omt_bn_stats(const OmtAct* x, int32_t n, int32_t c, int32_t h, int32_t w, fl
   float count = (float)((int64_t)n * h * w);
   float corr = count / std::max(count - 1.f, 1.f);
   bool fn = flags & OMT_BN_FUNCTIONAL;
-  bn_stats_fin<<<(unsigned)cdiv(c, 128), 128, 0, s>>>(x->p, lay == 0 ? (int64_t)h * w : 1, part, c, S, count, corr, momentum, eps,
+  bn_stats_fin<<<(unsigned)cdiv((int64_t)c * 32, 256), 256, 0, s>>>(x->p, lay == 0 ? (int64_t)h * w : 1, part, c, S, count, corr, momentum, eps,
                                                       mean, var, invstd, rm, rv, rm ? (fn ? new_rm : rm) : nullptr,
                                                       rm ? (fn ? new_rv : rv) : nullptr);
   return check_launch("bn_stats_fin");
@@ -382,7 +395,7 @@ int omt_bn_backward(const OmtAct* gy, const OmtAct* x, const OmtAct* y, const Om
   int S = 1;
   r = launch_part<1>(lay, x->p, gy->p, relu ? y->p : x->p, mean, invstd, relu, n, c, h, w, &S, part, s);
   if (r) return r;
-  bn_bwd_fin<<<(unsigned)cdiv(c, 128), 128, 0, s>>>(part, c, S, scale, dgb, raw);
+  bn_bwd_fin<<<(unsigned)cdiv((int64_t)c * 32, 256), 256, 0, s>>>(part, c, S, scale, dgb, raw);
   r = check_launch("bn_bwd_fin");
   if (r || !dx || !dx->p) return r;
   BnEw a{};

@@ -209,8 +209,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) {  // TMEM: BN fp32 columns (power of two >= 32)
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"((uint32_t)BN)
+  if (warp == 1) {  // TMEM: two accumulators of BN fp32 columns each (a power of two >= 32 in total)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"((uint32_t)(2 * BN))
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -261,9 +261,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
         for (int k = 0; k < BKF / UMMA_K; k++) {
           const uint64_t adv = (uint64_t)((k * UMMA_K * 4) >> 4);  // 32 bytes per k-step inside the swizzled row
-          umma_tf32(tmem_acc, a_lo + adv, b_hi + adv, idesc, (kb | k) ? 1u : 0u);
-          umma_tf32(tmem_acc, a_hi + adv, b_lo + adv, idesc, 1u);
-          umma_tf32(tmem_acc, a_hi + adv, b_hi + adv, idesc, 1u);
+          // two accumulators: the cross terms (2^-11 of the result) go to columns [BN, 2BN) so that the truncation the
+          // tensor core applies on every accumulate hits the main sum once per k-step instead of three times
+          umma_tf32(tmem_acc + BN, a_lo + adv, b_hi + adv, idesc, (kb | k) ? 1u : 0u);
+          umma_tf32(tmem_acc + BN, a_hi + adv, b_lo + adv, idesc, 1u);
+          umma_tf32(tmem_acc, a_hi + adv, b_hi + adv, idesc, (kb | k) ? 1u : 0u);
         }
         umma_commit(BAR(2 * S::STAGES + s));  // stage is free once these MMAs have read it
       }
@@ -307,8 +309,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const bool vec = g.y.sc == 1 && ((reinterpret_cast<uintptr_t>(yrow) & 15) == 0);
 #pragma unroll 1
       for (int c = 0; c < BN / 32; c++) {
-        uint32_t v[32];
+        uint32_t v[32], u[32];
         tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + c * 32, v);
+        tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + BN + c * 32, u);
+#pragma unroll
+        for (int j = 0; j < 32; j++) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(u[j]));
         if (m >= g.M) continue;
         const int nb = n0 + c * 32;
         if (nb >= g.N) continue;
@@ -335,7 +340,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   __syncthreads();
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"((uint32_t)BN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"((uint32_t)(2 * BN)) : "memory");
   }
 }
 
@@ -535,7 +540,7 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"((uint32_t)BN)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"((uint32_t)(2 * BN))
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -588,9 +593,9 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
           const uint64_t a_hi = smem_desc_mn_sw128(stage + koff, S::CH), a_lo = smem_desc_mn_sw128(stage + S::HALF + koff, S::CH);
           const uint64_t b_hi = smem_desc_mn_sw128(stage + S::A_BYTES + koff, S::CH);
           const uint64_t b_lo = smem_desc_mn_sw128(stage + S::HALF + S::A_BYTES + koff, S::CH);
-          umma_tf32(tmem_acc, a_lo, b_hi, idesc, (kb | k) ? 1u : 0u);
-          umma_tf32(tmem_acc, a_hi, b_lo, idesc, 1u);
-          umma_tf32(tmem_acc, a_hi, b_hi, idesc, 1u);
+          umma_tf32(tmem_acc + BN, a_lo, b_hi, idesc, (kb | k) ? 1u : 0u);  // cross terms in their own accumulator
+          umma_tf32(tmem_acc + BN, a_hi, b_lo, idesc, 1u);
+          umma_tf32(tmem_acc, a_hi, b_hi, idesc, (kb | k) ? 1u : 0u);
         }
         umma_commit(BAR(2 * S::STAGES + s));
       }
@@ -632,7 +637,11 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
       for (int c = half; c < BN / 32; c += 2) {
         uint32_t v[32];
         if (kblocks > 0) {
+          uint32_t u[32];
           tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + c * 32, v);
+          tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + BN + c * 32, u);
+#pragma unroll
+          for (int j = 0; j < 32; j++) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(u[j]));
         } else {
 #pragma unroll
           for (int j = 0; j < 32; j++) v[j] = 0u;  // a slice with no pixels contributes zeros
@@ -649,7 +658,7 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
   __syncthreads();
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"((uint32_t)BN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"((uint32_t)(2 * BN)) : "memory");
   }
 }
 

@@ -10,17 +10,24 @@
 
 namespace omt {
 
+// index -> (img, ch, y, x) in memory order of the layout; 32-bit arithmetic whenever the index fits (64-bit division is
+// emulated and would dominate these bandwidth-bound kernels)
+template <bool NHWC, class I>
+__device__ __forceinline__ void decode4_t(I i, int c, int h, int w, int& img, int& ch, int& y, int& x) {
+  if (NHWC) {
+    ch = (int)(i % (I)c); i /= (I)c;
+    x = (int)(i % (I)w); i /= (I)w;
+    y = (int)(i % (I)h); img = (int)(i / (I)h);
+  } else {
+    x = (int)(i % (I)w); i /= (I)w;
+    y = (int)(i % (I)h); i /= (I)h;
+    ch = (int)(i % (I)c); img = (int)(i / (I)c);
+  }
+}
 template <bool NHWC>
 __device__ __forceinline__ void decode4(int64_t i, int c, int h, int w, int& img, int& ch, int& y, int& x) {
-  if (NHWC) {
-    ch = (int)(i % c); i /= c;
-    x = (int)(i % w); i /= w;
-    y = (int)(i % h); img = (int)(i / h);
-  } else {
-    x = (int)(i % w); i /= w;
-    y = (int)(i % h); i /= h;
-    ch = (int)(i % c); img = (int)(i / c);
-  }
+  if (i < 0x7fffffffll) decode4_t<NHWC, uint32_t>((uint32_t)i, c, h, w, img, ch, y, x);
+  else decode4_t<NHWC, int64_t>(i, c, h, w, img, ch, y, x);
 }
 
 // ---- 2x2 stride-2 max pool with 2-bit argmax ----

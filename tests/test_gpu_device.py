@@ -207,7 +207,7 @@ def test_fused_stacks_train_eval_and_accumulate(omt):
         torch.manual_seed(0)
         ref = cls() if bias is None else cls(bias=bias)
         mod = copy.deepcopy(ref).to(D)
-        o1, o2 = torch.optim.Adam(ref.parameters(), 1e-3), torch.optim.Adam(mod.parameters(), 1e-3)
+        o1, o2 = torch.optim.SGD(ref.parameters(), 0.05, momentum=0.9), torch.optim.SGD(mod.parameters(), 0.05, momentum=0.9)
         shape = (64, 3, 32, 32) if cls is models.PlainCNN3 else (64, 1, 28, 28)
         X, y = torch.rand(*shape), torch.randint(0, 10, (64,))
         for _ in range(3):
