@@ -130,6 +130,22 @@ int omt_conv_dgrad(const OmtConvGeo* g, const OmtAct* gy, const float* w, const 
 int omt_conv_wgrad(const OmtConvGeo* g, const OmtAct* x, const OmtAct* gy, float* dw, float scale, uint32_t flags,
                    void* workspace, size_t workspace_bytes, omt_stream_t stream);
 
+/* Weight gradient for callers that must not allocate device memory. No counterpart in the reference.
+ * Some hosts of this library cannot call cudaMalloc while they run: code replaying a fixed launch sequence inside a
+ * real-time loop, or a process whose device memory was handed out in full at start-up and that has no allocator of its
+ * own to ask. omt_conv_wgrad needs split-K scratch (from the caller's workspace or the library's allocator); this
+ * variant runs the same exact-fp32 kernels with the scratch in a fixed array inside the library image instead, and
+ * calls no cudaMalloc, cudaFree or allocating library routine.
+ *   - Capacity: omt_conv_wgrad_noalloc_capacity() bytes (16 MiB) of split-K slabs; a geometry that needs more is refused
+ *     with OMT_ETOOBIG. Every GPU that loads the library holds that array until the process exits.
+ *   - The first call on each device looks up the array's device address (with that device current); make that first call
+ *     outside any stream capture.
+ *   - All calls on a device share the array. The slabs are fully overwritten by every call, so nothing needs clearing,
+ *     but two calls that overlap on the GPU (different streams) race on it: keep them on one stream or order them. */
+size_t omt_conv_wgrad_noalloc_capacity(void);
+int omt_conv_wgrad_noalloc(const OmtConvGeo* g, const OmtAct* x, const OmtAct* gy, float* dw, float scale,
+                           omt_stream_t stream);
+
 /* db[c] = sum over (n,h,w) of gy. Replaces csrc/kernels/csum_nchw.wgsl (csrc/conv.cpp:232-235). */
 int omt_conv_bias_grad(const OmtAct* gy, int32_t n, int32_t c, int32_t h, int32_t w, float* db, float scale,
                        omt_stream_t stream);

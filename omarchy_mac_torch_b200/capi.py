@@ -74,6 +74,8 @@ SIGNATURES = {
     "omt_conv_fwd": (_I, [_G, _A, _P, _P, _A, _P, _U, _P, _SZ, _P]),
     "omt_conv_dgrad": (_I, [_G, _A, _P, _A, _U, _P, _SZ, _P]),
     "omt_conv_wgrad": (_I, [_G, _A, _A, _P, _F, _U, _P, _SZ, _P]),
+    "omt_conv_wgrad_noalloc_capacity": (_SZ, []),
+    "omt_conv_wgrad_noalloc": (_I, [_G, _A, _A, _P, _F, _P]),
     "omt_conv_bias_grad": (_I, [_A, _I, _I, _I, _I, _P, _F, _P]),
     "omt_conv_timing": (_I, [_I]),
     "omt_conv_timing_read": (_I, [C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_int64), _I]),

@@ -404,6 +404,53 @@ size_t simt_wgrad_workspace(const OmtConvGeo* g) {
   return (size_t)slices * g->co * g->ci * g->ks * g->ks * sizeof(float);
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// weight gradient without any allocation
+// ---------------------------------------------------------------------------------------------------------------------
+// Scratch for the split-K slabs of omt_conv_wgrad_noalloc. It lives in the library image: every GPU that loads the
+// library holds these 16 MiB until the process exits. All calls on a device share it.
+constexpr size_t NOALLOC_SCRATCH_FLOATS = (size_t)4 << 20;
+static __device__ __align__(256) float g_noalloc_scratch[NOALLOC_SCRATCH_FLOATS];
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+static float* g_noalloc_ptr[NOALLOC_MAX_DEVICES];  // device address of g_noalloc_scratch, per device ordinal
+
+}  // namespace omt
+
+using namespace omt;
+
+extern "C" size_t omt_conv_wgrad_noalloc_capacity(void) { return NOALLOC_SCRATCH_FLOATS * sizeof(float); }
+
+extern "C" int omt_conv_wgrad_noalloc(const OmtConvGeo* g, const OmtAct* x, const OmtAct* gy, float* dw, float scale,
+                                      omt_stream_t stream) {
+  OMT_REQUIRE(g && g->groups == 1 && g->n > 0 && g->ci > 0 && g->co > 0 && g->ks >= 1 && g->ks <= 11 && g->stride >= 1 && g->stride <= 4 &&
+                  g->pad >= 0 && g->pad <= g->ks,
+              "omt_conv_wgrad_noalloc: needs a dense convolution with ks<=11, stride 1..4, pad<=ks");
+  OMT_REQUIRE(g->oh == (g->ih + 2 * g->pad - g->ks) / g->stride + 1 && g->ow == (g->iw + 2 * g->pad - g->ks) / g->stride + 1 && g->oh > 0 &&
+                  g->ow > 0,
+              "omt_conv_wgrad_noalloc: output size does not match the geometry");
+  OMT_REQUIRE(x && gy && x->p && gy->p && dw, "omt_conv_wgrad_noalloc: null pointer");
+  const size_t need = simt_wgrad_workspace(g);
+  if (need > NOALLOC_SCRATCH_FLOATS * sizeof(float)) {
+    set_error("omt_conv_wgrad_noalloc: this geometry needs %zu bytes of split-K scratch, the built-in scratch holds %zu", need,
+              NOALLOC_SCRATCH_FLOATS * sizeof(float));
+    return OMT_ETOOBIG;
+  }
+  int dev = -1;
+  OMT_CUDA(cudaGetDevice(&dev));
+  OMT_REQUIRE(dev >= 0 && dev < NOALLOC_MAX_DEVICES, "omt_conv_wgrad_noalloc: device ordinal %d out of range", dev);
+  if (!g_noalloc_ptr[dev]) {
+    // The array's name is only a host-side handle; the kernels need its address on the current device. Looked up once per
+    // device (this first call should therefore come before any stream capture).
+    float* p = nullptr;
+    OMT_CUDA(cudaGetSymbolAddress((void**)&p, g_noalloc_scratch));
+    g_noalloc_ptr[dev] = p;
+  }
+  return simt_conv_wgrad(g, x, gy, dw, scale, g_noalloc_ptr[dev], st(stream));
+}
+
+namespace omt {
+
 // ---- bias gradient: db[c] = sum gy[:, c, :, :] ---------------------------------------------------------------------
 // One block per (channel, slice) with 128-bit loads when the plane is contiguous, then a second tiny kernel; the
 // reference used one workgroup per channel (csrc/kernels/csum_nchw.wgsl), i.e. 64 blocks for 64 channels.
