@@ -90,6 +90,11 @@ __device__ __forceinline__ void tma_im2col_4d(uint32_t dst, const CUtensorMap* m
       ::"r"(dst), "l"(map), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n), "h"(ow), "h"(oh)
       : "memory");
 }
+__device__ __forceinline__ void tma_tile_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z, int w) {
+  asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+               ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z), "r"(w)
+               : "memory");
+}
 __device__ __forceinline__ void tma_tile_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
   asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
                ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z)
@@ -167,6 +172,11 @@ struct TcArgs {
   int cblocks;        // 32-channel blocks per tap
   int cpad;           // cblocks * 32
   uint32_t flags;
+  // "window" mode (few input channels): the A operand comes from a zero-padded [n][h][w][4] copy of the input through a
+  // tiled tensor map whose pixel dimension overlaps (stride = conv stride * 16 bytes), so one 32-float row holds 8
+  // consecutive input pixels x 4 channels = the (kx, c) run of a filter row. GEMM rows are win_w x win_h pixel rectangles.
+  int win_w, win_h;   // 0 = im2col mode
+  int tiles_x, tiles_y;
 };
 
 template <int BN>
@@ -223,7 +233,17 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // ---------------- TMA producer ----------------
     if (lane == 0) {
       const int ohw = g.oh * g.ow;
-      const int img0 = m0 / ohw, r0 = m0 - img0 * ohw, oy0 = r0 / g.ow, ox0 = r0 - oy0 * g.ow;
+      int img0, oy0, ox0;
+      if (g.win_w) {  // blockIdx.x enumerates (image, tile row, tile column)
+        const int per = g.tiles_x * g.tiles_y;
+        img0 = blockIdx.x / per;
+        const int r = blockIdx.x - img0 * per;
+        oy0 = (r / g.tiles_x) * g.win_h; ox0 = (r % g.tiles_x) * g.win_w;
+      } else {
+        img0 = m0 / ohw;
+        const int r0 = m0 - img0 * ohw;
+        oy0 = r0 / g.ow; ox0 = r0 - oy0 * g.ow;
+      }
       const int w0 = ox0 * g.stride + g.low_w, h0 = oy0 * g.stride + g.low_h;
       int issued = 0;
       for (int kb = 0; kb < kblocks; kb++) {
@@ -233,7 +253,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int ky = tap / g.kw, kx = tap - ky * g.kw;
         const uint32_t stage = smem_base + s * S::STAGE_BYTES;
         mbar_expect_tx(BAR(s), S::A_BYTES + 2 * S::B_BYTES);
-        tma_im2col_4d(stage, &map_a, BAR(s), cb * BKF, w0, h0, img0, (uint16_t)kx, (uint16_t)ky);
+        if (g.win_w) tma_tile_4d(stage, &map_a, BAR(s), cb * BKF, ox0, h0 + ky, img0);  // kw == 1: tap = filter row
+        else tma_im2col_4d(stage, &map_a, BAR(s), cb * BKF, w0, h0, img0, (uint16_t)kx, (uint16_t)ky);
         tma_tile_3d(stage + 2 * S::A_BYTES, &map_w, BAR(s), tap * g.cpad + cb * BKF, n0, 0);
         tma_tile_3d(stage + 2 * S::A_BYTES + S::B_BYTES, &map_w, BAR(s), tap * g.cpad + cb * BKF, n0, 1);
         issued = kb + 1;
@@ -302,9 +323,21 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (ok) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int q = warp & 3;  // TMEM lane quarter this warp may read
-      const int m = m0 + q * 32 + lane;
+      int m = m0 + q * 32 + lane;
       const int ohw = g.oh * g.ow;
-      const int img = m / ohw, r = m - img * ohw, oy = r / g.ow, ox = r - oy * g.ow;
+      int img, oy, ox;
+      if (g.win_w) {
+        const int per = g.tiles_x * g.tiles_y, r = q * 32 + lane;
+        img = blockIdx.x / per;
+        const int t = blockIdx.x - img * per;
+        oy = (t / g.tiles_x) * g.win_h + r / g.win_w; ox = (t % g.tiles_x) * g.win_w + r % g.win_w;
+        m = (oy < g.oh && ox < g.ow) ? 0 : g.M;  // rows outside the image are not stored
+        if (m) { oy = 0; ox = 0; }
+      } else {
+        img = m / ohw;
+        const int r = m - img * ohw;
+        oy = r / g.ow; ox = r - oy * g.ow;
+      }
       float* yrow = g.y.p + g.y.off(img, 0, oy * g.out_step + g.out_y0, ox * g.out_step + g.out_x0);
       const bool vec = g.y.sc == 1 && ((reinterpret_cast<uintptr_t>(yrow) & 15) == 0);
 #pragma unroll 1
@@ -352,9 +385,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // ---------------------------------------------------------------------------------------------------------------------
 struct SplitArgs {
   int co, ci, ks, kh, kw, cpad, dgrad, ky0, kx0, step;
+  int window;  // forward, window mode: tap = filter row ky, column k' = kx*4 + c
 };
 __global__ void __launch_bounds__(256) weight_split_kernel(const float* __restrict__ w, float* __restrict__ out, SplitArgs a) {
-  const int rows = a.dgrad ? a.ci : a.co, chans = a.dgrad ? a.co : a.ci, kk = a.kh * a.kw;
+  const int rows = a.dgrad ? a.ci : a.co, chans = a.window ? a.cpad : (a.dgrad ? a.co : a.ci), kk = a.kh * a.kw;
   const int64_t total = (int64_t)rows * kk * a.cpad;
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
@@ -364,7 +398,10 @@ __global__ void __launch_bounds__(256) weight_split_kernel(const float* __restri
   float v = 0.f;
   if (c < chans) {
     int ty = tap / a.kw, tx = tap - ty * a.kw;
-    if (a.dgrad) {
+    if (a.window) {
+      int kx = c >> 2, cc = c & 3;
+      v = (kx < a.ks && cc < a.ci) ? __ldg(w + (((int64_t)row * a.ci + cc) * a.ks + ty) * a.ks + kx) : 0.f;
+    } else if (a.dgrad) {
       int ky = a.ky0 + a.step * (a.kh - 1 - ty), kx = a.kx0 + a.step * (a.kw - 1 - tx);
       v = __ldg(w + (((int64_t)c * a.ci + row) * a.ks + ky) * a.ks + kx);
     } else {
@@ -738,6 +775,127 @@ int launch_wgrad(const OmtConvGeo* g, const WgPlan& w, const float* x, const flo
   return check_launch(BN == 64 ? "wgrad_tc_128x64" : (BN == 128 ? "wgrad_tc_128x128" : "wgrad_tc_128x256"));
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------------
+// window mode (ci <= 4): staging copy and host side
+// ---------------------------------------------------------------------------------------------------------------------
+// xs[n][ih][ws][4] = x[n][c][h][w - pad] (zero outside, zero for c >= ci): a channels-last copy padded to 4 channels and
+// by `pad` zero pixels on the left (and enough on the right), so that the window rows need no horizontal bounds handling.
+__global__ void __launch_bounds__(256) stage_window_kernel(ActView x, float* __restrict__ xs, int n, int ci, int ih, int iw, int ws, int pad) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t total = (int64_t)n * ih * ws;
+  if (i >= total) return;
+  const int wp = (int)(i % ws);
+  const int h = (int)((i / ws) % ih);
+  const int img = (int)(i / ((int64_t)ws * ih));
+  const int w = wp - pad;
+  float v[4] = {0.f, 0.f, 0.f, 0.f};
+  if (w >= 0 && w < iw) {
+    const float* p = x.p + x.off(img, 0, h, w);
+#pragma unroll
+    for (int c = 0; c < 4; c++)
+      if (c < ci) v[c] = __ldg(p + c * x.sc);
+  }
+  reinterpret_cast<float4*>(xs)[i] = make_float4(v[0], v[1], v[2], v[3]);
+}
+
+struct WinPlan {
+  int kb;       // 32-float blocks per filter row: ceil(ks * 4 / 32)
+  int ws;       // padded width of the staging copy
+  int win_w, win_h, tiles_x, tiles_y;
+  size_t stage_floats, split_floats_;
+};
+WinPlan plan_window(const OmtConvGeo* g) {
+  WinPlan w{};
+  w.kb = (int)cdiv(g->ks * 4, BKF);
+  w.ws = std::max(g->iw + 2 * g->pad, (g->ow - 1) * g->stride + 8 * w.kb) + 8;
+  // widest power-of-two tile row that wastes the fewest pixels
+  int best = 8;
+  double best_eff = 0;
+  for (int tw = 8; tw <= 128; tw *= 2) {
+    int th = BM / tw;
+    double eff = ((double)g->ow * g->oh) / ((double)cdiv(g->ow, tw) * tw * cdiv(g->oh, th) * th);
+    if (eff > best_eff + 1e-9) { best_eff = eff; best = tw; }
+  }
+  w.win_w = best; w.win_h = BM / best;
+  w.tiles_x = (int)cdiv(g->ow, w.win_w); w.tiles_y = (int)cdiv(g->oh, w.win_h);
+  w.stage_floats = (size_t)g->n * g->ih * w.ws * 4;
+  w.split_floats_ = (size_t)2 * g->co * g->ks * w.kb * BKF;
+  return w;
+}
+bool window_ok(const OmtConvGeo* g) {
+  if (g->ci > 4 || g->co < 8 || g->pad >= g->ks) return false;
+  // box height (win_h rows at the conv stride) must fit a TMA box
+  return 128 * g->stride <= 256 * 8;
+}
+
+template <int BN>
+int launch_window(const OmtConvGeo* g, const WinPlan& w, const float* xs, const float* wsplit, const TcArgs& args, cudaStream_t s) {
+  using S = Smem<BN>;
+  alignas(64) CUtensorMap map_a, map_w;
+  {
+    // dims: k' (floats of a window row), ox (overlapping, one conv stride apart), input row, image
+    cuuint64_t dims[4] = {(cuuint64_t)w.kb * BKF, (cuuint64_t)g->ow, (cuuint64_t)g->ih, (cuuint64_t)g->n};
+    cuuint64_t strides[3] = {(cuuint64_t)g->stride * 16, (cuuint64_t)w.ws * 16, (cuuint64_t)g->ih * w.ws * 16};
+    cuuint32_t box[4] = {BKF, (cuuint32_t)w.win_w, (cuuint32_t)(w.win_h * g->stride), 1};
+    cuuint32_t estr[4] = {1, 1, (cuuint32_t)g->stride, 1};
+    CUresult r = g_encode_tiled(&map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void*)xs, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+      set_error("cuTensorMapEncodeTiled (window operand) failed (%d)", (int)r);
+      return OMT_ECUDA;
+    }
+  }
+  {
+    const int kp = g->ks * args.cpad;
+    cuuint64_t dims[3] = {(cuuint64_t)kp, (cuuint64_t)g->co, 2};
+    cuuint64_t strides[2] = {(cuuint64_t)kp * 4, (cuuint64_t)kp * 4 * g->co};
+    cuuint32_t box[3] = {BKF, (cuuint32_t)BN, 1}, estr[3] = {1, 1, 1};
+    CUresult r = g_encode_tiled(&map_w, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)wsplit, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+      set_error("cuTensorMapEncodeTiled failed (%d)", (int)r);
+      return OMT_ECUDA;
+    }
+  }
+  static bool attr_set = false;
+  if (!attr_set) {
+    OMT_CUDA(cudaFuncSetAttribute(conv_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
+    attr_set = true;
+  }
+  dim3 grid((unsigned)(g->n * w.tiles_x * w.tiles_y), (unsigned)cdiv(args.N, BN));
+  conv_tc_kernel<BN><<<grid, TC_THREADS, S::TOTAL, s>>>(map_a, map_w, args);
+  return check_launch(BN == 64 ? "conv_tc_window_128x64" : (BN == 128 ? "conv_tc_window_128x128" : "conv_tc_window_128x256"));
+}
+
+int run_window_fwd(const OmtConvGeo* g, const OmtAct* x, const float* w, const float* bias, const OmtAct* y, uint32_t flags, void* ws, cudaStream_t s) {
+  const WinPlan wp = plan_window(g);
+  float* xs = (float*)ws;
+  float* wsplit = xs + ((wp.stage_floats + 63) / 64) * 64;
+  const int64_t total = (int64_t)g->n * g->ih * wp.ws;
+  stage_window_kernel<<<(unsigned)cdiv(total, 256), 256, 0, s>>>(view(x), xs, g->n, g->ci, g->ih, g->iw, wp.ws, g->pad);
+  int r = check_launch("conv_tc_stage_window");
+  if (r) return r;
+  TcArgs a{};
+  a.y = view(y); a.bias = bias;
+  a.M = g->n * g->oh * g->ow; a.N = g->co; a.oh = g->oh; a.ow = g->ow;
+  a.kh = g->ks; a.kw = 1; a.stride = g->stride; a.low_h = -g->pad; a.low_w = 0;
+  a.out_step = 1; a.out_y0 = 0; a.out_x0 = 0;
+  a.cblocks = wp.kb; a.cpad = wp.kb * BKF; a.flags = flags;
+  a.win_w = wp.win_w; a.win_h = wp.win_h; a.tiles_x = wp.tiles_x; a.tiles_y = wp.tiles_y;
+  SplitArgs sp{g->co, g->ci, g->ks, g->ks, 1, a.cpad, 0, 0, 0, 1, 1};
+  const int64_t wtotal = (int64_t)g->co * g->ks * a.cpad;
+  weight_split_kernel<<<(unsigned)cdiv(wtotal, 256), 256, 0, s>>>(w, wsplit, sp);
+  r = check_launch("conv_tc_weight_split");
+  if (r) return r;
+  const int bn = g->co <= 64 ? 64 : (g->co <= 128 ? 128 : 256);
+  switch (bn) {
+    case 64: return launch_window<64>(g, wp, xs, wsplit, a, s);
+    case 128: return launch_window<128>(g, wp, xs, wsplit, a, s);
+    default: return launch_window<256>(g, wp, xs, wsplit, a, s);
+  }
+}
+
 bool cl_ok(const OmtAct* a, int c, int h, int w) {
   return a && a->p && is_nhwc(a, c, h, w) && c % 4 == 0 && (reinterpret_cast<uintptr_t>(a->p) & 15) == 0;
 }
@@ -753,13 +911,19 @@ int tc_error_word() {
 // kind 0: a = x, b = y.  kind 1: a = gy, b = dx.  kind 2: weight gradient (not on this path yet)
 bool tc_supported(int kind, const OmtConvGeo* g, const OmtAct* a, const OmtAct* b) {
   if (!b || !b->p) return false;
-  if (kind == 0) return cl_ok(a, g->ci, g->ih, g->iw) && g->ci >= 8 && g->co >= 8 && g->pad < g->ks;
+  if (kind == 0) return (cl_ok(a, g->ci, g->ih, g->iw) && g->ci >= 8 && g->co >= 8 && g->pad < g->ks) || (a && a->p && window_ok(g));
   if (kind == 1) return cl_ok(a, g->co, g->oh, g->ow) && g->co >= 8 && g->ci >= 8 && g->pad < g->ks;
   // kind 2: a = x, b = gy
   return cl_ok(a, g->ci, g->ih, g->iw) && cl_ok(b, g->co, g->oh, g->ow) && g->ci >= 8 && g->co >= 8 && g->pad < g->ks;
 }
 size_t tc_workspace(int kind, const OmtConvGeo* g) {
-  if (kind == 0) return split_floats(g->co, g->ks, g->ci) * sizeof(float) + 256;
+  if (kind == 0) {
+    if (g->ci <= 4 && window_ok(g)) {
+      WinPlan w = plan_window(g);
+      return (((w.stage_floats + 63) / 64) * 64 + w.split_floats_) * sizeof(float) + 256;
+    }
+    return split_floats(g->co, g->ks, g->ci) * sizeof(float) + 256;
+  }
   if (kind == 1) return split_floats(g->ci, g->ks, g->co) * sizeof(float) + 256;
   return plan_wgrad(g).part_floats * sizeof(float) + 256;
 }
@@ -772,6 +936,7 @@ int tc_conv_fwd(const OmtConvGeo* g, const OmtAct* x, const float* w, const floa
     set_error("the CUDA driver does not export cuTensorMapEncodeTiled/Im2col");
     return OMT_ECUDA;
   }
+  if (g->ci <= 4) return run_window_fwd(g, x, w, bias, y, flags, ws, s);
   TcProblem p{x->p, g->n, g->ci, g->ih, g->iw, g->oh, g->ow, g->co, g->ks, g->ks, g->stride, -g->pad, -g->pad, 1, 0, 0};
   SplitArgs sp{g->co, g->ci, g->ks, 0, 0, 0, 0, 0, 0, 1};
   return run_tc(p, w, sp, (float*)ws, y, bias, flags, s);

@@ -69,6 +69,51 @@ def test_conv_default_path_matches_golden(capi, golden):
             assert rel_err(host(capi.conv_wgrad(xd, gd, ks, s, p)), golden[f"{name}_dw"]) <= TOL
 
 
+TC_SHAPES = [(2, 32, 64, 16, 1, 1, 0), (2, 64, 128, 16, 3, 1, 1), (4, 64, 200, 15, 3, 1, 1), (3, 24, 40, 17, 5, 1, 2), (2, 64, 64, 16, 3, 2, 1),
+             (2, 128, 256, 14, 1, 2, 0), (8, 256, 512, 14, 3, 1, 1), (2, 16, 32, 20, 7, 2, 3), (1, 8, 8, 9, 3, 1, 0), (2, 32, 32, 19, 3, 3, 1),
+             (2, 32, 48, 16, 1, 4, 0), (2, 16, 16, 21, 5, 2, 0), (1, 520, 264, 9, 3, 1, 1)]
+
+
+@pytest.mark.parametrize("shape", TC_SHAPES)
+def test_tensor_core_path_vs_aten_and_exact_path(capi, shape):
+    """tcgen05 3xTF32 kernels (OMT_FORCE_TC: fails instead of silently taking the CUDA-core path) on channels-last inputs:
+    forward with bias+ReLU into both layouts, input gradient for every stride (stride phases), weight gradient with
+    scale; against float64 aten on the CPU and against the exact-fp32 kernels. Shapes cover 1-4 stride, channel counts
+    that are not multiples of 32 / 64 / 128, ragged pixel tails, >256 output channels and k-blocks beyond one stage ring."""
+    n, ci, co, hw, ks, s, p = shape
+    torch.manual_seed(0)
+    x = torch.randn(n, ci, hw, hw)
+    w = torch.randn(co, ci, ks, ks) * 0.05
+    b = torch.randn(co)
+    oh = (hw + 2 * p - ks) // s + 1
+    gy = torch.randn(n, co, oh, oh)
+    y, dx, dw, _ = oracle.aten_conv(x.double(), w.double(), b.double(), s, p, gy.double())
+    y, dx, dw = y.relu().float().numpy(), dx.float().numpy(), dw.float().numpy()
+    xd, wd, bd, gd = dev(x, True), dev(w), dev(b), dev(gy, True)
+    before = capi.kernel_counts()
+    for cl in (True, False):
+        got = capi.conv_fwd(xd, wd, bd, s, p, flags=capi.FORCE_TC | capi.EPI_RELU, cl=cl)
+        assert rel_err(host(got), y) <= TOL
+    got_dx = capi.conv_dgrad(gd, wd, (hw, hw), s, p, flags=capi.FORCE_TC, cl=True)
+    assert rel_err(host(got_dx), dx) <= TOL
+    got_dw = capi.conv_wgrad(xd, gd, ks, s, p, flags=capi.FORCE_TC, scale=0.5)
+    assert rel_err(2 * host(got_dw), dw) <= TOL
+    capi.call("omt_sync")  # a tensor-core kernel that gave up on a barrier would be reported here
+    after = capi.kernel_counts()
+    assert sum(v - before.get(k, 0) for k, v in after.items() if k.startswith(("conv_tc_1", "wgrad_tc_1"))) >= 4
+    # the two paths agree with each other far inside the tolerance
+    exact = capi.conv_fwd(xd, wd, bd, s, p, flags=capi.FORCE_SIMT | capi.EPI_RELU, cl=True)
+    assert rel_err(host(capi.conv_fwd(xd, wd, bd, s, p, flags=capi.FORCE_TC | capi.EPI_RELU, cl=True)), host(exact)) <= 5e-5
+
+
+def test_tensor_core_path_refuses_what_it_cannot_take(capi):
+    x = torch.randn(2, 3, 16, 16, device="cuda")            # 3 channels, NCHW: not a TMA-loadable operand
+    w = torch.randn(8, 3, 3, 3, device="cuda")
+    with pytest.raises(capi.OmtError, match="tensor-core"):
+        capi.conv_fwd(x, w, None, 1, 1, flags=capi.FORCE_TC)
+    assert rel_err(host(capi.conv_fwd(x, w, None, 1, 1)), torch.nn.functional.conv2d(x.cpu(), w.cpu(), padding=1).numpy()) <= TOL
+
+
 def test_conv_epilogues_and_scale(capi):
     rng = np.random.default_rng(11)
     x = rng.standard_normal((2, 5, 10, 9)).astype(np.float32)
