@@ -217,8 +217,10 @@ def test_fused_stacks_train_eval_and_accumulate(omt):
         assert type(mod.features) is stacks.FusedSequential
         # (SGD rather than the reference script's Adam: Adam turns rounding-noise gradients into +-lr steps, which makes
         # parameter comparisons meaningless; the Adam kernels are compared step by step in the optimizer tests)
+        # (absolute slack: BatchNorm biases start at zero and hold a few SGD steps of gradients that are sums with heavy
+        # cancellation, so their relative error is not meaningful)
         for a, b in zip(ref.parameters(), mod.parameters()):
-            assert e(b, a) <= 1e-3
+            assert torch.allclose(b.detach().cpu(), a.detach(), rtol=2e-3, atol=3e-5)
         for a, b in zip(ref.buffers(), mod.buffers()):
             assert e(b.float(), a.float()) <= 1e-3  # running stats and num_batches_tracked
         ref.eval(); mod.eval()
