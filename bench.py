@@ -282,7 +282,9 @@ def dist_setup(n):
     import torch.distributed as dist
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
-    dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
+    import datetime
+    dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()),
+                            timeout=datetime.timedelta(seconds=180))  # a lost rank ends the job in minutes, not the default 10
     return rank, world
 
 
@@ -387,14 +389,18 @@ def main():
     launches = (capi.lib().omt_launch_count() - l0) // (args.steps + args.warmup)
     ms_e2e = time_steps(wl.e2e_step, args.steps, args.warmup, world, flush)
     clocks = sampler.stop() if rank == 0 else None
+    roof = wl.roofline(ms, peaks)  # runs extra steps: every rank takes part (they contain the gradient all-reduce)
+    barrier(world)
     if rank != 0:
+        if world > 1:
+            torch.distributed.destroy_process_group()
         return
     agg = world if wl.higher else 1  # throughput metrics aggregate over ranks; a step time does not
     line = {"metric": wl.metric, "value": wl.value(ms) * agg, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": wl.higher, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
             "config": {"workload": wl.name, **wl.shape, "l2": "flushed between timed iterations" if flush else "working set > L2"},
-            "roofline": wl.roofline(ms, peaks),
+            "roofline": roof,
             "e2e": {"value": wl.value(ms_e2e) * agg, "unit": wl.unit, "ms_per_step": ms_e2e, "h2d_bytes_per_step": wl.h2d_bytes,
                     "d2h_bytes_per_step": wl.d2h_bytes},
             "gpu_launches": int(launches) * args.steps, "clocks": clocks}
@@ -415,6 +421,8 @@ def main():
                                 "sample": f"{reps} steps of the same workload on PyTorch CPU aten (the reference's CPU arm), {cores} threads"
                                           + (f", batch {wl.cpu_batch} scaled x{wl.cpu_scale():g} to the full batch" if wl.cpu_scale() != 1 else "")}
     print(json.dumps(line))
+    if world > 1:
+        torch.distributed.destroy_process_group()
 
 
 if __name__ == "__main__":
