@@ -7,13 +7,14 @@
 // channel run starts on a 16-byte boundary (a TMA requirement). Weights are re-laid out per call into [2][co][ky][kx][c
 // padded to 32] (hi and lo planes, zero padded) by a small kernel; they are tiny next to the activations.
 //
-// One CTA computes a 128 x BN output tile. Warp roles (192 threads):
+// Persistent kernel: one CTA per SM walks 128 x BN output tiles. Warp roles (320 threads):
 //   warp 0       TMA producer: per k-block one im2col load of A (128 pixels x 32 channels of one filter tap) and two tiled
 //                loads of W (hi and lo planes), all completing on the stage's "loaded" mbarrier
 //   warp 1       allocates TMEM; one lane issues the MMAs: per 8-wide k-step three tcgen05.mma, then tcgen05.commit to
 //                free the stage; a final commit signals the epilogue
-//   warps 2..5   split A in place into hi (tf32-rounded) and lo, arrive on the stage's "split" mbarrier; afterwards they are
-//                the epilogue: tcgen05.ld of their 32-lane quarter of the accumulator, bias / ReLU, store in the output's layout
+//   warps 2..5   split A in place into hi (tf32-rounded) and lo, arrive on the stage's "split" mbarrier
+//   warps 6..9   epilogue: tcgen05.ld of their 32-lane quarter of the accumulators, bias / ReLU, store in the output's layout;
+//                for BN <= 128 TMEM holds two accumulator pairs, so the epilogue of tile i overlaps the main loop of tile i+1
 // Every mbarrier wait is bounded by a clock budget; on expiry the kernel raises an error word, all roles leave their loops,
 // TMEM is freed and the kernel returns (the host reports it as a failed launch at the next synchronisation).
 //
@@ -40,7 +41,7 @@ namespace {
 constexpr int BM = 128;        // output pixels per tile (UMMA M)
 constexpr int BKF = 32;        // floats per k-block (128 bytes)
 constexpr int UMMA_K = 8;      // tf32 MMA depth
-constexpr int TC_THREADS = 192;
+constexpr int TC_THREADS = 320;  // producer warp, MMA warp, 4 split warps, 4 epilogue warps
 constexpr long long WAIT_BUDGET_CLOCKS = 2000000000ll;  // ~1 s at B200 clocks
 
 __device__ int g_tc_error = 0;  // first failure: 1 = mbarrier wait expired
@@ -182,87 +183,110 @@ struct TcArgs {
 template <int BN>
 struct Smem {
   static constexpr int STAGES = BN == 256 ? 2 : (BN == 128 ? 3 : 4);
+  static constexpr int ACC_BUFS = BN == 256 ? 1 : 2;          // accumulator pairs in TMEM (512 columns in total at most)
+  static constexpr int TMEM_COLS = ACC_BUFS * 2 * BN;          // 256 or 512: a power of two
   static constexpr int A_BYTES = BM * 128, B_BYTES = BN * 128;
   static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
   static constexpr int BAR_OFF = STAGES * STAGE_BYTES;
+  static constexpr int NBARS = 3 * STAGES + 2 * ACC_BUFS;
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;  // barriers + alignment slack
 };
 
 // ---------------------------------------------------------------------------------------------------------------------
-// the kernel
+// the kernel: persistent, one CTA per SM walking output tiles t = blockIdx.x, blockIdx.x + gridDim.x, ...
 // ---------------------------------------------------------------------------------------------------------------------
+struct TileCoord {
+  int img0, oy0, ox0;  // first pixel of the tile (im2col mode: linear pixel run; window mode: top-left of the rectangle)
+  int m0, n0;
+};
+__device__ __forceinline__ TileCoord decode_tile(const TcArgs& g, int t, int n_tiles, int bn) {
+  TileCoord c;
+  const int mt = t / n_tiles;
+  c.n0 = (t - mt * n_tiles) * bn;
+  c.m0 = mt * BM;
+  if (g.win_w) {
+    const int per = g.tiles_x * g.tiles_y;
+    c.img0 = mt / per;
+    const int r = mt - c.img0 * per;
+    c.oy0 = (r / g.tiles_x) * g.win_h; c.ox0 = (r % g.tiles_x) * g.win_w;
+  } else {
+    const int ohw = g.oh * g.ow;
+    c.img0 = c.m0 / ohw;
+    const int r0 = c.m0 - c.img0 * ohw;
+    c.oy0 = r0 / g.ow; c.ox0 = r0 - c.oy0 * g.ow;
+  }
+  return c;
+}
+
 template <int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1)
-conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const TcArgs g) {
+conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const TcArgs g, const int m_tiles,
+               const int n_tiles) {
   using S = Smem<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const uint32_t smem_base = smem_u32(smem);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::BAR_OFF);
-  // barrier indices: [0,S) loaded, [S,2S) split, [2S,3S) free, 3S accumulator ready
+  // barrier indices: [0,S) loaded, [S,2S) split, [2S,3S) free, then ACC_BUFS x "accumulator full", ACC_BUFS x "accumulator drained"
   const uint32_t bar0 = smem_u32(bars);
   auto BAR = [&](int i) { return bar0 + 8u * i; };
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 3 * S::STAGES + 1);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 3 * S::STAGES + 2);
+  constexpr int ACC_FULL = 3 * S::STAGES, ACC_EMPTY = 3 * S::STAGES + S::ACC_BUFS;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + S::NBARS);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + S::NBARS + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
   const int kblocks = g.kh * g.kw * g.cblocks;
+  const int total_tiles = m_tiles * n_tiles;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S::STAGES; s++) {
       mbar_init(BAR(s), 1);                    // loaded: one arrive.expect_tx + TMA bytes
-      mbar_init(BAR(S::STAGES + s), 4);        // split: one arrival per transform warp
+      mbar_init(BAR(S::STAGES + s), 4);        // split: one arrival per split warp
       mbar_init(BAR(2 * S::STAGES + s), 1);    // free: tcgen05.commit
     }
-    mbar_init(BAR(3 * S::STAGES), 1);
+    for (int b = 0; b < S::ACC_BUFS; b++) {
+      mbar_init(BAR(ACC_FULL + b), 1);         // tcgen05.commit after the tile's last MMA
+      mbar_init(BAR(ACC_EMPTY + b), 4);        // one arrival per epilogue warp
+    }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) {  // TMEM: two accumulators of BN fp32 columns each (a power of two >= 32 in total)
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"((uint32_t)(2 * BN))
+  if (warp == 1) {  // TMEM: per buffer two accumulators of BN fp32 columns (main sum, cross terms)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)),
+                 "r"((uint32_t)S::TMEM_COLS)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const uint32_t tmem_acc = *tmem_slot;
+  const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
-      const int ohw = g.oh * g.ow;
-      int img0, oy0, ox0;
-      if (g.win_w) {  // blockIdx.x enumerates (image, tile row, tile column)
-        const int per = g.tiles_x * g.tiles_y;
-        img0 = blockIdx.x / per;
-        const int r = blockIdx.x - img0 * per;
-        oy0 = (r / g.tiles_x) * g.win_h; ox0 = (r % g.tiles_x) * g.win_w;
-      } else {
-        img0 = m0 / ohw;
-        const int r0 = m0 - img0 * ohw;
-        oy0 = r0 / g.ow; ox0 = r0 - oy0 * g.ow;
-      }
-      const int w0 = ox0 * g.stride + g.low_w, h0 = oy0 * g.stride + g.low_h;
-      int issued = 0;
-      for (int kb = 0; kb < kblocks; kb++) {
-        const int s = kb % S::STAGES, round = kb / S::STAGES;
-        if (round > 0 && !mbar_wait(BAR(2 * S::STAGES + s), (round - 1) & 1, abort_flag)) break;
-        const int tap = kb / g.cblocks, cb = kb - tap * g.cblocks;
-        const int ky = tap / g.kw, kx = tap - ky * g.kw;
-        const uint32_t stage = smem_base + s * S::STAGE_BYTES;
-        mbar_expect_tx(BAR(s), S::A_BYTES + 2 * S::B_BYTES);
-        if (g.win_w) tma_tile_4d(stage, &map_a, BAR(s), cb * BKF, ox0, h0 + ky, img0);  // kw == 1: tap = filter row
-        else tma_im2col_4d(stage, &map_a, BAR(s), cb * BKF, w0, h0, img0, (uint16_t)kx, (uint16_t)ky);
-        tma_tile_3d(stage + 2 * S::A_BYTES, &map_w, BAR(s), tap * g.cpad + cb * BKF, n0, 0);
-        tma_tile_3d(stage + 2 * S::A_BYTES + S::B_BYTES, &map_w, BAR(s), tap * g.cpad + cb * BKF, n0, 1);
-        issued = kb + 1;
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const TileCoord c = decode_tile(g, t, n_tiles, BN);
+        const int w0 = c.ox0 * g.stride + g.low_w, h0 = c.oy0 * g.stride + g.low_h;
+        for (int kb = 0; kb < kblocks; kb++, it++) {
+          const int s = it % S::STAGES, round = it / S::STAGES;
+          if (round > 0 && !mbar_wait(BAR(2 * S::STAGES + s), (round - 1) & 1, abort_flag)) { ok = false; break; }
+          const int tap = kb / g.cblocks, cb = kb - tap * g.cblocks;
+          const int ky = tap / g.kw, kx = tap - ky * g.kw;
+          const uint32_t stage = smem_base + s * S::STAGE_BYTES;
+          mbar_expect_tx(BAR(s), S::A_BYTES + 2 * S::B_BYTES);
+          if (g.win_w) tma_tile_4d(stage, &map_a, BAR(s), cb * BKF, c.ox0, h0 + ky, c.img0);  // kw == 1: tap = filter row
+          else tma_im2col_4d(stage, &map_a, BAR(s), cb * BKF, w0, h0, c.img0, (uint16_t)kx, (uint16_t)ky);
+          tma_tile_3d(stage + 2 * S::A_BYTES, &map_w, BAR(s), tap * g.cpad + cb * BKF, c.n0, 0);
+          tma_tile_3d(stage + 2 * S::A_BYTES + S::B_BYTES, &map_w, BAR(s), tap * g.cpad + cb * BKF, c.n0, 1);
+        }
       }
       if (*abort_flag) {  // drain: let the copies already in flight land before the CTA exits (bounded)
-        for (int kb = max(0, issued - S::STAGES); kb < issued; kb++) {
+        for (int k = max(0, it - S::STAGES); k < it; k++) {
           const long long t0 = clock64();
-          while (!mbar_try(BAR(kb % S::STAGES), (kb / S::STAGES) & 1) && clock64() - t0 < WAIT_BUDGET_CLOCKS) {}
+          while (!mbar_try(BAR(k % S::STAGES), (k / S::STAGES) & 1) && clock64() - t0 < WAIT_BUDGET_CLOCKS) {}
         }
       }
     }
@@ -270,90 +294,106 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       constexpr uint32_t idesc = idesc_tf32(BN);
+      int it = 0, tl = 0;
       bool ok = true;
-      for (int kb = 0; kb < kblocks && ok; kb++) {
-        const int s = kb % S::STAGES, round = kb / S::STAGES;
-        ok = mbar_wait(BAR(S::STAGES + s), round & 1, abort_flag) && mbar_wait(BAR(s), round & 1, abort_flag);
-        if (!ok) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t stage = smem_base + s * S::STAGE_BYTES;
-        const uint64_t a_hi = smem_desc_sw128(stage), a_lo = smem_desc_sw128(stage + S::A_BYTES);
-        const uint64_t b_hi = smem_desc_sw128(stage + 2 * S::A_BYTES), b_lo = smem_desc_sw128(stage + 2 * S::A_BYTES + S::B_BYTES);
-#pragma unroll
-        for (int k = 0; k < BKF / UMMA_K; k++) {
-          const uint64_t adv = (uint64_t)((k * UMMA_K * 4) >> 4);  // 32 bytes per k-step inside the swizzled row
-          // two accumulators: the cross terms (2^-11 of the result) go to columns [BN, 2BN) so that the truncation the
-          // tensor core applies on every accumulate hits the main sum once per k-step instead of three times
-          umma_tf32(tmem_acc + BN, a_lo + adv, b_hi + adv, idesc, (kb | k) ? 1u : 0u);
-          umma_tf32(tmem_acc + BN, a_hi + adv, b_lo + adv, idesc, 1u);
-          umma_tf32(tmem_acc, a_hi + adv, b_hi + adv, idesc, (kb | k) ? 1u : 0u);
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, tl++) {
+        const int b = tl % S::ACC_BUFS, use = tl / S::ACC_BUFS;
+        if (use > 0) {  // the epilogue must have drained this accumulator pair
+          ok = mbar_wait(BAR(ACC_EMPTY + b), (use - 1) & 1, abort_flag);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         }
-        umma_commit(BAR(2 * S::STAGES + s));  // stage is free once these MMAs have read it
+        const uint32_t acc = tmem_base + b * (2 * BN);
+        for (int kb = 0; kb < kblocks; kb++, it++) {
+          const int s = it % S::STAGES, round = it / S::STAGES;
+          ok = mbar_wait(BAR(S::STAGES + s), round & 1, abort_flag) && mbar_wait(BAR(s), round & 1, abort_flag);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t stage = smem_base + s * S::STAGE_BYTES;
+          const uint64_t a_hi = smem_desc_sw128(stage), a_lo = smem_desc_sw128(stage + S::A_BYTES);
+          const uint64_t b_hi = smem_desc_sw128(stage + 2 * S::A_BYTES), b_lo = smem_desc_sw128(stage + 2 * S::A_BYTES + S::B_BYTES);
+#pragma unroll
+          for (int k = 0; k < BKF / UMMA_K; k++) {
+            const uint64_t adv = (uint64_t)((k * UMMA_K * 4) >> 4);  // 32 bytes per k-step inside the swizzled row
+            // two accumulators: the cross terms (2^-11 of the result) go to columns [BN, 2BN) so that the truncation the
+            // tensor core applies on every accumulate hits the main sum once per k-step instead of three times
+            umma_tf32(acc + BN, a_lo + adv, b_hi + adv, idesc, (kb | k) ? 1u : 0u);
+            umma_tf32(acc + BN, a_hi + adv, b_lo + adv, idesc, 1u);
+            umma_tf32(acc, a_hi + adv, b_hi + adv, idesc, (kb | k) ? 1u : 0u);
+          }
+          umma_commit(BAR(2 * S::STAGES + s));  // stage is free once these MMAs have read it
+        }
+        if (ok) umma_commit(BAR(ACC_FULL + b));  // this tile's accumulators are complete
       }
-      if (ok) umma_commit(BAR(3 * S::STAGES));  // accumulator complete
+    }
+  } else if (warp < 6) {
+    // ---------------- operand split (warps 2..5) ----------------
+    const int t4 = threadIdx.x - 64;  // 0..127
+    int it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (int kb = 0; kb < kblocks; kb++, it++) {
+        const int s = it % S::STAGES, round = it / S::STAGES;
+        ok = mbar_wait(BAR(s), round & 1, abort_flag);
+        if (!ok) break;
+        uint4* hi = reinterpret_cast<uint4*>(smem + s * S::STAGE_BYTES);
+        uint4* lo = reinterpret_cast<uint4*>(smem + s * S::STAGE_BYTES + S::A_BYTES);
+#pragma unroll
+        for (int i = 0; i < S::A_BYTES / 16 / 128; i++) {
+          const int idx = i * 128 + t4;
+          uint4 v = hi[idx], h, l;
+          float f0 = __uint_as_float(v.x), f1 = __uint_as_float(v.y), f2 = __uint_as_float(v.z), f3 = __uint_as_float(v.w);
+          float h0 = tf32_rna(f0), h1 = tf32_rna(f1), h2 = tf32_rna(f2), h3 = tf32_rna(f3);
+          h.x = __float_as_uint(h0); h.y = __float_as_uint(h1); h.z = __float_as_uint(h2); h.w = __float_as_uint(h3);
+          l.x = __float_as_uint(tf32_rna(f0 - h0)); l.y = __float_as_uint(tf32_rna(f1 - h1));
+          l.z = __float_as_uint(tf32_rna(f2 - h2)); l.w = __float_as_uint(tf32_rna(f3 - h3));
+          hi[idx] = h;
+          lo[idx] = l;
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the tensor core
+        __syncwarp();
+        if (lane == 0) mbar_arrive(BAR(S::STAGES + s));
+      }
     }
   } else {
-    // ---------------- operand split (warps 2..5), then epilogue ----------------
-    const int t = threadIdx.x - 64;  // 0..127
+    // ---------------- epilogue (warps 6..9): overlaps the next tile's main loop when ACC_BUFS == 2 ----------------
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    int tl = 0;
     bool ok = true;
-    for (int kb = 0; kb < kblocks && ok; kb++) {
-      const int s = kb % S::STAGES, round = kb / S::STAGES;
-      ok = mbar_wait(BAR(s), round & 1, abort_flag);
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, tl++) {
+      const int b = tl % S::ACC_BUFS, use = tl / S::ACC_BUFS;
+      ok = mbar_wait(BAR(ACC_FULL + b), use & 1, abort_flag);
       if (!ok) break;
-      uint4* hi = reinterpret_cast<uint4*>(smem + s * S::STAGE_BYTES);
-      uint4* lo = reinterpret_cast<uint4*>(smem + s * S::STAGE_BYTES + S::A_BYTES);
-#pragma unroll
-      for (int i = 0; i < S::A_BYTES / 16 / 128; i++) {
-        const int idx = i * 128 + t;
-        uint4 v = hi[idx], h, l;
-        float f0 = __uint_as_float(v.x), f1 = __uint_as_float(v.y), f2 = __uint_as_float(v.z), f3 = __uint_as_float(v.w);
-        float h0 = tf32_rna(f0), h1 = tf32_rna(f1), h2 = tf32_rna(f2), h3 = tf32_rna(f3);
-        h.x = __float_as_uint(h0); h.y = __float_as_uint(h1); h.z = __float_as_uint(h2); h.w = __float_as_uint(h3);
-        l.x = __float_as_uint(tf32_rna(f0 - h0)); l.y = __float_as_uint(tf32_rna(f1 - h1));
-        l.z = __float_as_uint(tf32_rna(f2 - h2)); l.w = __float_as_uint(tf32_rna(f3 - h3));
-        hi[idx] = h;
-        lo[idx] = l;
-      }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the tensor core
-      __syncwarp();
-      if (lane == 0) mbar_arrive(BAR(S::STAGES + s));
-    }
-    // epilogue
-    if (ok) ok = mbar_wait(BAR(3 * S::STAGES), 0, abort_flag);
-    if (ok) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int q = warp & 3;  // TMEM lane quarter this warp may read
-      int m = m0 + q * 32 + lane;
-      const int ohw = g.oh * g.ow;
+      const TileCoord c = decode_tile(g, t, n_tiles, BN);
+      const uint32_t acc = tmem_base + b * (2 * BN) + ((uint32_t)(q * 32) << 16);
+      const int r = q * 32 + lane;
       int img, oy, ox;
+      bool valid;
       if (g.win_w) {
-        const int per = g.tiles_x * g.tiles_y, r = q * 32 + lane;
-        img = blockIdx.x / per;
-        const int t = blockIdx.x - img * per;
-        oy = (t / g.tiles_x) * g.win_h + r / g.win_w; ox = (t % g.tiles_x) * g.win_w + r % g.win_w;
-        m = (oy < g.oh && ox < g.ow) ? 0 : g.M;  // rows outside the image are not stored
-        if (m) { oy = 0; ox = 0; }
+        img = c.img0; oy = c.oy0 + r / g.win_w; ox = c.ox0 + r % g.win_w;
+        valid = oy < g.oh && ox < g.ow;
       } else {
+        const int m = c.m0 + r, ohw = g.oh * g.ow;
+        valid = m < g.M;
         img = m / ohw;
-        const int r = m - img * ohw;
-        oy = r / g.ow; ox = r - oy * g.ow;
+        const int rr = m - img * ohw;
+        oy = rr / g.ow; ox = rr - oy * g.ow;
       }
+      if (!valid) { img = 0; oy = 0; ox = 0; }
       float* yrow = g.y.p + g.y.off(img, 0, oy * g.out_step + g.out_y0, ox * g.out_step + g.out_x0);
       const bool vec = g.y.sc == 1 && ((reinterpret_cast<uintptr_t>(yrow) & 15) == 0);
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; c++) {
+      for (int ch = 0; ch < BN / 32; ch++) {
         uint32_t v[32], u[32];
-        tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + c * 32, v);
-        tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + BN + c * 32, u);
-#pragma unroll
-        for (int j = 0; j < 32; j++) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(u[j]));
-        if (m >= g.M) continue;
-        const int nb = n0 + c * 32;
-        if (nb >= g.N) continue;
+        tmem_ld32(acc + ch * 32, v);
+        tmem_ld32(acc + BN + ch * 32, u);
+        const int nb = c.n0 + ch * 32;
+        if (!valid || nb >= g.N) continue;
         float o[32];
 #pragma unroll
         for (int j = 0; j < 32; j++) {
-          float x = __uint_as_float(v[j]);
+          float x = __uint_as_float(v[j]) + __uint_as_float(u[j]);
           if ((g.flags & OMT_EPI_BIAS) && nb + j < g.N) x += __ldg(g.bias + nb + j);
           if (g.flags & OMT_EPI_RELU) x = fmaxf(x, 0.f);
           o[j] = x;
@@ -367,13 +407,17 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (nb + j < g.N) yrow[(int64_t)(nb + j) * g.y.sc] = o[j];
         }
       }
+      // hand the accumulator pair back to the MMA warp
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(BAR(ACC_EMPTY + b));
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"((uint32_t)(2 * BN)) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)S::TMEM_COLS) : "memory");
   }
 }
 
@@ -490,8 +534,9 @@ int launch_tc(const TcProblem& p, const float* wsplit, const TcArgs& args, cudaS
     OMT_CUDA(cudaFuncSetAttribute(conv_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
     attr_set = true;
   }
-  dim3 grid((unsigned)cdiv(args.M, BM), (unsigned)cdiv(args.N, BN));
-  conv_tc_kernel<BN><<<grid, TC_THREADS, S::TOTAL, s>>>(map_a, map_w, args);
+  const int m_tiles = (int)cdiv(args.M, BM), n_tiles = (int)cdiv(args.N, BN);
+  const unsigned grid = (unsigned)std::min<int64_t>((int64_t)m_tiles * n_tiles, sm_count());
+  conv_tc_kernel<BN><<<grid, TC_THREADS, S::TOTAL, s>>>(map_a, map_w, args, m_tiles, n_tiles);
   return check_launch(BN == 64 ? "conv_tc_128x64" : (BN == 128 ? "conv_tc_128x128" : "conv_tc_128x256"));
 }
 
@@ -863,8 +908,9 @@ int launch_window(const OmtConvGeo* g, const WinPlan& w, const float* xs, const 
     OMT_CUDA(cudaFuncSetAttribute(conv_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
     attr_set = true;
   }
-  dim3 grid((unsigned)(g->n * w.tiles_x * w.tiles_y), (unsigned)cdiv(args.N, BN));
-  conv_tc_kernel<BN><<<grid, TC_THREADS, S::TOTAL, s>>>(map_a, map_w, args);
+  const int m_tiles = g->n * w.tiles_x * w.tiles_y, n_tiles = (int)cdiv(args.N, BN);
+  const unsigned grid = (unsigned)std::min<int64_t>((int64_t)m_tiles * n_tiles, sm_count());
+  conv_tc_kernel<BN><<<grid, TC_THREADS, S::TOTAL, s>>>(map_a, map_w, args, m_tiles, n_tiles);
   return check_launch(BN == 64 ? "conv_tc_window_128x64" : (BN == 128 ? "conv_tc_window_128x128" : "conv_tc_window_128x256"));
 }
 
