@@ -41,7 +41,7 @@ namespace {
 constexpr int BM = 128;        // output pixels per tile (UMMA M)
 constexpr int BKF = 32;        // floats per k-block (128 bytes)
 constexpr int UMMA_K = 8;      // tf32 MMA depth
-constexpr int TC_THREADS = 320;  // producer warp, MMA warp, 4 split warps, 4 epilogue warps
+constexpr int TC_THREADS = 448;  // producer warp, MMA warp, 4 split warps, 8 epilogue warps
 constexpr long long WAIT_BUDGET_CLOCKS = 2000000000ll;  // ~1 s at B200 clocks
 
 __device__ int g_tc_error = 0;  // first failure: 1 = mbarrier wait expired
@@ -110,21 +110,40 @@ __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t desc_a, uint
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+// two 32-column loads (same lanes, two column ranges) and the wait, as one statement so that no use of the registers can be
+// scheduled before the wait
+__device__ __forceinline__ void tmem_ld32x2(uint32_t ta, uint32_t tb, uint32_t (&a)[32], uint32_t (&b)[32]) {
   asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, "
-      "%20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
-        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%64];\n\t"
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%65];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]), "=r"(a[4]), "=r"(a[5]), "=r"(a[6]), "=r"(a[7]), "=r"(a[8]), "=r"(a[9]), "=r"(a[10]), "=r"(a[11]), "=r"(a[12]), "=r"(a[13]), "=r"(a[14]), "=r"(a[15]), "=r"(a[16]), "=r"(a[17]), "=r"(a[18]), "=r"(a[19]), "=r"(a[20]), "=r"(a[21]), "=r"(a[22]), "=r"(a[23]), "=r"(a[24]), "=r"(a[25]), "=r"(a[26]), "=r"(a[27]), "=r"(a[28]), "=r"(a[29]), "=r"(a[30]), "=r"(a[31]),
+        "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3]), "=r"(b[4]), "=r"(b[5]), "=r"(b[6]), "=r"(b[7]), "=r"(b[8]), "=r"(b[9]), "=r"(b[10]), "=r"(b[11]), "=r"(b[12]), "=r"(b[13]), "=r"(b[14]), "=r"(b[15]), "=r"(b[16]), "=r"(b[17]), "=r"(b[18]), "=r"(b[19]), "=r"(b[20]), "=r"(b[21]), "=r"(b[22]), "=r"(b[23]), "=r"(b[24]), "=r"(b[25]), "=r"(b[26]), "=r"(b[27]), "=r"(b[28]), "=r"(b[29]), "=r"(b[30]), "=r"(b[31])
+      : "r"(ta), "r"(tb)
+      : "memory");
 }
 __device__ __forceinline__ float tf32_rna(float x) {
   uint32_t u;
   asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
   return __uint_as_float(u);
+}
+// 3xTF32 operand split. The tensor core reads a tf32 operand as the top 19 bits of the fp32 word in shared memory (the low
+// 13 mantissa bits are ignored), so the buffer TMA wrote already is the "hi" operand: hi = x with those bits cleared. Only
+// lo = x - hi (exact in fp32, then rounded to tf32) has to be produced, which saves one of the two shared-memory stores.
+#ifndef OMT_TC_IMPLICIT_HI
+#define OMT_TC_IMPLICIT_HI 1
+#endif
+__device__ __forceinline__ uint4 split_lo(uint4 v, uint4& h) {
+  float f0 = __uint_as_float(v.x), f1 = __uint_as_float(v.y), f2 = __uint_as_float(v.z), f3 = __uint_as_float(v.w);
+#if OMT_TC_IMPLICIT_HI
+  h.x = v.x & 0xffffe000u; h.y = v.y & 0xffffe000u; h.z = v.z & 0xffffe000u; h.w = v.w & 0xffffe000u;
+#else
+  h.x = __float_as_uint(tf32_rna(f0)); h.y = __float_as_uint(tf32_rna(f1)); h.z = __float_as_uint(tf32_rna(f2)); h.w = __float_as_uint(tf32_rna(f3));
+#endif
+  uint4 l;
+  l.x = __float_as_uint(tf32_rna(f0 - __uint_as_float(h.x))); l.y = __float_as_uint(tf32_rna(f1 - __uint_as_float(h.y)));
+  l.z = __float_as_uint(tf32_rna(f2 - __uint_as_float(h.z))); l.w = __float_as_uint(tf32_rna(f3 - __uint_as_float(h.w)));
+  return l;
 }
 
 // K-major operand tile with 128-byte rows and the 128B swizzle: 8-row atoms of 1024 bytes.
@@ -161,6 +180,15 @@ __device__ __forceinline__ void tma_tile_2d(uint32_t dst, const CUtensorMap* map
                : "memory");
 }
 
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int x, int y, int z, int w) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(map), "r"(src), "r"(x), "r"(y), "r"(z),
+               "r"(w)
+               : "memory");
+}
+
 struct TcArgs {
   ActView y;          // output activation (any strides)
   const float* bias;
@@ -173,6 +201,7 @@ struct TcArgs {
   int cblocks;        // 32-channel blocks per tap
   int cpad;           // cblocks * 32
   uint32_t flags;
+  int store_mode;     // 0: plain stores (any strides); 1: TMA stores of 32-row boxes of the [M, N] matrix; 2: of window rectangles
   // "window" mode (few input channels): the A operand comes from a zero-padded [n][h][w][4] copy of the input through a
   // tiled tensor map whose pixel dimension overlaps (stride = conv stride * 16 bytes), so one 32-float row holds 8
   // consecutive input pixels x 4 channels = the (kx, c) run of a filter row. GEMM rows are win_w x win_h pixel rectangles.
@@ -187,7 +216,9 @@ struct Smem {
   static constexpr int TMEM_COLS = ACC_BUFS * 2 * BN;          // 256 or 512: a power of two
   static constexpr int A_BYTES = BM * 128, B_BYTES = BN * 128;
   static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
-  static constexpr int BAR_OFF = STAGES * STAGE_BYTES;
+  static constexpr int EPI_OFF = STAGES * STAGE_BYTES;          // per epilogue warp one 32-row x 128-byte store buffer
+  static constexpr int EPI_BYTES = 8 * 4096;
+  static constexpr int BAR_OFF = EPI_OFF + EPI_BYTES;
   static constexpr int NBARS = 3 * STAGES + 2 * ACC_BUFS;
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;  // barriers + alignment slack
 };
@@ -220,8 +251,8 @@ __device__ __forceinline__ TileCoord decode_tile(const TcArgs& g, int t, int n_t
 
 template <int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1)
-conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const TcArgs g, const int m_tiles,
-               const int n_tiles) {
+conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_y,
+               const TcArgs g, const int m_tiles, const int n_tiles) {
   using S = Smem<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -246,7 +277,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
     for (int b = 0; b < S::ACC_BUFS; b++) {
       mbar_init(BAR(ACC_FULL + b), 1);         // tcgen05.commit after the tile's last MMA
-      mbar_init(BAR(ACC_EMPTY + b), 4);        // one arrival per epilogue warp
+      mbar_init(BAR(ACC_EMPTY + b), 8);        // one arrival per epilogue warp
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -341,13 +372,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
         for (int i = 0; i < S::A_BYTES / 16 / 128; i++) {
           const int idx = i * 128 + t4;
-          uint4 v = hi[idx], h, l;
-          float f0 = __uint_as_float(v.x), f1 = __uint_as_float(v.y), f2 = __uint_as_float(v.z), f3 = __uint_as_float(v.w);
-          float h0 = tf32_rna(f0), h1 = tf32_rna(f1), h2 = tf32_rna(f2), h3 = tf32_rna(f3);
-          h.x = __float_as_uint(h0); h.y = __float_as_uint(h1); h.z = __float_as_uint(h2); h.w = __float_as_uint(h3);
-          l.x = __float_as_uint(tf32_rna(f0 - h0)); l.y = __float_as_uint(tf32_rna(f1 - h1));
-          l.z = __float_as_uint(tf32_rna(f2 - h2)); l.w = __float_as_uint(tf32_rna(f3 - h3));
+          uint4 h;
+          const uint4 l = split_lo(hi[idx], h);
+#if !OMT_TC_IMPLICIT_HI
           hi[idx] = h;
+#endif
           lo[idx] = l;
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the tensor core
@@ -356,8 +385,14 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
     }
   } else {
-    // ---------------- epilogue (warps 6..9): overlaps the next tile's main loop when ACC_BUFS == 2 ----------------
-    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    // ---------------- epilogue (warps 6..13): overlaps the next tile's main loop when ACC_BUFS == 2 ----------------
+    // Two warps per TMEM lane quarter; each takes every other 32-column chunk.
+    const int q = warp & 3;           // TMEM lane quarter this warp may read
+    const int half = (warp - 6) >> 2;
+    // Dense channels-last outputs leave through shared memory: the warp lays its 32 rows x 32 channels out with the 128-byte
+    // swizzle (conflict-free 16-byte stores) and one lane issues a TMA store of the box, which clips rows and channels that
+    // fall outside the tensor.
+    uint8_t* buf = smem + S::EPI_OFF + (warp - 6) * 4096;
     int tl = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, tl++) {
@@ -384,12 +419,12 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       float* yrow = g.y.p + g.y.off(img, 0, oy * g.out_step + g.out_y0, ox * g.out_step + g.out_x0);
       const bool vec = g.y.sc == 1 && ((reinterpret_cast<uintptr_t>(yrow) & 15) == 0);
 #pragma unroll 1
-      for (int ch = 0; ch < BN / 32; ch++) {
+      for (int ch = half; ch < BN / 32; ch += 2) {
         uint32_t v[32], u[32];
-        tmem_ld32(acc + ch * 32, v);
-        tmem_ld32(acc + BN + ch * 32, u);
+        tmem_ld32x2(acc + ch * 32, acc + BN + ch * 32, v, u);
         const int nb = c.n0 + ch * 32;
-        if (!valid || nb >= g.N) continue;
+        if (nb >= g.N) continue;
+        if (!g.store_mode && !valid) continue;
         float o[32];
 #pragma unroll
         for (int j = 0; j < 32; j++) {
@@ -398,7 +433,24 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           if (g.flags & OMT_EPI_RELU) x = fmaxf(x, 0.f);
           o[j] = x;
         }
-        if (vec && nb + 32 <= g.N) {
+        if (g.store_mode) {
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // the previous box has left the buffer
+          __syncwarp();
+          float4* row = reinterpret_cast<float4*>(buf + lane * 128);
+#pragma unroll
+          for (int j = 0; j < 8; j++) row[j ^ (lane & 7)] = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) {
+            if (g.store_mode == 1) {
+              tma_store_2d(&map_y, smem_u32(buf), nb, c.m0 + q * 32);
+            } else {
+              const int r0 = q * 32;
+              tma_store_4d(&map_y, smem_u32(buf), nb, c.ox0 + r0 % g.win_w, c.oy0 + r0 / g.win_w, c.img0);
+            }
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+        } else if (vec && nb + 32 <= g.N) {
 #pragma unroll
           for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(yrow + nb + j) = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
         } else {
@@ -412,6 +464,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       __syncwarp();
       if (lane == 0) mbar_arrive(BAR(ACC_EMPTY + b));
     }
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // every box this warp stored has been written
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -494,8 +547,18 @@ struct TcProblem {  // a convolution of a channels-last activation `a` [n, ih, i
 int pick_bn(const TcProblem& p) {
   if (p.rows <= 64) return 64;
   if (p.rows <= 128) return 128;
+  // a short reduction leaves the 128x256 tile's epilogue exposed (its accumulators fill TMEM, so nothing overlaps it);
+  // 128x128 tiles double-buffer the accumulators and hide it
+  if (p.kh * p.kw * (int)cdiv(p.c, BKF) < 6) return 128;
   int64_t mt = cdiv((int64_t)p.n * p.oh * p.ow, BM);
   return (mt * cdiv(p.rows, 256) >= sm_count()) ? 256 : 128;
+}
+
+// dense channels-last output written pixel for pixel (no phase stride), 16-byte aligned rows
+bool dense_out(const TcArgs& a) {
+  const ActView& y = a.y;
+  return a.out_step == 1 && a.out_y0 == 0 && a.out_x0 == 0 && y.sc == 1 && y.sw == a.N && y.sh == (int64_t)a.ow * a.N &&
+         y.sn == (int64_t)a.oh * a.ow * a.N && a.N % 4 == 0 && (reinterpret_cast<uintptr_t>(y.p) & 15) == 0;
 }
 
 template <int BN>
@@ -534,9 +597,19 @@ int launch_tc(const TcProblem& p, const float* wsplit, const TcArgs& args, cudaS
     OMT_CUDA(cudaFuncSetAttribute(conv_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
     attr_set = true;
   }
-  const int m_tiles = (int)cdiv(args.M, BM), n_tiles = (int)cdiv(args.N, BN);
+  TcArgs a = args;
+  alignas(64) CUtensorMap map_y = map_w;  // placeholder when the epilogue stores directly
+  if (dense_out(a)) {  // the output is the row-major [M, N] matrix: 32 x 32 boxes leave through TMA
+    cuuint64_t dims[2] = {(cuuint64_t)a.N, (cuuint64_t)a.M};
+    cuuint64_t strides[1] = {(cuuint64_t)a.N * 4};
+    cuuint32_t box[2] = {32, 32}, estr[2] = {1, 1};
+    if (g_encode_tiled(&map_y, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)a.y.p, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                       CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS)
+      a.store_mode = 1;
+  }
+  const int m_tiles = (int)cdiv(a.M, BM), n_tiles = (int)cdiv(a.N, BN);
   const unsigned grid = (unsigned)std::min<int64_t>((int64_t)m_tiles * n_tiles, sm_count());
-  conv_tc_kernel<BN><<<grid, TC_THREADS, S::TOTAL, s>>>(map_a, map_w, args, m_tiles, n_tiles);
+  conv_tc_kernel<BN><<<grid, TC_THREADS, S::TOTAL, s>>>(map_a, map_w, map_y, a, m_tiles, n_tiles);
   return check_launch(BN == 64 ? "conv_tc_128x64" : (BN == 128 ? "conv_tc_128x128" : "conv_tc_128x256"));
 }
 
@@ -570,6 +643,7 @@ constexpr int PB = 32;            // pixels (reduction depth) per stage
 constexpr int WG_THREADS = 320;   // producer warp, MMA warp, 8 split/epilogue warps
 
 struct WgArgs {
+  int mode;          // bit 0: gy tile by one 3-D TMA box; bit 1: x is the plain [pixels, ci] matrix (1x1, stride 1), one 3-D box
   float* part;       // [slices][co][kcols] partial tiles
   int P;             // pixels = n * oh * ow
   int co;
@@ -642,13 +716,21 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         const int img = p0 / ohw, r = p0 - img * ohw, oy = r / g.ow, ox = r - oy * g.ow;
         const int w0 = ox * g.stride - g.pad, h0 = oy * g.stride - g.pad;
         const uint32_t stage = smem_base + s * S::STAGE_BYTES;
-        mbar_expect_tx(BAR(s), S::A_BYTES + nchunks * S::CH);
+        mbar_expect_tx(BAR(s), S::A_BYTES + ((g.mode & 2) ? S::B_BYTES : nchunks * S::CH));
+        if (g.mode & 1) {
+          tma_tile_3d(stage, &map_g, BAR(s), 0, p0, co0 / 32);
+        } else {
 #pragma unroll
-        for (int i = 0; i < 4; i++) tma_tile_2d(stage + i * S::CH, &map_g, BAR(s), co0 + 32 * i, p0);
-        for (int j = 0; j < nchunks; j++) {
-          const int chunk = chunk0 + j, tap = chunk / g.cblocks, cb = chunk - tap * g.cblocks;
-          const int ky = tap / g.ks, kx = tap - ky * g.ks;
-          tma_im2col_4d(stage + S::A_BYTES + j * S::CH, &map_x, BAR(s), cb * BKF, w0, h0, img, (uint16_t)kx, (uint16_t)ky);
+          for (int i = 0; i < 4; i++) tma_tile_2d(stage + i * S::CH, &map_g, BAR(s), co0 + 32 * i, p0);
+        }
+        if (g.mode & 2) {
+          tma_tile_3d(stage + S::A_BYTES, &map_x, BAR(s), 0, p0, chunk0);
+        } else {
+          for (int j = 0; j < nchunks; j++) {
+            const int chunk = chunk0 + j, tap = chunk / g.cblocks, cb = chunk - tap * g.cblocks;
+            const int ky = tap / g.ks, kx = tap - ky * g.ks;
+            tma_im2col_4d(stage + S::A_BYTES + j * S::CH, &map_x, BAR(s), cb * BKF, w0, h0, img, (uint16_t)kx, (uint16_t)ky);
+          }
         }
         issued = kb + 1;
       }
@@ -694,13 +776,11 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
       uint4* hi = reinterpret_cast<uint4*>(smem + s * S::STAGE_BYTES);
       uint4* lo = reinterpret_cast<uint4*>(smem + s * S::STAGE_BYTES + S::HALF);
       for (int idx = t; idx < n16; idx += 256) {
-        uint4 v = hi[idx], h, l;
-        float f0 = __uint_as_float(v.x), f1 = __uint_as_float(v.y), f2 = __uint_as_float(v.z), f3 = __uint_as_float(v.w);
-        float h0 = tf32_rna(f0), h1 = tf32_rna(f1), h2 = tf32_rna(f2), h3 = tf32_rna(f3);
-        h.x = __float_as_uint(h0); h.y = __float_as_uint(h1); h.z = __float_as_uint(h2); h.w = __float_as_uint(h3);
-        l.x = __float_as_uint(tf32_rna(f0 - h0)); l.y = __float_as_uint(tf32_rna(f1 - h1));
-        l.z = __float_as_uint(tf32_rna(f2 - h2)); l.w = __float_as_uint(tf32_rna(f3 - h3));
+        uint4 h;
+        const uint4 l = split_lo(hi[idx], h);
+#if !OMT_TC_IMPLICIT_HI
         hi[idx] = h;
+#endif
         lo[idx] = l;
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -720,8 +800,7 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         uint32_t v[32];
         if (kblocks > 0) {
           uint32_t u[32];
-          tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + c * 32, v);
-          tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + BN + c * 32, u);
+          tmem_ld32x2(tmem_acc + ((uint32_t)(q * 32) << 16) + c * 32, tmem_acc + ((uint32_t)(q * 32) << 16) + BN + c * 32, v, u);
 #pragma unroll
           for (int j = 0; j < 32; j++) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(u[j]));
         } else {
@@ -782,7 +861,21 @@ template <int BN>
 int launch_wgrad(const OmtConvGeo* g, const WgPlan& w, const float* x, const float* gy, float* part, cudaStream_t s) {
   using S = WgSmem<BN>;
   alignas(64) CUtensorMap map_x, map_g;
-  {
+  const int64_t P = (int64_t)g->n * g->oh * g->ow;
+  int mode = 0;
+  if (g->ks == 1 && g->stride == 1 && g->pad == 0 && g->ci % 32 == 0) {
+    // x is the row-major [P, ci] matrix: dims (32 channels, pixel, 32-channel block), one box = the whole B tile
+    cuuint64_t dims[3] = {32, (cuuint64_t)P, (cuuint64_t)(g->ci / 32)};
+    cuuint64_t strides[2] = {(cuuint64_t)g->ci * 4, 128};
+    cuuint32_t box[3] = {BKF, PB, BN / 32}, estr[3] = {1, 1, 1};
+    CUresult r = g_encode_tiled(&map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)x, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+      set_error("cuTensorMapEncodeTiled (x matrix) failed (%d)", (int)r);
+      return OMT_ECUDA;
+    }
+    mode |= 2;
+  } else {
     cuuint64_t dims[4] = {(cuuint64_t)g->ci, (cuuint64_t)g->iw, (cuuint64_t)g->ih, (cuuint64_t)g->n};
     cuuint64_t strides[3] = {(cuuint64_t)g->ci * 4, (cuuint64_t)g->iw * g->ci * 4, (cuuint64_t)g->ih * g->iw * g->ci * 4};
     int lower[2] = {-g->pad, -g->pad}, upper[2] = {g->pad - (g->ks - 1), g->pad - (g->ks - 1)};
@@ -795,8 +888,18 @@ int launch_wgrad(const OmtConvGeo* g, const WgPlan& w, const float* x, const flo
       return OMT_ECUDA;
     }
   }
-  {
-    const int64_t P = (int64_t)g->n * g->oh * g->ow;
+  if (g->co % 32 == 0) {  // gy [P, co]: the 128-channel tile as one box of four 32-channel blocks
+    cuuint64_t dims[3] = {32, (cuuint64_t)P, (cuuint64_t)(g->co / 32)};
+    cuuint64_t strides[2] = {(cuuint64_t)g->co * 4, 128};
+    cuuint32_t box[3] = {BKF, PB, 4}, estr[3] = {1, 1, 1};
+    CUresult r = g_encode_tiled(&map_g, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)gy, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+      set_error("cuTensorMapEncodeTiled (gy blocks) failed (%d)", (int)r);
+      return OMT_ECUDA;
+    }
+    mode |= 1;
+  } else {
     cuuint64_t dims[2] = {(cuuint64_t)g->co, (cuuint64_t)P};
     cuuint64_t strides[1] = {(cuuint64_t)g->co * 4};
     cuuint32_t box[2] = {BKF, PB}, estr[2] = {1, 1};
@@ -813,6 +916,7 @@ int launch_wgrad(const OmtConvGeo* g, const WgPlan& w, const float* x, const flo
     attr_set = true;
   }
   WgArgs a{};
+  a.mode = mode;
   a.part = part; a.P = g->n * g->oh * g->ow; a.co = g->co; a.oh = g->oh; a.ow = g->ow; a.ks = g->ks; a.stride = g->stride; a.pad = g->pad;
   a.cblocks = w.cblocks; a.cpad = w.cpad; a.chunks = w.chunks; a.blocks_per_slice = w.blocks_per_slice;
   dim3 grid((unsigned)cdiv(g->co, BM), (unsigned)cdiv(w.chunks, BN / 32), (unsigned)w.slices);
@@ -908,9 +1012,20 @@ int launch_window(const OmtConvGeo* g, const WinPlan& w, const float* xs, const 
     OMT_CUDA(cudaFuncSetAttribute(conv_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
     attr_set = true;
   }
-  const int m_tiles = g->n * w.tiles_x * w.tiles_y, n_tiles = (int)cdiv(args.N, BN);
+  TcArgs a = args;
+  alignas(64) CUtensorMap map_y = map_w;
+  if (dense_out(a)) {  // 32-pixel pieces of the tile's rectangle: a row segment, or several short rows
+    const int bw = std::min(w.win_w, 32), bh = 32 / bw;
+    cuuint64_t dims[4] = {(cuuint64_t)a.N, (cuuint64_t)g->ow, (cuuint64_t)g->oh, (cuuint64_t)g->n};
+    cuuint64_t strides[3] = {(cuuint64_t)a.N * 4, (cuuint64_t)g->ow * a.N * 4, (cuuint64_t)g->oh * g->ow * a.N * 4};
+    cuuint32_t box[4] = {32, (cuuint32_t)bw, (cuuint32_t)bh, 1}, estr[4] = {1, 1, 1, 1};
+    if (g_encode_tiled(&map_y, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void*)a.y.p, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                       CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS)
+      a.store_mode = 2;
+  }
+  const int m_tiles = g->n * w.tiles_x * w.tiles_y, n_tiles = (int)cdiv(a.N, BN);
   const unsigned grid = (unsigned)std::min<int64_t>((int64_t)m_tiles * n_tiles, sm_count());
-  conv_tc_kernel<BN><<<grid, TC_THREADS, S::TOTAL, s>>>(map_a, map_w, args, m_tiles, n_tiles);
+  conv_tc_kernel<BN><<<grid, TC_THREADS, S::TOTAL, s>>>(map_a, map_w, map_y, a, m_tiles, n_tiles);
   return check_launch(BN == 64 ? "conv_tc_window_128x64" : (BN == 128 ? "conv_tc_window_128x128" : "conv_tc_window_128x256"));
 }
 
