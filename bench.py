@@ -86,17 +86,25 @@ class ClockSampler:
 # workload: conv1 (C ABI)
 # ---------------------------------------------------------------------------------------------------------------------
 
-class Conv1:
-    name = "alexnet_conv1_fwd_dgrad_wgrad"
-    shape = dict(n=16, ci=3, co=64, hw=224, ks=11, stride=4, pad=2)
-    flops = 3 * 2 * 16 * 64 * 55 * 55 * 3 * 11 * 11  # tools/gemm_bench.py:29, three passes
+class ConvLayer:
+    """One conv layer's forward + input gradient + weight gradient (+ bias gradient) through the C ABI."""
     metric, unit, higher = "conv_tflops", "TFLOP/s", True
+
+    def __init__(self, name, n, ci, co, hw, ks, stride, pad, channels_last):
+        self.name, self.n, self.ci, self.co, self.hw, self.ks, self.stride, self.pad, self.cl = name, n, ci, co, hw, ks, stride, pad, channels_last
+        self.oh = (hw + 2 * pad - ks) // stride + 1
+        self.shape = dict(n=n, ci=ci, co=co, hw=hw, ks=ks, stride=stride, pad=pad, layout="channels_last" if channels_last else "nchw")
+        self.flops = 3 * 2 * n * co * self.oh * self.oh * ci * ks * ks  # tools/gemm_bench.py:29, three passes
+        self.h2d_bytes = (n * ci * hw * hw + co * ci * ks * ks + co + n * co * self.oh * self.oh) * 4
+        self.d2h_bytes = 4
 
     def host_inputs(self, seed):
         torch.manual_seed(seed)
-        x = torch.randn(16, 3, 224, 224)
-        conv = torch.nn.Conv2d(3, 64, 11, stride=4, padding=2)
-        gy = torch.randn(16, 64, 55, 55)
+        x = torch.randn(self.n, self.ci, self.hw, self.hw)
+        conv = torch.nn.Conv2d(self.ci, self.co, self.ks, stride=self.stride, padding=self.pad)
+        gy = torch.randn(self.n, self.co, self.oh, self.oh)
+        if self.cl:
+            x, gy = x.contiguous(memory_format=torch.channels_last), gy.contiguous(memory_format=torch.channels_last)
         return x, conv.weight.detach().clone(), conv.bias.detach().clone(), gy
 
     def cpu_setup(self):
@@ -117,9 +125,9 @@ class Conv1:
     def step(self, ins=None):
         c = self.capi
         x, w, b, gy = ins if ins is not None else self.d
-        y = c.conv_fwd(x, w, b, 4, 2)
-        dx = c.conv_dgrad(gy, w, (224, 224), 4, 2)
-        dw = c.conv_wgrad(x, gy, 11, 4, 2)
+        y = c.conv_fwd(x, w, b, self.stride, self.pad, cl=self.cl)
+        dx = c.conv_dgrad(gy, w, (self.hw, self.hw), self.stride, self.pad, cl=self.cl)
+        dw = c.conv_wgrad(x, gy, self.ks, self.stride, self.pad)
         db = c.conv_bias_grad(gy)
         return y, dx, dw, db
 
@@ -129,24 +137,36 @@ class Conv1:
         y, dx, dw, db = self.step(self.staging)
         return dw.sum().item()  # device->host read of a result scalar
 
-    h2d_bytes = (16 * 3 * 224 * 224 + 64 * 3 * 121 + 64 + 16 * 64 * 55 * 55) * 4
-    d2h_bytes = 4
-
     def value(self, ms):
         return self.flops / (ms * 1e-3) / 1e12
 
     def cpu_step(self, ins):
         x, w, b, gy = ins
-        y = torch.nn.functional.conv2d(x, w, b, stride=4, padding=2)
-        return torch.ops.aten.convolution_backward(gy, x, w, [64], [4, 4], [2, 2], [1, 1], False, [0, 0], 1, [True, True, True])
+        y = torch.nn.functional.conv2d(x, w, b, stride=self.stride, padding=self.pad)
+        return torch.ops.aten.convolution_backward(gy, x, w, [self.co], [self.stride] * 2, [self.pad] * 2, [1, 1], False, [0, 0], 1, [True, True, True])
 
     def roofline(self, ms, peaks):
-        # conv GEMMs: tensor pipe, 3xTF32-effective peak = tf32 dense (bf16/2) / 3
+        # conv GEMMs: tensor pipe, 3xTF32-effective peak = tf32 dense (bf16/2) / 3; per pass from the library's CUDA-event timing
+        self.capi.conv_timing(True)
+        for _ in range(3):
+            self.step()
+        torch.cuda.synchronize()
+        t = self.capi.conv_timing_read(reset=True)
+        self.capi.conv_timing(False)
         peak = peaks["bf16_tflops"] / 2 / 3
         ach = self.flops / (ms * 1e-3) / 1e12
         return {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak, "traffic": None,
-                "peak_source": f"{peaks['source']} bf16 burst / 2 (tf32) / 3 (3xTF32)"}
+                "peak_source": f"{peaks['source']} bf16 burst / 2 (tf32) / 3 (3xTF32)",
+                "kernel": "conv fwd + dgrad + wgrad of one layer (all kernels of the three calls)",
+                "per_pass": {k: {"tflops": (v[0] / (v[1] * 1e-3) / 1e12 if v[1] else None), "ms": v[1] / 3, "calls": v[2] // 3} for k, v in t.items()}}
 
+
+CONV = {
+    # BASELINE config 1: the AlexNet conv1 shape, NCHW as the reference benchmarks it
+    "conv1": lambda: ConvLayer("alexnet_conv1_fwd_dgrad_wgrad", 16, 3, 64, 224, 11, 4, 2, False),
+    # a mid-network ResNet layer, channels-last, inputs + outputs larger than L2: the small case the ncu captures use
+    "conv3x3": lambda: ConvLayer("conv3x3_256_28_b128_fwd_dgrad_wgrad", 128, 256, 256, 28, 3, 1, 1, True),
+}
 
 
 # ---------------------------------------------------------------------------------------------------------------------
@@ -273,7 +293,7 @@ TRAIN = {
                               _sgd(0.1, momentum=0.9, nesterov=True, weight_decay=1e-4), 16, "SGD lr .1 momentum .9 nesterov wd 1e-4"),
 }
 
-WORKLOADS = {"conv1": Conv1, **TRAIN}
+WORKLOADS = {**CONV, **TRAIN}
 
 
 def dist_setup(n):
@@ -362,7 +382,7 @@ def main():
                     help="for ncu --profile-from-start off: after the warm-up run ONE step between cudaProfilerStart/Stop and exit")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
-    wl = WORKLOADS[args.workload]() if args.workload != "conv1" else Conv1()
+    wl = WORKLOADS[args.workload]()
     if args.impl == "reference":
         return run_reference(args, wl)
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"

@@ -96,6 +96,11 @@ __device__ __forceinline__ void tma_tile_4d(uint32_t dst, const CUtensorMap* map
                ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z), "r"(w)
                : "memory");
 }
+__device__ __forceinline__ void tma_tile_5d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z, int w, int v) {
+  asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+               ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z), "r"(w), "r"(v)
+               : "memory");
+}
 __device__ __forceinline__ void tma_tile_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
   asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
                ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z)
@@ -643,7 +648,15 @@ constexpr int PB = 32;            // pixels (reduction depth) per stage
 constexpr int WG_THREADS = 320;   // producer warp, MMA warp, 8 split/epilogue warps
 
 struct WgArgs {
-  int mode;          // bit 0: gy tile by one 3-D TMA box; bit 1: x is the plain [pixels, ci] matrix (1x1, stride 1), one 3-D box
+  // bit 0: gy tile by one 3-D TMA box; bit 1: x is the plain [pixels, ci] matrix (1x1, stride 1), one 3-D box.
+  // bit 2: "rectangle" pixel blocks: a stage holds bw x bh pixels of bn images (bw*bh*bn = 32) so that both operands come
+  //        through tiled tensor maps, gy as one 5-D box and x as one 5-D box per filter tap (`cpi` 32-channel blocks each),
+  //        shifted by the tap and zero-filled outside the image.
+  // bit 3: with bit 2, "window" x operand for <= 4 input channels: the 32-float run (8 pixels x 4 channels) of a filter
+  //        row out of the padded 4-channel staging copy, one box per (filter row, 32-float block) chunk; bw = 32.
+  int mode;
+  int total_blocks;  // pixel blocks in all
+  int bw, bh, bn, tiles_x, tiles_y, cpi;
   float* part;       // [slices][co][kcols] partial tiles
   int P;             // pixels = n * oh * ow
   int co;
@@ -681,7 +694,7 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
   const int co0 = blockIdx.x * BM;
   const int chunk0 = blockIdx.y * (BN / 32);
   const int nchunks = min(BN / 32, g.chunks - chunk0);
-  const int total_blocks = (g.P + PB - 1) / PB;
+  const int total_blocks = g.total_blocks;
   const int blk_begin = blockIdx.z * g.blocks_per_slice;
   const int kblocks = max(0, min(g.blocks_per_slice, total_blocks - blk_begin));
 
@@ -712,10 +725,31 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
       for (int kb = 0; kb < kblocks; kb++) {
         const int s = kb % S::STAGES, round = kb / S::STAGES;
         if (round > 0 && !mbar_wait(BAR(2 * S::STAGES + s), (round - 1) & 1, abort_flag)) break;
+        const uint32_t stage = smem_base + s * S::STAGE_BYTES;
+        if (g.mode & 4) {
+          const int b = blk_begin + kb;
+          const int tx = b % g.tiles_x, r1 = b / g.tiles_x, ty = r1 % g.tiles_y, tn = r1 / g.tiles_y;
+          const int ox0 = tx * g.bw, oy0 = ty * g.bh, n0 = tn * g.bn;
+          mbar_expect_tx(BAR(s), S::A_BYTES + nchunks * S::CH);
+          tma_tile_5d(stage, &map_g, BAR(s), 0, ox0, oy0, n0, co0 / 32);
+          if (g.mode & 8) {
+            for (int j = 0; j < nchunks; j++) {
+              const int chunk = chunk0 + j, ky = chunk / g.cblocks, blk = chunk - ky * g.cblocks;
+              tma_tile_4d(stage + S::A_BYTES + j * S::CH, &map_x, BAR(s), blk * BKF, ox0, oy0 * g.stride + ky - g.pad, n0);
+            }
+          } else {
+            for (int j = 0; j < nchunks; j += g.cpi) {
+              const int chunk = chunk0 + j, tap = chunk / g.cblocks, cb = chunk - tap * g.cblocks;
+              const int ky = tap / g.ks, kx = tap - ky * g.ks;
+              tma_tile_5d(stage + S::A_BYTES + j * S::CH, &map_x, BAR(s), 0, ox0 * g.stride - g.pad + kx, oy0 * g.stride - g.pad + ky, n0, cb);
+            }
+          }
+          issued = kb + 1;
+          continue;
+        }
         const int p0 = (blk_begin + kb) * PB;
         const int img = p0 / ohw, r = p0 - img * ohw, oy = r / g.ow, ox = r - oy * g.ow;
         const int w0 = ox * g.stride - g.pad, h0 = oy * g.stride - g.pad;
-        const uint32_t stage = smem_base + s * S::STAGE_BYTES;
         mbar_expect_tx(BAR(s), S::A_BYTES + ((g.mode & 2) ? S::B_BYTES : nchunks * S::CH));
         if (g.mode & 1) {
           tma_tile_3d(stage, &map_g, BAR(s), 0, p0, co0 / 32);
@@ -824,106 +858,27 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
 }
 
 // dw[o][c][ky][kx] = scale * sum_z part[z][o][tap*cpad + c]
+// window mode (win_ks > 0): column of (c, ky, kx) is (ky*win_kb + kx/8)*32 + (kx%8)*4 + c, kcols = win_ks*win_kb*32
 __global__ void __launch_bounds__(256) wgrad_tc_reduce_kernel(const float* __restrict__ part, float* __restrict__ dw, int co, int ci, int kk,
-                                                              int cpad, int slices, float scale) {
+                                                              int cpad, int slices, float scale, int win_ks, int win_kb) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t total = (int64_t)co * ci * kk;
   if (i >= total) return;
   const int tap = (int)(i % kk);
   const int c = (int)((i / kk) % ci);
   const int o = (int)(i / ((int64_t)kk * ci));
-  const int64_t kcols = (int64_t)kk * cpad, slab = (int64_t)co * kcols;
-  const float* p = part + (int64_t)o * kcols + (int64_t)tap * cpad + c;
+  int64_t kcols = (int64_t)kk * cpad, col = (int64_t)tap * cpad + c;
+  if (win_ks) {
+    const int ky = tap / win_ks, kx = tap - ky * win_ks;
+    kcols = (int64_t)win_ks * win_kb * 32;
+    col = (int64_t)(ky * win_kb + kx / 8) * 32 + (kx % 8) * 4 + c;
+  }
+  const int64_t slab = (int64_t)co * kcols;
+  const float* p = part + (int64_t)o * kcols + col;
   float s = 0.f;
   for (int z = 0; z < slices; z++) s += __ldg(p + z * slab);
   dw[i] = s * scale;
 }
-
-struct WgPlan {
-  int bn, slices, blocks_per_slice, cblocks, cpad, chunks;
-  size_t part_floats;
-};
-WgPlan plan_wgrad(const OmtConvGeo* g) {
-  WgPlan w{};
-  w.cblocks = (int)cdiv(g->ci, BKF); w.cpad = w.cblocks * BKF; w.chunks = g->ks * g->ks * w.cblocks;
-  w.bn = w.chunks >= 6 ? 256 : (w.chunks >= 3 ? 128 : 64);
-  int64_t tiles = cdiv(g->co, BM) * cdiv(w.chunks, w.bn / 32);
-  int64_t total_blocks = cdiv((int64_t)g->n * g->oh * g->ow, PB);
-  int64_t want = std::max<int64_t>(1, (3 * sm_count()) / tiles);
-  int64_t slices = std::max<int64_t>(1, std::min<int64_t>(want, total_blocks / 8));
-  w.blocks_per_slice = (int)cdiv(total_blocks, slices);
-  w.slices = (int)cdiv(total_blocks, w.blocks_per_slice);
-  w.part_floats = (size_t)w.slices * g->co * w.chunks * 32;
-  return w;
-}
-
-template <int BN>
-int launch_wgrad(const OmtConvGeo* g, const WgPlan& w, const float* x, const float* gy, float* part, cudaStream_t s) {
-  using S = WgSmem<BN>;
-  alignas(64) CUtensorMap map_x, map_g;
-  const int64_t P = (int64_t)g->n * g->oh * g->ow;
-  int mode = 0;
-  if (g->ks == 1 && g->stride == 1 && g->pad == 0 && g->ci % 32 == 0) {
-    // x is the row-major [P, ci] matrix: dims (32 channels, pixel, 32-channel block), one box = the whole B tile
-    cuuint64_t dims[3] = {32, (cuuint64_t)P, (cuuint64_t)(g->ci / 32)};
-    cuuint64_t strides[2] = {(cuuint64_t)g->ci * 4, 128};
-    cuuint32_t box[3] = {BKF, PB, BN / 32}, estr[3] = {1, 1, 1};
-    CUresult r = g_encode_tiled(&map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)x, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) {
-      set_error("cuTensorMapEncodeTiled (x matrix) failed (%d)", (int)r);
-      return OMT_ECUDA;
-    }
-    mode |= 2;
-  } else {
-    cuuint64_t dims[4] = {(cuuint64_t)g->ci, (cuuint64_t)g->iw, (cuuint64_t)g->ih, (cuuint64_t)g->n};
-    cuuint64_t strides[3] = {(cuuint64_t)g->ci * 4, (cuuint64_t)g->iw * g->ci * 4, (cuuint64_t)g->ih * g->iw * g->ci * 4};
-    int lower[2] = {-g->pad, -g->pad}, upper[2] = {g->pad - (g->ks - 1), g->pad - (g->ks - 1)};
-    cuuint32_t estr[4] = {1, (cuuint32_t)g->stride, (cuuint32_t)g->stride, 1};
-    CUresult r = g_encode_im2col(&map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void*)x, dims, strides, lower, upper, BKF, PB, estr,
-                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) {
-      set_error("cuTensorMapEncodeIm2col failed (%d)", (int)r);
-      return OMT_ECUDA;
-    }
-  }
-  if (g->co % 32 == 0) {  // gy [P, co]: the 128-channel tile as one box of four 32-channel blocks
-    cuuint64_t dims[3] = {32, (cuuint64_t)P, (cuuint64_t)(g->co / 32)};
-    cuuint64_t strides[2] = {(cuuint64_t)g->co * 4, 128};
-    cuuint32_t box[3] = {BKF, PB, 4}, estr[3] = {1, 1, 1};
-    CUresult r = g_encode_tiled(&map_g, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)gy, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) {
-      set_error("cuTensorMapEncodeTiled (gy blocks) failed (%d)", (int)r);
-      return OMT_ECUDA;
-    }
-    mode |= 1;
-  } else {
-    cuuint64_t dims[2] = {(cuuint64_t)g->co, (cuuint64_t)P};
-    cuuint64_t strides[1] = {(cuuint64_t)g->co * 4};
-    cuuint32_t box[2] = {BKF, PB}, estr[2] = {1, 1};
-    CUresult r = g_encode_tiled(&map_g, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)gy, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) {
-      set_error("cuTensorMapEncodeTiled failed (%d)", (int)r);
-      return OMT_ECUDA;
-    }
-  }
-  static bool attr_set = false;
-  if (!attr_set) {
-    OMT_CUDA(cudaFuncSetAttribute(wgrad_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
-    attr_set = true;
-  }
-  WgArgs a{};
-  a.mode = mode;
-  a.part = part; a.P = g->n * g->oh * g->ow; a.co = g->co; a.oh = g->oh; a.ow = g->ow; a.ks = g->ks; a.stride = g->stride; a.pad = g->pad;
-  a.cblocks = w.cblocks; a.cpad = w.cpad; a.chunks = w.chunks; a.blocks_per_slice = w.blocks_per_slice;
-  dim3 grid((unsigned)cdiv(g->co, BM), (unsigned)cdiv(w.chunks, BN / 32), (unsigned)w.slices);
-  wgrad_tc_kernel<BN><<<grid, WG_THREADS, S::TOTAL, s>>>(map_x, map_g, a);
-  return check_launch(BN == 64 ? "wgrad_tc_128x64" : (BN == 128 ? "wgrad_tc_128x128" : "wgrad_tc_128x256"));
-}
-
 
 // ---------------------------------------------------------------------------------------------------------------------
 // window mode (ci <= 4): staging copy and host side
@@ -1057,6 +1012,144 @@ int run_window_fwd(const OmtConvGeo* g, const OmtAct* x, const float* w, const f
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// weight gradient: host side
+// ---------------------------------------------------------------------------------------------------------------------
+struct WgPlan {
+  int bn, slices, blocks_per_slice, cblocks, cpad, chunks;
+  int mode, total_blocks, bw, bh, bn_img, tiles_x, tiles_y, cpi;
+  int win_kb;           // window mode: 32-float blocks per filter row
+  size_t stage_floats;  // window mode: the padded 4-channel copy of x in front of the partial tiles
+  size_t part_floats;
+};
+WgPlan plan_wgrad(const OmtConvGeo* g) {
+  WgPlan w{};
+  const bool window = g->ci <= 4;
+  if (window) {
+    const WinPlan wp = plan_window(g);
+    w.win_kb = wp.kb; w.stage_floats = ((wp.stage_floats + 63) / 64) * 64;
+    w.cblocks = wp.kb; w.cpad = wp.kb * BKF; w.chunks = g->ks * wp.kb;
+  } else {
+    w.cblocks = (int)cdiv(g->ci, BKF); w.cpad = w.cblocks * BKF; w.chunks = g->ks * g->ks * w.cblocks;
+  }
+  w.bn = w.chunks >= 6 ? 256 : (w.chunks >= 3 ? 128 : 64);
+  const int64_t tiles = cdiv(g->co, BM) * cdiv(w.chunks, w.bn / 32);
+  int64_t total_blocks = cdiv((int64_t)g->n * g->oh * g->ow, PB);
+  const int per_tile = w.bn / 32;
+  w.cpi = std::min(w.cblocks, per_tile);
+  const bool aligned_taps = w.cblocks % w.cpi == 0 && per_tile % w.cpi == 0;
+  if (window) {
+    w.mode = 4 | 8;
+    w.bw = 32; w.bh = 1; w.bn_img = 1;
+  } else if (g->ks == 1 && g->stride == 1 && g->pad == 0 && g->ci % 32 == 0) {
+    w.mode = 2 | (g->co % 32 == 0 ? 1 : 0);
+  } else if (g->ci % 32 == 0 && g->co % 32 == 0 && aligned_taps && g->stride <= 8) {
+    // 32-pixel rectangles bw x bh x bn (powers of two) that waste the fewest pixels; wider rows on ties
+    w.mode = 4;
+    double best = -1;
+    for (int bw = 32; bw >= 1; bw >>= 1)
+      for (int bh = 32 / bw; bh >= 1; bh >>= 1) {
+        const int bn = 32 / (bw * bh);
+        if (bw * g->stride > 256 || bh * g->stride > 256) continue;
+        const double eff = ((double)g->ow * g->oh * g->n) /
+                           ((double)cdiv(g->ow, bw) * bw * cdiv(g->oh, bh) * bh * cdiv(g->n, bn) * bn);
+        if (eff > best + 1e-9) { best = eff; w.bw = bw; w.bh = bh; w.bn_img = bn; }
+      }
+  } else {
+    w.mode = g->co % 32 == 0 ? 1 : 0;
+  }
+  if (w.mode & 4) {
+    w.tiles_x = (int)cdiv(g->ow, w.bw); w.tiles_y = (int)cdiv(g->oh, w.bh);
+    total_blocks = (int64_t)w.tiles_x * w.tiles_y * cdiv(g->n, w.bn_img);
+  }
+  w.total_blocks = (int)total_blocks;
+  const int64_t want = std::max<int64_t>(1, (3 * sm_count()) / tiles);
+  const int64_t slices = std::max<int64_t>(1, std::min<int64_t>(want, total_blocks / 8));
+  w.blocks_per_slice = (int)cdiv(total_blocks, slices);
+  w.slices = (int)cdiv(total_blocks, w.blocks_per_slice);
+  w.part_floats = (size_t)w.slices * g->co * w.chunks * 32;
+  return w;
+}
+
+#define OMT_ENCODE(call, what)                                   \
+  do {                                                           \
+    CUresult r_ = (call);                                        \
+    if (r_ != CUDA_SUCCESS) {                                    \
+      set_error("%s failed (%d)", what, (int)r_);                \
+      return OMT_ECUDA;                                          \
+    }                                                            \
+  } while (0)
+
+// `x` is the channels-last activation, or in window mode the padded 4-channel staging copy
+template <int BN>
+int launch_wgrad(const OmtConvGeo* g, const WgPlan& w, const float* x, const float* gy, float* part, cudaStream_t s) {
+  using S = WgSmem<BN>;
+  alignas(64) CUtensorMap map_x, map_g;
+  const int64_t P = (int64_t)g->n * g->oh * g->ow;
+  constexpr auto F32 = CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  constexpr auto SW = CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B;
+  constexpr auto IL = CU_TENSOR_MAP_INTERLEAVE_NONE;
+  constexpr auto L2P = CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
+  constexpr auto FILL = CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE;
+  // ---- x ----
+  if (w.mode & 8) {
+    // staging copy [n][ih][ws][4]: dims (floats of a window row, ox with overlapping stride, input row, image)
+    const WinPlan wp = plan_window(g);
+    cuuint64_t dims[4] = {(cuuint64_t)wp.kb * BKF, (cuuint64_t)g->ow, (cuuint64_t)g->ih, (cuuint64_t)g->n};
+    cuuint64_t strides[3] = {(cuuint64_t)g->stride * 16, (cuuint64_t)wp.ws * 16, (cuuint64_t)g->ih * wp.ws * 16};
+    cuuint32_t box[4] = {BKF, PB, 1, 1}, estr[4] = {1, 1, 1, 1};
+    OMT_ENCODE(g_encode_tiled(&map_x, F32, 4, (void*)x, dims, strides, box, estr, IL, SW, L2P, FILL), "cuTensorMapEncodeTiled (window rows)");
+  } else if (w.mode & 4) {
+    cuuint64_t dims[5] = {32, (cuuint64_t)g->iw, (cuuint64_t)g->ih, (cuuint64_t)g->n, (cuuint64_t)(g->ci / 32)};
+    cuuint64_t strides[4] = {(cuuint64_t)g->ci * 4, (cuuint64_t)g->iw * g->ci * 4, (cuuint64_t)g->ih * g->iw * g->ci * 4, 128};
+    cuuint32_t box[5] = {BKF, (cuuint32_t)(w.bw * g->stride), (cuuint32_t)(w.bh * g->stride), (cuuint32_t)w.bn_img, (cuuint32_t)w.cpi};
+    cuuint32_t estr[5] = {1, (cuuint32_t)g->stride, (cuuint32_t)g->stride, 1, 1};
+    OMT_ENCODE(g_encode_tiled(&map_x, F32, 5, (void*)x, dims, strides, box, estr, IL, SW, L2P, FILL), "cuTensorMapEncodeTiled (x rectangles)");
+  } else if (w.mode & 2) {
+    // x is the row-major [P, ci] matrix: dims (32 channels, pixel, 32-channel block), one box = the whole B tile
+    cuuint64_t dims[3] = {32, (cuuint64_t)P, (cuuint64_t)(g->ci / 32)};
+    cuuint64_t strides[2] = {(cuuint64_t)g->ci * 4, 128};
+    cuuint32_t box[3] = {BKF, PB, BN / 32}, estr[3] = {1, 1, 1};
+    OMT_ENCODE(g_encode_tiled(&map_x, F32, 3, (void*)x, dims, strides, box, estr, IL, SW, L2P, FILL), "cuTensorMapEncodeTiled (x matrix)");
+  } else {
+    cuuint64_t dims[4] = {(cuuint64_t)g->ci, (cuuint64_t)g->iw, (cuuint64_t)g->ih, (cuuint64_t)g->n};
+    cuuint64_t strides[3] = {(cuuint64_t)g->ci * 4, (cuuint64_t)g->iw * g->ci * 4, (cuuint64_t)g->ih * g->iw * g->ci * 4};
+    int lower[2] = {-g->pad, -g->pad}, upper[2] = {g->pad - (g->ks - 1), g->pad - (g->ks - 1)};
+    cuuint32_t estr[4] = {1, (cuuint32_t)g->stride, (cuuint32_t)g->stride, 1};
+    OMT_ENCODE(g_encode_im2col(&map_x, F32, 4, (void*)x, dims, strides, lower, upper, BKF, PB, estr, IL, SW, L2P, FILL), "cuTensorMapEncodeIm2col");
+  }
+  // ---- gy ----
+  if (w.mode & 4) {
+    cuuint64_t dims[5] = {32, (cuuint64_t)g->ow, (cuuint64_t)g->oh, (cuuint64_t)g->n, (cuuint64_t)(g->co / 32)};
+    cuuint64_t strides[4] = {(cuuint64_t)g->co * 4, (cuuint64_t)g->ow * g->co * 4, (cuuint64_t)g->oh * g->ow * g->co * 4, 128};
+    cuuint32_t box[5] = {BKF, (cuuint32_t)w.bw, (cuuint32_t)w.bh, (cuuint32_t)w.bn_img, 4}, estr[5] = {1, 1, 1, 1, 1};
+    OMT_ENCODE(g_encode_tiled(&map_g, F32, 5, (void*)gy, dims, strides, box, estr, IL, SW, L2P, FILL), "cuTensorMapEncodeTiled (gy rectangles)");
+  } else if (w.mode & 1) {  // gy [P, co]: the 128-channel tile as one box of four 32-channel blocks
+    cuuint64_t dims[3] = {32, (cuuint64_t)P, (cuuint64_t)(g->co / 32)};
+    cuuint64_t strides[2] = {(cuuint64_t)g->co * 4, 128};
+    cuuint32_t box[3] = {BKF, PB, 4}, estr[3] = {1, 1, 1};
+    OMT_ENCODE(g_encode_tiled(&map_g, F32, 3, (void*)gy, dims, strides, box, estr, IL, SW, L2P, FILL), "cuTensorMapEncodeTiled (gy blocks)");
+  } else {
+    cuuint64_t dims[2] = {(cuuint64_t)g->co, (cuuint64_t)P};
+    cuuint64_t strides[1] = {(cuuint64_t)g->co * 4};
+    cuuint32_t box[2] = {BKF, PB}, estr[2] = {1, 1};
+    OMT_ENCODE(g_encode_tiled(&map_g, F32, 2, (void*)gy, dims, strides, box, estr, IL, SW, L2P, FILL), "cuTensorMapEncodeTiled (gy)");
+  }
+  static bool attr_set = false;
+  if (!attr_set) {
+    OMT_CUDA(cudaFuncSetAttribute(wgrad_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
+    attr_set = true;
+  }
+  WgArgs a{};
+  a.mode = w.mode; a.total_blocks = w.total_blocks;
+  a.bw = w.bw; a.bh = w.bh; a.bn = w.bn_img; a.tiles_x = w.tiles_x; a.tiles_y = w.tiles_y; a.cpi = w.cpi;
+  a.part = part; a.P = g->n * g->oh * g->ow; a.co = g->co; a.oh = g->oh; a.ow = g->ow; a.ks = g->ks; a.stride = g->stride; a.pad = g->pad;
+  a.cblocks = w.cblocks; a.cpad = w.cpad; a.chunks = w.chunks; a.blocks_per_slice = w.blocks_per_slice;
+  dim3 grid((unsigned)cdiv(g->co, BM), (unsigned)cdiv(w.chunks, BN / 32), (unsigned)w.slices);
+  wgrad_tc_kernel<BN><<<grid, WG_THREADS, S::TOTAL, s>>>(map_x, map_g, a);
+  return check_launch(BN == 64 ? "wgrad_tc_128x64" : (BN == 128 ? "wgrad_tc_128x128" : "wgrad_tc_128x256"));
+}
+
 bool cl_ok(const OmtAct* a, int c, int h, int w) {
   return a && a->p && is_nhwc(a, c, h, w) && c % 4 == 0 && (reinterpret_cast<uintptr_t>(a->p) & 15) == 0;
 }
@@ -1075,7 +1168,9 @@ bool tc_supported(int kind, const OmtConvGeo* g, const OmtAct* a, const OmtAct* 
   if (kind == 0) return (cl_ok(a, g->ci, g->ih, g->iw) && g->ci >= 8 && g->co >= 8 && g->pad < g->ks) || (a && a->p && window_ok(g));
   if (kind == 1) return cl_ok(a, g->co, g->oh, g->ow) && g->co >= 8 && g->ci >= 8 && g->pad < g->ks;
   // kind 2: a = x, b = gy
-  return cl_ok(a, g->ci, g->ih, g->iw) && cl_ok(b, g->co, g->oh, g->ow) && g->ci >= 8 && g->co >= 8 && g->pad < g->ks;
+  if (!cl_ok(b, g->co, g->oh, g->ow) || g->co < 8 || g->pad >= g->ks) return false;
+  if (g->ci <= 4) return a && a->p && window_ok(g) && g->co % 32 == 0;  // window mode reads x through a staging copy: any layout
+  return cl_ok(a, g->ci, g->ih, g->iw) && g->ci >= 8;
 }
 size_t tc_workspace(int kind, const OmtConvGeo* g) {
   if (kind == 0) {
@@ -1086,7 +1181,8 @@ size_t tc_workspace(int kind, const OmtConvGeo* g) {
     return split_floats(g->co, g->ks, g->ci) * sizeof(float) + 256;
   }
   if (kind == 1) return split_floats(g->ci, g->ks, g->co) * sizeof(float) + 256;
-  return plan_wgrad(g).part_floats * sizeof(float) + 256;
+  const WgPlan w = plan_wgrad(g);
+  return (w.stage_floats + w.part_floats) * sizeof(float) + 256;
 }
 
 int tc_conv_fwd(const OmtConvGeo* g, const OmtAct* x, const float* w, const float* bias, const OmtAct* y, float* stats, uint32_t flags, void* ws,
@@ -1153,16 +1249,26 @@ int tc_conv_wgrad(const OmtConvGeo* g, const OmtAct* x, const OmtAct* gy, float*
     return OMT_ECUDA;
   }
   const WgPlan w = plan_wgrad(g);
-  float* part = (float*)ws;
+  float* part = (float*)ws + w.stage_floats;
+  const float* xin = x->p;
+  if (w.mode & 8) {  // padded 4-channel copy of x, as in the forward window mode
+    const WinPlan wp = plan_window(g);
+    const int64_t total = (int64_t)g->n * g->ih * wp.ws;
+    stage_window_kernel<<<(unsigned)cdiv(total, 256), 256, 0, s>>>(view(x), (float*)ws, g->n, g->ci, g->ih, g->iw, wp.ws, g->pad);
+    int r0 = check_launch("conv_tc_stage_window");
+    if (r0) return r0;
+    xin = (const float*)ws;
+  }
   int r;
   switch (w.bn) {
-    case 64: r = launch_wgrad<64>(g, w, x->p, gy->p, part, s); break;
-    case 128: r = launch_wgrad<128>(g, w, x->p, gy->p, part, s); break;
-    default: r = launch_wgrad<256>(g, w, x->p, gy->p, part, s); break;
+    case 64: r = launch_wgrad<64>(g, w, xin, gy->p, part, s); break;
+    case 128: r = launch_wgrad<128>(g, w, xin, gy->p, part, s); break;
+    default: r = launch_wgrad<256>(g, w, xin, gy->p, part, s); break;
   }
   if (r) return r;
   const int64_t total = (int64_t)g->co * g->ci * g->ks * g->ks;
-  wgrad_tc_reduce_kernel<<<(unsigned)cdiv(total, 256), 256, 0, s>>>(part, dw, g->co, g->ci, g->ks * g->ks, w.cpad, w.slices, scale);
+  wgrad_tc_reduce_kernel<<<(unsigned)cdiv(total, 256), 256, 0, s>>>(part, dw, g->co, g->ci, g->ks * g->ks, w.cpad, w.slices, scale,
+                                                                     (w.mode & 8) ? g->ks : 0, w.win_kb);
   return check_launch("wgrad_tc_reduce");
 }
 

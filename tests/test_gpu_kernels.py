@@ -71,7 +71,11 @@ def test_conv_default_path_matches_golden(capi, golden):
 
 TC_SHAPES = [(2, 3, 64, 32, 7, 2, 3), (3, 3, 24, 63, 11, 4, 2), (2, 4, 24, 20, 5, 2, 2), (2, 1, 16, 28, 3, 1, 1), (2, 32, 64, 16, 1, 1, 0), (2, 64, 128, 16, 3, 1, 1), (4, 64, 200, 15, 3, 1, 1), (3, 24, 40, 17, 5, 1, 2), (2, 64, 64, 16, 3, 2, 1),
              (2, 128, 256, 14, 1, 2, 0), (8, 256, 512, 14, 3, 1, 1), (2, 16, 32, 20, 7, 2, 3), (1, 8, 8, 9, 3, 1, 0), (2, 32, 32, 19, 3, 3, 1),
-             (2, 32, 48, 16, 1, 4, 0), (2, 16, 16, 21, 5, 2, 0), (1, 520, 264, 9, 3, 1, 1)]
+             (2, 32, 48, 16, 1, 4, 0), (2, 16, 16, 21, 5, 2, 0), (1, 520, 264, 9, 3, 1, 1),
+             # weight-gradient operand modes: [pixels, ci] matrix with several 32-channel blocks; pixel rectangles for 7-, 8-, 9-
+             # and 12-wide outputs with stride 1 and 2, odd batch; window mode with 32-multiple output channels
+             (2, 64, 128, 16, 1, 1, 0), (4, 256, 512, 14, 1, 1, 0), (3, 128, 128, 7, 3, 1, 1), (5, 512, 64, 7, 3, 2, 1), (2, 96, 160, 9, 3, 1, 1),
+             (2, 64, 96, 12, 5, 2, 2), (3, 256, 64, 8, 1, 2, 0), (3, 3, 64, 63, 11, 4, 2), (2, 4, 32, 20, 5, 2, 2), (2, 1, 32, 28, 3, 1, 1), (2, 3, 96, 40, 3, 1, 1)]
 
 
 @pytest.mark.parametrize("shape", TC_SHAPES)
@@ -94,14 +98,20 @@ def test_tensor_core_path_vs_aten_and_exact_path(capi, shape):
     for cl in (True, False):
         got = capi.conv_fwd(xd, wd, bd, s, p, flags=capi.FORCE_TC | capi.EPI_RELU, cl=cl)
         assert rel_err(host(got), y) <= TOL
-    few = ci <= 4  # few input channels: the forward runs in window mode; the gradients take the library's default path
+    # few input channels: forward and weight gradient run in window mode (the weight gradient when co is a multiple of
+    # 32); the input gradient takes the library's default path
+    few = ci <= 4
+    wg_tc = not few or co % 32 == 0
     got_dx = capi.conv_dgrad(gd, wd, (hw, hw), s, p, flags=0 if few else capi.FORCE_TC, cl=True)
     assert rel_err(host(got_dx), dx) <= TOL
-    got_dw = capi.conv_wgrad(xd, gd, ks, s, p, flags=0 if few else capi.FORCE_TC, scale=0.5)
+    got_dw = capi.conv_wgrad(xd, gd, ks, s, p, flags=capi.FORCE_TC if wg_tc else 0, scale=0.5)
     assert rel_err(2 * host(got_dw), dw) <= TOL
+    if few and wg_tc:  # window mode stages x itself: an NCHW x is as good
+        got_dw = capi.conv_wgrad(dev(x), gd, ks, s, p, flags=capi.FORCE_TC, scale=0.5)
+        assert rel_err(2 * host(got_dw), dw) <= TOL
     capi.call("omt_sync")  # a tensor-core kernel that gave up on a barrier would be reported here
     after = capi.kernel_counts()
-    assert sum(v - before.get(k, 0) for k, v in after.items() if k.startswith(("conv_tc_1", "conv_tc_window", "wgrad_tc_1"))) >= (2 if few else 4)
+    assert sum(v - before.get(k, 0) for k, v in after.items() if k.startswith(("conv_tc_1", "conv_tc_window", "wgrad_tc_1"))) >= (2 + wg_tc if few else 4)
     # the two paths agree with each other far inside the tolerance
     exact = capi.conv_fwd(xd, wd, bd, s, p, flags=capi.FORCE_SIMT | capi.EPI_RELU, cl=True)
     assert rel_err(host(capi.conv_fwd(xd, wd, bd, s, p, flags=capi.FORCE_TC | capi.EPI_RELU, cl=True)), host(exact)) <= 5e-5
