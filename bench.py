@@ -175,11 +175,13 @@ CONV = {
 
 class Train:
     metric, unit, higher = "train_ms_per_step", "ms/step", False
+    compile = True  # --eager switches to the plain nn.Module call
 
     def __init__(self, name, make_model, shape, classes, make_opt, cpu_batch, note):
         self.name, self.make_model, self.in_shape, self.classes, self.make_opt = name, make_model, shape, classes, make_opt
         self.cpu_batch = min(cpu_batch, shape[0])
-        self.shape = {"batch_per_gpu": shape[0], "input": list(shape[1:]), "classes": classes, "optimizer": note}
+        self.shape = {"batch_per_gpu": shape[0], "input": list(shape[1:]), "classes": classes, "optimizer": note,
+                      "api": 'torch.compile(model, backend="omarchy_mac_torch")'}
 
     def host_inputs(self, seed, batch=None):
         g = torch.Generator().manual_seed(1000 + seed)
@@ -201,6 +203,8 @@ class Train:
         self.capi, self.core, self.dev = capi, core, omt.DEVICE
         capi.lib()
         self.model = self.build_model().to(self.dev)
+        # the package's compile backend: BatchNorm+ReLU(+residual add) fused in forward and backward graphs
+        self.fwd = torch.compile(self.model, backend="omarchy_mac_torch") if self.compile else self.model
         self.dp = None
         if world > 1:
             from omarchy_mac_torch_b200.dp import DataParallel
@@ -219,7 +223,7 @@ class Train:
             self.dp.zero_grad()
         else:
             self.opt.zero_grad(set_to_none=True)
-        loss = torch.nn.functional.cross_entropy(self.model(x), y)
+        loss = torch.nn.functional.cross_entropy(self.fwd(x), y)
         loss.backward()
         if self.dp is not None:
             self.dp.finish()
@@ -378,11 +382,15 @@ def main():
     ap.add_argument("--workload", default="resnet50", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--eager", action="store_true", help="training workloads: call the nn.Module directly instead of through the compile backend")
     ap.add_argument("--profile-step", action="store_true",
                     help="for ncu --profile-from-start off: after the warm-up run ONE step between cudaProfilerStart/Stop and exit")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     wl = WORKLOADS[args.workload]()
+    if args.eager and isinstance(wl, Train):
+        wl.compile = False
+        wl.shape["api"] = "eager nn.Module"
     if args.impl == "reference":
         return run_reference(args, wl)
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"

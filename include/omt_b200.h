@@ -184,6 +184,13 @@ int omt_bn_stats_from_sums(const float* sums, int64_t count, int32_t c, float* m
 /* y = (x-mean)*invstd*gamma+beta, ReLU with OMT_BN_RELU (bn_apply.wgsl:17-18, bn_relu.wgsl:17-18). */
 int omt_bn_apply(const OmtAct* x, const OmtAct* y, int32_t n, int32_t c, int32_t h, int32_t w, const float* mean,
                  const float* invstd, const float* gamma, const float* beta, uint32_t flags, omt_stream_t stream);
+/* y = (x-mean)*invstd*gamma+beta + res, ReLU with OMT_BN_RELU: the tail of a residual block (BatchNorm, add the
+ * identity branch, ReLU) in the pass bn_apply makes anyway. `res` has the layout of x; NULL (or res->p NULL) makes it
+ * omt_bn_apply. The reference's compile pass 1 (omarchy_mac_torch/compile.py:69-96) fuses BatchNorm+ReLU only; this is
+ * the same rewrite carried across the add. */
+int omt_bn_apply_add(const OmtAct* x, const OmtAct* res, const OmtAct* y, int32_t n, int32_t c, int32_t h, int32_t w,
+                     const float* mean, const float* invstd, const float* gamma, const float* beta, uint32_t flags,
+                     omt_stream_t stream);
 /* Eval mode: invstd = rsqrt(rv+eps) computed on the fly (bn_eval_inv.wgsl, bn_relu_rv.wgsl). */
 int omt_bn_eval(const OmtAct* x, const OmtAct* y, int32_t n, int32_t c, int32_t h, int32_t w, const float* rm,
                 const float* rv, const float* gamma, const float* beta, float eps, uint32_t flags,
@@ -195,6 +202,11 @@ int omt_bn_eval(const OmtAct* x, const OmtAct* y, int32_t n, int32_t c, int32_t 
 int omt_bn_backward(const OmtAct* gy, const OmtAct* x, const OmtAct* y, const OmtAct* dx, int32_t n, int32_t c,
                     int32_t h, int32_t w, const float* mean, const float* invstd, const float* gamma, float* dgb,
                     float scale, uint32_t flags, omt_stream_t stream);
+/* Same with a second output for the backward of omt_bn_apply_add: dres = gy masked by y>0, the gradient of the
+ * identity branch, written by the dx pass (needs OMT_BN_RELU and dx). dres NULL makes it omt_bn_backward. */
+int omt_bn_backward_add(const OmtAct* gy, const OmtAct* x, const OmtAct* y, const OmtAct* dx, const OmtAct* dres,
+                        int32_t n, int32_t c, int32_t h, int32_t w, const float* mean, const float* invstd,
+                        const float* gamma, float* dgb, float scale, uint32_t flags, omt_stream_t stream);
 
 /* ---- pooling: plan kernels (pool_fwd/bwd, avgpool_fwd/bwd, gap_fwd/bwd) and general ops (csrc/nn.cpp:137-222) --- */
 

@@ -85,8 +85,10 @@ SIGNATURES = {
     "omt_bn_stats": (_I, [_A, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _F, _F, _U, _P]),
     "omt_bn_stats_from_sums": (_I, [_P, _I64, _I, _P, _P, _P, _P, _P, _F, _F, _P]),
     "omt_bn_apply": (_I, [_A, _A, _I, _I, _I, _I, _P, _P, _P, _P, _U, _P]),
+    "omt_bn_apply_add": (_I, [_A, _A, _A, _I, _I, _I, _I, _P, _P, _P, _P, _U, _P]),
     "omt_bn_eval": (_I, [_A, _A, _I, _I, _I, _I, _P, _P, _P, _P, _F, _U, _P]),
     "omt_bn_backward": (_I, [_A, _A, _A, _A, _I, _I, _I, _I, _P, _P, _P, _P, _F, _U, _P]),
+    "omt_bn_backward_add": (_I, [_A, _A, _A, _A, _A, _I, _I, _I, _I, _P, _P, _P, _P, _F, _U, _P]),
     "omt_pool2_fwd": (_I, [_A, _A, _P, _I, _I, _I, _I, _P]),
     "omt_pool2_bwd": (_I, [_A, _P, _A, _I, _I, _I, _I, _P]),
     "omt_avgpool2_fwd": (_I, [_A, _A, _I, _I, _I, _I, _P]),

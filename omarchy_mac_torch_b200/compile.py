@@ -4,7 +4,9 @@ Dynamo captures the model and AOTAutograd lowers it to aten graphs for forward a
 those graphs to the fused `omt::` ops, and the graph runs op by op on the device:
 
   1. training BatchNorm2d followed by ReLU            -> omt.bn_relu_train
+     training BatchNorm2d, + identity branch, ReLU    -> omt.bn_add_relu_train (the tail of a residual block)
   2. threshold_backward -> native_batch_norm_backward -> omt.bn_relu_backward (ReLU mask folded into the BN backward)
+     the same where the masked gradient also feeds the identity branch -> omt.bn_add_relu_backward
   3. conv -> [eval BatchNorm] -> [ReLU]               -> omt.conv_act / omt.conv_bn_act_eval
 
 These are passes 1-3 of the reference's omarchy_mac_torch/compile.py:69-161. Its pass 4 (pointwise chains compiled to
@@ -87,6 +89,76 @@ def fuse_bn_relu(graph):
     return done
 
 
+def _same_shape(a, b):
+    va, vb = _meta(a), _meta(b)
+    return isinstance(va, torch.Tensor) and isinstance(vb, torch.Tensor) and va.shape == vb.shape and va.dtype == vb.dtype
+
+
+def fuse_bn_add_relu(graph):
+    """bn(x) + other -> relu, with the BatchNorm output and the sum used nowhere else."""
+    done = 0
+    for bn in list(graph.nodes):
+        if not _is(bn, aten._native_batch_norm_legit_functional.default):
+            continue
+        x, w, b, rm, rv, training, momentum, eps = bn.args[:8]
+        if not training or None in (w, b, rm, rv) or not _f32_4d(x):
+            continue
+        y = _items(bn).get(0)
+        add = _sole_user(y) if y is not None else None
+        if not _is(add, aten.add.Tensor) or len(add.args) != 2 or add.kwargs.get("alpha", 1) != 1:
+            continue
+        other = add.args[1] if add.args[0] is y else add.args[0]
+        if other is y or not isinstance(other, Node) or not _same_shape(other, y):
+            continue
+        relu = _sole_user(add)
+        if not _is(relu, aten.relu.default):
+            continue
+        # `other` may be computed after the BatchNorm (a downsample branch): the fused node goes where the add was, so every
+        # other consumer of the BatchNorm's outputs (batch statistics, running statistics) has to come after that point
+        order = {n: i for i, n in enumerate(graph.nodes)}
+        rest = {idx: gi for idx, gi in _items(bn).items() if idx != 0}
+        if any(order[u] < order[add] for gi in rest.values() for u in gi.users):
+            continue
+        with graph.inserting_before(add):
+            fused = graph.call_function(omt.bn_add_relu_train.default, (x, other, w, b, rm, rv, momentum, eps))
+        relu.replace_all_uses_with(_getitem_after(graph, relu, fused, 0, relu.meta))
+        for idx, gi in rest.items():
+            gi.replace_all_uses_with(_getitem_after(graph, relu, fused, idx, gi.meta))
+        for dead in [relu, add, y] + list(rest.values()) + [bn]:
+            graph.erase_node(dead)
+        done += 1
+    return done
+
+
+def fuse_bn_add_relu_backward(graph):
+    """native_batch_norm_backward of a ReLU-masked gradient whose masked form is used elsewhere too (the identity branch)."""
+    done = 0
+    for bw in list(graph.nodes):
+        if not _is(bw, aten.native_batch_norm_backward.default):
+            continue
+        g, x, w, _rm, _rv, mean, invstd, train, _eps, mask = bw.args[:10]
+        if not train or w is None or not _f32_4d(x):
+            continue
+        if not (_is(g, aten.threshold_backward.default) and g.args[2] == 0 and len(g.users) > 1):
+            continue
+        gout, y = g.args[0], g.args[1]
+        if not _same_shape(y, x):
+            continue
+        with graph.inserting_before(g):
+            fused = graph.call_function(omt.bn_add_relu_backward.default, (gout, x, y, w, mean, invstd, list(mask)))
+        with graph.inserting_after(fused):
+            dres = graph.call_function(operator.getitem, (fused, 3))
+        dres.meta = dict(g.meta)
+        for idx, gi in _items(bw).items():
+            gi.replace_all_uses_with(_getitem_after(graph, gi, fused, idx, gi.meta))
+            graph.erase_node(gi)
+        graph.erase_node(bw)
+        g.replace_all_uses_with(dres)
+        graph.erase_node(g)
+        done += 1
+    return done
+
+
 def fuse_bn_relu_backward(graph):
     done = 0
     for bw in list(graph.nodes):
@@ -154,7 +226,8 @@ def fuse_conv_epilogues(graph):
 def rewrite(gm):
     """Apply the three passes to a GraphModule in place; returns {pass: rewrites}."""
     g = gm.graph
-    stats = {"bn_relu": fuse_bn_relu(g), "bn_relu_backward": fuse_bn_relu_backward(g), "conv_epilogue": fuse_conv_epilogues(g)}
+    stats = {"bn_relu": fuse_bn_relu(g), "bn_add_relu": fuse_bn_add_relu(g), "bn_relu_backward": fuse_bn_relu_backward(g),
+             "bn_add_relu_backward": fuse_bn_add_relu_backward(g), "conv_epilogue": fuse_conv_epilogues(g)}
     g.eliminate_dead_code()
     g.lint()
     gm.recompile()

@@ -173,22 +173,23 @@ __global__ void __launch_bounds__(256) bn_bwd_fin(const float* __restrict__ part
 // ---------------------------------------------------------------------------------------------------------------
 struct BnEw {
   const float* x; const float* g; const float* y; float* out;
+  const float* res;  // KIND 0/1: optional residual added before the ReLU (same layout as x)
+  float* gz;         // KIND 2 with RELU: optional second output, the ReLU-masked incoming gradient
   const float* mean; const float* inv; const float* gamma; const float* beta; const float* dgb;
   float eps, m;
   int c, hw;
   int64_t total;
 };
 
+// gv: KIND 2 the (already masked) incoming gradient; KIND 0/1 the residual value (0 without one)
 template <int KIND, bool RELU>
-__device__ __forceinline__ float bn_ew_one(const BnEw& a, float xv, float gv, float yv, float mean, float inv, float ga, float be,
-                                           float dg, float db) {
+__device__ __forceinline__ float bn_ew_one(const BnEw& a, float xv, float gv, float mean, float inv, float ga, float be, float dg, float db) {
   if (KIND <= 1) {
-    float r = (xv - mean) * inv * ga + be;
+    float r = (xv - mean) * inv * ga + be + gv;
     return RELU ? fmaxf(r, 0.f) : r;
   } else {
-    float gz = RELU ? (yv > 0.f ? gv : 0.f) : gv;
     float xhat = (xv - mean) * inv;
-    return ga * inv / a.m * (a.m * gz - db - xhat * dg);
+    return ga * inv / a.m * (a.m * gv - db - xhat * dg);
   }
 }
 
@@ -196,10 +197,16 @@ template <int KIND, bool RELU, bool NHWC>
 __global__ void __launch_bounds__(256) bn_ew_vec4(BnEw a) {
   int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
   if (i >= a.total) return;
-  float4 xv = __ldg(reinterpret_cast<const float4*>(a.x + i)), gv = xv, yv = xv, o;
+  float4 xv = __ldg(reinterpret_cast<const float4*>(a.x + i)), gv = make_float4(0.f, 0.f, 0.f, 0.f), o;
   if (KIND == 2) {
     gv = __ldg(reinterpret_cast<const float4*>(a.g + i));
-    if (RELU) yv = __ldg(reinterpret_cast<const float4*>(a.y + i));
+    if (RELU) {
+      const float4 yv = __ldg(reinterpret_cast<const float4*>(a.y + i));
+      gv.x = yv.x > 0.f ? gv.x : 0.f; gv.y = yv.y > 0.f ? gv.y : 0.f; gv.z = yv.z > 0.f ? gv.z : 0.f; gv.w = yv.w > 0.f ? gv.w : 0.f;
+      if (a.gz) *reinterpret_cast<float4*>(a.gz + i) = gv;
+    }
+  } else if (a.res) {
+    gv = __ldg(reinterpret_cast<const float4*>(a.res + i));
   }
   if (NHWC) {
     int ch = a.total < 0x7fffffffll ? (int)((uint32_t)i % (uint32_t)a.c) : (int)(i % a.c);
@@ -209,20 +216,20 @@ __global__ void __launch_bounds__(256) bn_ew_vec4(BnEw a) {
     if (KIND <= 1) be = __ldg(reinterpret_cast<const float4*>(a.beta + ch));
     if (KIND == 1) { inv.x = rsqrtf(inv.x + a.eps); inv.y = rsqrtf(inv.y + a.eps); inv.z = rsqrtf(inv.z + a.eps); inv.w = rsqrtf(inv.w + a.eps); }
     if (KIND == 2) { dg = __ldg(reinterpret_cast<const float4*>(a.dgb + ch)); db = __ldg(reinterpret_cast<const float4*>(a.dgb + a.c + ch)); }
-    o.x = bn_ew_one<KIND, RELU>(a, xv.x, gv.x, yv.x, mean.x, inv.x, ga.x, be.x, dg.x, db.x);
-    o.y = bn_ew_one<KIND, RELU>(a, xv.y, gv.y, yv.y, mean.y, inv.y, ga.y, be.y, dg.y, db.y);
-    o.z = bn_ew_one<KIND, RELU>(a, xv.z, gv.z, yv.z, mean.z, inv.z, ga.z, be.z, dg.z, db.z);
-    o.w = bn_ew_one<KIND, RELU>(a, xv.w, gv.w, yv.w, mean.w, inv.w, ga.w, be.w, dg.w, db.w);
+    o.x = bn_ew_one<KIND, RELU>(a, xv.x, gv.x, mean.x, inv.x, ga.x, be.x, dg.x, db.x);
+    o.y = bn_ew_one<KIND, RELU>(a, xv.y, gv.y, mean.y, inv.y, ga.y, be.y, dg.y, db.y);
+    o.z = bn_ew_one<KIND, RELU>(a, xv.z, gv.z, mean.z, inv.z, ga.z, be.z, dg.z, db.z);
+    o.w = bn_ew_one<KIND, RELU>(a, xv.w, gv.w, mean.w, inv.w, ga.w, be.w, dg.w, db.w);
   } else {
     int ch = a.total < 0x7fffffffll ? (int)(((uint32_t)i / (uint32_t)a.hw) % (uint32_t)a.c) : (int)((i / a.hw) % a.c);
     float mean = __ldg(a.mean + ch), inv = __ldg(a.inv + ch), ga = __ldg(a.gamma + ch), be = 0.f, dg = 0.f, db = 0.f;
     if (KIND <= 1) be = __ldg(a.beta + ch);
     if (KIND == 1) inv = rsqrtf(inv + a.eps);
     if (KIND == 2) { dg = __ldg(a.dgb + ch); db = __ldg(a.dgb + a.c + ch); }
-    o.x = bn_ew_one<KIND, RELU>(a, xv.x, gv.x, yv.x, mean, inv, ga, be, dg, db);
-    o.y = bn_ew_one<KIND, RELU>(a, xv.y, gv.y, yv.y, mean, inv, ga, be, dg, db);
-    o.z = bn_ew_one<KIND, RELU>(a, xv.z, gv.z, yv.z, mean, inv, ga, be, dg, db);
-    o.w = bn_ew_one<KIND, RELU>(a, xv.w, gv.w, yv.w, mean, inv, ga, be, dg, db);
+    o.x = bn_ew_one<KIND, RELU>(a, xv.x, gv.x, mean, inv, ga, be, dg, db);
+    o.y = bn_ew_one<KIND, RELU>(a, xv.y, gv.y, mean, inv, ga, be, dg, db);
+    o.z = bn_ew_one<KIND, RELU>(a, xv.z, gv.z, mean, inv, ga, be, dg, db);
+    o.w = bn_ew_one<KIND, RELU>(a, xv.w, gv.w, mean, inv, ga, be, dg, db);
   }
   *reinterpret_cast<float4*>(a.out + i) = o;
 }
@@ -232,10 +239,14 @@ __global__ void __launch_bounds__(256) bn_ew_scalar(BnEw a, bool nhwc) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= a.total) return;
   int ch = nhwc ? (int)(i % a.c) : (int)((i / a.hw) % a.c);
-  float xv = __ldg(a.x + i), gv = KIND == 2 ? __ldg(a.g + i) : 0.f, yv = (KIND == 2 && RELU) ? __ldg(a.y + i) : 0.f;
+  float xv = __ldg(a.x + i), gv = KIND == 2 ? __ldg(a.g + i) : (a.res ? __ldg(a.res + i) : 0.f);
+  if (KIND == 2 && RELU) {
+    if (!(__ldg(a.y + i) > 0.f)) gv = 0.f;
+    if (a.gz) a.gz[i] = gv;
+  }
   float inv = __ldg(a.inv + ch);
   if (KIND == 1) inv = rsqrtf(inv + a.eps);
-  a.out[i] = bn_ew_one<KIND, RELU>(a, xv, gv, yv, __ldg(a.mean + ch), inv, __ldg(a.gamma + ch), KIND <= 1 ? __ldg(a.beta + ch) : 0.f,
+  a.out[i] = bn_ew_one<KIND, RELU>(a, xv, gv, __ldg(a.mean + ch), inv, __ldg(a.gamma + ch), KIND <= 1 ? __ldg(a.beta + ch) : 0.f,
                                    KIND == 2 ? __ldg(a.dgb + ch) : 0.f, KIND == 2 ? __ldg(a.dgb + a.c + ch) : 0.f);
 }
 
@@ -243,7 +254,7 @@ template <int KIND>
 static int launch_ew(const BnEw& a, bool relu, bool nhwc, cudaStream_t s, const char* name) {
   bool vec = nhwc ? (a.c % 4 == 0) : (a.hw % 4 == 0);
   vec = vec && ((reinterpret_cast<uintptr_t>(a.x) | reinterpret_cast<uintptr_t>(a.out) | reinterpret_cast<uintptr_t>(a.g) |
-                 reinterpret_cast<uintptr_t>(a.y)) & 15) == 0;
+                 reinterpret_cast<uintptr_t>(a.y) | reinterpret_cast<uintptr_t>(a.res) | reinterpret_cast<uintptr_t>(a.gz)) & 15) == 0;
   if (nhwc)  // per-channel tables are read as float4 too
     vec = vec && ((reinterpret_cast<uintptr_t>(a.mean) | reinterpret_cast<uintptr_t>(a.inv) | reinterpret_cast<uintptr_t>(a.gamma) |
                    reinterpret_cast<uintptr_t>(a.beta) | reinterpret_cast<uintptr_t>(a.dgb)) & 15) == 0;
@@ -353,15 +364,22 @@ int omt_bn_stats_from_sums(const float* sums, int64_t count, int32_t c, float* m
   return check_launch("bn_stats_from_sums");
 }
 
-int omt_bn_apply(const OmtAct* x, const OmtAct* y, int32_t n, int32_t c, int32_t h, int32_t w, const float* mean,
-                 const float* invstd, const float* gamma, const float* beta, uint32_t flags, omt_stream_t stream) {
+int omt_bn_apply_add(const OmtAct* x, const OmtAct* res, const OmtAct* y, int32_t n, int32_t c, int32_t h, int32_t w, const float* mean,
+                     const float* invstd, const float* gamma, const float* beta, uint32_t flags, omt_stream_t stream) {
   OMT_REQUIRE(x && y && x->p && y->p && mean && invstd && gamma && beta, "omt_bn_apply: bad arguments");
   int lay = layout_of(x, c, h, w);
   OMT_REQUIRE(lay >= 0 && layout_of(y, c, h, w) == lay, "omt_bn_apply: x and y must share an NCHW or NHWC contiguous layout");
+  const bool has_res = res && res->p;
+  OMT_REQUIRE(!has_res || layout_of(res, c, h, w) == lay, "omt_bn_apply_add: the residual must have the layout of x");
   BnEw a{};
   a.x = x->p; a.g = x->p; a.y = x->p; a.out = y->p; a.mean = mean; a.inv = invstd; a.gamma = gamma; a.beta = beta;
+  a.res = has_res ? res->p : nullptr;
   a.c = c; a.hw = h * w; a.total = (int64_t)n * c * h * w;
-  return launch_ew<0>(a, flags & OMT_BN_RELU, lay == 1, st(stream), "bn_apply");
+  return launch_ew<0>(a, flags & OMT_BN_RELU, lay == 1, st(stream), has_res ? "bn_apply_add" : "bn_apply");
+}
+int omt_bn_apply(const OmtAct* x, const OmtAct* y, int32_t n, int32_t c, int32_t h, int32_t w, const float* mean,
+                 const float* invstd, const float* gamma, const float* beta, uint32_t flags, omt_stream_t stream) {
+  return omt_bn_apply_add(x, nullptr, y, n, c, h, w, mean, invstd, gamma, beta, flags, stream);
 }
 
 int omt_bn_eval(const OmtAct* x, const OmtAct* y, int32_t n, int32_t c, int32_t h, int32_t w, const float* rm,
@@ -378,7 +396,14 @@ int omt_bn_eval(const OmtAct* x, const OmtAct* y, int32_t n, int32_t c, int32_t 
 int omt_bn_backward(const OmtAct* gy, const OmtAct* x, const OmtAct* y, const OmtAct* dx, int32_t n, int32_t c, int32_t h,
                     int32_t w, const float* mean, const float* invstd, const float* gamma, float* dgb, float scale,
                     uint32_t flags, omt_stream_t stream) {
+  return omt_bn_backward_add(gy, x, y, dx, nullptr, n, c, h, w, mean, invstd, gamma, dgb, scale, flags, stream);
+}
+int omt_bn_backward_add(const OmtAct* gy, const OmtAct* x, const OmtAct* y, const OmtAct* dx, const OmtAct* dres, int32_t n, int32_t c,
+                        int32_t h, int32_t w, const float* mean, const float* invstd, const float* gamma, float* dgb, float scale,
+                        uint32_t flags, omt_stream_t stream) {
   bool relu = flags & OMT_BN_RELU;
+  const bool has_dres = dres && dres->p;
+  OMT_REQUIRE(!has_dres || (relu && dx && dx->p), "omt_bn_backward_add: the masked gradient is written by the ReLU-masked dx pass");
   OMT_REQUIRE(gy && x && gy->p && x->p && mean && invstd && gamma && dgb, "omt_bn_backward: bad arguments");
   OMT_REQUIRE(!relu || (y && y->p), "omt_bn_backward: the ReLU mask needs y");
   int lay = layout_of(x, c, h, w);
@@ -399,9 +424,11 @@ int omt_bn_backward(const OmtAct* gy, const OmtAct* x, const OmtAct* y, const Om
   r = check_launch("bn_bwd_fin");
   if (r || !dx || !dx->p) return r;
   BnEw a{};
+  OMT_REQUIRE(!has_dres || layout_of(dres, c, h, w) == lay, "omt_bn_backward_add: dres must have the layout of x");
   a.x = x->p; a.g = gy->p; a.y = relu ? y->p : x->p; a.out = dx->p; a.mean = mean; a.inv = invstd; a.gamma = gamma; a.dgb = raw;
+  a.gz = has_dres ? dres->p : nullptr;
   a.m = (float)((int64_t)n * h * w); a.c = c; a.hw = h * w; a.total = (int64_t)n * c * h * w;
-  return launch_ew<2>(a, relu, lay == 1, st(stream), "bn_bwd_apply");
+  return launch_ew<2>(a, relu, lay == 1, st(stream), has_dres ? "bn_bwd_apply_add" : "bn_bwd_apply");
 }
 
 }  // extern "C"

@@ -861,11 +861,12 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
 // window mode (win_ks > 0): column of (c, ky, kx) is (ky*win_kb + kx/8)*32 + (kx%8)*4 + c, kcols = win_ks*win_kb*32
 __global__ void __launch_bounds__(256) wgrad_tc_reduce_kernel(const float* __restrict__ part, float* __restrict__ dw, int co, int ci, int kk,
                                                               int cpad, int slices, float scale, int win_ks, int win_kb) {
+  // threads run over (o, tap, c) with c fastest: the slab reads coalesce; the strided writes are 1/slices of the traffic
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t total = (int64_t)co * ci * kk;
   if (i >= total) return;
-  const int tap = (int)(i % kk);
-  const int c = (int)((i / kk) % ci);
+  const int c = (int)(i % ci);
+  const int tap = (int)((i / ci) % kk);
   const int o = (int)(i / ((int64_t)kk * ci));
   int64_t kcols = (int64_t)kk * cpad, col = (int64_t)tap * cpad + c;
   if (win_ks) {
@@ -877,7 +878,7 @@ __global__ void __launch_bounds__(256) wgrad_tc_reduce_kernel(const float* __res
   const float* p = part + (int64_t)o * kcols + col;
   float s = 0.f;
   for (int z = 0; z < slices; z++) s += __ldg(p + z * slab);
-  dw[i] = s * scale;
+  dw[((int64_t)o * ci + c) * kk + tap] = s * scale;
 }
 
 // ---------------------------------------------------------------------------------------------------------------------

@@ -3,6 +3,9 @@
 //
 //   omt::bn_relu_train      training BatchNorm2d + ReLU: statistics, then normalise + ReLU in one pass
 //   omt::bn_relu_backward   its backward: ReLU mask folded into the BN backward reductions and apply
+//   omt::bn_add_relu_train / omt::bn_add_relu_backward   the same pair across a residual add (BatchNorm, + identity, ReLU):
+//                           the forward reads the identity branch in the apply pass, the backward also returns the masked
+//                           gradient that flows into the identity branch
 //   omt::conv_act           conv2d + bias + optional ReLU in the GEMM epilogue
 //   omt::conv_bn_act_eval   eval conv2d + BatchNorm (folded into the conv's weights and bias) + optional ReLU
 //   omt::fused_pointwise    declared for schema parity; generated pointwise kernels are not built in this library
@@ -21,6 +24,17 @@ static std::tuple<Tensor, Tensor, Tensor> bn_relu_backward_ref(const Tensor& g, 
                                                                const Tensor& mean, const Tensor& invstd, std::array<bool, 3> mask) {
   Tensor gz = at::threshold_backward(g, y, 0);
   return at::native_batch_norm_backward(gz, x, w, std::nullopt, std::nullopt, mean, invstd, true, 0.0, mask);
+}
+static std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> bn_add_relu_train_ref(const Tensor& x, const Tensor& res, const Tensor& w, const Tensor& b,
+                                                                              const Tensor& rm, const Tensor& rv, double mom, double eps) {
+  auto r = at::_native_batch_norm_legit_functional(x, w, b, rm, rv, true, mom, eps);
+  return {at::relu(std::get<0>(r) + res), std::get<1>(r), std::get<2>(r), std::get<3>(r), std::get<4>(r)};
+}
+static std::tuple<Tensor, Tensor, Tensor, Tensor> bn_add_relu_backward_ref(const Tensor& g, const Tensor& x, const Tensor& y, const Tensor& w,
+                                                                           const Tensor& mean, const Tensor& invstd, std::array<bool, 3> mask) {
+  Tensor gz = at::threshold_backward(g, y, 0);
+  auto r = at::native_batch_norm_backward(gz, x, w, std::nullopt, std::nullopt, mean, invstd, true, 0.0, mask);
+  return {std::get<0>(r), std::get<1>(r), std::get<2>(r), gz};
 }
 static Tensor conv_act_ref(const Tensor& x, const Tensor& w, const std::optional<Tensor>& b, IntArrayRef stride, IntArrayRef padding, int64_t act_) {
   Tensor y = at::convolution(x, w, b, stride, padding, {1, 1}, false, {0, 0}, 1);
@@ -47,11 +61,13 @@ static Tensor fused_pointwise_ref(c10::string_view, at::TensorList) {
 static bool whole(const Tensor& t) { return f32(t) && t.is_contiguous(); }
 
 // mean and invstd are returned as two halves of one buffer (the reference's contract, csrc/fused.cpp:65-67)
-static std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> bn_relu_train_dev(const Tensor& x_, const Tensor& w, const Tensor& b, const Tensor& rm,
-                                                                          const Tensor& rv, double mom, double eps) {
+static std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> bn_res_relu_train(const Tensor& x_, const Tensor* res_, const Tensor& w, const Tensor& b,
+                                                                          const Tensor& rm, const Tensor& rv, double mom, double eps) {
   NEED(f32(x_) && x_.dim() == 4 && x_.numel() > 0 && whole(w) && whole(b) && whole(rm) && whole(rv), "4-D float32 with contiguous parameters");
+  NEED(!res_ || (f32(*res_) && res_->sizes() == x_.sizes()), "residual of the activation's shape");
   Tensor x = dense4(x_);
   if (layout4(x) == 1 && x.size(1) % 4 != 0) x = to_layout(x, 0);
+  Tensor res = res_ ? to_layout(*res_, layout4(x)) : Tensor();
   const int n = (int)x.size(0), c = (int)x.size(1), h = (int)x.size(2), wd = (int)x.size(3);
   Tensor nrm = empty_dev({c}, at::kFloat), nrv = empty_dev({c}, at::kFloat), stats = empty_dev({3 * (int64_t)c}, at::kFloat);
   Tensor y = dense4(empty_dev(x.sizes(), at::kFloat, layout4(x) == 1));
@@ -60,27 +76,51 @@ static std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> bn_relu_train_dev(cons
   check(omt_bn_stats(&ax, n, c, h, wd, s, s + 2 * c, s + c, fptr(rm), fptr(rv), fptr(nrm), fptr(nrv), (float)mom, (float)eps, OMT_BN_FUNCTIONAL,
                      cur_stream()),
         "bn_relu_train statistics");
-  check(omt_bn_apply(&ax, &ay, n, c, h, wd, s, s + c, fptr(w), fptr(b), OMT_BN_RELU, cur_stream()), "bn_relu_train apply");
+  OmtAct ar = res_ ? act(res) : null_act();
+  check(omt_bn_apply_add(&ax, &ar, &ay, n, c, h, wd, s, s + c, fptr(w), fptr(b), OMT_BN_RELU, cur_stream()), "bn_relu_train apply");
   return {y, stats.narrow(0, 0, c), stats.narrow(0, c, c), nrm, nrv};
 }
+static std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> bn_relu_train_dev(const Tensor& x, const Tensor& w, const Tensor& b, const Tensor& rm,
+                                                                          const Tensor& rv, double mom, double eps) {
+  return bn_res_relu_train(x, nullptr, w, b, rm, rv, mom, eps);
+}
+static std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> bn_add_relu_train_dev(const Tensor& x, const Tensor& res, const Tensor& w, const Tensor& b,
+                                                                              const Tensor& rm, const Tensor& rv, double mom, double eps) {
+  return bn_res_relu_train(x, &res, w, b, rm, rv, mom, eps);
+}
 
-static std::tuple<Tensor, Tensor, Tensor> bn_relu_backward_dev(const Tensor& g_, const Tensor& x_, const Tensor& y_, const Tensor& w,
-                                                               const Tensor& mean_, const Tensor& invstd_, std::array<bool, 3> mask) {
+static std::tuple<Tensor, Tensor, Tensor, Tensor> bn_res_relu_backward(const Tensor& g_, const Tensor& x_, const Tensor& y_, const Tensor& w,
+                                                                       const Tensor& mean_, const Tensor& invstd_, std::array<bool, 3> mask,
+                                                                       bool want_dres) {
   NEED(f32(g_) && f32(x_) && f32(y_) && x_.dim() == 4 && x_.numel() > 0 && whole(w) && f32(mean_) && f32(invstd_), "4-D float32");
   Tensor x = dense4(x_);
   if (layout4(x) == 1 && x.size(1) % 4 != 0) x = to_layout(x, 0);
   const int lay = layout4(x);
   Tensor g = to_layout(g_, lay), y = to_layout(y_, lay), mean = contig(mean_), inv = contig(invstd_);
   const int n = (int)x.size(0), c = (int)x.size(1), h = (int)x.size(2), wd = (int)x.size(3);
-  Tensor dgb = empty_dev({2, c}, at::kFloat), gx;
-  OmtAct ag = act(g), ax = act(x), ay = act(y), adx = null_act();
-  if (mask[0]) {
+  Tensor dgb = empty_dev({2, c}, at::kFloat), gx, gres;
+  OmtAct ag = act(g), ax = act(x), ay = act(y), adx = null_act(), adr = null_act();
+  if (mask[0] || want_dres) {  // the masked gradient is a by-product of the dx pass
     gx = dense4(empty_dev(x.sizes(), at::kFloat, lay == 1));
     adx = act(gx);
   }
-  check(omt_bn_backward(&ag, &ax, &ay, &adx, n, c, h, wd, fptr(mean), fptr(inv), fptr(w), dgb.data_ptr<float>(), 1.f, OMT_BN_RELU, cur_stream()),
+  if (want_dres) {
+    gres = dense4(empty_dev(x.sizes(), at::kFloat, lay == 1));
+    adr = act(gres);
+  }
+  check(omt_bn_backward_add(&ag, &ax, &ay, &adx, &adr, n, c, h, wd, fptr(mean), fptr(inv), fptr(w), dgb.data_ptr<float>(), 1.f, OMT_BN_RELU,
+                            cur_stream()),
         "bn_relu_backward");
-  return {gx, mask[1] ? dgb.select(0, 0) : Tensor(), mask[2] ? dgb.select(0, 1) : Tensor()};
+  return {mask[0] ? gx : Tensor(), mask[1] ? dgb.select(0, 0) : Tensor(), mask[2] ? dgb.select(0, 1) : Tensor(), gres};
+}
+static std::tuple<Tensor, Tensor, Tensor> bn_relu_backward_dev(const Tensor& g, const Tensor& x, const Tensor& y, const Tensor& w, const Tensor& mean,
+                                                               const Tensor& invstd, std::array<bool, 3> mask) {
+  auto r = bn_res_relu_backward(g, x, y, w, mean, invstd, mask, false);
+  return {std::get<0>(r), std::get<1>(r), std::get<2>(r)};
+}
+static std::tuple<Tensor, Tensor, Tensor, Tensor> bn_add_relu_backward_dev(const Tensor& g, const Tensor& x, const Tensor& y, const Tensor& w,
+                                                                           const Tensor& mean, const Tensor& invstd, std::array<bool, 3> mask) {
+  return bn_res_relu_backward(g, x, y, w, mean, invstd, mask, true);
 }
 
 static Tensor conv_act_dev(const Tensor& x_, const Tensor& w_, const std::optional<Tensor>& b, IntArrayRef stride, IntArrayRef padding, int64_t act_) {
@@ -129,6 +169,8 @@ static auto dev_or_composite(const char* name, const A&... a) {
 TORCH_LIBRARY(omt, m) {
   m.def("bn_relu_train(Tensor x, Tensor w, Tensor b, Tensor rm, Tensor rv, float momentum, float eps) -> (Tensor, Tensor, Tensor, Tensor, Tensor)");
   m.def("bn_relu_backward(Tensor g, Tensor x, Tensor y, Tensor w, Tensor mean, Tensor invstd, bool[3] mask) -> (Tensor, Tensor, Tensor)");
+  m.def("bn_add_relu_train(Tensor x, Tensor res, Tensor w, Tensor b, Tensor rm, Tensor rv, float momentum, float eps) -> (Tensor, Tensor, Tensor, Tensor, Tensor)");
+  m.def("bn_add_relu_backward(Tensor g, Tensor x, Tensor y, Tensor w, Tensor mean, Tensor invstd, bool[3] mask) -> (Tensor, Tensor, Tensor, Tensor)");
   m.def("conv_act(Tensor x, Tensor w, Tensor? b, int[] stride, int[] padding, int act) -> Tensor");
   m.def("conv_bn_act_eval(Tensor x, Tensor cw, Tensor? cb, Tensor w, Tensor b, Tensor rm, Tensor rv, float eps, int[] stride, int[] padding, int act) -> Tensor");
   m.def("fused_pointwise(str kernel, Tensor[] inputs) -> Tensor");
@@ -136,6 +178,8 @@ TORCH_LIBRARY(omt, m) {
 TORCH_LIBRARY_IMPL(omt, CompositeExplicitAutograd, m) {
   m.impl("bn_relu_train", &bn_relu_train_ref);
   m.impl("bn_relu_backward", &bn_relu_backward_ref);
+  m.impl("bn_add_relu_train", &bn_add_relu_train_ref);
+  m.impl("bn_add_relu_backward", &bn_add_relu_backward_ref);
   m.impl("conv_act", &conv_act_ref);
   m.impl("conv_bn_act_eval", &conv_bn_act_eval_ref);
   m.impl("fused_pointwise", &fused_pointwise_ref);
@@ -147,6 +191,14 @@ TORCH_LIBRARY_IMPL(omt, PrivateUse1, m) {
   m.impl("bn_relu_backward", [](const Tensor& g, const Tensor& x, const Tensor& y, const Tensor& w, const Tensor& mean, const Tensor& invstd,
                                 std::array<bool, 3> mask) {
     return dev_or_composite<&bn_relu_backward_dev, &bn_relu_backward_ref>("bn_relu_backward", g, x, y, w, mean, invstd, mask);
+  });
+  m.impl("bn_add_relu_train", [](const Tensor& x, const Tensor& res, const Tensor& w, const Tensor& b, const Tensor& rm, const Tensor& rv, double mom,
+                                 double eps) {
+    return dev_or_composite<&bn_add_relu_train_dev, &bn_add_relu_train_ref>("bn_add_relu_train", x, res, w, b, rm, rv, mom, eps);
+  });
+  m.impl("bn_add_relu_backward", [](const Tensor& g, const Tensor& x, const Tensor& y, const Tensor& w, const Tensor& mean, const Tensor& invstd,
+                                    std::array<bool, 3> mask) {
+    return dev_or_composite<&bn_add_relu_backward_dev, &bn_add_relu_backward_ref>("bn_add_relu_backward", g, x, y, w, mean, invstd, mask);
   });
   m.impl("conv_act", [](const Tensor& x, const Tensor& w, const std::optional<Tensor>& b, IntArrayRef s, IntArrayRef p, int64_t a) {
     return dev_or_composite<&conv_act_dev, &conv_act_ref>("conv_act", x, w, b, s, p, a);

@@ -138,6 +138,67 @@ __global__ void __launch_bounds__(256) maxpool_bwd_kernel(PoolArgs a, const int6
   a.y.p[a.y.off(img, ch, y, xx)] = acc;
 }
 
+// Channels-last, 4 channels per thread (c % 4 == 0, dense tensors): 128-bit loads and stores, two 128-bit index accesses.
+// x / gx are [n, ih, iw, c], y / gy / idx are [n, oh, ow, c].
+__global__ void __launch_bounds__(256) maxpool_fwd_nhwc4_kernel(PoolArgs a, int64_t* __restrict__ idx) {
+  const int c4 = a.c >> 2;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (int64_t)a.n * a.oh * a.ow * c4) return;
+  int img, cq, oy, ox;
+  decode4<true>(i, c4, a.oh, a.ow, img, cq, oy, ox);
+  const float* xp = a.x.p + ((int64_t)img * a.ih * a.iw) * a.c + cq * 4;
+  float best[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+  int bi[4] = {-1, -1, -1, -1};
+  bool done[4] = {false, false, false, false};
+  for (int ky = 0; ky < a.p.kh; ky++) {
+    const int y = oy * a.p.sh + ky * a.p.dh - a.p.ph;
+    if (y < 0 || y >= a.ih) continue;
+    for (int kx = 0; kx < a.p.kw; kx++) {
+      const int xx = ox * a.p.sw + kx * a.p.dw - a.p.pw;
+      if (xx < 0 || xx >= a.iw) continue;
+      const float4 v4 = __ldg(reinterpret_cast<const float4*>(xp + ((int64_t)y * a.iw + xx) * a.c));
+      const float v[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+      for (int k = 0; k < 4; k++) {
+        const bool nan = isnan_bits(v[k]);
+        if (!done[k] && (bi[k] < 0 || nan || v[k] > best[k])) {
+          best[k] = v[k]; bi[k] = y * a.iw + xx;
+          done[k] = nan;  // the first NaN of the window wins
+        }
+      }
+    }
+  }
+  const int64_t o = (((int64_t)img * a.oh + oy) * a.ow + ox) * a.c + cq * 4;
+  *reinterpret_cast<float4*>(a.y.p + o) = make_float4(best[0], best[1], best[2], best[3]);
+  longlong2* ip = reinterpret_cast<longlong2*>(idx + o);
+  ip[0] = make_longlong2(bi[0], bi[1]);
+  ip[1] = make_longlong2(bi[2], bi[3]);
+}
+__global__ void __launch_bounds__(256) maxpool_bwd_nhwc4_kernel(PoolArgs a, const int64_t* __restrict__ idx) {
+  // a.x = gy, a.y = gx
+  const int c4 = a.c >> 2;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (int64_t)a.n * a.ih * a.iw * c4) return;
+  int img, cq, y, xx;
+  decode4<true>(i, c4, a.ih, a.iw, img, cq, y, xx);
+  const int ylo = max(0, (y + a.p.ph - (a.p.kh - 1) * a.p.dh + a.p.sh - 1) / a.p.sh), yhi = min(a.oh - 1, (y + a.p.ph) / a.p.sh);
+  const int xlo = max(0, (xx + a.p.pw - (a.p.kw - 1) * a.p.dw + a.p.sw - 1) / a.p.sw), xhi = min(a.ow - 1, (xx + a.p.pw) / a.p.sw);
+  const long long me = (long long)y * a.iw + xx;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int oy = ylo; oy <= yhi; oy++)
+    for (int ox = xlo; ox <= xhi; ox++) {
+      const int64_t o = (((int64_t)img * a.oh + oy) * a.ow + ox) * a.c + cq * 4;
+      const longlong2* ip = reinterpret_cast<const longlong2*>(idx + o);
+      const longlong2 i0 = __ldg(ip), i1 = __ldg(ip + 1);
+      const float4 g = __ldg(reinterpret_cast<const float4*>(a.x.p + o));
+      if (i0.x == me) acc[0] += g.x;
+      if (i0.y == me) acc[1] += g.y;
+      if (i1.x == me) acc[2] += g.z;
+      if (i1.y == me) acc[3] += g.w;
+    }
+  *reinterpret_cast<float4*>(a.y.p + (((int64_t)img * a.ih + y) * a.iw + xx) * a.c + cq * 4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+}
+
 // ---- general average pool (aten divisor rules) ----
 __device__ __forceinline__ float avg_div(const PoolArgs& a, int oy, int ox) {
   if (a.divisor) return (float)a.divisor;
@@ -238,6 +299,9 @@ static int pool_check(const OmtPool* p, const char* who) {
   return OMT_OK;
 }
 
+static inline bool aligned16(const void* a, const void* b, const void* c) {
+  return ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c)) & 15) == 0;
+}
 #define LAUNCH_BY_LAYOUT(kern, nhwc, total, s, ...)                                      \
   do {                                                                                   \
     unsigned blocks_ = (unsigned)cdiv((total), 256);                                     \
@@ -290,6 +354,11 @@ int omt_maxpool_fwd(const OmtAct* x, const OmtAct* y, int64_t* idx, int32_t n, i
   int r = pool_check(p, "omt_maxpool_fwd");
   if (r) return r;
   OMT_REQUIRE(x && y && x->p && y->p && idx && n > 0 && c > 0 && oh > 0 && ow > 0, "omt_maxpool_fwd: bad arguments");
+  if (c % 4 == 0 && is_nhwc(x, c, ih, iw) && is_nhwc(y, c, oh, ow) && aligned16(x->p, y->p, idx)) {
+    const int64_t total = (int64_t)n * oh * ow * (c / 4);
+    maxpool_fwd_nhwc4_kernel<<<(unsigned)cdiv(total, 256), 256, 0, st(stream)>>>(pa(x, y, n, c, ih, iw, oh, ow, p, 0, 0), idx);
+    return check_launch("maxpool_fwd_nhwc4");
+  }
   LAUNCH_BY_LAYOUT(maxpool_fwd_kernel, chan_last(y), (int64_t)n * c * oh * ow, st(stream), pa(x, y, n, c, ih, iw, oh, ow, p, 0, 0), idx);
   return check_launch("maxpool_fwd");
 }
@@ -298,6 +367,11 @@ int omt_maxpool_bwd(const OmtAct* gy, const int64_t* idx, const OmtAct* gx, int3
   int r = pool_check(p, "omt_maxpool_bwd");
   if (r) return r;
   OMT_REQUIRE(gy && gx && gy->p && gx->p && idx && n > 0 && c > 0 && oh > 0 && ow > 0, "omt_maxpool_bwd: bad arguments");
+  if (c % 4 == 0 && is_nhwc(gy, c, oh, ow) && is_nhwc(gx, c, ih, iw) && aligned16(gy->p, gx->p, idx)) {
+    const int64_t total = (int64_t)n * ih * iw * (c / 4);
+    maxpool_bwd_nhwc4_kernel<<<(unsigned)cdiv(total, 256), 256, 0, st(stream)>>>(pa(gy, gx, n, c, ih, iw, oh, ow, p, 0, 0), idx);
+    return check_launch("maxpool_bwd_nhwc4");
+  }
   LAUNCH_BY_LAYOUT(maxpool_bwd_kernel, chan_last(gx), (int64_t)n * c * ih * iw, st(stream), pa(gy, gx, n, c, ih, iw, oh, ow, p, 0, 0),
                    idx);
   return check_launch("maxpool_bwd");

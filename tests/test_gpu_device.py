@@ -324,12 +324,60 @@ def test_omt_ops_device_vs_composite(omt):
     db = omt_ops.bn_relu_backward(g.to(D), x.to(D), dev[0], w.to(D), dev[1], dev[2], [True, True, True])
     for r, d in zip(rb, db):
         assert e(d, r) <= TOL
+    # the residual-block variants, in NCHW and (8 channels) channels-last
+    for xs, cl in ((x, False), (torch.randn(4, 8, 6, 5) * 2 + 1, True)):
+        c = xs.shape[1]
+        w_, b_, rm_, rv_ = torch.randn(c), torch.randn(c), torch.randn(c), torch.rand(c) + 0.5
+        res, g_ = torch.randn_like(xs), torch.randn_like(xs)
+        fmt = torch.channels_last if cl else torch.contiguous_format
+        xd, resd, gd = (t.to(D).contiguous(memory_format=fmt) for t in (xs, res, g_))
+        ref = omt_ops.bn_add_relu_train(xs, res, w_, b_, rm_, rv_, 0.1, 1e-5)
+        dev = omt_ops.bn_add_relu_train(xd, resd, *(t.to(D) for t in (w_, b_, rm_, rv_)), 0.1, 1e-5)
+        for r, d in zip(ref, dev):
+            assert e(d, r) <= TOL
+        rb = omt_ops.bn_add_relu_backward(g_, xs, ref[0], w_, ref[1], ref[2], [True, True, True])
+        db = omt_ops.bn_add_relu_backward(gd, xd, dev[0], w_.to(D), dev[1], dev[2], [True, True, True])
+        assert len(db) == 4
+        for r, d in zip(rb, db):
+            assert e(d, r) <= TOL
     cw, cb = torch.randn(5, 6, 3, 3) * 0.2, torch.randn(5)
     assert e(omt_ops.conv_act(x.to(D), cw.to(D), cb.to(D), [1, 1], [1, 1], 1), omt_ops.conv_act(x, cw, cb, [1, 1], [1, 1], 1)) <= TOL
     w5, b5, rm5, rv5 = torch.randn(5), torch.randn(5), torch.randn(5), torch.rand(5) + 0.5
     r = omt_ops.conv_bn_act_eval(x, cw, cb, w5, b5, rm5, rv5, 1e-5, [2, 2], [1, 1], 1)
     d = omt_ops.conv_bn_act_eval(*(t.to(D) for t in (x, cw, cb, w5, b5, rm5, rv5)), 1e-5, [2, 2], [1, 1], 1)
     assert e(d, r) <= TOL
+    assert not omt.FALLBACKS, dict(omt.FALLBACKS)
+
+
+def test_compile_backend_residual_blocks(omt):
+    """torch.compile(backend="omarchy_mac_torch") on a residual network: the BatchNorm -> + identity -> ReLU tails and their
+    backward run as the fused device ops, and one training step's gradients match the CPU's eager run."""
+    from omarchy_mac_torch_b200 import models
+    from omarchy_mac_torch_b200.native import core
+    torch.manual_seed(0)
+    ref = models.ResNet18(num_classes=10)
+    mod = copy.deepcopy(ref).to(D)
+    cmod = torch.compile(mod, backend="omarchy_mac_torch")
+    x, y = torch.randn(8, 3, 64, 64), torch.randint(0, 10, (8,))
+    omt.FALLBACKS.clear()
+    core.kernel_counts(True)
+    core.bridge_counts(True)
+    l1 = F.cross_entropy(ref(x), y); l1.backward()
+    l2 = F.cross_entropy(cmod(x.to(D)), y.to(D)); l2.backward()
+    kc, bc = core.kernel_counts(True), core.bridge_counts(True)
+    assert kc.get("bn_apply_add", 0) == 8 and kc.get("bn_bwd_apply_add", 0) == 8
+    assert not any(k.startswith(("relu", "threshold_backward")) for k in bc), bc  # no separate ReLU kernels left
+    assert abs(l1.item() - l2.item()) <= 1e-4 * abs(l1.item())
+    # Gradients against the same model run eagerly on the device (whose ops the other tests hold against the CPU): a
+    # whole-network comparison with the CPU is at the mercy of single ReLU inputs that sit within rounding of zero (one
+    # flipped mask among a layer's 32 values per channel moves that layer's BatchNorm gradients by 10 %).
+    eager = copy.deepcopy(ref).to(D)
+    eager.zero_grad()
+    F.cross_entropy(eager(x.to(D)), y.to(D)).backward()
+    for a, b in zip(eager.parameters(), mod.parameters()):
+        assert e(b.grad, a.grad) <= 1e-4
+    for a, b in zip(ref.buffers(), mod.buffers()):
+        assert e(b.float(), a.float()) <= 1e-4
     assert not omt.FALLBACKS, dict(omt.FALLBACKS)
 
 

@@ -97,6 +97,21 @@ def test_fx_passes_rewrite_and_preserve_results(pkg, monkeypatch):
         out = torch.compile(mod, backend=backend)(x)
         assert torch.allclose(out, ref(x), rtol=1e-4, atol=1e-5)
     assert sum(s["conv_epilogue"] for s in seen) == 3  # conv -> eval BN -> ReLU folded three times
+    # residual blocks: BatchNorm -> + identity -> ReLU (with and without a downsample branch) and its backward
+    seen.clear()
+    torch._dynamo.reset()
+    torch.manual_seed(1)
+    ref = models.ResNet18(num_classes=10)
+    mod = copy.deepcopy(ref)
+    x, y = torch.randn(4, 3, 32, 32), torch.randint(0, 10, (4,))
+    F.cross_entropy(ref(x), y).backward()
+    F.cross_entropy(torch.compile(mod, backend=backend)(x), y).backward()
+    assert sum(s["bn_add_relu"] for s in seen) == 8 and sum(s["bn_add_relu_backward"] for s in seen) == 8
+    assert sum(s["bn_relu"] for s in seen) == 9 and sum(s["bn_relu_backward"] for s in seen) == 9
+    for a, b in zip(ref.parameters(), mod.parameters()):
+        assert (a.grad - b.grad).abs().max() <= 1e-4 * a.grad.abs().max() + 1e-7
+    for a, b in zip(ref.buffers(), mod.buffers()):
+        assert torch.allclose(a.float(), b.float(), rtol=1e-5, atol=1e-6)
 
 
 def test_model_definitions_reproduce_reference_curves(pkg, golden_losses):
