@@ -175,13 +175,16 @@ CONV = {
 
 class Train:
     metric, unit, higher = "train_ms_per_step", "ms/step", False
-    compile = True  # --eager switches to the plain nn.Module call
+    # compile=True: call the model through torch.compile(backend="omarchy_mac_torch") (fused BatchNorm/ReLU/residual graphs);
+    # the small, launch-bound workloads are faster through the eager nn.Module call with the Sequential auto-fuse.
+    # --eager / --compile override.
 
-    def __init__(self, name, make_model, shape, classes, make_opt, cpu_batch, note):
+    def __init__(self, name, make_model, shape, classes, make_opt, cpu_batch, note, compile=False):
+        self.compile = compile
         self.name, self.make_model, self.in_shape, self.classes, self.make_opt = name, make_model, shape, classes, make_opt
         self.cpu_batch = min(cpu_batch, shape[0])
         self.shape = {"batch_per_gpu": shape[0], "input": list(shape[1:]), "classes": classes, "optimizer": note,
-                      "api": 'torch.compile(model, backend="omarchy_mac_torch")'}
+                      "api": 'torch.compile(model, backend="omarchy_mac_torch")' if compile else "eager nn.Module"}
 
     def host_inputs(self, seed, batch=None):
         g = torch.Generator().manual_seed(1000 + seed)
@@ -294,7 +297,8 @@ TRAIN = {
     "mobilenetv3": lambda: Train("mobilenetv3_small_b32_train", lambda: _models().MobileNetV3SE(), (32, 3, 224, 224), 1000,
                                  lambda p: torch.optim.AdamW(p, lr=1e-3, weight_decay=0.01), 32, "AdamW lr 1e-3 wd .01"),
     "resnet50": lambda: Train("resnet50_b256_train", lambda: _models().ResNet50(), (256, 3, 224, 224), 1000,
-                              _sgd(0.1, momentum=0.9, nesterov=True, weight_decay=1e-4), 16, "SGD lr .1 momentum .9 nesterov wd 1e-4"),
+                              _sgd(0.1, momentum=0.9, nesterov=True, weight_decay=1e-4), 16, "SGD lr .1 momentum .9 nesterov wd 1e-4",
+                              compile=True),
 }
 
 WORKLOADS = {**CONV, **TRAIN}
@@ -383,14 +387,15 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--eager", action="store_true", help="training workloads: call the nn.Module directly instead of through the compile backend")
+    ap.add_argument("--compile", action="store_true", help="training workloads: call the model through the compile backend")
     ap.add_argument("--profile-step", action="store_true",
                     help="for ncu --profile-from-start off: after the warm-up run ONE step between cudaProfilerStart/Stop and exit")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     wl = WORKLOADS[args.workload]()
-    if args.eager and isinstance(wl, Train):
-        wl.compile = False
-        wl.shape["api"] = "eager nn.Module"
+    if (args.eager or args.compile) and isinstance(wl, Train):
+        wl.compile = args.compile and not args.eager
+        wl.shape["api"] = 'torch.compile(model, backend="omarchy_mac_torch")' if wl.compile else "eager nn.Module"
     if args.impl == "reference":
         return run_reference(args, wl)
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
