@@ -124,6 +124,29 @@ __global__ void __launch_bounds__(256) strided_copy_kernel(ActView src, ActView 
 
 using namespace omt;
 
+// An NCHW-contiguous operand that the tensor-core path would take if it were channels-last: copy it into scratch from the
+// library's allocator (one transpose pass) when that is what stands between the call and the tensor cores. Only without a
+// caller workspace: omt_conv_workspace_bytes does not see layouts.
+struct ClCopy {
+  Scratch sc;
+  OmtAct act{};
+  bool made = false;
+  int make(const OmtAct* a, int n, int c, int h, int w, omt_stream_t stream) {
+    int r = sc.get(nullptr, 0, (size_t)n * c * h * w * sizeof(float), stream);
+    if (r) return r;
+    act.p = (float*)sc.p; act.sc = 1; act.sw = c; act.sh = (int64_t)w * c; act.sn = (int64_t)h * w * c;
+    made = true;
+    return omt_act_copy(a, &act, n, c, h, w, stream);
+  }
+};
+static bool could_be_cl(const OmtAct* a, int c, int h, int w) { return a && a->p && c % 4 == 0 && is_nchw(a, c, h, w) && !is_nhwc(a, c, h, w); }
+static OmtAct as_cl(const OmtAct* a, int c, int h, int w) {  // what the copy would look like (for the eligibility test)
+  OmtAct r = *a;
+  r.p = reinterpret_cast<float*>(256);  // aligned placeholder: only strides and alignment are inspected
+  r.sc = 1; r.sw = c; r.sh = (int64_t)w * c; r.sn = (int64_t)h * w * c;
+  return r;
+}
+
 extern "C" {
 
 size_t omt_conv_workspace_bytes(int kind, const OmtConvGeo* g, uint32_t flags) {
@@ -141,8 +164,18 @@ int omt_conv_fwd(const OmtConvGeo* g, const OmtAct* x, const float* w, const flo
   OMT_REQUIRE(!(flags & OMT_EPI_BIAS) || bias, "omt_conv_fwd: OMT_EPI_BIAS without a bias pointer");
   OMT_REQUIRE(!(flags & OMT_EPI_BNSTATS) || stats, "omt_conv_fwd: OMT_EPI_BNSTATS without a stats pointer");
   bool tc = !(flags & OMT_FORCE_SIMT) && tc_supported(0, g, x, y);
-  OMT_REQUIRE(tc || !(flags & OMT_FORCE_TC), "omt_conv_fwd: geometry/layout not covered by the tensor-core path");
   CallTimer timer(0, g, st(stream));
+  ClCopy xc;
+  if (!tc && !(flags & (OMT_FORCE_SIMT | OMT_FORCE_TC)) && !workspace && could_be_cl(x, g->ci, g->ih, g->iw)) {
+    OmtAct probe = as_cl(x, g->ci, g->ih, g->iw);
+    if (tc_supported(0, g, &probe, y)) {
+      r = xc.make(x, g->n, g->ci, g->ih, g->iw, stream);
+      if (r) return r;
+      x = &xc.act;
+      tc = true;
+    }
+  }
+  OMT_REQUIRE(tc || !(flags & OMT_FORCE_TC), "omt_conv_fwd: geometry/layout not covered by the tensor-core path");
   OMT_REQUIRE(tc || !(flags & OMT_EPI_BNSTATS), "omt_conv_fwd: OMT_EPI_BNSTATS needs the tensor-core path");
   if (!tc) return simt_conv_fwd(g, x, w, bias, y, flags, st(stream));
   Scratch sc;
@@ -157,8 +190,18 @@ int omt_conv_dgrad(const OmtConvGeo* g, const OmtAct* gy, const float* w, const 
   if (r) return r;
   OMT_REQUIRE(gy && dx && gy->p && dx->p && w, "omt_conv_dgrad: null pointer");
   bool tc = !(flags & OMT_FORCE_SIMT) && tc_supported(1, g, gy, dx);
-  OMT_REQUIRE(tc || !(flags & OMT_FORCE_TC), "omt_conv_dgrad: geometry/layout not covered by the tensor-core path");
   CallTimer timer(1, g, st(stream));
+  ClCopy gc;
+  if (!tc && !(flags & (OMT_FORCE_SIMT | OMT_FORCE_TC)) && !workspace && could_be_cl(gy, g->co, g->oh, g->ow)) {
+    OmtAct probe = as_cl(gy, g->co, g->oh, g->ow);
+    if (tc_supported(1, g, &probe, dx)) {
+      r = gc.make(gy, g->n, g->co, g->oh, g->ow, stream);
+      if (r) return r;
+      gy = &gc.act;
+      tc = true;
+    }
+  }
+  OMT_REQUIRE(tc || !(flags & OMT_FORCE_TC), "omt_conv_dgrad: geometry/layout not covered by the tensor-core path");
   if (!tc) return simt_conv_dgrad(g, gy, w, dx, st(stream));
   Scratch sc;
   r = sc.get(workspace, workspace_bytes, tc_workspace(1, g), stream);
@@ -172,8 +215,29 @@ int omt_conv_wgrad(const OmtConvGeo* g, const OmtAct* x, const OmtAct* gy, float
   if (r) return r;
   OMT_REQUIRE(x && gy && x->p && gy->p && dw, "omt_conv_wgrad: null pointer");
   bool tc = !(flags & OMT_FORCE_SIMT) && tc_supported(2, g, x, gy);
-  OMT_REQUIRE(tc || !(flags & OMT_FORCE_TC), "omt_conv_wgrad: geometry/layout not covered by the tensor-core path");
   CallTimer timer(2, g, st(stream));
+  ClCopy xc, gc;
+  if (!tc && !(flags & (OMT_FORCE_SIMT | OMT_FORCE_TC)) && !workspace) {
+    const bool cx = could_be_cl(x, g->ci, g->ih, g->iw), cg = could_be_cl(gy, g->co, g->oh, g->ow);
+    OmtAct px = cx ? as_cl(x, g->ci, g->ih, g->iw) : *x, pg = cg ? as_cl(gy, g->co, g->oh, g->ow) : *gy;
+    if ((cx || cg) && tc_supported(2, g, &px, &pg)) {
+      // a window-mode x (<= 4 channels) is staged by the kernel itself; everything else has to be channels-last
+      OmtAct only_g = *x;
+      const bool x_needed = cx && !tc_supported(2, g, &only_g, &pg);
+      if (x_needed) {
+        r = xc.make(x, g->n, g->ci, g->ih, g->iw, stream);
+        if (r) return r;
+        x = &xc.act;
+      }
+      if (cg) {
+        r = gc.make(gy, g->n, g->co, g->oh, g->ow, stream);
+        if (r) return r;
+        gy = &gc.act;
+      }
+      tc = true;
+    }
+  }
+  OMT_REQUIRE(tc || !(flags & OMT_FORCE_TC), "omt_conv_wgrad: geometry/layout not covered by the tensor-core path");
   Scratch sc;
   r = sc.get(workspace, workspace_bytes, tc ? tc_workspace(2, g) : simt_wgrad_workspace(g), stream);
   if (r) return r;

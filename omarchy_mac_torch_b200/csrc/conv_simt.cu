@@ -360,7 +360,100 @@ int simt_conv_fwd(const OmtConvGeo* g, const OmtAct* x, const float* w, const fl
   return launch_gemm<Fwd>(a, a.M, a.N, 1, s, "conv_fwd_simt");
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// Input gradient for <= 4 input channels (a network's first layer): the GEMM would have N = ci <= 4 columns, so instead
+// one thread owns one input pixel and all its channels. A block works on one stride phase (py, px) of one image: every
+// thread then needs the same filter taps (ky = ky0 + s*ty, kx = kx0 + s*tx; the phase algebra of csrc/conv.cpp:78-95),
+// whose weights sit in shared memory as float4 per (tap, co) and are read as warp-wide broadcasts, while consecutive
+// lanes read consecutive output pixels of gy.
+// ---------------------------------------------------------------------------------------------------------------------
+struct DgSmallArgs {
+  ActView gy, dx;
+  const float* w;
+  int n, ci, co, ih, iw, oh, ow, ks, stride, pad;
+};
+
+__global__ void __launch_bounds__(128) dgrad_small_ci_kernel(DgSmallArgs a) {
+  extern __shared__ float4 wsm[];  // [jy * jx][co]
+  const int s = a.stride;
+  const int py = blockIdx.y / s, px = blockIdx.y - py * s, img = blockIdx.z;
+  const int hi = (a.ih - py + s - 1) / s, wi = (a.iw - px + s - 1) / s;  // pixels of this phase
+  const int ky0 = (py + a.pad) % s, kx0 = (px + a.pad) % s;
+  const int jy = ky0 < a.ks ? (a.ks - ky0 + s - 1) / s : 0, jx = kx0 < a.ks ? (a.ks - kx0 + s - 1) / s : 0;
+  const int taps = jy * jx;
+  for (int i = threadIdx.x; i < taps * a.co; i += blockDim.x) {
+    const int t = i / a.co, o = i - t * a.co;
+    const int ky = ky0 + s * (t / jx), kx = kx0 + s * (t % jx);
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int c = 0; c < a.ci; c++) v[c] = __ldg(a.w + (((int64_t)o * a.ci + c) * a.ks + ky) * a.ks + kx);
+    wsm[i] = make_float4(v[0], v[1], v[2], v[3]);
+  }
+  __syncthreads();
+  const int p = blockIdx.x * blockDim.x + threadIdx.x;
+  if (p >= hi * wi) return;
+  const int yi = p / wi, xi = p - yi * wi;
+  const int y = py + s * yi, x = px + s * xi;
+  // output pixel reached through tap (ty, tx): oy = (y + pad - ky) / s = qy - ty with qy = (y + pad - ky0) / s
+  const int qy = (y + a.pad - ky0) / s, qx = (x + a.pad - kx0) / s;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  const bool vec = a.gy.sc == 1 && (a.co & 3) == 0 && ((reinterpret_cast<uintptr_t>(a.gy.p) & 15) == 0) && (a.gy.sw & 3) == 0 &&
+                   (a.gy.sh & 3) == 0 && (a.gy.sn & 3) == 0;
+  for (int ty = 0; ty < jy; ty++) {
+    const int oy = qy - ty;
+    if (oy < 0 || oy >= a.oh) continue;
+    for (int tx = 0; tx < jx; tx++) {
+      const int ox = qx - tx;
+      if (ox < 0 || ox >= a.ow) continue;
+      const float4* wt = wsm + (ty * jx + tx) * a.co;
+      const float* gp = a.gy.p + a.gy.off(img, 0, oy, ox);
+      if (vec) {
+        for (int o = 0; o < a.co; o += 4) {
+          const float4 g4 = __ldg(reinterpret_cast<const float4*>(gp + o));
+          const float gv[4] = {g4.x, g4.y, g4.z, g4.w};
+#pragma unroll
+          for (int k = 0; k < 4; k++) {
+            const float4 wv = wt[o + k];
+            acc[0] = fmaf(gv[k], wv.x, acc[0]); acc[1] = fmaf(gv[k], wv.y, acc[1]);
+            acc[2] = fmaf(gv[k], wv.z, acc[2]); acc[3] = fmaf(gv[k], wv.w, acc[3]);
+          }
+        }
+      } else {
+#pragma unroll 4
+        for (int o = 0; o < a.co; o++) {
+          const float gv = __ldg(gp + (int64_t)o * a.gy.sc);
+          const float4 wv = wt[o];
+          acc[0] = fmaf(gv, wv.x, acc[0]); acc[1] = fmaf(gv, wv.y, acc[1]);
+          acc[2] = fmaf(gv, wv.z, acc[2]); acc[3] = fmaf(gv, wv.w, acc[3]);
+        }
+      }
+    }
+  }
+  float* out = a.dx.p + a.dx.off(img, 0, y, x);
+  for (int c = 0; c < a.ci; c++) out[(int64_t)c * a.dx.sc] = acc[c];
+}
+
+bool dgrad_small_ci_ok(const OmtConvGeo* g) {
+  if (g->ci > 4 || g->groups != 1 || g->n > 65535 || g->stride * g->stride > 65535) return false;
+  const int jmax = (int)cdiv(g->ks, g->stride);
+  return (size_t)jmax * jmax * g->co * sizeof(float4) <= 200 * 1024;
+}
+int dgrad_small_ci(const OmtConvGeo* g, const OmtAct* gy, const float* w, const OmtAct* dx, cudaStream_t s) {
+  DgSmallArgs a{view(gy), view(dx), w, g->n, g->ci, g->co, g->ih, g->iw, g->oh, g->ow, g->ks, g->stride, g->pad};
+  const int jmax = (int)cdiv(g->ks, g->stride);
+  const size_t smem = (size_t)jmax * jmax * g->co * sizeof(float4);
+  static size_t attr = 0;
+  if (smem > 48 * 1024 && smem > attr) {
+    OMT_CUDA(cudaFuncSetAttribute(dgrad_small_ci_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attr = smem;
+  }
+  const int64_t per_phase = cdiv(g->ih, g->stride) * cdiv(g->iw, g->stride);
+  dim3 grid((unsigned)cdiv(per_phase, 128), (unsigned)(g->stride * g->stride), (unsigned)g->n);
+  dgrad_small_ci_kernel<<<grid, 128, smem, s>>>(a);
+  return check_launch("conv_dgrad_small_ci");
+}
+
 int simt_conv_dgrad(const OmtConvGeo* g, const OmtAct* gy, const float* w, const OmtAct* dx, cudaStream_t s) {
+  if (dgrad_small_ci_ok(g)) return dgrad_small_ci(g, gy, w, dx, s);
   ConvArgs a = base_args(g);
   a.a = view(gy); a.b = view(dx); a.w = w;
   int st_ = g->stride;

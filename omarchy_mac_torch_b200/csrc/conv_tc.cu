@@ -1064,7 +1064,9 @@ WgPlan plan_wgrad(const OmtConvGeo* g) {
     total_blocks = (int64_t)w.tiles_x * w.tiles_y * cdiv(g->n, w.bn_img);
   }
   w.total_blocks = (int)total_blocks;
-  const int64_t want = std::max<int64_t>(1, (3 * sm_count()) / tiles);
+  // one wave of CTAs: a CTA's fixed cost (TMEM allocation, first loads, 128 KB partial tile written and summed later) is
+  // worth 5-10 k-blocks, so fewer and longer split-K slices win over finer load balance (measured with 1-4 waves)
+  const int64_t want = std::max<int64_t>(1, sm_count() / tiles);
   const int64_t slices = std::max<int64_t>(1, std::min<int64_t>(want, total_blocks / 8));
   w.blocks_per_slice = (int)cdiv(total_blocks, slices);
   w.slices = (int)cdiv(total_blocks, w.blocks_per_slice);

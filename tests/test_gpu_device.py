@@ -44,7 +44,7 @@ def test_storage_semantics(omt):
     assert back.device.type == D and torch.equal(back.cpu(), x)
     assert torch.equal(xd.view(torch.int32).cpu(), x.view(torch.int32))
     assert torch.equal(xd.t()[1:3].contiguous().cpu(), x.t()[1:3].contiguous())
-    assert xd.sum().item() == pytest.approx(x.sum().item(), rel=1e-5)
+    assert xd.sum().item() == pytest.approx(x.sum().item(), rel=1e-5, abs=1e-5 * x.abs().sum().item())
     y = torch.arange(10, device=D)
     assert y.dtype == torch.int64 and y.cpu().tolist() == list(range(10))
     torch.manual_seed(3)
