@@ -169,6 +169,102 @@ CONV = {
 }
 
 
+class HbmKernels:
+    """The bandwidth-bound kernels of the path, each on tensors far larger than L2, through the C ABI: achieved GB/s =
+    algorithmic bytes / CUDA-event time. `value` is the geometric mean over the kernels; `roofline` reports the slowest."""
+    name = "hbm_bound_kernels"
+    metric, unit, higher = "hbm_kernels_gbs", "GB/s", True
+    shape = dict(bn="256x64x112x112 channels-last", depthwise="128x96x56x56 3x3 channels-last", optimizer="64M parameters in 160 tensors")
+    h2d_bytes = d2h_bytes = 0
+
+    def setup_gpu(self, seed, world=1):
+        from omarchy_mac_torch_b200 import capi
+        self.capi = capi
+        capi.lib()
+        torch.manual_seed(seed)
+        cl = torch.channels_last
+        x = torch.randn(256, 64, 112, 112, device="cuda").contiguous(memory_format=cl)
+        g = torch.randn_like(x)
+        c = x.shape[1]
+        gamma, beta, rm, rv = torch.rand(c, device="cuda") + 0.5, torch.randn(c, device="cuda"), torch.zeros(c, device="cuda"), torch.ones(c, device="cuda")
+        mean, var, inv = (torch.empty(c, device="cuda") for _ in range(3))
+        y = torch.empty_like(x)
+        dx = torch.empty_like(x)
+        dgb = torch.empty(2, c, device="cuda")
+        n, _, h, w = x.shape
+        A, P, sh = capi.act, capi.ptr, capi.stream_handle
+        ne = x.numel()
+        xd = torch.randn(128, 96, 56, 56, device="cuda").contiguous(memory_format=cl)
+        wd = torch.randn(96, 1, 3, 3, device="cuda")
+        gd = torch.randn_like(xd)
+        nd = xd.numel()
+        params = [torch.randn(400_000, device="cuda") for _ in range(160)]
+        grads = [torch.randn_like(t) for t in params]
+        ms_ = [torch.zeros_like(t) for t in params]
+        vs_ = [torch.zeros_like(t) for t in params]
+        steps = [torch.zeros((), device="cuda") for _ in params]
+        npar = sum(t.numel() for t in params)
+        call = capi.call
+        self.keep = (x, g, y, dx, xd, gd, params, grads, ms_, vs_, steps)
+        self.kernels = {
+            # name: (callable, algorithmic bytes)
+            "bn_statistics": (lambda: call("omt_bn_stats", A(x), n, c, h, w, P(mean), P(var), P(inv), P(rm), P(rv), None, None, 0.1, 1e-5, 0, sh()), 4 * ne),
+            "bn_apply_relu": (lambda: call("omt_bn_apply", A(x), A(y), n, c, h, w, P(mean), P(inv), P(gamma), P(beta), capi.BN_RELU, sh()), 8 * ne),
+            "bn_backward_relu": (lambda: call("omt_bn_backward", A(g), A(x), A(y), A(dx), n, c, h, w, P(mean), P(inv), P(gamma), P(dgb), 1.0, capi.BN_RELU, sh()), 24 * ne),
+            "depthwise_fwd": (lambda: capi.dw_fwd(xd, wd, None, 1, 1, cl=True), 8 * nd),
+            "depthwise_dgrad": (lambda: capi.dw_dgrad(gd, wd, (56, 56), 1, 1, cl=True), 8 * nd),
+            "depthwise_wgrad": (lambda: capi.dw_wgrad(xd, gd, 3, 1, 1), 8 * nd),
+            "maxpool3x3s2_fwd": (lambda: capi.maxpool_fwd(x, 3, 2, 1), 4 * ne + 12 * (ne // 4)),
+            "sgd_momentum": (lambda: capi.sgd(params, grads, ms_, 0.1, momentum=0.9, weight_decay=1e-4), 20 * npar),
+            "adamw": (lambda: capi.adam(params, grads, ms_, vs_, steps, 1e-3, weight_decay=0.01, decoupled=True), 28 * npar),
+        }
+        self.bytes_resident = 1 << 40
+        self.results = {}
+
+    def step(self):
+        for fn, _ in self.kernels.values():
+            fn()
+
+    e2e_step = step
+
+    def measure(self, reps=10):
+        for name, (fn, nbytes) in self.kernels.items():
+            for _ in range(3):
+                fn()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(reps):
+                fn()
+            b.record()
+            torch.cuda.synchronize()
+            ms = a.elapsed_time(b) / reps
+            self.results[name] = {"ms": ms, "gbs": nbytes / ms / 1e6, "bytes": nbytes}
+
+    def value(self, ms):
+        if not self.results:
+            self.measure()
+        return float(np.exp(np.mean([np.log(r["gbs"]) for r in self.results.values()])))
+
+    def roofline(self, ms, peaks):
+        if not self.results:
+            self.measure()
+        peak = peaks["hbm_gbs"]
+        worst = min(self.results, key=lambda k: self.results[k]["gbs"])
+        return {"bound": "hbm", "achieved": self.results[worst]["gbs"], "peak": peak, "unit": "GB/s", "frac": self.results[worst]["gbs"] / peak,
+                "traffic": None, "kernel": worst, "peak_source": f"{peaks['source']} copy bandwidth",
+                "per_kernel": {k: {"gbs": round(r["gbs"], 1), "frac": round(r["gbs"] / peak, 3), "ms": round(r["ms"], 4)} for k, r in self.results.items()}}
+
+    def cpu_setup(self):
+        return None
+
+    def cpu_step(self, ins):
+        x = torch.randn(16, 64, 112, 112)
+        torch.nn.functional.batch_norm(x, None, None, training=True)
+
+    def cpu_scale(self):
+        return 1.0
+
+
 # ---------------------------------------------------------------------------------------------------------------------
 # training workloads on the "omarchy_mac_torch" device
 # ---------------------------------------------------------------------------------------------------------------------
@@ -301,7 +397,7 @@ TRAIN = {
                               compile=True),
 }
 
-WORKLOADS = {**CONV, **TRAIN}
+WORKLOADS = {**CONV, **TRAIN, "hbm": HbmKernels}
 
 
 def dist_setup(n):
@@ -393,6 +489,8 @@ def main():
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     wl = WORKLOADS[args.workload]()
+    if args.workload == "hbm":
+        args.no_cpu_baseline = True  # a per-kernel bandwidth table has no single CPU counterpart
     if (args.eager or args.compile) and isinstance(wl, Train):
         wl.compile = args.compile and not args.eager
         wl.shape["api"] = 'torch.compile(model, backend="omarchy_mac_torch")' if wl.compile else "eager nn.Module"
