@@ -53,6 +53,7 @@ enum {
   OMT_EPI_BIAS = 1,        /* y += bias[co]          (reference hb bit 0, omarchy_mac_torch/gemm.py:37) */
   OMT_EPI_RELU = 2,        /* y = max(y, 0)          (reference hb bit 1, omarchy_mac_torch/gemm.py:38) */
   OMT_EPI_BNSTATS = 4,     /* also accumulate per-channel sum / sum of squares of y into stats[2*co] (must be zeroed) */
+  OMT_EPI_ACCUM = 8,       /* omt_conv_dgrad: dx += result (gradient of a tensor with a second consumer, e.g. a residual branch) */
   OMT_FORCE_SIMT = 0x100,  /* skip the tcgen05 path (used by tests to cross-check the two paths) */
   OMT_FORCE_TC = 0x200     /* fail with OMT_EINVAL instead of taking the SIMT path */
 };
@@ -120,7 +121,9 @@ int omt_conv_fwd(const OmtConvGeo* g, const OmtAct* x, const float* w, const flo
 
 /* dx[n,ci,ih,iw] = conv^T(gy, w). Any stride 1..4: strided convs are split into stride^2 phases, each a dense
  * GEMM over the taps that land on it, batched in one launch. Replaces gemm_grad_input (csrc/conv.cpp:78-100) and
- * kinds 1 and 5 (omarchy_mac_torch/gemm.py:43-80). */
+ * kinds 1 and 5 (omarchy_mac_torch/gemm.py:43-80). With OMT_EPI_ACCUM the result is added to what dx holds (autograd's
+ * accumulation of a second gradient into the same tensor, done in the epilogue); only the tensor-core path does that:
+ * other geometries return OMT_EINVAL and the caller adds separately. */
 int omt_conv_dgrad(const OmtConvGeo* g, const OmtAct* gy, const float* w, const OmtAct* dx, uint32_t flags,
                    void* workspace, size_t workspace_bytes, omt_stream_t stream);
 

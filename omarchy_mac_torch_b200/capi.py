@@ -10,7 +10,7 @@ _HERE = pathlib.Path(__file__).resolve().parent
 LIB_PATH = _HERE / "lib" / "libomt_b200.so"
 
 # flags (include/omt_b200.h)
-EPI_BIAS, EPI_RELU, EPI_BNSTATS, FORCE_SIMT, FORCE_TC = 1, 2, 4, 0x100, 0x200
+EPI_BIAS, EPI_RELU, EPI_BNSTATS, EPI_ACCUM, FORCE_SIMT, FORCE_TC = 1, 2, 4, 8, 0x100, 0x200
 BN_RELU, BN_FUNCTIONAL = 1, 2
 
 
@@ -211,11 +211,14 @@ def conv_fwd(x, w, bias=None, stride=1, pad=0, flags=0, cl=False, stats=None):
     return y
 
 
-def conv_dgrad(gy, w, in_hw, stride=1, pad=0, flags=0, cl=False):
+def conv_dgrad(gy, w, in_hw, stride=1, pad=0, flags=0, cl=False, acc=None):
+    """acc: a tensor to accumulate into (EPI_ACCUM) instead of a fresh output"""
     n, co = gy.shape[:2]
     _, ci, ks, _ = w.shape
     g = geo(n, ci, co, in_hw[0], in_hw[1], ks, stride, pad)
-    dx = _empty((n, ci, in_hw[0], in_hw[1]), gy, cl)
+    dx = acc if acc is not None else _empty((n, ci, in_hw[0], in_hw[1]), gy, cl)
+    if acc is not None:
+        flags |= EPI_ACCUM
     call("omt_conv_dgrad", g, act(gy), ptr(w), act(dx), flags, None, 0, stream_handle())
     return dx
 

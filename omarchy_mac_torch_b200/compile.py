@@ -8,6 +8,8 @@ those graphs to the fused `omt::` ops, and the graph runs op by op on the device
   2. threshold_backward -> native_batch_norm_backward -> omt.bn_relu_backward (ReLU mask folded into the BN backward)
      the same where the masked gradient also feeds the identity branch -> omt.bn_add_relu_backward
   3. conv -> [eval BatchNorm] -> [ReLU]               -> omt.conv_act / omt.conv_bn_act_eval
+  +  add(convolution_backward(...)[0], g) with g a gradient nobody else reads -> omt.conv_backward_acc (the input
+     gradient is accumulated into g by the conv epilogue: the joins of residual branches in the backward graph)
 
 These are passes 1-3 of the reference's omarchy_mac_torch/compile.py:69-161. Its pass 4 (pointwise chains compiled to
 generated shader source) is not part of this build. Every fused op has a composite definition in plain aten ops, so a
@@ -178,6 +180,47 @@ def fuse_bn_relu_backward(graph):
     return done
 
 
+def _fresh_gradient(n):
+    """A tensor this graph produced for exactly one consumer, so it may be accumulated into in place."""
+    if not (_is(n, operator.getitem) and len(n.users) == 1):
+        return False
+    src, idx = n.args
+    return ((_is(src, omt.bn_add_relu_backward.default) and idx == 3) or (_is(src, aten.convolution_backward.default) and idx == 0)
+            or (_is(src, omt.conv_backward_acc.default) and idx == 0) or (_is(src, omt.bn_relu_backward.default) and idx == 0)
+            or (_is(src, omt.bn_add_relu_backward.default) and idx == 0))
+
+
+def fuse_dgrad_accumulate(graph):
+    done = 0
+    for add in list(graph.nodes):
+        if not _is(add, aten.add.Tensor) or len(add.args) != 2 or add.kwargs.get("alpha", 1) != 1:
+            continue
+        for a, b in ((add.args[0], add.args[1]), (add.args[1], add.args[0])):
+            if not (_is(a, operator.getitem) and a.args[1] == 0 and len(a.users) == 1 and _is(a.args[0], aten.convolution_backward.default)):
+                continue
+            cb = a.args[0]
+            gy, x, w, _bias_sizes, stride, padding, dilation, transposed, _outpad, groups, mask = cb.args[:11]
+            if transposed or groups != 1 or list(dilation) != [1, 1] or not mask[0] or mask[2] or not _f32_4d(x):
+                continue
+            if len(set(stride)) != 1 or len(set(padding)) != 1 or a is b or not _fresh_gradient(b) or not _same_shape(a, b):
+                continue
+            order = {n: i for i, n in enumerate(graph.nodes)}
+            others = {idx: gi for idx, gi in _items(cb).items() if idx != 0}
+            if any(order[u] < order[add] for gi in others.values() for u in gi.users):
+                continue
+            with graph.inserting_before(add):
+                fused = graph.call_function(omt.conv_backward_acc.default, (gy, x, w, b, list(stride), list(padding), bool(mask[1])))
+            add.replace_all_uses_with(_getitem_after(graph, add, fused, 0, add.meta))
+            for idx, gi in others.items():
+                if idx == 1:
+                    gi.replace_all_uses_with(_getitem_after(graph, add, fused, 1, gi.meta))
+            for dead in [add, a] + list(others.values()) + [cb]:
+                graph.erase_node(dead)
+            done += 1
+            break
+    return done
+
+
 def _dense_conv(n):
     if not _is(n, aten.convolution.default):
         return False
@@ -227,7 +270,8 @@ def rewrite(gm):
     """Apply the three passes to a GraphModule in place; returns {pass: rewrites}."""
     g = gm.graph
     stats = {"bn_relu": fuse_bn_relu(g), "bn_add_relu": fuse_bn_add_relu(g), "bn_relu_backward": fuse_bn_relu_backward(g),
-             "bn_add_relu_backward": fuse_bn_add_relu_backward(g), "conv_epilogue": fuse_conv_epilogues(g)}
+             "bn_add_relu_backward": fuse_bn_add_relu_backward(g), "conv_epilogue": fuse_conv_epilogues(g),
+             "dgrad_accumulate": fuse_dgrad_accumulate(g)}
     g.eliminate_dead_code()
     g.lint()
     gm.recompile()

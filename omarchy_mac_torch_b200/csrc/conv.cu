@@ -20,7 +20,7 @@ bool tc_supported(int kind, const OmtConvGeo* g, const OmtAct* a, const OmtAct* 
 size_t tc_workspace(int kind, const OmtConvGeo* g);
 int tc_conv_fwd(const OmtConvGeo* g, const OmtAct* x, const float* w, const float* bias, const OmtAct* y, float* stats,
                 uint32_t flags, void* ws, cudaStream_t s);
-int tc_conv_dgrad(const OmtConvGeo* g, const OmtAct* gy, const float* w, const OmtAct* dx, void* ws, cudaStream_t s);
+int tc_conv_dgrad(const OmtConvGeo* g, const OmtAct* gy, const float* w, const OmtAct* dx, uint32_t flags, void* ws, cudaStream_t s);
 int tc_conv_wgrad(const OmtConvGeo* g, const OmtAct* x, const OmtAct* gy, float* dw, float scale, void* ws, cudaStream_t s);
 
 // ---- optional per-call timing of the three passes ----
@@ -202,11 +202,12 @@ int omt_conv_dgrad(const OmtConvGeo* g, const OmtAct* gy, const float* w, const 
     }
   }
   OMT_REQUIRE(tc || !(flags & OMT_FORCE_TC), "omt_conv_dgrad: geometry/layout not covered by the tensor-core path");
+  OMT_REQUIRE(tc || !(flags & OMT_EPI_ACCUM), "omt_conv_dgrad: OMT_EPI_ACCUM needs the tensor-core path");
   if (!tc) return simt_conv_dgrad(g, gy, w, dx, st(stream));
   Scratch sc;
   r = sc.get(workspace, workspace_bytes, tc_workspace(1, g), stream);
   if (r) return r;
-  return tc_conv_dgrad(g, gy, w, dx, sc.p, st(stream));
+  return tc_conv_dgrad(g, gy, w, dx, flags, sc.p, st(stream));
 }
 
 int omt_conv_wgrad(const OmtConvGeo* g, const OmtAct* x, const OmtAct* gy, float* dw, float scale, uint32_t flags, void* workspace,

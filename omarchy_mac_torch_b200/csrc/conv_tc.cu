@@ -188,6 +188,10 @@ __device__ __forceinline__ void tma_tile_2d(uint32_t dst, const CUtensorMap* map
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
 }
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src), "r"(x), "r"(y)
+               : "memory");
+}
 __device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int x, int y, int z, int w) {
   asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(map), "r"(src), "r"(x), "r"(y), "r"(z),
                "r"(w)
@@ -448,13 +452,18 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           __syncwarp();
           if (lane == 0) {
             if (g.store_mode == 1) {
-              tma_store_2d(&map_y, smem_u32(buf), nb, c.m0 + q * 32);
+              if (g.flags & OMT_EPI_ACCUM) tma_reduce_add_2d(&map_y, smem_u32(buf), nb, c.m0 + q * 32);
+              else tma_store_2d(&map_y, smem_u32(buf), nb, c.m0 + q * 32);
             } else {
               const int r0 = q * 32;
               tma_store_4d(&map_y, smem_u32(buf), nb, c.ox0 + r0 % g.win_w, c.oy0 + r0 / g.win_w, c.img0);
             }
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           }
+        } else if (g.flags & OMT_EPI_ACCUM) {  // every output element belongs to exactly one tile row: a plain read-add-write
+#pragma unroll
+          for (int j = 0; j < 32; j++)
+            if (nb + j < g.N) yrow[(int64_t)(nb + j) * g.y.sc] += o[j];
         } else if (vec && nb + 32 <= g.N) {
 #pragma unroll
           for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(yrow + nb + j) = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
@@ -644,7 +653,7 @@ int run_tc(const TcProblem& p, const float* w, SplitArgs sp, float* wsplit, cons
 // ---------------------------------------------------------------------------------------------------------------------
 // weight gradient kernel
 // ---------------------------------------------------------------------------------------------------------------------
-constexpr int PB = 32;            // pixels (reduction depth) per stage
+constexpr int PB = 16;            // pixels (reduction depth) per stage: shallow stages, twice as many of them
 constexpr int WG_THREADS = 320;   // producer warp, MMA warp, 8 split/epilogue warps
 
 struct WgArgs {
@@ -668,7 +677,7 @@ struct WgArgs {
 
 template <int BN>
 struct WgSmem {
-  static constexpr int STAGES = BN == 256 ? 2 : (BN == 128 ? 3 : 4);
+  static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
   static constexpr int CH = PB * 128;                 // one 32-pixel x 32-float box
   static constexpr int A_BYTES = 4 * CH, B_BYTES = (BN / 32) * CH;
   static constexpr int HALF = A_BYTES + B_BYTES;      // hi region; the lo region follows at +HALF
@@ -1041,16 +1050,16 @@ WgPlan plan_wgrad(const OmtConvGeo* g) {
   const bool aligned_taps = w.cblocks % w.cpi == 0 && per_tile % w.cpi == 0;
   if (window) {
     w.mode = 4 | 8;
-    w.bw = 32; w.bh = 1; w.bn_img = 1;
+    w.bw = PB; w.bh = 1; w.bn_img = 1;
   } else if (g->ks == 1 && g->stride == 1 && g->pad == 0 && g->ci % 32 == 0) {
     w.mode = 2 | (g->co % 32 == 0 ? 1 : 0);
   } else if (g->ci % 32 == 0 && g->co % 32 == 0 && aligned_taps && g->stride <= 8) {
-    // 32-pixel rectangles bw x bh x bn (powers of two) that waste the fewest pixels; wider rows on ties
+    // PB-pixel rectangles bw x bh x bn (powers of two) that waste the fewest pixels; wider rows on ties
     w.mode = 4;
     double best = -1;
-    for (int bw = 32; bw >= 1; bw >>= 1)
-      for (int bh = 32 / bw; bh >= 1; bh >>= 1) {
-        const int bn = 32 / (bw * bh);
+    for (int bw = PB; bw >= 1; bw >>= 1)
+      for (int bh = PB / bw; bh >= 1; bh >>= 1) {
+        const int bn = PB / (bw * bh);
         if (bw * g->stride > 256 || bh * g->stride > 256) continue;
         const double eff = ((double)g->ow * g->oh * g->n) /
                            ((double)cdiv(g->ow, bw) * bw * cdiv(g->oh, bh) * bh * cdiv(g->n, bn) * bn);
@@ -1206,7 +1215,8 @@ int tc_conv_fwd(const OmtConvGeo* g, const OmtAct* x, const float* w, const floa
 // padding ks-1-pad. Stride s: one stride-1 convolution per phase (py, px) of the input grid, over the taps ky = ky0 + s*ty
 // that reach that phase (the index algebra of the reference's host loop, csrc/conv.cpp:78-95), written to every s-th pixel;
 // phases no tap reaches stay zero.
-int tc_conv_dgrad(const OmtConvGeo* g, const OmtAct* gy, const float* w, const OmtAct* dx, void* ws, cudaStream_t st_) {
+int tc_conv_dgrad(const OmtConvGeo* g, const OmtAct* gy, const float* w, const OmtAct* dx, uint32_t flags, void* ws, cudaStream_t st_) {
+  const uint32_t epi = flags & OMT_EPI_ACCUM;
   if (!load_driver_entry_points()) {
     set_error("the CUDA driver does not export cuTensorMapEncodeTiled/Im2col");
     return OMT_ECUDA;
@@ -1220,8 +1230,8 @@ int tc_conv_dgrad(const OmtConvGeo* g, const OmtAct* gy, const float* w, const O
       if (hi <= 0 || wi <= 0) continue;
       const int ky0 = (py + g->pad) % s, kx0 = (px + g->pad) % s;
       const int jy = ky0 < g->ks ? (int)cdiv(g->ks - ky0, s) : 0, jx = kx0 < g->ks ? (int)cdiv(g->ks - kx0, s) : 0;
-      if (jy == 0 || jx == 0) {  // no tap lands on this phase: its pixels are zero
-        if (!zeroed) {
+      if (jy == 0 || jx == 0) {  // no tap lands on this phase: its pixels are zero (nothing to add when accumulating)
+        if (!zeroed && !epi) {
           OMT_REQUIRE(is_nhwc(dx, g->ci, g->ih, g->iw) || is_nchw(dx, g->ci, g->ih, g->iw), "strided input gradient needs a dense dx");
           OMT_CUDA(cudaMemsetAsync(dx->p, 0, (size_t)g->n * g->ci * g->ih * g->iw * sizeof(float), st_));
           zeroed = true;
@@ -1240,7 +1250,7 @@ int tc_conv_dgrad(const OmtConvGeo* g, const OmtAct* gy, const float* w, const O
       // output (i, j) of the phase reads gy[i + qy - ty, j + qx - tx]; with flipped taps ty' = jy-1-ty the first tap sits at qy-(jy-1)
       TcProblem p{gy->p, g->n, g->co, g->oh, g->ow, hi, wi, g->ci, jy, jx, 1, qy - (jy - 1), qx - (jx - 1), s, py, px};
       SplitArgs sp{g->co, g->ci, g->ks, 0, 0, 0, 1, ky0, kx0, s};
-      int r = run_tc(p, w, sp, wsplit, dx, nullptr, 0, st_);
+      int r = run_tc(p, w, sp, wsplit, dx, nullptr, epi, st_);
       if (r) return r;
       wsplit += 2 * (size_t)g->ci * jy * jx * (cdiv(g->co, BKF) * BKF);
     }

@@ -98,6 +98,42 @@ static std::tuple<Tensor, Tensor, Tensor> convolution_backward_(const Tensor& gy
   return {gx, gw, gb};
 }
 
+// omt::conv_backward_acc: convolution_backward whose input gradient is ADDED to `acc` (a gradient that another consumer
+// of the same tensor already produced) instead of being written to a new tensor and summed by a separate add. The
+// compile backend rewrites  add(convolution_backward(...)[0], other)  to it when `other` is used nowhere else. The
+// tensor-core epilogue does the accumulation (TMA reduce-add); geometries outside that path add separately.
+static std::tuple<Tensor, Tensor> conv_backward_acc_ref(const Tensor& gy, const Tensor& x, const Tensor& w, Tensor& acc, IntArrayRef stride,
+                                                        IntArrayRef padding, bool need_w) {
+  auto r = at::convolution_backward(gy, x, w, std::nullopt, stride, padding, {1, 1}, false, {0, 0}, 1, {true, need_w, false});
+  acc.add_(std::get<0>(r));
+  return {acc, std::get<1>(r)};
+}
+static std::tuple<Tensor, Tensor> conv_backward_acc_dev(const Tensor& gy_, const Tensor& x_, const Tensor& w_, Tensor& acc, IntArrayRef stride,
+                                                        IntArrayRef padding, bool need_w) {
+  std::string kind = conv_kind(x_, w_, stride, padding, {1, 1}, false, 1);
+  NEED(kind == "dense" && f32(gy_) && f32(acc) && acc.sizes() == x_.sizes(), "dense float32 convolution");
+  NEED(layout4(acc) >= 0 && (acc.is_contiguous() || acc.is_contiguous(at::MemoryFormat::ChannelsLast)), "accumulator must be dense");
+  Tensor gy = dense4(gy_), x = dense4(x_), w = contig(w_);
+  OmtConvGeo g = conv_geo(x.size(0), x.size(1), w.size(0), x.size(2), x.size(3), w.size(2), stride[0], padding[0], 1);
+  NEED(gy.size(2) == g.oh && gy.size(3) == g.ow, "grad_output size does not match the geometry");
+  OmtAct ag = act(gy), ax = act(x), aacc = act(acc);
+  int st = omt_conv_dgrad(&g, &ag, w.data_ptr<float>(), &aacc, OMT_EPI_ACCUM, nullptr, 0, cur_stream());
+  if (st == OMT_EINVAL) {  // not a tensor-core geometry: plain input gradient, then the add
+    Tensor gx = dense4(empty_dev(x.sizes(), at::kFloat, layout4(acc) == 1));
+    OmtAct adx = act(gx);
+    check(omt_conv_dgrad(&g, &ag, w.data_ptr<float>(), &adx, 0, nullptr, 0, cur_stream()), "conv input gradient");
+    acc.add_(gx);
+  } else {
+    check(st, "conv input gradient (accumulating)");
+  }
+  Tensor gw;
+  if (need_w) {
+    gw = empty_dev(w.sizes(), at::kFloat);
+    check(omt_conv_wgrad(&g, &ax, &ag, gw.data_ptr<float>(), 1.f, 0, nullptr, 0, cur_stream()), "conv weight gradient");
+  }
+  return {acc, gw};
+}
+
 void bind_conv(py::module_& m) {
   // Inert shims for the reference's generated-kernel planner (csrc/conv.cpp:239-283): kept so code written against the
   // reference's _native module keeps importing; the CUDA kernels need no runtime source generation or per-shape tuning.
@@ -111,6 +147,21 @@ void bind_conv(py::module_& m) {
   m.def("channels_last_mode", []() { return g_cl_mode; });
 }
 
+TORCH_LIBRARY_FRAGMENT(omt, m) {
+  m.def("conv_backward_acc(Tensor gy, Tensor x, Tensor w, Tensor(a!) acc, int[] stride, int[] padding, bool need_w) -> (Tensor(a!), Tensor)");
+}
+TORCH_LIBRARY_IMPL(omt, CompositeExplicitAutograd, m) { m.impl("conv_backward_acc", &conv_backward_acc_ref); }
+TORCH_LIBRARY_IMPL(omt, PrivateUse1, m) {
+  m.impl("conv_backward_acc", [](const Tensor& gy, const Tensor& x, const Tensor& w, Tensor& acc, IntArrayRef stride, IntArrayRef padding, bool need_w) {
+    OMT_LOCK;
+    try {
+      return conv_backward_acc_dev(gy, x, w, acc, stride, padding, need_w);
+    } catch (const Unsupported& e) {
+      note_fallback("conv_backward_acc", e.why);
+      return conv_backward_acc_ref(gy, x, w, acc, stride, padding, need_w);
+    }
+  });
+}
 TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
   OMT_IMPL(m, convolution, convolution_);
   OMT_IMPL(m, convolution_backward, convolution_backward_);

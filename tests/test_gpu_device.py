@@ -340,6 +340,17 @@ def test_omt_ops_device_vs_composite(omt):
         assert len(db) == 4
         for r, d in zip(rb, db):
             assert e(d, r) <= TOL
+    # input gradient accumulated into an existing gradient: tensor-core geometry (channels-last) and a fallback one (ci = 6)
+    for ci_, co_, cl in ((16, 24, True), (6, 5, False)):
+        xa, wa = torch.randn(3, ci_, 9, 9), torch.randn(co_, ci_, 3, 3) * 0.2
+        ga, acc0 = torch.randn(3, co_, 9, 9), torch.randn(3, ci_, 9, 9)
+        fmt = torch.channels_last if cl else torch.contiguous_format
+        r_acc, r_w = omt_ops.conv_backward_acc(ga, xa, wa, acc0.clone(), [1, 1], [1, 1], True)
+        accd = acc0.to(D).contiguous(memory_format=fmt)
+        d_acc, d_w = omt_ops.conv_backward_acc(ga.to(D).contiguous(memory_format=fmt), xa.to(D).contiguous(memory_format=fmt), wa.to(D), accd,
+                                               [1, 1], [1, 1], True)
+        assert d_acc.untyped_storage().data_ptr() == accd.untyped_storage().data_ptr()
+        assert e(d_acc, r_acc) <= TOL and e(d_w, r_w) <= TOL
     cw, cb = torch.randn(5, 6, 3, 3) * 0.2, torch.randn(5)
     assert e(omt_ops.conv_act(x.to(D), cw.to(D), cb.to(D), [1, 1], [1, 1], 1), omt_ops.conv_act(x, cw, cb, [1, 1], [1, 1], 1)) <= TOL
     w5, b5, rm5, rv5 = torch.randn(5), torch.randn(5), torch.randn(5), torch.rand(5) + 0.5

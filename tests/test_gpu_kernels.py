@@ -117,6 +117,29 @@ def test_tensor_core_path_vs_aten_and_exact_path(capi, shape):
     assert rel_err(host(capi.conv_fwd(xd, wd, bd, s, p, flags=capi.FORCE_TC | capi.EPI_RELU, cl=True)), host(exact)) <= 5e-5
 
 
+@pytest.mark.parametrize("shape,cl_out", [((4, 64, 96, 14, 3, 1, 1), True), ((2, 32, 64, 16, 1, 2, 0), True), ((2, 64, 64, 16, 3, 2, 1), True),
+                                          ((2, 32, 40, 15, 3, 1, 1), False)])
+def test_input_gradient_accumulates_in_the_epilogue(capi, shape, cl_out):
+    """OMT_EPI_ACCUM: dx += conv^T(gy, w) (TMA reduce-add for dense channels-last outputs, read-add-write for stride phases
+    and NCHW outputs) against a separate input gradient plus add; a geometry outside the tensor-core path is refused."""
+    n, ci, co, hw, ks, s, p = shape
+    torch.manual_seed(1)
+    w = torch.randn(co, ci, ks, ks) * 0.05
+    oh = (hw + 2 * p - ks) // s + 1
+    gy, base = torch.randn(n, co, oh, oh), torch.randn(n, ci, hw, hw)
+    x = torch.zeros(n, ci, hw, hw, dtype=torch.float64)
+    _, dx, _, _ = oracle.aten_conv(x, w.double(), None, s, p, gy.double())
+    want = (base.double() + dx).float().numpy()
+    acc = dev(base, cl_out).clone(memory_format=torch.preserve_format)
+    got = capi.conv_dgrad(dev(gy, True), dev(w), (hw, hw), s, p, acc=acc)
+    assert got.data_ptr() == acc.data_ptr()
+    assert rel_err(host(got), want) <= TOL
+    capi.call("omt_sync")
+    small = torch.randn(2, 3, 8, 8, device="cuda")  # ci = 3: the tensor cores do not take this input gradient
+    with pytest.raises(capi.OmtError, match="OMT_EPI_ACCUM"):
+        capi.conv_dgrad(torch.randn(2, 8, 8, 8, device="cuda"), torch.randn(8, 3, 3, 3, device="cuda"), (8, 8), 1, 1, acc=small)
+
+
 def test_tensor_core_path_refuses_what_it_cannot_take(capi):
     x = torch.randn(2, 16, 16, 16, device="cuda")           # 16 channels but NCHW: not a TMA-loadable operand
     w = torch.randn(8, 16, 3, 3, device="cuda")

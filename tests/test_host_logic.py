@@ -108,6 +108,7 @@ def test_fx_passes_rewrite_and_preserve_results(pkg, monkeypatch):
     F.cross_entropy(torch.compile(mod, backend=backend)(x), y).backward()
     assert sum(s["bn_add_relu"] for s in seen) == 8 and sum(s["bn_add_relu_backward"] for s in seen) == 8
     assert sum(s["bn_relu"] for s in seen) == 9 and sum(s["bn_relu_backward"] for s in seen) == 9
+    assert sum(s["dgrad_accumulate"] for s in seen) == 8  # the backward joins of the 8 residual blocks
     for a, b in zip(ref.parameters(), mod.parameters()):
         assert (a.grad - b.grad).abs().max() <= 1e-4 * a.grad.abs().max() + 1e-7
     for a, b in zip(ref.buffers(), mod.buffers()):
