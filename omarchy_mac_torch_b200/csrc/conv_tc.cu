@@ -653,7 +653,8 @@ int run_tc(const TcProblem& p, const float* w, SplitArgs sp, float* wsplit, cons
 // ---------------------------------------------------------------------------------------------------------------------
 // weight gradient kernel
 // ---------------------------------------------------------------------------------------------------------------------
-constexpr int PB = 16;            // pixels (reduction depth) per stage: shallow stages, twice as many of them
+// PB = pixels (reduction depth) per stage, a template parameter: 16 with twice the stages when a stage is one or two TMA boxes
+// per operand (covers the load latency better), 32 when a stage needs many boxes (their per-instruction cost dominates)
 constexpr int WG_THREADS = 320;   // producer warp, MMA warp, 8 split/epilogue warps
 
 struct WgArgs {
@@ -675,9 +676,9 @@ struct WgArgs {
   int blocks_per_slice;  // 32-pixel blocks per blockIdx.z
 };
 
-template <int BN>
+template <int BN, int PB>
 struct WgSmem {
-  static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int STAGES = (BN == 256 ? 2 : (BN == 128 ? 3 : 4)) * (32 / PB);
   static constexpr int CH = PB * 128;                 // one 32-pixel x 32-float box
   static constexpr int A_BYTES = 4 * CH, B_BYTES = (BN / 32) * CH;
   static constexpr int HALF = A_BYTES + B_BYTES;      // hi region; the lo region follows at +HALF
@@ -686,10 +687,10 @@ struct WgSmem {
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
 
-template <int BN>
+template <int BN, int PB>
 __global__ void __launch_bounds__(WG_THREADS, 1)
 wgrad_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_g, const WgArgs g) {
-  using S = WgSmem<BN>;
+  using S = WgSmem<BN, PB>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const uint32_t smem_base = smem_u32(smem);
@@ -1028,6 +1029,7 @@ int run_window_fwd(const OmtConvGeo* g, const OmtAct* x, const float* w, const f
 struct WgPlan {
   int bn, slices, blocks_per_slice, cblocks, cpad, chunks;
   int mode, total_blocks, bw, bh, bn_img, tiles_x, tiles_y, cpi;
+  int pb;               // pixels per stage (16 or 32)
   int win_kb;           // window mode: 32-float blocks per filter row
   size_t stage_floats;  // window mode: the padded 4-channel copy of x in front of the partial tiles
   size_t part_floats;
@@ -1044,16 +1046,22 @@ WgPlan plan_wgrad(const OmtConvGeo* g) {
   }
   w.bn = w.chunks >= 6 ? 256 : (w.chunks >= 3 ? 128 : 64);
   const int64_t tiles = cdiv(g->co, BM) * cdiv(w.chunks, w.bn / 32);
-  int64_t total_blocks = cdiv((int64_t)g->n * g->oh * g->ow, PB);
   const int per_tile = w.bn / 32;
   w.cpi = std::min(w.cblocks, per_tile);
   const bool aligned_taps = w.cblocks % w.cpi == 0 && per_tile % w.cpi == 0;
+  const bool matrix = !window && g->ks == 1 && g->stride == 1 && g->pad == 0 && g->ci % 32 == 0;
+  const bool rect = !window && !matrix && g->ci % 32 == 0 && g->co % 32 == 0 && aligned_taps && g->stride <= 8;
+  // x boxes per stage: 1 in matrix mode, per_tile / cpi in rectangle mode, per_tile in window / im2col mode
+  const bool few_boxes = (matrix && g->co % 32 == 0) || (rect && per_tile / w.cpi <= 2);
+  const int PB = few_boxes ? 16 : 32;
+  w.pb = PB;
+  int64_t total_blocks = cdiv((int64_t)g->n * g->oh * g->ow, PB);
   if (window) {
     w.mode = 4 | 8;
     w.bw = PB; w.bh = 1; w.bn_img = 1;
-  } else if (g->ks == 1 && g->stride == 1 && g->pad == 0 && g->ci % 32 == 0) {
+  } else if (matrix) {
     w.mode = 2 | (g->co % 32 == 0 ? 1 : 0);
-  } else if (g->ci % 32 == 0 && g->co % 32 == 0 && aligned_taps && g->stride <= 8) {
+  } else if (rect) {
     // PB-pixel rectangles bw x bh x bn (powers of two) that waste the fewest pixels; wider rows on ties
     w.mode = 4;
     double best = -1;
@@ -1093,9 +1101,9 @@ WgPlan plan_wgrad(const OmtConvGeo* g) {
   } while (0)
 
 // `x` is the channels-last activation, or in window mode the padded 4-channel staging copy
-template <int BN>
+template <int BN, int PB>
 int launch_wgrad(const OmtConvGeo* g, const WgPlan& w, const float* x, const float* gy, float* part, cudaStream_t s) {
-  using S = WgSmem<BN>;
+  using S = WgSmem<BN, PB>;
   alignas(64) CUtensorMap map_x, map_g;
   const int64_t P = (int64_t)g->n * g->oh * g->ow;
   constexpr auto F32 = CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
@@ -1149,7 +1157,7 @@ int launch_wgrad(const OmtConvGeo* g, const WgPlan& w, const float* x, const flo
   }
   static bool attr_set = false;
   if (!attr_set) {
-    OMT_CUDA(cudaFuncSetAttribute(wgrad_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
+    OMT_CUDA(cudaFuncSetAttribute((wgrad_tc_kernel<BN, PB>), cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
     attr_set = true;
   }
   WgArgs a{};
@@ -1158,7 +1166,7 @@ int launch_wgrad(const OmtConvGeo* g, const WgPlan& w, const float* x, const flo
   a.part = part; a.P = g->n * g->oh * g->ow; a.co = g->co; a.oh = g->oh; a.ow = g->ow; a.ks = g->ks; a.stride = g->stride; a.pad = g->pad;
   a.cblocks = w.cblocks; a.cpad = w.cpad; a.chunks = w.chunks; a.blocks_per_slice = w.blocks_per_slice;
   dim3 grid((unsigned)cdiv(g->co, BM), (unsigned)cdiv(w.chunks, BN / 32), (unsigned)w.slices);
-  wgrad_tc_kernel<BN><<<grid, WG_THREADS, S::TOTAL, s>>>(map_x, map_g, a);
+  wgrad_tc_kernel<BN, PB><<<grid, WG_THREADS, S::TOTAL, s>>>(map_x, map_g, a);
   return check_launch(BN == 64 ? "wgrad_tc_128x64" : (BN == 128 ? "wgrad_tc_128x128" : "wgrad_tc_128x256"));
 }
 
@@ -1274,9 +1282,9 @@ int tc_conv_wgrad(const OmtConvGeo* g, const OmtAct* x, const OmtAct* gy, float*
   }
   int r;
   switch (w.bn) {
-    case 64: r = launch_wgrad<64>(g, w, xin, gy->p, part, s); break;
-    case 128: r = launch_wgrad<128>(g, w, xin, gy->p, part, s); break;
-    default: r = launch_wgrad<256>(g, w, xin, gy->p, part, s); break;
+    case 64: r = w.pb == 16 ? launch_wgrad<64, 16>(g, w, xin, gy->p, part, s) : launch_wgrad<64, 32>(g, w, xin, gy->p, part, s); break;
+    case 128: r = w.pb == 16 ? launch_wgrad<128, 16>(g, w, xin, gy->p, part, s) : launch_wgrad<128, 32>(g, w, xin, gy->p, part, s); break;
+    default: r = w.pb == 16 ? launch_wgrad<256, 16>(g, w, xin, gy->p, part, s) : launch_wgrad<256, 32>(g, w, xin, gy->p, part, s); break;
   }
   if (r) return r;
   const int64_t total = (int64_t)g->co * g->ci * g->ks * g->ks;

@@ -30,15 +30,9 @@ static std::map<std::string, int64_t> kernel_counts(bool reset) {
 }
 
 PYBIND11_MODULE(_native, m) {
-  m.def("register_source", [](const std::string&, const std::string&) {}, "inert: kernels are compiled ahead of time");
-  m.def("validate_kernels", []() { return std::vector<std::string>(); }, "inert: returns no failures");
   m.def("init", []() { ensure_init(); });
   m.def("sync", []() { ensure_init(); check(omt_sync(), "synchronize"); check_errors(); });
-  m.def("flush", []() {});
   m.def("check_errors", []() { OMT_LOCK; check_errors(); });
-  m.def("set_queue", [](int, int) {});
-  m.def("set_target_backlog_ms", [](double) {});
-  m.def("queue_state", []() { return std::make_tuple(0, 0, 0, 0.0); });
   m.def("empty_cache", []() { omt_empty_cache(); });
   m.def("memory_allocated", []() { return (int64_t)omt_memory_allocated(); });
   m.def("memory_reserved", []() { return (int64_t)omt_memory_reserved(); });
@@ -49,9 +43,6 @@ PYBIND11_MODULE(_native, m) {
   });
   m.def("cuda_device_index", []() { return device_index(); });
   m.def("set_debug", [](bool on) { OMT_LOCK; stats().debug = on; });
-  m.def("debug_time_kernels", [](bool) {});
-  m.def("debug_skip_submit", [](bool) {});
-  m.def("kernel_times", [](bool) { return std::map<std::string, double>(); });
   m.def("kernel_counts", [](bool reset) { return kernel_counts(reset); });
   m.def("launch_count", []() { return (int64_t)omt_launch_count(); });
   m.def("bridge_counts", [](bool reset) {
@@ -64,29 +55,32 @@ PYBIND11_MODULE(_native, m) {
   m.def("reset_fallbacks", []() { OMT_LOCK; fallback_counts().clear(); });
   m.def("as_cuda", [](const Tensor& t) { return cuda_alias(t); }, "a CUDA tensor aliasing a device tensor's memory (collectives, interop)");
   m.def("from_cuda", [](const Tensor& t) { return wrap_cuda(t); }, "a device tensor aliasing a CUDA tensor's memory");
-  m.def("manual_seed", [](uint64_t s) {
+  // RNG of the device = one CPU generator (values are drawn on the host and copied, csrc/nn.cpp of this extension)
+  auto locked = [](auto&& fn) {
     auto* g = generator(std::nullopt);
     std::lock_guard<std::mutex> lock(g->mutex_);
-    g->set_current_seed(s);
-  });
-  m.def("seed", []() {
-    auto* g = generator(std::nullopt);
-    std::lock_guard<std::mutex> lock(g->mutex_);
-    uint64_t s = c10::detail::getNonDeterministicRandom();
-    g->set_current_seed(s);
+    return fn(*g);
+  };
+  m.def("manual_seed", [locked](uint64_t s) { locked([&](at::CPUGeneratorImpl& g) { g.set_current_seed(s); return 0; }); });
+  m.def("seed", [locked]() {
+    const uint64_t s = c10::detail::getNonDeterministicRandom();
+    locked([&](at::CPUGeneratorImpl& g) { g.set_current_seed(s); return 0; });
     return s;
   });
   m.def("initial_seed", []() { return generator(std::nullopt)->current_seed(); });
-  m.def("get_rng_state", []() {
-    auto* g = generator(std::nullopt);
-    std::lock_guard<std::mutex> lock(g->mutex_);
-    return Tensor(g->get_state());
+  m.def("get_rng_state", [locked]() { return locked([](at::CPUGeneratorImpl& g) { return Tensor(g.get_state()); }); });
+  m.def("set_rng_state", [locked](const Tensor& state) {
+    locked([&](at::CPUGeneratorImpl& g) { g.set_state(*state.unsafeGetTensorImpl()); return 0; });
   });
-  m.def("set_rng_state", [](const Tensor& state) {
-    auto* g = generator(std::nullopt);
-    std::lock_guard<std::mutex> lock(g->mutex_);
-    g->set_state(*state.unsafeGetTensorImpl());
-  });
+  // Names that only meant something for run-time generated WGSL and the wgpu submission queue: accepted, no effect.
+  m.def("register_source", [](const std::string&, const std::string&) {});
+  m.def("validate_kernels", []() { return std::vector<std::string>(); });
+  m.def("kernel_times", [](bool) { return std::map<std::string, double>(); });
+  m.def("queue_state", []() { return std::make_tuple(0, 0, 0, 0.0); });
+  m.def("set_queue", [](int, int) {});
+  m.def("set_target_backlog_ms", [](double) {});
+  for (const char* name : {"debug_time_kernels", "debug_skip_submit"}) m.def(name, [](bool) {});
+  m.def("flush", []() {});
   m.attr("built_with_torch") = TORCH_VERSION;
   bind_conv(m);
   bind_plans(m);
