@@ -272,15 +272,17 @@ class HbmKernels:
 class Train:
     metric, unit, higher = "train_ms_per_step", "ms/step", False
     # compile=True: call the model through torch.compile(backend="omarchy_mac_torch") (fused BatchNorm/ReLU/residual graphs);
-    # the small, launch-bound workloads are faster through the eager nn.Module call with the Sequential auto-fuse.
-    # --eager / --compile override.
+    # the small, launch-bound workloads are faster through the eager nn.Module call with the Sequential auto-fuse, and replay
+    # the whole step as one CUDA graph (graph=True; omarchy_mac_torch_b200.graphs.capture). --eager / --compile / --graph /
+    # --no-graph override.
 
-    def __init__(self, name, make_model, shape, classes, make_opt, cpu_batch, note, compile=False):
-        self.compile = compile
+    def __init__(self, name, make_model, shape, classes, make_opt, cpu_batch, note, compile=False, graph=False):
+        self.compile, self.graph = compile, graph
         self.name, self.make_model, self.in_shape, self.classes, self.make_opt = name, make_model, shape, classes, make_opt
         self.cpu_batch = min(cpu_batch, shape[0])
         self.shape = {"batch_per_gpu": shape[0], "input": list(shape[1:]), "classes": classes, "optimizer": note,
-                      "api": 'torch.compile(model, backend="omarchy_mac_torch")' if compile else "eager nn.Module"}
+                      "api": ('torch.compile(model, backend="omarchy_mac_torch")' if compile else "eager nn.Module")
+                             + (" + omarchy_mac_torch_b200.graphs.capture(step)" if graph else "")}
 
     def host_inputs(self, seed, batch=None):
         g = torch.Generator().manual_seed(1000 + seed)
@@ -330,12 +332,56 @@ class Train:
         return loss
 
     def step(self):
+        if self.graph:
+            return self._graphed()()
         return self._step(self.x, self.y)
 
+    def _graphed(self):
+        """The whole step (zero_grad, forward, backward, optimizer) as one CUDA graph over the static batch tensors."""
+        if not hasattr(self, "_g"):
+            from omarchy_mac_torch_b200 import graphs
+            self._g = graphs.capture(lambda: self._step(self.x, self.y))
+            self.launches_per_step = self._g.kernels
+        return self._g
+
     def e2e_step(self):
-        self.xs.copy_(self.xh, non_blocking=True)
-        self.ys.copy_(self.yh, non_blocking=True)
-        return self._step(self.xs, self.ys).item()  # device->host read of the loss
+        if self.graph:  # refill the static batch from pinned memory, replay, read the loss back
+            g = self._graphed()
+            self.x.copy_(self.xh, non_blocking=True)
+            self.y.copy_(self.yh, non_blocking=True)
+            return g().item()
+        return self._e2e_prefetch()
+
+    def _e2e_prefetch(self):
+        """One step fed from pinned host memory, as a prefetching data loader feeds it: this step's batch was copied to one
+        of two device buffers on a side stream while the previous step computed; the copy of the next step's batch is
+        issued now. Every step copies its whole batch host->device and reads its loss back, all inside the timed region."""
+        if not hasattr(self, "_pf"):
+            side = torch.cuda.Stream()
+            bufs = [(self.xs, self.ys), (torch.empty_like(self.xs), torch.empty_like(self.ys))]
+            ready = [torch.cuda.Event(), torch.cuda.Event()]   # copy into buffer k finished
+            freed = [torch.cuda.Event(), torch.cuda.Event()]   # compute that read buffer k finished
+            self._pf = {"side": side, "bufs": bufs, "ready": ready, "freed": freed, "i": 0}
+            self._prefetch(0, first=True)
+        pf = self._pf
+        k = pf["i"] % 2
+        torch.cuda.current_stream().wait_event(pf["ready"][k])
+        self._prefetch(1 - k)
+        x, y = pf["bufs"][k]
+        loss = self._step(x, y)
+        pf["freed"][k].record(torch.cuda.current_stream())
+        pf["i"] += 1
+        return loss.item()  # device->host read of the loss
+
+    def _prefetch(self, k, first=False):
+        pf = self._pf
+        with torch.cuda.stream(pf["side"]):
+            if not first:
+                pf["side"].wait_event(pf["freed"][k])  # the step that last read this buffer (recorded before its reuse)
+            x, y = pf["bufs"][k]
+            x.copy_(self.xh, non_blocking=True)
+            y.copy_(self.yh, non_blocking=True)
+            pf["ready"][k].record(pf["side"])
 
     def value(self, ms):
         return ms
@@ -360,7 +406,7 @@ class Train:
         # conv GEMMs measured live: two extra steps with the library's per-call CUDA-event timing switched on
         self.capi.conv_timing(True)
         for _ in range(2):
-            self.step()
+            self._step(self.x, self.y)  # eager even when the timed steps were graph replays: the timing wraps each call
         torch.cuda.synchronize()
         t = self.capi.conv_timing_read(reset=True)
         self.capi.conv_timing(False)
@@ -387,11 +433,12 @@ def _sgd(lr, **kw):
 
 TRAIN = {
     "plaincnn": lambda: Train("plaincnn_b128_train", lambda: _models().PlainCNN3(), (128, 3, 32, 32), 10, _sgd(0.05, momentum=0.9), 128,
-                              "SGD lr .05 momentum .9"),
+                              "SGD lr .05 momentum .9", graph=True),
     "resnet18": lambda: Train("resnet18_b32_train", lambda: _models().kaiming_normal_convs(_models().ResNet18(num_classes=1000)),
-                              (32, 3, 64, 64), 1000, _sgd(0.1, momentum=0.9, weight_decay=1e-4), 32, "SGD lr .1 momentum .9 wd 1e-4"),
+                              (32, 3, 64, 64), 1000, _sgd(0.1, momentum=0.9, weight_decay=1e-4), 32, "SGD lr .1 momentum .9 wd 1e-4", graph=True),
     "mobilenetv3": lambda: Train("mobilenetv3_small_b32_train", lambda: _models().MobileNetV3SE(), (32, 3, 224, 224), 1000,
-                                 lambda p: torch.optim.AdamW(p, lr=1e-3, weight_decay=0.01), 32, "AdamW lr 1e-3 wd .01"),
+                                 lambda p: torch.optim.AdamW(p, lr=1e-3, weight_decay=0.01, capturable=True), 32, "AdamW lr 1e-3 wd .01",
+                                 graph=True),
     "resnet50": lambda: Train("resnet50_b256_train", lambda: _models().ResNet50(), (256, 3, 224, 224), 1000,
                               _sgd(0.1, momentum=0.9, nesterov=True, weight_decay=1e-4), 16, "SGD lr .1 momentum .9 nesterov wd 1e-4",
                               compile=True),
@@ -484,6 +531,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--eager", action="store_true", help="training workloads: call the nn.Module directly instead of through the compile backend")
     ap.add_argument("--compile", action="store_true", help="training workloads: call the model through the compile backend")
+    ap.add_argument("--graph", action="store_true", help="training workloads: replay the whole step as one CUDA graph")
+    ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--profile-step", action="store_true",
                     help="for ncu --profile-from-start off: after the warm-up run ONE step between cudaProfilerStart/Stop and exit")
     args = ap.parse_args()
@@ -494,6 +543,8 @@ def main():
     if (args.eager or args.compile) and isinstance(wl, Train):
         wl.compile = args.compile and not args.eager
         wl.shape["api"] = 'torch.compile(model, backend="omarchy_mac_torch")' if wl.compile else "eager nn.Module"
+    if isinstance(wl, Train) and (args.graph or args.no_graph):
+        wl.graph = args.graph and not args.no_graph
     if args.impl == "reference":
         return run_reference(args, wl)
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
@@ -518,6 +569,8 @@ def main():
     l0 = capi.lib().omt_launch_count()
     ms = time_steps(wl.step, args.steps, args.warmup, world, flush)
     launches = (capi.lib().omt_launch_count() - l0) // (args.steps + args.warmup)
+    if getattr(wl, "launches_per_step", None):  # a replayed CUDA graph: the kernels recorded at capture, per replay
+        launches = wl.launches_per_step
     ms_e2e = time_steps(wl.e2e_step, args.steps, args.warmup, world, flush)
     clocks = sampler.stop() if rank == 0 else None
     roof = wl.roofline(ms, peaks)  # runs extra steps: every rank takes part (they contain the gradient all-reduce)

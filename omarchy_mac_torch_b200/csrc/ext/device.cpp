@@ -7,6 +7,9 @@
 // the GPU.
 #include "omt.h"
 
+#include <atomic>
+#include <c10/cuda/CUDAGuard.h>
+
 #include <ATen/CPUGeneratorImpl.h>
 #include <ATen/EmptyTensor.h>
 #include <ATen/detail/CUDAHooksInterface.h>
@@ -69,7 +72,26 @@ int device_index() {
   ensure_init();
   return g_index;
 }
-omt_stream_t cur_stream() { return (omt_stream_t)c10::cuda::getCurrentCUDAStream((c10::DeviceIndex)device_index()).stream(); }
+// Autograd runs backward nodes on worker threads whose current CUDA stream is their own default stream: it only carries
+// the forward's stream over for tensors of the process's accelerator type (CUDA), not for this PrivateUse1 device. A
+// process-wide override lets a scope (CUDA-graph capture and its warm-up, omarchy_mac_torch_b200.graphs) put every
+// thread's work of this device on one stream.
+static std::atomic<cudaStream_t> g_stream_override{nullptr};
+static std::atomic<bool> g_has_override{false};
+void set_stream_override(uint64_t cuda_stream, bool on) {
+  g_stream_override.store((cudaStream_t)cuda_stream);
+  g_has_override.store(on);
+}
+bool stream_override(cudaStream_t* s) {
+  if (!g_has_override.load(std::memory_order_relaxed)) return false;
+  *s = g_stream_override.load();
+  return true;
+}
+omt_stream_t cur_stream() {
+  cudaStream_t s;
+  if (stream_override(&s)) return (omt_stream_t)s;
+  return (omt_stream_t)c10::cuda::getCurrentCUDAStream((c10::DeviceIndex)device_index()).stream();
+}
 
 void check(int status, const char* what) {
   if (status == OMT_OK) return;
@@ -245,10 +267,38 @@ struct Guard final : c10::impl::DeviceGuardImplInterface {
   void uncheckedSetDevice(c10::Device) const noexcept override {
     if (g_index >= 0) cudaSetDevice(g_index);
   }
-  c10::Stream getStream(c10::Device d) const noexcept override { return c10::Stream(c10::Stream::DEFAULT, d); }
-  c10::Stream getDefaultStream(c10::Device d) const override { return c10::Stream(c10::Stream::DEFAULT, d); }
-  c10::Stream getNewStream(c10::Device d, int) const override { return c10::Stream(c10::Stream::DEFAULT, d); }
-  c10::Stream exchangeStream(c10::Stream s) const noexcept override { return s; }
+  // Streams of this device are PyTorch's CUDA streams of the GPU underneath, under the same stream ids. Autograd records
+  // the stream an op ran on and makes its worker thread run the backward node there (exchangeStream): without the
+  // mapping the backward of work issued on a side stream, or inside a CUDA-graph capture, would land on the worker
+  // thread's default stream.
+  static c10::DeviceIndex cuda_index() { return (c10::DeviceIndex)(g_index >= 0 ? g_index : 0); }
+  static c10::Stream as_mine(const c10::cuda::CUDAStream& cs) { return c10::Stream(c10::Stream::UNSAFE, c10::Device(kDev, 0), cs.id()); }
+  static c10::cuda::CUDAStream as_cuda(const c10::Stream& s) {
+    return c10::cuda::CUDAStream(c10::cuda::CUDAStream::UNCHECKED, c10::Stream(c10::Stream::UNSAFE, c10::Device(c10::kCUDA, cuda_index()), s.id()));
+  }
+  // (autograd's engine asks every registered backend for streams, also in processes that never touch a GPU)
+  static bool has_gpu() {
+    static const bool yes = c10::cuda::device_count() > 0;
+    return yes;
+  }
+  c10::Stream getStream(c10::Device d) const noexcept override {
+    if (!has_gpu()) return c10::Stream(c10::Stream::DEFAULT, d);
+    return as_mine(c10::cuda::getCurrentCUDAStream(cuda_index()));
+  }
+  c10::Stream getDefaultStream(c10::Device d) const override {
+    if (!has_gpu()) return c10::Stream(c10::Stream::DEFAULT, d);
+    return as_mine(c10::cuda::getDefaultCUDAStream(cuda_index()));
+  }
+  c10::Stream getNewStream(c10::Device d, int priority) const override {
+    if (!has_gpu()) return c10::Stream(c10::Stream::DEFAULT, d);
+    return as_mine(c10::cuda::getStreamFromPool(priority, cuda_index()));
+  }
+  c10::Stream exchangeStream(c10::Stream s) const noexcept override {
+    if (!has_gpu()) return s;
+    c10::Stream old = as_mine(c10::cuda::getCurrentCUDAStream(cuda_index()));
+    c10::cuda::setCurrentCUDAStream(as_cuda(s));
+    return old;
+  }
   c10::DeviceIndex deviceCount() const noexcept override { return 1; }
   void record(void** event, const c10::Stream&, const c10::DeviceIndex, const c10::EventFlag) const override {
     ensure_init();
@@ -418,7 +468,13 @@ static void bridge_impl(const c10::OperatorHandle& op, torch::jit::Stack* stack,
       v = cuda_dev;
     }
   }
-  op.redispatchBoxed(c10::DispatchKeySet(c10::DispatchKey::CUDA), stack);
+  {
+    // the ATen CUDA kernel launches on this thread's current CUDA stream: follow the override if one is set
+    std::optional<c10::cuda::CUDAStreamGuard> follow;
+    cudaStream_t forced;
+    if (stream_override(&forced)) follow.emplace(c10::cuda::getStreamFromExternal(forced, (c10::DeviceIndex)device_index()));
+    op.redispatchBoxed(c10::DispatchKeySet(c10::DispatchKey::CUDA), stack);
+  }
   map.adopt_resized();
   const size_t nret = schema.returns().size(), rbegin = stack->size() - nret;
   for (size_t i = 0; i < nret; i++) {

@@ -10,6 +10,7 @@ namespace omt {
 
 void bind_conv(py::module_& m);
 void bind_plans(py::module_& m);
+void set_stream_override(uint64_t cuda_stream, bool on);
 at::CPUGeneratorImpl* generator(const std::optional<at::Generator>& gen);
 
 static std::map<std::string, int64_t> kernel_counts(bool reset) {
@@ -53,6 +54,8 @@ PYBIND11_MODULE(_native, m) {
   });
   m.def("fallback_counts", []() { OMT_LOCK; return fallback_counts(); });
   m.def("reset_fallbacks", []() { OMT_LOCK; fallback_counts().clear(); });
+  m.def("set_stream_override", &set_stream_override,
+        "route the work of every thread (autograd workers included) to this cudaStream_t while `on`; graphs.capture uses it");
   m.def("as_cuda", [](const Tensor& t) { return cuda_alias(t); }, "a CUDA tensor aliasing a device tensor's memory (collectives, interop)");
   m.def("from_cuda", [](const Tensor& t) { return wrap_cuda(t); }, "a device tensor aliasing a CUDA tensor's memory");
   // RNG of the device = one CPU generator (values are drawn on the host and copied, csrc/nn.cpp of this extension)

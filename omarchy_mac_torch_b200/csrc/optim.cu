@@ -7,6 +7,10 @@
 // parameter (csrc/optim.cpp:20-25, 41-46); here a chunk table maps blocks to (tensor, offset).
 #include <vector>
 
+#include <cstring>
+#include <mutex>
+#include <vector>
+
 #include "common.cuh"
 
 namespace omt {
@@ -146,12 +150,33 @@ static int64_t stage_table(const OmtParam* table, int32_t count, bool adam, omt_
   }
   if (host.empty()) return 0;
   size_t bytes = host.size() * sizeof(DevParam);
-  int r = sc.get(nullptr, 0, bytes, stream);
-  if (r) return r;
-  // pageable source: the runtime stages it before returning, so `host` may die right after
-  cudaError_t e = cudaMemcpyAsync(sc.p, host.data(), bytes, cudaMemcpyHostToDevice, st(stream));
+  // The table of a training loop is the same every step (same parameter, gradient and state addresses), so device copies
+  // are kept and reused: no host-to-device copy on the steady-state path, which also keeps a step capturable in a CUDA
+  // graph (a copy from a temporary host buffer would be replayed from freed memory).
+  struct Cached { std::vector<DevParam> host; void* dev = nullptr; uint64_t used = 0; };
+  static std::mutex mu;
+  static Cached cache[8];
+  static uint64_t tick = 0;
+  std::lock_guard<std::mutex> lock(mu);
+  Cached* slot = &cache[0];
+  for (Cached& c : cache) {
+    if (c.dev && c.host.size() == host.size() && std::memcmp(c.host.data(), host.data(), bytes) == 0) {
+      c.used = ++tick;
+      sc.p = c.dev;  // not owned by the Scratch
+      return ((int64_t)host.size() << 40) | chunks;
+    }
+    if (c.used < slot->used) slot = &c;
+  }
+  if (slot->dev) omt_free(slot->dev);  // stream-ordered: kernels already queued with the old table are unaffected
+  slot->dev = omt_malloc(bytes, stream);
+  if (!slot->dev) return OMT_ENOMEM;
+  slot->host = std::move(host);
+  slot->used = ++tick;
+  // pageable source that stays alive in the cache entry
+  cudaError_t e = cudaMemcpyAsync(slot->dev, slot->host.data(), bytes, cudaMemcpyHostToDevice, st(stream));
   if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyAsync(optimizer table)");
-  return ((int64_t)host.size() << 40) | chunks;  // tensors in the high bits, chunks in the low 40
+  sc.p = slot->dev;
+  return ((int64_t)slot->host.size() << 40) | chunks;
 }
 
 }  // namespace omt

@@ -360,6 +360,42 @@ def test_omt_ops_device_vs_composite(omt):
     assert not omt.FALLBACKS, dict(omt.FALLBACKS)
 
 
+def test_step_graph_replays_match_eager_steps(omt):
+    """graphs.capture: the whole training step (zero_grad, fused-stack forward/backward, fused SGD) recorded once and
+    replayed; every replay has to do exactly what an eager step does, also after the static batch tensors are refilled."""
+    from omarchy_mac_torch_b200 import graphs, models
+    torch.manual_seed(0)
+    ref = models.ResNet18(num_classes=10)
+    a, b = copy.deepcopy(ref).to(D), copy.deepcopy(ref).to(D)
+    oa = torch.optim.SGD(a.parameters(), lr=0.01, momentum=0.9, weight_decay=1e-4)
+    ob = torch.optim.SGD(b.parameters(), lr=0.01, momentum=0.9, weight_decay=1e-4)
+    x, y = torch.randn(8, 3, 32, 32).to(D), torch.randint(0, 10, (8,)).to(D)
+
+    def step(m, o):
+        o.zero_grad(set_to_none=True)
+        loss = F.cross_entropy(m(x), y)
+        loss.backward()
+        o.step()
+        return loss
+
+    g = graphs.capture(lambda: step(b, ob), warmup=3)  # three real steps; the recorded run itself executes nothing
+    assert g.kernels > 50
+    for _ in range(3):
+        step(a, oa)
+    for it in range(3):
+        if it == 2:  # a new batch through the static tensors
+            x.copy_(torch.randn(8, 3, 32, 32))
+            y.copy_(torch.randint(0, 10, (8,)))
+        lb = g().item()
+        la = step(a, oa).item()
+        assert abs(la - lb) <= 1e-6 * abs(la)
+        for p, q in zip(a.parameters(), b.parameters()):
+            assert e(q, p.detach().cpu()) <= 1e-6
+    for p, q in zip(a.buffers(), b.buffers()):
+        assert e(q.float(), p.float().cpu()) <= 1e-6
+    assert not omt.FALLBACKS, dict(omt.FALLBACKS)
+
+
 def test_compile_backend_residual_blocks(omt):
     """torch.compile(backend="omarchy_mac_torch") on a residual network: the BatchNorm -> + identity -> ReLU tails and their
     backward run as the fused device ops, and one training step's gradients match the CPU's eager run."""
