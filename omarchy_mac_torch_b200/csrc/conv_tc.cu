@@ -30,6 +30,7 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <vector>
 #include <mutex>
 
 #include "common.cuh"
@@ -211,12 +212,21 @@ struct TcArgs {
   int cpad;           // cblocks * 32
   uint32_t flags;
   int store_mode;     // 0: plain stores (any strides); 1: TMA stores of 32-row boxes of the [M, N] matrix; 2: of window rectangles
-  // "window" mode (few input channels): the A operand comes from a zero-padded [n][h][w][4] copy of the input through a
-  // tiled tensor map whose pixel dimension overlaps (stride = conv stride * 16 bytes), so one 32-float row holds 8
-  // consecutive input pixels x 4 channels = the (kx, c) run of a filter row. GEMM rows are win_w x win_h pixel rectangles.
-  int win_w, win_h;   // 0 = im2col mode
-  int tiles_x, tiles_y;
+  // The last 16 bytes are shared by two modes that never occur together (growing this struct by 16 bytes made every
+  // tile of the kernel 2-3 us slower on the GPU, measured; the cause was not established, so its size is kept).
+  //  * "window" mode (win_w != 0; few input channels): the A operand comes from a zero-padded [n][h][w][4] copy of the
+  //    input through a tiled tensor map whose pixel dimension overlaps (stride = conv stride * 16 bytes), so one 32-float
+  //    row holds 8 consecutive input pixels x 4 channels = the (kx, c) run of a filter row. GEMM rows are win_w x win_h
+  //    pixel rectangles.
+  //  * split-K (the SPLITK kernel instantiation only; win_w is not looked at there): for problems with fewer tiles than
+  //    SMs, tile t = (output tile, split); a CTA reduces the k-blocks of its split and stores the raw sums to
+  //    part[split][M][N]; splitk_epilogue_kernel adds the splits in order and applies the epilogue.
+  union {
+    struct { int win_w, win_h, tiles_x, tiles_y; };
+    struct { int splits, unused_; float* part; };
+  };
 };
+static_assert(sizeof(TcArgs) == 128, "TcArgs is a kernel parameter whose size is performance-sensitive");
 
 template <int BN>
 struct Smem {
@@ -239,16 +249,17 @@ struct TileCoord {
   int img0, oy0, ox0;  // first pixel of the tile (im2col mode: linear pixel run; window mode: top-left of the rectangle)
   int m0, n0;
 };
-__device__ __forceinline__ TileCoord decode_tile(const TcArgs& g, int t, int n_tiles, int bn) {
+__device__ __forceinline__ TileCoord decode_tile(const TcArgs& g, int t, int n_tiles, int bn, int splits, int win_w) {
   TileCoord c;
+  t /= splits;
   const int mt = t / n_tiles;
   c.n0 = (t - mt * n_tiles) * bn;
   c.m0 = mt * BM;
-  if (g.win_w) {
+  if (win_w) {
     const int per = g.tiles_x * g.tiles_y;
     c.img0 = mt / per;
     const int r = mt - c.img0 * per;
-    c.oy0 = (r / g.tiles_x) * g.win_h; c.ox0 = (r % g.tiles_x) * g.win_w;
+    c.oy0 = (r / g.tiles_x) * g.win_h; c.ox0 = (r % g.tiles_x) * win_w;
   } else {
     const int ohw = g.oh * g.ow;
     c.img0 = c.m0 / ohw;
@@ -258,7 +269,7 @@ __device__ __forceinline__ TileCoord decode_tile(const TcArgs& g, int t, int n_t
   return c;
 }
 
-template <int BN>
+template <int BN, bool SPLITK>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_y,
                const TcArgs g, const int m_tiles, const int n_tiles) {
@@ -276,7 +287,19 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kblocks = g.kh * g.kw * g.cblocks;
-  const int total_tiles = m_tiles * n_tiles;
+  int splits = 1;  // a compile-time 1 in the common instantiation
+  if constexpr (SPLITK) splits = g.splits;
+  const int win_w = SPLITK ? 0 : g.win_w;  // the split-K fields alias the window fields
+  const int total_tiles = m_tiles * n_tiles * splits;
+  // k-block range of split sp: [sp * kblocks / splits, (sp + 1) * kblocks / splits)
+  auto kb_begin = [kblocks, splits](int t) -> int {
+    if constexpr (!SPLITK) return 0;
+    return (int)(((int64_t)(t % splits) * kblocks) / splits);
+  };
+  auto kb_end = [kblocks, splits](int t) -> int {
+    if constexpr (!SPLITK) return kblocks;
+    return (int)(((int64_t)(t % splits + 1) * kblocks) / splits);
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S::STAGES; s++) {
@@ -308,16 +331,16 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       int it = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        const TileCoord c = decode_tile(g, t, n_tiles, BN);
+        const TileCoord c = decode_tile(g, t, n_tiles, BN, splits, win_w);
         const int w0 = c.ox0 * g.stride + g.low_w, h0 = c.oy0 * g.stride + g.low_h;
-        for (int kb = 0; kb < kblocks; kb++, it++) {
+        for (int kb = kb_begin(t), kbe = kb_end(t); kb < kbe; kb++, it++) {
           const int s = it % S::STAGES, round = it / S::STAGES;
           if (round > 0 && !mbar_wait(BAR(2 * S::STAGES + s), (round - 1) & 1, abort_flag)) { ok = false; break; }
           const int tap = kb / g.cblocks, cb = kb - tap * g.cblocks;
           const int ky = tap / g.kw, kx = tap - ky * g.kw;
           const uint32_t stage = smem_base + s * S::STAGE_BYTES;
           mbar_expect_tx(BAR(s), S::A_BYTES + 2 * S::B_BYTES);
-          if (g.win_w) tma_tile_4d(stage, &map_a, BAR(s), cb * BKF, c.ox0, h0 + ky, c.img0);  // kw == 1: tap = filter row
+          if (win_w) tma_tile_4d(stage, &map_a, BAR(s), cb * BKF, c.ox0, h0 + ky, c.img0);  // kw == 1: tap = filter row
           else tma_im2col_4d(stage, &map_a, BAR(s), cb * BKF, w0, h0, c.img0, (uint16_t)kx, (uint16_t)ky);
           tma_tile_3d(stage + 2 * S::A_BYTES, &map_w, BAR(s), tap * g.cpad + cb * BKF, c.n0, 0);
           tma_tile_3d(stage + 2 * S::A_BYTES + S::B_BYTES, &map_w, BAR(s), tap * g.cpad + cb * BKF, c.n0, 1);
@@ -344,7 +367,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         }
         const uint32_t acc = tmem_base + b * (2 * BN);
-        for (int kb = 0; kb < kblocks; kb++, it++) {
+        const int kb0 = kb_begin(t);
+        for (int kb = kb0, kbe = kb_end(t); kb < kbe; kb++, it++) {
           const int s = it % S::STAGES, round = it / S::STAGES;
           ok = mbar_wait(BAR(S::STAGES + s), round & 1, abort_flag) && mbar_wait(BAR(s), round & 1, abort_flag);
           if (!ok) break;
@@ -357,9 +381,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const uint64_t adv = (uint64_t)((k * UMMA_K * 4) >> 4);  // 32 bytes per k-step inside the swizzled row
             // two accumulators: the cross terms (2^-11 of the result) go to columns [BN, 2BN) so that the truncation the
             // tensor core applies on every accumulate hits the main sum once per k-step instead of three times
-            umma_tf32(acc + BN, a_lo + adv, b_hi + adv, idesc, (kb | k) ? 1u : 0u);
+            const uint32_t accumulate = ((kb - kb0) | k) ? 1u : 0u;  // the split's first MMA overwrites the accumulators
+            umma_tf32(acc + BN, a_lo + adv, b_hi + adv, idesc, accumulate);
             umma_tf32(acc + BN, a_hi + adv, b_lo + adv, idesc, 1u);
-            umma_tf32(acc, a_hi + adv, b_hi + adv, idesc, (kb | k) ? 1u : 0u);
+            umma_tf32(acc, a_hi + adv, b_hi + adv, idesc, accumulate);
           }
           umma_commit(BAR(2 * S::STAGES + s));  // stage is free once these MMAs have read it
         }
@@ -372,7 +397,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     int it = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-      for (int kb = 0; kb < kblocks; kb++, it++) {
+      for (int kb = kb_begin(t), kbe = kb_end(t); kb < kbe; kb++, it++) {
         const int s = it % S::STAGES, round = it / S::STAGES;
         ok = mbar_wait(BAR(s), round & 1, abort_flag);
         if (!ok) break;
@@ -409,13 +434,13 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       ok = mbar_wait(BAR(ACC_FULL + b), use & 1, abort_flag);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const TileCoord c = decode_tile(g, t, n_tiles, BN);
+      const TileCoord c = decode_tile(g, t, n_tiles, BN, splits, win_w);
       const uint32_t acc = tmem_base + b * (2 * BN) + ((uint32_t)(q * 32) << 16);
       const int r = q * 32 + lane;
       int img, oy, ox;
       bool valid;
-      if (g.win_w) {
-        img = c.img0; oy = c.oy0 + r / g.win_w; ox = c.ox0 + r % g.win_w;
+      if (win_w) {
+        img = c.img0; oy = c.oy0 + r / win_w; ox = c.ox0 + r % win_w;
         valid = oy < g.oh && ox < g.ow;
       } else {
         const int m = c.m0 + r, ohw = g.oh * g.ow;
@@ -433,6 +458,14 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         tmem_ld32x2(acc + ch * 32, acc + BN + ch * 32, v, u);
         const int nb = c.n0 + ch * 32;
         if (nb >= g.N) continue;
+        if constexpr (SPLITK) {  // raw partial sums of this split; the epilogue runs in splitk_epilogue_kernel
+          if (!valid) continue;
+          float* prow = g.part + ((int64_t)(t % splits) * g.M + (c.m0 + r)) * g.N + nb;
+#pragma unroll
+          for (int j = 0; j < 32; j++)
+            if (nb + j < g.N) prow[j] = __uint_as_float(v[j]) + __uint_as_float(u[j]);
+          continue;
+        }
         if (!g.store_mode && !valid) continue;
         float o[32];
 #pragma unroll
@@ -456,7 +489,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               else tma_store_2d(&map_y, smem_u32(buf), nb, c.m0 + q * 32);
             } else {
               const int r0 = q * 32;
-              tma_store_4d(&map_y, smem_u32(buf), nb, c.ox0 + r0 % g.win_w, c.oy0 + r0 / g.win_w, c.img0);
+              tma_store_4d(&map_y, smem_u32(buf), nb, c.ox0 + r0 % win_w, c.oy0 + r0 / win_w, c.img0);
             }
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           }
@@ -568,6 +601,29 @@ int pick_bn(const TcProblem& p) {
   return (mt * cdiv(p.rows, 256) >= sm_count()) ? 256 : 128;
 }
 
+// split-K plan: only when the output tiles leave most SMs idle and the reduction is long enough to share
+int plan_splits(int64_t M, int64_t N, int kblocks, int bn) {
+  const int64_t tiles = cdiv(M, BM) * cdiv(N, bn);
+  if (tiles * 2 > sm_count() || kblocks < 8) return 1;
+  return (int)std::max<int64_t>(1, std::min<int64_t>(kblocks / 4, sm_count() / tiles));
+}
+
+// y(m, n) = epilogue(sum over splits of part[s][m][n]) for the GEMM row m = (img, oy, ox) of the (sub-)convolution
+__global__ void __launch_bounds__(256) splitk_epilogue_kernel(TcArgs g) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (int64_t)g.M * g.N) return;
+  const int n = (int)(i % g.N);
+  const int m = (int)(i / g.N);
+  float v = 0.f;
+  for (int s = 0; s < g.splits; s++) v += __ldg(g.part + ((int64_t)s * g.M + m) * g.N + n);
+  if (g.flags & OMT_EPI_BIAS) v += __ldg(g.bias + n);
+  if (g.flags & OMT_EPI_RELU) v = fmaxf(v, 0.f);
+  const int ohw = g.oh * g.ow, img = m / ohw, rr = m - img * ohw, oy = rr / g.ow, ox = rr - oy * g.ow;
+  float* dst = g.y.p + g.y.off(img, n, oy * g.out_step + g.out_y0, ox * g.out_step + g.out_x0);
+  if (g.flags & OMT_EPI_ACCUM) *dst += v;
+  else *dst = v;
+}
+
 // dense channels-last output written pixel for pixel (no phase stride), 16-byte aligned rows
 bool dense_out(const TcArgs& a) {
   const ActView& y = a.y;
@@ -576,7 +632,7 @@ bool dense_out(const TcArgs& a) {
 }
 
 template <int BN>
-int launch_tc(const TcProblem& p, const float* wsplit, const TcArgs& args, cudaStream_t s) {
+int launch_tc(const TcProblem& p, const float* wsplit, const TcArgs& args, int splits, float* part, cudaStream_t s) {
   using S = Smem<BN>;
   alignas(64) CUtensorMap map_a, map_w;
   {
@@ -608,12 +664,15 @@ int launch_tc(const TcProblem& p, const float* wsplit, const TcArgs& args, cudaS
   }
   static bool attr_set = false;
   if (!attr_set) {
-    OMT_CUDA(cudaFuncSetAttribute(conv_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
+    OMT_CUDA(cudaFuncSetAttribute((conv_tc_kernel<BN, false>), cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
+    OMT_CUDA(cudaFuncSetAttribute((conv_tc_kernel<BN, true>), cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
     attr_set = true;
   }
   TcArgs a = args;
   alignas(64) CUtensorMap map_y = map_w;  // placeholder when the epilogue stores directly
-  if (dense_out(a)) {  // the output is the row-major [M, N] matrix: 32 x 32 boxes leave through TMA
+  if (splits > 1) {  // partial tiles go to the workspace with plain stores (these fields alias the window fields, unused here)
+    a.splits = splits; a.unused_ = 0; a.part = part;
+  } else if (dense_out(a)) {  // the output is the row-major [M, N] matrix: 32 x 32 boxes leave through TMA
     cuuint64_t dims[2] = {(cuuint64_t)a.N, (cuuint64_t)a.M};
     cuuint64_t strides[1] = {(cuuint64_t)a.N * 4};
     cuuint32_t box[2] = {32, 32}, estr[2] = {1, 1};
@@ -622,15 +681,20 @@ int launch_tc(const TcProblem& p, const float* wsplit, const TcArgs& args, cudaS
       a.store_mode = 1;
   }
   const int m_tiles = (int)cdiv(a.M, BM), n_tiles = (int)cdiv(a.N, BN);
-  const unsigned grid = (unsigned)std::min<int64_t>((int64_t)m_tiles * n_tiles, sm_count());
-  conv_tc_kernel<BN><<<grid, TC_THREADS, S::TOTAL, s>>>(map_a, map_w, map_y, a, m_tiles, n_tiles);
-  return check_launch(BN == 64 ? "conv_tc_128x64" : (BN == 128 ? "conv_tc_128x128" : "conv_tc_128x256"));
+  const unsigned grid = (unsigned)std::min<int64_t>((int64_t)m_tiles * n_tiles * splits, sm_count());
+  if (splits > 1) conv_tc_kernel<BN, true><<<grid, TC_THREADS, S::TOTAL, s>>>(map_a, map_w, map_y, a, m_tiles, n_tiles);
+  else conv_tc_kernel<BN, false><<<grid, TC_THREADS, S::TOTAL, s>>>(map_a, map_w, map_y, a, m_tiles, n_tiles);
+  int r = check_launch(BN == 64 ? "conv_tc_128x64" : (BN == 128 ? "conv_tc_128x128" : "conv_tc_128x256"));
+  if (r || splits == 1) return r;
+  splitk_epilogue_kernel<<<(unsigned)cdiv((int64_t)a.M * a.N, 256), 256, 0, s>>>(a);
+  return check_launch("conv_tc_splitk_epilogue");
 }
 
 size_t split_floats(int rows, int ks, int chans) { return (size_t)2 * rows * ks * ks * (cdiv(chans, BKF) * BKF); }
 
 // one (sub-)convolution: re-lay the weights it needs into `wsplit`, then run the GEMM
-int run_tc(const TcProblem& p, const float* w, SplitArgs sp, float* wsplit, const OmtAct* y, const float* bias, uint32_t flags, cudaStream_t s) {
+int run_tc(const TcProblem& p, const float* w, SplitArgs sp, float* wsplit, float* part, const OmtAct* y, const float* bias, uint32_t flags,
+           cudaStream_t s) {
   TcArgs a{};
   a.y = view(y); a.bias = bias;
   a.M = p.n * p.oh * p.ow; a.N = p.rows; a.oh = p.oh; a.ow = p.ow;
@@ -643,11 +707,19 @@ int run_tc(const TcProblem& p, const float* w, SplitArgs sp, float* wsplit, cons
   weight_split_kernel<<<(unsigned)cdiv(total, 256), 256, 0, s>>>(w, wsplit, sp);
   int r = check_launch("conv_tc_weight_split");
   if (r) return r;
-  switch (pick_bn(p)) {
-    case 64: return launch_tc<64>(p, wsplit, a, s);
-    case 128: return launch_tc<128>(p, wsplit, a, s);
-    default: return launch_tc<256>(p, wsplit, a, s);
+  const int bn = pick_bn(p);
+  const int splits = plan_splits(a.M, a.N, p.kh * p.kw * a.cblocks, bn);
+  switch (bn) {
+    case 64: return launch_tc<64>(p, wsplit, a, splits, part, s);
+    case 128: return launch_tc<128>(p, wsplit, a, splits, part, s);
+    default: return launch_tc<256>(p, wsplit, a, splits, part, s);
   }
+}
+// floats of split-K partial tiles this (sub-)convolution needs (0 when it does not split)
+size_t part_floats(const TcProblem& p) {
+  const int64_t M = (int64_t)p.n * p.oh * p.ow;
+  const int splits = plan_splits(M, p.rows, p.kh * p.kw * (int)cdiv(p.c, BKF), pick_bn(p));
+  return splits > 1 ? (size_t)splits * M * p.rows : 0;
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -975,7 +1047,7 @@ int launch_window(const OmtConvGeo* g, const WinPlan& w, const float* xs, const 
   }
   static bool attr_set = false;
   if (!attr_set) {
-    OMT_CUDA(cudaFuncSetAttribute(conv_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
+    OMT_CUDA(cudaFuncSetAttribute((conv_tc_kernel<BN, false>), cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
     attr_set = true;
   }
   TcArgs a = args;
@@ -991,7 +1063,7 @@ int launch_window(const OmtConvGeo* g, const WinPlan& w, const float* xs, const 
   }
   const int m_tiles = g->n * w.tiles_x * w.tiles_y, n_tiles = (int)cdiv(a.N, BN);
   const unsigned grid = (unsigned)std::min<int64_t>((int64_t)m_tiles * n_tiles, sm_count());
-  conv_tc_kernel<BN><<<grid, TC_THREADS, S::TOTAL, s>>>(map_a, map_w, map_y, a, m_tiles, n_tiles);
+  conv_tc_kernel<BN, false><<<grid, TC_THREADS, S::TOTAL, s>>>(map_a, map_w, map_y, a, m_tiles, n_tiles);
   return check_launch(BN == 64 ? "conv_tc_window_128x64" : (BN == 128 ? "conv_tc_window_128x128" : "conv_tc_window_128x256"));
 }
 
@@ -1192,15 +1264,41 @@ bool tc_supported(int kind, const OmtConvGeo* g, const OmtAct* a, const OmtAct* 
   if (g->ci <= 4) return a && a->p && window_ok(g) && g->co % 32 == 0;  // window mode reads x through a staging copy: any layout
   return cl_ok(a, g->ci, g->ih, g->iw) && g->ci >= 8;
 }
+// the stride-phase sub-convolutions of an input gradient, in launch order (csrc/conv.cpp:78-95 of the reference)
+struct Phase { TcProblem p; int ky0, kx0, jy, jx; };
+static std::vector<Phase> dgrad_phases(const OmtConvGeo* g, const float* gy) {
+  std::vector<Phase> out;
+  const int s = g->stride;
+  for (int py = 0; py < s; py++)
+    for (int px = 0; px < s; px++) {
+      const int hi = (int)cdiv(g->ih - py, s), wi = (int)cdiv(g->iw - px, s);
+      if (hi <= 0 || wi <= 0) continue;
+      const int ky0 = (py + g->pad) % s, kx0 = (px + g->pad) % s;
+      const int jy = ky0 < g->ks ? (int)cdiv(g->ks - ky0, s) : 0, jx = kx0 < g->ks ? (int)cdiv(g->ks - kx0, s) : 0;
+      if (jy == 0 || jx == 0) continue;
+      const int qy = (py + g->pad - ky0) / s, qx = (px + g->pad - kx0) / s;
+      // output (i, j) of the phase reads gy[i + qy - ty, j + qx - tx]; with flipped taps ty' = jy-1-ty the first tap sits at qy-(jy-1)
+      TcProblem p{gy, g->n, g->co, g->oh, g->ow, hi, wi, g->ci, jy, jx, 1, qy - (jy - 1), qx - (jx - 1), s, py, px};
+      out.push_back({p, ky0, kx0, jy, jx});
+    }
+  return out;
+}
+static size_t dgrad_part_floats(const OmtConvGeo* g) {
+  size_t m = 0;
+  for (const Phase& ph : dgrad_phases(g, nullptr)) m = std::max(m, part_floats(ph.p));
+  return m;
+}
+
 size_t tc_workspace(int kind, const OmtConvGeo* g) {
   if (kind == 0) {
     if (g->ci <= 4 && window_ok(g)) {
       WinPlan w = plan_window(g);
       return (((w.stage_floats + 63) / 64) * 64 + w.split_floats_) * sizeof(float) + 256;
     }
-    return split_floats(g->co, g->ks, g->ci) * sizeof(float) + 256;
+    TcProblem p{nullptr, g->n, g->ci, g->ih, g->iw, g->oh, g->ow, g->co, g->ks, g->ks, g->stride, -g->pad, -g->pad, 1, 0, 0};
+    return (split_floats(g->co, g->ks, g->ci) + part_floats(p)) * sizeof(float) + 512;
   }
-  if (kind == 1) return split_floats(g->ci, g->ks, g->co) * sizeof(float) + 256;
+  if (kind == 1) return (split_floats(g->ci, g->ks, g->co) + dgrad_part_floats(g)) * sizeof(float) + 512;
   const WgPlan w = plan_wgrad(g);
   return (w.stage_floats + w.part_floats) * sizeof(float) + 256;
 }
@@ -1216,7 +1314,8 @@ int tc_conv_fwd(const OmtConvGeo* g, const OmtAct* x, const float* w, const floa
   if (g->ci <= 4) return run_window_fwd(g, x, w, bias, y, flags, ws, s);
   TcProblem p{x->p, g->n, g->ci, g->ih, g->iw, g->oh, g->ow, g->co, g->ks, g->ks, g->stride, -g->pad, -g->pad, 1, 0, 0};
   SplitArgs sp{g->co, g->ci, g->ks, 0, 0, 0, 0, 0, 0, 1};
-  return run_tc(p, w, sp, (float*)ws, y, bias, flags, s);
+  float* part = (float*)ws + ((split_floats(g->co, g->ks, g->ci) + 63) / 64) * 64;
+  return run_tc(p, w, sp, (float*)ws, part, y, bias, flags, s);
 }
 
 // Input gradient as forward convolutions of gy. Stride 1: one convolution with the weights transposed and flipped and
@@ -1231,6 +1330,7 @@ int tc_conv_dgrad(const OmtConvGeo* g, const OmtAct* gy, const float* w, const O
   }
   const int s = g->stride;
   float* wsplit = (float*)ws;
+  float* part = (float*)ws + ((split_floats(g->ci, g->ks, g->co) + 63) / 64) * 64;  // shared by the phases: they run in order
   bool zeroed = false;
   for (int py = 0; py < s; py++)
     for (int px = 0; px < s; px++) {
@@ -1258,7 +1358,7 @@ int tc_conv_dgrad(const OmtConvGeo* g, const OmtAct* gy, const float* w, const O
       // output (i, j) of the phase reads gy[i + qy - ty, j + qx - tx]; with flipped taps ty' = jy-1-ty the first tap sits at qy-(jy-1)
       TcProblem p{gy->p, g->n, g->co, g->oh, g->ow, hi, wi, g->ci, jy, jx, 1, qy - (jy - 1), qx - (jx - 1), s, py, px};
       SplitArgs sp{g->co, g->ci, g->ks, 0, 0, 0, 1, ky0, kx0, s};
-      int r = run_tc(p, w, sp, wsplit, dx, nullptr, epi, st_);
+      int r = run_tc(p, w, sp, wsplit, part, dx, nullptr, epi, st_);
       if (r) return r;
       wsplit += 2 * (size_t)g->ci * jy * jx * (cdiv(g->co, BKF) * BKF);
     }

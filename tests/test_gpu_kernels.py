@@ -75,7 +75,9 @@ TC_SHAPES = [(2, 3, 64, 32, 7, 2, 3), (3, 3, 24, 63, 11, 4, 2), (2, 4, 24, 20, 5
              # weight-gradient operand modes: [pixels, ci] matrix with several 32-channel blocks; pixel rectangles for 7-, 8-, 9-
              # and 12-wide outputs with stride 1 and 2, odd batch; window mode with 32-multiple output channels
              (2, 64, 128, 16, 1, 1, 0), (4, 256, 512, 14, 1, 1, 0), (3, 128, 128, 7, 3, 1, 1), (5, 512, 64, 7, 3, 2, 1), (2, 96, 160, 9, 3, 1, 1),
-             (2, 64, 96, 12, 5, 2, 2), (3, 256, 64, 8, 1, 2, 0), (3, 3, 64, 63, 11, 4, 2), (2, 4, 32, 20, 5, 2, 2), (2, 1, 32, 28, 3, 1, 1), (2, 3, 96, 40, 3, 1, 1)]
+             (2, 64, 96, 12, 5, 2, 2), (3, 256, 64, 8, 1, 2, 0), (3, 3, 64, 63, 11, 4, 2), (2, 4, 32, 20, 5, 2, 2), (2, 1, 32, 28, 3, 1, 1), (2, 3, 96, 40, 3, 1, 1),
+             # few output tiles and a long reduction: split-K in forward and input gradient (also per stride phase)
+             (2, 256, 256, 4, 3, 1, 1), (4, 512, 512, 2, 3, 1, 1), (8, 128, 256, 8, 3, 2, 1), (2, 512, 136, 4, 1, 1, 0)]
 
 
 @pytest.mark.parametrize("shape", TC_SHAPES)
@@ -118,7 +120,7 @@ def test_tensor_core_path_vs_aten_and_exact_path(capi, shape):
 
 
 @pytest.mark.parametrize("shape,cl_out", [((4, 64, 96, 14, 3, 1, 1), True), ((2, 32, 64, 16, 1, 2, 0), True), ((2, 64, 64, 16, 3, 2, 1), True),
-                                          ((2, 32, 40, 15, 3, 1, 1), False)])
+                                          ((2, 32, 40, 15, 3, 1, 1), False), ((2, 64, 256, 4, 3, 1, 1), True)])
 def test_input_gradient_accumulates_in_the_epilogue(capi, shape, cl_out):
     """OMT_EPI_ACCUM: dx += conv^T(gy, w) (TMA reduce-add for dense channels-last outputs, read-add-write for stride phases
     and NCHW outputs) against a separate input gradient plus add; a geometry outside the tensor-core path is refused."""
