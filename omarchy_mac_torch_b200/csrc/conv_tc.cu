@@ -272,7 +272,7 @@ __device__ __forceinline__ TileCoord decode_tile(const TcArgs& g, int t, int n_t
 template <int BN, bool SPLITK>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_y,
-               const TcArgs g, const int m_tiles, const int n_tiles) {
+               const TcArgs g) {
   using S = Smem<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -287,9 +287,12 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kblocks = g.kh * g.kw * g.cblocks;
+  const int n_tiles = (g.N + BN - 1) / BN;
   int splits = 1;  // a compile-time 1 in the common instantiation
   if constexpr (SPLITK) splits = g.splits;
   const int win_w = SPLITK ? 0 : g.win_w;  // the split-K fields alias the window fields
+  // GEMM row tiles: 128-pixel runs, or in window mode the rectangles of every image (M = images x oh x ow there)
+  const int m_tiles = win_w ? (g.M / (g.oh * g.ow)) * g.tiles_x * g.tiles_y : (g.M + BM - 1) / BM;
   const int total_tiles = m_tiles * n_tiles * splits;
   // k-block range of split sp: [sp * kblocks / splits, (sp + 1) * kblocks / splits)
   auto kb_begin = [kblocks, splits](int t) -> int {
@@ -682,8 +685,8 @@ int launch_tc(const TcProblem& p, const float* wsplit, const TcArgs& args, int s
   }
   const int m_tiles = (int)cdiv(a.M, BM), n_tiles = (int)cdiv(a.N, BN);
   const unsigned grid = (unsigned)std::min<int64_t>((int64_t)m_tiles * n_tiles * splits, sm_count());
-  if (splits > 1) conv_tc_kernel<BN, true><<<grid, TC_THREADS, S::TOTAL, s>>>(map_a, map_w, map_y, a, m_tiles, n_tiles);
-  else conv_tc_kernel<BN, false><<<grid, TC_THREADS, S::TOTAL, s>>>(map_a, map_w, map_y, a, m_tiles, n_tiles);
+  if (splits > 1) conv_tc_kernel<BN, true><<<grid, TC_THREADS, S::TOTAL, s>>>(map_a, map_w, map_y, a);
+  else conv_tc_kernel<BN, false><<<grid, TC_THREADS, S::TOTAL, s>>>(map_a, map_w, map_y, a);
   int r = check_launch(BN == 64 ? "conv_tc_128x64" : (BN == 128 ? "conv_tc_128x128" : "conv_tc_128x256"));
   if (r || splits == 1) return r;
   splitk_epilogue_kernel<<<(unsigned)cdiv((int64_t)a.M * a.N, 256), 256, 0, s>>>(a);
@@ -1063,7 +1066,7 @@ int launch_window(const OmtConvGeo* g, const WinPlan& w, const float* xs, const 
   }
   const int m_tiles = g->n * w.tiles_x * w.tiles_y, n_tiles = (int)cdiv(a.N, BN);
   const unsigned grid = (unsigned)std::min<int64_t>((int64_t)m_tiles * n_tiles, sm_count());
-  conv_tc_kernel<BN, false><<<grid, TC_THREADS, S::TOTAL, s>>>(map_a, map_w, map_y, a, m_tiles, n_tiles);
+  conv_tc_kernel<BN, false><<<grid, TC_THREADS, S::TOTAL, s>>>(map_a, map_w, map_y, a);
   return check_launch(BN == 64 ? "conv_tc_window_128x64" : (BN == 128 ? "conv_tc_window_128x128" : "conv_tc_window_128x256"));
 }
 
