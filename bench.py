@@ -310,7 +310,9 @@ class Train:
         if world > 1:
             from omarchy_mac_torch_b200.dp import DataParallel
             self.dp = DataParallel(self.model, bucket_mb=25.0)
-        self.opt = self.make_opt(self.model.parameters())
+        # (AdamW inside a captured CUDA graph keeps its step counters on the device: capturable=True)
+        self.opt = self.make_opt(self.model.parameters(), capturable=True) if (self.graph and "AdamW" in self.shape["optimizer"]) \
+            else self.make_opt(self.model.parameters())
         xh, yh = self.host_inputs(seed)
         self.xh, self.yh = xh.pin_memory(), yh.pin_memory()
         self.x, self.y = self.xh.to(self.dev), self.yh.to(self.dev)
@@ -437,7 +439,7 @@ TRAIN = {
     "resnet18": lambda: Train("resnet18_b32_train", lambda: _models().kaiming_normal_convs(_models().ResNet18(num_classes=1000)),
                               (32, 3, 64, 64), 1000, _sgd(0.1, momentum=0.9, weight_decay=1e-4), 32, "SGD lr .1 momentum .9 wd 1e-4", graph=True),
     "mobilenetv3": lambda: Train("mobilenetv3_small_b32_train", lambda: _models().MobileNetV3SE(), (32, 3, 224, 224), 1000,
-                                 lambda p: torch.optim.AdamW(p, lr=1e-3, weight_decay=0.01, capturable=True), 32, "AdamW lr 1e-3 wd .01",
+                                 lambda p, capturable=False: torch.optim.AdamW(p, lr=1e-3, weight_decay=0.01, capturable=capturable), 32, "AdamW lr 1e-3 wd .01",
                                  graph=True),
     "resnet50": lambda: Train("resnet50_b256_train", lambda: _models().ResNet50(), (256, 3, 224, 224), 1000,
                               _sgd(0.1, momentum=0.9, nesterov=True, weight_decay=1e-4), 16, "SGD lr .1 momentum .9 nesterov wd 1e-4",
