@@ -1,6 +1,6 @@
-"""Generates the golden fixtures in this directory. Run where the reference checkout is mounted:
+"""Generates the golden fixtures in this directory. Run where a checkout of the reference is available:
 
-    python tests/golden/make_golden.py [/root/reference]
+    python tests/golden/make_golden.py <path to the omarchy-mac-torch checkout>
 
 The reference ships no stored vectors; its checks compare the device with PyTorch's CPU aten on shape lists written in
 its scripts (notes/scripts/conv_kinds_check.py:5, notes/scripts/alexnet_ops_check.py:6,12,16, tools/gemm_bench.py:8-9)
@@ -137,5 +137,7 @@ def make_losses(ref_root):
 
 
 if __name__ == "__main__":
+    if len(sys.argv) != 2:
+        sys.exit(__doc__.split("\n\n")[1])
     make_ops()
-    make_losses(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    make_losses(sys.argv[1])
