@@ -5,13 +5,17 @@
 Prints ONE JSON line. A "step" is one pass of the hot path over one batch of synthetic input (seeded; the reference
 benchmarks on random tensors too). Workloads:
 
-  resnet50  (default) BASELINE config 5: ResNet-50 training step, batch 256 per GPU, 224x224, SGD nesterov, on the
-            "omarchy_mac_torch" device; with --gpus N each rank takes its own batch (weak scaling) and gradients are
-            averaged by the bucketed all-reduce of omarchy_mac_torch_b200.dp. This is the configuration the metric
-            "train ms/step at 1/2/4/8 B200" is quoted on, and it fits one GPU.
-  plaincnn / resnet18 / mobilenetv3   BASELINE configs 2-4, training step on the device.
-  conv1     BASELINE config 1: AlexNet conv1 fwd + dgrad + wgrad, x[16,3,224,224], w[64,3,11,11], stride 4, pad 2
+  resnet50  (default) ResNet-50 training step, batch 256 per GPU, 224x224, SGD nesterov, on the "omarchy_mac_torch"
+            device; with --gpus N each rank takes its own batch (weak scaling) and gradients are averaged by the
+            bucketed all-reduce of omarchy_mac_torch_b200.dp. This is the configuration the metric "train ms/step at
+            1/2/4/8 B200" is quoted on, and it fits one GPU. At N = 1 the line also carries a `secondary` block: the
+            AlexNet-conv1 layer, the ResNet-18 step and the bandwidth-bound kernel table, each a few seconds.
+  plaincnn / resnet18 / mobilenetv3   the three-block CNN (batch 128, 32x32), ResNet-18 (batch 32, 64x64) and
+            MobileNetV3-Small with squeeze-excite (batch 32, 224x224) training steps on the device.
+  conv1     AlexNet conv1 fwd + dgrad + wgrad, x[16,3,224,224], w[64,3,11,11], stride 4, pad 2
             (tools/gemm_bench.py "alex1"), called through the C ABI.
+  conv3x3   one 256->256 3x3 layer at 28x28, batch 128, channels-last (the small case of the ncu captures).
+  hbm       every bandwidth-bound kernel family on tensors far larger than L2.
 
 Timing: W >= 3 untimed warm-up steps, then K steps timed with CUDA events on the launching stream, a barrier and a
 device synchronize on both sides, max over ranks; L2 is flushed between timed iterations whenever the step's working
@@ -34,6 +38,19 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 L2_BYTES = 126 << 20
+
+# DRAM traffic of the tensor-core conv kernels, from the ncu capture of the `conv3x3` workload (profiles/
+# conv3x3_256_28_b128_tc_kernels_ncu_full.md): dram__bytes_read.sum + dram__bytes_write.sum per launch over the
+# algorithmic bytes of that launch (float32 x + y + w = 207.96 MB). Traffic grows with the activation bytes, so a step's
+# conv traffic is its algorithmic conv bytes per pass times these ratios.
+NCU_CONV_TRAFFIC = {"fwd": (107.9 + 59.6) / 207.96, "dgrad": (108.0 + 59.9) / 207.96, "wgrad": (205.6 + 4.2) / 207.96}
+NCU_CONV_TRAFFIC_SOURCE = ("ncu dram__bytes_read.sum + dram__bytes_write.sum of conv_tc_kernel / wgrad_tc_kernel on the conv3x3 case "
+                           "(fwd 167.5, dgrad 167.9, wgrad 209.8 MB per launch; 208.0 MB algorithmic), scaled by algorithmic bytes per pass")
+
+
+def conv_traffic(t, reps):
+    """Bytes of DRAM traffic per step for the conv calls recorded in `t` (omt_conv_timing_*), by the measured ratios."""
+    return sum(v[3] / reps * NCU_CONV_TRAFFIC[k] for k, v in t.items())
 
 
 def measured_peaks():
@@ -155,14 +172,15 @@ class ConvLayer:
         self.capi.conv_timing(False)
         peak = peaks["bf16_tflops"] / 2 / 3
         ach = self.flops / (ms * 1e-3) / 1e12
-        return {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak, "traffic": None,
+        return {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
+                "traffic": conv_traffic(t, 3), "traffic_source": NCU_CONV_TRAFFIC_SOURCE, "algorithmic_bytes": sum(v[3] for v in t.values()) / 3,
                 "peak_source": f"{peaks['source']} bf16 burst / 2 (tf32) / 3 (3xTF32)",
                 "kernel": "conv fwd + dgrad + wgrad of one layer (all kernels of the three calls)",
                 "per_pass": {k: {"tflops": (v[0] / (v[1] * 1e-3) / 1e12 if v[1] else None), "ms": v[1] / 3, "calls": v[2] // 3} for k, v in t.items()}}
 
 
 CONV = {
-    # BASELINE config 1: the AlexNet conv1 shape, NCHW as the reference benchmarks it
+    # the AlexNet conv1 shape, NCHW as the reference benchmarks it (tools/gemm_bench.py)
     "conv1": lambda: ConvLayer("alexnet_conv1_fwd_dgrad_wgrad", 16, 3, 64, 224, 11, 4, 2, False),
     # a mid-network ResNet layer, channels-last, inputs + outputs larger than L2: the small case the ncu captures use
     "conv3x3": lambda: ConvLayer("conv3x3_256_28_b128_fwd_dgrad_wgrad", 128, 256, 256, 28, 3, 1, 1, True),
@@ -417,7 +435,8 @@ class Train:
         sustained = peaks.get("bf16_tflops_sustained") or peaks["bf16_tflops"]
         peak = sustained / 2 / 3
         ach = flops / (conv_ms * 1e-3) / 1e12 if conv_ms else 0.0
-        return {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak, "traffic": None,
+        return {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
+                "traffic": conv_traffic(t, 2), "traffic_source": NCU_CONV_TRAFFIC_SOURCE, "algorithmic_bytes": sum(v[3] for v in t.values()) / 2,
                 "peak_source": f"{peaks['source']} bf16 sustained / 2 (tf32) / 3 (3xTF32)",
                 "kernel": "dense conv fwd + dgrad + wgrad (all conv calls of one step)",
                 "conv_flops_per_step": flops, "conv_ms_per_step": conv_ms, "conv_share_of_step": conv_ms / ms if ms else None,
@@ -442,7 +461,7 @@ TRAIN = {
                                  lambda p, capturable=False: torch.optim.AdamW(p, lr=1e-3, weight_decay=0.01, capturable=capturable), 32, "AdamW lr 1e-3 wd .01",
                                  graph=True),
     "resnet50": lambda: Train("resnet50_b256_train", lambda: _models().ResNet50(), (256, 3, 224, 224), 1000,
-                              _sgd(0.1, momentum=0.9, nesterov=True, weight_decay=1e-4), 16, "SGD lr .1 momentum .9 nesterov wd 1e-4",
+                              _sgd(0.1, momentum=0.9, nesterov=True, weight_decay=1e-4), 256, "SGD lr .1 momentum .9 nesterov wd 1e-4",
                               compile=True),
 }
 
@@ -494,31 +513,85 @@ def time_steps(fn, steps, warmup, world, flush):
     return max_over_ranks(total / steps, world)
 
 
+def secondary(peaks):
+    """Short measurements of the other named targets, carried beside the headline so that one run records them: the
+    AlexNet-conv1 layer through the C ABI (TFLOP/s of fwd+dgrad+wgrad against the burst 3xTF32 peak), the ResNet-18 batch-32
+    step (ms) and the bandwidth-bound kernel table (GB/s against the measured copy bandwidth). Same timing rules as the
+    headline (warm-up, CUDA events, L2 flushed where the working set is smaller than L2)."""
+    out = {}
+    for key, name, steps in (("conv1", "conv1", 30), ("resnet18", "resnet18", 30), ("hbm", "hbm", 1)):
+        try:
+            w = WORKLOADS[name]()
+            w.setup_gpu(seed=0, world=1)
+            if name == "hbm":
+                roof = w.roofline(0.0, peaks)
+                out[key] = {"unit": "GB/s", "peak": roof["peak"], "per_kernel": roof["per_kernel"], "slowest": roof["kernel"]}
+            else:
+                flush = w.bytes_resident < 2 * L2_BYTES
+                ms = time_steps(w.step, steps, 5, 1, flush)
+                out[key] = {"workload": w.name, "ms_per_step": ms, "value": w.value(ms), "unit": w.unit, **w.shape,
+                            "l2": "flushed between timed iterations" if flush else "working set > L2"}
+                if name == "conv1":
+                    roof = w.roofline(ms, peaks)
+                    out[key].update(frac=roof["frac"], peak=roof["peak"], peak_source=roof["peak_source"], per_pass=roof["per_pass"])
+                elif getattr(w, "launches_per_step", None):
+                    out[key]["kernels_per_step"] = w.launches_per_step
+            del w
+            torch.cuda.synchronize()
+        except Exception as e:  # a failure here must not take the headline line with it
+            out[key] = {"error": f"{type(e).__name__}: {e}"[:300]}
+    return out
+
+
+def config_of(wl, world):
+    """The `config` object: identical keys and values in this arm's line and in the reference arm's."""
+    cfg = {"workload": wl.name, **wl.shape}
+    if not wl.higher:
+        cfg["parallelism"] = f"dp{world}"
+    return cfg
+
+
+def cpu_arm(wl, warmup, steps, budget_s):
+    """Times the reference's CPU arm (PyTorch CPU aten on every host core, tools/acceptance.py:77,91) on the workload's own
+    shapes. One step is always run untimed first; if `warmup + steps` steps at that step's duration fit in `budget_s`
+    they all run, otherwise the remaining warm-up is dropped and as many timed steps as fit (at least 2) run. Returns
+    (ms per step, timed steps, warm-up steps, threads)."""
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    ins = wl.cpu_setup()
+    t0 = time.perf_counter()
+    wl.cpu_step(ins)
+    first = time.perf_counter() - t0
+    warm = 1
+    if (warmup - 1 + steps) * first <= budget_s:
+        for _ in range(warmup - 1):
+            wl.cpu_step(ins)
+            warm += 1
+    else:
+        steps = int(max(2, min(steps, (budget_s - first) // max(first, 1e-9))))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        wl.cpu_step(ins)
+    ms = (time.perf_counter() - t0) / steps * 1e3 * wl.cpu_scale()
+    return ms, steps, warm, cores
+
+
+def cpu_sample_text(wl, steps, warm, cores):
+    return (f"{steps} timed steps after {warm} warm-up of the same workload at its full size on PyTorch CPU aten ({torch.__version__}), "
+            f"{cores} threads" + (f", batch {wl.cpu_batch} scaled x{wl.cpu_scale():g} to the full batch" if wl.cpu_scale() != 1 else ""))
+
+
 def run_reference(args, wl):
     """The reference's CPU arm: PyTorch CPU aten on all host cores (tools/acceptance.py:77,91)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    cores = os.cpu_count() or 1
-    torch.set_num_threads(cores)
-    ins = wl.cpu_setup()
-    budget, t_start = 150.0, time.perf_counter()  # keep the whole arm within a few minutes
-    wl.cpu_step(ins)
-    for _ in range(max(0, min(args.warmup, 2) - 1)):
-        if time.perf_counter() - t_start < budget / 3:
-            wl.cpu_step(ins)
-    done, t0 = 0, time.perf_counter()
-    while done < args.steps and (done == 0 or time.perf_counter() - t_start < budget):
-        wl.cpu_step(ins)
-        done += 1
-    ms = (time.perf_counter() - t0) / done * 1e3 * wl.cpu_scale()
+    ms, steps, warm, cores = cpu_arm(wl, args.warmup, args.steps, budget_s=240.0)
     v = wl.value(ms)
-    line = {"impl": "reference", "metric": wl.metric, "value": v, "unit": wl.unit, "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": wl.higher, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f32", "data": "synthetic", "config": {"workload": wl.name, **wl.shape},
-            "cpu_baseline": {"value": v, "unit": wl.unit, "cores": cores, "kind": "reference",
-                             "sample": f"{done} steps of PyTorch CPU aten ({torch.__version__}) on {cores} threads"
-                                       + (f", batch {wl.cpu_batch} scaled x{wl.cpu_scale():g} to the full batch" if wl.cpu_scale() != 1 else "")},
+    line = {"impl": "reference", "metric": wl.metric, "value": v, "unit": wl.unit, "n_gpus": args.gpus, "steps": steps,
+            "warmup": warm, "ms_per_step": ms, "higher_is_better": wl.higher, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic", "config": config_of(wl, args.gpus),
+            "cpu_baseline": {"value": v, "unit": wl.unit, "cores": cores, "kind": "reference", "sample": cpu_sample_text(wl, steps, warm, cores)},
             "e2e": {"value": v, "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
 
@@ -531,6 +604,7 @@ def main():
     ap.add_argument("--workload", default="resnet50", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-secondary", action="store_true", help="resnet50 at N=1: skip the extra conv1 / resnet18 / hbm measurements")
     ap.add_argument("--eager", action="store_true", help="training workloads: call the nn.Module directly instead of through the compile backend")
     ap.add_argument("--compile", action="store_true", help="training workloads: call the model through the compile backend")
     ap.add_argument("--graph", action="store_true", help="training workloads: replay the whole step as one CUDA graph")
@@ -576,6 +650,7 @@ def main():
     ms_e2e = time_steps(wl.e2e_step, args.steps, args.warmup, world, flush)
     clocks = sampler.stop() if rank == 0 else None
     roof = wl.roofline(ms, peaks)  # runs extra steps: every rank takes part (they contain the gradient all-reduce)
+    spread = wl.dp.param_spread() if getattr(wl, "dp", None) is not None else None  # a collective: every rank calls it
     barrier(world)
     if rank != 0:
         if world > 1:
@@ -585,27 +660,22 @@ def main():
     line = {"metric": wl.metric, "value": wl.value(ms) * agg, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": wl.higher, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
-            "config": {"workload": wl.name, **wl.shape, "l2": "flushed between timed iterations" if flush else "working set > L2"},
+            "config": config_of(wl, world), "l2": "flushed between timed iterations" if flush else "working set > L2",
             "roofline": roof,
             "e2e": {"value": wl.value(ms_e2e) * agg, "unit": wl.unit, "ms_per_step": ms_e2e, "h2d_bytes_per_step": wl.h2d_bytes,
                     "d2h_bytes_per_step": wl.d2h_bytes},
             "gpu_launches": int(launches) * args.steps, "clocks": clocks}
     if not wl.higher:
         line["images_per_s"] = wl.in_shape[0] * world / (ms * 1e-3)
-        line["config"]["parallelism"] = f"dp{world}"
+    if spread is not None:  # replicas must end a step with bit-identical parameters: exactly 0
+        line["rank_param_spread"] = spread
+    if args.workload == "resnet50" and world == 1 and not args.no_secondary:
+        line["secondary"] = secondary(peaks)
     if not args.no_cpu_baseline:
-        cores = os.cpu_count() or 1
-        torch.set_num_threads(cores)
-        ins = wl.cpu_setup()
-        wl.cpu_step(ins)
-        reps, t0 = 0, time.perf_counter()
-        while reps < 1 or (time.perf_counter() - t0 < 12 and reps < 200):
-            wl.cpu_step(ins)
-            reps += 1
-        cms = (time.perf_counter() - t0) / reps * 1e3 * wl.cpu_scale()
+        # bounded sample of the same workload at its full size: one untimed step, then as many as fit in ~20 s (at least 2)
+        cms, csteps, cwarm, cores = cpu_arm(wl, 1, 200, budget_s=20.0)
         line["cpu_baseline"] = {"value": wl.value(cms), "unit": wl.unit, "cores": cores, "kind": "reference", "ms_per_step": cms,
-                                "sample": f"{reps} steps of the same workload on PyTorch CPU aten (the reference's CPU arm), {cores} threads"
-                                          + (f", batch {wl.cpu_batch} scaled x{wl.cpu_scale():g} to the full batch" if wl.cpu_scale() != 1 else "")}
+                                "sample": cpu_sample_text(wl, csteps, cwarm, cores)}
     print(json.dumps(line))
     if world > 1:
         torch.distributed.destroy_process_group()

@@ -52,7 +52,7 @@ typedef struct OmtAct {
 enum {
   OMT_EPI_BIAS = 1,        /* y += bias[co]          (reference hb bit 0, omarchy_mac_torch/gemm.py:37) */
   OMT_EPI_RELU = 2,        /* y = max(y, 0)          (reference hb bit 1, omarchy_mac_torch/gemm.py:38) */
-  OMT_EPI_BNSTATS = 4,     /* also accumulate per-channel sum / sum of squares of y into stats[2*co] (must be zeroed) */
+  OMT_EPI_BNSTATS = 4,     /* omt_conv_fwd: also write batch-norm partial statistics of y (see omt_conv_bnstats_groups) */
   OMT_EPI_ACCUM = 8,       /* omt_conv_dgrad: dx += result (gradient of a tensor with a second consumer, e.g. a residual branch) */
   OMT_FORCE_SIMT = 0x100,  /* skip the tcgen05 path (used by tests to cross-check the two paths) */
   OMT_FORCE_TC = 0x200     /* fail with OMT_EINVAL instead of taking the SIMT path */
@@ -115,9 +115,20 @@ size_t omt_conv_workspace_bytes(int kind, const OmtConvGeo* g, uint32_t flags);
 
 /* y[n,co,oh,ow] = conv(x, w) (+bias)(ReLU). w is [co, ci, ks, ks] contiguous. Replaces gemm_forward
  * (csrc/conv.cpp:70-77) and the kind-0 generated kernel (omarchy_mac_torch/gemm.py:25-42).
- * With OMT_EPI_BNSTATS, stats[0..co) += sum_y, stats[co..2co) += sum_y^2 of the stored values. */
+ * With OMT_EPI_BNSTATS the epilogue also reduces the values it stores into batch-norm partial statistics, so that the
+ * BatchNorm that follows need not read y for its statistics pass (the reference's plans run bn_stats_part over y,
+ * csrc/plans.cpp:180-194): for every group of 32 output rows and every channel, `stats` receives the group's sum and its
+ * sum of squared deviations from the group's own mean, then the groups' row counts; omt_bn_stats_from_partials merges
+ * them. `stats` must hold omt_conv_bnstats_floats(groups, co) floats; nothing needs zeroing; the result is
+ * deterministic. Only calls for which omt_conv_bnstats_groups() is non-zero may pass the flag. */
 int omt_conv_fwd(const OmtConvGeo* g, const OmtAct* x, const float* w, const float* bias, const OmtAct* y,
                  float* stats, uint32_t flags, void* workspace, size_t workspace_bytes, omt_stream_t stream);
+/* Number of 32-row groups omt_conv_fwd(OMT_EPI_BNSTATS) writes partial statistics for with these operands, or 0 when that
+ * call cannot produce them (a geometry or layout off the tensor-core path, an output that is not dense channels-last, a
+ * reduction split over several CTAs): the caller then runs omt_bn_stats on y instead. */
+int32_t omt_conv_bnstats_groups(const OmtConvGeo* g, const OmtAct* x, const OmtAct* y);
+/* Floats of the partial-statistics buffer: groups * (2 * co + 1) values and ceil(co / 32) words the merge uses. */
+size_t omt_conv_bnstats_floats(int32_t groups, int32_t co);
 
 /* dx[n,ci,ih,iw] = conv^T(gy, w). Any stride 1..4: strided convs are split into stride^2 phases, each a dense
  * GEMM over the taps that land on it, batched in one launch. Replaces gemm_grad_input (csrc/conv.cpp:78-100) and
@@ -160,6 +171,9 @@ int omt_conv_bias_grad(const OmtAct* gy, int32_t n, int32_t c, int32_t h, int32_
  * milliseconds and the number of calls; `reset` clears the records. */
 int omt_conv_timing(int enable);
 int omt_conv_timing_read(double flops[3], double ms[3], int64_t calls[3], int reset);
+/* The summed algorithmic bytes of the recorded calls per pass: float32 input + output activation + weights of each call
+ * (what one pass must move through HBM at least once). Read it before omt_conv_timing_read(..., reset = 1). */
+int omt_conv_timing_bytes(double bytes[3]);
 
 /* ---- depthwise convolution: reference dw_fwd/dw_gin/dw_gwt and dwg_* (csrc/conv.cpp:194-229) ------------------- */
 
@@ -181,9 +195,12 @@ enum { OMT_BN_RELU = 1 /* apply / mask ReLU */, OMT_BN_FUNCTIONAL = 2 /* running
 int omt_bn_stats(const OmtAct* x, int32_t n, int32_t c, int32_t h, int32_t w, float* mean, float* var,
                  float* invstd, float* rm, float* rv, float* new_rm, float* new_rv, float momentum, float eps,
                  uint32_t flags, omt_stream_t stream);
-/* Same, from sums the conv epilogue accumulated (OMT_EPI_BNSTATS): sums[0..c)=sum y, sums[c..2c)=sum y^2. */
-int omt_bn_stats_from_sums(const float* sums, int64_t count, int32_t c, float* mean, float* var, float* invstd,
-                           float* rm, float* rv, float momentum, float eps, omt_stream_t stream);
+/* Same outputs as omt_bn_stats, from the partial statistics a conv epilogue wrote (OMT_EPI_BNSTATS; `groups` from
+ * omt_conv_bnstats_groups): the groups are merged pairwise with the exact update for mean and squared deviations, in a
+ * fixed order, so the variance is accurate for any mean (the property bn_stats_part.wgsl:22-31 gets from its shift). */
+int omt_bn_stats_from_partials(const float* partials, int32_t groups, int32_t c, float* mean, float* var, float* invstd,
+                               float* rm, float* rv, float* new_rm, float* new_rv, float momentum, float eps,
+                               uint32_t flags, omt_stream_t stream);
 /* y = (x-mean)*invstd*gamma+beta, ReLU with OMT_BN_RELU (bn_apply.wgsl:17-18, bn_relu.wgsl:17-18). */
 int omt_bn_apply(const OmtAct* x, const OmtAct* y, int32_t n, int32_t c, int32_t h, int32_t w, const float* mean,
                  const float* invstd, const float* gamma, const float* beta, uint32_t flags, omt_stream_t stream);
@@ -194,6 +211,13 @@ int omt_bn_apply(const OmtAct* x, const OmtAct* y, int32_t n, int32_t c, int32_t
 int omt_bn_apply_add(const OmtAct* x, const OmtAct* res, const OmtAct* y, int32_t n, int32_t c, int32_t h, int32_t w,
                      const float* mean, const float* invstd, const float* gamma, const float* beta, uint32_t flags,
                      omt_stream_t stream);
+/* omt_bn_apply followed by the plan's 2x2 stride-2 max pool (omt_pool2_fwd) in one pass over x: z[n,c,h/2,w/2] is the
+ * pooled output and idx (strides of z; may be NULL) its argmax in {0..3}; y (full resolution, what the ReLU-masked
+ * backward reads; y->p may be NULL) is written on the way. The reference runs bn_relu then pool_fwd as two dispatches
+ * (csrc/plans.cpp:180-194, 188-199). Needs even h and w; the three tensors share one layout. */
+int omt_bn_apply_pool2(const OmtAct* x, const OmtAct* y, const OmtAct* z, uint8_t* idx, int32_t n, int32_t c, int32_t h,
+                       int32_t w, const float* mean, const float* invstd, const float* gamma, const float* beta,
+                       uint32_t flags, omt_stream_t stream);
 /* Eval mode: invstd = rsqrt(rv+eps) computed on the fly (bn_eval_inv.wgsl, bn_relu_rv.wgsl). */
 int omt_bn_eval(const OmtAct* x, const OmtAct* y, int32_t n, int32_t c, int32_t h, int32_t w, const float* rm,
                 const float* rv, const float* gamma, const float* beta, float eps, uint32_t flags,

@@ -79,13 +79,17 @@ SIGNATURES = {
     "omt_conv_bias_grad": (_I, [_A, _I, _I, _I, _I, _P, _F, _P]),
     "omt_conv_timing": (_I, [_I]),
     "omt_conv_timing_read": (_I, [C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_int64), _I]),
+    "omt_conv_timing_bytes": (_I, [C.POINTER(C.c_double)]),
     "omt_dw_fwd": (_I, [_G, _A, _P, _P, _A, _U, _P]),
     "omt_dw_dgrad": (_I, [_G, _A, _P, _A, _P]),
     "omt_dw_wgrad": (_I, [_G, _A, _A, _P, _F, _P]),
     "omt_bn_stats": (_I, [_A, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _F, _F, _U, _P]),
-    "omt_bn_stats_from_sums": (_I, [_P, _I64, _I, _P, _P, _P, _P, _P, _F, _F, _P]),
+    "omt_bn_stats_from_partials": (_I, [_P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _F, _F, _U, _P]),
+    "omt_conv_bnstats_groups": (C.c_int32, [_G, _A, _A]),
+    "omt_conv_bnstats_floats": (_SZ, [C.c_int32, C.c_int32]),
     "omt_bn_apply": (_I, [_A, _A, _I, _I, _I, _I, _P, _P, _P, _P, _U, _P]),
     "omt_bn_apply_add": (_I, [_A, _A, _A, _I, _I, _I, _I, _P, _P, _P, _P, _U, _P]),
+    "omt_bn_apply_pool2": (_I, [_A, _A, _A, _P, _I, _I, _I, _I, _P, _P, _P, _P, _U, _P]),
     "omt_bn_eval": (_I, [_A, _A, _I, _I, _I, _I, _P, _P, _P, _P, _F, _U, _P]),
     "omt_bn_backward": (_I, [_A, _A, _A, _A, _I, _I, _I, _I, _P, _P, _P, _P, _F, _U, _P]),
     "omt_bn_backward_add": (_I, [_A, _A, _A, _A, _A, _I, _I, _I, _I, _P, _P, _P, _P, _F, _U, _P]),
@@ -173,10 +177,11 @@ def conv_timing(enable):
 
 
 def conv_timing_read(reset=True):
-    """{pass: (flops, ms, calls)} for fwd / dgrad / wgrad since the last reset."""
-    f, m, c = (C.c_double * 3)(), (C.c_double * 3)(), (C.c_int64 * 3)()
+    """{pass: (flops, ms, calls, algorithmic bytes)} for fwd / dgrad / wgrad since the last reset."""
+    f, m, c, b = (C.c_double * 3)(), (C.c_double * 3)(), (C.c_int64 * 3)(), (C.c_double * 3)()
+    call("omt_conv_timing_bytes", b)
     call("omt_conv_timing_read", f, m, c, int(reset))
-    return {k: (f[i], m[i], c[i]) for i, k in enumerate(("fwd", "dgrad", "wgrad"))}
+    return {k: (f[i], m[i], c[i], b[i]) for i, k in enumerate(("fwd", "dgrad", "wgrad"))}
 
 
 def kernel_counts(reset=False):
@@ -278,6 +283,32 @@ def bn_train(x, gamma, beta, rm, rv, momentum=0.1, eps=1e-5, relu=False, functio
     y = torch.empty_like(x)
     call("omt_bn_apply", act(x), act(y), n, c, h, w, ptr(mean), ptr(invstd), ptr(gamma), ptr(beta), BN_RELU if relu else 0, stream_handle())
     return (y, mean, invstd, nrm, nrv) if functional else (y, mean, invstd)
+
+
+def conv_fwd_bnstats(x, w, bias=None, stride=1, pad=0, flags=0):
+    """Forward convolution into a channels-last y with the batch-norm partial statistics of y taken in the epilogue.
+    -> y, partials, groups; groups == 0 (and partials None) when this call cannot produce them."""
+    import torch
+    n, ci, ih, iw = x.shape
+    co, _, ks, _ = w.shape
+    g = geo(n, ci, co, ih, iw, ks, stride, pad)
+    y = _empty((n, co, g.oh, g.ow), x, True)
+    groups = lib().omt_conv_bnstats_groups(g, act(x), act(y))
+    if groups == 0:
+        return conv_fwd(x, w, bias, stride, pad, flags, cl=True), None, 0
+    part = torch.full((lib().omt_conv_bnstats_floats(groups, co),), float("nan"), device=x.device, dtype=torch.float32)
+    call("omt_conv_fwd", g, act(x), ptr(w), ptr(bias), act(y), ptr(part), flags | EPI_BNSTATS | (EPI_BIAS if bias is not None else 0), None, 0,
+         stream_handle())
+    return y, part, groups
+
+
+def bn_stats_from_partials(part, groups, c, rm=None, rv=None, momentum=0.1, eps=1e-5, functional=False):
+    """-> mean, var, invstd (and new_rm, new_rv when functional) from what conv_fwd_bnstats wrote."""
+    mean, var, invstd = (_empty((c,), part) for _ in range(3))
+    nrm, nrv = (_empty((c,), part), _empty((c,), part)) if functional else (None, None)
+    call("omt_bn_stats_from_partials", ptr(part), groups, c, ptr(mean), ptr(var), ptr(invstd), ptr(rm), ptr(rv), ptr(nrm), ptr(nrv), momentum, eps,
+         BN_FUNCTIONAL if functional else 0, stream_handle())
+    return (mean, var, invstd, nrm, nrv) if functional else (mean, var, invstd)
 
 
 def bn_eval(x, gamma, beta, rm, rv, eps=1e-5, relu=False):

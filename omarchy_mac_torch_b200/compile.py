@@ -8,6 +8,7 @@ those graphs to the fused `omt::` ops, and the graph runs op by op on the device
   2. threshold_backward -> native_batch_norm_backward -> omt.bn_relu_backward (ReLU mask folded into the BN backward)
      the same where the masked gradient also feeds the identity branch -> omt.bn_add_relu_backward
   3. conv -> [eval BatchNorm] -> [ReLU]               -> omt.conv_act / omt.conv_bn_act_eval
+     conv -> training BatchNorm [+ identity] [ReLU]   -> omt.conv_bn_train (batch statistics reduced in the conv epilogue)
   +  add(convolution_backward(...)[0], g) with g a gradient nobody else reads -> omt.conv_backward_acc (the input
      gradient is accumulated into g by the conv epilogue: the joins of residual branches in the backward graph)
 
@@ -266,12 +267,48 @@ def fuse_conv_epilogues(graph):
     return done
 
 
+def fuse_conv_bn_train(graph):
+    """A dense conv whose output feeds a training BatchNorm (already rewritten to omt.bn_relu_train / omt.bn_add_relu_train by
+    the passes above, or still the plain aten op): one op, so that the conv epilogue can reduce the batch statistics. The
+    conv output stays an output of the fused op (the backward graph keeps it)."""
+    done = 0
+    for bn in list(graph.nodes):
+        if _is(bn, omt.bn_relu_train.default):
+            x, res, (w, b, rm, rv, momentum, eps), act = bn.args[0], None, bn.args[1:7], 1
+        elif _is(bn, omt.bn_add_relu_train.default):
+            x, res, (w, b, rm, rv, momentum, eps), act = bn.args[0], bn.args[1], bn.args[2:8], 1
+        elif _is(bn, aten._native_batch_norm_legit_functional.default):
+            x, res, (w, b, rm, rv, training, momentum, eps), act = bn.args[0], None, bn.args[1:8], 0
+            if not training or None in (w, b, rm, rv):
+                continue
+        else:
+            continue
+        if not _dense_conv(x) or res is x:
+            continue
+        order = {n: i for i, n in enumerate(graph.nodes)}
+        if any(order[u] < order[bn] for u in x.users):  # every other reader of the conv output has to come after the fused op
+            continue
+        cx, cw, cb, stride, padding = x.args[:5]
+        with graph.inserting_before(bn):
+            fused = graph.call_function(omt.conv_bn_train.default, (cx, cw, cb, list(stride), list(padding), res, w, b, rm, rv, momentum, eps, act))
+            yconv = graph.call_function(operator.getitem, (fused, 0))
+        yconv.meta = dict(x.meta)
+        for idx, gi in _items(bn).items():
+            gi.replace_all_uses_with(_getitem_after(graph, bn, fused, idx + 1, gi.meta))
+            graph.erase_node(gi)
+        graph.erase_node(bn)
+        x.replace_all_uses_with(yconv)
+        graph.erase_node(x)
+        done += 1
+    return done
+
+
 def rewrite(gm):
     """Apply the three passes to a GraphModule in place; returns {pass: rewrites}."""
     g = gm.graph
     stats = {"bn_relu": fuse_bn_relu(g), "bn_add_relu": fuse_bn_add_relu(g), "bn_relu_backward": fuse_bn_relu_backward(g),
              "bn_add_relu_backward": fuse_bn_add_relu_backward(g), "conv_epilogue": fuse_conv_epilogues(g),
-             "dgrad_accumulate": fuse_dgrad_accumulate(g)}
+             "conv_bn_train": fuse_conv_bn_train(g), "dgrad_accumulate": fuse_dgrad_accumulate(g)}
     g.eliminate_dead_code()
     g.lint()
     gm.recompile()

@@ -291,6 +291,84 @@ static int launch_ew(const BnEw& a, bool relu, bool nhwc, cudaStream_t s, const 
   return check_launch(name);
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// normalise (+ReLU) and 2x2 stride-2 max pool in one pass: x is read once; y (full resolution, what the backward masks
+// with) is optional; z is the pooled output and idx in {0..3} = dy*2+dx of the first maximum (pool_fwd.wgsl:15-21).
+// ---------------------------------------------------------------------------------------------------------------
+struct BnPool {
+  ActView x, y, z;
+  uint8_t* idx;
+  const float* mean; const float* inv; const float* gamma; const float* beta;
+  int n, c, oh, ow;
+  bool relu;
+};
+__device__ __forceinline__ void pool4(const float v[4], float& best, int& bi) {
+  best = v[0]; bi = 0;
+  if (v[1] > best) { best = v[1]; bi = 1; }
+  if (v[2] > best) { best = v[2]; bi = 2; }
+  if (v[3] > best) { best = v[3]; bi = 3; }
+}
+// channels-last, c % 4 == 0: one thread per output pixel and 4 channels
+__global__ void __launch_bounds__(256) bn_pool2_nhwc4(BnPool a) {
+  const int c4 = a.c >> 2;
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (int64_t)a.n * a.oh * a.ow * c4) return;
+  const int ch = (int)(i % c4) * 4;
+  int64_t r = i / c4;
+  const int ox = (int)(r % a.ow); r /= a.ow;
+  const int oy = (int)(r % a.oh), img = (int)(r / a.oh);
+  const float4 mean = __ldg(reinterpret_cast<const float4*>(a.mean + ch)), inv = __ldg(reinterpret_cast<const float4*>(a.inv + ch));
+  const float4 ga = __ldg(reinterpret_cast<const float4*>(a.gamma + ch)), be = __ldg(reinterpret_cast<const float4*>(a.beta + ch));
+  const float iv[4] = {inv.x, inv.y, inv.z, inv.w}, gm[4] = {ga.x, ga.y, ga.z, ga.w}, mu[4] = {mean.x, mean.y, mean.z, mean.w}, bt[4] = {be.x, be.y, be.z, be.w};
+  float v[4][4];  // [channel][window position]
+#pragma unroll
+  for (int k = 0; k < 4; k++) {
+    const int64_t off = a.x.off(img, ch, 2 * oy + (k >> 1), 2 * ox + (k & 1));
+    const float4 xv = __ldg(reinterpret_cast<const float4*>(a.x.p + off));
+    const float in[4] = {xv.x, xv.y, xv.z, xv.w};
+    float o[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      // same operation order as bn_ew_one: ((x - mean) * inv) * gamma + beta
+      o[j] = (in[j] - mu[j]) * iv[j] * gm[j] + bt[j];
+      if (a.relu) o[j] = fmaxf(o[j], 0.f);
+      v[j][k] = o[j];
+    }
+    if (a.y.p) *reinterpret_cast<float4*>(a.y.p + a.y.off(img, ch, 2 * oy + (k >> 1), 2 * ox + (k & 1))) = make_float4(o[0], o[1], o[2], o[3]);
+  }
+  float best[4];
+  int bi[4];
+#pragma unroll
+  for (int j = 0; j < 4; j++) pool4(v[j], best[j], bi[j]);
+  const int64_t zo = a.z.off(img, ch, oy, ox);
+  *reinterpret_cast<float4*>(a.z.p + zo) = make_float4(best[0], best[1], best[2], best[3]);
+  if (a.idx) *reinterpret_cast<uchar4*>(a.idx + zo) = make_uchar4((uint8_t)bi[0], (uint8_t)bi[1], (uint8_t)bi[2], (uint8_t)bi[3]);
+}
+// any layout: one thread per output element, in the memory order of z
+template <bool NHWC>
+__global__ void __launch_bounds__(256) bn_pool2_scalar(BnPool a) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (int64_t)a.n * a.c * a.oh * a.ow) return;
+  int img, ch, oy, ox;
+  if (NHWC) { ch = (int)(i % a.c); i /= a.c; ox = (int)(i % a.ow); i /= a.ow; oy = (int)(i % a.oh); img = (int)(i / a.oh); }
+  else { ox = (int)(i % a.ow); i /= a.ow; oy = (int)(i % a.oh); i /= a.oh; ch = (int)(i % a.c); img = (int)(i / a.c); }
+  const float mean = __ldg(a.mean + ch), inv = __ldg(a.inv + ch), ga = __ldg(a.gamma + ch), be = __ldg(a.beta + ch);
+  float v[4];
+#pragma unroll
+  for (int k = 0; k < 4; k++) {
+    float o = (__ldg(a.x.p + a.x.off(img, ch, 2 * oy + (k >> 1), 2 * ox + (k & 1))) - mean) * inv * ga + be;
+    if (a.relu) o = fmaxf(o, 0.f);
+    v[k] = o;
+    if (a.y.p) a.y.p[a.y.off(img, ch, 2 * oy + (k >> 1), 2 * ox + (k & 1))] = o;
+  }
+  float best;
+  int bi;
+  pool4(v, best, bi);
+  const int64_t zo = a.z.off(img, ch, oy, ox);
+  a.z.p[zo] = best;
+  if (a.idx) a.idx[zo] = (uint8_t)bi;
+}
+
 // layout of an activation: 0 NCHW contiguous, 1 NHWC contiguous, -1 neither
 static int layout_of(const OmtAct* a, int c, int h, int w) {
   if (is_nchw(a, c, h, w)) return 0;
@@ -324,18 +402,68 @@ static int launch_part(int lay, const float* x, const float* g, const float* y, 
   return check_launch(MODE == 0 ? "bn_stats_part_nchw" : "bn_bwd_part_nchw");
 }
 
-// statistics from raw sums [2][c] accumulated by a conv epilogue
-__global__ void bn_from_sums_kernel(const float* sums, int c, float count, float corr, float momentum, float eps, float* mean,
-                                    float* var, float* invstd, float* rm, float* rv) {
-  int ch = blockIdx.x * blockDim.x + threadIdx.x;
-  if (ch >= c) return;
-  float m = sums[ch] / count, v = fmaxf(sums[c + ch] / count - m * m, 0.f);
-  if (mean) mean[ch] = m;
-  if (var) var[ch] = v;
-  if (invstd) invstd[ch] = rsqrtf(v + eps);
-  if (rm) {
-    rm[ch] += momentum * (m - rm[ch]);
-    rv[ch] += momentum * (v * corr - rv[ch]);
+// Statistics from the per-group partials a conv epilogue wrote (OMT_EPI_BNSTATS): for each 32-row group g and channel the
+// group's sum and the sum of squared deviations from the group's own mean, part[(2g + {0,1}) * c + ch], and the group's row
+// count cnt[g]. Two sets (n_a, mean_a, M2_a), (n_b, mean_b, M2_b) merge exactly (Chan et al.):
+//   n = n_a + n_b,  d = mean_b - mean_a,  mean = mean_a + d * n_b / n,  M2 = M2_a + M2_b + d^2 * n_a * n_b / n
+// so no sum ever holds more than the spread of the data, whatever the mean, and the order of the merges is fixed.
+struct Moments { float n, mean, m2; };
+__device__ __forceinline__ void merge(Moments& a, float nb, float mb, float m2b) {
+  if (nb <= 0.f) return;
+  const float n = a.n + nb, d = mb - a.mean, f = nb / n;
+  a.mean = fmaf(d, f, a.mean);
+  a.m2 += m2b + d * d * a.n * f;
+  a.n = n;
+}
+// One launch: block = 32 channels x 8 group lanes; slice sl of S takes groups sl*8 + lane, + S*8, ... and leaves its merged
+// moments in out[sl][3][c]; the block that finishes last for a channel block (a ticket counter in `tickets`, which must be
+// zero on entry and is reset on exit) merges the S slices in slice order and writes what bn_stats_fin writes.
+struct BnFromPartials {
+  const float* part; const float* cnt; unsigned* tickets; float* out;
+  int groups, c, S;
+  float momentum, eps;
+  float* mean; float* var; float* invstd; const float* rm_in; const float* rv_in; float* rm_out; float* rv_out;
+};
+__global__ void __launch_bounds__(256) bn_partials_kernel(BnFromPartials a) {
+  __shared__ float sh[3][8][32];
+  __shared__ bool last;
+  const int cx = threadIdx.x & 31, gl = threadIdx.x >> 5, ch = blockIdx.x * 32 + cx, sl = blockIdx.y, c = a.c;
+  Moments m{0.f, 0.f, 0.f};
+  if (ch < c) {
+    for (int g = sl * 8 + gl; g < a.groups; g += a.S * 8) {
+      const float n = __ldg(a.cnt + g);
+      if (n > 0.f) merge(m, n, __ldg(a.part + (int64_t)2 * g * c + ch) / n, __ldg(a.part + ((int64_t)2 * g + 1) * c + ch));
+    }
+  }
+  sh[0][gl][cx] = m.n; sh[1][gl][cx] = m.mean; sh[2][gl][cx] = m.m2;
+  __syncthreads();
+  if (gl == 0 && ch < c) {
+    for (int k = 1; k < 8; k++) merge(m, sh[0][k][cx], sh[1][k][cx], sh[2][k][cx]);
+    a.out[((int64_t)sl * 3) * c + ch] = m.n; a.out[((int64_t)sl * 3 + 1) * c + ch] = m.mean; a.out[((int64_t)sl * 3 + 2) * c + ch] = m.m2;
+  }
+  if (a.S > 1) {
+    __threadfence();  // this block's slice is visible before its ticket is
+    __syncthreads();
+    if (threadIdx.x == 0) last = atomicAdd(a.tickets + blockIdx.x, 1u) == (unsigned)a.S - 1;
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    if (threadIdx.x == 0) a.tickets[blockIdx.x] = 0;  // ready for the next call
+    if (gl != 0 || ch >= c) return;
+    m = Moments{0.f, 0.f, 0.f};
+    for (int k = 0; k < a.S; k++)
+      merge(m, __ldcg(a.out + ((int64_t)k * 3) * c + ch), __ldcg(a.out + ((int64_t)k * 3 + 1) * c + ch), __ldcg(a.out + ((int64_t)k * 3 + 2) * c + ch));
+  } else if (gl != 0 || ch >= c) {
+    return;
+  }
+  const float v = m.n > 0.f ? m.m2 / m.n : 0.f, corr = m.n / fmaxf(m.n - 1.f, 1.f);
+  if (a.mean) a.mean[ch] = m.mean;
+  if (a.var) a.var[ch] = v;
+  if (a.invstd) a.invstd[ch] = rsqrtf(v + a.eps);
+  if (a.rm_out) {
+    const float r0 = a.rm_in[ch], r1 = a.rv_in[ch];
+    a.rm_out[ch] = r0 + a.momentum * (m.mean - r0);
+    a.rv_out[ch] = r1 + a.momentum * (v * corr - r1);
   }
 }
 
@@ -371,13 +499,24 @@ int omt_bn_stats(const OmtAct* x, int32_t n, int32_t c, int32_t h, int32_t w, fl
   return check_launch("bn_stats_fin");
 }
 
-int omt_bn_stats_from_sums(const float* sums, int64_t count, int32_t c, float* mean, float* var, float* invstd, float* rm,
-                           float* rv, float momentum, float eps, omt_stream_t stream) {
-  OMT_REQUIRE(sums && c > 0 && count > 0, "omt_bn_stats_from_sums: bad arguments");
-  float cnt = (float)count;
-  bn_from_sums_kernel<<<(unsigned)cdiv(c, 128), 128, 0, st(stream)>>>(sums, c, cnt, cnt / std::max(cnt - 1.f, 1.f), momentum, eps, mean, var,
-                                                         invstd, rm, rv);
-  return check_launch("bn_stats_from_sums");
+int omt_bn_stats_from_partials(const float* partials, int32_t groups, int32_t c, float* mean, float* var, float* invstd, float* rm, float* rv,
+                               float* new_rm, float* new_rv, float momentum, float eps, uint32_t flags, omt_stream_t stream) {
+  OMT_REQUIRE(partials && c > 0 && groups > 0, "omt_bn_stats_from_partials: bad arguments");
+  OMT_REQUIRE(!(flags & OMT_BN_FUNCTIONAL) || (rm && rv && new_rm && new_rv), "omt_bn_stats_from_partials: functional mode needs rm, rv, new_rm, new_rv");
+  cudaStream_t s = st(stream);
+  const int gx = (int)cdiv(c, 32);
+  const int S = (int)std::max<int64_t>(1, std::min<int64_t>({cdiv(groups, 64), cdiv(4 * sm_count(), gx), 256}));
+  // per-slice moments from the caching allocator; the ticket counters sit behind the group counts in the caller's buffer,
+  // zeroed by the convolution that wrote the partials
+  Scratch sc;
+  int r = sc.get(nullptr, 0, (size_t)S * 3 * c * sizeof(float), stream);
+  if (r) return r;
+  const bool fn = flags & OMT_BN_FUNCTIONAL;
+  const float* cnt = partials + (size_t)2 * groups * c;
+  BnFromPartials a{partials, cnt, reinterpret_cast<unsigned*>(const_cast<float*>(cnt + groups)), (float*)sc.p, groups, c, S, momentum, eps,
+                   mean, var, invstd, rm, rv, rm ? (fn ? new_rm : rm) : nullptr, rm ? (fn ? new_rv : rv) : nullptr};
+  bn_partials_kernel<<<dim3(gx, S), 256, 0, s>>>(a);
+  return check_launch("bn_stats_from_partials");
 }
 
 int omt_bn_apply_add(const OmtAct* x, const OmtAct* res, const OmtAct* y, int32_t n, int32_t c, int32_t h, int32_t w, const float* mean,
@@ -396,6 +535,26 @@ int omt_bn_apply_add(const OmtAct* x, const OmtAct* res, const OmtAct* y, int32_
 int omt_bn_apply(const OmtAct* x, const OmtAct* y, int32_t n, int32_t c, int32_t h, int32_t w, const float* mean,
                  const float* invstd, const float* gamma, const float* beta, uint32_t flags, omt_stream_t stream) {
   return omt_bn_apply_add(x, nullptr, y, n, c, h, w, mean, invstd, gamma, beta, flags, stream);
+}
+
+int omt_bn_apply_pool2(const OmtAct* x, const OmtAct* y, const OmtAct* z, uint8_t* idx, int32_t n, int32_t c, int32_t h, int32_t w,
+                       const float* mean, const float* invstd, const float* gamma, const float* beta, uint32_t flags, omt_stream_t stream) {
+  OMT_REQUIRE(x && z && x->p && z->p && mean && invstd && gamma && beta && n > 0 && c > 0, "omt_bn_apply_pool2: bad arguments");
+  OMT_REQUIRE(h >= 2 && w >= 2 && h % 2 == 0 && w % 2 == 0, "omt_bn_apply_pool2: needs even height and width (got %d x %d)", h, w);
+  const int lay = layout_of(x, c, h, w);
+  OMT_REQUIRE(lay >= 0 && layout_of(z, c, h / 2, w / 2) == lay && (!y || !y->p || layout_of(y, c, h, w) == lay),
+              "omt_bn_apply_pool2: x, y and z must share an NCHW or NHWC contiguous layout");
+  BnPool a{view(x), y && y->p ? view(y) : ActView{nullptr, 0, 0, 0, 0}, view(z), idx, mean, invstd, gamma, beta, n, c, h / 2, w / 2,
+           (flags & OMT_BN_RELU) != 0};
+  const int64_t outs = (int64_t)n * c * (h / 2) * (w / 2);
+  const bool vec = lay == 1 && c % 4 == 0 &&
+                   ((reinterpret_cast<uintptr_t>(x->p) | reinterpret_cast<uintptr_t>(a.y.p) | reinterpret_cast<uintptr_t>(z->p) |
+                     reinterpret_cast<uintptr_t>(mean) | reinterpret_cast<uintptr_t>(invstd) | reinterpret_cast<uintptr_t>(gamma) |
+                     reinterpret_cast<uintptr_t>(beta)) & 15) == 0 && (reinterpret_cast<uintptr_t>(idx) & 3) == 0;
+  if (vec) bn_pool2_nhwc4<<<(unsigned)cdiv(outs / 4, 256), 256, 0, st(stream)>>>(a);
+  else if (lay == 1) bn_pool2_scalar<true><<<(unsigned)cdiv(outs, 256), 256, 0, st(stream)>>>(a);
+  else bn_pool2_scalar<false><<<(unsigned)cdiv(outs, 256), 256, 0, st(stream)>>>(a);
+  return check_launch("bn_apply_pool2");
 }
 
 int omt_bn_eval(const OmtAct* x, const OmtAct* y, int32_t n, int32_t c, int32_t h, int32_t w, const float* rm,

@@ -76,6 +76,23 @@ inline bool is_nhwc(const OmtAct* a, int c, int h, int w) {
   return a->sc == 1 && a->sw == c && a->sh == (int64_t)w * c && a->sn == (int64_t)h * w * c;
 }
 
+// Argument checks every dense-convolution entry point starts with (the reference's conv_kind / NEED rules,
+// csrc/conv.cpp:167-183): a square kernel up to 11, stride 1..4, pad <= ks, consistent output size, GEMM extents below 2^31.
+inline int check_dense(const OmtConvGeo* g, const char* who) {
+  OMT_REQUIRE(g != nullptr, "%s: null geometry", who);
+  OMT_REQUIRE(g->groups == 1, "%s: groups must be 1 (use omt_dw_* for depthwise)", who);
+  OMT_REQUIRE(g->n > 0 && g->ci > 0 && g->co > 0 && g->ih > 0 && g->iw > 0, "%s: empty tensor", who);
+  OMT_REQUIRE(g->ks >= 1 && g->ks <= 11 && g->stride >= 1 && g->stride <= 4 && g->pad >= 0 && g->pad <= g->ks,
+              "%s: needs ks<=11, stride 1..4, pad<=ks (got ks=%d stride=%d pad=%d)", who, g->ks, g->stride, g->pad);
+  OMT_REQUIRE(g->oh == (g->ih + 2 * g->pad - g->ks) / g->stride + 1 && g->ow == (g->iw + 2 * g->pad - g->ks) / g->stride + 1 &&
+                  g->oh > 0 && g->ow > 0,
+              "%s: output size does not match the geometry", who);
+  OMT_REQUIRE((int64_t)g->n * g->oh * g->ow < (1ll << 31) && (int64_t)g->n * g->ih * g->iw < (1ll << 31) &&
+                  (int64_t)g->co * g->ci * g->ks * g->ks < (1ll << 31),
+              "%s: GEMM extent exceeds 2^31", who);
+  return OMT_OK;
+}
+
 #ifdef __CUDACC__
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -22,13 +22,14 @@ int tc_conv_fwd(const OmtConvGeo* g, const OmtAct* x, const float* w, const floa
                 uint32_t flags, void* ws, cudaStream_t s);
 int tc_conv_dgrad(const OmtConvGeo* g, const OmtAct* gy, const float* w, const OmtAct* dx, uint32_t flags, void* ws, cudaStream_t s);
 int tc_conv_wgrad(const OmtConvGeo* g, const OmtAct* x, const OmtAct* gy, float* dw, float scale, void* ws, cudaStream_t s);
+int tc_bnstats_groups(const OmtConvGeo* g, const OmtAct* x, const OmtAct* y);
 
 // ---- optional per-call timing of the three passes ----
 static bool g_timing = false;
 struct TimedCall {
   cudaEvent_t a, b;
   int kind;
-  double flops;
+  double flops, bytes;
 };
 static std::vector<TimedCall> g_timed;
 static std::mutex g_timed_mu;
@@ -40,6 +41,7 @@ struct CallTimer {
     if (!on) return;
     c.kind = kind;
     c.flops = 2.0 * g->n * g->co * g->oh * g->ow * (double)g->ci * g->ks * g->ks;
+    c.bytes = 4.0 * ((double)g->n * g->ci * g->ih * g->iw + (double)g->n * g->co * g->oh * g->ow + (double)g->co * g->ci * g->ks * g->ks);
     if (cudaEventCreate(&c.a) != cudaSuccess || cudaEventCreate(&c.b) != cudaSuccess) { on = false; return; }
     cudaEventRecord(c.a, s);
   }
@@ -50,21 +52,6 @@ struct CallTimer {
     g_timed.push_back(c);
   }
 };
-
-static int check_dense(const OmtConvGeo* g, const char* who) {
-  OMT_REQUIRE(g != nullptr, "%s: null geometry", who);
-  OMT_REQUIRE(g->groups == 1, "%s: groups must be 1 (use omt_dw_* for depthwise)", who);
-  OMT_REQUIRE(g->n > 0 && g->ci > 0 && g->co > 0 && g->ih > 0 && g->iw > 0, "%s: empty tensor", who);
-  OMT_REQUIRE(g->ks >= 1 && g->ks <= 11 && g->stride >= 1 && g->stride <= 4 && g->pad >= 0 && g->pad <= g->ks,
-              "%s: needs ks<=11, stride 1..4, pad<=ks (got ks=%d stride=%d pad=%d)", who, g->ks, g->stride, g->pad);
-  OMT_REQUIRE(g->oh == (g->ih + 2 * g->pad - g->ks) / g->stride + 1 && g->ow == (g->iw + 2 * g->pad - g->ks) / g->stride + 1 &&
-                  g->oh > 0 && g->ow > 0,
-              "%s: output size does not match the geometry", who);
-  OMT_REQUIRE((int64_t)g->n * g->oh * g->ow < (1ll << 31) && (int64_t)g->n * g->ih * g->iw < (1ll << 31) &&
-                  (int64_t)g->co * g->ci * g->ks * g->ks < (1ll << 31),
-              "%s: GEMM extent exceeds 2^31", who);
-  return OMT_OK;
-}
 
 __global__ void __launch_bounds__(256) scale_copy_kernel(float* __restrict__ dst, const float* __restrict__ src, int64_t n, float scale) {
   int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
@@ -154,6 +141,16 @@ size_t omt_conv_workspace_bytes(int kind, const OmtConvGeo* g, uint32_t flags) {
   size_t simt = kind == 2 ? simt_wgrad_workspace(g) : 0;
   if (flags & OMT_FORCE_SIMT) return simt;
   return std::max(simt, tc_workspace(kind, g));
+}
+
+int32_t omt_conv_bnstats_groups(const OmtConvGeo* g, const OmtAct* x, const OmtAct* y) {
+  if (check_dense(g, "omt_conv_bnstats_groups") || !x || !y || !x->p || !y->p) return 0;
+  return tc_bnstats_groups(g, x, y);
+}
+
+size_t omt_conv_bnstats_floats(int32_t groups, int32_t co) {
+  if (groups <= 0 || co <= 0) return 0;
+  return (size_t)groups * (2 * (size_t)co + 1) + (size_t)cdiv(co, 32);
 }
 
 int omt_conv_fwd(const OmtConvGeo* g, const OmtAct* x, const float* w, const float* bias, const OmtAct* y, float* stats,
@@ -263,6 +260,13 @@ int omt_conv_timing_read(double flops[3], double ms[3], int64_t calls[3], int re
     for (auto& c : g_timed) { cudaEventDestroy(c.a); cudaEventDestroy(c.b); }
     g_timed.clear();
   }
+  return OMT_OK;
+}
+
+int omt_conv_timing_bytes(double bytes[3]) {
+  std::lock_guard<std::mutex> l(g_timed_mu);
+  for (int k = 0; k < 3; k++) bytes[k] = 0;
+  for (auto& c : g_timed) bytes[c.kind] += c.bytes;
   return OMT_OK;
 }
 

@@ -227,7 +227,7 @@ __global__ void __launch_bounds__(256) conv_gemm_simt(ConvArgs g) {
   __shared__ __align__(16) float Bs[2][BK][BN + 4];
   L ld(g, blockIdx.z);
   const int M = ld.M, N = ld.N;
-  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;  // M tiles on x: its limit is 2^31-1, y's is 65535
   if (m0 >= M) return;
   const int tid = threadIdx.x;
   const int a_k = L::A_MFAST ? (tid >> 5) : (tid & 7), a_r = L::A_MFAST ? (tid & 31) : (tid >> 3);
@@ -326,19 +326,21 @@ static int launch_gemm(const ConvArgs& a, int64_t Mmax, int64_t N, int gz, cudaS
   // tile choice: narrow-N tiles for tiny channel counts, smaller tiles when the grid would not fill the SMs
   int sms = sm_count();
   auto blocks = [&](int bm, int bn) { return cdiv(Mmax, bm) * cdiv(N, bn) * gz; };
+  // M tiles on grid.x (limit 2^31-1), N tiles on grid.y (limit 65535: N is a channel count, or ci*ks*ks for the weight gradient)
+  OMT_REQUIRE(cdiv(N, N <= 16 ? 16 : 64) <= 65535 && gz <= 65535, "%s: %lld GEMM columns exceed the launch grid", name, (long long)N);
   if (N <= 16) {
-    dim3 grid((unsigned)cdiv(N, 16), (unsigned)cdiv(Mmax, 256), gz);
+    dim3 grid((unsigned)cdiv(Mmax, 256), (unsigned)cdiv(N, 16), gz);
     conv_gemm_simt<L, 256, 16, 4, 4><<<grid, 256, 0, s>>>(a);
   } else if (N <= 64 || blocks(128, 128) < sms) {
     if (blocks(128, 64) < sms) {
-      dim3 grid((unsigned)cdiv(N, 64), (unsigned)cdiv(Mmax, 64), gz);
+      dim3 grid((unsigned)cdiv(Mmax, 64), (unsigned)cdiv(N, 64), gz);
       conv_gemm_simt<L, 64, 64, 4, 4><<<grid, 256, 0, s>>>(a);
     } else {
-      dim3 grid((unsigned)cdiv(N, 64), (unsigned)cdiv(Mmax, 128), gz);
+      dim3 grid((unsigned)cdiv(Mmax, 128), (unsigned)cdiv(N, 64), gz);
       conv_gemm_simt<L, 128, 64, 8, 4><<<grid, 256, 0, s>>>(a);
     }
   } else {
-    dim3 grid((unsigned)cdiv(N, 128), (unsigned)cdiv(Mmax, 128), gz);
+    dim3 grid((unsigned)cdiv(Mmax, 128), (unsigned)cdiv(N, 128), gz);
     conv_gemm_simt<L, 128, 128, 8, 8><<<grid, 256, 0, s>>>(a);
   }
   return check_launch(name);
@@ -516,12 +518,8 @@ extern "C" size_t omt_conv_wgrad_noalloc_capacity(void) { return NOALLOC_SCRATCH
 
 extern "C" int omt_conv_wgrad_noalloc(const OmtConvGeo* g, const OmtAct* x, const OmtAct* gy, float* dw, float scale,
                                       omt_stream_t stream) {
-  OMT_REQUIRE(g && g->groups == 1 && g->n > 0 && g->ci > 0 && g->co > 0 && g->ks >= 1 && g->ks <= 11 && g->stride >= 1 && g->stride <= 4 &&
-                  g->pad >= 0 && g->pad <= g->ks,
-              "omt_conv_wgrad_noalloc: needs a dense convolution with ks<=11, stride 1..4, pad<=ks");
-  OMT_REQUIRE(g->oh == (g->ih + 2 * g->pad - g->ks) / g->stride + 1 && g->ow == (g->iw + 2 * g->pad - g->ks) / g->stride + 1 && g->oh > 0 &&
-                  g->ow > 0,
-              "omt_conv_wgrad_noalloc: output size does not match the geometry");
+  int r = check_dense(g, "omt_conv_wgrad_noalloc");  // the same checks as omt_conv_wgrad (extents below 2^31 included)
+  if (r) return r;
   OMT_REQUIRE(x && gy && x->p && gy->p && dw, "omt_conv_wgrad_noalloc: null pointer");
   const size_t need = simt_wgrad_workspace(g);
   if (need > NOALLOC_SCRATCH_FLOATS * sizeof(float)) {

@@ -202,16 +202,21 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t sr
 struct TcArgs {
   ActView y;          // output activation (any strides)
   const float* bias;
+  // OMT_EPI_BNSTATS: per 32-row group g = 4 * (row tile) + (lane quarter) and channel the sum of the stored values and their
+  // squared deviations from the group's own mean, stats[(2g + {0,1}) * N + channel], then the groups' row counts at
+  // stats[2 * groups * N + g], then ceil(N / 32) zeroed words (ticket counters of the merging kernel). The merge
+  // (bn_partials_kernel) runs in a fixed order: deterministic, and exact for any mean.
+  float* stats;
   int M, N;           // GEMM extents: pixels, output channels
   int oh, ow;         // pixel grid of the GEMM rows (to decompose m)
-  int kh, kw;         // filter taps of this (sub-)convolution
-  int stride;         // traversal stride over the input
   int low_h, low_w;   // input coordinate of tap (0,0) for output pixel (0,0): -pad for a forward convolution
-  int out_step, out_y0, out_x0;  // GEMM row (oy, ox) is stored at (oy*out_step + out_y0, ox*out_step + out_x0)
   int cblocks;        // 32-channel blocks per tap
-  int cpad;           // cblocks * 32
   uint32_t flags;
+  int16_t kh, kw;     // filter taps of this (sub-)convolution
+  int8_t stride;      // traversal stride over the input
+  int8_t out_step, out_y0, out_x0;  // GEMM row (oy, ox) is stored at (oy*out_step + out_y0, ox*out_step + out_x0)
   int store_mode;     // 0: plain stores (any strides); 1: TMA stores of 32-row boxes of the [M, N] matrix; 2: of window rectangles
+  int reserved_[3];   // keeps the struct at 128 bytes (see below)
   // The last 16 bytes are shared by two modes that never occur together (growing this struct by 16 bytes made every
   // tile of the kernel 2-3 us slower on the GPU, measured; the cause was not established, so its size is kept).
   //  * "window" mode (win_w != 0; few input channels): the A operand comes from a zero-padded [n][h][w][4] copy of the
@@ -345,8 +350,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           mbar_expect_tx(BAR(s), S::A_BYTES + 2 * S::B_BYTES);
           if (win_w) tma_tile_4d(stage, &map_a, BAR(s), cb * BKF, c.ox0, h0 + ky, c.img0);  // kw == 1: tap = filter row
           else tma_im2col_4d(stage, &map_a, BAR(s), cb * BKF, w0, h0, c.img0, (uint16_t)kx, (uint16_t)ky);
-          tma_tile_3d(stage + 2 * S::A_BYTES, &map_w, BAR(s), tap * g.cpad + cb * BKF, c.n0, 0);
-          tma_tile_3d(stage + 2 * S::A_BYTES + S::B_BYTES, &map_w, BAR(s), tap * g.cpad + cb * BKF, c.n0, 1);
+          tma_tile_3d(stage + 2 * S::A_BYTES, &map_w, BAR(s), (tap * g.cblocks + cb) * BKF, c.n0, 0);
+          tma_tile_3d(stage + 2 * S::A_BYTES + S::B_BYTES, &map_w, BAR(s), (tap * g.cblocks + cb) * BKF, c.n0, 1);
         }
       }
       if (*abort_flag) {  // drain: let the copies already in flight land before the CTA exits (bounded)
@@ -495,6 +500,36 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               tma_store_4d(&map_y, smem_u32(buf), nb, c.ox0 + r0 % win_w, c.oy0 + r0 / win_w, c.img0);
             }
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+          if (g.flags & OMT_EPI_BNSTATS) {
+            // Batch-norm statistics of what was just stored, from the box in shared memory (the TMA store only reads it):
+            // lane l takes channel nb + l, i.e. column l of the 32 rows, whose 16-byte slot in row r is (l / 4) ^ (r & 7), so
+            // the 32 lanes of one load hit 32 different banks. One pass, shifted by the group's first valid row (the
+            // deviations are then of the order of the spread, whatever the mean).
+            const uint32_t vmask = __ballot_sync(0xffffffffu, valid);
+            const int cnt = __popc(vmask);
+            const int grp = (t / n_tiles) * 4 + q;
+            float s1 = 0.f, s2 = 0.f, shift = 0.f;
+            if (cnt) {
+              const int r0 = __ffs(vmask) - 1;
+              shift = *reinterpret_cast<const float*>(buf + r0 * 128 + ((((lane >> 2) ^ (r0 & 7)) << 4) | ((lane & 3) << 2)));
+#pragma unroll 8
+              for (int r = 0; r < 32; r++) {
+                const float v = *reinterpret_cast<const float*>(buf + r * 128 + ((((lane >> 2) ^ (r & 7)) << 4) | ((lane & 3) << 2)));
+                if ((vmask >> r) & 1u) {
+                  const float d = v - shift;
+                  s1 += d; s2 = fmaf(d, d, s2);
+                }
+              }
+            }
+            if (nb + lane < g.N) {
+              const float fc = (float)cnt;
+              g.stats[((int64_t)2 * grp) * g.N + nb + lane] = fmaf(fc, shift, s1);                          // sum of the group
+              g.stats[((int64_t)2 * grp + 1) * g.N + nb + lane] = cnt ? fmaxf(s2 - s1 * s1 / fc, 0.f) : 0.f;  // sum (v - group mean)^2
+            }
+            if (nb == 0 && lane == 0) g.stats[(int64_t)2 * m_tiles * 4 * g.N + grp] = (float)cnt;
+            // ticket counters of the kernel that merges the partials (one per 32 channels), behind the counts
+            if (grp == 0 && lane == 0) g.stats[(int64_t)m_tiles * 4 * (2 * g.N + 1) + (nb >> 5)] = 0.f;
           }
         } else if (g.flags & OMT_EPI_ACCUM) {  // every output element belongs to exactly one tile row: a plain read-add-write
 #pragma unroll
@@ -654,7 +689,7 @@ int launch_tc(const TcProblem& p, const float* wsplit, const TcArgs& args, int s
     }
   }
   {
-    const int kp = p.kh * p.kw * args.cpad;
+    const int kp = p.kh * p.kw * args.cblocks * BKF;
     cuuint64_t dims[3] = {(cuuint64_t)kp, (cuuint64_t)p.rows, 2};
     cuuint64_t strides[2] = {(cuuint64_t)kp * 4, (cuuint64_t)kp * 4 * p.rows};
     cuuint32_t box[3] = {BKF, (cuuint32_t)BN, 1}, estr[3] = {1, 1, 1};
@@ -665,12 +700,14 @@ int launch_tc(const TcProblem& p, const float* wsplit, const TcArgs& args, int s
       return OMT_ECUDA;
     }
   }
-  static bool attr_set = false;
-  if (!attr_set) {
-    OMT_CUDA(cudaFuncSetAttribute((conv_tc_kernel<BN, false>), cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
-    OMT_CUDA(cudaFuncSetAttribute((conv_tc_kernel<BN, true>), cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
-    attr_set = true;
-  }
+  // once per instantiation, from whichever thread gets here first (autograd's worker threads call these too)
+  static std::once_flag attr_once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(attr_once, [] {
+    attr_err = cudaFuncSetAttribute((conv_tc_kernel<BN, false>), cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+    if (attr_err == cudaSuccess) attr_err = cudaFuncSetAttribute((conv_tc_kernel<BN, true>), cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+  });
+  OMT_CUDA(attr_err);
   TcArgs a = args;
   alignas(64) CUtensorMap map_y = map_w;  // placeholder when the epilogue stores directly
   if (splits > 1) {  // partial tiles go to the workspace with plain stores (these fields alias the window fields, unused here)
@@ -683,6 +720,8 @@ int launch_tc(const TcProblem& p, const float* wsplit, const TcArgs& args, int s
                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS)
       a.store_mode = 1;
   }
+  // the statistics are taken from the 32 x 32 boxes staged for the TMA stores, by the kernel that owns the whole reduction
+  OMT_REQUIRE(!(a.flags & OMT_EPI_BNSTATS) || a.store_mode == 1, "OMT_EPI_BNSTATS needs a dense channels-last output and an unsplit reduction");
   const int m_tiles = (int)cdiv(a.M, BM), n_tiles = (int)cdiv(a.N, BN);
   const unsigned grid = (unsigned)std::min<int64_t>((int64_t)m_tiles * n_tiles * splits, sm_count());
   if (splits > 1) conv_tc_kernel<BN, true><<<grid, TC_THREADS, S::TOTAL, s>>>(map_a, map_w, map_y, a);
@@ -696,17 +735,18 @@ int launch_tc(const TcProblem& p, const float* wsplit, const TcArgs& args, int s
 size_t split_floats(int rows, int ks, int chans) { return (size_t)2 * rows * ks * ks * (cdiv(chans, BKF) * BKF); }
 
 // one (sub-)convolution: re-lay the weights it needs into `wsplit`, then run the GEMM
-int run_tc(const TcProblem& p, const float* w, SplitArgs sp, float* wsplit, float* part, const OmtAct* y, const float* bias, uint32_t flags,
-           cudaStream_t s) {
+int run_tc(const TcProblem& p, const float* w, SplitArgs sp, float* wsplit, float* part, const OmtAct* y, const float* bias, float* stats,
+           uint32_t flags, cudaStream_t s) {
   TcArgs a{};
   a.y = view(y); a.bias = bias;
   a.M = p.n * p.oh * p.ow; a.N = p.rows; a.oh = p.oh; a.ow = p.ow;
-  a.kh = p.kh; a.kw = p.kw; a.stride = p.stride; a.low_h = p.low_h; a.low_w = p.low_w;
-  a.out_step = p.out_step; a.out_y0 = p.out_y0; a.out_x0 = p.out_x0;
-  a.cblocks = (int)cdiv(p.c, BKF); a.cpad = a.cblocks * BKF;
-  a.flags = flags;
-  sp.kh = p.kh; sp.kw = p.kw; sp.cpad = a.cpad;
-  const int64_t total = (int64_t)p.rows * p.kh * p.kw * a.cpad;
+  a.kh = (int16_t)p.kh; a.kw = (int16_t)p.kw; a.stride = (int8_t)p.stride; a.low_h = p.low_h; a.low_w = p.low_w;
+  a.out_step = (int8_t)p.out_step; a.out_y0 = (int8_t)p.out_y0; a.out_x0 = (int8_t)p.out_x0;
+  a.cblocks = (int)cdiv(p.c, BKF);
+  a.flags = flags; a.stats = stats;
+  const int cpad = a.cblocks * BKF;
+  sp.kh = p.kh; sp.kw = p.kw; sp.cpad = cpad;
+  const int64_t total = (int64_t)p.rows * p.kh * p.kw * cpad;
   weight_split_kernel<<<(unsigned)cdiv(total, 256), 256, 0, s>>>(w, wsplit, sp);
   int r = check_launch("conv_tc_weight_split");
   if (r) return r;
@@ -1037,7 +1077,7 @@ int launch_window(const OmtConvGeo* g, const WinPlan& w, const float* xs, const 
     }
   }
   {
-    const int kp = g->ks * args.cpad;
+    const int kp = g->ks * args.cblocks * BKF;
     cuuint64_t dims[3] = {(cuuint64_t)kp, (cuuint64_t)g->co, 2};
     cuuint64_t strides[2] = {(cuuint64_t)kp * 4, (cuuint64_t)kp * 4 * g->co};
     cuuint32_t box[3] = {BKF, (cuuint32_t)BN, 1}, estr[3] = {1, 1, 1};
@@ -1048,11 +1088,10 @@ int launch_window(const OmtConvGeo* g, const WinPlan& w, const float* xs, const 
       return OMT_ECUDA;
     }
   }
-  static bool attr_set = false;
-  if (!attr_set) {
-    OMT_CUDA(cudaFuncSetAttribute((conv_tc_kernel<BN, false>), cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
-    attr_set = true;
-  }
+  static std::once_flag attr_once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(attr_once, [] { attr_err = cudaFuncSetAttribute((conv_tc_kernel<BN, false>), cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL); });
+  OMT_CUDA(attr_err);
   TcArgs a = args;
   alignas(64) CUtensorMap map_y = map_w;
   if (dense_out(a)) {  // 32-pixel pieces of the tile's rectangle: a row segment, or several short rows
@@ -1064,13 +1103,15 @@ int launch_window(const OmtConvGeo* g, const WinPlan& w, const float* xs, const 
                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS)
       a.store_mode = 2;
   }
+  OMT_REQUIRE(!(a.flags & OMT_EPI_BNSTATS) || a.store_mode == 2, "OMT_EPI_BNSTATS needs a dense channels-last output");
   const int m_tiles = g->n * w.tiles_x * w.tiles_y, n_tiles = (int)cdiv(a.N, BN);
   const unsigned grid = (unsigned)std::min<int64_t>((int64_t)m_tiles * n_tiles, sm_count());
   conv_tc_kernel<BN, false><<<grid, TC_THREADS, S::TOTAL, s>>>(map_a, map_w, map_y, a);
   return check_launch(BN == 64 ? "conv_tc_window_128x64" : (BN == 128 ? "conv_tc_window_128x128" : "conv_tc_window_128x256"));
 }
 
-int run_window_fwd(const OmtConvGeo* g, const OmtAct* x, const float* w, const float* bias, const OmtAct* y, uint32_t flags, void* ws, cudaStream_t s) {
+int run_window_fwd(const OmtConvGeo* g, const OmtAct* x, const float* w, const float* bias, const OmtAct* y, float* stats, uint32_t flags, void* ws,
+                   cudaStream_t s) {
   const WinPlan wp = plan_window(g);
   float* xs = (float*)ws;
   float* wsplit = xs + ((wp.stage_floats + 63) / 64) * 64;
@@ -1081,12 +1122,12 @@ int run_window_fwd(const OmtConvGeo* g, const OmtAct* x, const float* w, const f
   TcArgs a{};
   a.y = view(y); a.bias = bias;
   a.M = g->n * g->oh * g->ow; a.N = g->co; a.oh = g->oh; a.ow = g->ow;
-  a.kh = g->ks; a.kw = 1; a.stride = g->stride; a.low_h = -g->pad; a.low_w = 0;
+  a.kh = (int16_t)g->ks; a.kw = 1; a.stride = (int8_t)g->stride; a.low_h = -g->pad; a.low_w = 0;
   a.out_step = 1; a.out_y0 = 0; a.out_x0 = 0;
-  a.cblocks = wp.kb; a.cpad = wp.kb * BKF; a.flags = flags;
+  a.cblocks = wp.kb; a.flags = flags; a.stats = stats;
   a.win_w = wp.win_w; a.win_h = wp.win_h; a.tiles_x = wp.tiles_x; a.tiles_y = wp.tiles_y;
-  SplitArgs sp{g->co, g->ci, g->ks, g->ks, 1, a.cpad, 0, 0, 0, 1, 1};
-  const int64_t wtotal = (int64_t)g->co * g->ks * a.cpad;
+  SplitArgs sp{g->co, g->ci, g->ks, g->ks, 1, wp.kb * BKF, 0, 0, 0, 1, 1};
+  const int64_t wtotal = (int64_t)g->co * g->ks * wp.kb * BKF;
   weight_split_kernel<<<(unsigned)cdiv(wtotal, 256), 256, 0, s>>>(w, wsplit, sp);
   r = check_launch("conv_tc_weight_split");
   if (r) return r;
@@ -1230,11 +1271,10 @@ int launch_wgrad(const OmtConvGeo* g, const WgPlan& w, const float* x, const flo
     cuuint32_t box[2] = {BKF, PB}, estr[2] = {1, 1};
     OMT_ENCODE(g_encode_tiled(&map_g, F32, 2, (void*)gy, dims, strides, box, estr, IL, SW, L2P, FILL), "cuTensorMapEncodeTiled (gy)");
   }
-  static bool attr_set = false;
-  if (!attr_set) {
-    OMT_CUDA(cudaFuncSetAttribute((wgrad_tc_kernel<BN, PB>), cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
-    attr_set = true;
-  }
+  static std::once_flag attr_once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(attr_once, [] { attr_err = cudaFuncSetAttribute((wgrad_tc_kernel<BN, PB>), cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL); });
+  OMT_CUDA(attr_err);
   WgArgs a{};
   a.mode = w.mode; a.total_blocks = w.total_blocks;
   a.bw = w.bw; a.bh = w.bh; a.bn = w.bn_img; a.tiles_x = w.tiles_x; a.tiles_y = w.tiles_y; a.cpi = w.cpi;
@@ -1308,17 +1348,29 @@ size_t tc_workspace(int kind, const OmtConvGeo* g) {
 
 int tc_conv_fwd(const OmtConvGeo* g, const OmtAct* x, const float* w, const float* bias, const OmtAct* y, float* stats, uint32_t flags, void* ws,
                 cudaStream_t s) {
-  (void)stats;
-  OMT_REQUIRE(!(flags & OMT_EPI_BNSTATS), "OMT_EPI_BNSTATS is not implemented in the tensor-core epilogue yet");
   if (!load_driver_entry_points()) {
     set_error("the CUDA driver does not export cuTensorMapEncodeTiled/Im2col");
     return OMT_ECUDA;
   }
-  if (g->ci <= 4) return run_window_fwd(g, x, w, bias, y, flags, ws, s);
+  if (g->ci <= 4) return run_window_fwd(g, x, w, bias, y, stats, flags, ws, s);
   TcProblem p{x->p, g->n, g->ci, g->ih, g->iw, g->oh, g->ow, g->co, g->ks, g->ks, g->stride, -g->pad, -g->pad, 1, 0, 0};
   SplitArgs sp{g->co, g->ci, g->ks, 0, 0, 0, 0, 0, 0, 1};
   float* part = (float*)ws + ((split_floats(g->co, g->ks, g->ci) + 63) / 64) * 64;
-  return run_tc(p, w, sp, (float*)ws, part, y, bias, flags, s);
+  return run_tc(p, w, sp, (float*)ws, part, y, bias, stats, flags, s);
+}
+
+// 32-row groups the forward kernel reports statistics for (0: this call cannot: not a tensor-core geometry, an output that
+// is not dense channels-last, or a reduction split over CTAs). Same decisions as tc_conv_fwd makes.
+int tc_bnstats_groups(const OmtConvGeo* g, const OmtAct* x, const OmtAct* y) {
+  if (!tc_supported(0, g, x, y) || !is_nhwc(y, g->co, g->oh, g->ow) || g->co % 4 != 0 || (reinterpret_cast<uintptr_t>(y->p) & 15)) return 0;
+  if (g->ci <= 4) {
+    const WinPlan wp = plan_window(g);
+    return g->n * wp.tiles_x * wp.tiles_y * 4;
+  }
+  TcProblem p{x->p, g->n, g->ci, g->ih, g->iw, g->oh, g->ow, g->co, g->ks, g->ks, g->stride, -g->pad, -g->pad, 1, 0, 0};
+  const int64_t M = (int64_t)g->n * g->oh * g->ow;
+  if (plan_splits(M, g->co, g->ks * g->ks * (int)cdiv(g->ci, BKF), pick_bn(p)) > 1) return 0;
+  return (int)cdiv(M, BM) * 4;
 }
 
 // Input gradient as forward convolutions of gy. Stride 1: one convolution with the weights transposed and flipped and
@@ -1361,7 +1413,7 @@ int tc_conv_dgrad(const OmtConvGeo* g, const OmtAct* gy, const float* w, const O
       // output (i, j) of the phase reads gy[i + qy - ty, j + qx - tx]; with flipped taps ty' = jy-1-ty the first tap sits at qy-(jy-1)
       TcProblem p{gy->p, g->n, g->co, g->oh, g->ow, hi, wi, g->ci, jy, jx, 1, qy - (jy - 1), qx - (jx - 1), s, py, px};
       SplitArgs sp{g->co, g->ci, g->ks, 0, 0, 0, 1, ky0, kx0, s};
-      int r = run_tc(p, w, sp, wsplit, part, dx, nullptr, epi, st_);
+      int r = run_tc(p, w, sp, wsplit, part, dx, nullptr, nullptr, epi, st_);
       if (r) return r;
       wsplit += 2 * (size_t)g->ci * jy * jx * (cdiv(g->co, BKF) * BKF);
     }

@@ -52,6 +52,21 @@ Tensor conv_forward(const Tensor& x, const Tensor& w, const Tensor* bias, const 
   return out;
 }
 
+Tensor conv_forward_stats(const Tensor& x, const Tensor& w, const Tensor* bias, const OmtConvGeo& g, Tensor& partials, int& groups) {
+  Tensor out = dense4(empty_dev({g.n, g.co, g.oh, g.ow}, at::kFloat, prefer_cl(x, g.co)));
+  OmtAct ax = act(x), ay = act(out);
+  groups = omt_conv_bnstats_groups(&g, &ax, &ay);
+  uint32_t flags = bias ? OMT_EPI_BIAS : 0u;
+  if (groups > 0) {
+    partials = empty_dev({(int64_t)omt_conv_bnstats_floats(groups, g.co)}, at::kFloat);
+    flags |= OMT_EPI_BNSTATS;
+  }
+  check(omt_conv_fwd(&g, &ax, w.data_ptr<float>(), bias ? bias->data_ptr<float>() : nullptr, &ay, groups > 0 ? partials.data_ptr<float>() : nullptr,
+                     flags, nullptr, 0, cur_stream()),
+        "conv forward");
+  return out;
+}
+
 static Tensor convolution_(const Tensor& x_, const Tensor& w_, const std::optional<Tensor>& bias, IntArrayRef stride,
                            IntArrayRef padding, IntArrayRef dilation, bool transposed, IntArrayRef, int64_t groups) {
   std::string kind = conv_kind(x_, w_, stride, padding, dilation, transposed, groups);

@@ -6,6 +6,8 @@
 //   omt::bn_add_relu_train / omt::bn_add_relu_backward   the same pair across a residual add (BatchNorm, + identity, ReLU):
 //                           the forward reads the identity branch in the apply pass, the backward also returns the masked
 //                           gradient that flows into the identity branch
+//   omt::conv_bn_train      conv2d feeding a training BatchNorm2d (+ identity branch)(+ ReLU): the conv epilogue reduces the
+//                           batch statistics while it stores its output, so the BatchNorm reads that output once, not twice
 //   omt::conv_act           conv2d + bias + optional ReLU in the GEMM epilogue
 //   omt::conv_bn_act_eval   eval conv2d + BatchNorm (folded into the conv's weights and bias) + optional ReLU
 //   omt::fused_pointwise    declared for schema parity; generated pointwise kernels are not built in this library
@@ -36,6 +38,19 @@ static std::tuple<Tensor, Tensor, Tensor, Tensor> bn_add_relu_backward_ref(const
   auto r = at::native_batch_norm_backward(gz, x, w, std::nullopt, std::nullopt, mean, invstd, true, 0.0, mask);
   return {std::get<0>(r), std::get<1>(r), std::get<2>(r), gz};
 }
+// (yconv, z, mean, invstd, new_rm, new_rv): yconv is the conv output the backward graph keeps, z the block's output
+static std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor, Tensor> conv_bn_train_ref(const Tensor& x, const Tensor& cw, const std::optional<Tensor>& cb,
+                                                                                   IntArrayRef stride, IntArrayRef padding,
+                                                                                   const std::optional<Tensor>& res, const Tensor& w, const Tensor& b,
+                                                                                   const Tensor& rm, const Tensor& rv, double mom, double eps,
+                                                                                   int64_t act_) {
+  Tensor y = at::convolution(x, cw, cb, stride, padding, {1, 1}, false, {0, 0}, 1);
+  auto r = at::_native_batch_norm_legit_functional(y, w, b, rm, rv, true, mom, eps);
+  Tensor z = std::get<0>(r);
+  if (defined(res)) z = z + *res;
+  if (act_ == 1) z = at::relu(z);
+  return {y, z, std::get<1>(r), std::get<2>(r), std::get<3>(r), std::get<4>(r)};
+}
 static Tensor conv_act_ref(const Tensor& x, const Tensor& w, const std::optional<Tensor>& b, IntArrayRef stride, IntArrayRef padding, int64_t act_) {
   Tensor y = at::convolution(x, w, b, stride, padding, {1, 1}, false, {0, 0}, 1);
   return act_ == 1 ? at::relu(y) : y;
@@ -60,25 +75,35 @@ static Tensor fused_pointwise_ref(c10::string_view, at::TensorList) {
 
 static bool whole(const Tensor& t) { return f32(t) && t.is_contiguous(); }
 
-// mean and invstd are returned as two halves of one buffer (the reference's contract, csrc/fused.cpp:65-67)
+// Statistics then normalise(+ identity)(+ReLU). When `partials` comes from the conv that produced x_ (groups > 0) the
+// statistics are merged from them instead of being reduced from x_. mean and invstd are separate tensors: the reference
+// returns them as two halves of one buffer (csrc/fused.cpp:65-67), which an op schema without alias annotations may not do.
 static std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> bn_res_relu_train(const Tensor& x_, const Tensor* res_, const Tensor& w, const Tensor& b,
-                                                                          const Tensor& rm, const Tensor& rv, double mom, double eps) {
+                                                                          const Tensor& rm, const Tensor& rv, double mom, double eps,
+                                                                          bool relu = true, const Tensor* partials = nullptr, int groups = 0) {
   NEED(f32(x_) && x_.dim() == 4 && x_.numel() > 0 && whole(w) && whole(b) && whole(rm) && whole(rv), "4-D float32 with contiguous parameters");
   NEED(!res_ || (f32(*res_) && res_->sizes() == x_.sizes()), "residual of the activation's shape");
   Tensor x = dense4(x_);
   if (layout4(x) == 1 && x.size(1) % 4 != 0) x = to_layout(x, 0);
   Tensor res = res_ ? to_layout(*res_, layout4(x)) : Tensor();
   const int n = (int)x.size(0), c = (int)x.size(1), h = (int)x.size(2), wd = (int)x.size(3);
-  Tensor nrm = empty_dev({c}, at::kFloat), nrv = empty_dev({c}, at::kFloat), stats = empty_dev({3 * (int64_t)c}, at::kFloat);
+  Tensor nrm = empty_dev({c}, at::kFloat), nrv = empty_dev({c}, at::kFloat);
+  Tensor mean = empty_dev({c}, at::kFloat), inv = empty_dev({c}, at::kFloat);
   Tensor y = dense4(empty_dev(x.sizes(), at::kFloat, layout4(x) == 1));
-  float* s = stats.data_ptr<float>();
   OmtAct ax = act(x), ay = act(y);
-  check(omt_bn_stats(&ax, n, c, h, wd, s, s + 2 * c, s + c, fptr(rm), fptr(rv), fptr(nrm), fptr(nrv), (float)mom, (float)eps, OMT_BN_FUNCTIONAL,
-                     cur_stream()),
-        "bn_relu_train statistics");
+  if (partials && groups > 0 && x.is_same(x_)) {
+    check(omt_bn_stats_from_partials(partials->data_ptr<float>(), groups, c, fptr(mean), nullptr, fptr(inv), fptr(rm), fptr(rv), fptr(nrm), fptr(nrv),
+                                     (float)mom, (float)eps, OMT_BN_FUNCTIONAL, cur_stream()),
+          "batch statistics from the conv epilogue");
+  } else {
+    check(omt_bn_stats(&ax, n, c, h, wd, fptr(mean), nullptr, fptr(inv), fptr(rm), fptr(rv), fptr(nrm), fptr(nrv), (float)mom, (float)eps,
+                       OMT_BN_FUNCTIONAL, cur_stream()),
+          "bn_relu_train statistics");
+  }
   OmtAct ar = res_ ? act(res) : null_act();
-  check(omt_bn_apply_add(&ax, &ar, &ay, n, c, h, wd, s, s + c, fptr(w), fptr(b), OMT_BN_RELU, cur_stream()), "bn_relu_train apply");
-  return {y, stats.narrow(0, 0, c), stats.narrow(0, c, c), nrm, nrv};
+  check(omt_bn_apply_add(&ax, &ar, &ay, n, c, h, wd, fptr(mean), fptr(inv), fptr(w), fptr(b), relu ? OMT_BN_RELU : 0u, cur_stream()),
+        "bn_relu_train apply");
+  return {y, mean, inv, nrm, nrv};
 }
 static std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> bn_relu_train_dev(const Tensor& x, const Tensor& w, const Tensor& b, const Tensor& rm,
                                                                           const Tensor& rv, double mom, double eps) {
@@ -135,6 +160,27 @@ static Tensor conv_act_dev(const Tensor& x_, const Tensor& w_, const std::option
   return conv_forward(x, w, bb.defined() ? &bb : nullptr, g, act_ == 1);
 }
 
+static std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor, Tensor> conv_bn_train_dev(const Tensor& x_, const Tensor& cw_, const std::optional<Tensor>& cb,
+                                                                                   IntArrayRef stride, IntArrayRef padding,
+                                                                                   const std::optional<Tensor>& res, const Tensor& w, const Tensor& b,
+                                                                                   const Tensor& rm, const Tensor& rv, double mom, double eps,
+                                                                                   int64_t act_) {
+  NEED(f32(x_) && f32(cw_) && x_.dim() == 4 && cw_.dim() == 4 && x_.numel() > 0 && cw_.size(2) == cw_.size(3) && stride[0] == stride[1] &&
+           padding[0] == padding[1] && stride[0] >= 1 && stride[0] <= 4 && cw_.size(2) <= 11 && padding[0] <= cw_.size(2) &&
+           x_.size(1) == cw_.size(1) && (!defined(cb) || f32(*cb)),
+       "dense square conv");
+  NEED(whole(w) && whole(b) && whole(rm) && whole(rv) && w.numel() == cw_.size(0), "contiguous float32 BatchNorm parameters");
+  NEED(!defined(res) || f32(*res), "float32 residual");
+  Tensor x = dense4(x_), cw = contig(cw_);
+  OmtConvGeo g = conv_geo(x.size(0), x.size(1), cw.size(0), x.size(2), x.size(3), cw.size(2), stride[0], padding[0]);
+  NEED(g.oh > 0 && g.ow > 0, "empty output");
+  Tensor bb = defined(cb) ? contig(*cb) : Tensor(), partials;
+  int groups = 0;
+  Tensor y = conv_forward_stats(x, cw, bb.defined() ? &bb : nullptr, g, partials, groups);
+  auto r = bn_res_relu_train(y, defined(res) ? &*res : nullptr, w, b, rm, rv, mom, eps, act_ == 1, &partials, groups);
+  return {y, std::get<0>(r), std::get<1>(r), std::get<2>(r), std::get<3>(r), std::get<4>(r)};
+}
+
 static Tensor conv_bn_act_eval_dev(const Tensor& x, const Tensor& cw, const std::optional<Tensor>& cb, const Tensor& w, const Tensor& b,
                                    const Tensor& rm, const Tensor& rv, double eps, IntArrayRef stride, IntArrayRef padding, int64_t act_) {
   NEED(f32(cw) && f32(w) && f32(b) && f32(rm) && f32(rv), "float32");
@@ -171,6 +217,8 @@ TORCH_LIBRARY(omt, m) {
   m.def("bn_relu_backward(Tensor g, Tensor x, Tensor y, Tensor w, Tensor mean, Tensor invstd, bool[3] mask) -> (Tensor, Tensor, Tensor)");
   m.def("bn_add_relu_train(Tensor x, Tensor res, Tensor w, Tensor b, Tensor rm, Tensor rv, float momentum, float eps) -> (Tensor, Tensor, Tensor, Tensor, Tensor)");
   m.def("bn_add_relu_backward(Tensor g, Tensor x, Tensor y, Tensor w, Tensor mean, Tensor invstd, bool[3] mask) -> (Tensor, Tensor, Tensor, Tensor)");
+  m.def("conv_bn_train(Tensor x, Tensor cw, Tensor? cb, int[] stride, int[] padding, Tensor? res, Tensor w, Tensor b, Tensor rm, Tensor rv, "
+        "float momentum, float eps, int act) -> (Tensor, Tensor, Tensor, Tensor, Tensor, Tensor)");
   m.def("conv_act(Tensor x, Tensor w, Tensor? b, int[] stride, int[] padding, int act) -> Tensor");
   m.def("conv_bn_act_eval(Tensor x, Tensor cw, Tensor? cb, Tensor w, Tensor b, Tensor rm, Tensor rv, float eps, int[] stride, int[] padding, int act) -> Tensor");
   m.def("fused_pointwise(str kernel, Tensor[] inputs) -> Tensor");
@@ -180,6 +228,7 @@ TORCH_LIBRARY_IMPL(omt, CompositeExplicitAutograd, m) {
   m.impl("bn_relu_backward", &bn_relu_backward_ref);
   m.impl("bn_add_relu_train", &bn_add_relu_train_ref);
   m.impl("bn_add_relu_backward", &bn_add_relu_backward_ref);
+  m.impl("conv_bn_train", &conv_bn_train_ref);
   m.impl("conv_act", &conv_act_ref);
   m.impl("conv_bn_act_eval", &conv_bn_act_eval_ref);
   m.impl("fused_pointwise", &fused_pointwise_ref);
@@ -199,6 +248,11 @@ TORCH_LIBRARY_IMPL(omt, PrivateUse1, m) {
   m.impl("bn_add_relu_backward", [](const Tensor& g, const Tensor& x, const Tensor& y, const Tensor& w, const Tensor& mean, const Tensor& invstd,
                                     std::array<bool, 3> mask) {
     return dev_or_composite<&bn_add_relu_backward_dev, &bn_add_relu_backward_ref>("bn_add_relu_backward", g, x, y, w, mean, invstd, mask);
+  });
+  m.impl("conv_bn_train", [](const Tensor& x, const Tensor& cw, const std::optional<Tensor>& cb, IntArrayRef s, IntArrayRef p,
+                             const std::optional<Tensor>& res, const Tensor& w, const Tensor& b, const Tensor& rm, const Tensor& rv, double mom, double eps,
+                             int64_t a) {
+    return dev_or_composite<&conv_bn_train_dev, &conv_bn_train_ref>("conv_bn_train", x, cw, cb, s, p, res, w, b, rm, rv, mom, eps, a);
   });
   m.impl("conv_act", [](const Tensor& x, const Tensor& w, const std::optional<Tensor>& b, IntArrayRef s, IntArrayRef p, int64_t a) {
     return dev_or_composite<&conv_act_dev, &conv_act_ref>("conv_act", x, w, b, s, p, a);

@@ -140,6 +140,9 @@ OmtConvGeo conv_geo(int64_t n, int64_t ci, int64_t co, int64_t ih, int64_t iw, i
 // y = conv(x, w) (+bias)(ReLU) into a fresh tensor; x must be dense4. Output is channels-last when prefer_cl() says so.
 Tensor conv_forward(const Tensor& x, const Tensor& w, const Tensor* bias, const OmtConvGeo& g, bool relu);
 bool prefer_cl(const Tensor& x, int64_t co);
-extern int g_fold;  // eval-plan BN folding: 0 none, 1 into 1x1 convs, 2 into every conv
+// The same (no ReLU) with the batch-norm partial statistics of y taken in the GEMM epilogue when the call allows it: `groups`
+// is the number of 32-row groups in `partials` (0 and an undefined tensor otherwise; see omt_conv_bnstats_groups).
+Tensor conv_forward_stats(const Tensor& x, const Tensor& w, const Tensor* bias, const OmtConvGeo& g, Tensor& partials, int& groups);
+extern int g_fold;  // eval-plan BN folding (set_fold): 0 off, anything else folds BatchNorm into the conv that feeds it
 
 }  // namespace omt

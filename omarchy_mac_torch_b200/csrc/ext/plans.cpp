@@ -4,8 +4,10 @@
 // forward(x), backward(g) -> (gx | None, [grads]) and a `busy` flag; gradients are views into one slab (csrc/plans.cpp:54-60,
 // 319-328) so a data-parallel bucket can be reduced in place.
 //
-// What differs from the reference: the step list calls C-ABI kernels (BN+ReLU in one pass after the statistics, 1-byte
-// pool argmax, ReLU-masked BN backward), conv layers may carry a bias, eval plans fold BatchNorm into the weights of the
+// What differs from the reference: the step list calls C-ABI kernels; a training conv -> BatchNorm+ReLU -> max pool block is
+// three launches (the conv, whose epilogue also reduces the batch statistics; the merge of those partial statistics; one
+// pass that normalises, applies the ReLU and pools with a 1-byte argmax) where the reference runs five (csrc/plans.cpp:
+// 135-138, 180-199); the BN backward is ReLU-masked; conv layers may carry a bias, eval plans fold BatchNorm into the weights of the
 // conv that produces its input (one GEMM with bias+ReLU epilogue per conv-BN-ReLU block), and activations come from the
 // caching allocator per call instead of plan-owned buffers, so outputs need no copy out of the plan.
 #include "omt.h"
@@ -28,6 +30,8 @@ struct Layer {
 };
 struct Saved {  // what backward needs from forward, per layer
   Tensor x, y, stats, idx;
+  Tensor partials;  // a bn layer: partial batch statistics the conv in front of it reduced in its epilogue
+  int groups = 0;
 };
 struct GradSlot {
   int param;
@@ -138,12 +142,18 @@ static Tensor plan_forward(Plan& p, const Tensor& x_) {
         Tensor fb = ((bias ? (*bias - p.rms[B.bn]) : -p.rms[B.bn]) * scale + p.params[B.param + 1]).contiguous();
         cur = run_conv(cur, fw, &fb, L, true);
         li++;  // the bn layer is done
+      } else if (p.train && L.is_conv() && li + 1 < p.layers.size() && p.layers[li + 1].kind == "bn") {
+        // the conv epilogue reduces the BatchNorm's batch statistics while it stores its output
+        OmtConvGeo g = conv_geo(cur.size(0), cur.size(1), L.co, cur.size(2), cur.size(3), L.ks, 1, L.ks / 2, 1);
+        Saved& nx = p.saved[li + 1];
+        cur = conv_forward_stats(cur, wt, bias, g, nx.partials, nx.groups);
       } else {
         cur = run_conv(cur, wt, bias, L, false);
       }
     } else if (L.kind == "bn") {
       if (layout4(cur) == 1 && c % 4 != 0) {
         cur = to_layout(cur, 0);
+        sv.groups = 0;  // the partial statistics belong to the tensor the conv wrote; this copy is reduced the usual way
         if (p.train) sv.x = cur;
       }
       Tensor y = dense4(empty_dev(cur.sizes(), at::kFloat, layout4(cur) == 1));
@@ -151,12 +161,34 @@ static Tensor plan_forward(Plan& p, const Tensor& x_) {
       if (p.train) {
         sv.stats = empty_dev({3 * (int64_t)c}, at::kFloat);  // mean | invstd | var
         float* s = sv.stats.data_ptr<float>();
-        check(omt_bn_stats(&ax, n, c, h, w, s, s + 2 * c, s + c, fptr(p.rms[L.bn]), fptr(p.rvs[L.bn]), nullptr, nullptr, (float)L.momentum, kEps,
-                           0, cur_stream()),
-              "plan BN statistics");
+        if (sv.groups > 0) {
+          check(omt_bn_stats_from_partials(sv.partials.data_ptr<float>(), sv.groups, c, s, s + 2 * c, s + c, fptr(p.rms[L.bn]), fptr(p.rvs[L.bn]),
+                                           nullptr, nullptr, (float)L.momentum, kEps, 0, cur_stream()),
+                "plan BN statistics from the conv epilogue");
+        } else {
+          check(omt_bn_stats(&ax, n, c, h, w, s, s + 2 * c, s + c, fptr(p.rms[L.bn]), fptr(p.rvs[L.bn]), nullptr, nullptr, (float)L.momentum,
+                             kEps, 0, cur_stream()),
+                "plan BN statistics");
+        }
+        sv.partials = Tensor(); sv.groups = 0;
+        sv.y = y;
+        if (li + 1 < p.layers.size() && p.layers[li + 1].kind == "pool" && h % 2 == 0 && w % 2 == 0) {
+          // normalise + ReLU + 2x2 max pool in one pass; y is still written (the backward masks with it)
+          const bool cl = layout4(cur) == 1;
+          Tensor z = dense4(empty_dev({n, c, h / 2, w / 2}, at::kFloat, cl));
+          Tensor idx = empty_dev({n, c, h / 2, w / 2}, at::kByte, cl).as_strided(z.sizes(), z.strides());
+          OmtAct az = act(z);
+          check(omt_bn_apply_pool2(&ax, &ay, &az, idx.data_ptr<uint8_t>(), n, c, h, w, s, s + c, fptr(p.params[L.param]),
+                                   fptr(p.params[L.param + 1]), OMT_BN_RELU, cur_stream()),
+                "plan BN apply + max pool");
+          Saved& pv = p.saved[li + 1];
+          pv.x = y; pv.idx = idx;
+          cur = z;
+          li++;  // the pool layer is done
+          continue;
+        }
         check(omt_bn_apply(&ax, &ay, n, c, h, w, s, s + c, fptr(p.params[L.param]), fptr(p.params[L.param + 1]), OMT_BN_RELU, cur_stream()),
               "plan BN apply");
-        sv.y = y;
       } else {
         check(omt_bn_eval(&ax, &ay, n, c, h, w, fptr(p.rms[L.bn]), fptr(p.rvs[L.bn]), fptr(p.params[L.param]), fptr(p.params[L.param + 1]), kEps,
                           OMT_BN_RELU, cur_stream()),

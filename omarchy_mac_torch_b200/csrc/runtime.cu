@@ -28,7 +28,11 @@ void set_error(const char* fmt, ...) {
 }
 int cuda_fail(cudaError_t e, const char* what) {
   set_error("CUDA error %d (%s) in %s", (int)e, cudaGetErrorString(e), what);
-  if (e != cudaErrorMemoryAllocation && e != cudaErrorNotReady && !g_sticky) g_sticky = (int)e;
+  // Sticky only for errors that leave the device in doubt. A launch the runtime refused up front (bad grid, too much
+  // shared memory, a bad argument) or an allocation that failed has run nothing: the caller gets its code and carries on.
+  const bool recoverable = e == cudaErrorMemoryAllocation || e == cudaErrorNotReady || e == cudaErrorInvalidConfiguration ||
+                           e == cudaErrorInvalidValue || e == cudaErrorLaunchOutOfResources;
+  if (!recoverable && !g_sticky) g_sticky = (int)e;
   return OMT_ECUDA;
 }
 void note_launch(const char* kernel) {

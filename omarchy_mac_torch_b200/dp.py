@@ -45,6 +45,9 @@ class DataParallel:
     """Wraps a model whose parameters all live on one device. Usage per step:
 
         dp.zero_grad(); loss = f(model(x)); loss.backward(); dp.finish(); optimizer.step()
+
+    `optimizer.zero_grad()` in place of `dp.zero_grad()` works too (with set_to_none=True the gradients are moved back
+    into their buckets as they arrive, at the cost of one copy each).
     """
 
     def __init__(self, model, bucket_mb=25.0, group=None, as_comm_tensor=None):
@@ -74,9 +77,10 @@ class DataParallel:
         self.arrived = [0] * nb
         self.pending = []
         self.launch_order = []  # bucket ids in the order their reductions were launched during the last backward
+        self.views = [self.flat[ids[i]][offs[i]:offs[i] + p.numel()].view_as(p) for i, p in enumerate(self.params)]
         for i, p in enumerate(self.params):
-            p.grad = self.flat[ids[i]][offs[i]:offs[i] + p.numel()].view_as(p)
-            p.register_post_accumulate_grad_hook(self._make_hook(ids[i]))
+            p.grad = self.views[i]
+            p.register_post_accumulate_grad_hook(self._make_hook(ids[i], i))
         self.broadcast_parameters()
 
     def broadcast_parameters(self):
@@ -94,8 +98,14 @@ class DataParallel:
             return core.as_cuda(t)
         return t
 
-    def _make_hook(self, b):
-        def hook(_param):
+    def _make_hook(self, b, i=None):
+        def hook(param):
+            # `optimizer.zero_grad(set_to_none=True)` (torch's default) drops the view into the bucket, and the next backward
+            # then leaves a fresh gradient tensor outside it: move it back in and re-attach the view, so that what gets
+            # reduced is this step's gradient.
+            if i is not None and param.grad is not None and param.grad.data_ptr() != self.views[i].data_ptr():
+                self.views[i].copy_(param.grad)
+                param.grad = self.views[i]
             self.arrived[b] += 1
             if self.arrived[b] == self.expected[b]:
                 self._reduce(b)
@@ -128,3 +138,21 @@ class DataParallel:
             if got != want and self.world > 1:
                 dist.all_reduce(self.comm[b], op=dist.ReduceOp.SUM, group=self.group)
                 self.flat[b].div_(self.world)
+        # ready for the next backward whichever way the caller clears gradients (dp.zero_grad() or the optimizer's own)
+        self.arrived = [0] * len(self.flat)
+
+    def param_spread(self):
+        """max - min over ranks of a float64 checksum of all parameters (sum and sum of squares): 0.0 exactly when the
+        replicas are still identical after a step, which is what averaged gradients and identical optimizers must give."""
+        with torch.no_grad():
+            acc = torch.zeros(2, dtype=torch.float64, device=self.params[0].device)
+            for p in self.params:
+                d = p.detach().double()
+                acc[0] += d.sum()
+                acc[1] += (d * d).sum()
+        if self.world <= 1:
+            return 0.0
+        hi, lo = self._alias(acc.clone()), self._alias(acc.clone())
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX, group=self.group)
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN, group=self.group)
+        return float((hi - lo).abs().max().item())

@@ -4,9 +4,9 @@ depend on pixels). Architecture facts only; parameter registration order matches
 same initial weights and the recorded loss curves can be compared.
 
   PlainCNN, SeparableCNN, ResNet18, MobileNetV3Small   the reference's acceptance models (1x28x28 / 64x64 / 96x96 inputs)
-  PlainCNN3        BASELINE config 2: three conv3x3-BN-ReLU-MaxPool blocks (3->32->64->128) on 3x32x32, Linear 10
-  MobileNetV3SE    BASELINE config 4: MobileNetV3-Small with squeeze-excite, 3x3/5x5 depthwise, 224x224
-  ResNet50         BASELINE config 5: Bottleneck [3,4,6,3]
+  PlainCNN3        the three-block benchmark CNN: three conv3x3-BN-ReLU-MaxPool blocks (3->32->64->128) on 3x32x32, Linear 10
+  MobileNetV3SE    the MobileNetV3 benchmark: MobileNetV3-Small with squeeze-excite, 3x3/5x5 depthwise, 224x224
+  ResNet50         the data-parallel benchmark: Bottleneck [3,4,6,3], 25.6 M parameters
 """
 
 import torch
@@ -57,7 +57,7 @@ class SeparableCNN(nn.Module):
 
 
 class PlainCNN3(nn.Module):
-    """BASELINE config 2. The feature stack is one nn.Sequential so the auto-fuse hook can take it; the head is outside."""
+    """Three conv3x3-BN-ReLU-MaxPool blocks on 3x32x32 (batch 128 in the benchmark). The feature stack is one nn.Sequential so the auto-fuse hook can take it; the head is outside."""
 
     def __init__(self, widths=(32, 64, 128), num_classes=10, bias=True):
         super().__init__()
@@ -202,7 +202,7 @@ class _InvResSE(nn.Module):
 
 
 class MobileNetV3SE(nn.Module):
-    """BASELINE config 4: 3x3 s2 stem (16, hardswish), 11 inverted-residual blocks (kernel, expansion, out, SE,
+    """MobileNetV3-Small with squeeze-excite on 224x224: 3x3 s2 stem (16, hardswish), 11 inverted-residual blocks (kernel, expansion, out, SE,
     hardswish, stride) with 3x3/5x5 depthwise and squeeze-excite r=4, 1x1 conv to 576, avgpool, Linear 1024, Linear 1000."""
 
     CFG = [(3, 16, 16, True, False, 2), (3, 72, 24, False, False, 2), (3, 88, 24, False, False, 1), (5, 96, 40, True, True, 2),
@@ -226,7 +226,7 @@ class MobileNetV3SE(nn.Module):
 
 
 def kaiming_normal_convs(model):
-    """BASELINE config 3 asks for kaiming-normal conv init on ResNet-18."""
+    """Kaiming-normal initialisation of every convolution (the ResNet-18 benchmark configuration asks for it)."""
     for m in model.modules():
         if isinstance(m, nn.Conv2d):
             nn.init.kaiming_normal_(m.weight, mode="fan_out", nonlinearity="relu")

@@ -10,7 +10,7 @@ for p in (ROOT, ROOT / "tests" / "golden"):
     if str(p) not in sys.path:
         sys.path.insert(0, str(p))
 
-TOL = 1e-4  # max|err| / max|ref| per tensor (the bound BASELINE.json's north_star states)
+TOL = 1e-4  # max|err| / max|ref| per tensor (the parity bound of this project: every output and gradient tensor against PyTorch CPU aten)
 
 
 def pytest_configure(config):

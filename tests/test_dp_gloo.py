@@ -51,7 +51,7 @@ class Net(nn.Module):
         return self.head(self.b(y).mean((2, 3)))
 
 
-def _worker(rank, world, port, out):
+def _worker(rank, world, port, out, torch_zero_grad=False):
     sys.path.insert(0, str(ROOT))
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -64,22 +64,29 @@ def _worker(rank, world, port, out):
     xs, ys = X[rank * 4:(rank + 1) * 4], Y[rank * 4:(rank + 1) * 4]
     opt = torch.optim.SGD(model.parameters(), lr=0.1)
     for _ in range(2):
-        dp.zero_grad()
+        if torch_zero_grad:
+            opt.zero_grad()  # torch's default set_to_none=True: the hooks must bring the new gradients back into the buckets
+            dp.launch_order = []
+        else:
+            dp.zero_grad()
         F.cross_entropy(model(xs), ys).backward()
         order = list(dp.launch_order)
         dp.finish()
         opt.step()
+    spread = dp.param_spread()  # a collective: every rank calls it
     if rank == 0:
-        torch.save({"state": model.state_dict(), "order": order, "nb": len(dp.flat), "bucket_of": dp.bucket_of}, out)
+        torch.save({"state": model.state_dict(), "order": order, "nb": len(dp.flat), "bucket_of": dp.bucket_of, "spread": spread}, out)
     dist.barrier()
     dist.destroy_process_group()
 
 
-def test_two_ranks_match_single_process(tmp_path):
+@pytest.mark.parametrize("torch_zero_grad", [False, True], ids=["dp.zero_grad", "optimizer.zero_grad"])
+def test_two_ranks_match_single_process(tmp_path, torch_zero_grad):
     out = str(tmp_path / "rank0.pt")
     port = _free_port()
-    mp.spawn(_worker, args=(2, port, out), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, port, out, torch_zero_grad), nprocs=2, join=True)
     got = torch.load(out)
+    assert got["spread"] == 0.0  # the replicas hold bit-identical parameters after two steps
     # single process: same initial weights as rank 0, per-shard forward/backward (local BN statistics), averaged gradients
     torch.manual_seed(7)
     ref = Net()

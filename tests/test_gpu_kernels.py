@@ -142,6 +142,21 @@ def test_input_gradient_accumulates_in_the_epilogue(capi, shape, cl_out):
         capi.conv_dgrad(torch.randn(2, 8, 8, 8, device="cuda"), torch.randn(8, 3, 3, 3, device="cuda"), (8, 8), 1, 1, acc=small)
 
 
+def test_exact_path_takes_more_than_65535_row_tiles(capi):
+    """9.4 million output pixels on the exact-fp32 kernels: more GEMM row tiles than a launch grid's y or z extent holds
+    (the row tiles therefore run along x). Forward and input gradient, against aten on the CPU."""
+    torch.manual_seed(0)
+    x, w = torch.randn(64, 3, 384, 384), torch.randn(4, 3, 3, 3) * 0.2
+    y = torch.nn.functional.conv2d(x, w, padding=1)
+    assert y.shape[0] * y.shape[2] * y.shape[3] > 65535 * 128
+    got = capi.conv_fwd(dev(x), dev(w), None, 1, 1, flags=capi.FORCE_SIMT)
+    assert rel_err(host(got), y.numpy()) <= TOL
+    gy = torch.randn_like(y)
+    dx = torch.ops.aten.convolution_backward(gy, x, w, None, [1, 1], [1, 1], [1, 1], False, [0, 0], 1, [True, False, False])[0]
+    assert rel_err(host(capi.conv_dgrad(dev(gy), dev(w), (384, 384), 1, 1, flags=capi.FORCE_SIMT)), dx.numpy()) <= TOL
+    capi.call("omt_check_errors")
+
+
 def test_tensor_core_path_refuses_what_it_cannot_take(capi):
     x = torch.randn(2, 16, 16, 16, device="cuda")           # 16 channels but NCHW: not a TMA-loadable operand
     w = torch.randn(8, 16, 3, 3, device="cuda")
@@ -187,8 +202,58 @@ def test_conv_larger_shapes_vs_aten(capi, shape):
         assert rel_err(host(capi.conv_bias_grad(gd)), db.numpy()) <= TOL
 
 
+# the distinct convolution geometries of ResNet-50 on 224x224 inputs: (ci, co, input height, ks, stride)
+R50_LAYERS = [(3, 64, 224, 7, 2), (64, 64, 56, 1, 1), (64, 64, 56, 3, 1), (64, 256, 56, 1, 1), (256, 64, 56, 1, 1), (256, 128, 56, 1, 1), (128, 128, 56, 3, 2),
+              (128, 512, 28, 1, 1), (256, 512, 56, 1, 2), (512, 128, 28, 1, 1), (128, 128, 28, 3, 1), (512, 256, 28, 1, 1), (256, 256, 28, 3, 2),
+              (256, 1024, 14, 1, 1), (512, 1024, 28, 1, 2), (1024, 256, 14, 1, 1), (256, 256, 14, 3, 1), (1024, 512, 14, 1, 1), (512, 512, 14, 3, 2),
+              (512, 2048, 7, 1, 1), (1024, 2048, 14, 1, 2), (2048, 512, 7, 1, 1), (512, 512, 7, 3, 1)]
+
+
+@pytest.mark.parametrize("layer", R50_LAYERS, ids=lambda l: "ci%d_co%d_hw%d_k%d_s%d" % l)
+def test_resnet50_layer_geometries_on_tensor_cores(capi, layer):
+    """Every convolution geometry of the ResNet-50 training step (batch reduced to 4) on the tcgen05 kernels, channels-last:
+    forward, input gradient (also accumulating into an existing gradient, as the residual joins of the backward graph do)
+    and weight gradient against float64 aten on the CPU."""
+    ci, co, hw, ks, s = layer
+    n, p = 4, ks // 2
+    torch.manual_seed(ci + co + hw)
+    x, w = torch.randn(n, ci, hw, hw), torch.randn(co, ci, ks, ks) * (2.0 / (ci * ks * ks)) ** 0.5
+    oh = (hw + 2 * p - ks) // s + 1
+    gy = torch.randn(n, co, oh, oh)
+    y, dx, dw, _ = oracle.aten_conv(x.double(), w.double(), None, s, p, gy.double())
+    xd, wd, gd = dev(x, True), dev(w), dev(gy, True)
+    assert rel_err(host(capi.conv_fwd(xd, wd, None, s, p, flags=capi.FORCE_TC, cl=True)), y.float().numpy()) <= TOL
+    assert rel_err(host(capi.conv_wgrad(xd, gd, ks, s, p, flags=capi.FORCE_TC)), dw.float().numpy()) <= TOL
+    if ci > 4:  # the network input needs no gradient
+        assert rel_err(host(capi.conv_dgrad(gd, wd, (hw, hw), s, p, flags=capi.FORCE_TC, cl=True)), dx.float().numpy()) <= TOL
+        base = torch.randn(n, ci, hw, hw)
+        acc = dev(base, True).clone(memory_format=torch.preserve_format)
+        capi.conv_dgrad(gd, wd, (hw, hw), s, p, acc=acc)
+        assert rel_err(host(acc), (base.double() + dx).float().numpy()) <= TOL
+    capi.call("omt_sync")
+
+
+def test_alexnet_conv1_full_size_per_tensor_vs_aten(capi):
+    """AlexNet conv1 at full size (x [16,3,224,224], w [64,3,11,11], stride 4, pad 2; tools/gemm_bench.py:26-38): y, dx, dw
+    and db each compared per tensor with aten's convolution and convolution_backward on the CPU, on the library's default
+    path (NCHW operands, as the reference benchmarks the layer) and with channels-last operands."""
+    torch.manual_seed(0)
+    x = torch.randn(16, 3, 224, 224)
+    conv = torch.nn.Conv2d(3, 64, 11, stride=4, padding=2)
+    w, b = conv.weight.detach(), conv.bias.detach()
+    gy = torch.randn(16, 64, 55, 55)
+    y, dx, dw, db = oracle.aten_conv(x, w, b, 4, 2, gy)
+    for cl in (False, True):
+        xd, gd = dev(x, cl), dev(gy, cl)
+        assert rel_err(host(capi.conv_fwd(xd, dev(w), dev(b), 4, 2, cl=cl)), y.numpy()) <= TOL
+        assert rel_err(host(capi.conv_dgrad(gd, dev(w), (224, 224), 4, 2, cl=cl)), dx.numpy()) <= TOL
+        assert rel_err(host(capi.conv_wgrad(xd, gd, 11, 4, 2)), dw.numpy()) <= TOL
+        assert rel_err(host(capi.conv_bias_grad(gd)), db.numpy()) <= TOL
+    capi.call("omt_sync")
+
+
 def test_alexnet_conv1_full_size_properties(capi):
-    """BASELINE config 1 at full size through size-independent properties: linearity of each pass in its activation
+    """AlexNet conv1 at full size through size-independent properties: linearity of each pass in its activation
     argument and the adjoint identity <conv(x), gy> == <x, dgrad(gy)> == <w, wgrad(x, gy)>."""
     torch.manual_seed(0)
     x = torch.randn(16, 3, 224, 224, device="cuda")
@@ -236,6 +301,94 @@ def test_bn_golden(capi, golden, i, cl):
     assert rel_err(host(yr), np.maximum(G("y"), 0)) <= TOL
     dx, dg, db = capi.bn_backward(g, x, yr, mean, invstd, gamma, relu=True)
     assert rel_err(host(dx), G("relu_dx")) <= TOL and rel_err(host(dg), G("relu_dgamma")) <= TOL and rel_err(host(db), G("relu_dbeta")) <= TOL
+
+
+BNSTATS_SHAPES = [  # n, ci, co, hw, ks, stride, pad, bias, expect the statistics from the epilogue
+    (4, 64, 96, 14, 3, 1, 1, False, True),      # 784 pixels: the last row tile holds 16 valid rows
+    (2, 32, 40, 15, 3, 1, 1, True, True),       # 40 output channels: a ragged channel chunk
+    (8, 3, 64, 32, 3, 1, 1, True, True),        # <= 4 input channels: rectangles of output pixels as GEMM rows
+    (2, 3, 32, 35, 7, 2, 3, False, True),       # the same with a stride, odd sizes: rows outside the image are not counted
+    (16, 64, 64, 28, 3, 1, 1, False, True),     # 128 x 64 tiles
+    (16, 128, 128, 28, 3, 1, 1, True, True),    # 128 x 128 tiles
+    (32, 64, 256, 28, 1, 1, 0, False, True),    # 128 x 256 tiles, more tiles than SMs
+    (4, 256, 512, 8, 1, 1, 0, False, False),    # few tiles and a long reduction: split over CTAs, no statistics from the epilogue
+]
+
+
+@pytest.mark.parametrize("shape", BNSTATS_SHAPES, ids=lambda s: "n%d_ci%d_co%d_hw%d_k%d_s%d" % s[:6])
+def test_conv_epilogue_batch_norm_statistics(capi, shape):
+    """OMT_EPI_BNSTATS: the forward convolution reduces the batch-norm statistics of what it stores; merged, they must equal
+    the statistics of y taken in float64, y itself must be bit-identical to a call without the flag, and the running
+    statistics must follow. Twice in a row (the merge kernel's ticket counters reset themselves)."""
+    n, ci, co, hw, ks, s, p, bias, expect = shape
+    torch.manual_seed(3)
+    x = torch.randn(n, ci, hw, hw) + 0.5
+    w = torch.randn(co, ci, ks, ks) * 0.1
+    b = torch.randn(co) * 3 if bias else None
+    xd, wd, bd = dev(x, True), dev(w), dev(b)
+    plain = capi.conv_fwd(xd, wd, bd, s, p, cl=True)
+    for _ in range(2):
+        y, part, groups = capi.conv_fwd_bnstats(xd, wd, bd, s, p)
+        assert (groups > 0) == expect, groups
+        if not expect:
+            return
+        assert torch.equal(y, plain)
+        rm, rv = torch.randn(co, device="cuda"), torch.rand(co, device="cuda") + 0.5
+        mean, var, invstd, nrm, nrv = capi.bn_stats_from_partials(part, groups, co, rm, rv, momentum=0.1, eps=1e-5, functional=True)
+        y64 = y.double().cpu()
+        m64, v64 = y64.mean(dim=(0, 2, 3)), y64.var(dim=(0, 2, 3), unbiased=False)
+        cnt = y64.numel() // co
+        assert rel_err(host(mean), m64.float().numpy()) <= 1e-6
+        assert rel_err(host(var), v64.float().numpy()) <= 1e-5
+        assert rel_err(host(invstd), (1 / torch.sqrt(v64 + 1e-5)).float().numpy()) <= 1e-5
+        assert rel_err(host(nrm), (rm.cpu().double() * 0.9 + 0.1 * m64).float().numpy()) <= 1e-6
+        assert rel_err(host(nrv), (rv.cpu().double() * 0.9 + 0.1 * v64 * cnt / (cnt - 1)).float().numpy()) <= 1e-5
+    capi.call("omt_sync")
+
+
+def test_conv_epilogue_statistics_survive_a_large_mean(capi):
+    """Outputs whose mean is 1000 standard deviations away from zero (a large bias on tiny activations): the grouped, exactly
+    merged moments keep the variance, where sums of y and y^2 in float32 would lose it entirely."""
+    torch.manual_seed(4)
+    x, w = torch.randn(8, 32, 28, 28), torch.randn(64, 32, 3, 3) * 0.006
+    b = torch.full((64,), 100.0)
+    y, part, groups = capi.conv_fwd_bnstats(dev(x, True), dev(w), dev(b), 1, 1)
+    assert groups > 0
+    mean, var, invstd = capi.bn_stats_from_partials(part, groups, 64)
+    y64 = y.double().cpu()
+    v64 = y64.var(dim=(0, 2, 3), unbiased=False)
+    assert float((y64.mean(dim=(0, 2, 3)) / v64.sqrt()).min()) > 500
+    assert rel_err(host(invstd), (1 / torch.sqrt(v64 + 1e-5)).float().numpy()) <= 1e-3
+    assert rel_err(host(mean), y64.mean(dim=(0, 2, 3)).float().numpy()) <= 1e-6
+
+
+@pytest.mark.parametrize("cl", [False, True], ids=["nchw", "nhwc"])
+@pytest.mark.parametrize("shape", [(3, 8, 6, 10), (2, 5, 4, 6), (4, 32, 16, 16)])
+def test_bn_apply_with_max_pool(capi, shape, cl):
+    """omt_bn_apply_pool2 against omt_bn_apply followed by omt_pool2_fwd: same y, same pooled values, same argmax bytes."""
+    n, c, h, w = shape
+    if cl and c % 4:
+        pytest.skip("channels-last BN kernels need c % 4 == 0")
+    torch.manual_seed(5)
+    x = dev(torch.randn(n, c, h, w) * 2 + 1, cl)
+    gamma, beta = dev(torch.randn(c)), dev(torch.randn(c))
+    rm, rv = torch.zeros(c, device="cuda"), torch.ones(c, device="cuda")
+    y_ref, mean, invstd = capi.bn_train(x, gamma, beta, rm, rv, relu=True)
+    z_ref, idx_ref = capi.pool2_fwd(y_ref)
+    y = torch.empty_like(x)
+    z = torch.empty_like(z_ref)
+    idx = torch.empty_like(idx_ref)
+    capi.call("omt_bn_apply_pool2", capi.act(x), capi.act(y), capi.act(z), capi.ptr(idx), n, c, h, w, capi.ptr(mean), capi.ptr(invstd), capi.ptr(gamma),
+              capi.ptr(beta), capi.BN_RELU, capi.stream_handle())
+    assert torch.equal(y, y_ref) and torch.equal(z, z_ref) and torch.equal(idx, idx_ref)
+    z2 = torch.empty_like(z_ref)   # without y and without the argmax (an eval caller)
+    capi.call("omt_bn_apply_pool2", capi.act(x), capi.null_act(), capi.act(z2), None, n, c, h, w, capi.ptr(mean), capi.ptr(invstd), capi.ptr(gamma),
+              capi.ptr(beta), capi.BN_RELU, capi.stream_handle())
+    assert torch.equal(z2, z_ref)
+    with pytest.raises(capi.OmtError, match="even"):
+        odd = dev(torch.randn(1, 4, 5, 6), cl)
+        capi.call("omt_bn_apply_pool2", capi.act(odd), capi.null_act(), capi.act(torch.empty(1, 4, 2, 3, device="cuda")), None, 1, 4, 5, 6, capi.ptr(mean),
+                  capi.ptr(invstd), capi.ptr(gamma), capi.ptr(beta), 0, capi.stream_handle())
 
 
 @pytest.mark.parametrize("cl", [False, True], ids=["nchw", "nhwc"])

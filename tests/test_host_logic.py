@@ -86,6 +86,7 @@ def test_fx_passes_rewrite_and_preserve_results(pkg, monkeypatch):
     F.cross_entropy(ref(x), y).backward()
     F.cross_entropy(torch.compile(mod, backend=backend)(x), y).backward()
     assert sum(s["bn_relu"] for s in seen) == 3 and sum(s["bn_relu_backward"] for s in seen) == 3
+    assert sum(s["conv_bn_train"] for s in seen) == 3  # each conv + BatchNorm + ReLU became one op
     for a, b in zip(ref.parameters(), mod.parameters()):
         assert torch.allclose(a.grad, b.grad, rtol=1e-4, atol=1e-6)
     for a, b in zip(ref.buffers(), mod.buffers()):
@@ -109,6 +110,7 @@ def test_fx_passes_rewrite_and_preserve_results(pkg, monkeypatch):
     assert sum(s["bn_add_relu"] for s in seen) == 8 and sum(s["bn_add_relu_backward"] for s in seen) == 8
     assert sum(s["bn_relu"] for s in seen) == 9 and sum(s["bn_relu_backward"] for s in seen) == 9
     assert sum(s["dgrad_accumulate"] for s in seen) == 8  # the backward joins of the 8 residual blocks
+    assert sum(s["conv_bn_train"] for s in seen) == 20    # every conv feeds a BatchNorm: 9 + ReLU, 8 + identity + ReLU, 3 downsample (plain)
     for a, b in zip(ref.parameters(), mod.parameters()):
         assert (a.grad - b.grad).abs().max() <= 1e-4 * a.grad.abs().max() + 1e-7
     for a, b in zip(ref.buffers(), mod.buffers()):
