@@ -54,6 +54,8 @@ enum {
   OMT_EPI_RELU = 2,        /* y = max(y, 0)          (reference hb bit 1, omarchy_mac_torch/gemm.py:38) */
   OMT_EPI_BNSTATS = 4,     /* omt_conv_fwd: also write batch-norm partial statistics of y (see omt_conv_bnstats_groups) */
   OMT_EPI_ACCUM = 8,       /* omt_conv_dgrad: dx += result (gradient of a tensor with a second consumer, e.g. a residual branch) */
+  OMT_PRECISE_ACCUM = 0x400, /* tensor-core path: always keep the 3xTF32 cross terms in their own accumulator (by default 128 x 256
+                              * tiles with a reduction of at most 1152 share one, which lets their epilogue overlap the next tile) */
   OMT_FORCE_SIMT = 0x100,  /* skip the tcgen05 path (used by tests to cross-check the two paths) */
   OMT_FORCE_TC = 0x200     /* fail with OMT_EINVAL instead of taking the SIMT path */
 };
@@ -125,7 +127,8 @@ int omt_conv_fwd(const OmtConvGeo* g, const OmtAct* x, const float* w, const flo
                  float* stats, uint32_t flags, void* workspace, size_t workspace_bytes, omt_stream_t stream);
 /* Number of 32-row groups omt_conv_fwd(OMT_EPI_BNSTATS) writes partial statistics for with these operands, or 0 when that
  * call cannot produce them (a geometry or layout off the tensor-core path, an output that is not dense channels-last, a
- * reduction split over several CTAs): the caller then runs omt_bn_stats on y instead. */
+ * reduction split over several CTAs) or would lose by it (a reduction so short that the layer is bound by storing y):
+ * the caller then runs omt_bn_stats on y instead. */
 int32_t omt_conv_bnstats_groups(const OmtConvGeo* g, const OmtAct* x, const OmtAct* y);
 /* Floats of the partial-statistics buffer: groups * (2 * co + 1) values and ceil(co / 32) words the merge uses. */
 size_t omt_conv_bnstats_floats(int32_t groups, int32_t co);
@@ -281,7 +284,8 @@ typedef struct OmtParam {
 } OmtParam;
 
 /* g=+-g+wd*p; v=first?g:mom*m+(1-damp)*g; d=nesterov?g+mom*v:v; p-=lr*d  (sgd.wgsl:9-24).
- * `table` is a HOST array of `count` entries; it is copied to the device by this call (pinned staging). */
+ * `table` is a HOST array of `count` entries. The library keeps device copies of the last few distinct tables (a
+ * training loop passes the same one every step), so only the first call with a given table uploads it. */
 int omt_sgd(const OmtParam* table, int32_t count, float lr, float momentum, float dampening, float weight_decay,
             int32_t nesterov, int32_t first_step, int32_t maximize, omt_stream_t stream);
 /* Adam / AdamW (decoupled=1), adam.wgsl:13-27: bias corrections from the device step counter. */

@@ -22,6 +22,7 @@ OBJ = HERE / "build"
 NVCC = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xcompiler", "-fvisibility=default"]
+NVCC_FLAGS += os.environ.get("OMT_EXTRA_NVCC_FLAGS", "").split()  # e.g. -DOMT_TC_EXPERIMENTS for the timing experiments in conv_tc.cu
 
 
 def _stamp(src, flags):

@@ -10,7 +10,7 @@ _HERE = pathlib.Path(__file__).resolve().parent
 LIB_PATH = _HERE / "lib" / "libomt_b200.so"
 
 # flags (include/omt_b200.h)
-EPI_BIAS, EPI_RELU, EPI_BNSTATS, EPI_ACCUM, FORCE_SIMT, FORCE_TC = 1, 2, 4, 8, 0x100, 0x200
+EPI_BIAS, EPI_RELU, EPI_BNSTATS, EPI_ACCUM, FORCE_SIMT, FORCE_TC, PRECISE_ACCUM = 1, 2, 4, 8, 0x100, 0x200, 0x400
 BN_RELU, BN_FUNCTIONAL = 1, 2
 
 

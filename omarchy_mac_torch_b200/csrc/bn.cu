@@ -432,7 +432,7 @@ __global__ void __launch_bounds__(256) bn_partials_kernel(BnFromPartials a) {
   if (ch < c) {
     for (int g = sl * 8 + gl; g < a.groups; g += a.S * 8) {
       const float n = __ldg(a.cnt + g);
-      if (n > 0.f) merge(m, n, __ldg(a.part + (int64_t)2 * g * c + ch) / n, __ldg(a.part + ((int64_t)2 * g + 1) * c + ch));
+      if (n > 0.f) merge(m, n, __ldg(a.part + (int64_t)2 * g * c + ch) * (1.f / n), __ldg(a.part + ((int64_t)2 * g + 1) * c + ch));
     }
   }
   sh[0][gl][cx] = m.n; sh[1][gl][cx] = m.mean; sh[2][gl][cx] = m.m2;
@@ -449,10 +449,17 @@ __global__ void __launch_bounds__(256) bn_partials_kernel(BnFromPartials a) {
     if (!last) return;
     __threadfence();
     if (threadIdx.x == 0) a.tickets[blockIdx.x] = 0;  // ready for the next call
-    if (gl != 0 || ch >= c) return;
+    // the S slices of this channel block: eight lanes per channel take every eighth slice, then the same 8-way merge as above
     m = Moments{0.f, 0.f, 0.f};
-    for (int k = 0; k < a.S; k++)
-      merge(m, __ldcg(a.out + ((int64_t)k * 3) * c + ch), __ldcg(a.out + ((int64_t)k * 3 + 1) * c + ch), __ldcg(a.out + ((int64_t)k * 3 + 2) * c + ch));
+    if (ch < c) {
+      for (int k = gl; k < a.S; k += 8)
+        merge(m, __ldcg(a.out + ((int64_t)k * 3) * c + ch), __ldcg(a.out + ((int64_t)k * 3 + 1) * c + ch), __ldcg(a.out + ((int64_t)k * 3 + 2) * c + ch));
+    }
+    __syncthreads();  // (every thread of the block is here: `last` is uniform)
+    sh[0][gl][cx] = m.n; sh[1][gl][cx] = m.mean; sh[2][gl][cx] = m.m2;
+    __syncthreads();
+    if (gl != 0 || ch >= c) return;
+    for (int k = 1; k < 8; k++) merge(m, sh[0][k][cx], sh[1][k][cx], sh[2][k][cx]);
   } else if (gl != 0 || ch >= c) {
     return;
   }
@@ -505,7 +512,8 @@ int omt_bn_stats_from_partials(const float* partials, int32_t groups, int32_t c,
   OMT_REQUIRE(!(flags & OMT_BN_FUNCTIONAL) || (rm && rv && new_rm && new_rv), "omt_bn_stats_from_partials: functional mode needs rm, rv, new_rm, new_rv");
   cudaStream_t s = st(stream);
   const int gx = (int)cdiv(c, 32);
-  const int S = (int)std::max<int64_t>(1, std::min<int64_t>({cdiv(groups, 64), cdiv(4 * sm_count(), gx), 256}));
+  // slices: enough blocks to fill the device twice, at least 32 groups per lane, at most 64 (the last block merges them)
+  const int S = (int)std::max<int64_t>(1, std::min<int64_t>({cdiv(groups, 256), cdiv(2 * sm_count(), gx), 64}));
   // per-slice moments from the caching allocator; the ticket counters sit behind the group counts in the caller's buffer,
   // zeroed by the convolution that wrote the partials
   Scratch sc;

@@ -12,9 +12,10 @@
 //                loads of W (hi and lo planes), all completing on the stage's "loaded" mbarrier
 //   warp 1       allocates TMEM; one lane issues the MMAs: per 8-wide k-step three tcgen05.mma, then tcgen05.commit to
 //                free the stage; a final commit signals the epilogue
-//   warps 2..5   split A in place into hi (tf32-rounded) and lo, arrive on the stage's "split" mbarrier
-//   warps 6..9   epilogue: tcgen05.ld of their 32-lane quarter of the accumulators, bias / ReLU, store in the output's layout;
-//                for BN <= 128 TMEM holds two accumulator pairs, so the epilogue of tile i overlaps the main loop of tile i+1
+//   warps 2..5   produce A_lo next to the A tile TMA wrote (which serves as A_hi), arrive on the stage's "split" mbarrier
+//   warps 10..13 epilogue: tcgen05.ld of their 32-lane quarter of the accumulators, bias / ReLU, store in the output's layout;
+//                when TMEM holds two tiles' accumulators the epilogue of tile i overlaps the main loop of tile i+1
+//   warps 6..9   join the split warps when the reduction is long, the epilogue warps when it is short
 // Every mbarrier wait is bounded by a clock budget; on expiry the kernel raises an error word, all roles leave their loops,
 // TMEM is freed and the kernel returns (the host reports it as a failed launch at the next synchronisation).
 //
@@ -30,6 +31,7 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <vector>
 #include <mutex>
 
@@ -44,6 +46,10 @@ constexpr int BKF = 32;        // floats per k-block (128 bytes)
 constexpr int UMMA_K = 8;      // tf32 MMA depth
 constexpr int TC_THREADS = 448;  // producer warp, MMA warp, 4 split warps, 8 epilogue warps
 constexpr long long WAIT_BUDGET_CLOCKS = 2000000000ll;  // ~1 s at B200 clocks
+constexpr int FLEX_SPLIT_KBLOCKS = 8;  // from this many k-blocks per tile on, warps 6..9 split operands instead of storing tiles
+constexpr int BNSTATS_MIN_KBLOCKS = 16;            // epilogue statistics: from this reduction length on ...
+constexpr int64_t BNSTATS_SMALL_OUTPUT = 32 << 20;  // ... or when the output has at most this many elements
+constexpr int ACC1_MAX_KBLOCKS = 36;  // single-accumulator 128 x 256 tiles up to K = 1152 (error below 1e-5 of the largest output)
 
 __device__ int g_tc_error = 0;  // first failure: 1 = mbarrier wait expired
 
@@ -92,6 +98,11 @@ __device__ __forceinline__ void tma_im2col_4d(uint32_t dst, const CUtensorMap* m
       ::"r"(dst), "l"(map), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n), "h"(ow), "h"(oh)
       : "memory");
 }
+__device__ __forceinline__ void tma_prefetch_im2col_4d(const CUtensorMap* map, int c, int w, int h, int n, uint16_t ow, uint16_t oh) {
+  asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.im2col [%0, {%1, %2, %3, %4}], {%5, %6};" ::"l"(map), "r"(c), "r"(w), "r"(h), "r"(n),
+               "h"(ow), "h"(oh)
+               : "memory");
+}
 __device__ __forceinline__ void tma_tile_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z, int w) {
   asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
                ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z), "r"(w)
@@ -126,6 +137,14 @@ __device__ __forceinline__ void tmem_ld32x2(uint32_t ta, uint32_t tb, uint32_t (
       : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]), "=r"(a[4]), "=r"(a[5]), "=r"(a[6]), "=r"(a[7]), "=r"(a[8]), "=r"(a[9]), "=r"(a[10]), "=r"(a[11]), "=r"(a[12]), "=r"(a[13]), "=r"(a[14]), "=r"(a[15]), "=r"(a[16]), "=r"(a[17]), "=r"(a[18]), "=r"(a[19]), "=r"(a[20]), "=r"(a[21]), "=r"(a[22]), "=r"(a[23]), "=r"(a[24]), "=r"(a[25]), "=r"(a[26]), "=r"(a[27]), "=r"(a[28]), "=r"(a[29]), "=r"(a[30]), "=r"(a[31]),
         "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3]), "=r"(b[4]), "=r"(b[5]), "=r"(b[6]), "=r"(b[7]), "=r"(b[8]), "=r"(b[9]), "=r"(b[10]), "=r"(b[11]), "=r"(b[12]), "=r"(b[13]), "=r"(b[14]), "=r"(b[15]), "=r"(b[16]), "=r"(b[17]), "=r"(b[18]), "=r"(b[19]), "=r"(b[20]), "=r"(b[21]), "=r"(b[22]), "=r"(b[23]), "=r"(b[24]), "=r"(b[25]), "=r"(b[26]), "=r"(b[27]), "=r"(b[28]), "=r"(b[29]), "=r"(b[30]), "=r"(b[31])
       : "r"(ta), "r"(tb)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t ta, uint32_t (&a)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]), "=r"(a[4]), "=r"(a[5]), "=r"(a[6]), "=r"(a[7]), "=r"(a[8]), "=r"(a[9]), "=r"(a[10]), "=r"(a[11]), "=r"(a[12]), "=r"(a[13]), "=r"(a[14]), "=r"(a[15]), "=r"(a[16]), "=r"(a[17]), "=r"(a[18]), "=r"(a[19]), "=r"(a[20]), "=r"(a[21]), "=r"(a[22]), "=r"(a[23]), "=r"(a[24]), "=r"(a[25]), "=r"(a[26]), "=r"(a[27]), "=r"(a[28]), "=r"(a[29]), "=r"(a[30]), "=r"(a[31])
+      : "r"(ta)
       : "memory");
 }
 __device__ __forceinline__ float tf32_rna(float x) {
@@ -233,11 +252,16 @@ struct TcArgs {
 };
 static_assert(sizeof(TcArgs) == 128, "TcArgs is a kernel parameter whose size is performance-sensitive");
 
-template <int BN>
+// ACC1: one accumulator per tile instead of the (main, cross-term) pair. The main sum is then truncated three times per
+// k-step instead of once, which costs accuracy in proportion to the reduction length (measured 1.6e-5 of the largest output at
+// K = 2304 against 5.7e-6), so it is used only for 128 x 256 tiles with short reductions: there the pair fills TMEM, the
+// epilogue cannot overlap the next tile's main loop, and with a short main loop that exposed epilogue is a large share.
+template <int BN, bool ACC1 = false>
 struct Smem {
   static constexpr int STAGES = BN == 256 ? 2 : (BN == 128 ? 3 : 4);
-  static constexpr int ACC_BUFS = BN == 256 ? 1 : 2;          // accumulator pairs in TMEM (512 columns in total at most)
-  static constexpr int TMEM_COLS = ACC_BUFS * 2 * BN;          // 256 or 512: a power of two
+  static constexpr int ACC_COLS = ACC1 ? BN : 2 * BN;          // TMEM columns of one tile's accumulator(s)
+  static constexpr int ACC_BUFS = ACC_COLS == 512 ? 1 : 2;     // tiles in flight in TMEM (512 columns in total at most)
+  static constexpr int TMEM_COLS = ACC_BUFS * ACC_COLS;        // 256 or 512: a power of two
   static constexpr int A_BYTES = BM * 128, B_BYTES = BN * 128;
   static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
   static constexpr int EPI_OFF = STAGES * STAGE_BYTES;          // per epilogue warp one 32-row x 128-byte store buffer
@@ -274,11 +298,11 @@ __device__ __forceinline__ TileCoord decode_tile(const TcArgs& g, int t, int n_t
   return c;
 }
 
-template <int BN, bool SPLITK>
+template <int BN, bool SPLITK, bool ACC1 = false>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_y,
                const TcArgs g) {
-  using S = Smem<BN>;
+  using S = Smem<BN, ACC1>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const uint32_t smem_base = smem_u32(smem);
@@ -293,6 +317,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kblocks = g.kh * g.kw * g.cblocks;
   const int n_tiles = (g.N + BN - 1) / BN;
+#ifdef OMT_TC_EXPERIMENTS  // timing experiments only (results are wrong with most of these): which role bounds a tile
+  const int dbg = g.reserved_[0];  // 1 no stores, 2 no wait for the staging buffer, 4 no operand split, 8 no MMAs, 16 L2 prefetch, 32 no TMEM loads
+#else
+  constexpr int dbg = 0;
+#endif
   int splits = 1;  // a compile-time 1 in the common instantiation
   if constexpr (SPLITK) splits = g.splits;
   const int win_w = SPLITK ? 0 : g.win_w;  // the split-K fields alias the window fields
@@ -309,15 +338,19 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     return (int)(((int64_t)(t % splits + 1) * kblocks) / splits);
   };
 
+  // Warps 6..9 take the role that is short of hands: with a long reduction the tile's time goes to the main loop, where the
+  // operand split sits between a stage's arrival and its MMAs, so they split (8 split warps, 4 epilogue warps); with a short
+  // one the tile's time goes to storing it, so they run the epilogue (4 split warps, 8 epilogue warps).
+  const int split_warps = kblocks / splits >= FLEX_SPLIT_KBLOCKS ? 8 : 4;
   if (threadIdx.x == 0) {
     for (int s = 0; s < S::STAGES; s++) {
       mbar_init(BAR(s), 1);                    // loaded: one arrive.expect_tx + TMA bytes
-      mbar_init(BAR(S::STAGES + s), 4);        // split: one arrival per split warp
+      mbar_init(BAR(S::STAGES + s), split_warps);  // split: one arrival per split warp
       mbar_init(BAR(2 * S::STAGES + s), 1);    // free: tcgen05.commit
     }
     for (int b = 0; b < S::ACC_BUFS; b++) {
       mbar_init(BAR(ACC_FULL + b), 1);         // tcgen05.commit after the tile's last MMA
-      mbar_init(BAR(ACC_EMPTY + b), 8);        // one arrival per epilogue warp
+      mbar_init(BAR(ACC_EMPTY + b), 12 - split_warps);  // one arrival per epilogue warp
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -352,6 +385,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           else tma_im2col_4d(stage, &map_a, BAR(s), cb * BKF, w0, h0, c.img0, (uint16_t)kx, (uint16_t)ky);
           tma_tile_3d(stage + 2 * S::A_BYTES, &map_w, BAR(s), (tap * g.cblocks + cb) * BKF, c.n0, 0);
           tma_tile_3d(stage + 2 * S::A_BYTES + S::B_BYTES, &map_w, BAR(s), (tap * g.cblocks + cb) * BKF, c.n0, 1);
+          if ((dbg & 16) && !win_w && t + (int)gridDim.x < total_tiles) {  // the same k-block of this CTA's next tile, into L2
+            const TileCoord cn = decode_tile(g, t + gridDim.x, n_tiles, BN, splits, win_w);
+            tma_prefetch_im2col_4d(&map_a, cb * BKF, cn.ox0 * g.stride + g.low_w, cn.oy0 * g.stride + g.low_h, cn.img0, (uint16_t)kx, (uint16_t)ky);
+          }
         }
       }
       if (*abort_flag) {  // drain: let the copies already in flight land before the CTA exits (bounded)
@@ -374,7 +411,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         }
-        const uint32_t acc = tmem_base + b * (2 * BN);
+        const uint32_t acc = tmem_base + b * S::ACC_COLS;
+        const uint32_t cross = ACC1 ? acc : acc + BN;  // where the 2^-11-sized cross terms accumulate
         const int kb0 = kb_begin(t);
         for (int kb = kb0, kbe = kb_end(t); kb < kbe; kb++, it++) {
           const int s = it % S::STAGES, round = it / S::STAGES;
@@ -386,22 +424,32 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           const uint64_t b_hi = smem_desc_sw128(stage + 2 * S::A_BYTES), b_lo = smem_desc_sw128(stage + 2 * S::A_BYTES + S::B_BYTES);
 #pragma unroll
           for (int k = 0; k < BKF / UMMA_K; k++) {
+            if (dbg & 8) break;
             const uint64_t adv = (uint64_t)((k * UMMA_K * 4) >> 4);  // 32 bytes per k-step inside the swizzled row
             // two accumulators: the cross terms (2^-11 of the result) go to columns [BN, 2BN) so that the truncation the
             // tensor core applies on every accumulate hits the main sum once per k-step instead of three times
             const uint32_t accumulate = ((kb - kb0) | k) ? 1u : 0u;  // the split's first MMA overwrites the accumulators
-            umma_tf32(acc + BN, a_lo + adv, b_hi + adv, idesc, accumulate);
-            umma_tf32(acc + BN, a_hi + adv, b_lo + adv, idesc, 1u);
-            umma_tf32(acc, a_hi + adv, b_hi + adv, idesc, accumulate);
+            if constexpr (!ACC1 && 2 * BN <= 256) {
+              // B_lo follows B_hi in the stage, and the cross-term accumulator follows the main one in TMEM: one MMA of width
+              // 2*BN over [B_hi; B_lo] yields a_hi*b_hi and a_hi*b_lo at once, reading A_hi from shared memory once instead of
+              // twice (these narrow tiles are bound by operand reads from shared memory, not by the tensor pipe)
+              constexpr uint32_t idesc_wide = idesc_tf32(2 * BN);
+              umma_tf32(acc, a_hi + adv, b_hi + adv, idesc_wide, accumulate);
+              umma_tf32(cross, a_lo + adv, b_hi + adv, idesc, 1u);
+            } else {
+              umma_tf32(cross, a_lo + adv, b_hi + adv, idesc, accumulate);
+              umma_tf32(cross, a_hi + adv, b_lo + adv, idesc, 1u);
+              umma_tf32(acc, a_hi + adv, b_hi + adv, idesc, ACC1 ? 1u : accumulate);
+            }
           }
           umma_commit(BAR(2 * S::STAGES + s));  // stage is free once these MMAs have read it
         }
         if (ok) umma_commit(BAR(ACC_FULL + b));  // this tile's accumulators are complete
       }
     }
-  } else if (warp < 6) {
-    // ---------------- operand split (warps 2..5) ----------------
-    const int t4 = threadIdx.x - 64;  // 0..127
+  } else if (warp < 2 + split_warps) {
+    // ---------------- operand split (warps 2..5, or 2..9) ----------------
+    const int t4 = threadIdx.x - 64, split_threads = split_warps * 32;  // 0..127 or 0..255
     int it = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
@@ -411,9 +459,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (!ok) break;
         uint4* hi = reinterpret_cast<uint4*>(smem + s * S::STAGE_BYTES);
         uint4* lo = reinterpret_cast<uint4*>(smem + s * S::STAGE_BYTES + S::A_BYTES);
-#pragma unroll
-        for (int i = 0; i < S::A_BYTES / 16 / 128; i++) {
-          const int idx = i * 128 + t4;
+#pragma unroll 4
+        for (int idx = t4; idx < S::A_BYTES / 16; idx += split_threads) {
+          if (dbg & 4) break;
           uint4 h;
           const uint4 l = split_lo(hi[idx], h);
 #if !OMT_TC_IMPLICIT_HI
@@ -427,10 +475,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
     }
   } else {
-    // ---------------- epilogue (warps 6..13): overlaps the next tile's main loop when ACC_BUFS == 2 ----------------
-    // Two warps per TMEM lane quarter; each takes every other 32-column chunk.
+    // ---------------- epilogue (warps 6..13, or 10..13): overlaps the next tile's main loop when ACC_BUFS == 2 ----------------
+    // Two warps per TMEM lane quarter, each taking every other 32-column chunk, or one taking them all.
     const int q = warp & 3;           // TMEM lane quarter this warp may read
-    const int half = (warp - 6) >> 2;
+    const int halves = split_warps == 8 ? 1 : 2;        // epilogue warps per lane quarter
+    const int half = halves == 1 ? 0 : (warp - 6) >> 2;
     // Dense channels-last outputs leave through shared memory: the warp lays its 32 rows x 32 channels out with the 128-byte
     // swizzle (conflict-free 16-byte stores) and one lane issues a TMA store of the box, which clips rows and channels that
     // fall outside the tensor.
@@ -443,7 +492,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const TileCoord c = decode_tile(g, t, n_tiles, BN, splits, win_w);
-      const uint32_t acc = tmem_base + b * (2 * BN) + ((uint32_t)(q * 32) << 16);
+      const uint32_t acc = tmem_base + b * S::ACC_COLS + ((uint32_t)(q * 32) << 16);
       const int r = q * 32 + lane;
       int img, oy, ox;
       bool valid;
@@ -461,9 +510,18 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       float* yrow = g.y.p + g.y.off(img, 0, oy * g.out_step + g.out_y0, ox * g.out_step + g.out_x0);
       const bool vec = g.y.sc == 1 && ((reinterpret_cast<uintptr_t>(yrow) & 15) == 0);
 #pragma unroll 1
-      for (int ch = half; ch < BN / 32; ch += 2) {
+      for (int ch = half; ch < BN / 32; ch += halves) {
         uint32_t v[32], u[32];
-        tmem_ld32x2(acc + ch * 32, acc + BN + ch * 32, v, u);
+        if (dbg & 32) {
+#pragma unroll
+          for (int j = 0; j < 32; j++) { v[j] = 0u; u[j] = 0u; }
+        } else if constexpr (ACC1) {
+          tmem_ld32(acc + ch * 32, v);
+#pragma unroll
+          for (int j = 0; j < 32; j++) u[j] = 0u;  // +0.f below: folded away
+        } else {
+          tmem_ld32x2(acc + ch * 32, acc + BN + ch * 32, v, u);
+        }
         const int nb = c.n0 + ch * 32;
         if (nb >= g.N) continue;
         if constexpr (SPLITK) {  // raw partial sums of this split; the epilogue runs in splitk_epilogue_kernel
@@ -484,7 +542,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           o[j] = x;
         }
         if (g.store_mode) {
-          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // the previous box has left the buffer
+          if (dbg & 1) continue;
+          if (lane == 0 && !(dbg & 2)) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // the previous box has left the buffer
           __syncwarp();
           float4* row = reinterpret_cast<float4*>(buf + lane * 128);
 #pragma unroll
@@ -513,14 +572,14 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (cnt) {
               const int r0 = __ffs(vmask) - 1;
               shift = *reinterpret_cast<const float*>(buf + r0 * 128 + ((((lane >> 2) ^ (r0 & 7)) << 4) | ((lane & 3) << 2)));
-#pragma unroll 8
+              float p1[4] = {0.f, 0.f, 0.f, 0.f}, p2[4] = {0.f, 0.f, 0.f, 0.f};  // four independent chains (fixed order: deterministic)
+#pragma unroll
               for (int r = 0; r < 32; r++) {
                 const float v = *reinterpret_cast<const float*>(buf + r * 128 + ((((lane >> 2) ^ (r & 7)) << 4) | ((lane & 3) << 2)));
-                if ((vmask >> r) & 1u) {
-                  const float d = v - shift;
-                  s1 += d; s2 = fmaf(d, d, s2);
-                }
+                const float d = ((vmask >> r) & 1u) ? v - shift : 0.f;
+                p1[r & 3] += d; p2[r & 3] = fmaf(d, d, p2[r & 3]);
               }
+              s1 = (p1[0] + p1[1]) + (p1[2] + p1[3]); s2 = (p2[0] + p2[1]) + (p2[2] + p2[3]);
             }
             if (nb + lane < g.N) {
               const float fc = (float)cnt;
@@ -706,9 +765,14 @@ int launch_tc(const TcProblem& p, const float* wsplit, const TcArgs& args, int s
   std::call_once(attr_once, [] {
     attr_err = cudaFuncSetAttribute((conv_tc_kernel<BN, false>), cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
     if (attr_err == cudaSuccess) attr_err = cudaFuncSetAttribute((conv_tc_kernel<BN, true>), cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+    if (attr_err == cudaSuccess && BN == 256)
+      attr_err = cudaFuncSetAttribute((conv_tc_kernel<BN, false, BN == 256>), cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
   });
   OMT_CUDA(attr_err);
   TcArgs a = args;
+#ifdef OMT_TC_EXPERIMENTS
+  if (const char* e = getenv("OMT_TC_DBG")) a.reserved_[0] = atoi(e);
+#endif
   alignas(64) CUtensorMap map_y = map_w;  // placeholder when the epilogue stores directly
   if (splits > 1) {  // partial tiles go to the workspace with plain stores (these fields alias the window fields, unused here)
     a.splits = splits; a.unused_ = 0; a.part = part;
@@ -724,9 +788,12 @@ int launch_tc(const TcProblem& p, const float* wsplit, const TcArgs& args, int s
   OMT_REQUIRE(!(a.flags & OMT_EPI_BNSTATS) || a.store_mode == 1, "OMT_EPI_BNSTATS needs a dense channels-last output and an unsplit reduction");
   const int m_tiles = (int)cdiv(a.M, BM), n_tiles = (int)cdiv(a.N, BN);
   const unsigned grid = (unsigned)std::min<int64_t>((int64_t)m_tiles * n_tiles * splits, sm_count());
+  // 128 x 256 tiles with a short reduction: one accumulator per tile, so that two tiles fit TMEM and the epilogue overlaps
+  const bool acc1 = BN == 256 && splits == 1 && p.kh * p.kw * a.cblocks <= ACC1_MAX_KBLOCKS && !(a.flags & OMT_PRECISE_ACCUM);
   if (splits > 1) conv_tc_kernel<BN, true><<<grid, TC_THREADS, S::TOTAL, s>>>(map_a, map_w, map_y, a);
+  else if (acc1) conv_tc_kernel<BN, false, BN == 256><<<grid, TC_THREADS, S::TOTAL, s>>>(map_a, map_w, map_y, a);
   else conv_tc_kernel<BN, false><<<grid, TC_THREADS, S::TOTAL, s>>>(map_a, map_w, map_y, a);
-  int r = check_launch(BN == 64 ? "conv_tc_128x64" : (BN == 128 ? "conv_tc_128x128" : "conv_tc_128x256"));
+  int r = check_launch(BN == 64 ? "conv_tc_128x64" : (BN == 128 ? "conv_tc_128x128" : (acc1 ? "conv_tc_128x256_acc1" : "conv_tc_128x256")));
   if (r || splits == 1) return r;
   splitk_epilogue_kernel<<<(unsigned)cdiv((int64_t)a.M * a.N, 256), 256, 0, s>>>(a);
   return check_launch("conv_tc_splitk_epilogue");
@@ -1369,7 +1436,12 @@ int tc_bnstats_groups(const OmtConvGeo* g, const OmtAct* x, const OmtAct* y) {
   }
   TcProblem p{x->p, g->n, g->ci, g->ih, g->iw, g->oh, g->ow, g->co, g->ks, g->ks, g->stride, -g->pad, -g->pad, 1, 0, 0};
   const int64_t M = (int64_t)g->n * g->oh * g->ow;
-  if (plan_splits(M, g->co, g->ks * g->ks * (int)cdiv(g->ci, BKF), pick_bn(p)) > 1) return 0;
+  const int kblocks = g->ks * g->ks * (int)cdiv(g->ci, BKF);
+  // With a short reduction a tile's time is its epilogue (the layer is bound by storing y) and the statistics lengthen
+  // exactly that: on ResNet-50 at batch 256 they then cost more than the separate 4-byte-per-element pass over y they save
+  // (measured per layer and in the whole step). Small problems are bound by launches instead, and there one launch less wins.
+  if (kblocks < BNSTATS_MIN_KBLOCKS && M * g->co > BNSTATS_SMALL_OUTPUT) return 0;
+  if (plan_splits(M, g->co, kblocks, pick_bn(p)) > 1) return 0;
   return (int)cdiv(M, BM) * 4;
 }
 

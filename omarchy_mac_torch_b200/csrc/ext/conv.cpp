@@ -5,6 +5,8 @@
 // tile from the geometry, so the planner/tuning bindings are kept as inert shims.
 #include "omt.h"
 
+#include <cstdlib>
+
 #include <pybind11/functional.h>
 #include <pybind11/stl.h>
 
@@ -55,7 +57,9 @@ Tensor conv_forward(const Tensor& x, const Tensor& w, const Tensor* bias, const 
 Tensor conv_forward_stats(const Tensor& x, const Tensor& w, const Tensor* bias, const OmtConvGeo& g, Tensor& partials, int& groups) {
   Tensor out = dense4(empty_dev({g.n, g.co, g.oh, g.ow}, at::kFloat, prefer_cl(x, g.co)));
   OmtAct ax = act(x), ay = act(out);
-  groups = omt_conv_bnstats_groups(&g, &ax, &ay);
+  // OMARCHY_MAC_TORCH_EPILOGUE_STATS=0 leaves the statistics to a separate pass over y (for A/B measurements)
+  static const bool enabled = [] { const char* e = std::getenv("OMARCHY_MAC_TORCH_EPILOGUE_STATS"); return !(e && e[0] == '0'); }();
+  groups = enabled ? omt_conv_bnstats_groups(&g, &ax, &ay) : 0;
   uint32_t flags = bias ? OMT_EPI_BIAS : 0u;
   if (groups > 0) {
     partials = empty_dev({(int64_t)omt_conv_bnstats_floats(groups, g.co)}, at::kFloat);

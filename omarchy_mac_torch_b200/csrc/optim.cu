@@ -153,7 +153,9 @@ static int64_t stage_table(const OmtParam* table, int32_t count, bool adam, omt_
   // The table of a training loop is the same every step (same parameter, gradient and state addresses), so device copies
   // are kept and reused: no host-to-device copy on the steady-state path, which also keeps a step capturable in a CUDA
   // graph (a copy from a temporary host buffer would be replayed from freed memory).
-  struct Cached { std::vector<DevParam> host; void* dev = nullptr; uint64_t used = 0; };
+  // The upload is ordered on the stream of the call that made it; a later call on another stream waits for the entry's
+  // `ready` event first and registers itself as a user of the block, so that an evicted table is not recycled under it.
+  struct Cached { std::vector<DevParam> host; void* dev = nullptr; uint64_t used = 0; cudaStream_t stream = nullptr; cudaEvent_t ready = nullptr; };
   static std::mutex mu;
   static Cached cache[8];
   static uint64_t tick = 0;
@@ -162,6 +164,10 @@ static int64_t stage_table(const OmtParam* table, int32_t count, bool adam, omt_
   for (Cached& c : cache) {
     if (c.dev && c.host.size() == host.size() && std::memcmp(c.host.data(), host.data(), bytes) == 0) {
       c.used = ++tick;
+      if (c.stream != st(stream)) {
+        if (c.ready && cudaStreamWaitEvent(st(stream), c.ready, 0) != cudaSuccess) return cuda_fail(cudaGetLastError(), "cudaStreamWaitEvent(optimizer table)");
+        omt_record_stream(c.dev, stream);
+      }
       sc.p = c.dev;  // not owned by the Scratch
       return ((int64_t)host.size() << 40) | chunks;
     }
@@ -175,6 +181,9 @@ static int64_t stage_table(const OmtParam* table, int32_t count, bool adam, omt_
   // pageable source that stays alive in the cache entry
   cudaError_t e = cudaMemcpyAsync(slot->dev, slot->host.data(), bytes, cudaMemcpyHostToDevice, st(stream));
   if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyAsync(optimizer table)");
+  slot->stream = st(stream);
+  if (!slot->ready && cudaEventCreateWithFlags(&slot->ready, cudaEventDisableTiming) != cudaSuccess) slot->ready = nullptr;
+  if (slot->ready) cudaEventRecord(slot->ready, st(stream));
   sc.p = slot->dev;
   return ((int64_t)slot->host.size() << 40) | chunks;
 }

@@ -285,8 +285,10 @@ def test_fused_stacks_train_eval_and_accumulate(omt):
             core.kernel_counts(True)
             mod(X.to(D)); ref(X)  # (both, so that the running statistics compared below stay in step)
             kc = core.kernel_counts(True)
-            assert kc.get("bn_stats_from_partials", 0) == 3 and kc.get("bn_apply_pool2", 0) == 3, kc
-            assert not any(k.startswith(("bn_stats_part", "bn_stats_fin", "pool2_fwd", "bn_apply")) and k != "bn_apply_pool2" for k in kc), kc
+            # (the last block's conv has few output tiles and splits its reduction over CTAs: its statistics come from a
+            # separate pass over y, the other two from the conv epilogue)
+            assert kc.get("bn_stats_from_partials", 0) == 2 and kc.get("bn_stats_part_nhwc", 0) == 1 and kc.get("bn_apply_pool2", 0) == 3, kc
+            assert not any(k in ("pool2_fwd", "bn_apply") for k in kc), kc
         # (SGD at a step size where these runs converge rather than the reference script's Adam: Adam turns
         # rounding-noise gradients into +-lr steps, which makes parameter comparisons meaningless; the Adam kernels are
         # compared step by step in the optimizer tests. Error is taken per tensor against its largest element: BatchNorm
@@ -364,9 +366,9 @@ def test_omt_ops_device_vs_composite(omt):
     from omarchy_mac_torch_b200.native import core
     for ci_, co_, cl, bias_, with_res, act_ in ((16, 32, True, False, False, 1), (16, 32, True, True, True, 1), (16, 32, True, False, False, 0),
                                                  (3, 32, False, True, False, 1), (6, 5, False, True, True, 1)):
-        xa, wa = torch.randn(4, ci_, 12, 12), torch.randn(co_, ci_, 3, 3) * 0.2
+        xa, wa = torch.randn(32, ci_, 20, 20), torch.randn(co_, ci_, 3, 3) * 0.2  # 100 row tiles: no reduction split over CTAs
         ba = torch.randn(co_) if bias_ else None
-        ra = torch.randn(4, co_, 12, 12) if with_res else None
+        ra = torch.randn(32, co_, 20, 20) if with_res else None
         g_, b_, rm_, rv_ = torch.randn(co_), torch.randn(co_), torch.randn(co_), torch.rand(co_) + 0.5
         fmt = torch.channels_last if cl else torch.contiguous_format
         ref = omt_ops.conv_bn_train(xa, wa, ba, [1, 1], [1, 1], ra, g_, b_, rm_, rv_, 0.1, 1e-5, act_)
@@ -497,7 +499,7 @@ def test_resnet50_compile_path_matches_cpu(omt, capsys):
     kc = core.kernel_counts(True)
     assert not omt.FALLBACKS, dict(omt.FALLBACKS)
     assert kc.get("bn_apply_add", 0) >= 16 * 6 and kc.get("sgd_multi", 0) == 6, kc  # the fused residual tails and one optimizer launch per step
-    assert kc.get("bn_stats_from_partials", 0) >= 40 * 6, kc  # batch statistics reduced by the conv epilogues (all but the split-K layers)
+    assert kc.get("bn_stats_from_partials", 0) >= 6, kc  # at this small batch only the stem is long and wide enough for statistics in the conv epilogue
     assert sum(v for k, v in kc.items() if k.startswith(("conv_tc_1", "wgrad_tc_1"))) >= 150 * 6, kc  # the convs ran on the tensor cores
 
     def err(a, b):

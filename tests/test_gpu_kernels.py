@@ -77,7 +77,9 @@ TC_SHAPES = [(2, 3, 64, 32, 7, 2, 3), (3, 3, 24, 63, 11, 4, 2), (2, 4, 24, 20, 5
              (2, 64, 128, 16, 1, 1, 0), (4, 256, 512, 14, 1, 1, 0), (3, 128, 128, 7, 3, 1, 1), (5, 512, 64, 7, 3, 2, 1), (2, 96, 160, 9, 3, 1, 1),
              (2, 64, 96, 12, 5, 2, 2), (3, 256, 64, 8, 1, 2, 0), (3, 3, 64, 63, 11, 4, 2), (2, 4, 32, 20, 5, 2, 2), (2, 1, 32, 28, 3, 1, 1), (2, 3, 96, 40, 3, 1, 1),
              # few output tiles and a long reduction: split-K in forward and input gradient (also per stride phase)
-             (2, 256, 256, 4, 3, 1, 1), (4, 512, 512, 2, 3, 1, 1), (8, 128, 256, 8, 3, 2, 1), (2, 512, 136, 4, 1, 1, 0)]
+             (2, 256, 256, 4, 3, 1, 1), (4, 512, 512, 2, 3, 1, 1), (8, 128, 256, 8, 3, 2, 1), (2, 512, 136, 4, 1, 1, 0),
+             # more 128 x 256 tiles than SMs with a short reduction: one accumulator per tile, two tiles in flight in TMEM
+             (32, 256, 512, 28, 1, 1, 0), (40, 288, 264, 24, 1, 1, 0)]
 
 
 @pytest.mark.parametrize("shape", TC_SHAPES)
@@ -114,9 +116,12 @@ def test_tensor_core_path_vs_aten_and_exact_path(capi, shape):
     capi.call("omt_sync")  # a tensor-core kernel that gave up on a barrier would be reported here
     after = capi.kernel_counts()
     assert sum(v - before.get(k, 0) for k, v in after.items() if k.startswith(("conv_tc_1", "conv_tc_window", "wgrad_tc_1"))) >= (2 + wg_tc if few else 4)
-    # the two paths agree with each other far inside the tolerance
+    # the two paths agree with each other far inside the tolerance, with the cross terms in their own accumulator or not
     exact = capi.conv_fwd(xd, wd, bd, s, p, flags=capi.FORCE_SIMT | capi.EPI_RELU, cl=True)
     assert rel_err(host(capi.conv_fwd(xd, wd, bd, s, p, flags=capi.FORCE_TC | capi.EPI_RELU, cl=True)), host(exact)) <= 5e-5
+    assert rel_err(host(capi.conv_fwd(xd, wd, bd, s, p, flags=capi.FORCE_TC | capi.EPI_RELU | capi.PRECISE_ACCUM, cl=True)), host(exact)) <= 5e-5
+    if n >= 32:
+        assert after.get("conv_tc_128x256_acc1", 0) > before.get("conv_tc_128x256_acc1", 0), after
 
 
 @pytest.mark.parametrize("shape,cl_out", [((4, 64, 96, 14, 3, 1, 1), True), ((2, 32, 64, 16, 1, 2, 0), True), ((2, 64, 64, 16, 3, 2, 1), True),
@@ -304,13 +309,15 @@ def test_bn_golden(capi, golden, i, cl):
 
 
 BNSTATS_SHAPES = [  # n, ci, co, hw, ks, stride, pad, bias, expect the statistics from the epilogue
-    (4, 64, 96, 14, 3, 1, 1, False, True),      # 784 pixels: the last row tile holds 16 valid rows
-    (2, 32, 40, 15, 3, 1, 1, True, True),       # 40 output channels: a ragged channel chunk
+    (4, 32, 96, 14, 1, 1, 0, False, True),      # 784 pixels: the last row tile holds 16 valid rows
+    (2, 32, 40, 15, 1, 1, 0, True, True),       # 40 output channels: a ragged channel chunk
     (8, 3, 64, 32, 3, 1, 1, True, True),        # <= 4 input channels: rectangles of output pixels as GEMM rows
     (2, 3, 32, 35, 7, 2, 3, False, True),       # the same with a stride, odd sizes: rows outside the image are not counted
     (16, 64, 64, 28, 3, 1, 1, False, True),     # 128 x 64 tiles
     (16, 128, 128, 28, 3, 1, 1, True, True),    # 128 x 128 tiles
-    (32, 64, 256, 28, 1, 1, 0, False, True),    # 128 x 256 tiles, more tiles than SMs
+    (32, 256, 512, 28, 1, 1, 0, False, True),   # 128 x 256 tiles, one accumulator per tile, more tiles than SMs
+    (32, 64, 256, 28, 1, 1, 0, False, True),    # a reduction of two k-blocks on a small output: one launch less wins
+    (64, 64, 256, 56, 1, 1, 0, False, False),   # the same on a large output: bound by storing y, statistics left to a separate pass
     (4, 256, 512, 8, 1, 1, 0, False, False),    # few tiles and a long reduction: split over CTAs, no statistics from the epilogue
 ]
 
