@@ -188,7 +188,16 @@ int omt_dw_wgrad(const OmtConvGeo* g, const OmtAct* x, const OmtAct* gy, float* 
 
 /* ---- batch norm: reference batch_norm_ / batch_norm_backward_ (csrc/nn.cpp:25-78), bn_relu_* (csrc/fused.cpp) --- */
 
-enum { OMT_BN_RELU = 1 /* apply / mask ReLU */, OMT_BN_FUNCTIONAL = 2 /* running stats go to new_rm/new_rv */ };
+enum {
+  OMT_BN_RELU = 1,       /* apply / mask ReLU */
+  OMT_BN_FUNCTIONAL = 2, /* running stats go to new_rm/new_rv */
+  /* ReLU mask as bits. omt_bn_apply(_add) with OMT_BN_RELU also writes, directly behind y (at y.p + n*c*h*w, so y's
+   * allocation must extend ceil(n*c*h*w / 32) words further), one bit per element in memory order: word k, bit b =
+   * (y[32k + b] > 0). omt_bn_backward(_add) with OMT_BN_RELU then takes the mask from those words and reads none of y's
+   * values: 1/8 byte per element and pass instead of 4. The reference's bn_bwd_part / bn_bwd_apply shaders read y
+   * (bn_bwd_part.wgsl:25-38, bn_bwd_apply.wgsl:19-23). */
+  OMT_BN_MASKBITS = 4
+};
 
 /* Per-channel batch statistics. mean[c], var[c] (biased), from shifted sums like bn_stats_part/fin
  * (csrc/kernels/bn_stats_part.wgsl:22-31, bn_stats_fin.wgsl:15-21). Also updates the running statistics:

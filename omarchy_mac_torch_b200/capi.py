@@ -11,7 +11,7 @@ LIB_PATH = _HERE / "lib" / "libomt_b200.so"
 
 # flags (include/omt_b200.h)
 EPI_BIAS, EPI_RELU, EPI_BNSTATS, EPI_ACCUM, FORCE_SIMT, FORCE_TC, PRECISE_ACCUM = 1, 2, 4, 8, 0x100, 0x200, 0x400
-BN_RELU, BN_FUNCTIONAL = 1, 2
+BN_RELU, BN_FUNCTIONAL, BN_MASKBITS = 1, 2, 4
 
 
 class OmtError(RuntimeError):

@@ -13,6 +13,15 @@
 namespace omt {
 
 // ---------------------------------------------------------------------------------------------------------------
+// ReLU bit mask. The forward pass can leave, behind y, one bit per element in memory order: word k, bit b = (y[32k + b] > 0).
+// The backward passes then read 1/8 byte per element for the mask instead of 4 (they use nothing else of y).
+// ---------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t mask_nibble(const uint32_t* __restrict__ bits, int64_t e) {  // elements e..e+3, e % 4 == 0
+  return (__ldg(bits + (e >> 5)) >> (uint32_t)(e & 31)) & 0xFu;
+}
+__device__ __forceinline__ bool mask_bit(const uint32_t* __restrict__ bits, int64_t e) { return (__ldg(bits + (e >> 5)) >> (uint32_t)(e & 31)) & 1u; }
+
+// ---------------------------------------------------------------------------------------------------------------
 // partial sums. part layout: [c][S][2]
 // ---------------------------------------------------------------------------------------------------------------
 
@@ -20,8 +29,8 @@ namespace omt {
 // MODE 0: stats of x (shifted by x[0,ch,0,0]); MODE 1: backward sums (sum g, sum g*xhat), g masked by y>0 if RELU.
 template <int MODE, bool RELU>
 __global__ void __launch_bounds__(256) bn_part_nchw(const float* __restrict__ x, const float* __restrict__ g,
-                                                    const float* __restrict__ y, const float* __restrict__ mean,
-                                                    const float* __restrict__ invstd, int n, int c, int hw, int S,
+                                                    const float* __restrict__ y, const uint32_t* __restrict__ bits,
+                                                    const float* __restrict__ mean, const float* __restrict__ invstd, int n, int c, int hw, int S,
                                                     float* __restrict__ part) {
   __shared__ float red[32];
   const int ch = blockIdx.x, sl = blockIdx.y;
@@ -45,9 +54,14 @@ __global__ void __launch_bounds__(256) bn_part_nchw(const float* __restrict__ x,
         } else {
           float4 gv = __ldg(g4 + e);
           if (RELU) {
-            float4 yv = __ldg(y4 + e);
-            gv.x = yv.x > 0.f ? gv.x : 0.f; gv.y = yv.y > 0.f ? gv.y : 0.f;
-            gv.z = yv.z > 0.f ? gv.z : 0.f; gv.w = yv.w > 0.f ? gv.w : 0.f;
+            if (bits) {
+              const uint32_t m = mask_nibble(bits, base + 4 * (int64_t)e);
+              gv.x = (m & 1u) ? gv.x : 0.f; gv.y = (m & 2u) ? gv.y : 0.f; gv.z = (m & 4u) ? gv.z : 0.f; gv.w = (m & 8u) ? gv.w : 0.f;
+            } else {
+              float4 yv = __ldg(y4 + e);
+              gv.x = yv.x > 0.f ? gv.x : 0.f; gv.y = yv.y > 0.f ? gv.y : 0.f;
+              gv.z = yv.z > 0.f ? gv.z : 0.f; gv.w = yv.w > 0.f ? gv.w : 0.f;
+            }
           }
           s1 += (gv.x + gv.y) + (gv.z + gv.w);
           s2 += (gv.x * (xv.x - a0) + gv.y * (xv.y - a0) + gv.z * (xv.z - a0) + gv.w * (xv.w - a0)) * a1;
@@ -61,7 +75,7 @@ __global__ void __launch_bounds__(256) bn_part_nchw(const float* __restrict__ x,
           s1 += d; s2 += d * d;
         } else {
           float gv = __ldg(g + base + e);
-          if (RELU) gv = __ldg(y + base + e) > 0.f ? gv : 0.f;
+          if (RELU) gv = (bits ? mask_bit(bits, base + e) : __ldg(y + base + e) > 0.f) ? gv : 0.f;
           s1 += gv; s2 += gv * (xv - a0) * a1;
         }
       }
@@ -78,8 +92,8 @@ __global__ void __launch_bounds__(256) bn_part_nchw(const float* __restrict__ x,
 // NHWC: x is [P pixels][c]. Block = CX channel groups of 4 x PY pixel lanes; slice sl takes pixels sl*PY+py, +S*PY ...
 template <int MODE, bool RELU>
 __global__ void __launch_bounds__(256) bn_part_nhwc(const float* __restrict__ x, const float* __restrict__ g,
-                                                    const float* __restrict__ y, const float* __restrict__ mean,
-                                                    const float* __restrict__ invstd, int64_t P, int c, int S, int CX,
+                                                    const float* __restrict__ y, const uint32_t* __restrict__ bits,
+                                                    const float* __restrict__ mean, const float* __restrict__ invstd, int64_t P, int c, int S, int CX,
                                                     float* __restrict__ part) {
   __shared__ float4 sh1[256], sh2[256];
   const int cx = threadIdx.x % CX, py = threadIdx.x / CX, PY = blockDim.x / CX;
@@ -114,9 +128,14 @@ __global__ void __launch_bounds__(256) bn_part_nhwc(const float* __restrict__ x,
       } else {
         float4 gv = __ldg(reinterpret_cast<const float4*>(g + p * c + c4));
         if (RELU) {
-          float4 yv = __ldg(reinterpret_cast<const float4*>(y + p * c + c4));
-          gv.x = yv.x > 0.f ? gv.x : 0.f; gv.y = yv.y > 0.f ? gv.y : 0.f;
-          gv.z = yv.z > 0.f ? gv.z : 0.f; gv.w = yv.w > 0.f ? gv.w : 0.f;
+          if (bits) {
+            const uint32_t m = mask_nibble(bits, p * c + c4);
+            gv.x = (m & 1u) ? gv.x : 0.f; gv.y = (m & 2u) ? gv.y : 0.f; gv.z = (m & 4u) ? gv.z : 0.f; gv.w = (m & 8u) ? gv.w : 0.f;
+          } else {
+            float4 yv = __ldg(reinterpret_cast<const float4*>(y + p * c + c4));
+            gv.x = yv.x > 0.f ? gv.x : 0.f; gv.y = yv.y > 0.f ? gv.y : 0.f;
+            gv.z = yv.z > 0.f ? gv.z : 0.f; gv.w = yv.w > 0.f ? gv.w : 0.f;
+          }
         }
         s1.x += gv.x; s1.y += gv.y; s1.z += gv.z; s1.w += gv.w;
         s2.x += gv.x * (xv.x - a0.x) * a1.x; s2.y += gv.y * (xv.y - a0.y) * a1.y;
@@ -191,6 +210,8 @@ struct BnEw {
   const float* x; const float* g; const float* y; float* out;
   const float* res;  // KIND 0/1: optional residual added before the ReLU (same layout as x)
   float* gz;         // KIND 2 with RELU: optional second output, the ReLU-masked incoming gradient
+  uint32_t* bits_out;       // KIND 0 with RELU: optional ReLU bit mask of the output (one bit per element, memory order)
+  const uint32_t* bits_in;  // KIND 2 with RELU: the mask comes from these bits instead of from y's values
   const float* mean; const float* inv; const float* gamma; const float* beta; const float* dgb;
   float eps, m;
   int c, hw;
@@ -212,13 +233,18 @@ __device__ __forceinline__ float bn_ew_one(const BnEw& a, float xv, float gv, fl
 template <int KIND, bool RELU, bool NHWC>
 __global__ void __launch_bounds__(256) bn_ew_vec4(BnEw a) {
   int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
-  if (i >= a.total) return;
+  if (i >= a.total) return;  // (exited lanes of the last warp: the mask words below then carry unspecified bits past the end, which nobody reads)
   float4 xv = __ldg(reinterpret_cast<const float4*>(a.x + i)), gv = make_float4(0.f, 0.f, 0.f, 0.f), o;
   if (KIND == 2) {
     gv = __ldg(reinterpret_cast<const float4*>(a.g + i));
     if (RELU) {
-      const float4 yv = __ldg(reinterpret_cast<const float4*>(a.y + i));
-      gv.x = yv.x > 0.f ? gv.x : 0.f; gv.y = yv.y > 0.f ? gv.y : 0.f; gv.z = yv.z > 0.f ? gv.z : 0.f; gv.w = yv.w > 0.f ? gv.w : 0.f;
+      if (a.bits_in) {
+        const uint32_t m = mask_nibble(a.bits_in, i);
+        gv.x = (m & 1u) ? gv.x : 0.f; gv.y = (m & 2u) ? gv.y : 0.f; gv.z = (m & 4u) ? gv.z : 0.f; gv.w = (m & 8u) ? gv.w : 0.f;
+      } else {
+        const float4 yv = __ldg(reinterpret_cast<const float4*>(a.y + i));
+        gv.x = yv.x > 0.f ? gv.x : 0.f; gv.y = yv.y > 0.f ? gv.y : 0.f; gv.z = yv.z > 0.f ? gv.z : 0.f; gv.w = yv.w > 0.f ? gv.w : 0.f;
+      }
       if (a.gz) *reinterpret_cast<float4*>(a.gz + i) = gv;
     }
   } else if (a.res) {
@@ -248,6 +274,12 @@ __global__ void __launch_bounds__(256) bn_ew_vec4(BnEw a) {
     o.w = bn_ew_one<KIND, RELU>(a, xv.w, gv.w, mean, inv, ga, be, dg, db);
   }
   *reinterpret_cast<float4*>(a.out + i) = o;
+  if (KIND == 0 && RELU && a.bits_out) {  // 8 lanes x 4 elements make one word; lane 0 of each group of 8 stores it
+    const int lane = threadIdx.x & 31;
+    uint32_t v = ((o.x > 0.f ? 1u : 0u) | (o.y > 0.f ? 2u : 0u) | (o.z > 0.f ? 4u : 0u) | (o.w > 0.f ? 8u : 0u)) << (4 * (lane & 7));
+    v |= __shfl_xor_sync(0xffffffffu, v, 1); v |= __shfl_xor_sync(0xffffffffu, v, 2); v |= __shfl_xor_sync(0xffffffffu, v, 4);
+    if ((lane & 7) == 0) a.bits_out[i >> 5] = v;
+  }
 }
 
 template <int KIND, bool RELU>
@@ -257,13 +289,18 @@ __global__ void __launch_bounds__(256) bn_ew_scalar(BnEw a, bool nhwc) {
   int ch = nhwc ? (int)(i % a.c) : (int)((i / a.hw) % a.c);
   float xv = __ldg(a.x + i), gv = KIND == 2 ? __ldg(a.g + i) : (a.res ? __ldg(a.res + i) : 0.f);
   if (KIND == 2 && RELU) {
-    if (!(__ldg(a.y + i) > 0.f)) gv = 0.f;
+    if (!(a.bits_in ? mask_bit(a.bits_in, i) : __ldg(a.y + i) > 0.f)) gv = 0.f;
     if (a.gz) a.gz[i] = gv;
   }
   float inv = __ldg(a.inv + ch);
   if (KIND == 1) inv = rsqrtf(inv + a.eps);
-  a.out[i] = bn_ew_one<KIND, RELU>(a, xv, gv, __ldg(a.mean + ch), inv, __ldg(a.gamma + ch), KIND <= 1 ? __ldg(a.beta + ch) : 0.f,
-                                   KIND == 2 ? __ldg(a.dgb + ch) : 0.f, KIND == 2 ? __ldg(a.dgb + a.c + ch) : 0.f);
+  const float o = bn_ew_one<KIND, RELU>(a, xv, gv, __ldg(a.mean + ch), inv, __ldg(a.gamma + ch), KIND <= 1 ? __ldg(a.beta + ch) : 0.f,
+                                        KIND == 2 ? __ldg(a.dgb + ch) : 0.f, KIND == 2 ? __ldg(a.dgb + a.c + ch) : 0.f);
+  a.out[i] = o;
+  if (KIND == 0 && RELU && a.bits_out) {  // a warp covers 32 consecutive elements starting at a multiple of 32: one word
+    const uint32_t v = __ballot_sync(0xffffffffu, o > 0.f);
+    if ((threadIdx.x & 31) == 0) a.bits_out[i >> 5] = v;
+  }
 }
 
 template <int KIND>
@@ -378,8 +415,8 @@ static int layout_of(const OmtAct* a, int c, int h, int w) {
 
 // partial-sum launch shared by forward statistics (MODE 0) and backward (MODE 1)
 template <int MODE>
-static int launch_part(int lay, const float* x, const float* g, const float* y, const float* mean, const float* invstd, bool relu,
-                       int n, int c, int h, int w, int* S_out, float* part, cudaStream_t s) {
+static int launch_part(int lay, const float* x, const float* g, const float* y, const uint32_t* bits, const float* mean, const float* invstd,
+                       bool relu, int n, int c, int h, int w, int* S_out, float* part, cudaStream_t s) {
   const int hw = h * w;
   if (lay == 1 && c % 4 == 0) {
     int64_t P = (int64_t)n * hw;
@@ -389,16 +426,16 @@ static int launch_part(int lay, const float* x, const float* g, const float* y, 
     int S = (int)std::max<int64_t>(1, std::min<int64_t>(cdiv(P, PY * 4), cdiv(4 * sm_count(), gx)));
     *S_out = S;
     dim3 grid(gx, S);
-    if (relu) bn_part_nhwc<MODE, true><<<grid, 256, 0, s>>>(x, g, y, mean, invstd, P, c, S, CX, part);
-    else bn_part_nhwc<MODE, false><<<grid, 256, 0, s>>>(x, g, y, mean, invstd, P, c, S, CX, part);
+    if (relu) bn_part_nhwc<MODE, true><<<grid, 256, 0, s>>>(x, g, y, bits, mean, invstd, P, c, S, CX, part);
+    else bn_part_nhwc<MODE, false><<<grid, 256, 0, s>>>(x, g, y, bits, mean, invstd, P, c, S, CX, part);
     return check_launch(MODE == 0 ? "bn_stats_part_nhwc" : "bn_bwd_part_nhwc");
   }
   // NCHW (also used for channels-last with c % 4 != 0 through the caller's layout check)
   int S = (int)std::max<int64_t>(1, std::min<int64_t>(n, cdiv(4 * sm_count(), c)));
   *S_out = S;
   dim3 grid(c, S);
-  if (relu) bn_part_nchw<MODE, true><<<grid, 256, 0, s>>>(x, g, y, mean, invstd, n, c, hw, S, part);
-  else bn_part_nchw<MODE, false><<<grid, 256, 0, s>>>(x, g, y, mean, invstd, n, c, hw, S, part);
+  if (relu) bn_part_nchw<MODE, true><<<grid, 256, 0, s>>>(x, g, y, bits, mean, invstd, n, c, hw, S, part);
+  else bn_part_nchw<MODE, false><<<grid, 256, 0, s>>>(x, g, y, bits, mean, invstd, n, c, hw, S, part);
   return check_launch(MODE == 0 ? "bn_stats_part_nchw" : "bn_bwd_part_nchw");
 }
 
@@ -495,7 +532,7 @@ int omt_bn_stats(const OmtAct* x, int32_t n, int32_t c, int32_t h, int32_t w, fl
   if (r) return r;
   float* part = (float*)sc.p;
   int S = 1;
-  r = launch_part<0>(lay, x->p, nullptr, nullptr, nullptr, nullptr, false, n, c, h, w, &S, part, s);
+  r = launch_part<0>(lay, x->p, nullptr, nullptr, nullptr, nullptr, nullptr, false, n, c, h, w, &S, part, s);
   if (r) return r;
   float count = (float)((int64_t)n * h * w);
   float corr = count / std::max(count - 1.f, 1.f);
@@ -538,6 +575,8 @@ int omt_bn_apply_add(const OmtAct* x, const OmtAct* res, const OmtAct* y, int32_
   a.x = x->p; a.g = x->p; a.y = x->p; a.out = y->p; a.mean = mean; a.inv = invstd; a.gamma = gamma; a.beta = beta;
   a.res = has_res ? res->p : nullptr;
   a.c = c; a.hw = h * w; a.total = (int64_t)n * c * h * w;
+  OMT_REQUIRE(!(flags & OMT_BN_MASKBITS) || (flags & OMT_BN_RELU), "omt_bn_apply: OMT_BN_MASKBITS is the mask of the ReLU: it needs OMT_BN_RELU");
+  if (flags & OMT_BN_MASKBITS) a.bits_out = reinterpret_cast<uint32_t*>(y->p + a.total);
   return launch_ew<0>(a, flags & OMT_BN_RELU, lay == 1, st(stream), has_res ? "bn_apply_add" : "bn_apply");
 }
 int omt_bn_apply(const OmtAct* x, const OmtAct* y, int32_t n, int32_t c, int32_t h, int32_t w, const float* mean,
@@ -601,7 +640,9 @@ int omt_bn_backward_add(const OmtAct* gy, const OmtAct* x, const OmtAct* y, cons
   float* part = (float*)sc.p;
   float* raw = part + part_floats(c);
   int S = 1;
-  r = launch_part<1>(lay, x->p, gy->p, relu ? y->p : x->p, mean, invstd, relu, n, c, h, w, &S, part, s);
+  // OMT_BN_MASKBITS: the ReLU mask is the bit words the forward pass left behind y; y's values are not read
+  const uint32_t* bits = (relu && (flags & OMT_BN_MASKBITS)) ? reinterpret_cast<const uint32_t*>(y->p + (int64_t)n * c * h * w) : nullptr;
+  r = launch_part<1>(lay, x->p, gy->p, relu ? y->p : x->p, bits, mean, invstd, relu, n, c, h, w, &S, part, s);
   if (r) return r;
   bn_bwd_fin<<<(unsigned)cdiv((int64_t)c * 32, 256), 256, 0, s>>>(part, c, S, scale, dgb, raw);
   r = check_launch("bn_bwd_fin");
@@ -610,6 +651,7 @@ int omt_bn_backward_add(const OmtAct* gy, const OmtAct* x, const OmtAct* y, cons
   OMT_REQUIRE(!has_dres || layout_of(dres, c, h, w) == lay, "omt_bn_backward_add: dres must have the layout of x");
   a.x = x->p; a.g = gy->p; a.y = relu ? y->p : x->p; a.out = dx->p; a.mean = mean; a.inv = invstd; a.gamma = gamma; a.dgb = raw;
   a.gz = has_dres ? dres->p : nullptr;
+  a.bits_in = bits;
   a.m = (float)((int64_t)n * h * w); a.c = c; a.hw = h * w; a.total = (int64_t)n * c * h * w;
   return launch_ew<2>(a, relu, lay == 1, st(stream), has_dres ? "bn_bwd_apply_add" : "bn_bwd_apply");
 }

@@ -8,6 +8,7 @@
 #include "omt.h"
 
 #include <atomic>
+#include <unordered_map>
 #include <c10/cuda/CUDAGuard.h>
 
 #include <ATen/CPUGeneratorImpl.h>
@@ -118,7 +119,24 @@ void debug_end(const char* op) {  // OMARCHY_MAC_TORCH_DEBUG=1: surface asynchro
 // allocator
 // ------------------------------------------------------------------------------------------------
 
-static void free_block(void* p) { omt_free(p); }
+static std::mutex g_mask_mu;
+static std::unordered_map<const void*, int64_t> g_relu_masks;  // allocation start -> elements whose ReLU mask sits behind them
+void relu_mask_note(const void* p, int64_t numel) {
+  std::lock_guard<std::mutex> l(g_mask_mu);
+  g_relu_masks[p] = numel;
+}
+bool relu_mask_known(const void* p, int64_t numel) {
+  std::lock_guard<std::mutex> l(g_mask_mu);
+  auto it = g_relu_masks.find(p);
+  return it != g_relu_masks.end() && it->second == numel;
+}
+static void free_block(void* p) {
+  {
+    std::lock_guard<std::mutex> l(g_mask_mu);
+    if (!g_relu_masks.empty()) g_relu_masks.erase(p);
+  }
+  omt_free(p);
+}
 
 struct Allocator final : c10::Allocator {
   c10::DataPtr allocate(size_t n) override {
@@ -145,6 +163,14 @@ Tensor empty_dev(IntArrayRef size, c10::ScalarType dt, bool channels_last) {
   return at::detail::empty_generic(size, &g_alloc, ks, dt,
                                    channels_last && size.size() == 4 ? std::optional<at::MemoryFormat>(at::MemoryFormat::ChannelsLast)
                                                                      : std::nullopt);
+}
+
+Tensor empty_dev_tail(IntArrayRef size, bool channels_last, int64_t tail_floats) {
+  TORCH_INTERNAL_ASSERT(size.size() == 4);
+  const int64_t n = size[0], c = size[1], h = size[2], w = size[3], numel = n * c * h * w;
+  Tensor flat = empty_dev({numel + tail_floats}, at::kFloat);
+  std::vector<int64_t> st = channels_last ? std::vector<int64_t>{h * w * c, 1, w * c, c} : std::vector<int64_t>{c * h * w, h * w, w, 1};
+  return flat.as_strided(size, st, 0);
 }
 
 // ------------------------------------------------------------------------------------------------

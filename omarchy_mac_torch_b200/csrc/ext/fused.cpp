@@ -89,7 +89,10 @@ static std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> bn_res_relu_train(cons
   const int n = (int)x.size(0), c = (int)x.size(1), h = (int)x.size(2), wd = (int)x.size(3);
   Tensor nrm = empty_dev({c}, at::kFloat), nrv = empty_dev({c}, at::kFloat);
   Tensor mean = empty_dev({c}, at::kFloat), inv = empty_dev({c}, at::kFloat);
-  Tensor y = dense4(empty_dev(x.sizes(), at::kFloat, layout4(x) == 1));
+  // With a ReLU the output's allocation extends by one bit per element: the apply pass leaves the ReLU mask there, and the
+  // backward op (which receives this same tensor as its `y`) reads those bits instead of y's values.
+  const int64_t numel = x.numel();
+  Tensor y = relu ? empty_dev_tail(x.sizes(), layout4(x) == 1, (numel + 31) / 32) : dense4(empty_dev(x.sizes(), at::kFloat, layout4(x) == 1));
   OmtAct ax = act(x), ay = act(y);
   if (partials && groups > 0 && x.is_same(x_)) {
     check(omt_bn_stats_from_partials(partials->data_ptr<float>(), groups, c, fptr(mean), nullptr, fptr(inv), fptr(rm), fptr(rv), fptr(nrm), fptr(nrv),
@@ -101,8 +104,10 @@ static std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> bn_res_relu_train(cons
           "bn_relu_train statistics");
   }
   OmtAct ar = res_ ? act(res) : null_act();
-  check(omt_bn_apply_add(&ax, &ar, &ay, n, c, h, wd, fptr(mean), fptr(inv), fptr(w), fptr(b), relu ? OMT_BN_RELU : 0u, cur_stream()),
+  check(omt_bn_apply_add(&ax, &ar, &ay, n, c, h, wd, fptr(mean), fptr(inv), fptr(w), fptr(b), relu ? (OMT_BN_RELU | OMT_BN_MASKBITS) : 0u,
+                         cur_stream()),
         "bn_relu_train apply");
+  if (relu) relu_mask_note(y.data_ptr(), numel);
   return {y, mean, inv, nrm, nrv};
 }
 static std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> bn_relu_train_dev(const Tensor& x, const Tensor& w, const Tensor& b, const Tensor& rm,
@@ -122,6 +127,8 @@ static std::tuple<Tensor, Tensor, Tensor, Tensor> bn_res_relu_backward(const Ten
   if (layout4(x) == 1 && x.size(1) % 4 != 0) x = to_layout(x, 0);
   const int lay = layout4(x);
   Tensor g = to_layout(g_, lay), y = to_layout(y_, lay), mean = contig(mean_), inv = contig(invstd_);
+  // y as the forward op made it (same allocation, same layout, not a copy) carries its ReLU mask as bits behind its values
+  const bool bits = y.data_ptr() == y_.data_ptr() && y.storage_offset() == 0 && relu_mask_known(y.data_ptr(), y.numel());
   const int n = (int)x.size(0), c = (int)x.size(1), h = (int)x.size(2), wd = (int)x.size(3);
   Tensor dgb = empty_dev({2, c}, at::kFloat), gx, gres;
   OmtAct ag = act(g), ax = act(x), ay = act(y), adx = null_act(), adr = null_act();
@@ -133,8 +140,8 @@ static std::tuple<Tensor, Tensor, Tensor, Tensor> bn_res_relu_backward(const Ten
     gres = dense4(empty_dev(x.sizes(), at::kFloat, lay == 1));
     adr = act(gres);
   }
-  check(omt_bn_backward_add(&ag, &ax, &ay, &adx, &adr, n, c, h, wd, fptr(mean), fptr(inv), fptr(w), dgb.data_ptr<float>(), 1.f, OMT_BN_RELU,
-                            cur_stream()),
+  check(omt_bn_backward_add(&ag, &ax, &ay, &adx, &adr, n, c, h, wd, fptr(mean), fptr(inv), fptr(w), dgb.data_ptr<float>(), 1.f,
+                            OMT_BN_RELU | (bits ? OMT_BN_MASKBITS : 0u), cur_stream()),
         "bn_relu_backward");
   return {mask[0] ? gx : Tensor(), mask[1] ? dgb.select(0, 0) : Tensor(), mask[2] ? dgb.select(0, 1) : Tensor(), gres};
 }

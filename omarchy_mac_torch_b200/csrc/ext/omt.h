@@ -58,6 +58,12 @@ inline bool is_dev(const Tensor& t) { return t.defined() && t.device().type() ==
 inline bool f32(const Tensor& t) { return is_dev(t) && t.scalar_type() == at::kFloat; }
 inline bool defined(const std::optional<Tensor>& t) { return t && t->defined(); }
 Tensor empty_dev(IntArrayRef size, c10::ScalarType dt, bool channels_last = false);
+// A dense float32 4-D tensor (NCHW or channels-last) whose allocation extends `tail_floats` floats beyond its elements.
+Tensor empty_dev_tail(IntArrayRef size, bool channels_last, int64_t tail_floats);
+// ReLU bit masks kept behind activations (OMT_BN_MASKBITS): the forward op notes that the allocation starting at `p` carries
+// the mask of its `numel` elements; the backward op asks; the entry goes when the allocation is freed.
+void relu_mask_note(const void* p, int64_t numel);
+bool relu_mask_known(const void* p, int64_t numel);
 inline float* fptr(const Tensor& t) { return t.defined() ? t.data_ptr<float>() : nullptr; }
 inline float* fptr(const std::optional<Tensor>& t) { return defined(t) ? t->data_ptr<float>() : nullptr; }
 

@@ -459,28 +459,27 @@ def test_compile_backend_residual_blocks(omt):
 
 def test_resnet50_compile_path_matches_cpu(omt, capsys):
     """The benchmarked code path at a size the CPU finishes in seconds: ResNet-50 (Bottleneck [3,4,6,3]) called through
-    torch.compile(backend="omarchy_mac_torch"), SGD lr 0.1 momentum 0.9 nesterov weight decay 1e-4, batch 8 at 112x112,
+    torch.compile(backend="omarchy_mac_torch"), SGD momentum 0.9 nesterov weight decay 1e-4, batch 8 at 112x112,
     1 warm-up + 5 steps, against the same run on the CPU (tools/acceptance.py:51-98).
 
-    Three checks. (1) Step 0: the loss agrees to 1e-5 and every parameter's gradient is as close to a CPU float64 run as
-    the CPU's own fp32 run is (bound per tensor: max(1e-3, 4 x the CPU fp32 error)). (2) The parameters after the first
-    optimizer step (nesterov momentum + weight decay through the fused kernel) by the same rule. (3) The loss curve:
-    1e-3 relative per step where the run is that well conditioned. At lr 0.1 this network is chaotic from the second
-    step on (the CPU run on 1 thread and on 8 threads differ by 4e-2 at step 2 and by 50 % at step 3), so each step's
-    bound is max(1e-3, 10 x the CPU fp32 run's own distance from the float64 run) and both distances are printed."""
+    Run A, the benchmark's exact configuration (default initialisation, lr 0.1). At this batch size that run is chaotic from
+    the third step on: the CPU on 1 thread and on 8 threads differ by 4e-2 at step 2 and by 50 % at step 3, and CPU fp32
+    differs from CPU float64 by 10 % at step 2. What can be held to a bound is held: step 0's loss to 1e-5; every parameter's
+    gradient at step 0, and every parameter after the first optimizer step (nesterov momentum + weight decay through the
+    fused kernel), as close to a CPU float64 run as the CPU's own fp32 run is (per tensor: max(1e-3, 4 x the CPU fp32
+    error)); the losses of steps 0-2 within max(1e-3, 10 x the CPU fp32 run's distance from float64). All six losses and
+    distances are printed.
+
+    Run B, the same network, optimizer and code path made well conditioned (the last BatchNorm scale of every block starts at
+    zero, the usual ResNet-50 recipe, and lr 0.02; CPU fp32 then tracks float64 to 3e-7): all six losses within the plain
+    1e-3 of the CPU's, and the final parameters within 1e-3 per tensor."""
     from omarchy_mac_torch_b200 import models
     from omarchy_mac_torch_b200.native import core
-    torch.manual_seed(0)
-    ref = models.ResNet50()
-    ref64, mod = copy.deepcopy(ref).double(), copy.deepcopy(ref).to(D)
-    cmod = torch.compile(mod, backend="omarchy_mac_torch")
     x, y = torch.randn(8, 3, 112, 112), torch.randint(0, 1000, (8,))
-    make_opt = lambda m: torch.optim.SGD(m.parameters(), lr=0.1, momentum=0.9, nesterov=True, weight_decay=1e-4)
-    omt.FALLBACKS.clear()
-    core.kernel_counts(True)
 
-    def run(call, model, xx, yy):
-        opt, losses, grads, after = make_opt(model), [], None, None
+    def run(call, model, xx, yy, lr):
+        opt = torch.optim.SGD(model.parameters(), lr=lr, momentum=0.9, nesterov=True, weight_decay=1e-4)
+        losses, grads, after = [], None, None
         for it in range(6):
             loss = F.cross_entropy(call(xx), yy)
             opt.zero_grad()
@@ -493,18 +492,26 @@ def test_resnet50_compile_path_matches_cpu(omt, capsys):
             losses.append(loss.item())
         return losses, grads, after
 
-    l_cpu, g_cpu, p_cpu = run(ref, ref, x, y)
-    l_64, g_64, p_64 = run(ref64, ref64, x.double(), y)
-    l_dev, g_dev, p_dev = run(cmod, mod, x.to(D), y.to(D))
+    def err(a, b):
+        return float((a - b).abs().max() / b.abs().max().clamp_min(1e-30))
+
+    rel = lambda a, b: [abs(p - q) / max(abs(p), 1e-6) for p, q in zip(a, b)]
+
+    # ---- run A: the benchmark's configuration
+    torch.manual_seed(0)
+    ref = models.ResNet50()
+    ref64, mod = copy.deepcopy(ref).double(), copy.deepcopy(ref).to(D)
+    cmod = torch.compile(mod, backend="omarchy_mac_torch")
+    omt.FALLBACKS.clear()
+    core.kernel_counts(True)
+    l_cpu, g_cpu, p_cpu = run(ref, ref, x, y, 0.1)
+    l_64, g_64, p_64 = run(ref64, ref64, x.double(), y, 0.1)
+    l_dev, g_dev, p_dev = run(cmod, mod, x.to(D), y.to(D), 0.1)
     kc = core.kernel_counts(True)
     assert not omt.FALLBACKS, dict(omt.FALLBACKS)
     assert kc.get("bn_apply_add", 0) >= 16 * 6 and kc.get("sgd_multi", 0) == 6, kc  # the fused residual tails and one optimizer launch per step
     assert kc.get("bn_stats_from_partials", 0) >= 6, kc  # at this small batch only the stem is long and wide enough for statistics in the conv epilogue
     assert sum(v for k, v in kc.items() if k.startswith(("conv_tc_1", "wgrad_tc_1"))) >= 150 * 6, kc  # the convs ran on the tensor cores
-
-    def err(a, b):
-        return float((a - b).abs().max() / b.abs().max().clamp_min(1e-30))
-
     assert abs(l_dev[0] - l_cpu[0]) <= 1e-5 * abs(l_cpu[0])
     names = [n for n, _ in ref.named_parameters()]
     worst_g = worst_p = 0.0
@@ -513,15 +520,32 @@ def test_resnet50_compile_path_matches_cpu(omt, capsys):
         assert eg <= max(1e-3, 4 * err(gc, g6)), ("gradient", n, eg, err(gc, g6))
         assert ep <= max(1e-3, 4 * err(pc, p6)), ("parameter after one step", n, ep, err(pc, p6))
         worst_g, worst_p = max(worst_g, eg), max(worst_p, ep)
-    rel = lambda a, b: [abs(p - q) / max(abs(p), 1e-6) for p, q in zip(a, b)]
     d_cpu, d_64, noise = rel(l_cpu, l_dev), rel(l_64, l_dev), rel(l_64, l_cpu)
     cpu_g = max(err(gc, g6) for gc, g6 in zip(g_cpu, g_64))
     with capsys.disabled():
-        print(f"\nresnet50 compile path: worst gradient error vs float64 {worst_g:.2e} (the CPU's own: {cpu_g:.2e}), worst parameter error {worst_p:.2e}")
+        print(f"\nresnet50 compile path, lr 0.1: worst gradient error vs float64 {worst_g:.2e} (the CPU's own: {cpu_g:.2e}), worst parameter error {worst_p:.2e}")
         print("  device vs CPU fp32 :", [f"{v:.1e}" for v in d_cpu])
         print("  device vs CPU fp64 :", [f"{v:.1e}" for v in d_64])
         print("  CPU fp32 vs fp64   :", [f"{v:.1e}" for v in noise])
-    _assert_losses_track(l_dev, l_cpu, l_64, "resnet50 through the compile backend")
+    _assert_losses_track(l_dev[:3], l_cpu[:3], l_64[:3], "resnet50 through the compile backend")
+
+    # ---- run B: well conditioned
+    torch._dynamo.reset()
+    torch.manual_seed(0)
+    ref = models.ResNet50()
+    for m in ref.modules():
+        if isinstance(m, models._Bottleneck):
+            nn.init.zeros_(m.b3.weight)
+    mod = copy.deepcopy(ref).to(D)
+    cmod = torch.compile(mod, backend="omarchy_mac_torch")
+    l_cpu, _, _ = run(ref, ref, x, y, 0.02)
+    l_dev, _, _ = run(cmod, mod, x.to(D), y.to(D), 0.02)
+    assert not omt.FALLBACKS, dict(omt.FALLBACKS)
+    with capsys.disabled():
+        print("  well-conditioned run, device vs CPU fp32:", [f"{v:.1e}" for v in rel(l_cpu, l_dev)], "losses", [f"{v:.4f}" for v in l_dev])
+    assert max(rel(l_cpu, l_dev)) <= 1e-3, (l_cpu, l_dev)
+    for (n, a), b in zip(ref.named_parameters(), mod.parameters()):
+        assert err(b.detach().double().cpu(), a.detach().double()) <= 1e-3, n
 
 
 def test_compile_backend(omt):

@@ -399,6 +399,54 @@ def test_bn_apply_with_max_pool(capi, shape, cl):
 
 
 @pytest.mark.parametrize("cl", [False, True], ids=["nchw", "nhwc"])
+@pytest.mark.parametrize("shape", [(3, 8, 6, 10), (2, 5, 3, 7), (4, 32, 16, 16), (2, 12, 5, 5), (5, 64, 9, 11)])
+def test_bn_relu_mask_as_bits(capi, shape, cl):
+    """OMT_BN_MASKBITS: the apply pass leaves the ReLU mask as one bit per element behind y, the backward passes take the
+    mask from those bits. Checked: the bits are (y > 0) in memory order; a backward that sees only the bits (y's values
+    overwritten first) equals the backward that reads y; with and without the identity-branch gradient."""
+    n, c, h, w = shape
+    if cl and c % 4:
+        pytest.skip("channels-last BN kernels need c % 4 == 0")
+    torch.manual_seed(7)
+    numel = n * c * h * w
+    words = (numel + 31) // 32
+    x = dev(torch.randn(n, c, h, w) * 2 + 0.3, cl)
+    g = dev(torch.randn(n, c, h, w), cl)
+    res = dev(torch.randn(n, c, h, w), cl)
+    gamma, beta = dev(torch.randn(c)), dev(torch.randn(c))
+    rm, rv = torch.zeros(c, device="cuda"), torch.ones(c, device="cuda")
+    _, mean, invstd = capi.bn_train(x, gamma, beta, rm, rv, relu=True)
+    for with_res in (False, True):
+        flat = torch.full((numel + words,), float("nan"), device="cuda")
+        strides = (h * w * c, 1, w * c, c) if cl else (c * h * w, h * w, w, 1)
+        y = flat.as_strided((n, c, h, w), strides, 0)
+        capi.call("omt_bn_apply_add", capi.act(x), capi.act(res) if with_res else capi.null_act(), capi.act(y), n, c, h, w, capi.ptr(mean), capi.ptr(invstd),
+                  capi.ptr(gamma), capi.ptr(beta), capi.BN_RELU | capi.BN_MASKBITS, capi.stream_handle())
+        torch.cuda.synchronize()
+        y_ref = torch.empty_like(x)
+        capi.call("omt_bn_apply_add", capi.act(x), capi.act(res) if with_res else capi.null_act(), capi.act(y_ref), n, c, h, w, capi.ptr(mean),
+                  capi.ptr(invstd), capi.ptr(gamma), capi.ptr(beta), capi.BN_RELU, capi.stream_handle())
+        assert torch.equal(y, y_ref)
+        got = flat[numel:].view(torch.int32).cpu().numpy().view(np.uint32)
+        want = np.packbits((flat[:numel] > 0).cpu().numpy().astype(np.uint8), bitorder="little")
+        want = np.concatenate([want, np.zeros(-len(want) % 4, np.uint8)]).view(np.uint32)
+        valid = np.full(words * 32, False); valid[:numel] = True
+        keep = np.packbits(valid.astype(np.uint8), bitorder="little").view(np.uint32)  # bits past the end are unspecified
+        assert np.array_equal(got & keep, want & keep)
+        ref = capi.bn_backward(g, x, y_ref, mean, invstd, gamma, relu=True)
+        dres_ref = torch.empty_like(x)
+        dres = torch.empty_like(x)
+        dx_ref, dx, dgb_ref, dgb = torch.empty_like(x), torch.empty_like(x), torch.empty(2, c, device="cuda"), torch.empty(2, c, device="cuda")
+        capi.call("omt_bn_backward_add", capi.act(g), capi.act(x), capi.act(y_ref), capi.act(dx_ref), capi.act(dres_ref), n, c, h, w, capi.ptr(mean),
+                  capi.ptr(invstd), capi.ptr(gamma), capi.ptr(dgb_ref), 1.0, capi.BN_RELU, capi.stream_handle())
+        flat[:numel] = -1.0  # the values of y are gone: only the bits can tell the mask now
+        capi.call("omt_bn_backward_add", capi.act(g), capi.act(x), capi.act(y), capi.act(dx), capi.act(dres), n, c, h, w, capi.ptr(mean), capi.ptr(invstd),
+                  capi.ptr(gamma), capi.ptr(dgb), 1.0, capi.BN_RELU | capi.BN_MASKBITS, capi.stream_handle())
+        assert torch.equal(dx, dx_ref) and torch.equal(dres, dres_ref) and torch.equal(dgb, dgb_ref)
+        assert torch.equal(dx_ref, ref[0])
+
+
+@pytest.mark.parametrize("cl", [False, True], ids=["nchw", "nhwc"])
 def test_bn_large_mean_is_stable(capi, cl):
     """Shifted sums keep the variance accurate when |mean| >> std (bn_stats_part.wgsl:22-31)."""
     torch.manual_seed(1)
