@@ -109,6 +109,14 @@ uint64_t omt_launch_count(void);
 /* Writes "name=count\n" lines for every kernel launched since the last reset; returns bytes needed. */
 size_t omt_kernel_counts(char* buf, size_t n, int reset);
 
+/* Per-kernel device timing (reference set_debug_time_kernels / kernel_times, csrc/runtime.cpp:598-610, bound in
+ * csrc/module.cpp:30-33). While enabled, every kernel this library launches is bracketed by CUDA events on its stream
+ * (the first kernel of an entry point from an event recorded at its start, the following ones from their predecessor).
+ * omt_kernel_times waits for the recorded events and writes "name=milliseconds\n" lines, summed per kernel name; it
+ * returns the bytes needed. A debugging aid: it creates two events per launch and is not meant for timed runs. */
+int omt_kernel_timing(int enable);
+size_t omt_kernel_times(char* buf, size_t n, int reset);
+
 /* ---- dense convolution: reference gemm_forward / gemm_grad_input / gemm_grad_weight + csum_nchw ---------------- */
 
 /* Scratch bytes omt_conv_* needs for this geometry (kind: 0 fwd, 1 dgrad, 2 wgrad). When the caller passes
@@ -166,6 +174,17 @@ int omt_conv_wgrad_noalloc(const OmtConvGeo* g, const OmtAct* x, const OmtAct* g
 /* db[c] = sum over (n,h,w) of gy. Replaces csrc/kernels/csum_nchw.wgsl (csrc/conv.cpp:232-235). */
 int omt_conv_bias_grad(const OmtAct* gy, int32_t n, int32_t c, int32_t h, int32_t w, float* db, float scale,
                        omt_stream_t stream);
+
+/* out[M,N] (row-major) = A[M,K] * B[K,N] (+ bias[N]) in float32 on the same tensor-core kernels: a matrix product is the
+ * 1x1 case of the implicit GEMM (rows = pixels). Replaces mm_into / mm_ / addmm_ (csrc/linalg.cpp:25-92; the generated
+ * kind-4 kernel, omarchy_mac_torch/gemm.py). A and B are given by pointer and element strides (row stride, column stride);
+ * three operand layouts map onto the three conv passes and are taken without a copy:
+ *   A row-major, B column-major (B = W^T with W [N,K] row-major: nn.Linear forward)          -> the forward kernel (+ bias)
+ *   A row-major, B row-major    (grad_output * W: nn.Linear's input gradient)                -> the input-gradient kernel
+ *   A column-major, B row-major (A = G^T with G [K,M] row-major: nn.Linear's weight gradient) -> the weight-gradient kernel
+ * Any other stride pattern, or a bias outside the first case, returns OMT_EINVAL (the caller copies or adds). */
+int omt_gemm(const float* a, int64_t a_row_stride, int64_t a_col_stride, const float* b, int64_t b_row_stride,
+             int64_t b_col_stride, const float* bias, float* out, int32_t M, int32_t N, int32_t K, omt_stream_t stream);
 
 /* Per-call device timing of the dense-conv entry points (reference debug_time_kernels / kernel_times,
  * csrc/runtime.cpp:598-610, csrc/module.cpp:30-33). While enabled, omt_conv_fwd/dgrad/wgrad bracket their launches with

@@ -447,35 +447,51 @@ static int launch_part(int lay, const float* x, const float* g, const float* y, 
 struct Moments { float n, mean, m2; };
 __device__ __forceinline__ void merge(Moments& a, float nb, float mb, float m2b) {
   if (nb <= 0.f) return;
-  const float n = a.n + nb, d = mb - a.mean, f = nb / n;
+  const float n = a.n + nb, d = mb - a.mean, f = __fdividef(nb, n);
   a.mean = fmaf(d, f, a.mean);
   a.m2 += m2b + d * d * a.n * f;
   a.n = n;
 }
-// One launch: block = 32 channels x 8 group lanes; slice sl of S takes groups sl*8 + lane, + S*8, ... and leaves its merged
-// moments in out[sl][3][c]; the block that finishes last for a channel block (a ticket counter in `tickets`, which must be
-// zero on entry and is reset on exit) merges the S slices in slice order and writes what bn_stats_fin writes.
+// One launch: block = 32 channels x 16 group lanes; slice sl of S takes groups sl*16 + lane, + S*16, ... (two independent
+// chains per lane, merged at the end) and leaves its merged moments in out[sl][3][c]; the block that finishes last for a
+// channel block (a ticket counter in `tickets`, which must be zero on entry and is reset on exit) merges the S slices,
+// 16 lanes per channel again, and writes what bn_stats_fin writes. Every order of merging is fixed: deterministic.
 struct BnFromPartials {
   const float* part; const float* cnt; unsigned* tickets; float* out;
   int groups, c, S;
   float momentum, eps;
   float* mean; float* var; float* invstd; const float* rm_in; const float* rv_in; float* rm_out; float* rv_out;
 };
-__global__ void __launch_bounds__(256) bn_partials_kernel(BnFromPartials a) {
-  __shared__ float sh[3][8][32];
-  __shared__ bool last;
-  const int cx = threadIdx.x & 31, gl = threadIdx.x >> 5, ch = blockIdx.x * 32 + cx, sl = blockIdx.y, c = a.c;
-  Moments m{0.f, 0.f, 0.f};
-  if (ch < c) {
-    for (int g = sl * 8 + gl; g < a.groups; g += a.S * 8) {
-      const float n = __ldg(a.cnt + g);
-      if (n > 0.f) merge(m, n, __ldg(a.part + (int64_t)2 * g * c + ch) * (1.f / n), __ldg(a.part + ((int64_t)2 * g + 1) * c + ch));
-    }
-  }
+constexpr int MERGE_LANES = 16;
+__device__ __forceinline__ void merge_lanes(Moments& m, float (*sh)[MERGE_LANES][32], int gl, int cx) {  // result in lane 0
   sh[0][gl][cx] = m.n; sh[1][gl][cx] = m.mean; sh[2][gl][cx] = m.m2;
   __syncthreads();
+  if (gl == 0)
+    for (int k = 1; k < MERGE_LANES; k++) merge(m, sh[0][k][cx], sh[1][k][cx], sh[2][k][cx]);
+}
+__global__ void __launch_bounds__(32 * MERGE_LANES) bn_partials_kernel(BnFromPartials a) {
+  __shared__ float sh[3][MERGE_LANES][32];
+  __shared__ bool last;
+  const int cx = threadIdx.x & 31, gl = threadIdx.x >> 5, ch = blockIdx.x * 32 + cx, sl = blockIdx.y, c = a.c;
+  Moments m{0.f, 0.f, 0.f}, m1{0.f, 0.f, 0.f};
+  if (ch < c) {
+    const int step = a.S * MERGE_LANES;
+    int g = sl * MERGE_LANES + gl;
+    for (; g + step < a.groups; g += 2 * step) {
+      const float n0 = __ldg(a.cnt + g), n1 = __ldg(a.cnt + g + step);
+      const float s0 = __ldg(a.part + (int64_t)2 * g * c + ch), q0 = __ldg(a.part + ((int64_t)2 * g + 1) * c + ch);
+      const float s1 = __ldg(a.part + (int64_t)2 * (g + step) * c + ch), q1 = __ldg(a.part + ((int64_t)2 * (g + step) + 1) * c + ch);
+      if (n0 > 0.f) merge(m, n0, __fdividef(s0, n0), q0);
+      if (n1 > 0.f) merge(m1, n1, __fdividef(s1, n1), q1);
+    }
+    if (g < a.groups) {
+      const float n0 = __ldg(a.cnt + g);
+      if (n0 > 0.f) merge(m, n0, __fdividef(__ldg(a.part + (int64_t)2 * g * c + ch), n0), __ldg(a.part + ((int64_t)2 * g + 1) * c + ch));
+    }
+    merge(m, m1.n, m1.mean, m1.m2);
+  }
+  merge_lanes(m, sh, gl, cx);
   if (gl == 0 && ch < c) {
-    for (int k = 1; k < 8; k++) merge(m, sh[0][k][cx], sh[1][k][cx], sh[2][k][cx]);
     a.out[((int64_t)sl * 3) * c + ch] = m.n; a.out[((int64_t)sl * 3 + 1) * c + ch] = m.mean; a.out[((int64_t)sl * 3 + 2) * c + ch] = m.m2;
   }
   if (a.S > 1) {
@@ -486,20 +502,14 @@ __global__ void __launch_bounds__(256) bn_partials_kernel(BnFromPartials a) {
     if (!last) return;
     __threadfence();
     if (threadIdx.x == 0) a.tickets[blockIdx.x] = 0;  // ready for the next call
-    // the S slices of this channel block: eight lanes per channel take every eighth slice, then the same 8-way merge as above
     m = Moments{0.f, 0.f, 0.f};
-    if (ch < c) {
-      for (int k = gl; k < a.S; k += 8)
+    if (ch < c)
+      for (int k = gl; k < a.S; k += MERGE_LANES)
         merge(m, __ldcg(a.out + ((int64_t)k * 3) * c + ch), __ldcg(a.out + ((int64_t)k * 3 + 1) * c + ch), __ldcg(a.out + ((int64_t)k * 3 + 2) * c + ch));
-    }
     __syncthreads();  // (every thread of the block is here: `last` is uniform)
-    sh[0][gl][cx] = m.n; sh[1][gl][cx] = m.mean; sh[2][gl][cx] = m.m2;
-    __syncthreads();
-    if (gl != 0 || ch >= c) return;
-    for (int k = 1; k < 8; k++) merge(m, sh[0][k][cx], sh[1][k][cx], sh[2][k][cx]);
-  } else if (gl != 0 || ch >= c) {
-    return;
+    merge_lanes(m, sh, gl, cx);
   }
+  if (gl != 0 || ch >= c) return;
   const float v = m.n > 0.f ? m.m2 / m.n : 0.f, corr = m.n / fmaxf(m.n - 1.f, 1.f);
   if (a.mean) a.mean[ch] = m.mean;
   if (a.var) a.var[ch] = v;
@@ -550,7 +560,7 @@ int omt_bn_stats_from_partials(const float* partials, int32_t groups, int32_t c,
   cudaStream_t s = st(stream);
   const int gx = (int)cdiv(c, 32);
   // slices: enough blocks to fill the device twice, at least 32 groups per lane, at most 64 (the last block merges them)
-  const int S = (int)std::max<int64_t>(1, std::min<int64_t>({cdiv(groups, 256), cdiv(2 * sm_count(), gx), 64}));
+  const int S = (int)std::max<int64_t>(1, std::min<int64_t>({cdiv(groups, 16 * MERGE_LANES), cdiv(2 * sm_count(), gx), 64}));
   // per-slice moments from the caching allocator; the ticket counters sit behind the group counts in the caller's buffer,
   // zeroed by the convolution that wrote the partials
   Scratch sc;
@@ -560,7 +570,7 @@ int omt_bn_stats_from_partials(const float* partials, int32_t groups, int32_t c,
   const float* cnt = partials + (size_t)2 * groups * c;
   BnFromPartials a{partials, cnt, reinterpret_cast<unsigned*>(const_cast<float*>(cnt + groups)), (float*)sc.p, groups, c, S, momentum, eps,
                    mean, var, invstd, rm, rv, rm ? (fn ? new_rm : rm) : nullptr, rm ? (fn ? new_rv : rv) : nullptr};
-  bn_partials_kernel<<<dim3(gx, S), 256, 0, s>>>(a);
+  bn_partials_kernel<<<dim3(gx, S), 32 * MERGE_LANES, 0, s>>>(a);
   return check_launch("bn_stats_from_partials");
 }
 

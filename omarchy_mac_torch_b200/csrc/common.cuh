@@ -31,7 +31,15 @@ int check_launch(const char* kernel);             // note_launch + cudaGetLastEr
     }                                \
   } while (0)
 
-inline cudaStream_t st(omt_stream_t s) { return (cudaStream_t)s; }
+// Per-kernel timing (omt_kernel_timing): every entry point turns its stream handle into a cudaStream_t with st(), which,
+// while timing is on, records a "begin" event there; check_launch() then records an event after each launch, and a
+// kernel's time is the distance to the event before it on the same thread.
+extern bool g_kernel_timing;
+void timing_begin(cudaStream_t s);
+inline cudaStream_t st(omt_stream_t s) {
+  if (g_kernel_timing) timing_begin((cudaStream_t)s);
+  return (cudaStream_t)s;
+}
 inline int64_t cdiv(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
 int sm_count();  // SMs of the current device (148 on B200)

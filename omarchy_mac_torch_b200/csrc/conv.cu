@@ -243,6 +243,34 @@ int omt_conv_wgrad(const OmtConvGeo* g, const OmtAct* x, const OmtAct* gy, float
   return simt_conv_wgrad(g, x, gy, dw, scale, (float*)sc.p, st(stream));
 }
 
+int omt_gemm(const float* a, int64_t a_rs, int64_t a_cs, const float* b, int64_t b_rs, int64_t b_cs, const float* bias, float* out, int32_t M,
+             int32_t N, int32_t K, omt_stream_t stream) {
+  OMT_REQUIRE(a && b && out && M > 0 && N > 0 && K > 0, "omt_gemm: bad arguments");
+  // a [rows, ch] row-major matrix as a channels-last activation of 1x1 images
+  auto rows_act = [](const float* p, int64_t ch) { return OmtAct{const_cast<float*>(p), ch, 1, ch, ch}; };
+  const bool a_rm = a_cs == 1 && a_rs == K, a_cm = a_rs == 1 && a_cs == M, b_rm = b_cs == 1 && b_rs == N, b_cm = b_rs == 1 && b_cs == K;
+  OmtAct o = rows_act(out, N);
+  if (a_rm && b_cm) {  // out[m, n] = sum_k A[m, k] W[n, k]: forward of a 1x1 convolution with weights W
+    OmtConvGeo g{M, K, N, 1, 1, 1, 1, 1, 1, 0, 1};
+    OmtAct x = rows_act(a, K);
+    return omt_conv_fwd(&g, &x, b, bias, &o, nullptr, bias ? OMT_EPI_BIAS : 0u, nullptr, 0, stream);
+  }
+  OMT_REQUIRE(!bias, "omt_gemm: a bias is added only when B is column-major (the nn.Linear forward case)");
+  if (a_rm && b_rm) {  // out[m, n] = sum_k A[m, k] B[k, n]: input gradient of a 1x1 convolution with weights B [co = K, ci = N]
+    OmtConvGeo g{M, N, K, 1, 1, 1, 1, 1, 1, 0, 1};
+    OmtAct gy = rows_act(a, K);
+    return omt_conv_dgrad(&g, &gy, b, &o, 0, nullptr, 0, stream);
+  }
+  if (a_cm && b_rm) {  // out[m, n] = sum_k G[k, m] B[k, n]: weight gradient over K "pixels", gy = G [K, co = M], x = B [K, ci = N]
+    OmtConvGeo g{K, N, M, 1, 1, 1, 1, 1, 1, 0, 1};
+    OmtAct gy = rows_act(a, M), x = rows_act(b, N);
+    return omt_conv_wgrad(&g, &x, &gy, out, 1.f, 0, nullptr, 0, stream);
+  }
+  set_error("omt_gemm: operand strides (%lld,%lld) x (%lld,%lld) match none of the three supported layouts", (long long)a_rs, (long long)a_cs,
+            (long long)b_rs, (long long)b_cs);
+  return OMT_EINVAL;
+}
+
 int omt_conv_timing(int enable) {
   g_timing = enable != 0;
   return OMT_OK;

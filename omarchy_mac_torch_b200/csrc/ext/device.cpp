@@ -326,13 +326,22 @@ struct Guard final : c10::impl::DeviceGuardImplInterface {
     return old;
   }
   c10::DeviceIndex deviceCount() const noexcept override { return 1; }
-  void record(void** event, const c10::Stream&, const c10::DeviceIndex, const c10::EventFlag) const override {
+  // The CUDA stream behind a stream of this device: the one PyTorch names (autograd records events on the producer's stream
+  // and makes the consumer's stream wait, from threads whose current stream is a third one), unless a process-wide
+  // override is in force (a CUDA-graph capture keeps all of the device's work on its capture stream).
+  static omt_stream_t handle(const c10::Stream& s) {
+    cudaStream_t o;
+    if (stream_override(&o)) return (omt_stream_t)o;
+    if (!has_gpu()) return cur_stream();
+    return (omt_stream_t)as_cuda(s).stream();
+  }
+  void record(void** event, const c10::Stream& s, const c10::DeviceIndex, const c10::EventFlag) const override {
     ensure_init();
     if (!*event) *event = omt_event_create(0);
-    check(omt_event_record((omt_event_t)*event, cur_stream()), "event record");
+    check(omt_event_record((omt_event_t)*event, handle(s)), "event record");
   }
-  void block(void* event, const c10::Stream&) const override {
-    if (event) check(omt_stream_wait_event(cur_stream(), (omt_event_t)event), "stream wait event");
+  void block(void* event, const c10::Stream& s) const override {
+    if (event) check(omt_stream_wait_event(handle(s), (omt_event_t)event), "stream wait event");
   }
   bool queryEvent(void* event) const override { return !event || omt_event_query((omt_event_t)event) == 1; }
   void destroyEvent(void* event, const c10::DeviceIndex) const noexcept override {
@@ -341,13 +350,13 @@ struct Guard final : c10::impl::DeviceGuardImplInterface {
   void synchronizeEvent(void* event) const override {
     if (event) check(omt_event_sync((omt_event_t)event), "event synchronize");
   }
-  bool queryStream(const c10::Stream&) const override { return omt_stream_query(cur_stream()) == 1; }
-  void synchronizeStream(const c10::Stream&) const override { check(omt_stream_sync(cur_stream()), "stream synchronize"); }
+  bool queryStream(const c10::Stream& s) const override { return omt_stream_query(handle(s)) == 1; }
+  void synchronizeStream(const c10::Stream& s) const override { check(omt_stream_sync(handle(s)), "stream synchronize"); }
   void synchronizeDevice(const c10::DeviceIndex) const override {
     ensure_init();
     check(omt_sync(), "device synchronize");
   }
-  void recordDataPtrOnStream(const c10::DataPtr& p, const c10::Stream&) const override { omt_record_stream(p.get(), cur_stream()); }
+  void recordDataPtrOnStream(const c10::DataPtr& p, const c10::Stream& s) const override { omt_record_stream(p.get(), handle(s)); }
 };
 C10_REGISTER_GUARD_IMPL(PrivateUse1, Guard);
 

@@ -78,11 +78,28 @@ PYBIND11_MODULE(_native, m) {
   // Names that only meant something for run-time generated WGSL and the wgpu submission queue: accepted, no effect.
   m.def("register_source", [](const std::string&, const std::string&) {});
   m.def("validate_kernels", []() { return std::vector<std::string>(); });
-  m.def("kernel_times", [](bool) { return std::map<std::string, double>(); });
+  m.def("kernel_times", [](bool reset) {  // {kernel: summed milliseconds} since debug_time_kernels(True)
+    size_t n = omt_kernel_times(nullptr, 0, 0);
+    std::string buf(n + 1, '\0');
+    omt_kernel_times(buf.data(), buf.size(), reset ? 1 : 0);
+    std::map<std::string, double> out;
+    size_t pos = 0;
+    while (pos < buf.size()) {
+      size_t eol = buf.find('\n', pos);
+      if (eol == std::string::npos) break;
+      std::string line = buf.substr(pos, eol - pos);
+      size_t eq = line.rfind('=');
+      if (eq != std::string::npos) out[line.substr(0, eq)] = std::stod(line.substr(eq + 1));
+      pos = eol + 1;
+    }
+    return out;
+  }, py::arg("reset") = true);
+  m.def("debug_time_kernels", [](bool on) { omt_kernel_timing(on ? 1 : 0); });
+  m.def("set_mm_planner", [](py::object) {});  // the reference's generated-GEMM planner hook (csrc/linalg.cpp:94-96): nothing to plan here
   m.def("queue_state", []() { return std::make_tuple(0, 0, 0, 0.0); });
   m.def("set_queue", [](int, int) {});
   m.def("set_target_backlog_ms", [](double) {});
-  for (const char* name : {"debug_time_kernels", "debug_skip_submit"}) m.def(name, [](bool) {});
+  m.def("debug_skip_submit", [](bool) {});
   m.def("flush", []() {});
   m.attr("built_with_torch") = TORCH_VERSION;
   bind_conv(m);

@@ -1,6 +1,7 @@
 // Runtime half of libomt_b200.so: device selection, error state, caching allocator, streams/events, transfers,
 // launch accounting. Replaces the reference's wgpu runtime (csrc/runtime.cpp) and the allocator / guard parts of
 // csrc/device.cpp with CUDA equivalents behind a C ABI.
+#include <algorithm>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -35,10 +36,34 @@ int cuda_fail(cudaError_t e, const char* what) {
   if (!recoverable && !g_sticky) g_sticky = (int)e;
   return OMT_ECUDA;
 }
-void note_launch(const char* kernel) {
+// ---- per-kernel device timing (reference debug_time_kernels / kernel_times, csrc/runtime.cpp:598-610) ----
+bool g_kernel_timing = false;
+struct TimedLaunch { std::string name; cudaEvent_t a, b; };
+static std::vector<TimedLaunch> g_timed_launches;  // guarded by g_mu
+static thread_local cudaStream_t t_stream = nullptr;
+static thread_local cudaEvent_t t_prev = nullptr;    // the event the next launch on this thread starts from
+void timing_begin(cudaStream_t s) {
+  cudaEvent_t e;
+  if (cudaEventCreate(&e) != cudaSuccess) return;
+  cudaEventRecord(e, s);
+  t_stream = s; t_prev = e;
+}
+static void timing_after_launch(const char* kernel) {
+  if (!t_prev) return;
+  cudaEvent_t e;
+  if (cudaEventCreate(&e) != cudaSuccess) return;
+  cudaEventRecord(e, t_stream);
   std::lock_guard<std::mutex> l(g_mu);
-  g_launches++;
-  g_kcount[kernel]++;
+  g_timed_launches.push_back({kernel, t_prev, e});  // (events are shared between neighbours: destroyed once, at read-out)
+  t_prev = e;
+}
+void note_launch(const char* kernel) {
+  {
+    std::lock_guard<std::mutex> l(g_mu);
+    g_launches++;
+    g_kcount[kernel]++;
+  }
+  if (g_kernel_timing) timing_after_launch(kernel);
 }
 int check_launch(const char* kernel) {
   note_launch(kernel);
@@ -340,6 +365,44 @@ int omt_memset(void* dst, int byte, size_t bytes, omt_stream_t s) {
   if (!bytes) return OMT_OK;
   OMT_CUDA(cudaMemsetAsync(dst, byte, bytes, st(s)));
   return OMT_OK;
+}
+
+int omt_kernel_timing(int enable) {
+  g_kernel_timing = enable != 0;
+  return OMT_OK;
+}
+size_t omt_kernel_times(char* buf, size_t n, int reset) {
+  std::vector<TimedLaunch> launches;
+  {
+    std::lock_guard<std::mutex> l(g_mu);
+    launches = g_timed_launches;
+    if (reset) g_timed_launches.clear();
+  }
+  std::map<std::string, double> ms;
+  std::vector<cudaEvent_t> events;
+  for (auto& t : launches) {
+    float v = 0.f;
+    if (cudaEventSynchronize(t.b) == cudaSuccess && cudaEventElapsedTime(&v, t.a, t.b) == cudaSuccess) ms[t.name] += v;
+    events.push_back(t.a); events.push_back(t.b);
+  }
+  (void)cudaGetLastError();
+  if (reset) {
+    std::sort(events.begin(), events.end());
+    events.erase(std::unique(events.begin(), events.end()), events.end());
+    for (cudaEvent_t e : events) cudaEventDestroy(e);
+  }
+  std::string s;
+  char line[160];
+  for (auto& kv : ms) {
+    snprintf(line, sizeof(line), "%s=%.6f\n", kv.first.c_str(), kv.second);
+    s += line;
+  }
+  if (buf && n) {
+    size_t c = s.size() < n - 1 ? s.size() : n - 1;
+    memcpy(buf, s.data(), c);
+    buf[c] = 0;
+  }
+  return s.size() + 1;
 }
 
 uint64_t omt_launch_count(void) { return g_launches; }

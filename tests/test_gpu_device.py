@@ -389,6 +389,93 @@ def test_omt_ops_device_vs_composite(omt):
     assert not omt.FALLBACKS, dict(omt.FALLBACKS)
 
 
+def test_linear_layers_run_on_the_conv_gemm_kernels(omt):
+    """aten::mm / aten::addmm on the device (csrc/linalg.cpp:62-92 of the reference): nn.Linear forward, input gradient and
+    weight gradient are the three layouts omt_gemm maps onto the forward / input-gradient / weight-gradient kernels;
+    against float64 on the CPU. Sizes: the AlexNet classifier's first layer at batch 16, the MobileNetV3 head, ragged
+    sizes that leave the tensor-core path (exact-fp32 kernels), and operand layouts that need a copy."""
+    from omarchy_mac_torch_b200.native import core
+    torch.manual_seed(0)
+    omt.FALLBACKS.clear()
+    core.bridge_counts(True)
+    for batch, fin, fout in ((16, 9216, 4096), (32, 576, 1024), (32, 1024, 1000), (256, 2048, 1000), (7, 37, 11), (64, 64, 8)):
+        lin = nn.Linear(fin, fout)
+        x = torch.randn(batch, fin)
+        gy = torch.randn(batch, fout)
+        x64 = x.double().requires_grad_()
+        lin64 = copy.deepcopy(lin).double()
+        y64 = lin64(x64)
+        y64.backward(gy.double())
+        lind = copy.deepcopy(lin).to(D)
+        xd = x.to(D).requires_grad_()
+        core.kernel_counts(True)
+        yd = lind(xd)
+        yd.backward(gy.to(D))
+        kc = core.kernel_counts(True)
+        assert e(yd, y64.float()) <= TOL and e(xd.grad, x64.grad.float()) <= TOL, (batch, fin, fout)
+        assert e(lind.weight.grad, lin64.weight.grad.float()) <= TOL and e(lind.bias.grad, lin64.bias.grad.float()) <= TOL, (batch, fin, fout)
+        if fin % 32 == 0 and fout % 8 == 0:  # tensor-core geometries: forward, input gradient and weight gradient kernels all ran
+            assert sum(v for k, v in kc.items() if k.startswith("conv_tc_1")) >= 2 and sum(v for k, v in kc.items() if k.startswith("wgrad_tc_1")) >= 1, kc
+    # plain products in every combination of operand layouts, and addmm forms outside the nn.Linear case (served by the bridge)
+    a, b = torch.randn(48, 40), torch.randn(40, 24)
+    want = (a.double() @ b.double()).float()
+    ad, bd = a.to(D), b.to(D)
+    for aa in (ad, ad.t().contiguous().t()):
+        for bb in (bd, bd.t().contiguous().t()):
+            assert e(aa @ bb, want) <= TOL
+    assert e(torch.mm(ad[:, ::2], bd[::2]), (a[:, ::2].double() @ b[::2].double()).float()) <= TOL  # strided: copied
+    bias = torch.randn(48, 24)
+    assert e(torch.addmm(bias.to(D), ad, bd, beta=0.5, alpha=2.0), torch.addmm(bias, a, b, beta=0.5, alpha=2.0)) <= TOL
+    bc = core.bridge_counts(True)
+    assert not any(k.startswith("aten::mm") for k in bc), bc
+    assert all("mm" not in k or "addmm" in k for k in omt.FALLBACKS), dict(omt.FALLBACKS)
+    omt.FALLBACKS.clear()
+
+
+def test_side_stream_producer_and_default_stream_consumer(omt):
+    """Events and record_stream act on the stream they are given, not on the calling thread's current stream: a tensor
+    produced on a side stream, handed over by an event, consumed on the default stream."""
+    side = torch.Stream(device=D)
+    base = torch.randn(1 << 22).to(D)
+    omt.synchronize()
+    with side:
+        t = base
+        for _ in range(20):   # enough queued work that the consumer would run ahead without the event
+            t = t * 1.0001 + 1.0
+        ev = torch.Event(D)
+        ev.record(side)
+    t.record_stream(torch.accelerator.current_stream())
+    ev.wait(torch.accelerator.current_stream())
+    got = (t * 2).cpu()
+    want = base.cpu()
+    for _ in range(20):
+        want = want * 1.0001 + 1.0
+    assert torch.allclose(got, want * 2, rtol=1e-5, atol=1e-5)
+    side.synchronize()
+    assert side.query()
+
+
+def test_kernel_times_reports_device_time_per_kernel(omt):
+    """debug_time_kernels / kernel_times (csrc/module.cpp:30-33 of the reference): per-kernel device time from CUDA events."""
+    from omarchy_mac_torch_b200.native import core
+    conv = nn.Conv2d(16, 32, 3, padding=1).to(D)
+    x = torch.randn(8, 16, 32, 32).to(D).contiguous(memory_format=torch.channels_last)
+    conv(x)
+    core.kernel_times(True)
+    core.debug_time_kernels(True)
+    try:
+        for _ in range(3):
+            conv(x)
+        omt.synchronize()
+        times = core.kernel_times(True)
+    finally:
+        core.debug_time_kernels(False)
+    conv_ms = sum(v for k, v in times.items() if k.startswith("conv_tc_1"))
+    assert conv_ms > 0 and all(0 <= v < 50 for v in times.values()), times
+    assert "conv_tc_weight_split" in times
+    assert core.kernel_times(True) == {}
+
+
 def test_step_graph_replays_match_eager_steps(omt):
     """graphs.capture: the whole training step (zero_grad, fused-stack forward/backward, fused SGD) recorded once and
     replayed; every replay has to do exactly what an eager step does, also after the static batch tensors are refilled."""
@@ -465,10 +552,12 @@ def test_resnet50_compile_path_matches_cpu(omt, capsys):
     Run A, the benchmark's exact configuration (default initialisation, lr 0.1). At this batch size that run is chaotic from
     the third step on: the CPU on 1 thread and on 8 threads differ by 4e-2 at step 2 and by 50 % at step 3, and CPU fp32
     differs from CPU float64 by 10 % at step 2. What can be held to a bound is held: step 0's loss to 1e-5; every parameter's
-    gradient at step 0, and every parameter after the first optimizer step (nesterov momentum + weight decay through the
-    fused kernel), as close to a CPU float64 run as the CPU's own fp32 run is (per tensor: max(1e-3, 4 x the CPU fp32
-    error)); the losses of steps 0-2 within max(1e-3, 10 x the CPU fp32 run's distance from float64). All six losses and
-    distances are printed.
+    gradients at step 0 and the parameters after the first optimizer step (nesterov momentum + weight decay through the
+    fused kernel) against a CPU float64 run, measured the way the CPU's own fp32 run can be measured: over all tensors
+    together (relative L2 distance: at most max(1e-3, 4 x the CPU's), and per tensor (max norm: at most max(1e-3, 4 x the
+    CPU's error on that tensor, 2 x the CPU's worst tensor): single ReLU inputs within rounding of zero flip their mask in
+    one fp32 run and not in another, which moves a 4x4-pixel layer's gradients by 10-20 %, on the CPU as well); the losses
+    of steps 0-2 within max(1e-3, 10 x the CPU fp32 run's distance from float64). All six losses and distances are printed.
 
     Run B, the same network, optimizer and code path made well conditioned (the last BatchNorm scale of every block starts at
     zero, the usual ResNet-50 recipe, and lr 0.02; CPU fp32 then tracks float64 to 3e-7): all six losses within the plain
@@ -514,16 +603,24 @@ def test_resnet50_compile_path_matches_cpu(omt, capsys):
     assert sum(v for k, v in kc.items() if k.startswith(("conv_tc_1", "wgrad_tc_1"))) >= 150 * 6, kc  # the convs ran on the tensor cores
     assert abs(l_dev[0] - l_cpu[0]) <= 1e-5 * abs(l_cpu[0])
     names = [n for n, _ in ref.named_parameters()]
+
+    def l2_all(a, b):
+        return (sum(float(((u - v) ** 2).sum()) for u, v in zip(a, b)) / sum(float((v ** 2).sum()) for v in b)) ** 0.5
+
+    assert l2_all(g_dev, g_64) <= max(1e-3, 4 * l2_all(g_cpu, g_64)), (l2_all(g_dev, g_64), l2_all(g_cpu, g_64))
+    assert l2_all(p_dev, p_64) <= max(1e-3, 4 * l2_all(p_cpu, p_64)), (l2_all(p_dev, p_64), l2_all(p_cpu, p_64))
+    cpu_g = max(err(gc, g6) for gc, g6 in zip(g_cpu, g_64))
+    cpu_p = max(err(pc, p6) for pc, p6 in zip(p_cpu, p_64))
     worst_g = worst_p = 0.0
     for n, gd, gc, g6, pd, pc, p6 in zip(names, g_dev, g_cpu, g_64, p_dev, p_cpu, p_64):
         eg, ep = err(gd, g6), err(pd, p6)
-        assert eg <= max(1e-3, 4 * err(gc, g6)), ("gradient", n, eg, err(gc, g6))
-        assert ep <= max(1e-3, 4 * err(pc, p6)), ("parameter after one step", n, ep, err(pc, p6))
+        assert eg <= max(1e-3, 4 * err(gc, g6), 2 * cpu_g), ("gradient", n, eg, err(gc, g6), cpu_g)
+        assert ep <= max(1e-3, 4 * err(pc, p6), 2 * cpu_p), ("parameter after one step", n, ep, err(pc, p6), cpu_p)
         worst_g, worst_p = max(worst_g, eg), max(worst_p, ep)
     d_cpu, d_64, noise = rel(l_cpu, l_dev), rel(l_64, l_dev), rel(l_64, l_cpu)
-    cpu_g = max(err(gc, g6) for gc, g6 in zip(g_cpu, g_64))
     with capsys.disabled():
-        print(f"\nresnet50 compile path, lr 0.1: worst gradient error vs float64 {worst_g:.2e} (the CPU's own: {cpu_g:.2e}), worst parameter error {worst_p:.2e}")
+        print(f"\nresnet50 compile path, lr 0.1: gradients vs float64, all tensors (L2) {l2_all(g_dev, g_64):.2e} (the CPU's own: {l2_all(g_cpu, g_64):.2e}), "
+              f"worst tensor (max norm) {worst_g:.2e} (the CPU's own: {cpu_g:.2e}), worst parameter error {worst_p:.2e}")
         print("  device vs CPU fp32 :", [f"{v:.1e}" for v in d_cpu])
         print("  device vs CPU fp64 :", [f"{v:.1e}" for v in d_64])
         print("  CPU fp32 vs fp64   :", [f"{v:.1e}" for v in noise])
