@@ -294,13 +294,21 @@ class Train:
     # the whole step as one CUDA graph (graph=True; omarchy_mac_torch_b200.graphs.capture). --eager / --compile / --graph /
     # --no-graph override.
 
-    def __init__(self, name, make_model, shape, classes, make_opt, cpu_batch, note, compile=False, graph=False):
-        self.compile, self.graph = compile, graph
+    def __init__(self, name, make_model, shape, classes, make_opt, cpu_batch, note, compile=False, graph=False, regions=False):
+        self.compile, self.graph, self.regions = compile, graph, regions
         self.name, self.make_model, self.in_shape, self.classes, self.make_opt = name, make_model, shape, classes, make_opt
         self.cpu_batch = min(cpu_batch, shape[0])
-        self.shape = {"batch_per_gpu": shape[0], "input": list(shape[1:]), "classes": classes, "optimizer": note,
-                      "api": ('torch.compile(model, backend="omarchy_mac_torch")' if compile else "eager nn.Module")
-                             + (" + omarchy_mac_torch_b200.graphs.capture(step)" if graph else "")}
+        self.shape = {"batch_per_gpu": shape[0], "input": list(shape[1:]), "classes": classes, "optimizer": note, "api": ""}
+        self.set_api()
+
+    def set_api(self):
+        if self.compile and self.regions:
+            api = 'omarchy_mac_torch_b200.compile.compile_regions(model): torch.compile(backend="omarchy_mac_torch") of the stem and of each block'
+        elif self.compile:
+            api = 'torch.compile(model, backend="omarchy_mac_torch")'
+        else:
+            api = "eager nn.Module"
+        self.shape["api"] = api + (" + omarchy_mac_torch_b200.graphs.capture(step)" if self.graph else "")
 
     def host_inputs(self, seed, batch=None):
         g = torch.Generator().manual_seed(1000 + seed)
@@ -322,8 +330,14 @@ class Train:
         self.capi, self.core, self.dev = capi, core, omt.DEVICE
         capi.lib()
         self.model = self.build_model().to(self.dev)
-        # the package's compile backend: BatchNorm+ReLU(+residual add) fused in forward and backward graphs
-        self.fwd = torch.compile(self.model, backend="omarchy_mac_torch") if self.compile else self.model
+        # the package's compile backend: BatchNorm+ReLU(+residual add) fused in forward and backward graphs. A model that names
+        # its regions is compiled region by region, so that each region's gradients reach the data-parallel hooks as soon as
+        # its own backward graph is done (the bucket all-reduces then overlap the rest of the backward pass).
+        if self.compile and self.regions:
+            from omarchy_mac_torch_b200.compile import compile_regions
+            self.fwd = compile_regions(self.model)
+        else:
+            self.fwd = torch.compile(self.model, backend="omarchy_mac_torch") if self.compile else self.model
         self.dp = None
         if world > 1:
             from omarchy_mac_torch_b200.dp import DataParallel
@@ -462,7 +476,7 @@ TRAIN = {
                                  graph=True),
     "resnet50": lambda: Train("resnet50_b256_train", lambda: _models().ResNet50(), (256, 3, 224, 224), 1000,
                               _sgd(0.1, momentum=0.9, nesterov=True, weight_decay=1e-4), 256, "SGD lr .1 momentum .9 nesterov wd 1e-4",
-                              compile=True),
+                              compile=True, regions=True),
 }
 
 WORKLOADS = {**CONV, **TRAIN, "hbm": HbmKernels}
@@ -609,6 +623,7 @@ def main():
     ap.add_argument("--compile", action="store_true", help="training workloads: call the model through the compile backend")
     ap.add_argument("--graph", action="store_true", help="training workloads: replay the whole step as one CUDA graph")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--whole-graph", action="store_true", help="compile the model as one graph instead of region by region")
     ap.add_argument("--profile-step", action="store_true",
                     help="for ncu --profile-from-start off: after the warm-up run ONE step between cudaProfilerStart/Stop and exit")
     args = ap.parse_args()
@@ -616,11 +631,14 @@ def main():
     wl = WORKLOADS[args.workload]()
     if args.workload == "hbm":
         args.no_cpu_baseline = True  # a per-kernel bandwidth table has no single CPU counterpart
-    if (args.eager or args.compile) and isinstance(wl, Train):
-        wl.compile = args.compile and not args.eager
-        wl.shape["api"] = 'torch.compile(model, backend="omarchy_mac_torch")' if wl.compile else "eager nn.Module"
-    if isinstance(wl, Train) and (args.graph or args.no_graph):
-        wl.graph = args.graph and not args.no_graph
+    if isinstance(wl, Train):
+        if args.eager or args.compile:
+            wl.compile = args.compile and not args.eager
+        if args.whole_graph:
+            wl.regions = False
+        if args.graph or args.no_graph:
+            wl.graph = args.graph and not args.no_graph
+        wl.set_api()
     if args.impl == "reference":
         return run_reference(args, wl)
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"

@@ -324,6 +324,28 @@ def _compile(gm, example_inputs):
 
 
 backend = aot_autograd(fw_compiler=_compile, bw_compiler=_compile, inference_compiler=_compile)
+
+
+def compile_regions(model, regions=None):
+    """Compile a model region by region instead of as one graph, in place, and return the model.
+
+    A whole model compiled at once has ONE backward graph, so every parameter's gradient becomes visible to autograd hooks
+    when that graph ends: a data-parallel wrapper that reduces gradient buckets from such hooks (omarchy_mac_torch_b200.dp)
+    could only start its all-reduces after the last backward kernel. Compiled region by region (for a residual network: the
+    stem and each block), the backward graphs run one after the other and each region's gradients arrive as soon as its own
+    graph is done, so the reductions of the last layers' buckets run underneath the backward of the earlier layers.
+    The rewrites of this backend never cross a block boundary, so nothing is lost. `regions` lists (parent module, child
+    name) pairs; by default the model's own `compile_regions()` method supplies them."""
+    if regions is None:
+        regions = model.compile_regions()
+    for parent, name in regions:
+        child = getattr(parent, name) if not name.isdigit() else parent[int(name)]
+        compiled = torch.compile(child, backend=DEVICE)
+        if name.isdigit():
+            parent[int(name)] = compiled
+        else:
+            setattr(parent, name, compiled)
+    return model
 try:
     register_backend(name=DEVICE)(backend)
 except Exception:  # already registered (module re-import)

@@ -199,6 +199,98 @@ __global__ void __launch_bounds__(256) maxpool_bwd_nhwc4_kernel(PoolArgs a, cons
   *reinterpret_cast<float4*>(a.y.p + (((int64_t)img * a.ih + y) * a.iw + xx) * a.c + cq * 4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
 }
 
+// The same for a compile-time window (KS x KS, stride ST, no dilation): ResNet's 3x3 stride-2 stem pool and the like. A
+// thread produces TX consecutive outputs of a row for its 4 channels, so that the (TX-1)*ST + KS input pixels of a window
+// row are loaded once and shared by the windows; window bounds and strides are constants, so the index arithmetic is
+// shifts and the loops unroll. Same update rule as above (first maximum wins, the first NaN wins outright).
+template <int KS, int ST, int TX>
+__global__ void __launch_bounds__(256) maxpool_fwd_nhwc4_fixed_kernel(PoolArgs a, int64_t* __restrict__ idx) {
+  constexpr int SPAN = (TX - 1) * ST + KS;
+  const int c4 = a.c >> 2, gx = (a.ow + TX - 1) / TX;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (int64_t)a.n * a.oh * gx * c4) return;
+  int img, cq, oy, xg;
+  decode4<true>(i, c4, a.oh, gx, img, cq, oy, xg);
+  const int ox0 = xg * TX, y0 = oy * ST - a.p.ph, x0 = ox0 * ST - a.p.pw;
+  const float* xp = a.x.p + ((int64_t)img * a.ih * a.iw) * a.c + cq * 4;
+  float best[TX][4];
+  int bi[TX][4];
+  bool done[TX][4];
+#pragma unroll
+  for (int j = 0; j < TX; j++)
+#pragma unroll
+    for (int k = 0; k < 4; k++) { best[j][k] = -INFINITY; bi[j][k] = -1; done[j][k] = false; }
+#pragma unroll
+  for (int ky = 0; ky < KS; ky++) {
+    const int y = y0 + ky;
+    if (y < 0 || y >= a.ih) continue;
+    float4 in[SPAN];
+#pragma unroll
+    for (int k = 0; k < SPAN; k++) {
+      const int xx = x0 + k;
+      in[k] = (xx >= 0 && xx < a.iw) ? __ldg(reinterpret_cast<const float4*>(xp + ((int64_t)y * a.iw + xx) * a.c)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int j = 0; j < TX; j++)
+#pragma unroll
+      for (int kx = 0; kx < KS; kx++) {
+        const int xx = x0 + j * ST + kx;
+        if (xx < 0 || xx >= a.iw) continue;
+        const float4 v4 = in[j * ST + kx];
+        const float v[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+          const bool nan = isnan_bits(v[k]);
+          if (!done[j][k] && (bi[j][k] < 0 || nan || v[k] > best[j][k])) {
+            best[j][k] = v[k]; bi[j][k] = y * a.iw + xx;
+            done[j][k] = nan;
+          }
+        }
+      }
+  }
+#pragma unroll
+  for (int j = 0; j < TX; j++) {
+    if (ox0 + j >= a.ow) break;
+    const int64_t o = (((int64_t)img * a.oh + oy) * a.ow + ox0 + j) * a.c + cq * 4;
+    *reinterpret_cast<float4*>(a.y.p + o) = make_float4(best[j][0], best[j][1], best[j][2], best[j][3]);
+    longlong2* ip = reinterpret_cast<longlong2*>(idx + o);
+    ip[0] = make_longlong2(bi[j][0], bi[j][1]);
+    ip[1] = make_longlong2(bi[j][2], bi[j][3]);
+  }
+}
+template <int KS, int ST>
+__global__ void __launch_bounds__(256) maxpool_bwd_nhwc4_fixed_kernel(PoolArgs a, const int64_t* __restrict__ idx) {
+  // a.x = gy, a.y = gx; the windows that can hold input (y, xx): output rows ceil((y + p - KS + 1) / ST) .. floor((y + p) / ST)
+  constexpr int NW = (KS + ST - 1) / ST;  // at most this many windows per axis
+  const int c4 = a.c >> 2;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (int64_t)a.n * a.ih * a.iw * c4) return;
+  int img, cq, y, xx;
+  decode4<true>(i, c4, a.ih, a.iw, img, cq, y, xx);
+  const int yhi = (y + a.p.ph) / ST, xhi = (xx + a.p.pw) / ST;
+  const long long me = (long long)y * a.iw + xx;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int dy = 0; dy < NW; dy++) {
+    const int oy = yhi - dy;
+    if (oy < 0 || oy >= a.oh || oy * ST - a.p.ph + KS <= y) continue;
+#pragma unroll
+    for (int dx = 0; dx < NW; dx++) {
+      const int ox = xhi - dx;
+      if (ox < 0 || ox >= a.ow || ox * ST - a.p.pw + KS <= xx) continue;
+      const int64_t o = (((int64_t)img * a.oh + oy) * a.ow + ox) * a.c + cq * 4;
+      const longlong2* ip = reinterpret_cast<const longlong2*>(idx + o);
+      const longlong2 i0 = __ldg(ip), i1 = __ldg(ip + 1);
+      const float4 g = __ldg(reinterpret_cast<const float4*>(a.x.p + o));
+      if (i0.x == me) acc[0] += g.x;
+      if (i0.y == me) acc[1] += g.y;
+      if (i1.x == me) acc[2] += g.z;
+      if (i1.y == me) acc[3] += g.w;
+    }
+  }
+  *reinterpret_cast<float4*>(a.y.p + (((int64_t)img * a.ih + y) * a.iw + xx) * a.c + cq * 4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+}
+
 // ---- general average pool (aten divisor rules) ----
 __device__ __forceinline__ float avg_div(const PoolArgs& a, int oy, int ox) {
   if (a.divisor) return (float)a.divisor;
@@ -356,6 +448,17 @@ int omt_maxpool_fwd(const OmtAct* x, const OmtAct* y, int64_t* idx, int32_t n, i
   OMT_REQUIRE(x && y && x->p && y->p && idx && n > 0 && c > 0 && oh > 0 && ow > 0, "omt_maxpool_fwd: bad arguments");
   if (c % 4 == 0 && is_nhwc(x, c, ih, iw) && is_nhwc(y, c, oh, ow) && aligned16(x->p, y->p, idx)) {
     const int64_t total = (int64_t)n * oh * ow * (c / 4);
+    const bool square = p->kh == p->kw && p->sh == p->sw && p->dh == 1 && p->dw == 1;
+    if (square && p->kh == 3 && p->sh == 2) {
+      maxpool_fwd_nhwc4_fixed_kernel<3, 2, 4><<<(unsigned)cdiv((int64_t)n * oh * cdiv(ow, 4) * (c / 4), 256), 256, 0, st(stream)>>>(
+          pa(x, y, n, c, ih, iw, oh, ow, p, 0, 0), idx);
+      return check_launch("maxpool_fwd_nhwc4_k3s2");
+    }
+    if (square && p->kh == 2 && p->sh == 2) {
+      maxpool_fwd_nhwc4_fixed_kernel<2, 2, 4><<<(unsigned)cdiv((int64_t)n * oh * cdiv(ow, 4) * (c / 4), 256), 256, 0, st(stream)>>>(
+          pa(x, y, n, c, ih, iw, oh, ow, p, 0, 0), idx);
+      return check_launch("maxpool_fwd_nhwc4_k2s2");
+    }
     maxpool_fwd_nhwc4_kernel<<<(unsigned)cdiv(total, 256), 256, 0, st(stream)>>>(pa(x, y, n, c, ih, iw, oh, ow, p, 0, 0), idx);
     return check_launch("maxpool_fwd_nhwc4");
   }
@@ -369,6 +472,15 @@ int omt_maxpool_bwd(const OmtAct* gy, const int64_t* idx, const OmtAct* gx, int3
   OMT_REQUIRE(gy && gx && gy->p && gx->p && idx && n > 0 && c > 0 && oh > 0 && ow > 0, "omt_maxpool_bwd: bad arguments");
   if (c % 4 == 0 && is_nhwc(gy, c, oh, ow) && is_nhwc(gx, c, ih, iw) && aligned16(gy->p, gx->p, idx)) {
     const int64_t total = (int64_t)n * ih * iw * (c / 4);
+    const bool square = p->kh == p->kw && p->sh == p->sw && p->dh == 1 && p->dw == 1;
+    if (square && p->kh == 3 && p->sh == 2) {
+      maxpool_bwd_nhwc4_fixed_kernel<3, 2><<<(unsigned)cdiv(total, 256), 256, 0, st(stream)>>>(pa(gy, gx, n, c, ih, iw, oh, ow, p, 0, 0), idx);
+      return check_launch("maxpool_bwd_nhwc4_k3s2");
+    }
+    if (square && p->kh == 2 && p->sh == 2) {
+      maxpool_bwd_nhwc4_fixed_kernel<2, 2><<<(unsigned)cdiv(total, 256), 256, 0, st(stream)>>>(pa(gy, gx, n, c, ih, iw, oh, ow, p, 0, 0), idx);
+      return check_launch("maxpool_bwd_nhwc4_k2s2");
+    }
     maxpool_bwd_nhwc4_kernel<<<(unsigned)cdiv(total, 256), 256, 0, st(stream)>>>(pa(gy, gx, n, c, ih, iw, oh, ow, p, 0, 0), idx);
     return check_launch("maxpool_bwd_nhwc4");
   }

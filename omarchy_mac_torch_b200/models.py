@@ -140,6 +140,10 @@ class ResNet50(nn.Module):
     def forward(self, x):
         return self.head(torch.flatten(nn.functional.adaptive_avg_pool2d(self.layers(self.stem(x)), 1), 1))
 
+    def compile_regions(self):
+        """(parent, child name) of the parts to compile separately (compile.compile_regions): the stem and every block."""
+        return [(self, "stem")] + [(self.layers, str(i)) for i in range(len(self.layers))]
+
 
 class _InvRes(nn.Module):
     def __init__(self, ci, co, expand, stride, k=3):

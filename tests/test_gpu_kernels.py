@@ -357,7 +357,7 @@ def test_conv_epilogue_statistics_survive_a_large_mean(capi):
     """Outputs whose mean is 1000 standard deviations away from zero (a large bias on tiny activations): the grouped, exactly
     merged moments keep the variance, where sums of y and y^2 in float32 would lose it entirely."""
     torch.manual_seed(4)
-    x, w = torch.randn(8, 32, 28, 28), torch.randn(64, 32, 3, 3) * 0.006
+    x, w = torch.randn(16, 32, 28, 28), torch.randn(64, 32, 3, 3) * 0.006
     b = torch.full((64,), 100.0)
     y, part, groups = capi.conv_fwd_bnstats(dev(x, True), dev(w), dev(b), 1, 1)
     assert groups > 0

@@ -131,3 +131,29 @@ def test_model_definitions_reproduce_reference_curves(pkg, golden_losses):
             loss = F.cross_entropy(m(x), y); opt.zero_grad(); loss.backward(); opt.step(); out.append(loss.item())
         assert max(abs(a - b) / abs(b) for a, b in zip(out, g["losses"][:3])) < 1e-5
     assert sum(p.numel() for p in models.ResNet50().parameters()) == 25557032
+
+
+def test_compile_regions_matches_eager_and_delivers_gradients_region_by_region(pkg):
+    """compile.compile_regions: the stem and every block become separate compiled graphs; results equal the eager model's,
+    and parameter gradients arrive region by region during backward (last block first), which is what lets a data-parallel
+    wrapper start reducing the last layers' buckets while the earlier layers' backward still runs."""
+    from omarchy_mac_torch_b200 import compile as C, models
+    torch.manual_seed(0)
+    ref = models.ResNet50(num_classes=10, layers=(1, 1, 1, 1))
+    mod = copy.deepcopy(ref)
+    assert [n for _, n in mod.compile_regions()] == ["stem", "0", "1", "2", "3"]
+    C.compile_regions(mod)
+    order = []
+    for name, p in mod.named_parameters():
+        p.register_post_accumulate_grad_hook(lambda _p, name=name: order.append(name))
+    x, y = torch.randn(2, 3, 32, 32), torch.randint(0, 10, (2,))
+    F.cross_entropy(ref(x), y).backward()
+    F.cross_entropy(mod(x), y).backward()
+    for (n, a), b in zip(ref.named_parameters(), mod.parameters()):
+        assert torch.allclose(a.grad, b.grad, rtol=1e-4, atol=1e-6), n
+    region = lambda n: n.split(".")[1] if n.startswith("layers.") else n.split(".")[0]
+    seen = []
+    for n in order:
+        if not seen or seen[-1] != region(n):
+            seen.append(region(n))
+    assert seen == ["head", "3", "2", "1", "0", "stem"], seen  # each region's gradients arrive together, in backward order
