@@ -332,19 +332,39 @@ def compile_regions(model, regions=None):
     A whole model compiled at once has ONE backward graph, so every parameter's gradient becomes visible to autograd hooks
     when that graph ends: a data-parallel wrapper that reduces gradient buckets from such hooks (omarchy_mac_torch_b200.dp)
     could only start its all-reduces after the last backward kernel. Compiled region by region (for a residual network: the
-    stem and each block), the backward graphs run one after the other and each region's gradients arrive as soon as its own
-    graph is done, so the reductions of the last layers' buckets run underneath the backward of the earlier layers.
-    The rewrites of this backend never cross a block boundary, so nothing is lost. `regions` lists (parent module, child
-    name) pairs; by default the model's own `compile_regions()` method supplies them."""
+    stem and a few groups of blocks), the backward graphs run one after the other and each region's gradients arrive as soon
+    as its own graph is done, so the reductions of the last layers' buckets run underneath the backward of the earlier
+    layers. The rewrites of this backend never cross a block boundary, so nothing is lost; every region costs a fraction of a
+    millisecond of host time per step, which is why the regions are a handful and not every block.
+
+    `regions` lists (parent module, child name) pairs and (nn.Sequential, (start, stop)) pairs, the latter covering the
+    Sequential completely and in order; by default the model's own `compile_regions()` method supplies them. Parameter
+    names do not change."""
     if regions is None:
         regions = model.compile_regions()
-    for parent, name in regions:
-        child = getattr(parent, name) if not name.isdigit() else parent[int(name)]
-        compiled = torch.compile(child, backend=DEVICE)
-        if name.isdigit():
-            parent[int(name)] = compiled
+    groups = {}
+    for parent, what in regions:
+        if isinstance(what, str):
+            child = getattr(parent, what)
+            if isinstance(child, torch.nn.Sequential):  # as one slice over the whole of it (below)
+                groups.setdefault(id(child), (child, []))[1].append((0, len(child), torch.compile(torch.nn.Sequential(*list(child)), backend=DEVICE)))
+            else:  # the module stays where it is, under its name; its forward runs compiled
+                fn = torch.compile(type(child).forward, backend=DEVICE)
+                child.forward = (lambda *a, _m=child, _f=fn, **k: _f(_m, *a, **k))
         else:
-            setattr(parent, name, compiled)
+            start, stop = what
+            groups.setdefault(id(parent), (parent, []))[1].append((start, stop, torch.compile(torch.nn.Sequential(*list(parent)[start:stop]), backend=DEVICE)))
+    for parent, parts in groups.values():
+        parts.sort(key=lambda p: p[0])
+        assert parts[0][0] == 0 and parts[-1][1] == len(parent) and all(a[1] == b[0] for a, b in zip(parts, parts[1:])), \
+            "the slices must cover the Sequential completely and in order"
+        chain = [p[2] for p in parts]
+
+        def forward(x, chain=chain):
+            for part in chain:
+                x = part(x)
+            return x
+        parent.forward = forward  # the children stay registered under their own names; only the call path changes
     return model
 try:
     register_backend(name=DEVICE)(backend)

@@ -282,6 +282,67 @@ __global__ void __launch_bounds__(256) bn_ew_vec4(BnEw a) {
   }
 }
 
+// Channels-last with c % 32 == 0 and a pixel count divisible by 4: a thread takes its 4 channels of FOUR consecutive pixels,
+// so the per-channel parameters (four to six 128-bit loads) are fetched once per 64 bytes of activation instead of once
+// per 16, and four independent activation loads are in flight per thread. Same arithmetic as bn_ew_vec4.
+template <int KIND, bool RELU>
+__global__ void __launch_bounds__(256) bn_ew_nhwc_px4(BnEw a) {
+  const int c4 = a.c >> 2;
+  const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;  // t = pixel group * c4 + channel quad
+  const int64_t pg = t < 0x7fffffffll ? (int64_t)((uint32_t)t / (uint32_t)c4) : t / c4;
+  const int ch = (int)(t - pg * c4) * 4;
+  const int64_t i0 = pg * 4 * a.c + ch;
+  if (i0 >= a.total) return;  // (c4 % 8 == 0: the 8 lanes that share a mask word leave together)
+  const float4 mean = __ldg(reinterpret_cast<const float4*>(a.mean + ch));
+  float4 inv = __ldg(reinterpret_cast<const float4*>(a.inv + ch));
+  const float4 ga = __ldg(reinterpret_cast<const float4*>(a.gamma + ch));
+  float4 be = ga, dg = ga, db = ga;
+  if (KIND <= 1) be = __ldg(reinterpret_cast<const float4*>(a.beta + ch));
+  if (KIND == 1) { inv.x = rsqrtf(inv.x + a.eps); inv.y = rsqrtf(inv.y + a.eps); inv.z = rsqrtf(inv.z + a.eps); inv.w = rsqrtf(inv.w + a.eps); }
+  if (KIND == 2) { dg = __ldg(reinterpret_cast<const float4*>(a.dgb + ch)); db = __ldg(reinterpret_cast<const float4*>(a.dgb + a.c + ch)); }
+  float4 xv[4], gv[4];
+  uint32_t mk[4] = {0xFu, 0xFu, 0xFu, 0xFu};
+#pragma unroll
+  for (int k = 0; k < 4; k++) {
+    const int64_t i = i0 + (int64_t)k * a.c;
+    xv[k] = __ldg(reinterpret_cast<const float4*>(a.x + i));
+    gv[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (KIND == 2) {
+      gv[k] = __ldg(reinterpret_cast<const float4*>(a.g + i));
+      if (RELU) {
+        if (a.bits_in) {
+          mk[k] = mask_nibble(a.bits_in, i);
+        } else {
+          const float4 yv = __ldg(reinterpret_cast<const float4*>(a.y + i));
+          mk[k] = (yv.x > 0.f ? 1u : 0u) | (yv.y > 0.f ? 2u : 0u) | (yv.z > 0.f ? 4u : 0u) | (yv.w > 0.f ? 8u : 0u);
+        }
+      }
+    } else if (a.res) {
+      gv[k] = __ldg(reinterpret_cast<const float4*>(a.res + i));
+    }
+  }
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int k = 0; k < 4; k++) {
+    const int64_t i = i0 + (int64_t)k * a.c;
+    float4 g = gv[k], o;
+    if (KIND == 2 && RELU) {
+      g.x = (mk[k] & 1u) ? g.x : 0.f; g.y = (mk[k] & 2u) ? g.y : 0.f; g.z = (mk[k] & 4u) ? g.z : 0.f; g.w = (mk[k] & 8u) ? g.w : 0.f;
+      if (a.gz) *reinterpret_cast<float4*>(a.gz + i) = g;
+    }
+    o.x = bn_ew_one<KIND, RELU>(a, xv[k].x, g.x, mean.x, inv.x, ga.x, be.x, dg.x, db.x);
+    o.y = bn_ew_one<KIND, RELU>(a, xv[k].y, g.y, mean.y, inv.y, ga.y, be.y, dg.y, db.y);
+    o.z = bn_ew_one<KIND, RELU>(a, xv[k].z, g.z, mean.z, inv.z, ga.z, be.z, dg.z, db.z);
+    o.w = bn_ew_one<KIND, RELU>(a, xv[k].w, g.w, mean.w, inv.w, ga.w, be.w, dg.w, db.w);
+    *reinterpret_cast<float4*>(a.out + i) = o;
+    if (KIND == 0 && RELU && a.bits_out) {  // 8 lanes x 4 elements make one word; lane 0 of each group of 8 stores it
+      uint32_t v = ((o.x > 0.f ? 1u : 0u) | (o.y > 0.f ? 2u : 0u) | (o.z > 0.f ? 4u : 0u) | (o.w > 0.f ? 8u : 0u)) << (4 * (lane & 7));
+      v |= __shfl_xor_sync(0xffffffffu, v, 1); v |= __shfl_xor_sync(0xffffffffu, v, 2); v |= __shfl_xor_sync(0xffffffffu, v, 4);
+      if ((lane & 7) == 0) a.bits_out[i >> 5] = v;
+    }
+  }
+}
+
 template <int KIND, bool RELU>
 __global__ void __launch_bounds__(256) bn_ew_scalar(BnEw a, bool nhwc) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -311,7 +372,11 @@ static int launch_ew(const BnEw& a, bool relu, bool nhwc, cudaStream_t s, const 
   if (nhwc)  // per-channel tables are read as float4 too
     vec = vec && ((reinterpret_cast<uintptr_t>(a.mean) | reinterpret_cast<uintptr_t>(a.inv) | reinterpret_cast<uintptr_t>(a.gamma) |
                    reinterpret_cast<uintptr_t>(a.beta) | reinterpret_cast<uintptr_t>(a.dgb)) & 15) == 0;
-  if (vec) {
+  if (vec && nhwc && a.c % 32 == 0 && (a.total / a.c) % 4 == 0) {
+    const unsigned blocks = (unsigned)cdiv(a.total / 16, 256);
+    if (relu) bn_ew_nhwc_px4<KIND, true><<<blocks, 256, 0, s>>>(a);
+    else bn_ew_nhwc_px4<KIND, false><<<blocks, 256, 0, s>>>(a);
+  } else if (vec) {
     unsigned blocks = (unsigned)cdiv(a.total / 4, 256);
     if (nhwc) {
       if (relu) bn_ew_vec4<KIND, true, true><<<blocks, 256, 0, s>>>(a);

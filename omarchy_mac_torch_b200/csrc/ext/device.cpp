@@ -360,6 +360,12 @@ struct Guard final : c10::impl::DeviceGuardImplInterface {
 };
 C10_REGISTER_GUARD_IMPL(PrivateUse1, Guard);
 
+// Tensor.record_stream(stream): the allocator must not hand the block out again before that stream's pending work is done
+static void record_stream_impl(Tensor& self, c10::Stream s) {
+  if (!self.defined() || !self.has_storage() || !self.storage().data()) return;
+  check(omt_record_stream(self.storage().mutable_data(), Guard::handle(s)), "record_stream");
+}
+
 // ------------------------------------------------------------------------------------------------
 // hooks and generator (random fills are drawn on the host with this device's own generator, then uploaded)
 // ------------------------------------------------------------------------------------------------
@@ -544,6 +550,7 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
   m.impl("view_as_real", &at::native::view_as_real);
   m.impl("view_as_complex", &at::native::view_as_complex);
   m.impl("set_.source_Storage", &at::native::set_);
+  m.impl("record_stream", &record_stream_impl);
 }
 
 }  // namespace omt

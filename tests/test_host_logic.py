@@ -141,7 +141,8 @@ def test_compile_regions_matches_eager_and_delivers_gradients_region_by_region(p
     torch.manual_seed(0)
     ref = models.ResNet50(num_classes=10, layers=(1, 1, 1, 1))
     mod = copy.deepcopy(ref)
-    assert [n for _, n in mod.compile_regions()] == ["stem", "0", "1", "2", "3"]
+    assert [n for _, n in mod.compile_regions()] == ["stem", (0, 2), (2, 3), (3, 4)]
+    assert [n for _, n in models.ResNet50().compile_regions()] == ["stem", (0, 6), (6, 11), (11, 16)]
     C.compile_regions(mod)
     order = []
     for name, p in mod.named_parameters():
@@ -151,9 +152,10 @@ def test_compile_regions_matches_eager_and_delivers_gradients_region_by_region(p
     F.cross_entropy(mod(x), y).backward()
     for (n, a), b in zip(ref.named_parameters(), mod.parameters()):
         assert torch.allclose(a.grad, b.grad, rtol=1e-4, atol=1e-6), n
-    region = lambda n: n.split(".")[1] if n.startswith("layers.") else n.split(".")[0]
+    region = lambda n: {"0": "a", "1": "a", "2": "b", "3": "c"}[n.split(".")[1]] if n.startswith("layers.") else n.split(".")[0]
     seen = []
     for n in order:
         if not seen or seen[-1] != region(n):
             seen.append(region(n))
-    assert seen == ["head", "3", "2", "1", "0", "stem"], seen  # each region's gradients arrive together, in backward order
+    assert seen == ["head", "c", "b", "a", "stem"], seen  # each region's gradients arrive together, in backward order
+    assert [n for n, _ in mod.named_parameters()] == [n for n, _ in ref.named_parameters()]
