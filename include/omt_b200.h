@@ -320,6 +320,37 @@ int omt_sgd(const OmtParam* table, int32_t count, float lr, float momentum, floa
 int omt_adam(const OmtParam* table, int32_t count, float lr, float beta1, float beta2, float eps,
              float weight_decay, int32_t decoupled, int32_t maximize, omt_stream_t stream);
 
+/* ---- fused pointwise chains: reference omt::fused_pointwise (csrc/fused.cpp:139-170) + compile pass 4 ---------------- */
+
+/* A chain of elementwise ops as a straight-line program. The reference generates shader source per chain
+ * (omarchy_mac_torch/compile.py:256-336); here the chain is data for one ahead-of-time kernel. Instruction j computes value
+ * slot OMT_PW_MAX_INPUTS + j from up to three operands; an operand >= 0 names a value slot (0..n_inputs-1: the inputs;
+ * OMT_PW_MAX_INPUTS + i: the result of an earlier instruction i), an operand < 0 names literal[-1 - operand]. The last
+ * instruction's value is the output. Op semantics follow the aten ops of the reference's table (compile.py:176-222):
+ * ADD/SUB/RSUB take alpha as third operand; THRESHOLD_BWD is (grad, self, threshold); the *_BWD ops are (grad, x or y). */
+enum {
+  OMT_PW_ADD, OMT_PW_SUB, OMT_PW_RSUB, OMT_PW_MUL, OMT_PW_DIV, OMT_PW_NEG, OMT_PW_RELU, OMT_PW_EXP, OMT_PW_LOG, OMT_PW_SQRT,
+  OMT_PW_RSQRT, OMT_PW_RECIP, OMT_PW_ABS, OMT_PW_TANH, OMT_PW_SIGMOID, OMT_PW_SILU, OMT_PW_MAX, OMT_PW_MIN, OMT_PW_POW,
+  OMT_PW_THRESHOLD_BWD, OMT_PW_SIGMOID_BWD, OMT_PW_TANH_BWD, OMT_PW_SILU_BWD, OMT_PW_GELU, OMT_PW_GELU_TANH, OMT_PW_GELU_BWD,
+  OMT_PW_GELU_TANH_BWD, OMT_PW_CLAMP, OMT_PW_HARDSWISH, OMT_PW_HARDSWISH_BWD, OMT_PW_HARDSIGMOID, OMT_PW_HARDSIGMOID_BWD,
+  OMT_PW_OP_COUNT
+};
+#define OMT_PW_MAX_INPUTS 6
+#define OMT_PW_MAX_INSTR 24
+#define OMT_PW_MAX_LITERALS 24
+typedef struct OmtPwInstr {
+  int32_t op, a, b, c;
+} OmtPwInstr;
+typedef struct OmtPwProgram {
+  int32_t n_instr;
+  OmtPwInstr instr[OMT_PW_MAX_INSTR];
+  float literal[OMT_PW_MAX_LITERALS];
+} OmtPwProgram;
+/* out = program(inputs) elementwise over `shape` (rank <= 8). in_strides holds 8 element strides per input (0 in a
+ * dimension the input broadcasts along), out_strides the output's. One launch. */
+int omt_pointwise(const OmtPwProgram* prog, int32_t n_inputs, const float* const* inputs, const int64_t* in_strides,
+                  const int64_t* out_strides, const int32_t* shape, int32_t rank, float* out, omt_stream_t stream);
+
 /* ---- small helpers used by plans and data parallel ---------------------------------------------------------------- */
 
 /* dst = src * scale over n floats (bucket averaging after all-reduce; icopy.wgsl when scale == 1). */

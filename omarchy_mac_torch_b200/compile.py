@@ -12,10 +12,15 @@ those graphs to the fused `omt::` ops, and the graph runs op by op on the device
   +  add(convolution_backward(...)[0], g) with g a gradient nobody else reads -> omt.conv_backward_acc (the input
      gradient is accumulated into g by the conv epilogue: the joins of residual branches in the backward graph)
 
-These are passes 1-3 of the reference's omarchy_mac_torch/compile.py:69-161. Its pass 4 (pointwise chains compiled to
-generated shader source) is not part of this build. Every fused op has a composite definition in plain aten ops, so a
-rewritten graph is always correct, on any device. OMARCHY_MAC_TORCH_COMPILE_DEBUG=1 prints what each pass did."""
+  4. chains of elementwise ops (add/mul/relu/sigmoid/hardswish/..., their backward forms, scalars folded in) that only
+     feed one another                                   -> omt.fused_pointwise (one kernel, one pass over memory)
 
+These are passes 1-4 of the reference's omarchy_mac_torch/compile.py:69-161, 256-336. Its pass 4 generates shader source
+for every chain; here the chain is encoded as a small program string that one ahead-of-time interpreter kernel runs
+(csrc/pointwise.cu). Every fused op has a composite definition in plain aten ops, so a rewritten graph is always
+correct, on any device. OMARCHY_MAC_TORCH_COMPILE_DEBUG=1 prints what each pass did."""
+
+import math
 import operator
 import os
 
@@ -303,12 +308,143 @@ def fuse_conv_bn_train(graph):
     return done
 
 
+# ---- pass 4: pointwise chains ----------------------------------------------------------------------------------------------
+# aten op -> (mnemonic of csrc/ext/fused.cpp's program text, operand builder). The builder gets the call's positional
+# operands (already turned into operand tokens) and kwargs and returns the three operand tokens of the instruction;
+# `lit(x)` interns a number. Same op coverage as the reference's table (compile.py:176-222) plus the hard-swish family.
+def _pw_table():
+    def binary_alpha(a, kw, lit):
+        return a[0], a[1], lit(kw.get("alpha", 1))
+
+    def binary(a, kw, lit):
+        return a[0], a[1], a[0]
+
+    def unary(a, kw, lit):
+        return a[0], a[0], a[0]
+
+    def clamp(a, kw, lit):
+        lo = a[1] if len(a) > 1 and a[1] is not None else lit(-math.inf)
+        hi = a[2] if len(a) > 2 and a[2] is not None else lit(math.inf)
+        return a[0], lo, hi
+
+    def gelu(name):
+        return lambda kw: name + ("_tanh" if kw.get("approximate", "none") == "tanh" else "")
+
+    t = {
+        aten.add.Tensor: ("add", binary_alpha), aten.sub.Tensor: ("sub", binary_alpha), aten.add.Scalar: ("add", binary_alpha),
+        aten.sub.Scalar: ("sub", binary_alpha), aten.rsub.Scalar: ("rsub", binary_alpha),
+        aten.mul.Tensor: ("mul", binary), aten.div.Tensor: ("div", binary), aten.mul.Scalar: ("mul", binary), aten.div.Scalar: ("div", binary),
+        aten.maximum.default: ("max", binary), aten.minimum.default: ("min", binary), aten.pow.Tensor_Scalar: ("pow", binary),
+        aten.sigmoid_backward.default: ("sigmoid_bwd", binary), aten.tanh_backward.default: ("tanh_bwd", binary),
+        aten.silu_backward.default: ("silu_bwd", binary), aten.hardswish_backward.default: ("hardswish_bwd", binary),
+        aten.hardsigmoid_backward.default: ("hardsigmoid_bwd", binary),
+        aten.threshold_backward.default: ("threshold_bwd", lambda a, kw, lit: (a[0], a[1], a[2])),
+        aten.clamp.default: ("clamp", clamp),
+        aten.gelu.default: (gelu("gelu"), unary), aten.gelu_backward.default: (lambda kw: gelu("gelu")(kw) + "_bwd", binary),
+    }
+    for op, name in ((aten.neg, "neg"), (aten.relu, "relu"), (aten.exp, "exp"), (aten.log, "log"), (aten.sqrt, "sqrt"), (aten.rsqrt, "rsqrt"),
+                     (aten.reciprocal, "recip"), (aten.abs, "abs"), (aten.tanh, "tanh"), (aten.sigmoid, "sigmoid"), (aten.silu, "silu"),
+                     (aten.hardswish, "hardswish"), (aten.hardsigmoid, "hardsigmoid")):
+        t[op.default] = (name, unary)
+    return t
+
+
+_PW = _pw_table()
+_PW_KWARGS = {aten.gelu.default: {"approximate"}, aten.gelu_backward.default: {"approximate"}}
+_PW_MAX_INPUTS, _PW_MAX_INSTR, _PW_MAX_LITERALS = 6, 24, 24  # limits of the interpreter kernel (include/omt_b200.h)
+_PW_SCALAR_ONLY = {aten.pow.Tensor_Scalar: (1,), aten.threshold_backward.default: (2,), aten.clamp.default: (1, 2)}  # operands that must be numbers
+
+
+def _f32_dev(n):
+    v = _meta(n)
+    return isinstance(v, torch.Tensor) and v.dtype == torch.float32 and (_ANY_DEVICE or v.device.type == DEVICE)
+
+
+def _pointwise_ok(n):
+    if n.op != "call_function" or n.target not in _PW or not _f32_dev(n) or _meta(n).dim() > 8 or _meta(n).numel() == 0:
+        return False
+    for k, a in enumerate(n.args):
+        if isinstance(a, Node):
+            if not _f32_dev(a) or k in _PW_SCALAR_ONLY.get(n.target, ()):
+                return False
+        elif isinstance(a, bool) or not (isinstance(a, (int, float)) or a is None):
+            return False
+        elif a is None and n.target is not aten.clamp.default:
+            return False
+    return set(n.kwargs) <= (_PW_KWARGS.get(n.target, set()) | {"alpha"}) and not isinstance(n.kwargs.get("alpha", 1), Node)
+
+
+def fuse_pointwise(graph):
+    """Greedy chains: a node joins the group of a producer whose only user it is and whose shape it has (so nothing but the
+    chain's last value leaves it), as long as the group stays within the kernel's limits."""
+    group_of, groups = {}, []
+    for n in graph.nodes:
+        if not _pointwise_ok(n):
+            continue
+        shape = tuple(_meta(n).shape)
+        target = None
+        for a in n.args:
+            if isinstance(a, Node) and a in group_of and len(a.users) == 1 and tuple(_meta(a).shape) == shape:
+                target = group_of[a]
+                break
+        if target is not None:
+            g = groups[target]
+            external = {a for m in g + [n] for a in m.args if isinstance(a, Node) and a not in g and a is not n}
+            if len(external) > _PW_MAX_INPUTS or len(g) + 1 > _PW_MAX_INSTR:
+                target = None
+        if target is None:
+            groups.append([n])
+            group_of[n] = len(groups) - 1
+        else:
+            groups[target].append(n)
+            group_of[n] = target
+    done = 0
+    for g in groups:
+        if len(g) < 2:
+            continue
+        members, inputs, literals, instrs = set(g), [], [], []
+
+        def lit(v):
+            v = float(v)
+            text = "nan" if math.isnan(v) else ("inf" if v == math.inf else ("-inf" if v == -math.inf else v.hex()))
+            if text not in literals:
+                literals.append(text)
+            return f"#{literals.index(text)}"
+
+        for m in g:
+            for a in m.args:
+                if isinstance(a, Node) and a not in members and a not in inputs:
+                    inputs.append(a)
+        token = {a: f"v{i}" for i, a in enumerate(inputs)}
+        for j, m in enumerate(g):
+            name, build = _PW[m.target]
+            if callable(name):
+                name = name(m.kwargs)
+            ops = [token[a] if isinstance(a, Node) else (None if a is None else lit(a)) for a in m.args]
+            a, b, c = build(ops, m.kwargs, lit)
+            instrs.append(f"{name},{a},{b},{c}")
+            token[m] = f"t{j}"
+        if len(literals) > _PW_MAX_LITERALS or not inputs:
+            continue
+        program = f"pw1|{len(inputs)}|{';'.join(instrs)}|{','.join(literals)}"
+        last = g[-1]
+        with graph.inserting_before(last):
+            fused = graph.call_function(omt.fused_pointwise.default, (program, list(inputs)))
+        fused.meta = dict(last.meta)
+        last.replace_all_uses_with(fused)
+        for m in reversed(g):
+            graph.erase_node(m)
+        done += 1
+    return done
+
+
 def rewrite(gm):
-    """Apply the three passes to a GraphModule in place; returns {pass: rewrites}."""
+    """Apply the passes to a GraphModule in place; returns {pass: rewrites}."""
     g = gm.graph
     stats = {"bn_relu": fuse_bn_relu(g), "bn_add_relu": fuse_bn_add_relu(g), "bn_relu_backward": fuse_bn_relu_backward(g),
              "bn_add_relu_backward": fuse_bn_add_relu_backward(g), "conv_epilogue": fuse_conv_epilogues(g),
              "conv_bn_train": fuse_conv_bn_train(g), "dgrad_accumulate": fuse_dgrad_accumulate(g)}
+    stats["pointwise"] = fuse_pointwise(g)
     g.eliminate_dead_code()
     g.lint()
     gm.recompile()

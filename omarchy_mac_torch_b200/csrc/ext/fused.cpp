@@ -10,7 +10,9 @@
 //                           batch statistics while it stores its output, so the BatchNorm reads that output once, not twice
 //   omt::conv_act           conv2d + bias + optional ReLU in the GEMM epilogue
 //   omt::conv_bn_act_eval   eval conv2d + BatchNorm (folded into the conv's weights and bias) + optional ReLU
-//   omt::fused_pointwise    declared for schema parity; generated pointwise kernels are not built in this library
+//   omt::fused_pointwise    a chain of elementwise ops in one kernel (compile pass 4). The reference passes the name of a
+//                           shader it generated for the chain; here the `kernel` string is the chain itself, a small
+//                           straight-line program that one ahead-of-time interpreter kernel runs (omt_pointwise)
 #include "omt.h"
 
 namespace omt {
@@ -67,8 +69,119 @@ static Tensor conv_bn_act_eval_ref(const Tensor& x, const Tensor& cw, const std:
   auto f = fold_bn(cw, cb, w, b, rm, rv, eps);
   return conv_act_ref(x, f.first, f.second, stride, padding, act_);
 }
-static Tensor fused_pointwise_ref(c10::string_view, at::TensorList) {
-  TORCH_CHECK(false, "omt::fused_pointwise: generated pointwise kernels are not built in this library");
+// ---- pointwise programs ------------------------------------------------------------------------------------------------
+// Text form, written by compile.py's pass 4:  "pw1|<n inputs>|<op>,<a>,<b>,<c>;...|<literal>,<literal>,..."  with operands
+// vK (input K), tJ (result of instruction J) and #L (literal L; numbers in C hex-float notation, or inf / -inf / nan).
+static const char* const kPwNames[OMT_PW_OP_COUNT] = {
+    "add", "sub", "rsub", "mul", "div", "neg", "relu", "exp", "log", "sqrt", "rsqrt", "recip", "abs", "tanh", "sigmoid", "silu", "max", "min", "pow",
+    "threshold_bwd", "sigmoid_bwd", "tanh_bwd", "silu_bwd", "gelu", "gelu_tanh", "gelu_bwd", "gelu_tanh_bwd", "clamp", "hardswish", "hardswish_bwd",
+    "hardsigmoid", "hardsigmoid_bwd"};
+struct PwParsed {
+  OmtPwProgram prog{};
+  int n_inputs = 0, n_literals = 0;
+};
+static std::vector<std::string> split(const std::string& s, char sep) {
+  std::vector<std::string> out;
+  size_t pos = 0;
+  while (true) {
+    size_t e = s.find(sep, pos);
+    out.push_back(s.substr(pos, e == std::string::npos ? std::string::npos : e - pos));
+    if (e == std::string::npos) break;
+    pos = e + 1;
+  }
+  return out;
+}
+static const PwParsed& parse_program(const std::string& text) {
+  static std::mutex mu;
+  static std::map<std::string, PwParsed> cache;
+  std::lock_guard<std::mutex> l(mu);
+  auto it = cache.find(text);
+  if (it != cache.end()) return it->second;
+  PwParsed p;
+  auto parts = split(text, '|');
+  TORCH_CHECK(parts.size() == 4 && parts[0] == "pw1", "omt::fused_pointwise: not a pointwise program: ", text);
+  p.n_inputs = std::stoi(parts[1]);
+  TORCH_CHECK(p.n_inputs >= 1 && p.n_inputs <= OMT_PW_MAX_INPUTS, "omt::fused_pointwise: 1 to ", OMT_PW_MAX_INPUTS, " inputs");
+  if (!parts[3].empty())
+    for (auto& lit : split(parts[3], ',')) {
+      TORCH_CHECK(p.n_literals < OMT_PW_MAX_LITERALS, "omt::fused_pointwise: too many literals");
+      p.prog.literal[p.n_literals++] = std::strtof(lit.c_str(), nullptr);
+    }
+  for (auto& ins : split(parts[2], ';')) {
+    auto f = split(ins, ',');
+    TORCH_CHECK(f.size() == 4 && p.prog.n_instr < OMT_PW_MAX_INSTR, "omt::fused_pointwise: malformed or too long program: ", text);
+    OmtPwInstr& o = p.prog.instr[p.prog.n_instr];
+    o.op = -1;
+    for (int k = 0; k < OMT_PW_OP_COUNT; k++)
+      if (f[0] == kPwNames[k]) o.op = k;
+    TORCH_CHECK(o.op >= 0, "omt::fused_pointwise: unknown op '", f[0], "'");
+    int32_t* dst[3] = {&o.a, &o.b, &o.c};
+    for (int q = 0; q < 3; q++) {
+      const std::string& t = f[q + 1];
+      TORCH_CHECK(t.size() >= 2, "omt::fused_pointwise: malformed operand '", t, "'");
+      const int v = std::stoi(t.substr(1));
+      if (t[0] == 'v') { TORCH_CHECK(v >= 0 && v < p.n_inputs, "omt::fused_pointwise: input out of range"); *dst[q] = v; }
+      else if (t[0] == 't') { TORCH_CHECK(v >= 0 && v < p.prog.n_instr, "omt::fused_pointwise: use before definition"); *dst[q] = OMT_PW_MAX_INPUTS + v; }
+      else if (t[0] == '#') { TORCH_CHECK(v >= 0 && v < p.n_literals, "omt::fused_pointwise: literal out of range"); *dst[q] = -1 - v; }
+      else TORCH_CHECK(false, "omt::fused_pointwise: malformed operand '", t, "'");
+    }
+    p.prog.n_instr++;
+  }
+  TORCH_CHECK(p.prog.n_instr >= 1, "omt::fused_pointwise: empty program");
+  return cache.emplace(text, p).first->second;
+}
+
+// composite definition: the program evaluated op by op with aten (any device)
+static Tensor fused_pointwise_ref(c10::string_view kernel, at::TensorList ins) {
+  const PwParsed& p = parse_program(std::string(kernel));
+  TORCH_CHECK((int)ins.size() == p.n_inputs, "omt::fused_pointwise: the program takes ", p.n_inputs, " inputs, got ", ins.size());
+  std::vector<Tensor> val(OMT_PW_MAX_INPUTS + p.prog.n_instr);
+  for (int k = 0; k < p.n_inputs; k++) val[k] = ins[k];
+  auto lit = [&](int32_t o) -> double { TORCH_CHECK(o < 0, "omt::fused_pointwise: this operand must be a number"); return p.prog.literal[-1 - o]; };
+  auto ten = [&](int32_t o) -> Tensor { return o >= 0 ? val[o] : at::scalar_tensor(p.prog.literal[-1 - o], ins[0].options()); };
+  Tensor r;
+  for (int j = 0; j < p.prog.n_instr; j++) {
+    const OmtPwInstr& i = p.prog.instr[j];
+    switch (i.op) {
+      case OMT_PW_ADD: r = at::add(ten(i.a), ten(i.b), lit(i.c)); break;
+      case OMT_PW_SUB: r = at::sub(ten(i.a), ten(i.b), lit(i.c)); break;
+      case OMT_PW_RSUB: r = at::sub(ten(i.b), ten(i.a), lit(i.c)); break;
+      case OMT_PW_MUL: r = at::mul(ten(i.a), ten(i.b)); break;
+      case OMT_PW_DIV: r = at::div(ten(i.a), ten(i.b)); break;
+      case OMT_PW_NEG: r = at::neg(ten(i.a)); break;
+      case OMT_PW_RELU: r = at::relu(ten(i.a)); break;
+      case OMT_PW_EXP: r = at::exp(ten(i.a)); break;
+      case OMT_PW_LOG: r = at::log(ten(i.a)); break;
+      case OMT_PW_SQRT: r = at::sqrt(ten(i.a)); break;
+      case OMT_PW_RSQRT: r = at::rsqrt(ten(i.a)); break;
+      case OMT_PW_RECIP: r = at::reciprocal(ten(i.a)); break;
+      case OMT_PW_ABS: r = at::abs(ten(i.a)); break;
+      case OMT_PW_TANH: r = at::tanh(ten(i.a)); break;
+      case OMT_PW_SIGMOID: r = at::sigmoid(ten(i.a)); break;
+      case OMT_PW_SILU: r = at::silu(ten(i.a)); break;
+      case OMT_PW_MAX: r = at::maximum(ten(i.a), ten(i.b)); break;
+      case OMT_PW_MIN: r = at::minimum(ten(i.a), ten(i.b)); break;
+      case OMT_PW_POW: r = at::pow(ten(i.a), lit(i.b)); break;
+      case OMT_PW_THRESHOLD_BWD: r = at::threshold_backward(ten(i.a), ten(i.b), lit(i.c)); break;
+      case OMT_PW_SIGMOID_BWD: r = at::sigmoid_backward(ten(i.a), ten(i.b)); break;
+      case OMT_PW_TANH_BWD: r = at::tanh_backward(ten(i.a), ten(i.b)); break;
+      case OMT_PW_SILU_BWD: r = at::silu_backward(ten(i.a), ten(i.b)); break;
+      case OMT_PW_GELU: r = at::gelu(ten(i.a), "none"); break;
+      case OMT_PW_GELU_TANH: r = at::gelu(ten(i.a), "tanh"); break;
+      case OMT_PW_GELU_BWD: r = at::gelu_backward(ten(i.a), ten(i.b), "none"); break;
+      case OMT_PW_GELU_TANH_BWD: r = at::gelu_backward(ten(i.a), ten(i.b), "tanh"); break;
+      case OMT_PW_CLAMP: r = at::clamp(ten(i.a), lit(i.b), lit(i.c)); break;
+      case OMT_PW_HARDSWISH: r = at::hardswish(ten(i.a)); break;
+      case OMT_PW_HARDSWISH_BWD: r = at::hardswish_backward(ten(i.a), ten(i.b)); break;
+      case OMT_PW_HARDSIGMOID: r = at::hardsigmoid(ten(i.a)); break;
+      case OMT_PW_HARDSIGMOID_BWD: r = at::hardsigmoid_backward(ten(i.a), ten(i.b)); break;
+      default: TORCH_CHECK(false, "omt::fused_pointwise: bad op");
+    }
+    val[OMT_PW_MAX_INPUTS + j] = r;
+  }
+  std::vector<int64_t> shape = ins[0].sizes().vec();  // (a chain whose last value is narrower than its inputs broadcasts like them)
+  for (auto& t : ins) shape = at::infer_size(shape, t.sizes());
+  return r.sizes() == IntArrayRef(shape) ? r : r.expand(shape).contiguous();
 }
 
 // ---- device implementations ------------------------------------------------------------------------------------------------
@@ -195,7 +308,40 @@ static Tensor conv_bn_act_eval_dev(const Tensor& x, const Tensor& cw, const std:
   return conv_act_dev(x, f.first, f.second, stride, padding, act_);
 }
 
-static Tensor fused_pointwise_dev(c10::string_view kernel, at::TensorList ins) { return fused_pointwise_ref(kernel, ins); }
+// device: one launch of the interpreter kernel. The output takes the layout of the first full-shape dense input (so a
+// channels-last chain stays channels-last), else it is contiguous.
+static Tensor fused_pointwise_dev(c10::string_view kernel, at::TensorList ins) {
+  const PwParsed& p = parse_program(std::string(kernel));
+  NEED((int)ins.size() == p.n_inputs, "input count");
+  std::vector<int64_t> shape = ins[0].sizes().vec();
+  for (auto& t : ins) {
+    NEED(f32(t), "float32 device inputs");
+    shape = at::infer_size(shape, t.sizes());
+  }
+  const int R = (int)shape.size();
+  NEED(R <= 8, "rank <= 8");
+  int64_t numel = 1;
+  for (int64_t d : shape) numel *= d;
+  NEED(numel > 0 && numel < (1ll << 40), "empty or oversized output");
+  Tensor out;
+  for (auto& t : ins)
+    if (!out.defined() && t.sizes() == IntArrayRef(shape) && t.is_non_overlapping_and_dense() && !t.is_contiguous())
+      out = empty_dev({numel}, at::kFloat).as_strided(shape, t.strides());
+  if (!out.defined()) out = empty_dev(shape, at::kFloat);
+  const float* ptrs[OMT_PW_MAX_INPUTS] = {};
+  int64_t strides[OMT_PW_MAX_INPUTS * 8] = {}, ostr[8] = {};
+  int32_t shp[8] = {};
+  for (int d = 0; d < R; d++) { shp[d] = (int32_t)shape[d]; ostr[d] = out.stride(d); NEED(shape[d] < (1ll << 31), "dimension below 2^31"); }
+  for (size_t k = 0; k < ins.size(); k++) {
+    ptrs[k] = ins[k].data_ptr<float>();
+    for (int d = 0; d < R; d++) {
+      const int di = d - (R - (int)ins[k].dim());
+      strides[k * 8 + d] = (di >= 0 && ins[k].size(di) != 1) ? ins[k].stride(di) : 0;
+    }
+  }
+  check(omt_pointwise(&p.prog, p.n_inputs, ptrs, strides, ostr, shp, R, out.data_ptr<float>(), cur_stream()), "fused pointwise chain");
+  return out;
+}
 
 // eager entry points for the non-functional BatchNorm variants that traced / compiled graphs call (csrc/fused.cpp:173-181)
 static std::tuple<Tensor, Tensor, Tensor> bn_legit(const Tensor& x, const std::optional<Tensor>& w, const std::optional<Tensor>& b, Tensor& rm,
@@ -268,7 +414,9 @@ TORCH_LIBRARY_IMPL(omt, PrivateUse1, m) {
                                 const Tensor& rm, const Tensor& rv, double eps, IntArrayRef s, IntArrayRef p, int64_t a) {
     return dev_or_composite<&conv_bn_act_eval_dev, &conv_bn_act_eval_ref>("conv_bn_act_eval", x, cw, cb, w, b, rm, rv, eps, s, p, a);
   });
-  m.impl("fused_pointwise", &fused_pointwise_dev);
+  m.impl("fused_pointwise", [](c10::string_view kernel, at::TensorList ins) {
+    return dev_or_composite<&fused_pointwise_dev, &fused_pointwise_ref>("fused_pointwise", kernel, ins);
+  });
 }
 TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
   OMT_IMPL(m, _native_batch_norm_legit, bn_legit);

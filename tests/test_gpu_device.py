@@ -480,6 +480,81 @@ def test_kernel_times_reports_device_time_per_kernel(omt):
     assert core.kernel_times(True) == {}
 
 
+def test_fused_pointwise_programs_on_the_device(omt):
+    """omt::fused_pointwise: the interpreter kernel against the composite definition on the CPU, for every op of the table,
+    with broadcast and scalar operands, channels-last inputs (the output keeps that layout) and a maximal-length chain."""
+    fp = torch.ops.omt.fused_pointwise
+    h = lambda *v: ",".join("nan" if x != x else ("inf" if x == float("inf") else ("-inf" if x == float("-inf") else float(x).hex())) for x in v)
+    torch.manual_seed(0)
+    a, b = torch.randn(3, 8, 5, 7), torch.randn(3, 8, 5, 7)
+    pos = a.abs() + 0.1
+    one = lambda op, second="v1", third="v0": f"pw1|2|{op},v0,{second},{third};mul,t0,#0,t0|{h(1.0, 0.5, 0.0, 2.0)}"
+    cases = [(one(op), (a, b)) for op in ("mul", "div", "max", "min", "sigmoid_bwd", "tanh_bwd", "silu_bwd", "gelu_bwd", "gelu_tanh_bwd",
+                                           "hardswish_bwd", "hardsigmoid_bwd")]
+    cases += [(one(op, "v0"), (a, b)) for op in ("neg", "relu", "exp", "abs", "tanh", "sigmoid", "silu", "gelu", "gelu_tanh", "hardswish", "hardsigmoid")]
+    cases += [(one(op, "v0"), (pos, b)) for op in ("log", "sqrt", "rsqrt", "recip")]
+    cases += [(one("add", "v1", "#1"), (a, b)), (one("sub", "v1", "#3"), (a, b)), (one("rsub", "#3", "#1"), (a, b)), (one("pow", "#3"), (a, b)),
+              (one("pow", "#1"), (pos, b)), (one("threshold_bwd", "v1", "#2"), (a, b)), (one("clamp", "#1", "#3"), (a, b))]
+    # broadcasting: a per-channel [1,8,1,1] operand and a [7] operand; a scalar-only second operand
+    cases.append((f"pw1|3|mul,v0,v1,v0;add,t0,v2,#0;hardswish,t1,t1,t1|{h(1.0)}", (a, torch.randn(1, 8, 1, 1), torch.randn(7))))
+    # a 24-instruction chain
+    chain = ";".join(["add,v0,v1,#0"] + [f"{'tanh' if j % 2 else 'add'},t{j - 1},v1,#0" for j in range(1, 24)])
+    cases.append((f"pw1|2|{chain}|{h(0.25)}", (a, b)))
+    for prog, ins in cases:
+        want = fp(prog, list(ins))
+        got = fp(prog, [t.to(D) for t in ins])
+        assert got.device.type == D and got.shape == want.shape
+        assert e(got, want) <= 1e-5, prog
+    # channels-last inputs: the output keeps the layout, and the kernel walks memory linearly
+    acl, bcl = (t.to(D).contiguous(memory_format=torch.channels_last) for t in (a, b))
+    got = fp(cases[0][0], [acl, bcl])
+    assert got.is_contiguous(memory_format=torch.channels_last) and e(got, fp(cases[0][0], [a, b])) <= 1e-5
+    mixed = fp(cases[0][0], [acl, b.to(D)])   # one NHWC, one NCHW operand: general indexing
+    assert e(mixed, fp(cases[0][0], [a, b])) <= 1e-5
+    # NaN handling follows aten: maximum / minimum propagate, clamp keeps NaN
+    n1 = torch.tensor([float("nan"), 1.0, -2.0, float("nan")])
+    n2 = torch.tensor([0.0, float("nan"), 3.0, float("nan")])
+    for op in ("max", "min"):
+        prog = f"pw1|2|{op},v0,v1,v0;add,t0,#0,#1|{h(0.0, 1.0)}"
+        got, want = fp(prog, [n1.to(D), n2.to(D)]).cpu(), fp(prog, [n1, n2])
+        assert torch.equal(torch.isnan(got), torch.isnan(want)) and torch.equal(got[~torch.isnan(got)], want[~torch.isnan(want)])
+    with pytest.raises(RuntimeError, match="pointwise"):
+        fp("pw1|1|frobnicate,v0,v0,v0|", [a.to(D)])
+    assert not omt.FALLBACKS, dict(omt.FALLBACKS)
+
+
+def test_compile_backend_fuses_pointwise_chains_on_the_device(omt):
+    """Pass 4 end to end: a squeeze-excite style block (global pool, two 1x1 convs, hard-sigmoid gate, scale, residual add,
+    hard-swish) compiled for the device; outputs and gradients against the eager CPU model."""
+    from omarchy_mac_torch_b200.native import core
+
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.fc1, self.fc2 = nn.Conv2d(16, 8, 1), nn.Conv2d(8, 16, 1)
+
+        def forward(self, x):
+            g = F.hardsigmoid(self.fc2(F.relu(self.fc1(F.adaptive_avg_pool2d(x, 1)))))
+            return F.hardswish(x * g + x) * 0.5 + torch.tanh(x)
+
+    torch.manual_seed(0)
+    ref = Block()
+    mod = copy.deepcopy(ref).to(D)
+    x = torch.randn(4, 16, 12, 12)
+    x1, x2 = x.clone().requires_grad_(), x.to(D).requires_grad_()
+    omt.FALLBACKS.clear()
+    core.kernel_counts(True)
+    ref(x1).square().sum().backward()
+    out = torch.compile(mod, backend="omarchy_mac_torch")(x2)
+    out.square().sum().backward()
+    kc = core.kernel_counts(True)
+    assert kc.get("pointwise_program", 0) >= 2, kc
+    assert e(out, ref(x)) <= TOL and e(x2.grad, x1.grad) <= TOL
+    for a_, b_ in zip(ref.parameters(), mod.parameters()):
+        assert e(b_.grad, a_.grad) <= TOL
+    assert not omt.FALLBACKS, dict(omt.FALLBACKS)
+
+
 def test_step_graph_replays_match_eager_steps(omt):
     """graphs.capture: the whole training step (zero_grad, fused-stack forward/backward, fused SGD) recorded once and
     replayed; every replay has to do exactly what an eager step does, also after the static batch tensors are refilled."""

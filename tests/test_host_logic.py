@@ -159,3 +159,45 @@ def test_compile_regions_matches_eager_and_delivers_gradients_region_by_region(p
             seen.append(region(n))
     assert seen == ["head", "c", "b", "a", "stem"], seen  # each region's gradients arrive together, in backward order
     assert [n for n, _ in mod.named_parameters()] == [n for n, _ in ref.named_parameters()]
+
+
+def test_pointwise_chains_become_one_op_and_keep_their_results(pkg, monkeypatch):
+    """Pass 4 on CPU graphs: chains of elementwise ops (forward and the backward forms autograd derives from them) collapse
+    into omt.fused_pointwise programs; outputs and gradients equal the unfused model's."""
+    from torch._dynamo.backends.common import aot_autograd
+    from functorch.compile import make_boxed_func
+    from omarchy_mac_torch_b200 import compile as C
+    monkeypatch.setattr(C, "_ANY_DEVICE", True)
+    seen, programs = [], []
+
+    def compiler(gm, _inputs):
+        seen.append(C.rewrite(gm))
+        programs.extend(n.args[0] for n in gm.graph.nodes if n.op == "call_function" and n.target is torch.ops.omt.fused_pointwise.default)
+        return make_boxed_func(gm.forward)
+
+    backend = aot_autograd(fw_compiler=compiler, bw_compiler=compiler, inference_compiler=compiler)
+
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.scale = torch.nn.Parameter(torch.randn(1, 6, 1, 1))
+
+        def forward(self, x, r):
+            y = F.hardswish(x * self.scale + 0.5)                  # broadcast of a [1,6,1,1] parameter, a scalar folded in
+            y = torch.sigmoid(y) * torch.tanh(r) - 2.0 * r       # two inputs, alpha
+            y = F.gelu(y, approximate="tanh").clamp(min=-0.1) ** 2
+            return F.silu(y).relu()
+
+    torch.manual_seed(0)
+    ref = Net()
+    mod = copy.deepcopy(ref)
+    x, r = torch.randn(4, 6, 5, 5), torch.randn(4, 6, 5, 5)
+    x1, x2 = x.clone().requires_grad_(), x.clone().requires_grad_()
+    ref(x1, r).square().sum().backward()
+    out = torch.compile(mod, backend=backend)(x2, r)
+    out.square().sum().backward()
+    assert torch.allclose(out, ref(x, r), rtol=1e-5, atol=1e-6)
+    assert torch.allclose(x1.grad, x2.grad, rtol=1e-4, atol=1e-6) and torch.allclose(ref.scale.grad, mod.scale.grad, rtol=1e-4, atol=1e-5)
+    assert sum(s["pointwise"] for s in seen) >= 2 and programs, seen   # at least one chain in the forward and one in the backward graph
+    assert all(p.startswith("pw1|") and 2 <= len(p.split("|")[2].split(";")) <= 24 for p in programs), programs
+    assert any("hardswish" in p for p in programs) and any("_bwd" in p for p in programs), programs
