@@ -77,11 +77,12 @@ struct ActView {  // OmtAct by value for kernels
   __host__ __device__ int64_t off(int n, int c, int h, int w) const { return n * sn + c * sc + h * sh + w * sw; }
 };
 inline ActView view(const OmtAct* a) { return ActView{a->p, a->sn, a->sc, a->sh, a->sw}; }
+// (the stride of a dimension of size 1 never enters an address: a [n, c, 1, 1] tensor is both layouts at once)
 inline bool is_nchw(const OmtAct* a, int c, int h, int w) {
-  return a->sw == 1 && a->sh == w && a->sc == (int64_t)h * w && a->sn == (int64_t)c * h * w;
+  return (w == 1 || a->sw == 1) && (h == 1 || a->sh == w) && (c == 1 || a->sc == (int64_t)h * w) && a->sn == (int64_t)c * h * w;
 }
 inline bool is_nhwc(const OmtAct* a, int c, int h, int w) {
-  return a->sc == 1 && a->sw == c && a->sh == (int64_t)w * c && a->sn == (int64_t)h * w * c;
+  return (c == 1 || a->sc == 1) && (w == 1 || a->sw == c) && (h == 1 || a->sh == (int64_t)w * c) && a->sn == (int64_t)h * w * c;
 }
 
 // Argument checks every dense-convolution entry point starts with (the reference's conv_kind / NEED rules,

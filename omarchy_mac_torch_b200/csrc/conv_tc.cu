@@ -724,7 +724,7 @@ __global__ void __launch_bounds__(256) splitk_epilogue_kernel(TcArgs g) {
 // dense channels-last output written pixel for pixel (no phase stride), 16-byte aligned rows
 bool dense_out(const TcArgs& a) {
   const ActView& y = a.y;
-  return a.out_step == 1 && a.out_y0 == 0 && a.out_x0 == 0 && y.sc == 1 && y.sw == a.N && y.sh == (int64_t)a.ow * a.N &&
+  return a.out_step == 1 && a.out_y0 == 0 && a.out_x0 == 0 && y.sc == 1 && (a.ow == 1 || y.sw == a.N) && (a.oh == 1 || y.sh == (int64_t)a.ow * a.N) &&
          y.sn == (int64_t)a.oh * a.ow * a.N && a.N % 4 == 0 && (reinterpret_cast<uintptr_t>(y.p) & 15) == 0;
 }
 

@@ -52,7 +52,21 @@ static void fused_adamw_(at::TensorList params, at::TensorList grads, at::Tensor
             found_inf);
 }
 
+// torch.optim advances the device-resident step counters of a fused optimizer with _foreach_add_(steps, 1). Without a
+// kernel for this device that op decomposes into one add per tensor (one launch per parameter); here the whole list goes
+// through ATen's multi-tensor CUDA kernel on aliases of the same memory: one or two launches.
+static void foreach_add_scalar_(at::TensorList self, const at::Scalar& scalar) {
+  std::vector<Tensor> alias;
+  alias.reserve(self.size());
+  for (const Tensor& t : self) {
+    NEED(is_dev(t), "device tensors");
+    alias.push_back(cuda_alias(t));
+  }
+  at::_foreach_add_(alias, scalar);
+}
+
 TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
+  OMT_IMPL(m, _foreach_add__Scalar, foreach_add_scalar_);
   OMT_IMPL(m, _fused_sgd_, fused_sgd_);
   OMT_IMPL(m, _fused_adam_, fused_adam_);
   OMT_IMPL(m, _fused_adamw_, fused_adamw_);
