@@ -476,7 +476,7 @@ TRAIN = {
                                  graph=True),
     "resnet50": lambda: Train("resnet50_b256_train", lambda: _models().ResNet50(), (256, 3, 224, 224), 1000,
                               _sgd(0.1, momentum=0.9, nesterov=True, weight_decay=1e-4), 256, "SGD lr .1 momentum .9 nesterov wd 1e-4",
-                              compile=True, regions=True),
+                              compile=True),
 }
 
 WORKLOADS = {**CONV, **TRAIN, "hbm": HbmKernels}
@@ -623,7 +623,9 @@ def main():
     ap.add_argument("--compile", action="store_true", help="training workloads: call the model through the compile backend")
     ap.add_argument("--graph", action="store_true", help="training workloads: replay the whole step as one CUDA graph")
     ap.add_argument("--no-graph", action="store_true")
-    ap.add_argument("--whole-graph", action="store_true", help="compile the model as one graph instead of region by region")
+    ap.add_argument("--regions", action="store_true",
+                    help="compile the model region by region (compile.compile_regions) instead of as one graph: gradient buckets then "
+                         "reduce under the backward pass, at the price of some host time per region")
     ap.add_argument("--profile-step", action="store_true",
                     help="for ncu --profile-from-start off: after the warm-up run ONE step between cudaProfilerStart/Stop and exit")
     args = ap.parse_args()
@@ -634,8 +636,8 @@ def main():
     if isinstance(wl, Train):
         if args.eager or args.compile:
             wl.compile = args.compile and not args.eager
-        if args.whole_graph:
-            wl.regions = False
+        if args.regions:
+            wl.regions = True
         if args.graph or args.no_graph:
             wl.graph = args.graph and not args.no_graph
         wl.set_api()

@@ -8,6 +8,9 @@
  *     legacy default stream); no torch or C++ types cross this boundary;
  *   - returns 0 on success or a negative OMT_E* code; the message is read with omt_last_error();
  *   - never throws, never falls back to the host: there is no CPU path in this library.
+ * There are no collective entry points here: the one exchange step of data-parallel training (the gradient all-reduce)
+ * is issued by the Python layer through torch.distributed's NCCL backend on the buckets this library's kernels wrote, so
+ * the library neither links NCCL nor touches peer memory.
  * All tensors are float32 unless stated. Activations are addressed through OmtAct (pointer + element strides), so
  * the same entry point serves NCHW-contiguous tensors (the reference's only layout, csrc/device.cpp:60-66 base0)
  * and channels-last (NHWC) tensors, which is what the tensor-core kernels prefer.
@@ -163,8 +166,10 @@ int omt_conv_wgrad(const OmtConvGeo* g, const OmtAct* x, const OmtAct* gy, float
  * calls no cudaMalloc, cudaFree or allocating library routine.
  *   - Capacity: omt_conv_wgrad_noalloc_capacity() bytes (16 MiB) of split-K slabs; a geometry that needs more is refused
  *     with OMT_ETOOBIG. Every GPU that loads the library holds that array until the process exits.
- *   - The first call on each device looks up the array's device address (with that device current); make that first call
- *     outside any stream capture.
+ *   - The first call on each device looks up the array's device address (with that device current). With CUDA's lazy
+ *     module loading that lookup is also what makes the driver load the library's image and back the 16 MiB array with
+ *     device memory, so the FIRST call per device can itself need memory: make it once at start-up, before the process
+ *     hands out the rest of the device's memory, and outside any stream capture. Later calls allocate nothing.
  *   - All calls on a device share the array. The slabs are fully overwritten by every call, so nothing needs clearing,
  *     but two calls that overlap on the GPU (different streams) race on it: keep them on one stream or order them. */
 size_t omt_conv_wgrad_noalloc_capacity(void);
