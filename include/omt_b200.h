@@ -356,6 +356,30 @@ typedef struct OmtPwProgram {
 int omt_pointwise(const OmtPwProgram* prog, int32_t n_inputs, const float* const* inputs, const int64_t* in_strides,
                   const int64_t* out_strides, const int32_t* shape, int32_t rank, float* out, omt_stream_t stream);
 
+/* ---- classification loss --------------------------------------------------------------------------------------------- */
+/* F.cross_entropy on [rows, cols] float32 logits decomposes into log_softmax and nll_loss; the reference runs them as
+ * softmax.wgsl (mode 1), nll_fwd.wgsl + two row reductions + a division, nll_bwd.wgsl and softmax_bwd.wgsl
+ * (csrc/reduce.cpp:128-201). Matrices are dense row-major; targets are int64 class indices; `weight` ([cols]) may be NULL;
+ * rows whose target equals ignore_index contribute nothing; reduction: 0 none (loss is [rows], total_weight 0),
+ * 1 mean (sum of -w*logp / sum of w), 2 sum. A target outside [0, cols) makes the loss NaN and gets a zero gradient. */
+/* logp = x - logsumexp(x) along each row. */
+int omt_log_softmax(const float* x, float* logp, int64_t rows, int32_t cols, omt_stream_t stream);
+/* dx = g - exp(logp) * rowsum(g). */
+int omt_log_softmax_backward(const float* g, const float* logp, float* dx, int64_t rows, int32_t cols, omt_stream_t stream);
+/* loss and total weight from log-probabilities, one launch (rows summed in a fixed order by the last block). */
+int omt_nll_loss(const float* logp, const int64_t* target, const float* weight, float* loss, float* total_weight, int64_t rows,
+                 int32_t cols, int64_t ignore_index, int32_t reduction, omt_stream_t stream);
+/* dlogp: -w[t] * g (/ total_weight for mean) at the target column, 0 elsewhere; g is [rows] for reduction none, else [1]. */
+int omt_nll_loss_backward(const float* g, const int64_t* target, const float* weight, const float* total_weight, float* dlogp,
+                          int64_t rows, int32_t cols, int64_t ignore_index, int32_t reduction, omt_stream_t stream);
+/* Both steps in one launch from the logits: writes logp (what the backward needs), loss and total_weight. */
+int omt_softmax_nll(const float* x, const int64_t* target, const float* weight, float* logp, float* loss, float* total_weight,
+                    int64_t rows, int32_t cols, int64_t ignore_index, int32_t reduction, omt_stream_t stream);
+/* Gradient with respect to the logits in one launch: (exp(logp) - onehot(target)) * w[t] * g (/ total_weight). */
+int omt_softmax_nll_backward(const float* g, const float* logp, const int64_t* target, const float* weight,
+                             const float* total_weight, float* dx, int64_t rows, int32_t cols, int64_t ignore_index,
+                             int32_t reduction, omt_stream_t stream);
+
 /* ---- small helpers used by plans and data parallel ---------------------------------------------------------------- */
 
 /* dst = src * scale over n floats (bucket averaging after all-reduce; icopy.wgsl when scale == 1). */

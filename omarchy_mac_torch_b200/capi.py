@@ -81,6 +81,12 @@ SIGNATURES = {
     "omt_kernel_times": (_SZ, [C.c_char_p, _SZ, _I]),
     "omt_gemm": (_I, [_P, _I64, _I64, _P, _I64, _I64, _P, _P, _I, _I, _I, _P]),
     "omt_pointwise": (_I, [_P, _I, _P, _P, _P, _P, _I, _P, _P]),
+    "omt_log_softmax": (_I, [_P, _P, _I64, _I, _P]),
+    "omt_log_softmax_backward": (_I, [_P, _P, _P, _I64, _I, _P]),
+    "omt_nll_loss": (_I, [_P, _P, _P, _P, _P, _I64, _I, _I64, _I, _P]),
+    "omt_nll_loss_backward": (_I, [_P, _P, _P, _P, _P, _I64, _I, _I64, _I, _P]),
+    "omt_softmax_nll": (_I, [_P, _P, _P, _P, _P, _P, _I64, _I, _I64, _I, _P]),
+    "omt_softmax_nll_backward": (_I, [_P, _P, _P, _P, _P, _P, _I64, _I, _I64, _I, _P]),
     "omt_conv_timing": (_I, [_I]),
     "omt_conv_timing_read": (_I, [C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_int64), _I]),
     "omt_conv_timing_bytes": (_I, [C.POINTER(C.c_double)]),

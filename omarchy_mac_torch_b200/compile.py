@@ -1,6 +1,6 @@
 """torch.compile backend: `torch.compile(model, backend="omarchy_mac_torch")`.
 
-Dynamo captures the model and AOTAutograd lowers it to aten graphs for forward and backward. Three FX passes then rewrite
+Dynamo captures the model and AOTAutograd lowers it to aten graphs for forward and backward. FX passes then rewrite
 those graphs to the fused `omt::` ops, and the graph runs op by op on the device:
 
   1. training BatchNorm2d followed by ReLU            -> omt.bn_relu_train
@@ -14,6 +14,9 @@ those graphs to the fused `omt::` ops, and the graph runs op by op on the device
 
   4. chains of elementwise ops (add/mul/relu/sigmoid/hardswish/..., their backward forms, scalars folded in) that only
      feed one another                                   -> omt.fused_pointwise (one kernel, one pass over memory)
+
+  5. _log_softmax -> nll_loss_forward (what F.cross_entropy lowers to) -> omt.softmax_nll, and in the backward graph
+     nll_loss_backward -> _log_softmax_backward_data -> omt.softmax_nll_backward: the loss is two launches per step
 
 These are passes 1-4 of the reference's omarchy_mac_torch/compile.py:69-161, 256-336. Its pass 4 generates shader source
 for every chain; here the chain is encoded as a small program string that one ahead-of-time interpreter kernel runs
@@ -438,12 +441,61 @@ def fuse_pointwise(graph):
     return done
 
 
+def _f32_2d(n):
+    v = _meta(n)
+    return isinstance(v, torch.Tensor) and v.dtype == torch.float32 and v.dim() == 2 and (_ANY_DEVICE or v.device.type == DEVICE)
+
+
+def fuse_softmax_nll(graph):
+    """Pass 5: the two halves of F.cross_entropy on a [batch, classes] matrix, forward and backward."""
+    done = 0
+    order = {n: i for i, n in enumerate(graph.nodes)}
+    for nll in list(graph.nodes):
+        if _is(nll, aten.nll_loss_forward.default):
+            lp, target, weight, reduction, ignore = nll.args[:5]
+            if not (_is(lp, aten._log_softmax.default) and _f32_2d(lp) and lp.args[1] in (1, -1) and not lp.args[2]):
+                continue
+            # the fused op takes the place of _log_softmax (other readers of logp, e.g. the copy saved for backward, may come
+            # before nll_loss_forward), so its other operands must exist by then
+            if any(isinstance(a, Node) and order[a] > order[lp] for a in (target, weight)):
+                continue
+            with graph.inserting_before(lp):
+                fused = graph.call_function(omt.softmax_nll.default, (lp.args[0], target, weight, reduction, ignore))
+            items = _items(nll)
+            for idx, new_idx in ((0, 0), (1, 2)):
+                gi = items.get(idx)
+                if gi is not None:
+                    gi.replace_all_uses_with(_getitem_after(graph, gi, fused, new_idx, gi.meta))
+                    graph.erase_node(gi)
+            graph.erase_node(nll)
+            lp.replace_all_uses_with(_getitem_after(graph, lp, fused, 1, lp.meta))
+            graph.erase_node(lp)
+            done += 1
+        elif _is(nll, aten.nll_loss_backward.default):
+            g, lp, target, weight, reduction, ignore, tw = nll.args[:7]
+            user = _sole_user(nll)
+            # nll_loss_backward is the gradient of logp; when the only reader is a _log_softmax_backward_data taking it as its
+            # gradient, that op's `output` operand is logp itself (possibly through detach nodes): the chain rule of the pair
+            if not (_is(user, aten._log_softmax_backward_data.default) and user.args[0] is nll and _f32_2d(lp) and _meta(user.args[1]) is not None
+                    and _meta(user.args[1]).shape == _meta(lp).shape and user.args[2] in (1, -1) and user.args[3] == torch.float32):
+                continue
+            with graph.inserting_before(user):
+                fused = graph.call_function(omt.softmax_nll_backward.default, (g, lp, target, weight, reduction, ignore, tw))
+            fused.meta = dict(user.meta)
+            user.replace_all_uses_with(fused)
+            graph.erase_node(user)
+            graph.erase_node(nll)
+            done += 1
+    return done
+
+
 def rewrite(gm):
     """Apply the passes to a GraphModule in place; returns {pass: rewrites}."""
     g = gm.graph
     stats = {"bn_relu": fuse_bn_relu(g), "bn_add_relu": fuse_bn_add_relu(g), "bn_relu_backward": fuse_bn_relu_backward(g),
              "bn_add_relu_backward": fuse_bn_add_relu_backward(g), "conv_epilogue": fuse_conv_epilogues(g),
              "conv_bn_train": fuse_conv_bn_train(g), "dgrad_accumulate": fuse_dgrad_accumulate(g)}
+    stats["softmax_nll"] = fuse_softmax_nll(g)
     stats["pointwise"] = fuse_pointwise(g)
     g.eliminate_dead_code()
     g.lint()

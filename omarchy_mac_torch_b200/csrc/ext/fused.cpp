@@ -353,18 +353,6 @@ static std::tuple<Tensor, Tensor, Tensor> bn_legit_no_training(const Tensor& x, 
   return at::native_batch_norm(x, w, b, rm, rv, false, mom, eps);
 }
 
-// Device implementation first; when it declines (Unsupported) the composite runs instead and the reason is recorded.
-template <auto Dev, auto Ref, class... A>
-static auto dev_or_composite(const char* name, const A&... a) {
-  OMT_LOCK;
-  try {
-    return Dev(a...);
-  } catch (const Unsupported& e) {
-    note_fallback(name, e.why);
-    return Ref(a...);
-  }
-}
-
 TORCH_LIBRARY(omt, m) {
   m.def("bn_relu_train(Tensor x, Tensor w, Tensor b, Tensor rm, Tensor rv, float momentum, float eps) -> (Tensor, Tensor, Tensor, Tensor, Tensor)");
   m.def("bn_relu_backward(Tensor g, Tensor x, Tensor y, Tensor w, Tensor mean, Tensor invstd, bool[3] mask) -> (Tensor, Tensor, Tensor)");

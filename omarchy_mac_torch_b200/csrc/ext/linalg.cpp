@@ -1,6 +1,6 @@
 // aten::mm and aten::addmm for 2-D float32 tensors on the device: the classifier heads and their gradients run on the same
 // tcgen05 3xTF32 kernels as the convolutions (a matrix product is the 1x1 case of the implicit GEMM), through omt_gemm.
-// Same op coverage as the reference's csrc/linalg.cpp:62-92 for mm and addmm (its bmm stays with the bridge); the
+// Same op coverage as the reference's csrc/linalg.cpp:62-92 (mm, addmm, bmm); the
 // reference's planner callback for generated GEMM kernels (csrc/linalg.cpp:94-96) has no counterpart, set_mm_planner is
 // an inert shim in module.cpp.
 #include "omt.h"
@@ -56,7 +56,25 @@ static Tensor addmm_(const Tensor& bias, const Tensor& a, const Tensor& b, const
   return out;
 }
 
+// batched product (reference csrc/linalg.cpp:81-92, which puts the batch on the dispatch's z dimension): here one GEMM
+// launch per matrix of the batch; batches of many small matrices are better served by ATen's batched kernel and stay
+// with the bridge
+static Tensor bmm_(const Tensor& a, const Tensor& b) {
+  NEED(f32(a) && f32(b) && a.dim() == 3 && b.dim() == 3 && a.size(0) == b.size(0) && a.size(2) == b.size(1), "float32 3-D bmm");
+  NEED(a.numel() > 0 && b.numel() > 0 && a.size(0) <= 64 && a.size(1) * b.size(2) >= 128 * 128, "empty operands, or a batch of many small matrices");
+  Tensor out = empty_dev({a.size(0), a.size(1), b.size(2)}, at::kFloat);
+  for (int64_t i = 0; i < a.size(0); i++) {
+    Tensor ai = a.select(0, i), bi = b.select(0, i), oi = out.select(0, i);
+    if (!gemm_into(ai, bi, nullptr, oi)) {
+      Tensor ac = contig(ai);
+      NEED(gemm_into(ac, bi, nullptr, oi), "operand layout");
+    }
+  }
+  return out;
+}
+
 TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
+  OMT_IMPL(m, bmm, bmm_);
   OMT_IMPL(m, mm, mm_);
   OMT_IMPL(m, addmm, addmm_);
 }

@@ -140,6 +140,18 @@ void impl_name(torch::Library& m, F f) {
   m.impl(name.c_str(), f);
 }
 
+// omt:: ops: device implementation first; when it declines (Unsupported) the composite runs instead and the reason is recorded.
+template <auto Dev, auto Ref, class... A>
+auto dev_or_composite(const char* name, const A&... a) {
+  OMT_LOCK;
+  try {
+    return Dev(a...);
+  } catch (const Unsupported& e) {
+    note_fallback(name, e.why);
+    return Ref(a...);
+  }
+}
+
 // ---- conv (conv.cpp), used by fused.cpp and plans.cpp ---------------------------------------------------------------
 OmtConvGeo conv_geo(int64_t n, int64_t ci, int64_t co, int64_t ih, int64_t iw, int64_t ks, int64_t stride, int64_t pad,
                     int64_t groups = 1);

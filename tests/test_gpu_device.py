@@ -432,6 +432,50 @@ def test_linear_layers_run_on_the_conv_gemm_kernels(omt):
     omt.FALLBACKS.clear()
 
 
+def test_cross_entropy_on_the_device_eager_and_compiled(omt):
+    """F.cross_entropy lowers to _log_softmax + nll_loss_forward (+ their backward ops): all four run on the library's kernels
+    (reference csrc/reduce.cpp:141-201), and the compile backend fuses each pair into one launch; losses and gradients
+    against the CPU, bridge untouched. Also bmm on the GEMM kernels (csrc/linalg.cpp:81-92)."""
+    from omarchy_mac_torch_b200.native import core
+    torch.manual_seed(0)
+    omt.FALLBACKS.clear()
+    core.bridge_counts(True)
+    for rows, cols, kw in ((256, 1000, {}), (32, 10, dict(reduction="sum", ignore_index=3)), (7, 5, dict(reduction="none")),
+                           (64, 100, dict(weight=torch.rand(100) + 0.5))):
+        x = torch.randn(rows, cols) * 2
+        t = torch.randint(0, cols, (rows,))
+        t[1] = 3
+        xc = x.clone().requires_grad_()
+        ref = F.cross_entropy(xc, t, **kw)
+        ref.sum().backward()
+        kwd = {k: (v.to(D) if torch.is_tensor(v) else v) for k, v in kw.items()}
+        for compiled in (False, True):
+            xd = x.to(D).requires_grad_()
+            fn = (lambda a, b: F.cross_entropy(a, b, **kwd))
+            if compiled:
+                fn = torch.compile(fn, backend="omarchy_mac_torch")
+            core.kernel_counts(True)
+            out = fn(xd, t.to(D))
+            out.sum().backward()
+            kc = core.kernel_counts(True)
+            assert e(out, ref.detach()) <= 1e-5 and e(xd.grad, xc.grad) <= 1e-5, (rows, cols, kw, compiled)
+            if compiled:
+                assert kc.get("softmax_nll_fwd") == 1 and kc.get("softmax_nll_bwd") == 1 and "nll_fwd" not in kc and "log_softmax" not in kc, kc
+            else:
+                assert kc.get("log_softmax") == 1 and kc.get("nll_fwd") == 1 and kc.get("nll_bwd") == 1 and kc.get("log_softmax_bwd") == 1, kc
+    bc = core.bridge_counts(True)
+    assert not any("softmax" in k or "nll" in k for k in bc), bc
+    assert not any("softmax" in k or "nll" in k for k in omt.FALLBACKS), dict(omt.FALLBACKS)
+    a, b = torch.randn(3, 130, 70), torch.randn(3, 70, 160)
+    core.kernel_counts(True)
+    got = torch.bmm(a.to(D), b.to(D))
+    kc = core.kernel_counts(True)
+    assert e(got, torch.bmm(a.double(), b.double()).float()) <= TOL
+    assert sum(kc.values()) >= 3, kc   # one GEMM per matrix of the batch
+    assert not any("bmm" in k for k in core.bridge_counts(True))
+    omt.FALLBACKS.clear()
+
+
 def test_side_stream_producer_and_default_stream_consumer(omt):
     """Events and record_stream act on the stream they are given, not on the calling thread's current stream: a tensor
     produced on a side stream, handed over by an event recorded and waited for from the default stream's thread state.

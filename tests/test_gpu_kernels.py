@@ -599,3 +599,89 @@ def test_act_copy_layout_change(capi):
     z = torch.empty_like(x)
     capi.call("omt_act_copy", capi.act(y), capi.act(z), 3, 10, 7, 5, capi.stream_handle())
     assert torch.equal(x, z)
+
+
+def _np_cross_entropy(x, t, w, ignore, reduction):
+    """float64 restatement of log_softmax + nll_loss (the definition the reference's softmax/nll kernels implement,
+    csrc/reduce.cpp:128-201): returns logp, loss, total weight, gradient of the logits for an upstream gradient of ones."""
+    x = x.astype(np.float64)
+    lp = x - x.max(1, keepdims=True)
+    lp = lp - np.log(np.exp(lp).sum(1, keepdims=True))
+    ww = np.ones(x.shape[1]) if w is None else w.astype(np.float64)
+    live = t != ignore
+    wr = np.where(live, ww[np.where(live, t, 0)], 0.0)
+    rows = -wr * lp[np.arange(len(t)), np.where(live, t, 0)]
+    tw = wr.sum()
+    hot = np.zeros_like(lp)
+    hot[np.arange(len(t)), np.where(live, t, 0)] = 1.0
+    scale = wr / tw if reduction == 1 else wr
+    dx = (np.exp(lp) - hot) * scale[:, None]
+    loss = rows if reduction == 0 else rows.sum() / tw if reduction == 1 else rows.sum()
+    return lp, loss, (0.0 if reduction == 0 else tw), dx
+
+
+@pytest.mark.parametrize("reduction", [0, 1, 2], ids=["none", "mean", "sum"])
+@pytest.mark.parametrize("rows,cols,weighted", [(256, 1000, False), (32, 10, True), (5, 3, False), (1, 1, False), (4099, 33, True), (3, 5000, False)])
+def test_log_softmax_and_nll_loss(capi, rows, cols, weighted, reduction):
+    """The four loss entry points and the fused pair against a float64 restatement and against aten on the CPU; rows with the
+    ignored class, class weights, every reduction; one warp per row with ragged column counts; the sum over rows is ordered."""
+    rng = np.random.default_rng(rows * 31 + cols)
+    x = (rng.standard_normal((rows, cols)) * 3).astype(np.float32)
+    t = rng.integers(0, cols, rows)
+    ignore = -100 if cols == 1 else 1
+    if rows > 2:
+        t[1] = ignore
+    w = (rng.random(cols) + 0.5).astype(np.float32) if weighted else None
+    lp_ref, loss_ref, tw_ref, dx_ref = _np_cross_entropy(x, t, w, ignore, reduction)
+    xd, td, wd = dev(x), dev(t), dev(w)
+    sh, P = capi.stream_handle, capi.ptr
+    lp = torch.empty_like(xd)
+    capi.call("omt_log_softmax", P(xd), P(lp), rows, cols, sh())
+    assert rel_err(host(lp), lp_ref) <= 1e-6
+    loss = torch.full((rows if reduction == 0 else 1,), 7.0, device="cuda")
+    tw = torch.full((1,), 7.0, device="cuda")
+    capi.call("omt_nll_loss", P(lp), P(td), P(wd), P(loss), P(tw), rows, cols, ignore, reduction, sh())
+    assert rel_err(host(loss).reshape(np.shape(loss_ref)), loss_ref) <= 1e-6 and abs(float(tw) - tw_ref) <= 1e-6 * max(1.0, tw_ref)
+    # aten on the CPU agrees with the restatement (pins the restatement) and with the device
+    xt = torch.tensor(x, requires_grad=True)
+    red = ["none", "mean", "sum"][reduction]
+    at_loss = torch.nn.functional.cross_entropy(xt, torch.tensor(t), weight=None if w is None else torch.tensor(w), ignore_index=ignore, reduction=red)
+    at_loss.sum().backward()
+    if np.all(np.isfinite(loss_ref)):
+        assert rel_err(at_loss.detach().numpy().reshape(np.shape(loss_ref)), loss_ref) <= 1e-5
+        assert rel_err(xt.grad.numpy(), dx_ref) <= 1e-5
+    # fused forward: same three results from the logits in one launch, bit-identical to the two-step path
+    lp2, loss2, tw2 = torch.empty_like(xd), torch.empty_like(loss), torch.empty_like(tw)
+    n0 = capi.lib().omt_launch_count()
+    capi.call("omt_softmax_nll", P(xd), P(td), P(wd), P(lp2), P(loss2), P(tw2), rows, cols, ignore, reduction, sh())
+    assert capi.lib().omt_launch_count() - n0 == 1
+    assert torch.equal(lp2, lp) and torch.equal(loss2, loss) and torch.equal(tw2, tw)
+    # backward, two-step and fused
+    g = torch.ones(rows if reduction == 0 else 1, device="cuda")
+    dlp, dx, dx2 = torch.empty_like(xd), torch.empty_like(xd), torch.empty_like(xd)
+    capi.call("omt_nll_loss_backward", P(g), P(td), P(wd), P(tw), P(dlp), rows, cols, ignore, reduction, sh())
+    capi.call("omt_log_softmax_backward", P(dlp), P(lp), P(dx), rows, cols, sh())
+    capi.call("omt_softmax_nll_backward", P(g), P(lp), P(td), P(wd), P(tw), P(dx2), rows, cols, ignore, reduction, sh())
+    if np.all(np.isfinite(dx_ref)):
+        assert rel_err(host(dx), dx_ref) <= 1e-5 and rel_err(host(dx2), dx_ref) <= 1e-5
+    # the fused forward is deterministic (ordered sum over rows by the last block)
+    capi.call("omt_softmax_nll", P(xd), P(td), P(wd), P(lp2), P(loss2), P(tw2), rows, cols, ignore, reduction, sh())
+    assert torch.equal(loss2, loss)
+
+
+def test_nll_loss_refuses_bad_arguments(capi):
+    x = torch.zeros(4, 3, device="cuda")
+    t = torch.zeros(4, dtype=torch.int64, device="cuda")
+    out = torch.zeros(4, device="cuda")
+    P, sh = capi.ptr, capi.stream_handle
+    with pytest.raises(capi.OmtError):
+        capi.call("omt_nll_loss", P(x), P(t), None, P(out), P(out), 4, 3, -100, 3, sh())
+    with pytest.raises(capi.OmtError):
+        capi.call("omt_log_softmax", P(x), P(x), 0, 3, sh())
+    # a target outside [0, cols): NaN loss, zero gradient row, no fault
+    t[2] = 9
+    lp, loss, tw, dx = torch.empty_like(x), torch.zeros(1, device="cuda"), torch.zeros(1, device="cuda"), torch.empty_like(x)
+    capi.call("omt_softmax_nll", P(x), P(t), None, P(lp), P(loss), P(tw), 4, 3, -100, 1, sh())
+    assert torch.isnan(loss).all() and float(tw) == 3.0
+    capi.call("omt_softmax_nll_backward", P(torch.ones(1, device="cuda")), P(lp), P(t), None, P(tw), P(dx), 4, 3, -100, 1, sh())
+    assert torch.all(dx[2] == 0) and torch.isfinite(dx).all()

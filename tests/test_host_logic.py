@@ -201,3 +201,40 @@ def test_pointwise_chains_become_one_op_and_keep_their_results(pkg, monkeypatch)
     assert sum(s["pointwise"] for s in seen) >= 2 and programs, seen   # at least one chain in the forward and one in the backward graph
     assert all(p.startswith("pw1|") and 2 <= len(p.split("|")[2].split(";")) <= 24 for p in programs), programs
     assert any("hardswish" in p for p in programs) and any("_bwd" in p for p in programs), programs
+
+
+@pytest.mark.parametrize("reduction,weighted", [("mean", False), ("sum", True), ("none", False)])
+def test_cross_entropy_becomes_the_fused_pair(pkg, monkeypatch, reduction, weighted):
+    """Pass 5 on CPU graphs: log_softmax + nll_loss (what F.cross_entropy lowers to) become omt.softmax_nll in the forward
+    graph and omt.softmax_nll_backward in the backward graph; loss and gradient equal the unfused ones (ignore_index too)."""
+    from torch._dynamo.backends.common import aot_autograd
+    from functorch.compile import make_boxed_func
+    from omarchy_mac_torch_b200 import compile as C
+    monkeypatch.setattr(C, "_ANY_DEVICE", True)
+    seen, targets = [], []
+
+    def compiler(gm, _inputs):
+        seen.append(C.rewrite(gm))
+        targets.extend(str(n.target) for n in gm.graph.nodes if n.op == "call_function")
+        return make_boxed_func(gm.forward)
+
+    backend = aot_autograd(fw_compiler=compiler, bw_compiler=compiler, inference_compiler=compiler)
+    torch.manual_seed(0)
+    w = torch.rand(7) + 0.5 if weighted else None
+
+    def loss_fn(x, t):
+        out = F.cross_entropy(x * 1.5, t, weight=w, reduction=reduction, ignore_index=3)
+        return out.sum() if reduction == "none" else out
+
+    x = torch.randn(9, 7)
+    t = torch.randint(0, 7, (9,))
+    t[2] = 3
+    x1, x2 = x.clone().requires_grad_(), x.clone().requires_grad_()
+    ref = loss_fn(x1, t)
+    ref.backward()
+    out = torch.compile(loss_fn, backend=backend)(x2, t)
+    out.backward()
+    assert torch.allclose(out, ref, rtol=1e-6, atol=1e-7) and torch.allclose(x1.grad, x2.grad, rtol=1e-5, atol=1e-7)
+    assert sum(s["softmax_nll"] for s in seen) == 2, seen
+    assert "omt.softmax_nll.default" in targets and "omt.softmax_nll_backward.default" in targets
+    assert not any("nll_loss" in s or "_log_softmax" in s for s in targets), targets
