@@ -192,7 +192,7 @@ class HbmKernels:
     algorithmic bytes / CUDA-event time. `value` is the geometric mean over the kernels; `roofline` reports the slowest."""
     name = "hbm_bound_kernels"
     metric, unit, higher = "hbm_kernels_gbs", "GB/s", True
-    shape = dict(bn="256x64x112x112 channels-last", depthwise="128x96x56x56 3x3 channels-last", optimizer="64M parameters in 160 tensors")
+    shape = dict(bn="256x64x112x112 channels-last", depthwise="128x96x56x56 3x3 and 5x5 stride 1; 64x96x112x112 -> 56x56 stride 2; channels-last", optimizer="64M parameters in 160 tensors")
     h2d_bytes = d2h_bytes = 0
 
     def setup_gpu(self, seed, world=1):
@@ -216,6 +216,10 @@ class HbmKernels:
         wd = torch.randn(96, 1, 3, 3, device="cuda")
         gd = torch.randn_like(xd)
         nd = xd.numel()
+        wd5 = torch.randn(96, 1, 5, 5, device="cuda")
+        xs2 = torch.randn(64, 96, 112, 112, device="cuda").contiguous(memory_format=cl)   # stride-2 cases: 112^2 -> 56^2
+        gs2 = torch.randn(64, 96, 56, 56, device="cuda").contiguous(memory_format=cl)
+        ns2 = xs2.numel() + gs2.numel()
         params = [torch.randn(400_000, device="cuda") for _ in range(160)]
         grads = [torch.randn_like(t) for t in params]
         ms_ = [torch.zeros_like(t) for t in params]
@@ -223,7 +227,7 @@ class HbmKernels:
         steps = [torch.zeros((), device="cuda") for _ in params]
         npar = sum(t.numel() for t in params)
         call = capi.call
-        self.keep = (x, g, y, dx, xd, gd, params, grads, ms_, vs_, steps)
+        self.keep = (x, g, y, dx, xd, gd, xs2, gs2, wd5, params, grads, ms_, vs_, steps)
         self.kernels = {
             # name: (callable, algorithmic bytes)
             "bn_statistics": (lambda: call("omt_bn_stats", A(x), n, c, h, w, P(mean), P(var), P(inv), P(rm), P(rv), None, None, 0.1, 1e-5, 0, sh()), 4 * ne),
@@ -232,6 +236,13 @@ class HbmKernels:
             "depthwise_fwd": (lambda: capi.dw_fwd(xd, wd, None, 1, 1, cl=True), 8 * nd),
             "depthwise_dgrad": (lambda: capi.dw_dgrad(gd, wd, (56, 56), 1, 1, cl=True), 8 * nd),
             "depthwise_wgrad": (lambda: capi.dw_wgrad(xd, gd, 3, 1, 1), 8 * nd),
+            "depthwise5x5_fwd": (lambda: capi.dw_fwd(xd, wd5, None, 1, 2, cl=True), 8 * nd),
+            "depthwise5x5_dgrad": (lambda: capi.dw_dgrad(gd, wd5, (56, 56), 1, 2, cl=True), 8 * nd),
+            "depthwise5x5_wgrad": (lambda: capi.dw_wgrad(xd, gd, 5, 1, 2), 8 * nd),
+            "depthwise3x3s2_fwd": (lambda: capi.dw_fwd(xs2, wd, None, 2, 1, cl=True), 4 * ns2),
+            "depthwise3x3s2_dgrad": (lambda: capi.dw_dgrad(gs2, wd, (112, 112), 2, 1, cl=True), 4 * ns2),
+            "depthwise3x3s2_wgrad": (lambda: capi.dw_wgrad(xs2, gs2, 3, 2, 1), 4 * ns2),
+            "depthwise5x5s2_fwd": (lambda: capi.dw_fwd(xs2, wd5, None, 2, 2, cl=True), 4 * ns2),
             "maxpool3x3s2_fwd": (lambda: capi.maxpool_fwd(x, 3, 2, 1), 4 * ne + 12 * (ne // 4)),
             "sgd_momentum": (lambda: capi.sgd(params, grads, ms_, 0.1, momentum=0.9, weight_decay=1e-4), 20 * npar),
             "adamw": (lambda: capi.adam(params, grads, ms_, vs_, steps, 1e-3, weight_decay=0.01, decoupled=True), 28 * npar),

@@ -49,6 +49,7 @@ constexpr long long WAIT_BUDGET_CLOCKS = 2000000000ll;  // ~1 s at B200 clocks
 constexpr int FLEX_SPLIT_KBLOCKS = 8;  // from this many k-blocks per tile on, warps 6..9 split operands instead of storing tiles
 constexpr int BNSTATS_MIN_KBLOCKS = 16;            // epilogue statistics: from this reduction length on ...
 constexpr int64_t BNSTATS_SMALL_OUTPUT = 32 << 20;  // ... or when the output has at most this many elements
+constexpr int PAIR_MIN_KBLOCKS = 8;   // CTA pairs from this reduction length on (measured: +2..6 % from 8 k-blocks, -6..9 % at 2..4)
 constexpr int ACC1_MAX_KBLOCKS = 36;  // single-accumulator 128 x 256 tiles up to K = 1152 (error below 1e-5 of the largest output)
 
 __device__ int g_tc_error = 0;  // first failure: 1 = mbarrier wait expired
@@ -66,23 +67,33 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
+// CLUSTER: acquire at cluster scope, for a barrier that threads of the other CTA of a pair arrive on
+template <bool CLUSTER = false>
 __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
   uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
+  if constexpr (CLUSTER)
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+  else
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
   return ok != 0;
 }
 // Bounded wait. Returns false when the budget expired or another role already gave up.
+template <bool CLUSTER = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try(bar, parity)) return true;
+  if (mbar_try<CLUSTER>(bar, parity)) return true;
   const long long t0 = clock64();
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < 256; i++)
-      if (mbar_try(bar, parity)) return true;
+      if (mbar_try<CLUSTER>(bar, parity)) return true;
     if (*abort_flag) return false;
     if (clock64() - t0 > WAIT_BUDGET_CLOCKS) {
       *abort_flag = 1;
@@ -123,6 +134,53 @@ __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t desc_a, uint
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
+}
+// ---- CTA pairs (cta_group::2): two CTAs of a cluster, on the two SMs of a TPC, run one MMA of 256 rows. Each holds its own 128
+// rows of A and HALF of the B tile in shared memory, its own 128 x N accumulator in TMEM; CTA rank 0 issues for both. ----
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_id_x() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%clusterid.x;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_count_x() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%nclusterid.x;" : "=r"(r));
+  return r;
+}
+// the shared::cluster address of `addr` (a shared::cta address of this CTA's layout) in the CTA of rank `rank`
+__device__ __forceinline__ uint32_t mapa_rank(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {  // release at cluster scope: a barrier in either CTA of the pair
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {  // every thread of both CTAs
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// B tile rows of this CTA; the bytes are counted on the barrier `cluster_bar` of CTA rank 0
+__device__ __forceinline__ void tma_tile_3d_pair(uint32_t dst, const CUtensorMap* map, uint32_t cluster_bar, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+               ::"r"(dst), "l"(map), "r"(cluster_bar), "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
+__device__ __forceinline__ void umma_tf32_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrives on the barrier at this offset in BOTH CTAs of the pair once the MMAs issued so far have completed
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar), "h"((uint16_t)3)
+               : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -181,9 +239,9 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
   d |= (uint64_t)2 << 61;                        // SWIZZLE_128B
   return d;
 }
-constexpr uint32_t idesc_tf32(int n, bool mn_major = false) {
+constexpr uint32_t idesc_tf32(int n, bool mn_major = false, int m = BM) {  // m = 256: the rows of both CTAs of a pair
   return (1u << 4) /* D = f32 */ | (2u << 7) /* A = tf32 */ | (2u << 10) /* B = tf32 */ | (mn_major ? (3u << 15) : 0u) /* A, B majors */ |
-         ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+         ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 // MN-major tf32 operand. The only shared-memory layout the tensor core accepts for it is "128B swizzle with 32-byte
 // atomicity": 128-byte rows (32 floats along M/N) for consecutive k, 32-byte granules XOR-ed with the row index modulo 4, so
@@ -256,18 +314,20 @@ static_assert(sizeof(TcArgs) == 128, "TcArgs is a kernel parameter whose size is
 // k-step instead of once, which costs accuracy in proportion to the reduction length (measured 1.6e-5 of the largest output at
 // K = 2304 against 5.7e-6), so it is used only for 128 x 256 tiles with short reductions: there the pair fills TMEM, the
 // epilogue cannot overlap the next tile's main loop, and with a short main loop that exposed epilogue is a large share.
-template <int BN, bool ACC1 = false>
+// PAIR: the CTA is one of a cta_group::2 pair and stages only its half of the B tile (BN / 2 weight rows), which leaves room
+// for a third stage at BN = 256.
+template <int BN, bool ACC1 = false, bool PAIR = false>
 struct Smem {
-  static constexpr int STAGES = BN == 256 ? 2 : (BN == 128 ? 3 : 4);
+  static constexpr int STAGES = PAIR ? 3 : (BN == 256 ? 2 : (BN == 128 ? 3 : 4));
   static constexpr int ACC_COLS = ACC1 ? BN : 2 * BN;          // TMEM columns of one tile's accumulator(s)
   static constexpr int ACC_BUFS = ACC_COLS == 512 ? 1 : 2;     // tiles in flight in TMEM (512 columns in total at most)
   static constexpr int TMEM_COLS = ACC_BUFS * ACC_COLS;        // 256 or 512: a power of two
-  static constexpr int A_BYTES = BM * 128, B_BYTES = BN * 128;
+  static constexpr int A_BYTES = BM * 128, B_BYTES = (PAIR ? BN / 2 : BN) * 128;
   static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
   static constexpr int EPI_OFF = STAGES * STAGE_BYTES;          // per epilogue warp one 32-row x 128-byte store buffer
   static constexpr int EPI_BYTES = 8 * 4096;
   static constexpr int BAR_OFF = EPI_OFF + EPI_BYTES;
-  static constexpr int NBARS = 3 * STAGES + 2 * ACC_BUFS;
+  static constexpr int NBARS = 3 * STAGES + 2 * ACC_BUFS + (PAIR ? STAGES : 0);  // a pair has separate "A loaded" / "B loaded" barriers
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;  // barriers + alignment slack
 };
 
@@ -298,11 +358,23 @@ __device__ __forceinline__ TileCoord decode_tile(const TcArgs& g, int t, int n_t
   return c;
 }
 
-template <int BN, bool SPLITK, bool ACC1 = false>
+// PAIR (launched as clusters of two CTAs; the host picks it for an even number of row tiles): the pair works on row tiles 2p
+// and 2p + 1 of the same 256 columns with ONE stream of tcgen05.mma.cta_group::2 instructions (M = 256) that CTA rank 0
+// issues. Each CTA loads and splits its own A rows and loads half of the B tile, so per k-block a CTA moves 176 KB through
+// shared memory instead of 256 KB -- the shared-memory bandwidth, not the tensor pipe, bounds the single-CTA kernel. Who
+// signals what:
+//   A loaded [s]   own CTA, by its TMA                        -> own split warps
+//   B loaded [s]   rank 0's barrier, by both CTAs' TMA        -> rank 0's MMA thread
+//   split    [s]   rank 0's barrier, split warps of both CTAs -> rank 0's MMA thread (also covers "A loaded" of both CTAs)
+//   free     [s]   both CTAs (multicast commit)               -> own producer
+//   acc full [b]   both CTAs (multicast commit)               -> own epilogue warps
+//   acc empty[b]   rank 0's barrier, epilogue warps of both   -> rank 0's MMA thread
+template <int BN, bool SPLITK, bool ACC1 = false, bool PAIR = false>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_y,
                const TcArgs g) {
-  using S = Smem<BN, ACC1>;
+  static_assert(!PAIR || (BN == 256 && !SPLITK), "CTA pairs: 256-column tiles, unsplit reduction");
+  using S = Smem<BN, ACC1, PAIR>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const uint32_t smem_base = smem_u32(smem);
@@ -311,6 +383,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const uint32_t bar0 = smem_u32(bars);
   auto BAR = [&](int i) { return bar0 + 8u * i; };
   constexpr int ACC_FULL = 3 * S::STAGES, ACC_EMPTY = 3 * S::STAGES + S::ACC_BUFS;
+  constexpr int B_LOADED = 3 * S::STAGES + 2 * S::ACC_BUFS;  // PAIR only; BAR(s) is then "A loaded"
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+  // a barrier of CTA rank 0 as both CTAs of a pair address it
+  auto LEADER = [&](int i) { return PAIR ? mapa_rank(BAR(i), 0u) : BAR(i); };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + S::NBARS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + S::NBARS + 1);
 
@@ -328,6 +404,14 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   // GEMM row tiles: 128-pixel runs, or in window mode the rectangles of every image (M = images x oh x ow there)
   const int m_tiles = win_w ? (g.M / (g.oh * g.ow)) * g.tiles_x * g.tiles_y : (g.M + BM - 1) / BM;
   const int total_tiles = m_tiles * n_tiles * splits;
+  // the CTA's (or the pair's) walk over the tiles: work item i of `work_items`, `work_step` apart, is this CTA's tile tile_of(i)
+  const int work_items = PAIR ? (m_tiles / 2) * n_tiles : total_tiles;
+  const int work_first = PAIR ? (int)cluster_id_x() : (int)blockIdx.x, work_step = PAIR ? (int)cluster_count_x() : (int)gridDim.x;
+  auto tile_of = [n_tiles, rank](int i) -> int {
+    if constexpr (!PAIR) return i;
+    const int mp = i / n_tiles;
+    return (2 * mp + (int)rank) * n_tiles + (i - mp * n_tiles);
+  };
   // k-block range of split sp: [sp * kblocks / splits, (sp + 1) * kblocks / splits)
   auto kb_begin = [kblocks, splits](int t) -> int {
     if constexpr (!SPLITK) return 0;
@@ -343,26 +427,36 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   // one the tile's time goes to storing it, so they run the epilogue (4 split warps, 8 epilogue warps).
   const int split_warps = kblocks / splits >= FLEX_SPLIT_KBLOCKS ? 8 : 4;
   if (threadIdx.x == 0) {
+    constexpr int ctas = PAIR ? 2 : 1;  // arrivals from both CTAs meet on rank 0's barriers
     for (int s = 0; s < S::STAGES; s++) {
       mbar_init(BAR(s), 1);                    // loaded: one arrive.expect_tx + TMA bytes
-      mbar_init(BAR(S::STAGES + s), split_warps);  // split: one arrival per split warp
+      mbar_init(BAR(S::STAGES + s), ctas * split_warps);  // split: one arrival per split warp
       mbar_init(BAR(2 * S::STAGES + s), 1);    // free: tcgen05.commit
+      if constexpr (PAIR) mbar_init(BAR(B_LOADED + s), 1);
     }
     for (int b = 0; b < S::ACC_BUFS; b++) {
       mbar_init(BAR(ACC_FULL + b), 1);         // tcgen05.commit after the tile's last MMA
-      mbar_init(BAR(ACC_EMPTY + b), 12 - split_warps);  // one arrival per epilogue warp
+      mbar_init(BAR(ACC_EMPTY + b), ctas * (12 - split_warps));  // one arrival per epilogue warp
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {  // TMEM: per buffer two accumulators of BN fp32 columns (main sum, cross terms)
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)),
-                 "r"((uint32_t)S::TMEM_COLS)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if constexpr (PAIR) {  // the same warp of both CTAs, the same columns in both
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)),
+                   "r"((uint32_t)S::TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)),
+                   "r"((uint32_t)S::TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();  // the other CTA's barriers are initialised before anything here signals them
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
 
@@ -371,7 +465,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (lane == 0) {
       int it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (int i = work_first; i < work_items && ok; i += work_step) {
+        const int t = tile_of(i);
         const TileCoord c = decode_tile(g, t, n_tiles, BN, splits, win_w);
         const int w0 = c.ox0 * g.stride + g.low_w, h0 = c.oy0 * g.stride + g.low_h;
         for (int kb = kb_begin(t), kbe = kb_end(t); kb < kbe; kb++, it++) {
@@ -380,6 +475,17 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           const int tap = kb / g.cblocks, cb = kb - tap * g.cblocks;
           const int ky = tap / g.kw, kx = tap - ky * g.kw;
           const uint32_t stage = smem_base + s * S::STAGE_BYTES;
+          if constexpr (PAIR) {
+            // rank 0 announces the B bytes of both CTAs; the other CTA's copies may land first (the count goes negative until then)
+            if (rank == 0) mbar_expect_tx(BAR(B_LOADED + s), 4 * S::B_BYTES);
+            mbar_expect_tx(BAR(s), S::A_BYTES);
+            tma_im2col_4d(stage, &map_a, BAR(s), cb * BKF, w0, h0, c.img0, (uint16_t)kx, (uint16_t)ky);
+            const uint32_t bbar = LEADER(B_LOADED + s);
+            const int row0 = c.n0 + (int)rank * (BN / 2);  // this CTA's half of the weight rows
+            tma_tile_3d_pair(stage + 2 * S::A_BYTES, &map_w, bbar, (tap * g.cblocks + cb) * BKF, row0, 0);
+            tma_tile_3d_pair(stage + 2 * S::A_BYTES + S::B_BYTES, &map_w, bbar, (tap * g.cblocks + cb) * BKF, row0, 1);
+            continue;
+          }
           mbar_expect_tx(BAR(s), S::A_BYTES + 2 * S::B_BYTES);
           if (win_w) tma_tile_4d(stage, &map_a, BAR(s), cb * BKF, c.ox0, h0 + ky, c.img0);  // kw == 1: tap = filter row
           else tma_im2col_4d(stage, &map_a, BAR(s), cb * BKF, w0, h0, c.img0, (uint16_t)kx, (uint16_t)ky);
@@ -396,18 +502,32 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           const long long t0 = clock64();
           while (!mbar_try(BAR(k % S::STAGES), (k / S::STAGES) & 1) && clock64() - t0 < WAIT_BUDGET_CLOCKS) {}
         }
+      } else if (PAIR) {
+        // the last stages' "free" arrivals come from the other SM's commit: let them land in this CTA's barriers before it exits
+        for (int k = max(0, it - S::STAGES); k < it; k++)
+          if (!mbar_wait(BAR(2 * S::STAGES + k % S::STAGES), (k / S::STAGES) & 1, abort_flag)) break;
       }
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0) {
-      constexpr uint32_t idesc = idesc_tf32(BN);
+    if (lane == 0 && rank == 0) {  // (of a pair, only CTA rank 0 issues: its instructions drive both SMs' tensor cores)
+      constexpr uint32_t idesc = idesc_tf32(BN, false, PAIR ? 2 * BM : BM);
+      // one instruction stream for both forms: `mma` multiplies 128 (or, for a pair, 256) rows of A by the BN columns of B
+      auto mma = [](uint32_t d, uint64_t da, uint64_t db, uint32_t id, uint32_t accumulate) {
+        if constexpr (PAIR) umma_tf32_pair(d, da, db, id, accumulate);
+        else umma_tf32(d, da, db, id, accumulate);
+      };
+      auto commit = [](uint32_t bar) {
+        if constexpr (PAIR) umma_commit_pair(bar);
+        else umma_commit(bar);
+      };
       int it = 0, tl = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, tl++) {
+      for (int i = work_first; i < work_items && ok; i += work_step, tl++) {
+        const int t = tile_of(i);
         const int b = tl % S::ACC_BUFS, use = tl / S::ACC_BUFS;
         if (use > 0) {  // the epilogue must have drained this accumulator pair
-          ok = mbar_wait(BAR(ACC_EMPTY + b), (use - 1) & 1, abort_flag);
+          ok = mbar_wait<PAIR>(BAR(ACC_EMPTY + b), (use - 1) & 1, abort_flag);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         }
@@ -416,7 +536,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int kb0 = kb_begin(t);
         for (int kb = kb0, kbe = kb_end(t); kb < kbe; kb++, it++) {
           const int s = it % S::STAGES, round = it / S::STAGES;
-          ok = mbar_wait(BAR(S::STAGES + s), round & 1, abort_flag) && mbar_wait(BAR(s), round & 1, abort_flag);
+          // (for a pair "split" also stands for "A loaded" in both CTAs: the split warps waited for it before they arrived)
+          ok = mbar_wait<PAIR>(BAR(S::STAGES + s), round & 1, abort_flag) && mbar_wait(BAR(PAIR ? B_LOADED + s : s), round & 1, abort_flag);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t stage = smem_base + s * S::STAGE_BYTES;
@@ -437,14 +558,14 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               umma_tf32(acc, a_hi + adv, b_hi + adv, idesc_wide, accumulate);
               umma_tf32(cross, a_lo + adv, b_hi + adv, idesc, 1u);
             } else {
-              umma_tf32(cross, a_lo + adv, b_hi + adv, idesc, accumulate);
-              umma_tf32(cross, a_hi + adv, b_lo + adv, idesc, 1u);
-              umma_tf32(acc, a_hi + adv, b_hi + adv, idesc, ACC1 ? 1u : accumulate);
+              mma(cross, a_lo + adv, b_hi + adv, idesc, accumulate);
+              mma(cross, a_hi + adv, b_lo + adv, idesc, 1u);
+              mma(acc, a_hi + adv, b_hi + adv, idesc, ACC1 ? 1u : accumulate);
             }
           }
-          umma_commit(BAR(2 * S::STAGES + s));  // stage is free once these MMAs have read it
+          commit(BAR(2 * S::STAGES + s));  // stage is free once these MMAs have read it
         }
-        if (ok) umma_commit(BAR(ACC_FULL + b));  // this tile's accumulators are complete
+        if (ok) commit(BAR(ACC_FULL + b));  // this tile's accumulators are complete
       }
     }
   } else if (warp < 2 + split_warps) {
@@ -452,7 +573,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int t4 = threadIdx.x - 64, split_threads = split_warps * 32;  // 0..127 or 0..255
     int it = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+    for (int i = work_first; i < work_items && ok; i += work_step) {
+      const int t = tile_of(i);
       for (int kb = kb_begin(t), kbe = kb_end(t); kb < kbe; kb++, it++) {
         const int s = it % S::STAGES, round = it / S::STAGES;
         ok = mbar_wait(BAR(s), round & 1, abort_flag);
@@ -471,7 +593,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the tensor core
         __syncwarp();
-        if (lane == 0) mbar_arrive(BAR(S::STAGES + s));
+        if (lane == 0) {
+          if constexpr (PAIR) mbar_arrive_cluster(LEADER(S::STAGES + s));
+          else mbar_arrive(BAR(S::STAGES + s));
+        }
       }
     }
   } else {
@@ -486,7 +611,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint8_t* buf = smem + S::EPI_OFF + (warp - 6) * 4096;
     int tl = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, tl++) {
+    for (int i = work_first; i < work_items && ok; i += work_step, tl++) {
+      const int t = tile_of(i);
       const int b = tl % S::ACC_BUFS, use = tl / S::ACC_BUFS;
       ok = mbar_wait(BAR(ACC_FULL + b), use & 1, abort_flag);
       if (!ok) break;
@@ -606,15 +732,20 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       // hand the accumulator pair back to the MMA warp
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
-      if (lane == 0) mbar_arrive(BAR(ACC_EMPTY + b));
+      if (lane == 0) {
+        if constexpr (PAIR) mbar_arrive_cluster(LEADER(ACC_EMPTY + b));
+        else mbar_arrive(BAR(ACC_EMPTY + b));
+      }
     }
     if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // every box this warp stored has been written
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();  // neither CTA leaves (or frees TMEM) while the other may still signal it or read its tiles
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)S::TMEM_COLS) : "memory");
+    if constexpr (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)S::TMEM_COLS) : "memory");
+    else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)S::TMEM_COLS) : "memory");
   }
 }
 
@@ -691,9 +822,8 @@ struct TcProblem {  // a convolution of a channels-last activation `a` [n, ih, i
 int pick_bn(const TcProblem& p) {
   if (p.rows <= 64) return 64;
   if (p.rows <= 128) return 128;
-  // a short reduction leaves the 128x256 tile's epilogue exposed (its accumulators fill TMEM, so nothing overlaps it);
-  // 128x128 tiles double-buffer the accumulators and hide it
-  if (p.kh * p.kw * (int)cdiv(p.c, BKF) < 6) return 128;
+  // (128 x 256 tiles with a short reduction use one accumulator per tile and two TMEM buffers, so their epilogue overlaps the
+  // next tile like that of the 128 x 128 tiles, and A is read half as often: measured 0.344 -> 0.295 ms on 64 -> 256 1x1 at 56^2)
   int64_t mt = cdiv((int64_t)p.n * p.oh * p.ow, BM);
   return (mt * cdiv(p.rows, 256) >= sm_count()) ? 256 : 128;
 }
@@ -728,10 +858,58 @@ bool dense_out(const TcArgs& a) {
          y.sn == (int64_t)a.oh * a.ow * a.N && a.N % 4 == 0 && (reinterpret_cast<uintptr_t>(y.p) & 15) == 0;
 }
 
+// CTA pairs are used unless OMARCHY_MAC_TORCH_CTA_PAIRS=0 (read once)
+static bool cta_pairs_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("OMARCHY_MAC_TORCH_CTA_PAIRS");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+// clusters of two CTAs of the pair kernel that can be resident at once (0: the launch form is not available), once per instantiation
+template <bool ACC1>
+static int pair_clusters() {
+  using SP = Smem<256, ACC1, true>;
+  static std::once_flag once;
+  static int clusters = 0;
+  std::call_once(once, [] {
+    auto kernel = conv_tc_kernel<256, false, ACC1, true>;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SP::TOTAL) != cudaSuccess) { cudaGetLastError(); return; }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)(sm_count() & ~1)); cfg.blockDim = dim3(TC_THREADS); cfg.dynamicSmemBytes = SP::TOTAL;
+    cudaLaunchAttribute at{};
+    at.id = cudaLaunchAttributeClusterDimension;
+    at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
+    cfg.attrs = &at; cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) { cudaGetLastError(); return; }
+    clusters = std::min(n, sm_count() / 2);
+  });
+  return clusters;
+}
+template <bool ACC1>
+static int launch_pair(const CUtensorMap& map_a, const CUtensorMap& map_w, const CUtensorMap& map_y, const TcArgs& a, int clusters, cudaStream_t s) {
+  using SP = Smem<256, ACC1, true>;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(2u * (unsigned)clusters); cfg.blockDim = dim3(TC_THREADS); cfg.dynamicSmemBytes = SP::TOTAL; cfg.stream = s;
+  cudaLaunchAttribute at{};
+  at.id = cudaLaunchAttributeClusterDimension;
+  at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
+  cfg.attrs = &at; cfg.numAttrs = 1;
+  OMT_CUDA(cudaLaunchKernelEx(&cfg, conv_tc_kernel<256, false, ACC1, true>, map_a, map_w, map_y, a));
+  return check_launch(ACC1 ? "conv_tc_256x256_pair_acc1" : "conv_tc_256x256_pair");
+}
+
 template <int BN>
 int launch_tc(const TcProblem& p, const float* wsplit, const TcArgs& args, int splits, float* part, cudaStream_t s) {
   using S = Smem<BN>;
   alignas(64) CUtensorMap map_a, map_w;
+  // 128 x 256 tiles with a short reduction: one accumulator per tile, so that two tiles fit TMEM and the epilogue overlaps
+  const bool acc1 = BN == 256 && splits == 1 && p.kh * p.kw * args.cblocks <= ACC1_MAX_KBLOCKS && !(args.flags & OMT_PRECISE_ACCUM);
+  // two CTAs per 256 x 256 tile pair when the row tiles pair up (each CTA then stages half of the weight tile)
+  int clusters = 0;
+  if (BN == 256 && splits == 1 && cdiv(args.M, BM) % 2 == 0 && p.kh * p.kw * args.cblocks >= PAIR_MIN_KBLOCKS && cta_pairs_enabled()) clusters = acc1 ? pair_clusters<true>() : pair_clusters<false>();
+  const bool pair = clusters > 0;
   {
     cuuint64_t dims[4] = {(cuuint64_t)p.c, (cuuint64_t)p.iw, (cuuint64_t)p.ih, (cuuint64_t)p.n};
     cuuint64_t strides[3] = {(cuuint64_t)p.c * 4, (cuuint64_t)p.iw * p.c * 4, (cuuint64_t)p.ih * p.iw * p.c * 4};
@@ -751,7 +929,7 @@ int launch_tc(const TcProblem& p, const float* wsplit, const TcArgs& args, int s
     const int kp = p.kh * p.kw * args.cblocks * BKF;
     cuuint64_t dims[3] = {(cuuint64_t)kp, (cuuint64_t)p.rows, 2};
     cuuint64_t strides[2] = {(cuuint64_t)kp * 4, (cuuint64_t)kp * 4 * p.rows};
-    cuuint32_t box[3] = {BKF, (cuuint32_t)BN, 1}, estr[3] = {1, 1, 1};
+    cuuint32_t box[3] = {BKF, (cuuint32_t)(pair ? BN / 2 : BN), 1}, estr[3] = {1, 1, 1};
     CUresult r = g_encode_tiled(&map_w, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)wsplit, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
@@ -788,8 +966,10 @@ int launch_tc(const TcProblem& p, const float* wsplit, const TcArgs& args, int s
   OMT_REQUIRE(!(a.flags & OMT_EPI_BNSTATS) || a.store_mode == 1, "OMT_EPI_BNSTATS needs a dense channels-last output and an unsplit reduction");
   const int m_tiles = (int)cdiv(a.M, BM), n_tiles = (int)cdiv(a.N, BN);
   const unsigned grid = (unsigned)std::min<int64_t>((int64_t)m_tiles * n_tiles * splits, sm_count());
-  // 128 x 256 tiles with a short reduction: one accumulator per tile, so that two tiles fit TMEM and the epilogue overlaps
-  const bool acc1 = BN == 256 && splits == 1 && p.kh * p.kw * a.cblocks <= ACC1_MAX_KBLOCKS && !(a.flags & OMT_PRECISE_ACCUM);
+  if (pair) {
+    const int work = (m_tiles / 2) * n_tiles;
+    return acc1 ? launch_pair<true>(map_a, map_w, map_y, a, std::min(work, clusters), s) : launch_pair<false>(map_a, map_w, map_y, a, std::min(work, clusters), s);
+  }
   if (splits > 1) conv_tc_kernel<BN, true><<<grid, TC_THREADS, S::TOTAL, s>>>(map_a, map_w, map_y, a);
   else if (acc1) conv_tc_kernel<BN, false, BN == 256><<<grid, TC_THREADS, S::TOTAL, s>>>(map_a, map_w, map_y, a);
   else conv_tc_kernel<BN, false><<<grid, TC_THREADS, S::TOTAL, s>>>(map_a, map_w, map_y, a);
