@@ -6,6 +6,8 @@
 // Semantics: reference dw_fwd/dw_gin/dw_gwt (stride 1, "same" padding) and dwg_fwd/dwg_gin/dwg_gwt (general) in
 // csrc/kernels/, dispatched from csrc/conv.cpp:194-229. One code path covers both families here.
 #include <algorithm>
+#include <mutex>
+#include <type_traits>
 
 #include "common.cuh"
 
@@ -391,6 +393,418 @@ __global__ void __launch_bounds__(256) dw_wgrad_fin_kernel(const float* __restri
   if (lane == 0) out[i] = s * scale;
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// Rolling kernels (channels-last, dense, 16-byte aligned, ks in {3, 5, 7}, stride 1 or 2). A thread owns a strip of TX
+// output columns and `seg_rows` output rows for CH channels and walks DOWN the strip's input rows once: each input row is
+// loaded once and feeds the R = ceil(ks / stride) output rows it overlaps, whose partial sums wait in registers. Against
+// one output row per thread (dw_rows_nhwc4_kernel) that cuts the loads per output pixel from ks * span / TX to span / TX:
+// the 5x5 kernels were bound by L1 traffic (65 bytes per output element), not by HBM.
+//   CH = 4 (128-bit accesses) for 3x3, whose nine weights also stay in registers; CH = 2 (64-bit) for 5x5 and 7x7, where the
+//   R x TX partial sums of four channels would not fit.
+// ---------------------------------------------------------------------------------------------------------------------
+template <int CH>
+struct Vec {
+  float v[CH];
+};
+template <int CH>
+__device__ __forceinline__ Vec<CH> ldv(const float* p) {
+  Vec<CH> r;
+  if constexpr (CH == 4) {
+    const float4 t = __ldg(reinterpret_cast<const float4*>(p));
+    r.v[0] = t.x; r.v[1] = t.y; r.v[2] = t.z; r.v[3] = t.w;
+  } else {
+    const float2 t = __ldg(reinterpret_cast<const float2*>(p));
+    r.v[0] = t.x; r.v[1] = t.y;
+  }
+  return r;
+}
+template <int CH>
+__device__ __forceinline__ void stv(float* p, const Vec<CH>& r) {
+  if constexpr (CH == 4) *reinterpret_cast<float4*>(p) = make_float4(r.v[0], r.v[1], r.v[2], r.v[3]);
+  else *reinterpret_cast<float2*>(p) = make_float2(r.v[0], r.v[1]);
+}
+template <int CH>
+__device__ __forceinline__ Vec<CH> zerov() {
+  Vec<CH> r;
+#pragma unroll
+  for (int k = 0; k < CH; k++) r.v[k] = 0.f;
+  return r;
+}
+template <int CH>
+__device__ __forceinline__ void fmav(Vec<CH>& acc, const Vec<CH>& a, const Vec<CH>& b) {
+#pragma unroll
+  for (int k = 0; k < CH; k++) acc.v[k] = fmaf(a.v[k], b.v[k], acc.v[k]);
+}
+// two channels: one packed multiply-add (fma.rn.f32x2, the two-lane FP32 instruction of sm_100): same rounding per lane
+template <>
+__device__ __forceinline__ void fmav<2>(Vec<2>& acc, const Vec<2>& a, const Vec<2>& b) {
+  asm("{\n\t.reg .b64 ra, rb, rc;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%0, %1};\n\t"
+      "fma.rn.f32x2 rc, ra, rb, rc;\n\tmov.b64 {%0, %1}, rc;\n\t}"
+      : "+f"(acc.v[0]), "+f"(acc.v[1])
+      : "f"(a.v[0]), "f"(a.v[1]), "f"(b.v[0]), "f"(b.v[1]));
+}
+__host__ __device__ constexpr int floor_div(int a, int b) { return a >= 0 ? a / b : -((-a + b - 1) / b); }
+__host__ __device__ constexpr int pos_mod(int a, int b) { return ((a % b) + b) % b; }
+
+// one row of SPAN input pixels starting at column x0 (zero outside the image)
+template <int CH, int SPAN>
+__device__ __forceinline__ void load_span(Vec<CH> (&in)[SPAN], const float* __restrict__ row, int x0, int iw, int c, bool interior) {
+  if (interior) {
+#pragma unroll
+    for (int k = 0; k < SPAN; k++) in[k] = ldv<CH>(row + (int64_t)k * c);
+  } else {
+#pragma unroll
+    for (int k = 0; k < SPAN; k++) in[k] = (x0 + k >= 0 && x0 + k < iw) ? ldv<CH>(row + (int64_t)k * c) : zerov<CH>();
+  }
+}
+
+// Input rows reach the rolling kernels through a private ring in shared memory, filled by cp.async DEPTH rows ahead of their
+// use: the copies hold no registers while in flight, so a thread keeps (DEPTH - 1) * SPAN vectors travelling at 8-12 warps per
+// SM (with plain loads and one row in flight these kernels sat at 42 % of the DRAM bandwidth, stalled on the scoreboard).
+// Layout [slot][k][thread]: consecutive threads, consecutive vectors; nobody else touches a thread's slots, so no block barrier.
+constexpr int ROLL_THREADS = 128, ROLL_DEPTH = 4;
+template <int CH>
+__device__ __forceinline__ void cp_async_vec(uint32_t dst, const float* src, bool valid) {  // !valid: zeros are written
+  const uint32_t n = valid ? CH * 4 : 0;
+  if constexpr (CH == 4) asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+  else asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+template <int CH, int SPAN>
+struct RowRing {
+  uint32_t base;  // shared-memory address of this thread's vector in slot 0, k = 0
+  __device__ __forceinline__ uint32_t at(int slot, int k) const { return base + (uint32_t)((slot * SPAN + k) * ROLL_THREADS * CH * 4); }
+  // request row `r` (pointer to its pixel x0; pixels outside [0, iw) become zeros; `safe` always points inside the tensor)
+  __device__ __forceinline__ void request(int r, bool row_valid, const float* row, const float* safe, int x0, int iw, int c) const {
+    if (row_valid) {
+      const int slot = r % ROLL_DEPTH;
+#pragma unroll
+      for (int k = 0; k < SPAN; k++) {
+        const bool in = x0 + k >= 0 && x0 + k < iw;
+        cp_async_vec<CH>(at(slot, k), in ? row + (int64_t)k * c : safe, in);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");  // (an empty group when the row lies outside the image: the count stays uniform)
+  }
+  __device__ __forceinline__ void wait_oldest() const { asm volatile("cp.async.wait_group %0;" ::"n"(ROLL_DEPTH - 1) : "memory"); }
+  __device__ __forceinline__ void read(int r, Vec<CH> (&in)[SPAN]) const {
+    const int slot = r % ROLL_DEPTH;
+#pragma unroll
+    for (int k = 0; k < SPAN; k++) {
+      if constexpr (CH == 4) {
+        float4 t;
+        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(t.x), "=f"(t.y), "=f"(t.z), "=f"(t.w) : "r"(at(slot, k)) : "memory");
+        in[k].v[0] = t.x; in[k].v[1] = t.y; in[k].v[2] = t.z; in[k].v[3] = t.w;
+      } else {
+        float2 t;
+        asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(t.x), "=f"(t.y) : "r"(at(slot, k)) : "memory");
+        in[k].v[0] = t.x; in[k].v[1] = t.y;
+      }
+    }
+  }
+};
+template <int CH, int SPAN>
+constexpr size_t ring_bytes() { return (size_t)ROLL_DEPTH * SPAN * ROLL_THREADS * CH * 4; }
+
+// Forward (FLIP = false) and stride-1 input gradient (FLIP = true: taps mirrored, pad = ks-1-pad, the caller swaps the tensors).
+template <int KS, int S, bool FLIP, int TX, int CH, bool WREG>
+__global__ void __launch_bounds__(ROLL_THREADS) dw_roll_kernel(DwArgs a, const float* __restrict__ wt, int seg_rows, int segs) {
+  constexpr int SPAN = (TX - 1) * S + KS, R = (KS + S - 1) / S, U = R * S;
+  extern __shared__ __align__(16) uint8_t ring_raw[];
+  const int cqn = a.c / CH, gx = (a.ow + TX - 1) / TX;
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (int64_t)a.n * segs * gx * cqn) return;
+  int img, cq, seg, xg;
+  decode<true>(i, cqn, segs, gx, img, cq, seg, xg);
+  const int ch = cq * CH, ox0 = xg * TX;
+  const int oy_begin = seg * seg_rows, nrows = min(seg_rows, a.oh - oy_begin);
+  const int sy0 = oy_begin * S - a.pad, x0 = ox0 * S - a.pad;
+  const int n_in = (nrows - 1) * S + KS;  // input rows the strip touches
+  // pointer to input pixel (sy0, x0) of this thread's channels; only dereferenced where that pixel exists
+  const float* xbase = a.x.p + (((int64_t)img * a.ih + sy0) * a.iw + x0) * a.c + ch;
+  const int64_t rs = (int64_t)a.iw * a.c;
+  const float* wq = wt + ch;
+  Vec<CH> wreg[WREG ? KS * KS : 1];
+  if constexpr (WREG) {
+#pragma unroll
+    for (int t = 0; t < KS * KS; t++) wreg[t] = ldv<CH>(wq + (FLIP ? KS * KS - 1 - t : t) * a.c);
+  }
+  Vec<CH> acc[R][TX];
+#pragma unroll
+  for (int q = 0; q < R; q++)
+#pragma unroll
+    for (int j = 0; j < TX; j++) acc[q][j] = zerov<CH>();
+  Vec<CH> b = zerov<CH>();
+  if (a.flags & OMT_EPI_BIAS) b = ldv<CH>(a.bias + ch);
+  const bool relu = a.flags & OMT_EPI_RELU;
+  float* ybase = a.y.p + (((int64_t)img * a.oh + oy_begin) * a.ow + ox0) * a.c + ch;
+  const RowRing<CH, SPAN> ring{(uint32_t)__cvta_generic_to_shared(ring_raw) + threadIdx.x * CH * 4};
+  auto row_valid = [&](int r) { return r < n_in && sy0 + r >= 0 && sy0 + r < a.ih; };
+  const float* safe = a.x.p + ch;
+#pragma unroll
+  for (int d = 0; d < ROLL_DEPTH; d++) ring.request(d, row_valid(d), xbase + d * rs, safe, x0, a.iw, a.c);
+  if constexpr (S == 1 && KS >= 5) {
+    // Large filters: the walk unrolled over its R-row period is tens of KB of code, and the kernel then waits for instructions
+    // (measured: 1.1 "no instruction" stalls per issue at 5x5). Here the loop body is ONE input row: acc[ky] holds the sums of
+    // the output row that this input row is filter row ky of, and the sums move up one place per row (R * TX moves against
+    // KS * KS * TX multiply-adds).
+#pragma unroll 1
+    for (int r = 0; r < n_in; r++) {
+      ring.wait_oldest();
+      const bool have = row_valid(r);
+      Vec<CH> in[SPAN];
+      if (have) ring.read(r, in);
+      ring.request(r + ROLL_DEPTH, row_valid(r + ROLL_DEPTH), xbase + (r + ROLL_DEPTH) * rs, safe, x0, a.iw, a.c);
+      if (have) {
+#pragma unroll
+        for (int ky = 0; ky < KS; ky++) {
+          const int q = r - ky;
+          if (q < 0 || q >= nrows) continue;
+#pragma unroll
+          for (int kx = 0; kx < KS; kx++) {
+            const int t = FLIP ? (KS - 1 - ky) * KS + (KS - 1 - kx) : ky * KS + kx;
+            const Vec<CH> wv = WREG ? wreg[ky * KS + kx] : ldv<CH>(wq + t * a.c);
+#pragma unroll
+            for (int j = 0; j < TX; j++) fmav<CH>(acc[ky][j], in[j + kx], wv);
+          }
+        }
+      }
+      const int q = r - (KS - 1);  // complete after this row
+      if (q >= 0 && q < nrows) {
+        float* yp = ybase + (int64_t)q * a.ow * a.c;
+#pragma unroll
+        for (int j = 0; j < TX; j++) {
+          if (ox0 + j < a.ow) {
+            Vec<CH> o;
+#pragma unroll
+            for (int k = 0; k < CH; k++) {
+              o.v[k] = acc[KS - 1][j].v[k] + b.v[k];
+              if (relu) o.v[k] = fmaxf(o.v[k], 0.f);
+            }
+            stv<CH>(yp + (int64_t)j * a.c, o);
+          }
+        }
+      }
+#pragma unroll
+      for (int ky = KS - 1; ky > 0; ky--)
+#pragma unroll
+        for (int j = 0; j < TX; j++) acc[ky][j] = acc[ky - 1][j];
+#pragma unroll
+      for (int j = 0; j < TX; j++) acc[0][j] = zerov<CH>();
+    }
+    return;
+  }
+  for (int base = 0; base < n_in; base += U) {
+    const int qb = base / S;  // output row (within the strip) whose first input row is `base`
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const int r = base + u;
+      if (r >= n_in) break;
+      ring.wait_oldest();
+      const bool have = row_valid(r);
+      Vec<CH> in[SPAN];
+      if (have) ring.read(r, in);
+      ring.request(r + ROLL_DEPTH, row_valid(r + ROLL_DEPTH), xbase + (r + ROLL_DEPTH) * rs, safe, x0, a.iw, a.c);  // into the slot just read
+      if (have) {
+#pragma unroll
+        for (int ky = 0; ky < KS; ky++) {
+          if (pos_mod(u - ky, S) != 0) continue;  // (known at compile time once u and ky are unrolled)
+          const int dq = floor_div(u - ky, S), slot = pos_mod(dq, R);
+          const int q = qb + dq;  // input row r is filter row ky of output row q
+          if (q < 0 || q >= nrows) continue;
+#pragma unroll
+          for (int kx = 0; kx < KS; kx++) {
+            const int t = FLIP ? (KS - 1 - ky) * KS + (KS - 1 - kx) : ky * KS + kx;
+            const Vec<CH> wv = WREG ? wreg[ky * KS + kx] : ldv<CH>(wq + t * a.c);
+#pragma unroll
+            for (int j = 0; j < TX; j++) fmav<CH>(acc[slot][j], in[j * S + kx], wv);
+          }
+        }
+      }
+      if (pos_mod(u - (KS - 1), S) == 0) {  // this was the last input row of an output row: store it, free its sums
+        const int dq = floor_div(u - (KS - 1), S), slot = pos_mod(dq, R);
+        const int q = qb + dq;
+        if (q >= 0 && q < nrows) {
+          float* yp = ybase + (int64_t)q * a.ow * a.c;
+#pragma unroll
+          for (int j = 0; j < TX; j++) {
+            if (ox0 + j < a.ow) {
+              Vec<CH> o;
+#pragma unroll
+              for (int k = 0; k < CH; k++) {
+                o.v[k] = acc[slot][j].v[k] + b.v[k];
+                if (relu) o.v[k] = fmaxf(o.v[k], 0.f);
+              }
+              stv<CH>(yp + (int64_t)j * a.c, o);
+            }
+            acc[slot][j] = zerov<CH>();
+          }
+        }
+      }
+    }
+  }
+}
+
+// Input gradient of a stride-2 convolution: dx(yy, xx) sums the taps with ky = (yy + pad) mod 2, kx = (xx + pad) mod 2 (mod 2),
+// gy pixel ((yy + pad - ky) / 2, (xx + pad - kx) / 2). A thread produces TX (even) consecutive pixels of one dx row: per
+// tap row it loads the G gy pixels they share once; which of them pixel j pairs with tap kx is known at compile time up to
+// the parity of the strip's first column, so no division or modulo is left per tap.
+template <int KS, int TX, int CH>
+__global__ void __launch_bounds__(256) dw_dgrad_s2_kernel(DwArgs a, const float* __restrict__ wt) {  // a.x = gy, a.y = dx
+  constexpr int HALF = (KS - 1) / 2, G = HALF + TX / 2 + 1;
+  const int cqn = a.c / CH, gx = (a.iw + TX - 1) / TX;
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (int64_t)a.n * a.ih * gx * cqn) return;
+  int img, cq, yy, xg;
+  decode<true>(i, cqn, a.ih, gx, img, cq, yy, xg);
+  const int ch = cq * CH, x0 = xg * TX;
+  const int e = x0 + a.pad, pe = e & 1, h = e >> 1, ey = yy + a.pad;
+  const int ox_base = h - HALF;
+  const float* gimg = a.x.p + (int64_t)img * a.oh * a.ow * a.c + ch;
+  const float* wq = wt + ch;
+  Vec<CH> acc[TX];
+#pragma unroll
+  for (int j = 0; j < TX; j++) acc[j] = zerov<CH>();
+  const bool interior = ox_base >= 0 && ox_base + G <= a.ow;
+  for (int ky = ey & 1; ky < KS; ky += 2) {
+    if (ey < ky) break;
+    const int oy = (ey - ky) >> 1;
+    if (oy >= a.oh) continue;
+    Vec<CH> g[G];
+    load_span<CH, G>(g, gimg + ((int64_t)oy * a.ow + ox_base) * a.c, ox_base, a.ow, a.c, interior);
+    const float* wr = wq + (int64_t)ky * KS * a.c;
+    auto taps = [&](auto parity) {
+      constexpr int PE = decltype(parity)::value;
+#pragma unroll
+      for (int j = 0; j < TX; j++) {
+#pragma unroll
+        for (int m = 0; m <= HALF; m++) {
+          const int kx = ((PE + j) & 1) + 2 * m;
+          if (kx >= KS) continue;
+          fmav<CH>(acc[j], g[HALF + ((PE + j) >> 1) - m], ldv<CH>(wr + kx * a.c));
+        }
+      }
+    };
+    if (pe) taps(std::integral_constant<int, 1>{});
+    else taps(std::integral_constant<int, 0>{});
+  }
+  float* yp = a.y.p + (((int64_t)img * a.ih + yy) * a.iw + x0) * a.c + ch;
+#pragma unroll
+  for (int j = 0; j < TX; j++)
+    if (x0 + j < a.iw) stv<CH>(yp + (int64_t)j * a.c, acc[j]);
+}
+
+// Weight gradient, rolling: a (channel group, pixel lane) thread walks strips of TX columns x seg_rows output rows; an input row
+// is loaded once and meets the R gy rows it overlaps (kept in registers), every tap's sum stays in registers for the
+// whole walk. Pixel lanes are summed through shared memory in a fixed order, slices (blockIdx.y) by dw_wgrad_fin_kernel.
+template <int KS, int S, int TX, int CH>
+__global__ void __launch_bounds__(ROLL_THREADS) dw_wgrad_roll_kernel(DwArgs a, int SL, int CL, int seg_rows, int segs, float* __restrict__ part) {
+  constexpr int SPAN = (TX - 1) * S + KS, R = (KS + S - 1) / S, U = R * S;
+  extern __shared__ __align__(16) uint8_t ring_raw[];  // the row ring; after the walk its start is reused as [PL][CL] vectors of CH floats
+  const int PL = blockDim.x / CL;
+  const int cl = threadIdx.x % CL, pl = threadIdx.x / CL;
+  const int cq = blockIdx.x * CL + cl, sl = blockIdx.y;
+  const bool live = pl < PL && cq < a.c / CH;
+  const int ch = cq * CH;
+  Vec<CH> acc[KS * KS];
+#pragma unroll
+  for (int t = 0; t < KS * KS; t++) acc[t] = zerov<CH>();
+  if (live) {
+    const uint32_t gx = (uint32_t)(a.ow + TX - 1) / TX;
+    const uint32_t items = (uint32_t)a.n * segs * gx;
+    const int64_t rs = (int64_t)a.iw * a.c;
+    const RowRing<CH, SPAN> ring{(uint32_t)__cvta_generic_to_shared(ring_raw) + threadIdx.x * CH * 4};
+    const float* safe = a.x.p + ch;
+    for (uint32_t it = (uint32_t)sl * PL + pl; it < items; it += (uint32_t)SL * PL) {
+      const uint32_t xg = it % gx, r_ = it / gx;
+      const int seg = (int)(r_ % (uint32_t)segs), img = (int)(r_ / (uint32_t)segs);
+      const int ox0 = (int)xg * TX, oy_begin = seg * seg_rows, nrows = min(seg_rows, a.oh - oy_begin);
+      const int sy0 = oy_begin * S - a.pad, x0 = ox0 * S - a.pad;
+      const int n_in = (nrows - 1) * S + KS;
+      const float* xbase = a.x.p + (((int64_t)img * a.ih + sy0) * a.iw + x0) * a.c + ch;
+      const float* gbase = a.y.p + (((int64_t)img * a.oh + oy_begin) * a.ow + ox0) * a.c + ch;
+      const bool gfull = ox0 + TX <= a.ow;
+      Vec<CH> g[R][TX];
+      auto row_valid = [&](int r) { return r < n_in && sy0 + r >= 0 && sy0 + r < a.ih; };
+#pragma unroll
+      for (int d = 0; d < ROLL_DEPTH; d++) ring.request(d, row_valid(d), xbase + d * rs, safe, x0, a.iw, a.c);
+      if constexpr (S == 1 && KS >= 5) {  // one input row per trip, g[ky] = the gy row this input row is filter row ky of (see dw_roll_kernel)
+#pragma unroll 1
+        for (int r = 0; r < n_in; r++) {
+#pragma unroll
+          for (int ky = KS - 1; ky > 0; ky--)
+#pragma unroll
+            for (int j = 0; j < TX; j++) g[ky][j] = g[ky - 1][j];
+          if (r < nrows) load_span<CH, TX>(g[0], gbase + (int64_t)r * a.ow * a.c, ox0, a.ow, a.c, gfull);
+          ring.wait_oldest();
+          const bool have = row_valid(r);
+          Vec<CH> in[SPAN];
+          if (have) ring.read(r, in);
+          ring.request(r + ROLL_DEPTH, row_valid(r + ROLL_DEPTH), xbase + (r + ROLL_DEPTH) * rs, safe, x0, a.iw, a.c);
+          if (!have) continue;
+#pragma unroll
+          for (int ky = 0; ky < KS; ky++) {
+            const int q = r - ky;
+            if (q < 0 || q >= nrows) continue;
+#pragma unroll
+            for (int kx = 0; kx < KS; kx++)
+#pragma unroll
+              for (int j = 0; j < TX; j++) fmav<CH>(acc[ky * KS + kx], g[ky][j], in[j + kx]);
+          }
+        }
+        continue;
+      }
+      for (int base = 0; base < n_in; base += U) {
+        const int qb = base / S;
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+          const int r = base + u;
+          if (r >= n_in) break;
+          if (u % S == 0) {  // the first input row of output row q: its gy pixels enter the ring
+            const int dq = u / S, slot = dq % R, q = qb + dq;
+            if (q < nrows) load_span<CH, TX>(g[slot], gbase + (int64_t)q * a.ow * a.c, ox0, a.ow, a.c, gfull);
+          }
+          ring.wait_oldest();
+          const bool have = row_valid(r);
+          Vec<CH> in[SPAN];
+          if (have) ring.read(r, in);
+          ring.request(r + ROLL_DEPTH, row_valid(r + ROLL_DEPTH), xbase + (r + ROLL_DEPTH) * rs, safe, x0, a.iw, a.c);
+          if (!have) continue;
+#pragma unroll
+          for (int ky = 0; ky < KS; ky++) {
+            if (pos_mod(u - ky, S) != 0) continue;
+            const int dq = floor_div(u - ky, S), slot = pos_mod(dq, R);
+            const int q = qb + dq;
+            if (q < 0 || q >= nrows) continue;
+#pragma unroll
+            for (int kx = 0; kx < KS; kx++)
+#pragma unroll
+              for (int j = 0; j < TX; j++) fmav<CH>(acc[ky * KS + kx], g[slot][j], in[j * S + kx]);
+          }
+        }
+      }
+    }
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");  // (only empty groups can be pending here)
+  Vec<CH>* red = reinterpret_cast<Vec<CH>*>(ring_raw);
+#pragma unroll
+  for (int t = 0; t < KS * KS; t++) {
+    __syncthreads();
+    if (pl < PL) red[pl * CL + cl] = acc[t];
+    __syncthreads();
+    if (pl == 0 && live) {
+      Vec<CH> s4 = red[cl];
+      for (int k = 1; k < PL; k++) {
+        const Vec<CH> v = red[k * CL + cl];
+#pragma unroll
+        for (int e = 0; e < CH; e++) s4.v[e] += v.v[e];
+      }
+      const int kk = KS * KS;
+#pragma unroll
+      for (int e = 0; e < CH; e++) part[((int64_t)(ch + e) * SL + sl) * kk + t] = s4.v[e];
+    }
+  }
+}
+
 static int check_geo(const OmtConvGeo* g, const char* who) {
   OMT_REQUIRE(g && g->groups == g->ci && g->ci == g->co && g->ci >= 1, "%s: depthwise needs groups == ci == co", who);
   OMT_REQUIRE(g->ks >= 1 && g->ks <= 11 && g->stride >= 1 && g->stride <= 4 && g->pad >= 0 && g->pad <= g->ks,
@@ -409,15 +823,49 @@ static DwArgs mk(const OmtConvGeo* g, const OmtAct* x, const OmtAct* y, const fl
 }
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 static bool rows_ok(const OmtConvGeo* g) { return (g->ks == 3 || g->ks == 5 || g->ks == 7) && (g->stride == 1 || g->stride == 2); }
+// strips of the rolling kernels: as tall as possible (a strip re-reads ks - stride input rows of its upper neighbour) while
+// the launch still has `want` work items; returns rows per strip, sets the strips per column
+static int strip_rows(int oh, int ks, int64_t items_per_seg, int64_t want, int& segs) {
+  const int64_t by_work = std::max<int64_t>(1, cdiv(want, std::max<int64_t>(1, items_per_seg)));
+  const int most = std::max(1, oh / std::min(oh, ks + 1));  // no strip shorter than ks + 1 rows (unless the image is)
+  const int rows = (int)cdiv(oh, std::min<int64_t>(by_work, most));
+  segs = (int)cdiv(oh, rows);
+  return rows;
+}
+// the rolling kernels' rings can exceed the 48 KB a kernel gets without asking; once per kernel
+template <auto Kernel>
+static void allow_shared_memory(size_t bytes) {
+  static std::once_flag once;
+  std::call_once(once, [bytes] {
+    if (cudaFuncSetAttribute(Kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) != cudaSuccess) cudaGetLastError();  // (the launch reports it)
+  });
+}
+template <int KS, int S, bool FLIP>
+static void launch_roll(const DwArgs& a, const float* wt, cudaStream_t s) {
+  constexpr int CH = KS == 3 ? 4 : 2, TX = 4, SPAN = (TX - 1) * S + KS;
+  constexpr bool WREG = KS <= 5;  // the filter in registers: no loads but the input rows inside the walk
+  const int64_t per_seg = (int64_t)a.n * cdiv(a.ow, TX) * (a.c / CH);
+  int segs;
+  const int rows = strip_rows(a.oh, KS, per_seg, (int64_t)sm_count() * 1536, segs);
+  constexpr size_t smem = ring_bytes<CH, SPAN>();
+  allow_shared_memory<dw_roll_kernel<KS, S, FLIP, TX, CH, WREG>>(smem);
+  dw_roll_kernel<KS, S, FLIP, TX, CH, WREG><<<(unsigned)cdiv(per_seg * segs, ROLL_THREADS), ROLL_THREADS, smem, s>>>(a, wt, rows, segs);
+}
+template <int KS, int S, int TX, int CH>
+static void launch_wgrad_roll(const DwArgs& a, dim3 grid, int SL, int CL, int rows, int segs, float* part, cudaStream_t s) {
+  constexpr size_t smem = ring_bytes<CH, (TX - 1) * S + KS>();
+  allow_shared_memory<dw_wgrad_roll_kernel<KS, S, TX, CH>>(smem);
+  dw_wgrad_roll_kernel<KS, S, TX, CH><<<grid, ROLL_THREADS, smem, s>>>(a, SL, CL, rows, segs, part);
+}
+// Which kernel serves which case (measured on 128 x 96 x 56 x 56 and 64 x 96 x 112 x 112 -> 56 x 56, fraction of the copy
+// bandwidth): stride 1, 3x3 and 5x5: the rolling kernel (3x3: 0.75 against 0.66); stride 2 and 7x7: one output row per thread
+// (3x3 stride 2: 0.82 against 0.62 -- half of a strip's input rows serve one output row only, the ring buys nothing).
 template <int KS, bool FLIP>
 static void launch_rows_ks(const DwArgs& a, int stride, const float* wt, cudaStream_t s) {
-  // 8 output pixels per thread for 3x3 stride 1 on wide rows (fewer redundant input and weight loads), else 4
-  const bool wide = KS == 3 && stride == 1 && a.ow >= 16;
-  const int tx = wide ? 8 : 4;
-  const int64_t total = (int64_t)a.n * a.oh * cdiv(a.ow, tx) * (a.c / 4);
+  if (stride == 1 && KS <= 5) return launch_roll<KS == 7 ? 5 : KS, 1, FLIP>(a, wt, s);
+  const int64_t total = (int64_t)a.n * a.oh * cdiv(a.ow, 4) * (a.c / 4);
   const unsigned blocks = (unsigned)cdiv(total, 256);
-  if (wide) dw_rows_nhwc4_kernel<KS == 3 ? 3 : KS, 1, FLIP, KS == 3 ? 8 : 4><<<blocks, 256, 0, s>>>(a, wt);
-  else if (stride == 1) dw_rows_nhwc4_kernel<KS, 1, FLIP, 4><<<blocks, 256, 0, s>>>(a, wt);
+  if (stride == 1) dw_rows_nhwc4_kernel<KS, 1, FLIP, 4><<<blocks, 256, 0, s>>>(a, wt);
   else dw_rows_nhwc4_kernel<KS, 2, FLIP, 4><<<blocks, 256, 0, s>>>(a, wt);
 }
 // `a` describes the convolution the kernel performs (for the flipped input gradient: gy -> dx with stride 1)
@@ -484,6 +932,14 @@ int omt_dw_dgrad(const OmtConvGeo* g, const OmtAct* gy, const float* w, const Om
     }
     const int kk = g->ks * g->ks;
     dw_weight_tc_kernel<<<(unsigned)cdiv((int64_t)g->ci * kk, 256), 256, 0, st(stream)>>>(w, (float*)sc.p, g->ci, kk);
+    if (g->stride == 2 && rows_ok(g)) {
+      const int64_t threads = (int64_t)g->n * g->ih * cdiv(g->iw, 4) * (g->ci / 4);
+      const unsigned blocks = (unsigned)cdiv(threads, 256);
+      if (g->ks == 3) dw_dgrad_s2_kernel<3, 4, 4><<<blocks, 256, 0, st(stream)>>>(a, (const float*)sc.p);
+      else if (g->ks == 5) dw_dgrad_s2_kernel<5, 4, 4><<<blocks, 256, 0, st(stream)>>>(a, (const float*)sc.p);
+      else dw_dgrad_s2_kernel<7, 4, 4><<<blocks, 256, 0, st(stream)>>>(a, (const float*)sc.p);
+      return check_launch("dw_dgrad_s2_nhwc4");
+    }
     dw_dgrad_nhwc4_kernel<<<(unsigned)cdiv(total / 4, 256), 256, 0, st(stream)>>>(a, (const float*)sc.p);
     return check_launch("dw_dgrad_nhwc4");
   }
@@ -503,22 +959,42 @@ int omt_dw_wgrad(const OmtConvGeo* g, const OmtAct* x, const OmtAct* gy, float* 
   const bool reg = g->ks == 3 || g->ks == 5 || g->ks == 7;
   if (is_nhwc(x, c, g->ih, g->iw) && is_nhwc(gy, c, g->oh, g->ow) && c % 4 == 0 && (g->ks == 3 || g->ks == 5) && g->stride <= 2 &&
       aligned16(x->p) && aligned16(gy->p)) {
-    const int c4 = c / 4;
-    const int CL = std::min(c4, 32), PL = 256 / CL;
-    const int gx = (int)cdiv(c4, CL);
-    const int64_t items = (int64_t)g->n * g->oh * cdiv(g->ow, 4);
-    const int S = (int)std::max<int64_t>(1, std::min<int64_t>(cdiv(items, (int64_t)PL * 4), cdiv(4 * sm_count(), gx)));
+    float* part = nullptr;
+    int S = 1;
     Scratch sc;
-    r = sc.get(nullptr, 0, (size_t)c * S * kk * sizeof(float), stream);
-    if (r) return r;
-    float* part = (float*)sc.p;
-    dim3 grid(gx, S);
-    const size_t smem = (size_t)PL * CL * sizeof(float4);
-    if (g->ks == 3 && g->stride == 1) dw_wgrad_nhwc4_kernel<3, 1><<<grid, 256, smem, s>>>(a, S, CL, part);
-    else if (g->ks == 3) dw_wgrad_nhwc4_kernel<3, 2><<<grid, 256, smem, s>>>(a, S, CL, part);
-    else if (g->stride == 1) dw_wgrad_nhwc4_kernel<5, 1><<<grid, 256, smem, s>>>(a, S, CL, part);
-    else dw_wgrad_nhwc4_kernel<5, 2><<<grid, 256, smem, s>>>(a, S, CL, part);
-    r = check_launch("dw_wgrad_nhwc4");
+    if (g->stride == 1) {
+      // rolling strips; 4 channels per thread for 3x3, 2 for 5x5 (25 tap sums per channel)
+      const int CH = g->ks == 3 ? 4 : 2, TX = 4;
+      const int cqn = c / CH;
+      const int CL = std::min(cqn, 32), PL = ROLL_THREADS / CL;
+      const int gx = (int)cdiv(cqn, CL);
+      const int64_t per_seg = (int64_t)g->n * cdiv(g->ow, TX);
+      // three resident blocks per SM; strips short enough that every pixel lane walks at least four of them
+      S = (int)std::max<int64_t>(1, cdiv(3 * sm_count(), gx));
+      int segs;
+      const int rows = strip_rows(g->oh, g->ks, per_seg, (int64_t)4 * S * PL, segs);
+      S = (int)std::max<int64_t>(1, std::min<int64_t>(S, cdiv(per_seg * segs, PL)));
+      r = sc.get(nullptr, 0, (size_t)c * S * kk * sizeof(float), stream);
+      if (r) return r;
+      part = (float*)sc.p;
+      dim3 grid(gx, S);
+      if (g->ks == 3) launch_wgrad_roll<3, 1, 4, 4>(a, grid, S, CL, rows, segs, part, s);
+      else launch_wgrad_roll<5, 1, 4, 2>(a, grid, S, CL, rows, segs, part, s);
+    } else {  // stride 2: a group of four output pixels per trip (measured 0.77 of the copy bandwidth against 0.61 for strips)
+      const int c4 = c / 4;
+      const int CL = std::min(c4, 32), PL = 256 / CL;
+      const int gx = (int)cdiv(c4, CL);
+      const int64_t items = (int64_t)g->n * g->oh * cdiv(g->ow, 4);
+      S = (int)std::max<int64_t>(1, std::min<int64_t>(cdiv(items, (int64_t)PL * 4), cdiv(4 * sm_count(), gx)));
+      r = sc.get(nullptr, 0, (size_t)c * S * kk * sizeof(float), stream);
+      if (r) return r;
+      part = (float*)sc.p;
+      dim3 grid(gx, S);
+      const size_t smem = (size_t)PL * CL * sizeof(float4);
+      if (g->ks == 3) dw_wgrad_nhwc4_kernel<3, 2><<<grid, 256, smem, s>>>(a, S, CL, part);
+      else dw_wgrad_nhwc4_kernel<5, 2><<<grid, 256, smem, s>>>(a, S, CL, part);
+    }
+    r = check_launch(g->stride == 1 ? "dw_wgrad_strips_nhwc" : "dw_wgrad_nhwc4");
     if (r) return r;
     const int64_t total = (int64_t)c * kk;
     dw_wgrad_fin_kernel<<<(unsigned)cdiv(total * 32, 256), 256, 0, s>>>(part, total, kk, S, scale, dw);

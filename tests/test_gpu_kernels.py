@@ -115,13 +115,14 @@ def test_tensor_core_path_vs_aten_and_exact_path(capi, shape):
         assert rel_err(2 * host(got_dw), dw) <= TOL
     capi.call("omt_sync")  # a tensor-core kernel that gave up on a barrier would be reported here
     after = capi.kernel_counts()
-    assert sum(v - before.get(k, 0) for k, v in after.items() if k.startswith(("conv_tc_1", "conv_tc_window", "wgrad_tc_1"))) >= (2 + wg_tc if few else 4)
+    assert sum(v - before.get(k, 0) for k, v in after.items() if k.startswith(("conv_tc_1", "conv_tc_2", "conv_tc_window", "wgrad_tc_1"))) >= (2 + wg_tc if few else 4)
     # the two paths agree with each other far inside the tolerance, with the cross terms in their own accumulator or not
     exact = capi.conv_fwd(xd, wd, bd, s, p, flags=capi.FORCE_SIMT | capi.EPI_RELU, cl=True)
     assert rel_err(host(capi.conv_fwd(xd, wd, bd, s, p, flags=capi.FORCE_TC | capi.EPI_RELU, cl=True)), host(exact)) <= 5e-5
     assert rel_err(host(capi.conv_fwd(xd, wd, bd, s, p, flags=capi.FORCE_TC | capi.EPI_RELU | capi.PRECISE_ACCUM, cl=True)), host(exact)) <= 5e-5
     if n >= 32:
-        assert after.get("conv_tc_128x256_acc1", 0) > before.get("conv_tc_128x256_acc1", 0), after
+        acc1 = lambda kc: sum(v for k, v in kc.items() if k.endswith("_acc1"))  # single-accumulator tiles, one CTA or a CTA pair
+        assert acc1(after) > acc1(before), after
 
 
 @pytest.mark.parametrize("shape,cl_out", [((4, 64, 96, 14, 3, 1, 1), True), ((2, 32, 64, 16, 1, 2, 0), True), ((2, 64, 64, 16, 3, 2, 1), True),
@@ -685,3 +686,35 @@ def test_nll_loss_refuses_bad_arguments(capi):
     assert torch.isnan(loss).all() and float(tw) == 3.0
     capi.call("omt_softmax_nll_backward", P(torch.ones(1, device="cuda")), P(lp), P(t), None, P(tw), P(dx), 4, 3, -100, 1, sh())
     assert torch.all(dx[2] == 0) and torch.isfinite(dx).all()
+
+
+@pytest.mark.parametrize("shape", [(2, 8, 14, 3, 1, 1), (3, 12, 23, 3, 1, 1), (2, 16, 29, 5, 1, 2), (2, 8, 31, 5, 2, 2), (2, 8, 30, 3, 2, 1),
+                                   (1, 4, 33, 7, 1, 3), (2, 4, 35, 7, 2, 3), (2, 96, 28, 3, 2, 1), (2, 8, 19, 3, 1, 0), (2, 8, 22, 5, 2, 0),
+                                   (2, 8, 12, 3, 1, 2), (1, 40, 9, 5, 1, 2), (4, 24, 57, 3, 1, 1), (2, 8, 6, 5, 2, 2), (1, 4, 3, 3, 1, 1)],
+                         ids=lambda s: "n%d_c%d_hw%d_k%d_s%d_p%d" % s)
+def test_depthwise_strip_kernels_vs_aten(capi, shape):
+    """Channels-last depthwise forward, input gradient (stride 1: mirrored forward; stride 2: parity gather) and weight gradient
+    for 3x3 / 5x5 / 7x7, strides 1 and 2: the kernels that walk strips of output rows with partial sums in registers. Widths
+    and heights that are not multiples of the strip size, pads 0..ks-1, images smaller than one strip; bias + ReLU epilogue.
+    Against float64 aten on the CPU (the reference's own oracle for dw_fwd / dw_gin / dw_gwt)."""
+    n, c, hw, ks, s, p = shape
+    torch.manual_seed(hw * 7 + ks)
+    x = torch.randn(n, c, hw, hw + 3)
+    w = torch.randn(c, 1, ks, ks) * 0.3
+    b = torch.randn(c)
+    oh, ow = (hw + 2 * p - ks) // s + 1, (hw + 3 + 2 * p - ks) // s + 1
+    gy = torch.randn(n, c, oh, ow)
+    x64 = x.double().requires_grad_()
+    w64 = w.double().requires_grad_()
+    y64 = torch.nn.functional.conv2d(x64, w64, b.double(), s, p, groups=c)
+    y64.backward(gy.double())
+    xd, wd, bd, gd = dev(x, True), dev(w), dev(b), dev(gy, True)
+    y = capi.dw_fwd(xd, wd, bd, s, p, flags=capi.EPI_RELU, cl=True)
+    assert rel_err(host(y), y64.detach().relu().float().numpy()) <= 2e-6
+    y = capi.dw_fwd(xd, wd, None, s, p, cl=True)
+    assert rel_err(host(y), (y64.detach() - b.double().view(1, -1, 1, 1)).float().numpy()) <= 2e-6
+    dx = capi.dw_dgrad(gd, wd, (hw, hw + 3), s, p, cl=True)
+    assert rel_err(host(dx), x64.grad.float().numpy()) <= 2e-6
+    dw = capi.dw_wgrad(xd, gd, ks, s, p, scale=0.5)
+    assert rel_err(2 * host(dw), w64.grad.float().numpy()) <= 1e-5
+    capi.call("omt_sync")
