@@ -134,6 +134,92 @@ static OmtAct as_cl(const OmtAct* a, int c, int h, int w) {  // what the copy wo
   return r;
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// Input gradient for <= 4 input channels (a network's first layer) on the tensor cores. As an implicit GEMM per stride phase
+// its tiles would have ci <= 4 useful columns, and the work of loading and splitting the gy tiles does not shrink with the
+// columns. So the sum is taken the other way round: T[p][(ky, kx, c)] = sum_co gy[p][co] * w[co][c][ky][kx] for every output
+// pixel p is ONE dense product with ci * ks * ks columns (the input gradient of a 1x1 convolution: tcgen05 kernels, no waste),
+// and dx(y, x, c) then gathers its taps from T (col2im): oy = (y + pad - ky) / s for the ky on y's stride phase
+// (csrc/conv.cpp:78-95), likewise ox. T costs one write and one read of P * ci * ks^2 floats; for AlexNet's first layer
+// (n = 16) that is 70 MB against a GEMM of 2.3 GFLOP. Used only with scratch from the library's allocator (T can be large).
+// ---------------------------------------------------------------------------------------------------------------------
+namespace omt {
+constexpr size_t TAPS_MAX_BYTES = (size_t)1 << 30;  // beyond this T the CUDA-core kernel runs instead
+
+__global__ void __launch_bounds__(256) taps_weight_kernel(const float* __restrict__ w, float* __restrict__ wm, int co, int ci, int kk, int colsp) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;  // wm[o][t * ci + c] = w[o][c][t]; columns past ci * kk are zero
+  if (i >= co * colsp) return;
+  const int o = i / colsp, col = i - o * colsp;
+  const int t = col / ci, c = col - t * ci;
+  wm[i] = t < kk ? __ldg(w + ((int64_t)o * ci + c) * kk + t) : 0.f;
+}
+
+struct Col2imArgs {
+  const float* T;
+  ActView dx;
+  int n, ci, ih, iw, oh, ow, ks, stride, pad, colsp;
+};
+// one thread per input pixel (consecutive threads, consecutive x): the s threads of one stride period read s * ci consecutive
+// floats of one row of T per tap
+__global__ void __launch_bounds__(256) col2im_kernel(Col2imArgs a) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (int64_t)a.n * a.ih * a.iw) return;
+  const int x = (int)(i % a.iw);
+  const int64_t r = i / a.iw;
+  const int y = (int)(r % a.ih), img = (int)(r / a.ih);
+  const int s = a.stride;
+  const int ky0 = (y + a.pad) % s, kx0 = (x + a.pad) % s;
+  const int qy = (y + a.pad - ky0) / s, qx = (x + a.pad - kx0) / s;  // output pixel reached through tap (ky0 + s*ty, kx0 + s*tx) is (qy - ty, qx - tx)
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int ky = ky0, oy = qy; ky < a.ks; ky += s, oy--) {
+    if (oy < 0) break;
+    if (oy >= a.oh) continue;
+    for (int kx = kx0, ox = qx; kx < a.ks; kx += s, ox--) {
+      if (ox < 0) break;
+      if (ox >= a.ow) continue;
+      const float* t = a.T + (((int64_t)img * a.oh + oy) * a.ow + ox) * a.colsp + (ky * a.ks + kx) * a.ci;
+      for (int c = 0; c < a.ci; c++) acc[c] += __ldg(t + c);
+    }
+  }
+  float* out = a.dx.p + a.dx.off(img, 0, y, x);
+  for (int c = 0; c < a.ci; c++) out[(int64_t)c * a.dx.sc] = acc[c];
+}
+
+static int taps_cols(const OmtConvGeo* g) { return (int)cdiv((int64_t)g->ci * g->ks * g->ks, 8) * 8; }  // (a multiple of 32 bytes per row of T)
+static OmtConvGeo taps_geo(const OmtConvGeo* g) { return OmtConvGeo{g->n, taps_cols(g), g->co, g->oh, g->ow, g->oh, g->ow, 1, 1, 0, 1}; }
+// gy: the channels-last gradient (or what its channels-last copy would look like)
+static bool dgrad_by_taps_ok(const OmtConvGeo* g, const OmtAct* gy_cl) {
+  if (g->ci > 4 || g->groups != 1 || taps_cols(g) < 8) return false;
+  const OmtConvGeo g1 = taps_geo(g);
+  if ((size_t)g->n * g->oh * g->ow * g1.ci * sizeof(float) > TAPS_MAX_BYTES) return false;
+  OmtAct t{reinterpret_cast<float*>(256), (int64_t)g1.ci * g->oh * g->ow, 1, (int64_t)g1.ci * g->ow, g1.ci};
+  return tc_supported(1, &g1, gy_cl, &t);
+}
+static int dgrad_by_taps(const OmtConvGeo* g, const OmtAct* gy, const float* w, const OmtAct* dx, omt_stream_t stream) {
+  const OmtConvGeo g1 = taps_geo(g);
+  const int colsp = g1.ci, kk = g->ks * g->ks;
+  const size_t P = (size_t)g->n * g->oh * g->ow;
+  const size_t wm_floats = ((size_t)g->co * colsp + 63) / 64 * 64;
+  Scratch sc, ws;
+  int r = sc.get(nullptr, 0, (wm_floats + P * colsp) * sizeof(float), stream);
+  if (r) return r;
+  r = ws.get(nullptr, 0, tc_workspace(1, &g1), stream);
+  if (r) return r;
+  float* wm = (float*)sc.p;
+  float* T = wm + wm_floats;
+  cudaStream_t s = st(stream);
+  taps_weight_kernel<<<(unsigned)cdiv((int64_t)g->co * colsp, 256), 256, 0, s>>>(w, wm, g->co, g->ci, kk, colsp);
+  r = check_launch("conv_dgrad_taps_weights");
+  if (r) return r;
+  OmtAct t{T, (int64_t)colsp * g->oh * g->ow, 1, (int64_t)colsp * g->ow, colsp};
+  r = tc_conv_dgrad(&g1, gy, wm, &t, 0, ws.p, s);
+  if (r) return r;
+  Col2imArgs a{T, view(dx), g->n, g->ci, g->ih, g->iw, g->oh, g->ow, g->ks, g->stride, g->pad, colsp};
+  col2im_kernel<<<(unsigned)cdiv((int64_t)g->n * g->ih * g->iw, 256), 256, 0, s>>>(a);
+  return check_launch("conv_dgrad_col2im");
+}
+}  // namespace omt
+
 extern "C" {
 
 size_t omt_conv_workspace_bytes(int kind, const OmtConvGeo* g, uint32_t flags) {
@@ -196,6 +282,19 @@ int omt_conv_dgrad(const OmtConvGeo* g, const OmtAct* gy, const float* w, const 
       if (r) return r;
       gy = &gc.act;
       tc = true;
+    }
+  }
+  // few input channels: the product over all taps on the tensor cores, then a gather (library scratch only)
+  if (!tc && g->ci <= 4 && !(flags & (OMT_FORCE_SIMT | OMT_EPI_ACCUM)) && !workspace) {
+    const bool cg = could_be_cl(gy, g->co, g->oh, g->ow);
+    OmtAct probe = cg ? as_cl(gy, g->co, g->oh, g->ow) : *gy;
+    if (dgrad_by_taps_ok(g, &probe)) {
+      if (cg) {
+        r = gc.make(gy, g->n, g->co, g->oh, g->ow, stream);
+        if (r) return r;
+        gy = &gc.act;
+      }
+      return dgrad_by_taps(g, gy, w, dx, stream);
     }
   }
   OMT_REQUIRE(tc || !(flags & OMT_FORCE_TC), "omt_conv_dgrad: geometry/layout not covered by the tensor-core path");

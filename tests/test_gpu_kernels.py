@@ -718,3 +718,28 @@ def test_depthwise_strip_kernels_vs_aten(capi, shape):
     dw = capi.dw_wgrad(xd, gd, ks, s, p, scale=0.5)
     assert rel_err(2 * host(dw), w64.grad.float().numpy()) <= 1e-5
     capi.call("omt_sync")
+
+
+@pytest.mark.parametrize("cl", [False, True], ids=["nchw", "nhwc"])
+@pytest.mark.parametrize("shape", [(4, 3, 64, 63, 11, 4, 2), (2, 4, 32, 17, 3, 1, 1), (2, 1, 32, 20, 5, 2, 2), (3, 3, 96, 30, 7, 2, 3),
+                                   (2, 3, 64, 33, 7, 2, 0), (2, 2, 32, 9, 3, 3, 1), (1, 3, 32, 12, 1, 1, 0)],
+                         ids=lambda s: "n%d_ci%d_co%d_hw%d_k%d_s%d_p%d" % s)
+def test_input_gradient_of_a_first_layer_by_taps(capi, shape, cl):
+    """Input gradient for <= 4 input channels: one tensor-core product over all taps, then the col2im gather (stride phases of
+    csrc/conv.cpp:78-95); gy in either layout, dx NCHW; against float64 aten and the exact-fp32 kernel; the kernels that ran
+    are the tensor-core ones."""
+    n, ci, co, hw, ks, s, p = shape
+    torch.manual_seed(co + hw)
+    x = torch.randn(n, ci, hw, hw + 2, dtype=torch.float64, requires_grad=True)
+    w = torch.randn(co, ci, ks, ks) * 0.1
+    y = torch.nn.functional.conv2d(x, w.double(), None, s, p)
+    gy = torch.randn(y.shape)
+    y.backward(gy.double())
+    before = capi.kernel_counts()
+    got = capi.conv_dgrad(dev(gy, cl), dev(w), (hw, hw + 2), s, p)
+    capi.call("omt_sync")
+    after = capi.kernel_counts()
+    assert rel_err(host(got), x.grad.float().numpy()) <= 2e-5
+    assert after.get("conv_dgrad_col2im", 0) == before.get("conv_dgrad_col2im", 0) + 1, after
+    exact = capi.conv_dgrad(dev(gy, cl), dev(w), (hw, hw + 2), s, p, flags=capi.FORCE_SIMT)
+    assert rel_err(host(got), host(exact)) <= 2e-5
