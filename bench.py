@@ -227,6 +227,9 @@ class HbmKernels:
         steps = [torch.zeros((), device="cuda") for _ in params]
         npar = sum(t.numel() for t in params)
         call = capi.call
+        yp, ip = capi.maxpool_fwd(x, 3, 2, 1)   # indices and a gradient for the max-pool backward case
+        gp = torch.randn_like(yp)
+        self.keep_pool = (yp, ip, gp)
         self.keep = (x, g, y, dx, xd, gd, xs2, gs2, wd5, params, grads, ms_, vs_, steps)
         self.kernels = {
             # name: (callable, algorithmic bytes)
@@ -244,6 +247,7 @@ class HbmKernels:
             "depthwise3x3s2_wgrad": (lambda: capi.dw_wgrad(xs2, gs2, 3, 2, 1), 4 * ns2),
             "depthwise5x5s2_fwd": (lambda: capi.dw_fwd(xs2, wd5, None, 2, 2, cl=True), 4 * ns2),
             "maxpool3x3s2_fwd": (lambda: capi.maxpool_fwd(x, 3, 2, 1), 4 * ne + 12 * (ne // 4)),
+            "maxpool3x3s2_bwd": (lambda: capi.maxpool_bwd(gp, ip, (h, w), 3, 2, 1), 4 * ne + 12 * (ne // 4)),
             "sgd_momentum": (lambda: capi.sgd(params, grads, ms_, 0.1, momentum=0.9, weight_decay=1e-4), 20 * npar),
             "adamw": (lambda: capi.adam(params, grads, ms_, vs_, steps, 1e-3, weight_decay=0.01, decoupled=True), 28 * npar),
         }

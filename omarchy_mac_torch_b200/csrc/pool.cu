@@ -213,38 +213,50 @@ __global__ void __launch_bounds__(256) maxpool_fwd_nhwc4_fixed_kernel(PoolArgs a
   decode4<true>(i, c4, a.oh, gx, img, cq, oy, xg);
   const int ox0 = xg * TX, y0 = oy * ST - a.p.ph, x0 = ox0 * ST - a.p.pw;
   const float* xp = a.x.p + ((int64_t)img * a.ih * a.iw) * a.c + cq * 4;
+  // "first maximum wins, the first NaN wins outright" without per-element flags: the running best starts at -inf with the
+  // index of the window's first element (what an all -inf window reports), a value replaces it when it is larger, or when it
+  // is a NaN and the best is not one yet; after that no comparison with the NaN best succeeds.
   float best[TX][4];
   int bi[TX][4];
-  bool done[TX][4];
+  const int yf = max(y0, 0);
 #pragma unroll
-  for (int j = 0; j < TX; j++)
+  for (int j = 0; j < TX; j++) {
+    const int first = yf * a.iw + max(x0 + j * ST, 0);
 #pragma unroll
-    for (int k = 0; k < 4; k++) { best[j][k] = -INFINITY; bi[j][k] = -1; done[j][k] = false; }
+    for (int k = 0; k < 4; k++) { best[j][k] = -INFINITY; bi[j][k] = first; }
+  }
+  const bool interior = x0 >= 0 && x0 + SPAN <= a.iw;
 #pragma unroll
   for (int ky = 0; ky < KS; ky++) {
     const int y = y0 + ky;
     if (y < 0 || y >= a.ih) continue;
     float4 in[SPAN];
+    const float* row = xp + ((int64_t)y * a.iw + x0) * a.c;
+    if (interior) {
 #pragma unroll
-    for (int k = 0; k < SPAN; k++) {
-      const int xx = x0 + k;
-      in[k] = (xx >= 0 && xx < a.iw) ? __ldg(reinterpret_cast<const float4*>(xp + ((int64_t)y * a.iw + xx) * a.c)) : make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int k = 0; k < SPAN; k++) in[k] = __ldg(reinterpret_cast<const float4*>(row + (int64_t)k * a.c));
+    } else {
+#pragma unroll
+      for (int k = 0; k < SPAN; k++) {
+        const int xx = x0 + k;
+        in[k] = (xx >= 0 && xx < a.iw) ? __ldg(reinterpret_cast<const float4*>(row + (int64_t)k * a.c)) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
     }
+    const int rowi = y * a.iw + x0;
 #pragma unroll
     for (int j = 0; j < TX; j++)
 #pragma unroll
       for (int kx = 0; kx < KS; kx++) {
-        const int xx = x0 + j * ST + kx;
-        if (xx < 0 || xx >= a.iw) continue;
+        if (!interior) {
+          const int xx = x0 + j * ST + kx;
+          if (xx < 0 || xx >= a.iw) continue;
+        }
         const float4 v4 = in[j * ST + kx];
         const float v[4] = {v4.x, v4.y, v4.z, v4.w};
 #pragma unroll
         for (int k = 0; k < 4; k++) {
-          const bool nan = isnan_bits(v[k]);
-          if (!done[j][k] && (bi[j][k] < 0 || nan || v[k] > best[j][k])) {
-            best[j][k] = v[k]; bi[j][k] = y * a.iw + xx;
-            done[j][k] = nan;
-          }
+          const float b = best[j][k];
+          if ((v[k] > b) | ((v[k] != v[k]) & (b == b))) { best[j][k] = v[k]; bi[j][k] = rowi + j * ST + kx; }
         }
       }
   }
