@@ -1039,22 +1039,30 @@ struct WgArgs {
   int blocks_per_slice;  // 32-pixel blocks per blockIdx.z
 };
 
-template <int BN, int PB>
+// PAIR: the CTA is one of a cta_group::2 pair (two 128-row co tiles, one stream of 256-row MMAs) and stages only its half of
+// the x columns; the smaller stages leave room for a deeper ring.
+template <int BN, int PB, bool PAIR = false>
 struct WgSmem {
-  static constexpr int STAGES = (BN >= 192 ? 2 : (BN == 128 ? 3 : 4)) * (32 / PB);
   static constexpr int TMEM_COLS = 2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512);  // main + cross-term accumulators, a power of two
   static constexpr int CH = PB * 128;                 // one 32-pixel x 32-float box
-  static constexpr int A_BYTES = 4 * CH, B_BYTES = (BN / 32) * CH;
+  static constexpr int B_CHUNKS = BN / 32 / (PAIR ? 2 : 1);  // 32-column chunks of x this CTA stages
+  static constexpr int A_BYTES = 4 * CH, B_BYTES = B_CHUNKS * CH;
   static constexpr int HALF = A_BYTES + B_BYTES;      // hi region; the lo region follows at +HALF
   static constexpr int STAGE_BYTES = 2 * HALF;
+  static constexpr int STAGES = PAIR ? (200 * 1024 / STAGE_BYTES < 8 ? 200 * 1024 / STAGE_BYTES : 8) : (BN >= 192 ? 2 : (BN == 128 ? 3 : 4)) * (32 / PB);
   static constexpr int BAR_OFF = STAGES * STAGE_BYTES;
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
 
-template <int BN, int PB>
+// PAIR (clusters of two CTAs along blockIdx.x, i.e. two neighbouring co tiles of the same columns and slice): each CTA loads
+// and splits its own gy rows and HALF of the x chunks; the split warps of both arrive on CTA rank 0's "split" barrier, whose
+// MMA thread issues tcgen05.mma.cta_group::2 (M = 256) for both and signals "free" / "accumulator ready" in both CTAs with
+// multicast commits. Both operands are split on the fly here, so halving the x side removes a third of a stage's
+// shared-memory traffic (the single-CTA kernel is bound by it).
+template <int BN, int PB, bool PAIR = false>
 __global__ void __launch_bounds__(WG_THREADS, 1)
 wgrad_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_g, const WgArgs g) {
-  using S = WgSmem<BN, PB>;
+  using S = WgSmem<BN, PB, PAIR>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const uint32_t smem_base = smem_u32(smem);
@@ -1066,8 +1074,11 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int co0 = blockIdx.x * BM;
-  const int chunk0 = blockIdx.y * (BN / 32);
-  const int nchunks = min(BN / 32, g.chunks - chunk0);
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+  const int nchunks = min(BN / 32, g.chunks - (int)blockIdx.y * (BN / 32));  // columns of the tile (the epilogue's view)
+  const int nown = PAIR ? S::B_CHUNKS : nchunks;                               // x chunks this CTA loads (pairs take full tiles only)
+  const int chunk0 = blockIdx.y * (BN / 32) + (int)rank * (PAIR ? S::B_CHUNKS : 0);
+  auto LEADER = [&](int i) { return PAIR ? mapa_rank(BAR(i), 0u) : BAR(i); };
   const int total_blocks = g.total_blocks;
   const int blk_begin = blockIdx.z * g.blocks_per_slice;
   const int kblocks = max(0, min(g.blocks_per_slice, total_blocks - blk_begin));
@@ -1075,7 +1086,7 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
   if (threadIdx.x == 0) {
     for (int s = 0; s < S::STAGES; s++) {
       mbar_init(BAR(s), 1);
-      mbar_init(BAR(S::STAGES + s), 8);
+      mbar_init(BAR(S::STAGES + s), PAIR ? 16 : 8);  // the split warps (of both CTAs of a pair)
       mbar_init(BAR(2 * S::STAGES + s), 1);
     }
     mbar_init(BAR(3 * S::STAGES), 1);
@@ -1083,13 +1094,21 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)),
-                 "r"((uint32_t)S::TMEM_COLS)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if constexpr (PAIR) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)),
+                   "r"((uint32_t)S::TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)),
+                   "r"((uint32_t)S::TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_acc = *tmem_slot;
 
@@ -1105,15 +1124,15 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
           const int b = blk_begin + kb;
           const int tx = b % g.tiles_x, r1 = b / g.tiles_x, ty = r1 % g.tiles_y, tn = r1 / g.tiles_y;
           const int ox0 = tx * g.bw, oy0 = ty * g.bh, n0 = tn * g.bn;
-          mbar_expect_tx(BAR(s), S::A_BYTES + nchunks * S::CH);
+          mbar_expect_tx(BAR(s), S::A_BYTES + nown * S::CH);
           tma_tile_5d(stage, &map_g, BAR(s), 0, ox0, oy0, n0, co0 / 32);
           if (g.mode & 8) {
-            for (int j = 0; j < nchunks; j++) {
+            for (int j = 0; j < nown; j++) {
               const int chunk = chunk0 + j, ky = chunk / g.cblocks, blk = chunk - ky * g.cblocks;
               tma_tile_4d(stage + S::A_BYTES + j * S::CH, &map_x, BAR(s), blk * BKF, ox0, oy0 * g.stride + ky - g.pad, n0);
             }
           } else {
-            for (int j = 0; j < nchunks; j += g.cpi) {
+            for (int j = 0; j < nown; j += g.cpi) {
               const int chunk = chunk0 + j, tap = chunk / g.cblocks, cb = chunk - tap * g.cblocks;
               const int ky = tap / g.ks, kx = tap - ky * g.ks;
               tma_tile_5d(stage + S::A_BYTES + j * S::CH, &map_x, BAR(s), 0, ox0 * g.stride - g.pad + kx, oy0 * g.stride - g.pad + ky, n0, cb);
@@ -1125,7 +1144,7 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         const int p0 = (blk_begin + kb) * PB;
         const int img = p0 / ohw, r = p0 - img * ohw, oy = r / g.ow, ox = r - oy * g.ow;
         const int w0 = ox * g.stride - g.pad, h0 = oy * g.stride - g.pad;
-        mbar_expect_tx(BAR(s), S::A_BYTES + ((g.mode & 2) ? S::B_BYTES : nchunks * S::CH));
+        mbar_expect_tx(BAR(s), S::A_BYTES + ((g.mode & 2) ? S::B_BYTES : nown * S::CH));
         if (g.mode & 1) {
           tma_tile_3d(stage, &map_g, BAR(s), 0, p0, co0 / 32);
         } else {
@@ -1135,7 +1154,7 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         if (g.mode & 2) {
           tma_tile_3d(stage + S::A_BYTES, &map_x, BAR(s), 0, p0, chunk0);
         } else {
-          for (int j = 0; j < nchunks; j++) {
+          for (int j = 0; j < nown; j++) {
             const int chunk = chunk0 + j, tap = chunk / g.cblocks, cb = chunk - tap * g.cblocks;
             const int ky = tap / g.ks, kx = tap - ky * g.ks;
             tma_im2col_4d(stage + S::A_BYTES + j * S::CH, &map_x, BAR(s), cb * BKF, w0, h0, img, (uint16_t)kx, (uint16_t)ky);
@@ -1148,15 +1167,27 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
           const long long t0 = clock64();
           while (!mbar_try(BAR(kb % S::STAGES), (kb / S::STAGES) & 1) && clock64() - t0 < WAIT_BUDGET_CLOCKS) {}
         }
+      } else if (PAIR) {  // the last "free" arrivals come from the other SM's commit: let them land before this CTA exits
+        for (int kb = max(0, issued - S::STAGES); kb < issued; kb++)
+          if (!mbar_wait(BAR(2 * S::STAGES + kb % S::STAGES), (kb / S::STAGES) & 1, abort_flag)) break;
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc = idesc_tf32(BN, true);
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = idesc_tf32(BN, true, PAIR ? 2 * BM : BM);
+      auto umma_tf32 = [](uint32_t d, uint64_t da, uint64_t db, uint32_t id, uint32_t accumulate) {
+        if constexpr (PAIR) umma_tf32_pair(d, da, db, id, accumulate);
+        else omt::umma_tf32(d, da, db, id, accumulate);
+      };
+      auto umma_commit = [](uint32_t bar) {
+        if constexpr (PAIR) umma_commit_pair(bar);
+        else omt::umma_commit(bar);
+      };
       bool ok = true;
       for (int kb = 0; kb < kblocks && ok; kb++) {
         const int s = kb % S::STAGES, round = kb / S::STAGES;
-        ok = mbar_wait(BAR(S::STAGES + s), round & 1, abort_flag) && mbar_wait(BAR(s), round & 1, abort_flag);
+        // (a pair's "split" barrier counts the split warps of both CTAs, each of which waited for its own loads)
+        ok = mbar_wait<PAIR>(BAR(S::STAGES + s), round & 1, abort_flag) && (PAIR || mbar_wait(BAR(s), round & 1, abort_flag));
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t stage = smem_base + s * S::STAGE_BYTES;
@@ -1177,7 +1208,7 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
   } else {
     const int t = threadIdx.x - 64;  // 0..255
     bool ok = true;
-    const int n16 = (S::A_BYTES + nchunks * S::CH) / 16;  // 16-byte words that were loaded this stage
+    const int n16 = (S::A_BYTES + nown * S::CH) / 16;  // 16-byte words that were loaded this stage
     for (int kb = 0; kb < kblocks && ok; kb++) {
       const int s = kb % S::STAGES, round = kb / S::STAGES;
       ok = mbar_wait(BAR(s), round & 1, abort_flag);
@@ -1194,7 +1225,10 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
-      if (lane == 0) mbar_arrive(BAR(S::STAGES + s));
+      if (lane == 0) {
+        if constexpr (PAIR) mbar_arrive_cluster(LEADER(S::STAGES + s));
+        else mbar_arrive(BAR(S::STAGES + s));
+      }
     }
     // epilogue: warps 2..9; quarter = warp & 3, column half = (warp - 2) / 4
     if (ok && kblocks > 0) ok = mbar_wait(BAR(3 * S::STAGES), 0, abort_flag);
@@ -1217,7 +1251,7 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
           for (int j = 0; j < 32; j++) v[j] = 0u;  // a slice with no pixels contributes zeros
         }
         if (row >= g.co || c >= nchunks) continue;
-        float4* dst = reinterpret_cast<float4*>(prow + (chunk0 + c) * 32);
+        float4* dst = reinterpret_cast<float4*>(prow + ((int)blockIdx.y * (BN / 32) + c) * 32);  // (chunk0 is this CTA's first LOADED chunk)
 #pragma unroll
         for (int j = 0; j < 32; j += 4)
           dst[j / 4] = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
@@ -1226,9 +1260,11 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"((uint32_t)S::TMEM_COLS) : "memory");
+    if constexpr (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"((uint32_t)S::TMEM_COLS) : "memory");
+    else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"((uint32_t)S::TMEM_COLS) : "memory");
   }
 }
 
@@ -1396,6 +1432,7 @@ struct WgPlan {
   int bn, slices, blocks_per_slice, cblocks, cpad, chunks;
   int mode, total_blocks, bw, bh, bn_img, tiles_x, tiles_y, cpi;
   int pb;               // pixels per stage (16 or 32)
+  bool pair;            // clusters of two CTAs (cta_group::2)
   int win_kb;           // window mode: 32-float blocks per filter row
   size_t stage_floats;  // window mode: the padded 4-channel copy of x in front of the partial tiles
   size_t part_floats;
@@ -1417,13 +1454,19 @@ WgPlan plan_wgrad(const OmtConvGeo* g) {
     if (cdiv(w.chunks, bn / 32) * bn <= cdiv(w.chunks, w.bn / 32) * w.bn) w.bn = bn;
   const int64_t tiles = cdiv(g->co, BM) * cdiv(w.chunks, w.bn / 32);
   const int per_tile = w.bn / 32;
-  w.cpi = std::gcd(w.cblocks, per_tile);  // 32-channel blocks one x box carries: a box never straddles two taps or two tiles
+  // CTA pairs: two co tiles share the x columns, each CTA staging half of them (full tiles only, not the window mode)
+  // (measured at batch 256: 256-column tiles +5..16 %, e.g. 256 -> 256 3x3 at 14^2 0.310 -> 0.271 ms; 128-column tiles lose a
+  // third, their stages being too short to hide the cross-SM barrier round trip)
+  w.pair = !window && w.bn >= 192 && cdiv(g->co, BM) % 2 == 0 && w.chunks % per_tile == 0 && per_tile % 2 == 0 && g->co % 32 == 0 &&
+           g->ci % 32 == 0 && cta_pairs_enabled();
+  const int per_cta = w.pair ? per_tile / 2 : per_tile;
+  w.cpi = std::gcd(w.cblocks, per_cta);  // 32-channel blocks one x box carries: a box never straddles two taps, two tiles or two CTAs
   const bool aligned_taps = true;
   const bool matrix = !window && g->ks == 1 && g->stride == 1 && g->pad == 0 && g->ci % 32 == 0;
   const bool rect = !window && !matrix && g->ci % 32 == 0 && g->co % 32 == 0 && aligned_taps && g->stride <= 8;
   // x boxes per stage: 1 in matrix mode, per_tile / cpi in rectangle mode, per_tile in window / im2col mode
-  const bool few_boxes = (matrix && g->co % 32 == 0) || (rect && per_tile / w.cpi <= 2);
-  const int PB = few_boxes ? 16 : 32;
+  const bool few_boxes = (matrix && g->co % 32 == 0) || (rect && per_cta / w.cpi <= 2);
+  const int PB = few_boxes && !w.pair ? 16 : 32;  // (a pair synchronises two SMs per stage: fewer, larger stages)
   w.pb = PB;
   int64_t total_blocks = cdiv((int64_t)g->n * g->oh * g->ow, PB);
   if (window) {
@@ -1471,9 +1514,9 @@ WgPlan plan_wgrad(const OmtConvGeo* g) {
   } while (0)
 
 // `x` is the channels-last activation, or in window mode the padded 4-channel staging copy
-template <int BN, int PB>
+template <int BN, int PB, bool PAIR = false>
 int launch_wgrad(const OmtConvGeo* g, const WgPlan& w, const float* x, const float* gy, float* part, cudaStream_t s) {
-  using S = WgSmem<BN, PB>;
+  using S = WgSmem<BN, PB, PAIR>;
   alignas(64) CUtensorMap map_x, map_g;
   const int64_t P = (int64_t)g->n * g->oh * g->ow;
   constexpr auto F32 = CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
@@ -1499,7 +1542,7 @@ int launch_wgrad(const OmtConvGeo* g, const WgPlan& w, const float* x, const flo
     // x is the row-major [P, ci] matrix: dims (32 channels, pixel, 32-channel block), one box = the whole B tile
     cuuint64_t dims[3] = {32, (cuuint64_t)P, (cuuint64_t)(g->ci / 32)};
     cuuint64_t strides[2] = {(cuuint64_t)g->ci * 4, 128};
-    cuuint32_t box[3] = {BKF, PB, BN / 32}, estr[3] = {1, 1, 1};
+    cuuint32_t box[3] = {BKF, PB, (cuuint32_t)S::B_CHUNKS}, estr[3] = {1, 1, 1};
     OMT_ENCODE(g_encode_tiled(&map_x, F32, 3, (void*)x, dims, strides, box, estr, IL, SW, L2P, FILL), "cuTensorMapEncodeTiled (x matrix)");
   } else {
     cuuint64_t dims[4] = {(cuuint64_t)g->ci, (cuuint64_t)g->iw, (cuuint64_t)g->ih, (cuuint64_t)g->n};
@@ -1527,7 +1570,7 @@ int launch_wgrad(const OmtConvGeo* g, const WgPlan& w, const float* x, const flo
   }
   static std::once_flag attr_once;
   static cudaError_t attr_err = cudaSuccess;
-  std::call_once(attr_once, [] { attr_err = cudaFuncSetAttribute((wgrad_tc_kernel<BN, PB>), cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL); });
+  std::call_once(attr_once, [] { attr_err = cudaFuncSetAttribute((wgrad_tc_kernel<BN, PB, PAIR>), cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL); });
   OMT_CUDA(attr_err);
   WgArgs a{};
   a.mode = w.mode; a.total_blocks = w.total_blocks;
@@ -1535,8 +1578,18 @@ int launch_wgrad(const OmtConvGeo* g, const WgPlan& w, const float* x, const flo
   a.part = part; a.P = g->n * g->oh * g->ow; a.co = g->co; a.oh = g->oh; a.ow = g->ow; a.ks = g->ks; a.stride = g->stride; a.pad = g->pad;
   a.cblocks = w.cblocks; a.cpad = w.cpad; a.chunks = w.chunks; a.blocks_per_slice = w.blocks_per_slice;
   dim3 grid((unsigned)cdiv(g->co, BM), (unsigned)cdiv(w.chunks, BN / 32), (unsigned)w.slices);
+  if constexpr (PAIR) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid; cfg.blockDim = dim3(WG_THREADS); cfg.dynamicSmemBytes = S::TOTAL; cfg.stream = s;
+    cudaLaunchAttribute at{};
+    at.id = cudaLaunchAttributeClusterDimension;
+    at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
+    cfg.attrs = &at; cfg.numAttrs = 1;
+    OMT_CUDA(cudaLaunchKernelEx(&cfg, wgrad_tc_kernel<BN, PB, true>, map_x, map_g, a));
+    return check_launch(BN == 64 ? "wgrad_tc_256x64_pair" : (BN == 128 ? "wgrad_tc_256x128_pair" : (BN == 192 ? "wgrad_tc_256x192_pair" : "wgrad_tc_256x256_pair")));
+  }
   wgrad_tc_kernel<BN, PB><<<grid, WG_THREADS, S::TOTAL, s>>>(map_x, map_g, a);
-  return check_launch(BN == 64 ? "wgrad_tc_128x64" : (BN == 128 ? "wgrad_tc_128x128" : "wgrad_tc_128x256"));
+  return check_launch(BN == 64 ? "wgrad_tc_128x64" : (BN == 128 ? "wgrad_tc_128x128" : (BN == 192 ? "wgrad_tc_128x192" : "wgrad_tc_128x256")));
 }
 
 bool cl_ok(const OmtAct* a, int c, int h, int w) {
@@ -1696,10 +1749,14 @@ int tc_conv_wgrad(const OmtConvGeo* g, const OmtAct* x, const OmtAct* gy, float*
   }
   int r;
   switch (w.bn) {
-    case 64: r = w.pb == 16 ? launch_wgrad<64, 16>(g, w, xin, gy->p, part, s) : launch_wgrad<64, 32>(g, w, xin, gy->p, part, s); break;
-    case 128: r = w.pb == 16 ? launch_wgrad<128, 16>(g, w, xin, gy->p, part, s) : launch_wgrad<128, 32>(g, w, xin, gy->p, part, s); break;
-    case 192: r = w.pb == 16 ? launch_wgrad<192, 16>(g, w, xin, gy->p, part, s) : launch_wgrad<192, 32>(g, w, xin, gy->p, part, s); break;
-    default: r = w.pb == 16 ? launch_wgrad<256, 16>(g, w, xin, gy->p, part, s) : launch_wgrad<256, 32>(g, w, xin, gy->p, part, s); break;
+#define OMT_WG(BN_)                                                                                                                   \
+  (w.pair ? (w.pb == 16 ? launch_wgrad<BN_, 16, true>(g, w, xin, gy->p, part, s) : launch_wgrad<BN_, 32, true>(g, w, xin, gy->p, part, s)) \
+          : (w.pb == 16 ? launch_wgrad<BN_, 16>(g, w, xin, gy->p, part, s) : launch_wgrad<BN_, 32>(g, w, xin, gy->p, part, s)))
+    case 64: r = OMT_WG(64); break;
+    case 128: r = OMT_WG(128); break;
+    case 192: r = OMT_WG(192); break;
+    default: r = OMT_WG(256); break;
+#undef OMT_WG
   }
   if (r) return r;
   const int64_t total = (int64_t)g->co * g->ci * g->ks * g->ks;

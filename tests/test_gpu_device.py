@@ -415,7 +415,7 @@ def test_linear_layers_run_on_the_conv_gemm_kernels(omt):
         assert e(yd, y64.float()) <= TOL and e(xd.grad, x64.grad.float()) <= TOL, (batch, fin, fout)
         assert e(lind.weight.grad, lin64.weight.grad.float()) <= TOL and e(lind.bias.grad, lin64.bias.grad.float()) <= TOL, (batch, fin, fout)
         if fin % 32 == 0 and fout % 8 == 0:  # tensor-core geometries: forward, input gradient and weight gradient kernels all ran
-            assert sum(v for k, v in kc.items() if k.startswith(("conv_tc_1", "conv_tc_2"))) >= 2 and sum(v for k, v in kc.items() if k.startswith("wgrad_tc_1")) >= 1, kc
+            assert sum(v for k, v in kc.items() if k.startswith(("conv_tc_1", "conv_tc_2"))) >= 2 and sum(v for k, v in kc.items() if k.startswith(("wgrad_tc_1", "wgrad_tc_2"))) >= 1, kc
     # plain products in every combination of operand layouts, and addmm forms outside the nn.Linear case (served by the bridge)
     a, b = torch.randn(48, 40), torch.randn(40, 24)
     want = (a.double() @ b.double()).float()
@@ -723,7 +723,7 @@ def test_resnet50_compile_path_matches_cpu(omt, capsys):
     assert not omt.FALLBACKS, dict(omt.FALLBACKS)
     assert kc.get("bn_apply_add", 0) >= 16 * 6 and kc.get("sgd_multi", 0) == 6, kc  # the fused residual tails and one optimizer launch per step
     assert kc.get("bn_stats_from_partials", 0) >= 6, kc  # at this small batch only the stem is long and wide enough for statistics in the conv epilogue
-    assert sum(v for k, v in kc.items() if k.startswith(("conv_tc_1", "conv_tc_2", "wgrad_tc_1"))) >= 150 * 6, kc  # the convs ran on the tensor cores
+    assert sum(v for k, v in kc.items() if k.startswith(("conv_tc_1", "conv_tc_2", "wgrad_tc_1", "wgrad_tc_2"))) >= 150 * 6, kc  # the convs ran on the tensor cores
     assert abs(l_dev[0] - l_cpu[0]) <= 1e-5 * abs(l_cpu[0])
     names = [n for n, _ in ref.named_parameters()]
 

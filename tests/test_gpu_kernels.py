@@ -115,7 +115,7 @@ def test_tensor_core_path_vs_aten_and_exact_path(capi, shape):
         assert rel_err(2 * host(got_dw), dw) <= TOL
     capi.call("omt_sync")  # a tensor-core kernel that gave up on a barrier would be reported here
     after = capi.kernel_counts()
-    assert sum(v - before.get(k, 0) for k, v in after.items() if k.startswith(("conv_tc_1", "conv_tc_2", "conv_tc_window", "wgrad_tc_1"))) >= (2 + wg_tc if few else 4)
+    assert sum(v - before.get(k, 0) for k, v in after.items() if k.startswith(("conv_tc_1", "conv_tc_2", "conv_tc_window", "wgrad_tc_1", "wgrad_tc_2"))) >= (2 + wg_tc if few else 4)
     # the two paths agree with each other far inside the tolerance, with the cross terms in their own accumulator or not
     exact = capi.conv_fwd(xd, wd, bd, s, p, flags=capi.FORCE_SIMT | capi.EPI_RELU, cl=True)
     assert rel_err(host(capi.conv_fwd(xd, wd, bd, s, p, flags=capi.FORCE_TC | capi.EPI_RELU, cl=True)), host(exact)) <= 5e-5
