@@ -183,6 +183,21 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar), "h"((uint16_t)3)
                : "memory");
 }
+// A operand from tensor memory (lane = row, one column per tf32 element), B from shared memory
+__device__ __forceinline__ void umma_tf32_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// the calling warp's 32 lanes x 16 columns from registers: lane i writes v[0..15] to columns [col, col + 16) of its TMEM lane
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]),
+        "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+      : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -317,12 +332,15 @@ static_assert(sizeof(TcArgs) == 128, "TcArgs is a kernel parameter whose size is
 // epilogue cannot overlap the next tile's main loop, and with a short main loop that exposed epilogue is a large share.
 // PAIR: the CTA is one of a cta_group::2 pair and stages only its half of the B tile (BN / 2 weight rows), which leaves room
 // for a third stage at BN = 256.
-template <int BN, bool ACC1 = false, bool PAIR = false>
+// ATMEM (64-column tiles): the A operand reaches the tensor core from tensor memory. The accumulators of the two tiles in flight
+// take 256 of the 512 columns; the other 256 hold a ring of four A stages (32 columns of the hi operand, 32 of the lo).
+template <int BN, bool ACC1 = false, bool PAIR = false, bool ATMEM = false>
 struct Smem {
-  static constexpr int STAGES = PAIR ? 3 : (BN == 256 ? 2 : (BN == 128 ? 3 : 4));
+  static constexpr int A_RING_COL = 256, A_STAGE_COLS = 64;
+  static constexpr int STAGES = PAIR ? (BN == 256 ? 3 : 4) : (BN == 256 ? 2 : (BN == 128 ? 3 : 4));
   static constexpr int ACC_COLS = ACC1 ? BN : 2 * BN;          // TMEM columns of one tile's accumulator(s)
   static constexpr int ACC_BUFS = ACC_COLS == 512 ? 1 : 2;     // tiles in flight in TMEM (512 columns in total at most)
-  static constexpr int TMEM_COLS = ACC_BUFS * ACC_COLS;        // 256 or 512: a power of two
+  static constexpr int TMEM_COLS = ATMEM ? 512 : ACC_BUFS * ACC_COLS;  // 256 or 512: a power of two
   static constexpr int A_BYTES = BM * 128, B_BYTES = (PAIR ? BN / 2 : BN) * 128;
   static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
   static constexpr int EPI_OFF = STAGES * STAGE_BYTES;          // per epilogue warp one 32-row x 128-byte store buffer
@@ -370,12 +388,18 @@ __device__ __forceinline__ TileCoord decode_tile(const TcArgs& g, int t, int n_t
 //   free     [s]   both CTAs (multicast commit)               -> own producer
 //   acc full [b]   both CTAs (multicast commit)               -> own epilogue warps
 //   acc empty[b]   rank 0's barrier, epilogue warps of both   -> rank 0's MMA thread
-template <int BN, bool SPLITK, bool ACC1 = false, bool PAIR = false>
+// ATMEM (64-column tiles): these tiles do little arithmetic per byte of A, and A crossed shared memory five times per k-block
+// (TMA write, split read, lo write, two MMA reads): 104 KB per k-block against 384 tensor clocks. Here the split warps read
+// the A tile once (each lane its own row), and write hi and lo into tensor memory with tcgen05.st; the MMAs take A from
+// there (tcgen05.mma with a tensor-memory A operand), so shared memory sees 56 KB per k-block.
+template <int BN, bool SPLITK, bool ACC1 = false, bool PAIR = false, bool ATMEM = false>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_y,
                const TcArgs g) {
-  static_assert(!PAIR || (BN == 256 && !SPLITK), "CTA pairs: 256-column tiles, unsplit reduction");
-  using S = Smem<BN, ACC1, PAIR>;
+  static_assert(!PAIR || !SPLITK, "CTA pairs: unsplit reduction");
+  static_assert(!ATMEM || (BN == 64 && !SPLITK && !PAIR && !ACC1), "A from tensor memory: 64-column tiles");
+  using S = Smem<BN, ACC1, PAIR, ATMEM>;
+  static_assert(!ATMEM || S::STAGES * S::A_STAGE_COLS <= 512 - S::A_RING_COL, "the A ring must fit beside the accumulators");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const uint32_t smem_base = smem_u32(smem);
@@ -551,7 +575,12 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             // two accumulators: the cross terms (2^-11 of the result) go to columns [BN, 2BN) so that the truncation the
             // tensor core applies on every accumulate hits the main sum once per k-step instead of three times
             const uint32_t accumulate = ((kb - kb0) | k) ? 1u : 0u;  // the split's first MMA overwrites the accumulators
-            if constexpr (!ACC1 && 2 * BN <= 256) {
+            if constexpr (ATMEM) {
+              constexpr uint32_t idesc_wide = idesc_tf32(2 * BN);
+              const uint32_t a_t = tmem_base + S::A_RING_COL + s * S::A_STAGE_COLS + k * UMMA_K;  // hi; lo is 32 columns on
+              umma_tf32_ts(acc, a_t, b_hi + adv, idesc_wide, accumulate);
+              umma_tf32_ts(cross, a_t + 32, b_hi + adv, idesc, 1u);
+            } else if constexpr (!ACC1 && !PAIR && 2 * BN <= 256) {
               // B_lo follows B_hi in the stage, and the cross-term accumulator follows the main one in TMEM: one MMA of width
               // 2*BN over [B_hi; B_lo] yields a_hi*b_hi and a_hi*b_lo at once, reading A_hi from shared memory once instead of
               // twice (these narrow tiles are bound by operand reads from shared memory, not by the tensor pipe)
@@ -580,6 +609,32 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int s = it % S::STAGES, round = it / S::STAGES;
         ok = mbar_wait(BAR(s), round & 1, abort_flag);
         if (!ok) break;
+        if constexpr (ATMEM) {
+          // lane = row of the tile's lane quarter this warp may touch in tensor memory; with eight split warps two share a
+          // quarter and take 16 of the 32 k-columns each. A row is 128 bytes, its 16-byte chunks XOR-swizzled by (row & 7).
+          const int q = warp & 3, halves = split_warps / 4, half = halves == 1 ? 0 : (warp - 2) >> 2;
+          const int row = q * 32 + lane;
+          const uint8_t* rp = smem + s * S::STAGE_BYTES + row * 128;
+          const uint32_t tcol = tmem_base + ((uint32_t)(q * 32) << 16) + S::A_RING_COL + s * S::A_STAGE_COLS;
+          for (int c16 = half; c16 < 2; c16 += halves) {  // columns [16 * c16, 16 * c16 + 16)
+            uint32_t h[16], l[16];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+              const uint4 v = *reinterpret_cast<const uint4*>(rp + (((c16 * 4 + j) ^ (row & 7)) << 4));
+              uint4 hh;
+              const uint4 ll = split_lo(v, hh);
+              h[4 * j] = v.x; h[4 * j + 1] = v.y; h[4 * j + 2] = v.z; h[4 * j + 3] = v.w;  // (the tensor core reads the top 19 bits)
+              l[4 * j] = ll.x; l[4 * j + 1] = ll.y; l[4 * j + 2] = ll.z; l[4 * j + 3] = ll.w;
+            }
+            tmem_st16(tcol + 16 * c16, h);
+            tmem_st16(tcol + 32 + 16 * c16, l);
+          }
+          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive(BAR(S::STAGES + s));
+          continue;
+        }
         uint4* hi = reinterpret_cast<uint4*>(smem + s * S::STAGE_BYTES);
         uint4* lo = reinterpret_cast<uint4*>(smem + s * S::STAGE_BYTES + S::A_BYTES);
 #pragma unroll 4
@@ -867,14 +922,22 @@ static bool cta_pairs_enabled() {
   }();
   return on;
 }
+// 64-column tiles take their A operand from tensor memory unless OMARCHY_MAC_TORCH_A_TMEM=0 (read once)
+static bool a_tmem_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("OMARCHY_MAC_TORCH_A_TMEM");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
 // clusters of two CTAs of the pair kernel that can be resident at once (0: the launch form is not available), once per instantiation
-template <bool ACC1>
+template <int BN, bool ACC1>
 static int pair_clusters() {
-  using SP = Smem<256, ACC1, true>;
+  using SP = Smem<BN, ACC1, true>;
   static std::once_flag once;
   static int clusters = 0;
   std::call_once(once, [] {
-    auto kernel = conv_tc_kernel<256, false, ACC1, true>;
+    auto kernel = conv_tc_kernel<BN, false, ACC1, true>;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SP::TOTAL) != cudaSuccess) { cudaGetLastError(); return; }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3((unsigned)(sm_count() & ~1)); cfg.blockDim = dim3(TC_THREADS); cfg.dynamicSmemBytes = SP::TOTAL;
@@ -888,17 +951,17 @@ static int pair_clusters() {
   });
   return clusters;
 }
-template <bool ACC1>
+template <int BN, bool ACC1>
 static int launch_pair(const CUtensorMap& map_a, const CUtensorMap& map_w, const CUtensorMap& map_y, const TcArgs& a, int clusters, cudaStream_t s) {
-  using SP = Smem<256, ACC1, true>;
+  using SP = Smem<BN, ACC1, true>;
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(2u * (unsigned)clusters); cfg.blockDim = dim3(TC_THREADS); cfg.dynamicSmemBytes = SP::TOTAL; cfg.stream = s;
   cudaLaunchAttribute at{};
   at.id = cudaLaunchAttributeClusterDimension;
   at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
   cfg.attrs = &at; cfg.numAttrs = 1;
-  OMT_CUDA(cudaLaunchKernelEx(&cfg, conv_tc_kernel<256, false, ACC1, true>, map_a, map_w, map_y, a));
-  return check_launch(ACC1 ? "conv_tc_256x256_pair_acc1" : "conv_tc_256x256_pair");
+  OMT_CUDA(cudaLaunchKernelEx(&cfg, conv_tc_kernel<BN, false, ACC1, true>, map_a, map_w, map_y, a));
+  return check_launch(BN == 64 ? "conv_tc_256x64_pair" : (BN == 128 ? "conv_tc_256x128_pair" : (ACC1 ? "conv_tc_256x256_pair_acc1" : "conv_tc_256x256_pair")));
 }
 
 template <int BN>
@@ -909,7 +972,10 @@ int launch_tc(const TcProblem& p, const float* wsplit, const TcArgs& args, int s
   const bool acc1 = BN == 256 && splits == 1 && p.kh * p.kw * args.cblocks <= ACC1_MAX_KBLOCKS && !(args.flags & OMT_PRECISE_ACCUM);
   // two CTAs per 256 x 256 tile pair when the row tiles pair up (each CTA then stages half of the weight tile)
   int clusters = 0;
-  if (BN == 256 && splits == 1 && cdiv(args.M, BM) % 2 == 0 && p.kh * p.kw * args.cblocks >= PAIR_MIN_KBLOCKS && cta_pairs_enabled()) clusters = acc1 ? pair_clusters<true>() : pair_clusters<false>();
+  // (only the 256-column tiles: measured on 64- and 128-column tiles, pairs lose 30-40 % -- they give up the double-width MMA
+  // over [B_hi; B_lo] and pay the cross-SM barrier round trip on stages that are short already)
+  if (BN == 256 && splits == 1 && cdiv(args.M, BM) % 2 == 0 && p.kh * p.kw * args.cblocks >= PAIR_MIN_KBLOCKS && cta_pairs_enabled())
+    clusters = acc1 ? pair_clusters<256, true>() : pair_clusters<256, false>();
   const bool pair = clusters > 0;
   {
     cuuint64_t dims[4] = {(cuuint64_t)p.c, (cuuint64_t)p.iw, (cuuint64_t)p.ih, (cuuint64_t)p.n};
@@ -946,6 +1012,8 @@ int launch_tc(const TcProblem& p, const float* wsplit, const TcArgs& args, int s
     if (attr_err == cudaSuccess) attr_err = cudaFuncSetAttribute((conv_tc_kernel<BN, true>), cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
     if (attr_err == cudaSuccess && BN == 256)
       attr_err = cudaFuncSetAttribute((conv_tc_kernel<BN, false, BN == 256>), cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+    if (attr_err == cudaSuccess && BN == 64)
+      attr_err = cudaFuncSetAttribute((conv_tc_kernel<BN, false, false, false, BN == 64>), cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
   });
   OMT_CUDA(attr_err);
   TcArgs a = args;
@@ -969,12 +1037,14 @@ int launch_tc(const TcProblem& p, const float* wsplit, const TcArgs& args, int s
   const unsigned grid = (unsigned)std::min<int64_t>((int64_t)m_tiles * n_tiles * splits, sm_count());
   if (pair) {
     const int work = (m_tiles / 2) * n_tiles;
-    return acc1 ? launch_pair<true>(map_a, map_w, map_y, a, std::min(work, clusters), s) : launch_pair<false>(map_a, map_w, map_y, a, std::min(work, clusters), s);
+    return acc1 ? launch_pair<256, true>(map_a, map_w, map_y, a, std::min(work, clusters), s)
+                : launch_pair<256, false>(map_a, map_w, map_y, a, std::min(work, clusters), s);
   }
   if (splits > 1) conv_tc_kernel<BN, true><<<grid, TC_THREADS, S::TOTAL, s>>>(map_a, map_w, map_y, a);
   else if (acc1) conv_tc_kernel<BN, false, BN == 256><<<grid, TC_THREADS, S::TOTAL, s>>>(map_a, map_w, map_y, a);
+  else if (BN == 64 && a_tmem_enabled()) conv_tc_kernel<BN, false, false, false, BN == 64><<<grid, TC_THREADS, S::TOTAL, s>>>(map_a, map_w, map_y, a);
   else conv_tc_kernel<BN, false><<<grid, TC_THREADS, S::TOTAL, s>>>(map_a, map_w, map_y, a);
-  int r = check_launch(BN == 64 ? "conv_tc_128x64" : (BN == 128 ? "conv_tc_128x128" : (acc1 ? "conv_tc_128x256_acc1" : "conv_tc_128x256")));
+  int r = check_launch(BN == 64 ? (splits == 1 && a_tmem_enabled() ? "conv_tc_128x64_atmem" : "conv_tc_128x64") : (BN == 128 ? "conv_tc_128x128" : (acc1 ? "conv_tc_128x256_acc1" : "conv_tc_128x256")));
   if (r || splits == 1) return r;
   splitk_epilogue_kernel<<<(unsigned)cdiv((int64_t)a.M * a.N, 256), 256, 0, s>>>(a);
   return check_launch("conv_tc_splitk_epilogue");
