@@ -332,17 +332,19 @@ static_assert(sizeof(TcArgs) == 128, "TcArgs is a kernel parameter whose size is
 // epilogue cannot overlap the next tile's main loop, and with a short main loop that exposed epilogue is a large share.
 // PAIR: the CTA is one of a cta_group::2 pair and stages only its half of the B tile (BN / 2 weight rows), which leaves room
 // for a third stage at BN = 256.
-// ATMEM (64-column tiles): the A operand reaches the tensor core from tensor memory. The accumulators of the two tiles in flight
-// take 256 of the 512 columns; the other 256 hold a ring of four A stages (32 columns of the hi operand, 32 of the lo).
+// ATMEM (64-column tiles): the lo half of the A operand reaches the tensor core from tensor memory. The accumulators of the two
+// tiles in flight take 256 of the 512 columns; the other 256 hold one 32-column A_lo tile per stage. Without A_lo a stage is
+// 32 KB of shared memory, so the ring is six stages deep instead of four.
 template <int BN, bool ACC1 = false, bool PAIR = false, bool ATMEM = false>
 struct Smem {
-  static constexpr int A_RING_COL = 256, A_STAGE_COLS = 64;
-  static constexpr int STAGES = PAIR ? (BN == 256 ? 3 : 4) : (BN == 256 ? 2 : (BN == 128 ? 3 : 4));
+  static constexpr int A_RING_COL = 256, A_STAGE_COLS = 32;
+  static constexpr int STAGES = ATMEM ? 6 : (PAIR ? (BN == 256 ? 3 : 4) : (BN == 256 ? 2 : (BN == 128 ? 3 : 4)));
   static constexpr int ACC_COLS = ACC1 ? BN : 2 * BN;          // TMEM columns of one tile's accumulator(s)
   static constexpr int ACC_BUFS = ACC_COLS == 512 ? 1 : 2;     // tiles in flight in TMEM (512 columns in total at most)
   static constexpr int TMEM_COLS = ATMEM ? 512 : ACC_BUFS * ACC_COLS;  // 256 or 512: a power of two
   static constexpr int A_BYTES = BM * 128, B_BYTES = (PAIR ? BN / 2 : BN) * 128;
-  static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
+  static constexpr int B_OFF = ATMEM ? A_BYTES : 2 * A_BYTES;  // B_hi behind A_hi (and A_lo, when that lives in shared memory)
+  static constexpr int STAGE_BYTES = B_OFF + 2 * B_BYTES;
   static constexpr int EPI_OFF = STAGES * STAGE_BYTES;          // per epilogue warp one 32-row x 128-byte store buffer
   static constexpr int EPI_BYTES = 8 * 4096;
   static constexpr int BAR_OFF = EPI_OFF + EPI_BYTES;
@@ -388,10 +390,10 @@ __device__ __forceinline__ TileCoord decode_tile(const TcArgs& g, int t, int n_t
 //   free     [s]   both CTAs (multicast commit)               -> own producer
 //   acc full [b]   both CTAs (multicast commit)               -> own epilogue warps
 //   acc empty[b]   rank 0's barrier, epilogue warps of both   -> rank 0's MMA thread
-// ATMEM (64-column tiles): these tiles do little arithmetic per byte of A, and A crossed shared memory five times per k-block
-// (TMA write, split read, lo write, two MMA reads): 104 KB per k-block against 384 tensor clocks. Here the split warps read
-// the A tile once (each lane its own row), and write hi and lo into tensor memory with tcgen05.st; the MMAs take A from
-// there (tcgen05.mma with a tensor-memory A operand), so shared memory sees 56 KB per k-block.
+// ATMEM (64-column tiles): the split warps read the A tile once (each lane its own row) and put lo = tf32(x - hi) into tensor
+// memory with tcgen05.st instead of into shared memory; the cross-term MMA takes its A operand from there (tcgen05.mma with a
+// tensor-memory A). A stage then is A_hi + B in shared memory (32 KB), and the ring is six deep instead of four: these
+// tiles wait for operands, not for the tensor pipe or shared memory (measured: 36 % tensor-active, 42 % of the L1 peak).
 template <int BN, bool SPLITK, bool ACC1 = false, bool PAIR = false, bool ATMEM = false>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_y,
@@ -507,15 +509,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             tma_im2col_4d(stage, &map_a, BAR(s), cb * BKF, w0, h0, c.img0, (uint16_t)kx, (uint16_t)ky);
             const uint32_t bbar = LEADER(B_LOADED + s);
             const int row0 = c.n0 + (int)rank * (BN / 2);  // this CTA's half of the weight rows
-            tma_tile_3d_pair(stage + 2 * S::A_BYTES, &map_w, bbar, (tap * g.cblocks + cb) * BKF, row0, 0);
-            tma_tile_3d_pair(stage + 2 * S::A_BYTES + S::B_BYTES, &map_w, bbar, (tap * g.cblocks + cb) * BKF, row0, 1);
+            tma_tile_3d_pair(stage + S::B_OFF, &map_w, bbar, (tap * g.cblocks + cb) * BKF, row0, 0);
+            tma_tile_3d_pair(stage + S::B_OFF + S::B_BYTES, &map_w, bbar, (tap * g.cblocks + cb) * BKF, row0, 1);
             continue;
           }
           mbar_expect_tx(BAR(s), S::A_BYTES + 2 * S::B_BYTES);
           if (win_w) tma_tile_4d(stage, &map_a, BAR(s), cb * BKF, c.ox0, h0 + ky, c.img0);  // kw == 1: tap = filter row
           else tma_im2col_4d(stage, &map_a, BAR(s), cb * BKF, w0, h0, c.img0, (uint16_t)kx, (uint16_t)ky);
-          tma_tile_3d(stage + 2 * S::A_BYTES, &map_w, BAR(s), (tap * g.cblocks + cb) * BKF, c.n0, 0);
-          tma_tile_3d(stage + 2 * S::A_BYTES + S::B_BYTES, &map_w, BAR(s), (tap * g.cblocks + cb) * BKF, c.n0, 1);
+          tma_tile_3d(stage + S::B_OFF, &map_w, BAR(s), (tap * g.cblocks + cb) * BKF, c.n0, 0);
+          tma_tile_3d(stage + S::B_OFF + S::B_BYTES, &map_w, BAR(s), (tap * g.cblocks + cb) * BKF, c.n0, 1);
           if ((dbg & 16) && !win_w && t + (int)gridDim.x < total_tiles) {  // the same k-block of this CTA's next tile, into L2
             const TileCoord cn = decode_tile(g, t + gridDim.x, n_tiles, BN, splits, win_w);
             tma_prefetch_im2col_4d(&map_a, cb * BKF, cn.ox0 * g.stride + g.low_w, cn.oy0 * g.stride + g.low_h, cn.img0, (uint16_t)kx, (uint16_t)ky);
@@ -567,7 +569,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t stage = smem_base + s * S::STAGE_BYTES;
           const uint64_t a_hi = smem_desc_sw128(stage), a_lo = smem_desc_sw128(stage + S::A_BYTES);
-          const uint64_t b_hi = smem_desc_sw128(stage + 2 * S::A_BYTES), b_lo = smem_desc_sw128(stage + 2 * S::A_BYTES + S::B_BYTES);
+          const uint64_t b_hi = smem_desc_sw128(stage + S::B_OFF), b_lo = smem_desc_sw128(stage + S::B_OFF + S::B_BYTES);
 #pragma unroll
           for (int k = 0; k < BKF / UMMA_K; k++) {
             if (dbg & 8) break;
@@ -577,9 +579,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const uint32_t accumulate = ((kb - kb0) | k) ? 1u : 0u;  // the split's first MMA overwrites the accumulators
             if constexpr (ATMEM) {
               constexpr uint32_t idesc_wide = idesc_tf32(2 * BN);
-              const uint32_t a_t = tmem_base + S::A_RING_COL + s * S::A_STAGE_COLS + k * UMMA_K;  // hi; lo is 32 columns on
-              umma_tf32_ts(acc, a_t, b_hi + adv, idesc_wide, accumulate);
-              umma_tf32_ts(cross, a_t + 32, b_hi + adv, idesc, 1u);
+              umma_tf32(acc, a_hi + adv, b_hi + adv, idesc_wide, accumulate);  // A_hi is the tile TMA wrote: from shared memory
+              umma_tf32_ts(cross, tmem_base + S::A_RING_COL + s * S::A_STAGE_COLS + k * UMMA_K, b_hi + adv, idesc, 1u);
             } else if constexpr (!ACC1 && !PAIR && 2 * BN <= 256) {
               // B_lo follows B_hi in the stage, and the cross-term accumulator follows the main one in TMEM: one MMA of width
               // 2*BN over [B_hi; B_lo] yields a_hi*b_hi and a_hi*b_lo at once, reading A_hi from shared memory once instead of
@@ -617,17 +618,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           const uint8_t* rp = smem + s * S::STAGE_BYTES + row * 128;
           const uint32_t tcol = tmem_base + ((uint32_t)(q * 32) << 16) + S::A_RING_COL + s * S::A_STAGE_COLS;
           for (int c16 = half; c16 < 2; c16 += halves) {  // columns [16 * c16, 16 * c16 + 16)
-            uint32_t h[16], l[16];
+            uint32_t l[16];
 #pragma unroll
             for (int j = 0; j < 4; j++) {
               const uint4 v = *reinterpret_cast<const uint4*>(rp + (((c16 * 4 + j) ^ (row & 7)) << 4));
               uint4 hh;
               const uint4 ll = split_lo(v, hh);
-              h[4 * j] = v.x; h[4 * j + 1] = v.y; h[4 * j + 2] = v.z; h[4 * j + 3] = v.w;  // (the tensor core reads the top 19 bits)
               l[4 * j] = ll.x; l[4 * j + 1] = ll.y; l[4 * j + 2] = ll.z; l[4 * j + 3] = ll.w;
             }
-            tmem_st16(tcol + 16 * c16, h);
-            tmem_st16(tcol + 32 + 16 * c16, l);
+            tmem_st16(tcol + 16 * c16, l);
           }
           asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
           asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -922,7 +921,8 @@ static bool cta_pairs_enabled() {
   }();
   return on;
 }
-// 64-column tiles take their A operand from tensor memory unless OMARCHY_MAC_TORCH_A_TMEM=0 (read once)
+static_assert(Smem<64, false, false, true>::TOTAL == Smem<64>::TOTAL, "both 64-column kernels are launched with the same shared-memory size");
+// 64-column tiles take their A_lo operand from tensor memory unless OMARCHY_MAC_TORCH_A_TMEM=0 (read once)
 static bool a_tmem_enabled() {
   static const bool on = [] {
     const char* e = getenv("OMARCHY_MAC_TORCH_A_TMEM");
@@ -1446,7 +1446,11 @@ int launch_window(const OmtConvGeo* g, const WinPlan& w, const float* xs, const 
   }
   static std::once_flag attr_once;
   static cudaError_t attr_err = cudaSuccess;
-  std::call_once(attr_once, [] { attr_err = cudaFuncSetAttribute((conv_tc_kernel<BN, false>), cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL); });
+  std::call_once(attr_once, [] {
+    attr_err = cudaFuncSetAttribute((conv_tc_kernel<BN, false>), cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+    if (attr_err == cudaSuccess && BN == 64)
+      attr_err = cudaFuncSetAttribute((conv_tc_kernel<BN, false, false, false, BN == 64>), cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+  });
   OMT_CUDA(attr_err);
   TcArgs a = args;
   alignas(64) CUtensorMap map_y = map_w;
@@ -1462,7 +1466,8 @@ int launch_window(const OmtConvGeo* g, const WinPlan& w, const float* xs, const 
   OMT_REQUIRE(!(a.flags & OMT_EPI_BNSTATS) || a.store_mode == 2, "OMT_EPI_BNSTATS needs a dense channels-last output");
   const int m_tiles = g->n * w.tiles_x * w.tiles_y, n_tiles = (int)cdiv(a.N, BN);
   const unsigned grid = (unsigned)std::min<int64_t>((int64_t)m_tiles * n_tiles, sm_count());
-  conv_tc_kernel<BN, false><<<grid, TC_THREADS, S::TOTAL, s>>>(map_a, map_w, map_y, a);
+  if (BN == 64 && a_tmem_enabled()) conv_tc_kernel<BN, false, false, false, BN == 64><<<grid, TC_THREADS, S::TOTAL, s>>>(map_a, map_w, map_y, a);
+  else conv_tc_kernel<BN, false><<<grid, TC_THREADS, S::TOTAL, s>>>(map_a, map_w, map_y, a);
   return check_launch(BN == 64 ? "conv_tc_window_128x64" : (BN == 128 ? "conv_tc_window_128x128" : "conv_tc_window_128x256"));
 }
 
