@@ -880,7 +880,11 @@ int pick_bn(const TcProblem& p) {
   // (128 x 256 tiles with a short reduction use one accumulator per tile and two TMEM buffers, so their epilogue overlaps the
   // next tile like that of the 128 x 128 tiles, and A is read half as often: measured 0.344 -> 0.295 ms on 64 -> 256 1x1 at 56^2)
   int64_t mt = cdiv((int64_t)p.n * p.oh * p.ow, BM);
-  return (mt * cdiv(p.rows, 256) >= sm_count()) ? 256 : 128;
+  if (mt * cdiv(p.rows, 256) < sm_count()) return 128;
+  // tile quantisation: rounds of the persistent loop with either width; a 128 x 256 tile costs about 1.8 tiles of 128 x 128
+  // (e.g. 196 tiles of 256 columns on 148 SMs pay 2 rounds for 1.3; 392 of 128 columns pay 3 for 2.6)
+  const int64_t r256 = cdiv(mt * cdiv(p.rows, 256), sm_count()), r128 = cdiv(mt * cdiv(p.rows, 128), sm_count());
+  return 10 * r128 < 18 * r256 ? 128 : 256;
 }
 
 // split-K plan: only when the output tiles leave most SMs idle and the reduction is long enough to share
