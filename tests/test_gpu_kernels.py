@@ -120,7 +120,7 @@ def test_tensor_core_path_vs_aten_and_exact_path(capi, shape):
     exact = capi.conv_fwd(xd, wd, bd, s, p, flags=capi.FORCE_SIMT | capi.EPI_RELU, cl=True)
     assert rel_err(host(capi.conv_fwd(xd, wd, bd, s, p, flags=capi.FORCE_TC | capi.EPI_RELU, cl=True)), host(exact)) <= 5e-5
     assert rel_err(host(capi.conv_fwd(xd, wd, bd, s, p, flags=capi.FORCE_TC | capi.EPI_RELU | capi.PRECISE_ACCUM, cl=True)), host(exact)) <= 5e-5
-    if n >= 32:
+    if n == 32:  # (the n = 40 shape is split into 128-column tiles: fewer rounds of the persistent loop on 148 SMs)
         acc1 = lambda kc: sum(v for k, v in kc.items() if k.endswith("_acc1"))  # single-accumulator tiles, one CTA or a CTA pair
         assert acc1(after) > acc1(before), after
 
