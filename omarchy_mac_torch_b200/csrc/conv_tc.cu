@@ -31,6 +31,7 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <cstdint>
 #include <cstdlib>
 #include <vector>
 #include <mutex>
@@ -1526,11 +1527,13 @@ WgPlan plan_wgrad(const OmtConvGeo* g) {
   } else {
     w.cblocks = (int)cdiv(g->ci, BKF); w.cpad = w.cblocks * BKF; w.chunks = g->ks * g->ks * w.cblocks;
   }
-  // tile width: the one that pads the 32-column chunks least (18 chunks of a 64-channel 3x3 layer: 3 x 192 columns, not
-  // 3 x 256 with the last tile a quarter full; measured 0.83 -> 0.62 ms there); the wider on ties
+  // tile width: the widest that pads the 32-column chunks (nearly) least (18 chunks of a 64-channel 3x3 layer: 3 x 192 columns,
+  // not 3 x 256 with the last tile a quarter full; measured 0.83 -> 0.76 ms there)
+  int64_t least = INT64_MAX;
+  for (int bn : {64, 128, 192, 256}) least = std::min<int64_t>(least, cdiv(w.chunks, bn / 32) * bn);
   w.bn = 64;
-  for (int bn : {128, 192, 256})
-    if (cdiv(w.chunks, bn / 32) * bn <= cdiv(w.chunks, w.bn / 32) * w.bn) w.bn = bn;
+  for (int bn : {128, 192, 256})  // (a wider tile may pad up to 15 % more: AlexNet conv1's 22 chunks run faster as 3 x 256 than as 11 x 64)
+    if (cdiv(w.chunks, bn / 32) * bn * 100 <= least * 115) w.bn = bn;
   const int64_t tiles = cdiv(g->co, BM) * cdiv(w.chunks, w.bn / 32);
   const int per_tile = w.bn / 32;
   // CTA pairs: two co tiles share the x columns, each CTA staging half of them (full tiles only, not the window mode)
