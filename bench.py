@@ -544,11 +544,12 @@ def time_steps(fn, steps, warmup, world, flush):
 
 def secondary(peaks):
     """Short measurements of the other named targets, carried beside the headline so that one run records them: the
-    AlexNet-conv1 layer through the C ABI (TFLOP/s of fwd+dgrad+wgrad against the burst 3xTF32 peak), the ResNet-18 batch-32
-    step (ms) and the bandwidth-bound kernel table (GB/s against the measured copy bandwidth). Same timing rules as the
+    AlexNet-conv1 layer through the C ABI (TFLOP/s of fwd+dgrad+wgrad against the burst 3xTF32 peak), the PlainCNN, ResNet-18
+    and MobileNetV3 training steps (ms, kernels per step) and the bandwidth-bound kernel table (GB/s against the measured copy bandwidth). Same timing rules as the
     headline (warm-up, CUDA events, L2 flushed where the working set is smaller than L2)."""
     out = {}
-    for key, name, steps in (("conv1", "conv1", 30), ("resnet18", "resnet18", 30), ("hbm", "hbm", 1)):
+    for key, name, steps in (("conv1", "conv1", 30), ("plaincnn", "plaincnn", 30), ("resnet18", "resnet18", 30), ("mobilenetv3", "mobilenetv3", 20),
+                             ("hbm", "hbm", 1)):
         try:
             w = WORKLOADS[name]()
             w.setup_gpu(seed=0, world=1)
