@@ -126,7 +126,9 @@ def test_tensor_core_path_vs_aten_and_exact_path(capi, shape):
 
 
 @pytest.mark.parametrize("shape,cl_out", [((4, 64, 96, 14, 3, 1, 1), True), ((2, 32, 64, 16, 1, 2, 0), True), ((2, 64, 64, 16, 3, 2, 1), True),
-                                          ((2, 32, 40, 15, 3, 1, 1), False), ((2, 64, 256, 4, 3, 1, 1), True)])
+                                          ((2, 32, 40, 15, 3, 1, 1), False), ((2, 64, 256, 4, 3, 1, 1), True),
+                                          # 256-column tiles on CTA pairs: one accumulator (8 k-blocks) and two (72 k-blocks)
+                                          ((32, 256, 256, 28, 1, 1, 0), True), ((32, 256, 256, 28, 3, 1, 1), True)])
 def test_input_gradient_accumulates_in_the_epilogue(capi, shape, cl_out):
     """OMT_EPI_ACCUM: dx += conv^T(gy, w) (TMA reduce-add for dense channels-last outputs, read-add-write for stride phases
     and NCHW outputs) against a separate input gradient plus add; a geometry outside the tensor-core path is refused."""
