@@ -15,6 +15,8 @@ those graphs to the fused `omt::` ops, and the graph runs op by op on the device
   4. chains of elementwise ops (add/mul/relu/sigmoid/hardswish/..., their backward forms, scalars folded in) that only
      feed one another                                   -> omt.fused_pointwise (one kernel, one pass over memory)
 
+  6. num_batches_tracked + 1 of all BatchNorm layers -> one aten._foreach_add (one launch instead of one per layer)
+
   5. _log_softmax -> nll_loss_forward (what F.cross_entropy lowers to) -> omt.softmax_nll, and in the backward graph
      nll_loss_backward -> _log_softmax_backward_data -> omt.softmax_nll_backward: the loss is two launches per step
 
@@ -489,6 +491,26 @@ def fuse_softmax_nll(graph):
     return done
 
 
+def fuse_step_counters(graph):
+    """Pass 6: `num_batches_tracked + 1` of every BatchNorm layer (an int64 scalar graph input each) as one _foreach_add."""
+    adds = []
+    for n in graph.nodes:
+        if not (_is(n, aten.add.Tensor) and len(n.args) == 2 and n.args[1] == 1 and not n.kwargs):
+            continue
+        src, v = n.args[0], _meta(n.args[0])
+        if (isinstance(src, Node) and src.op == "placeholder" and isinstance(v, torch.Tensor) and v.dtype == torch.int64 and v.dim() == 0
+                and (_ANY_DEVICE or v.device.type == DEVICE)):
+            adds.append(n)
+    if len(adds) < 2:
+        return 0
+    with graph.inserting_before(adds[0]):  # every operand is a graph input, so the first add's place is as good as any
+        fused = graph.call_function(aten._foreach_add.Scalar, ([n.args[0] for n in adds], 1))
+    for i, n in enumerate(adds):
+        n.replace_all_uses_with(_getitem_after(graph, n, fused, i, n.meta))
+        graph.erase_node(n)
+    return len(adds)
+
+
 def rewrite(gm):
     """Apply the passes to a GraphModule in place; returns {pass: rewrites}."""
     g = gm.graph
@@ -496,6 +518,7 @@ def rewrite(gm):
              "bn_add_relu_backward": fuse_bn_add_relu_backward(g), "conv_epilogue": fuse_conv_epilogues(g),
              "conv_bn_train": fuse_conv_bn_train(g), "dgrad_accumulate": fuse_dgrad_accumulate(g)}
     stats["softmax_nll"] = fuse_softmax_nll(g)
+    stats["step_counters"] = fuse_step_counters(g)
     stats["pointwise"] = fuse_pointwise(g)
     g.eliminate_dead_code()
     g.lint()

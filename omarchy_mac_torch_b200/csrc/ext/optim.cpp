@@ -65,7 +65,23 @@ static void foreach_add_scalar_(at::TensorList self, const at::Scalar& scalar) {
   at::_foreach_add_(alias, scalar);
 }
 
+// The functional form: the compile backend gathers the step counters of all BatchNorm layers of a graph (num_batches_tracked
+// + 1, one tiny launch each otherwise) into one call.
+static std::vector<Tensor> foreach_add_scalar(at::TensorList self, const at::Scalar& scalar) {
+  std::vector<Tensor> alias;
+  alias.reserve(self.size());
+  for (const Tensor& t : self) {
+    NEED(is_dev(t), "device tensors");
+    alias.push_back(cuda_alias(t));
+  }
+  std::vector<Tensor> out;
+  out.reserve(self.size());
+  for (const Tensor& t : at::_foreach_add(alias, scalar)) out.push_back(wrap_cuda(t));
+  return out;
+}
+
 TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
+  OMT_IMPL(m, _foreach_add_Scalar, foreach_add_scalar);
   OMT_IMPL(m, _foreach_add__Scalar, foreach_add_scalar_);
   OMT_IMPL(m, _fused_sgd_, fused_sgd_);
   OMT_IMPL(m, _fused_adam_, fused_adam_);

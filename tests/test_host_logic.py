@@ -238,3 +238,32 @@ def test_cross_entropy_becomes_the_fused_pair(pkg, monkeypatch, reduction, weigh
     assert sum(s["softmax_nll"] for s in seen) == 2, seen
     assert "omt.softmax_nll.default" in targets and "omt.softmax_nll_backward.default" in targets
     assert not any("nll_loss" in s or "_log_softmax" in s for s in targets), targets
+
+
+def test_step_counters_of_all_batch_norm_layers_advance_in_one_op(pkg, monkeypatch):
+    """Pass 6 on a CPU graph: the `num_batches_tracked + 1` of every BatchNorm layer become one aten._foreach_add; the counters
+    and the outputs equal the unfused model's, also over a second step."""
+    from torch._dynamo.backends.common import aot_autograd
+    from functorch.compile import make_boxed_func
+    from omarchy_mac_torch_b200 import compile as C
+    monkeypatch.setattr(C, "_ANY_DEVICE", True)
+    seen, targets = [], []
+
+    def compiler(gm, _inputs):
+        seen.append(C.rewrite(gm))
+        targets.extend(str(n.target) for n in gm.graph.nodes if n.op == "call_function")
+        return make_boxed_func(gm.forward)
+
+    backend = aot_autograd(fw_compiler=compiler, bw_compiler=compiler, inference_compiler=compiler)
+    torch.manual_seed(0)
+    ref = torch.nn.Sequential(torch.nn.Conv2d(3, 8, 3, padding=1, bias=False), torch.nn.BatchNorm2d(8), torch.nn.ReLU(),
+                              torch.nn.Conv2d(8, 8, 3, padding=1, bias=False), torch.nn.BatchNorm2d(8), torch.nn.ReLU(),
+                              torch.nn.Conv2d(8, 4, 1), torch.nn.BatchNorm2d(4))
+    mod = copy.deepcopy(ref)
+    fn = torch.compile(mod, backend=backend)
+    x = torch.randn(2, 3, 8, 8)
+    for _ in range(2):
+        assert torch.allclose(fn(x), ref(x), rtol=1e-5, atol=1e-6)
+    assert seen[0]["step_counters"] == 3 and "aten._foreach_add.Scalar" in targets
+    assert [int(v) for k, v in mod.state_dict().items() if "num_batches" in k] == [2, 2, 2]
+    assert all(torch.allclose(a, b, rtol=1e-5, atol=1e-6) for a, b in zip(mod.state_dict().values(), ref.state_dict().values()))
