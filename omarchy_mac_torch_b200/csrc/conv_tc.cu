@@ -403,6 +403,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   static_assert(!ATMEM || (BN == 64 && !SPLITK && !PAIR && !ACC1), "A from tensor memory: 64-column tiles");
   using S = Smem<BN, ACC1, PAIR, ATMEM>;
   static_assert(!ATMEM || S::STAGES * S::A_STAGE_COLS <= 512 - S::A_RING_COL, "the A ring must fit beside the accumulators");
+  // k-blocks per barrier hand-off. A narrow tile's k-block is a few hundred tensor clocks, and the load -> split -> MMA -> free
+  // chain costs about as much again in wake-ups, so the 64-column tiles move two k-blocks per hand-off: the ring of S::STAGES
+  // k-block buffers is then RING groups of KPS, with one set of barriers per group.
+  constexpr int KPS = ATMEM ? 2 : 1, RING = S::STAGES / KPS;
+  static_assert(S::STAGES % KPS == 0, "whole groups");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const uint32_t smem_base = smem_u32(smem);
@@ -497,9 +502,23 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int t = tile_of(i);
         const TileCoord c = decode_tile(g, t, n_tiles, BN, splits, win_w);
         const int w0 = c.ox0 * g.stride + g.low_w, h0 = c.oy0 * g.stride + g.low_h;
-        for (int kb = kb_begin(t), kbe = kb_end(t); kb < kbe; kb++, it++) {
-          const int s = it % S::STAGES, round = it / S::STAGES;
+        for (int kb = kb_begin(t), kbe = kb_end(t); kb < kbe; kb += KPS, it++) {
+          const int s = it % RING, round = it / RING;
           if (round > 0 && !mbar_wait(BAR(2 * S::STAGES + s), (round - 1) & 1, abort_flag)) { ok = false; break; }
+          if constexpr (KPS > 1) {  // a group of up to KPS k-blocks behind one "loaded" barrier
+            const int nk = min(KPS, kbe - kb);
+            mbar_expect_tx(BAR(s), nk * (S::A_BYTES + 2 * S::B_BYTES));
+            for (int j = 0; j < nk; j++) {
+              const int tap = (kb + j) / g.cblocks, cb = (kb + j) - tap * g.cblocks;
+              const int ky = tap / g.kw, kx = tap - ky * g.kw;
+              const uint32_t stage = smem_base + (s * KPS + j) * S::STAGE_BYTES;
+              if (win_w) tma_tile_4d(stage, &map_a, BAR(s), cb * BKF, c.ox0, h0 + ky, c.img0);
+              else tma_im2col_4d(stage, &map_a, BAR(s), cb * BKF, w0, h0, c.img0, (uint16_t)kx, (uint16_t)ky);
+              tma_tile_3d(stage + S::B_OFF, &map_w, BAR(s), (tap * g.cblocks + cb) * BKF, c.n0, 0);
+              tma_tile_3d(stage + S::B_OFF + S::B_BYTES, &map_w, BAR(s), (tap * g.cblocks + cb) * BKF, c.n0, 1);
+            }
+            continue;
+          }
           const int tap = kb / g.cblocks, cb = kb - tap * g.cblocks;
           const int ky = tap / g.kw, kx = tap - ky * g.kw;
           const uint32_t stage = smem_base + s * S::STAGE_BYTES;
@@ -526,14 +545,14 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
       }
       if (*abort_flag) {  // drain: let the copies already in flight land before the CTA exits (bounded)
-        for (int k = max(0, it - S::STAGES); k < it; k++) {
+        for (int k = max(0, it - RING); k < it; k++) {
           const long long t0 = clock64();
-          while (!mbar_try(BAR(k % S::STAGES), (k / S::STAGES) & 1) && clock64() - t0 < WAIT_BUDGET_CLOCKS) {}
+          while (!mbar_try(BAR(k % RING), (k / RING) & 1) && clock64() - t0 < WAIT_BUDGET_CLOCKS) {}
         }
       } else if (PAIR) {
         // the last stages' "free" arrivals come from the other SM's commit: let them land in this CTA's barriers before it exits
-        for (int k = max(0, it - S::STAGES); k < it; k++)
-          if (!mbar_wait(BAR(2 * S::STAGES + k % S::STAGES), (k / S::STAGES) & 1, abort_flag)) break;
+        for (int k = max(0, it - RING); k < it; k++)
+          if (!mbar_wait(BAR(2 * S::STAGES + k % RING), (k / RING) & 1, abort_flag)) break;
       }
     }
   } else if (warp == 1) {
@@ -562,12 +581,30 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const uint32_t acc = tmem_base + b * S::ACC_COLS;
         const uint32_t cross = ACC1 ? acc : acc + BN;  // where the 2^-11-sized cross terms accumulate
         const int kb0 = kb_begin(t);
-        for (int kb = kb0, kbe = kb_end(t); kb < kbe; kb++, it++) {
-          const int s = it % S::STAGES, round = it / S::STAGES;
+        for (int kb = kb0, kbe = kb_end(t); kb < kbe; kb += KPS, it++) {
+          const int s = it % RING, round = it / RING;
           // (for a pair "split" also stands for "A loaded" in both CTAs: the split warps waited for it before they arrived)
           ok = mbar_wait<PAIR>(BAR(S::STAGES + s), round & 1, abort_flag) && mbar_wait(BAR(PAIR ? B_LOADED + s : s), round & 1, abort_flag);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          if constexpr (KPS > 1) {  // (ATMEM) the group's k-blocks one after the other, one commit
+            constexpr uint32_t idesc_wide = idesc_tf32(2 * BN);
+            const int nk = min(KPS, kbe - kb);
+            for (int j = 0; j < nk; j++) {
+              const int ss = s * KPS + j;
+              const uint32_t stage = smem_base + ss * S::STAGE_BYTES;
+              const uint64_t a_hi = smem_desc_sw128(stage), b_hi = smem_desc_sw128(stage + S::B_OFF);
+#pragma unroll
+              for (int k = 0; k < BKF / UMMA_K; k++) {
+                const uint64_t adv = (uint64_t)((k * UMMA_K * 4) >> 4);
+                const uint32_t accumulate = ((kb + j - kb0) | k) ? 1u : 0u;
+                umma_tf32(acc, a_hi + adv, b_hi + adv, idesc_wide, accumulate);  // A_hi is the tile TMA wrote: from shared memory
+                umma_tf32_ts(cross, tmem_base + S::A_RING_COL + ss * S::A_STAGE_COLS + k * UMMA_K, b_hi + adv, idesc, 1u);
+              }
+            }
+            commit(BAR(2 * S::STAGES + s));
+            continue;
+          }
           const uint32_t stage = smem_base + s * S::STAGE_BYTES;
           const uint64_t a_hi = smem_desc_sw128(stage), a_lo = smem_desc_sw128(stage + S::A_BYTES);
           const uint64_t b_hi = smem_desc_sw128(stage + S::B_OFF), b_lo = smem_desc_sw128(stage + S::B_OFF + S::B_BYTES);
@@ -578,11 +615,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             // two accumulators: the cross terms (2^-11 of the result) go to columns [BN, 2BN) so that the truncation the
             // tensor core applies on every accumulate hits the main sum once per k-step instead of three times
             const uint32_t accumulate = ((kb - kb0) | k) ? 1u : 0u;  // the split's first MMA overwrites the accumulators
-            if constexpr (ATMEM) {
-              constexpr uint32_t idesc_wide = idesc_tf32(2 * BN);
-              umma_tf32(acc, a_hi + adv, b_hi + adv, idesc_wide, accumulate);  // A_hi is the tile TMA wrote: from shared memory
-              umma_tf32_ts(cross, tmem_base + S::A_RING_COL + s * S::A_STAGE_COLS + k * UMMA_K, b_hi + adv, idesc, 1u);
-            } else if constexpr (!ACC1 && !PAIR && 2 * BN <= 256) {
+            if constexpr (!ACC1 && !PAIR && 2 * BN <= 256) {
               // B_lo follows B_hi in the stage, and the cross-term accumulator follows the main one in TMEM: one MMA of width
               // 2*BN over [B_hi; B_lo] yields a_hi*b_hi and a_hi*b_lo at once, reading A_hi from shared memory once instead of
               // twice (these narrow tiles are bound by operand reads from shared memory, not by the tensor pipe)
@@ -607,8 +640,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     bool ok = true;
     for (int i = work_first; i < work_items && ok; i += work_step) {
       const int t = tile_of(i);
-      for (int kb = kb_begin(t), kbe = kb_end(t); kb < kbe; kb++, it++) {
-        const int s = it % S::STAGES, round = it / S::STAGES;
+      for (int kb = kb_begin(t), kbe = kb_end(t); kb < kbe; kb += KPS, it++) {
+        const int s = it % RING, round = it / RING;
         ok = mbar_wait(BAR(s), round & 1, abort_flag);
         if (!ok) break;
         if constexpr (ATMEM) {
@@ -616,18 +649,22 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           // quarter and take 16 of the 32 k-columns each. A row is 128 bytes, its 16-byte chunks XOR-swizzled by (row & 7).
           const int q = warp & 3, halves = split_warps / 4, half = halves == 1 ? 0 : (warp - 2) >> 2;
           const int row = q * 32 + lane;
-          const uint8_t* rp = smem + s * S::STAGE_BYTES + row * 128;
-          const uint32_t tcol = tmem_base + ((uint32_t)(q * 32) << 16) + S::A_RING_COL + s * S::A_STAGE_COLS;
-          for (int c16 = half; c16 < 2; c16 += halves) {  // columns [16 * c16, 16 * c16 + 16)
-            uint32_t l[16];
+          const int nk = min(KPS, kbe - kb);
+          for (int jb = 0; jb < nk; jb++) {
+            const int ss = s * KPS + jb;
+            const uint8_t* rp = smem + ss * S::STAGE_BYTES + row * 128;
+            const uint32_t tcol = tmem_base + ((uint32_t)(q * 32) << 16) + S::A_RING_COL + ss * S::A_STAGE_COLS;
+            for (int c16 = half; c16 < 2; c16 += halves) {  // columns [16 * c16, 16 * c16 + 16)
+              uint32_t l[16];
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-              const uint4 v = *reinterpret_cast<const uint4*>(rp + (((c16 * 4 + j) ^ (row & 7)) << 4));
-              uint4 hh;
-              const uint4 ll = split_lo(v, hh);
-              l[4 * j] = ll.x; l[4 * j + 1] = ll.y; l[4 * j + 2] = ll.z; l[4 * j + 3] = ll.w;
+              for (int j = 0; j < 4; j++) {
+                const uint4 v = *reinterpret_cast<const uint4*>(rp + (((c16 * 4 + j) ^ (row & 7)) << 4));
+                uint4 hh;
+                const uint4 ll = split_lo(v, hh);
+                l[4 * j] = ll.x; l[4 * j + 1] = ll.y; l[4 * j + 2] = ll.z; l[4 * j + 3] = ll.w;
+              }
+              tmem_st16(tcol + 16 * c16, l);
             }
-            tmem_st16(tcol + 16 * c16, l);
           }
           asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
           asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
