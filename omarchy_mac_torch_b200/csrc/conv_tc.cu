@@ -583,8 +583,18 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int kb0 = kb_begin(t);
         for (int kb = kb0, kbe = kb_end(t); kb < kbe; kb += KPS, it++) {
           const int s = it % RING, round = it / RING;
-          // (for a pair "split" also stands for "A loaded" in both CTAs: the split warps waited for it before they arrived)
-          ok = mbar_wait<PAIR>(BAR(S::STAGES + s), round & 1, abort_flag) && mbar_wait(BAR(PAIR ? B_LOADED + s : s), round & 1, abort_flag);
+          // One CTA: the products that need only what TMA loaded (a_hi x b_hi, a_hi x b_lo) are issued as soon as the stage has
+          // landed, while the split warps still produce a_lo; the a_lo x b_hi products follow when "split" arrives. That takes the
+          // split out of the load -> split -> MMA -> free chain for two thirds of the tensor work.
+          // (For a pair "split" also stands for "A loaded" in both CTAs, so everything waits for it there.)
+          auto split_done = [&]() {
+            const bool r = mbar_wait<PAIR>(BAR(S::STAGES + s), round & 1, abort_flag);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            return r;
+          };
+          // (The 64-column tiles with two k-blocks per hand-off measured slower that way -- 0.430 against 0.403 ms on 64 -> 64
+          // 3x3 -- and wait for the split first, like the pairs.)
+          ok = (!(PAIR || KPS > 1) || split_done()) && mbar_wait(BAR(PAIR ? B_LOADED + s : s), round & 1, abort_flag);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           if constexpr (KPS > 1) {  // (ATMEM) the group's k-blocks one after the other, one commit
@@ -597,8 +607,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
               for (int k = 0; k < BKF / UMMA_K; k++) {
                 const uint64_t adv = (uint64_t)((k * UMMA_K * 4) >> 4);
-                const uint32_t accumulate = ((kb + j - kb0) | k) ? 1u : 0u;
-                umma_tf32(acc, a_hi + adv, b_hi + adv, idesc_wide, accumulate);  // A_hi is the tile TMA wrote: from shared memory
+                umma_tf32(acc, a_hi + adv, b_hi + adv, idesc_wide, ((kb + j - kb0) | k) ? 1u : 0u);  // A_hi is the tile TMA wrote: from shared memory
                 umma_tf32_ts(cross, tmem_base + S::A_RING_COL + ss * S::A_STAGE_COLS + k * UMMA_K, b_hi + adv, idesc, 1u);
               }
             }
@@ -608,6 +617,31 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           const uint32_t stage = smem_base + s * S::STAGE_BYTES;
           const uint64_t a_hi = smem_desc_sw128(stage), a_lo = smem_desc_sw128(stage + S::A_BYTES);
           const uint64_t b_hi = smem_desc_sw128(stage + S::B_OFF), b_lo = smem_desc_sw128(stage + S::B_OFF + S::B_BYTES);
+          if constexpr (!PAIR) {
+#pragma unroll
+            for (int k = 0; k < BKF / UMMA_K; k++) {
+              if (dbg & 8) break;
+              const uint64_t adv = (uint64_t)((k * UMMA_K * 4) >> 4);
+              const uint32_t accumulate = ((kb - kb0) | k) ? 1u : 0u;  // the split's first MMA overwrites the accumulators
+              if constexpr (!ACC1 && 2 * BN <= 256) {
+                // B_lo follows B_hi in the stage, and the cross-term accumulator follows the main one in TMEM: one MMA of width
+                // 2*BN over [B_hi; B_lo] yields a_hi*b_hi and a_hi*b_lo at once
+                umma_tf32(acc, a_hi + adv, b_hi + adv, idesc_tf32(2 * BN), accumulate);
+              } else {
+                umma_tf32(acc, a_hi + adv, b_hi + adv, idesc, accumulate);
+                umma_tf32(cross, a_hi + adv, b_lo + adv, idesc, ACC1 ? 1u : accumulate);
+              }
+            }
+            ok = split_done();
+            if (!ok) break;
+#pragma unroll
+            for (int k = 0; k < BKF / UMMA_K; k++) {
+              if (dbg & 8) break;
+              umma_tf32(cross, a_lo + (uint64_t)((k * UMMA_K * 4) >> 4), b_hi + (uint64_t)((k * UMMA_K * 4) >> 4), idesc, 1u);
+            }
+            commit(BAR(2 * S::STAGES + s));
+            continue;
+          }
 #pragma unroll
           for (int k = 0; k < BKF / UMMA_K; k++) {
             if (dbg & 8) break;
