@@ -989,14 +989,18 @@ bool dense_out(const TcArgs& a) {
          y.sn == (int64_t)a.oh * a.ow * a.N && a.N % 4 == 0 && (reinterpret_cast<uintptr_t>(y.p) & 15) == 0;
 }
 
-// CTA pairs are used unless OMARCHY_MAC_TORCH_CTA_PAIRS=0 (read once)
-static bool cta_pairs_enabled() {
-  static const bool on = [] {
+// OMARCHY_MAC_TORCH_CTA_PAIRS (read once): 0 = no CTA pairs, 1 (default) = in the weight gradient, 2 = also in forward / input
+// gradient. Measured on the ResNet-50 step: with the a_hi products issued ahead of the split, single-CTA forward / input
+// gradient tiles take 25.3 ms per step against 26.0 ms for pairs (which cannot issue ahead: rank 0 learns that the other
+// CTA's A tile has landed only through its split warps); the weight gradient takes 15.0 ms with pairs against 15.5.
+static int cta_pairs_mode() {
+  static const int mode = [] {
     const char* e = getenv("OMARCHY_MAC_TORCH_CTA_PAIRS");
-    return !(e && e[0] == '0');
+    return e && e[0] >= '0' && e[0] <= '2' ? e[0] - '0' : 1;
   }();
-  return on;
+  return mode;
 }
+static bool cta_pairs_enabled() { return cta_pairs_mode() >= 1; }
 static_assert(Smem<64, false, false, true>::TOTAL == Smem<64>::TOTAL, "both 64-column kernels are launched with the same shared-memory size");
 // 64-column tiles take their A_lo operand from tensor memory unless OMARCHY_MAC_TORCH_A_TMEM=0 (read once)
 static bool a_tmem_enabled() {
@@ -1050,7 +1054,7 @@ int launch_tc(const TcProblem& p, const float* wsplit, const TcArgs& args, int s
   int clusters = 0;
   // (only the 256-column tiles: measured on 64- and 128-column tiles, pairs lose 30-40 % -- they give up the double-width MMA
   // over [B_hi; B_lo] and pay the cross-SM barrier round trip on stages that are short already)
-  if (BN == 256 && splits == 1 && cdiv(args.M, BM) % 2 == 0 && p.kh * p.kw * args.cblocks >= PAIR_MIN_KBLOCKS && cta_pairs_enabled())
+  if (BN == 256 && splits == 1 && cdiv(args.M, BM) % 2 == 0 && p.kh * p.kw * args.cblocks >= PAIR_MIN_KBLOCKS && cta_pairs_mode() >= 2)
     clusters = acc1 ? pair_clusters<256, true>() : pair_clusters<256, false>();
   const bool pair = clusters > 0;
   {
@@ -1333,10 +1337,35 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
       for (int kb = 0; kb < kblocks && ok; kb++) {
         const int s = kb % S::STAGES, round = kb / S::STAGES;
         // (a pair's "split" barrier counts the split warps of both CTAs, each of which waited for its own loads)
+        const uint32_t stage = smem_base + s * S::STAGE_BYTES;
+        if constexpr (!PAIR) {
+          // one CTA: a_hi x b_hi needs only what TMA loaded and is issued while the split warps still work on the stage
+          ok = mbar_wait(BAR(s), round & 1, abort_flag);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+          for (int k = 0; k < PB / UMMA_K; k++) {
+            const uint32_t koff = k * 1024;
+            umma_tf32(tmem_acc, smem_desc_mn_sw128(stage + koff, S::CH), smem_desc_mn_sw128(stage + S::A_BYTES + koff, S::CH), idesc, (kb | k) ? 1u : 0u);
+          }
+          ok = mbar_wait(BAR(S::STAGES + s), round & 1, abort_flag);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+          for (int k = 0; k < PB / UMMA_K; k++) {
+            const uint32_t koff = k * 1024;
+            const uint64_t a_hi = smem_desc_mn_sw128(stage + koff, S::CH), a_lo = smem_desc_mn_sw128(stage + S::HALF + koff, S::CH);
+            const uint64_t b_hi = smem_desc_mn_sw128(stage + S::A_BYTES + koff, S::CH);
+            const uint64_t b_lo = smem_desc_mn_sw128(stage + S::HALF + S::A_BYTES + koff, S::CH);
+            umma_tf32(tmem_acc + BN, a_lo, b_hi, idesc, (kb | k) ? 1u : 0u);  // cross terms in their own accumulator
+            umma_tf32(tmem_acc + BN, a_hi, b_lo, idesc, 1u);
+          }
+          umma_commit(BAR(2 * S::STAGES + s));
+          continue;
+        }
         ok = mbar_wait<PAIR>(BAR(S::STAGES + s), round & 1, abort_flag) && (PAIR || mbar_wait(BAR(s), round & 1, abort_flag));
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t stage = smem_base + s * S::STAGE_BYTES;
 #pragma unroll
         for (int k = 0; k < PB / UMMA_K; k++) {
           const uint32_t koff = k * 1024;  // next group of 8 pixel rows
