@@ -1648,7 +1648,10 @@ WgPlan plan_wgrad(const OmtConvGeo* g) {
   const bool rect = !window && !matrix && g->ci % 32 == 0 && g->co % 32 == 0 && aligned_taps && g->stride <= 8;
   // x boxes per stage: 1 in matrix mode, per_tile / cpi in rectangle mode, per_tile in window / im2col mode
   const bool few_boxes = (matrix && g->co % 32 == 0) || (rect && per_cta / w.cpi <= 2);
-  const int PB = few_boxes && !w.pair ? 16 : 32;  // (a pair synchronises two SMs per stage: fewer, larger stages)
+  // 16-pixel stages (twice as many of them) only where 32-pixel ones would leave a ring of two: wide single-CTA tiles whose x
+  // operand is one box. Elsewhere a stage's barrier hand-offs cost more than the deeper ring gains (measured at batch 256:
+  // 64 -> 256 1x1 0.324 -> 0.269 ms, 128 -> 128 3x3 0.398 -> 0.332 with 32-pixel stages; 256 -> 64 1x1 0.261 -> 0.288 the other way).
+  const int PB = few_boxes && matrix && w.bn >= 192 && !w.pair ? 16 : 32;  // (a pair synchronises two SMs per stage: fewer, larger stages)
   w.pb = PB;
   int64_t total_blocks = cdiv((int64_t)g->n * g->oh * g->ow, PB);
   if (window) {
