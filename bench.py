@@ -43,9 +43,9 @@ L2_BYTES = 126 << 20
 # conv3x3_256_28_b128_tc_kernels_ncu_full.md): dram__bytes_read.sum + dram__bytes_write.sum per launch over the
 # algorithmic bytes of that launch (float32 x + y + w = 207.96 MB). Traffic grows with the activation bytes, so a step's
 # conv traffic is its algorithmic conv bytes per pass times these ratios.
-NCU_CONV_TRAFFIC = {"fwd": (107.8 + 60.7) / 207.96, "dgrad": (108.1 + 62.3) / 207.96, "wgrad": (205.8 + 4.3) / 207.96}
+NCU_CONV_TRAFFIC = {"fwd": (107.8 + 59.6) / 207.96, "dgrad": (108.0 + 60.3) / 207.96, "wgrad": (205.6 + 4.5) / 207.96}
 NCU_CONV_TRAFFIC_SOURCE = ("ncu dram__bytes_read.sum + dram__bytes_write.sum of conv_tc_kernel / wgrad_tc_kernel on the conv3x3 case "
-                           "(fwd 168.5, dgrad 170.4, wgrad 210.1 MB per launch; 208.0 MB algorithmic), scaled by algorithmic bytes per pass")
+                           "(fwd 167.4, dgrad 168.3, wgrad 210.1 MB per launch; 208.0 MB algorithmic), scaled by algorithmic bytes per pass")
 
 
 def conv_traffic(t, reps):
