@@ -1002,6 +1002,14 @@ static int cta_pairs_mode() {
 }
 static bool cta_pairs_enabled() { return cta_pairs_mode() >= 1; }
 static_assert(Smem<64, false, false, true>::TOTAL == Smem<64>::TOTAL, "both 64-column kernels are launched with the same shared-memory size");
+// the weight gradient of 3x3 layers with at most 64 output channels pairs taps unless OMARCHY_MAC_TORCH_TAP_PAIRS=0 (read once)
+static bool tap_pairs_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("OMARCHY_MAC_TORCH_TAP_PAIRS");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
 // 64-column tiles take their A_lo operand from tensor memory unless OMARCHY_MAC_TORCH_A_TMEM=0 (read once)
 static bool a_tmem_enabled() {
   static const bool on = [] {
@@ -1177,6 +1185,11 @@ struct WgArgs {
   //        shifted by the tap and zero-filled outside the image.
   // bit 3: with bit 2, "window" x operand for <= 4 input channels: the 32-float run (8 pixels x 4 channels) of a filter
   //        row out of the padded 4-channel staging copy, one box per (filter row, 32-float block) chunk; bw = 32.
+  // bit 4: with bit 2, "paired taps" for co <= 64 (3x3, stride 1, pad 1): the lower half of the 128-row gy tile would be empty,
+  //        so it holds gy shifted by one pixel to the right (zero past the row's end) and every x column gives two taps:
+  //        sum_p gy[p + 1] x[p + (ky, 1)] = sum_q gy[q] x[q + (ky, 0)] (the q at the row's start multiplies padding). The
+  //        tile's columns run over the six taps (ky, 1), (ky, 2) only ("virtual" chunks, `chunks`); the epilogue writes
+  //        rows 0-63 to those taps' columns and rows 64-127 of the (ky, 1) columns to the (ky, 0) columns.
   int mode;
   int total_blocks;  // pixel blocks in all
   int bw, bh, bn, tiles_x, tiles_y, cpi;
@@ -1185,7 +1198,8 @@ struct WgArgs {
   int co;
   int oh, ow, ks, stride, pad;
   int cblocks, cpad; // 32-channel blocks per tap
-  int chunks;        // ks * ks * cblocks: 32-wide column chunks of the output
+  int chunks;        // ks * ks * cblocks: 32-wide column chunks of the output (paired taps: 6 * cblocks, the columns computed)
+  int out_chunks;    // 32-wide column chunks of a row of `part`
   int blocks_per_slice;  // 32-pixel blocks per blockIdx.z
 };
 
@@ -1275,7 +1289,12 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
           const int tx = b % g.tiles_x, r1 = b / g.tiles_x, ty = r1 % g.tiles_y, tn = r1 / g.tiles_y;
           const int ox0 = tx * g.bw, oy0 = ty * g.bh, n0 = tn * g.bn;
           mbar_expect_tx(BAR(s), S::A_BYTES + nown * S::CH);
-          tma_tile_5d(stage, &map_g, BAR(s), 0, ox0, oy0, n0, co0 / 32);
+          if (g.mode & 16) {  // two boxes of two channel blocks: gy, and gy one pixel to the right
+            tma_tile_5d(stage, &map_g, BAR(s), 0, ox0, oy0, n0, 0);
+            tma_tile_5d(stage + 2 * S::CH, &map_g, BAR(s), 0, ox0 + 1, oy0, n0, 0);
+          } else {
+            tma_tile_5d(stage, &map_g, BAR(s), 0, ox0, oy0, n0, co0 / 32);
+          }
           if (g.mode & 8) {
             for (int j = 0; j < nown; j++) {
               const int chunk = chunk0 + j, ky = chunk / g.cblocks, blk = chunk - ky * g.cblocks;
@@ -1284,7 +1303,8 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
           } else {
             for (int j = 0; j < nown; j += g.cpi) {
               const int chunk = chunk0 + j, tap = chunk / g.cblocks, cb = chunk - tap * g.cblocks;
-              const int ky = tap / g.ks, kx = tap - ky * g.ks;
+              int ky = tap / g.ks, kx = tap - ky * g.ks;
+              if (g.mode & 16) { ky = tap >> 1; kx = 1 + (tap & 1); }
               tma_tile_5d(stage + S::A_BYTES + j * S::CH, &map_x, BAR(s), 0, ox0 * g.stride - g.pad + kx, oy0 * g.stride - g.pad + ky, n0, cb);
             }
           }
@@ -1410,8 +1430,9 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     if (ok) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int q = warp & 3, half = (warp - 2) >> 2;
-      const int row = co0 + q * 32 + lane;
-      const int kcols = g.chunks * 32;
+      const bool paired = g.mode & 16;
+      const int row = paired ? ((q & 1) * 32 + lane) : (co0 + q * 32 + lane);  // paired taps: rows 64-127 are the same channels again
+      const int kcols = g.out_chunks * 32;
       float* prow = g.part + ((int64_t)blockIdx.z * g.co + row) * kcols;
 #pragma unroll 1
       for (int c = half; c < BN / 32; c += 2) {
@@ -1426,7 +1447,13 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
           for (int j = 0; j < 32; j++) v[j] = 0u;  // a slice with no pixels contributes zeros
         }
         if (row >= g.co || c >= nchunks) continue;
-        float4* dst = reinterpret_cast<float4*>(prow + ((int)blockIdx.y * (BN / 32) + c) * 32);  // (chunk0 is this CTA's first LOADED chunk)
+        int out_chunk = (int)blockIdx.y * (BN / 32) + c;  // (chunk0 is this CTA's first LOADED chunk)
+        if (paired) {  // column chunk of tap (ky, 1 + sel): rows 0-63 are that tap, rows 64-127 the tap to its left
+          const int vt = out_chunk / g.cblocks, cb = out_chunk - vt * g.cblocks, ky = vt >> 1, sel = vt & 1;
+          if (q >= 2 && sel) continue;  // (ky, 1) again: rows 0-63 of the other column chunk own it
+          out_chunk = (ky * 3 + (q >= 2 ? 0 : 1 + sel)) * g.cblocks + cb;
+        }
+        float4* dst = reinterpret_cast<float4*>(prow + out_chunk * 32);
 #pragma unroll
         for (int j = 0; j < 32; j += 4)
           dst[j / 4] = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
@@ -1611,6 +1638,7 @@ int run_window_fwd(const OmtConvGeo* g, const OmtAct* x, const float* w, const f
 struct WgPlan {
   int bn, slices, blocks_per_slice, cblocks, cpad, chunks;
   int mode, total_blocks, bw, bh, bn_img, tiles_x, tiles_y, cpi;
+  int vchunks;          // column chunks the tiles run over: `chunks`, or with paired taps (mode bit 4) those of six taps
   int pb;               // pixels per stage (16 or 32)
   bool pair;            // clusters of two CTAs (cta_group::2)
   int win_kb;           // window mode: 32-float blocks per filter row
@@ -1627,19 +1655,24 @@ WgPlan plan_wgrad(const OmtConvGeo* g) {
   } else {
     w.cblocks = (int)cdiv(g->ci, BKF); w.cpad = w.cblocks * BKF; w.chunks = g->ks * g->ks * w.cblocks;
   }
+  // at most 64 output channels leave half of the 128-row tile empty: a 3x3 stride-1 layer fills it with gy shifted by one pixel
+  // and computes six taps' columns instead of nine (64 -> 64 3x3 at 56^2, batch 256: 0.72 ms as nine taps)
+  const bool paired_taps = !window && g->ks == 3 && g->stride == 1 && g->pad == 1 && g->co <= 64 && g->co % 32 == 0 && g->ci % 32 == 0 &&
+                           tap_pairs_enabled();
+  w.vchunks = paired_taps ? 6 * w.cblocks : w.chunks;
   // tile width: the widest that pads the 32-column chunks (nearly) least (18 chunks of a 64-channel 3x3 layer: 3 x 192 columns,
   // not 3 x 256 with the last tile a quarter full; measured 0.83 -> 0.76 ms there)
   int64_t least = INT64_MAX;
-  for (int bn : {64, 128, 192, 256}) least = std::min<int64_t>(least, cdiv(w.chunks, bn / 32) * bn);
+  for (int bn : {64, 128, 192, 256}) least = std::min<int64_t>(least, cdiv(w.vchunks, bn / 32) * bn);
   w.bn = 64;
   for (int bn : {128, 192, 256})  // (a wider tile may pad up to 15 % more: AlexNet conv1's 22 chunks run faster as 3 x 256 than as 11 x 64)
-    if (cdiv(w.chunks, bn / 32) * bn * 100 <= least * 115) w.bn = bn;
-  const int64_t tiles = cdiv(g->co, BM) * cdiv(w.chunks, w.bn / 32);
+    if (cdiv(w.vchunks, bn / 32) * bn * 100 <= least * 115) w.bn = bn;
+  const int64_t tiles = cdiv(g->co, BM) * cdiv(w.vchunks, w.bn / 32);
   const int per_tile = w.bn / 32;
   // CTA pairs: two co tiles share the x columns, each CTA staging half of them (full tiles only, not the window mode)
   // (measured at batch 256: 256-column tiles +5..16 %, e.g. 256 -> 256 3x3 at 14^2 0.310 -> 0.271 ms; 128-column tiles lose a
   // third, their stages being too short to hide the cross-SM barrier round trip)
-  w.pair = !window && w.bn >= 192 && cdiv(g->co, BM) % 2 == 0 && w.chunks % per_tile == 0 && per_tile % 2 == 0 && g->co % 32 == 0 &&
+  w.pair = !window && !paired_taps && w.bn >= 192 && cdiv(g->co, BM) % 2 == 0 && w.chunks % per_tile == 0 && per_tile % 2 == 0 && g->co % 32 == 0 &&
            g->ci % 32 == 0 && cta_pairs_enabled();
   const int per_cta = w.pair ? per_tile / 2 : per_tile;
   w.cpi = std::gcd(w.cblocks, per_cta);  // 32-channel blocks one x box carries: a box never straddles two taps, two tiles or two CTAs
@@ -1661,7 +1694,7 @@ WgPlan plan_wgrad(const OmtConvGeo* g) {
     w.mode = 2 | (g->co % 32 == 0 ? 1 : 0);
   } else if (rect) {
     // PB-pixel rectangles bw x bh x bn (powers of two) that waste the fewest pixels; wider rows on ties
-    w.mode = 4;
+    w.mode = paired_taps ? 4 | 16 : 4;
     double best = -1;
     for (int bw = PB; bw >= 1; bw >>= 1)
       for (int bh = PB / bw; bh >= 1; bh >>= 1) {
@@ -1740,7 +1773,7 @@ int launch_wgrad(const OmtConvGeo* g, const WgPlan& w, const float* x, const flo
   if (w.mode & 4) {
     cuuint64_t dims[5] = {32, (cuuint64_t)g->ow, (cuuint64_t)g->oh, (cuuint64_t)g->n, (cuuint64_t)(g->co / 32)};
     cuuint64_t strides[4] = {(cuuint64_t)g->co * 4, (cuuint64_t)g->ow * g->co * 4, (cuuint64_t)g->oh * g->ow * g->co * 4, 128};
-    cuuint32_t box[5] = {BKF, (cuuint32_t)w.bw, (cuuint32_t)w.bh, (cuuint32_t)w.bn_img, 4}, estr[5] = {1, 1, 1, 1, 1};
+    cuuint32_t box[5] = {BKF, (cuuint32_t)w.bw, (cuuint32_t)w.bh, (cuuint32_t)w.bn_img, (w.mode & 16) ? 2u : 4u}, estr[5] = {1, 1, 1, 1, 1};
     OMT_ENCODE(g_encode_tiled(&map_g, F32, 5, (void*)gy, dims, strides, box, estr, IL, SW, L2P, FILL), "cuTensorMapEncodeTiled (gy rectangles)");
   } else if (w.mode & 1) {  // gy [P, co]: the 128-channel tile as one box of four 32-channel blocks
     cuuint64_t dims[3] = {32, (cuuint64_t)P, (cuuint64_t)(g->co / 32)};
@@ -1761,8 +1794,8 @@ int launch_wgrad(const OmtConvGeo* g, const WgPlan& w, const float* x, const flo
   a.mode = w.mode; a.total_blocks = w.total_blocks;
   a.bw = w.bw; a.bh = w.bh; a.bn = w.bn_img; a.tiles_x = w.tiles_x; a.tiles_y = w.tiles_y; a.cpi = w.cpi;
   a.part = part; a.P = g->n * g->oh * g->ow; a.co = g->co; a.oh = g->oh; a.ow = g->ow; a.ks = g->ks; a.stride = g->stride; a.pad = g->pad;
-  a.cblocks = w.cblocks; a.cpad = w.cpad; a.chunks = w.chunks; a.blocks_per_slice = w.blocks_per_slice;
-  dim3 grid((unsigned)cdiv(g->co, BM), (unsigned)cdiv(w.chunks, BN / 32), (unsigned)w.slices);
+  a.cblocks = w.cblocks; a.cpad = w.cpad; a.chunks = w.vchunks; a.out_chunks = w.chunks; a.blocks_per_slice = w.blocks_per_slice;
+  dim3 grid((unsigned)cdiv(g->co, BM), (unsigned)cdiv(w.vchunks, BN / 32), (unsigned)w.slices);
   if constexpr (PAIR) {
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = grid; cfg.blockDim = dim3(WG_THREADS); cfg.dynamicSmemBytes = S::TOTAL; cfg.stream = s;
@@ -1774,6 +1807,7 @@ int launch_wgrad(const OmtConvGeo* g, const WgPlan& w, const float* x, const flo
     return check_launch(BN == 64 ? "wgrad_tc_256x64_pair" : (BN == 128 ? "wgrad_tc_256x128_pair" : (BN == 192 ? "wgrad_tc_256x192_pair" : "wgrad_tc_256x256_pair")));
   }
   wgrad_tc_kernel<BN, PB><<<grid, WG_THREADS, S::TOTAL, s>>>(map_x, map_g, a);
+  if (w.mode & 16) return check_launch(BN == 64 ? "wgrad_tc_128x64_tap_pairs" : (BN == 128 ? "wgrad_tc_128x128_tap_pairs" : (BN == 192 ? "wgrad_tc_128x192_tap_pairs" : "wgrad_tc_128x256_tap_pairs")));
   return check_launch(BN == 64 ? "wgrad_tc_128x64" : (BN == 128 ? "wgrad_tc_128x128" : (BN == 192 ? "wgrad_tc_128x192" : "wgrad_tc_128x256")));
 }
 

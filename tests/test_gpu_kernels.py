@@ -241,6 +241,29 @@ def test_resnet50_layer_geometries_on_tensor_cores(capi, layer):
     capi.call("omt_sync")
 
 
+@pytest.mark.parametrize("shape", [(3, 64, 64, 13, 9), (2, 32, 64, 56, 56), (5, 96, 32, 7, 20), (4, 64, 64, 33, 1), (2, 128, 64, 1, 17)],
+                         ids=lambda s: "n%d_ci%d_co%d_%dx%d" % s)
+def test_weight_gradient_of_narrow_3x3_layers_pairs_taps(capi, shape):
+    """3x3 stride-1 pad-1 layers with at most 64 output channels: the weight-gradient kernel fills the empty half of its 128-row
+    gy tile with gy shifted by one pixel, so that one x column yields two taps. Image edges (the shifted operand's zero fill
+    and the padding the identity relies on), widths of one pixel and pixel counts that do not fill a block, against float64
+    aten on the CPU."""
+    n, ci, co, h, w_ = shape
+    torch.manual_seed(n * 1000 + ci + co + h)
+    x, gy = torch.randn(n, ci, h, w_), torch.randn(n, co, h, w_)
+    wt = torch.zeros(co, ci, 3, 3, dtype=torch.float64)
+    _, _, dw, _ = oracle.aten_conv(x.double(), wt, None, 1, 1, gy.double())
+    before = capi.kernel_counts()
+    got = host(capi.conv_wgrad(dev(x, True), dev(gy, True), 3, 1, 1, flags=capi.FORCE_TC))
+    after = capi.kernel_counts()
+    pairs = lambda kc: sum(v for k, v in kc.items() if k.endswith("_tap_pairs"))
+    assert pairs(after) == pairs(before) + 1, after
+    assert rel_err(got, dw.float().numpy()) <= TOL
+    for tap in range(9):  # per tap: an error in one tap's columns must not hide behind the others' magnitude
+        assert rel_err(got[:, :, tap // 3, tap % 3], dw[:, :, tap // 3, tap % 3].float().numpy()) <= 2 * TOL, tap
+    capi.call("omt_sync")
+
+
 def test_alexnet_conv1_full_size_per_tensor_vs_aten(capi):
     """AlexNet conv1 at full size (x [16,3,224,224], w [64,3,11,11], stride 4, pad 2; tools/gemm_bench.py:26-38): y, dx, dw
     and db each compared per tensor with aten's convolution and convolution_backward on the CPU, on the library's default
