@@ -33,6 +33,7 @@
 #include <algorithm>
 #include <cstdint>
 #include <cstdlib>
+#include <cstring>
 #include <vector>
 #include <mutex>
 #include <numeric>
@@ -1185,11 +1186,13 @@ struct WgArgs {
   //        shifted by the tap and zero-filled outside the image.
   // bit 3: with bit 2, "window" x operand for <= 4 input channels: the 32-float run (8 pixels x 4 channels) of a filter
   //        row out of the padded 4-channel staging copy, one box per (filter row, 32-float block) chunk; bw = 32.
-  // bit 4: with bit 2, "paired taps" for co <= 64 (3x3, stride 1, pad 1): the lower half of the 128-row gy tile would be empty,
-  //        so it holds gy shifted by one pixel to the right (zero past the row's end) and every x column gives two taps:
-  //        sum_p gy[p + 1] x[p + (ky, 1)] = sum_q gy[q] x[q + (ky, 0)] (the q at the row's start multiplies padding). The
-  //        tile's columns run over the six taps (ky, 1), (ky, 2) only ("virtual" chunks, `chunks`); the epilogue writes
-  //        rows 0-63 to those taps' columns and rows 64-127 of the (ky, 1) columns to the (ky, 0) columns.
+  // bit 4: with bit 2, "paired taps" for co <= 64: the lower half of the 128-row gy tile would be empty, so it holds gy
+  //        shifted by one pixel (shift_x) or one row (shift_y), zero outside the image, and every x column gives two taps:
+  //        sum_p gy[p + 1] x[p * stride + k] = sum_q gy[q] x[q * stride + (k - stride)]. The tile's columns run over the
+  //        taps `top[v]` only ("virtual" chunks, `chunks`); the epilogue writes rows 0-63 to the columns of top[v] and rows
+  //        64-127 to those of bot[v] (< 0: none). The q = 0 term of the second sum has no p: it must multiply padding
+  //        (3x3, stride 1, pad 1 pairing (ky, 1) with (ky, 0)), or the pixel blocks start one row above the image
+  //        (shift_y; window mode, where top/bot are filter rows).
   int mode;
   int total_blocks;  // pixel blocks in all
   int bw, bh, bn, tiles_x, tiles_y, cpi;
@@ -1200,6 +1203,8 @@ struct WgArgs {
   int cblocks, cpad; // 32-channel blocks per tap
   int chunks;        // ks * ks * cblocks: 32-wide column chunks of the output (paired taps: 6 * cblocks, the columns computed)
   int out_chunks;    // 32-wide column chunks of a row of `part`
+  int8_t top[16], bot[16];
+  int8_t shift_x, shift_y;
   int blocks_per_slice;  // 32-pixel blocks per blockIdx.z
 };
 
@@ -1287,24 +1292,24 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         if (g.mode & 4) {
           const int b = blk_begin + kb;
           const int tx = b % g.tiles_x, r1 = b / g.tiles_x, ty = r1 % g.tiles_y, tn = r1 / g.tiles_y;
-          const int ox0 = tx * g.bw, oy0 = ty * g.bh, n0 = tn * g.bn;
+          const int ox0 = tx * g.bw, oy0 = ty * g.bh - ((g.mode & 16) ? g.shift_y : 0), n0 = tn * g.bn;
           mbar_expect_tx(BAR(s), S::A_BYTES + nown * S::CH);
-          if (g.mode & 16) {  // two boxes of two channel blocks: gy, and gy one pixel to the right
+          if (g.mode & 16) {  // two boxes of two channel blocks: gy, and gy one pixel to the right / one row down
             tma_tile_5d(stage, &map_g, BAR(s), 0, ox0, oy0, n0, 0);
-            tma_tile_5d(stage + 2 * S::CH, &map_g, BAR(s), 0, ox0 + 1, oy0, n0, 0);
+            tma_tile_5d(stage + 2 * S::CH, &map_g, BAR(s), 0, ox0 + g.shift_x, oy0 + g.shift_y, n0, 0);
           } else {
             tma_tile_5d(stage, &map_g, BAR(s), 0, ox0, oy0, n0, co0 / 32);
           }
           if (g.mode & 8) {
             for (int j = 0; j < nown; j++) {
-              const int chunk = chunk0 + j, ky = chunk / g.cblocks, blk = chunk - ky * g.cblocks;
+              const int chunk = chunk0 + j, v = chunk / g.cblocks, blk = chunk - v * g.cblocks;
+              const int ky = (g.mode & 16) ? g.top[v] : v;
               tma_tile_4d(stage + S::A_BYTES + j * S::CH, &map_x, BAR(s), blk * BKF, ox0, oy0 * g.stride + ky - g.pad, n0);
             }
           } else {
             for (int j = 0; j < nown; j += g.cpi) {
-              const int chunk = chunk0 + j, tap = chunk / g.cblocks, cb = chunk - tap * g.cblocks;
-              int ky = tap / g.ks, kx = tap - ky * g.ks;
-              if (g.mode & 16) { ky = tap >> 1; kx = 1 + (tap & 1); }
+              const int chunk = chunk0 + j, v = chunk / g.cblocks, cb = chunk - v * g.cblocks;
+              const int tap = (g.mode & 16) ? g.top[v] : v, ky = tap / g.ks, kx = tap - ky * g.ks;
               tma_tile_5d(stage + S::A_BYTES + j * S::CH, &map_x, BAR(s), 0, ox0 * g.stride - g.pad + kx, oy0 * g.stride - g.pad + ky, n0, cb);
             }
           }
@@ -1448,10 +1453,10 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         }
         if (row >= g.co || c >= nchunks) continue;
         int out_chunk = (int)blockIdx.y * (BN / 32) + c;  // (chunk0 is this CTA's first LOADED chunk)
-        if (paired) {  // column chunk of tap (ky, 1 + sel): rows 0-63 are that tap, rows 64-127 the tap to its left
-          const int vt = out_chunk / g.cblocks, cb = out_chunk - vt * g.cblocks, ky = vt >> 1, sel = vt & 1;
-          if (q >= 2 && sel) continue;  // (ky, 1) again: rows 0-63 of the other column chunk own it
-          out_chunk = (ky * 3 + (q >= 2 ? 0 : 1 + sel)) * g.cblocks + cb;
+        if (paired) {  // rows 0-63 are the tap (or filter row) that was loaded, rows 64-127 the one a gy shift before it
+          const int v = out_chunk / g.cblocks, cb = out_chunk - v * g.cblocks, t = q >= 2 ? g.bot[v] : g.top[v];
+          if (t < 0) continue;
+          out_chunk = t * g.cblocks + cb;
         }
         float4* dst = reinterpret_cast<float4*>(prow + out_chunk * 32);
 #pragma unroll
@@ -1638,7 +1643,8 @@ int run_window_fwd(const OmtConvGeo* g, const OmtAct* x, const float* w, const f
 struct WgPlan {
   int bn, slices, blocks_per_slice, cblocks, cpad, chunks;
   int mode, total_blocks, bw, bh, bn_img, tiles_x, tiles_y, cpi;
-  int vchunks;          // column chunks the tiles run over: `chunks`, or with paired taps (mode bit 4) those of six taps
+  int vchunks;          // column chunks the tiles run over: `chunks`, or with paired taps (mode bit 4) those of the taps loaded
+  int8_t top[16], bot[16], shift_x, shift_y;  // paired taps: per loaded tap (window mode: filter row) the outputs of the two tile halves
   int pb;               // pixels per stage (16 or 32)
   bool pair;            // clusters of two CTAs (cta_group::2)
   int win_kb;           // window mode: 32-float blocks per filter row
@@ -1655,11 +1661,32 @@ WgPlan plan_wgrad(const OmtConvGeo* g) {
   } else {
     w.cblocks = (int)cdiv(g->ci, BKF); w.cpad = w.cblocks * BKF; w.chunks = g->ks * g->ks * w.cblocks;
   }
-  // at most 64 output channels leave half of the 128-row tile empty: a 3x3 stride-1 layer fills it with gy shifted by one pixel
-  // and computes six taps' columns instead of nine (64 -> 64 3x3 at 56^2, batch 256: 0.72 ms as nine taps)
-  const bool paired_taps = !window && g->ks == 3 && g->stride == 1 && g->pad == 1 && g->co <= 64 && g->co % 32 == 0 && g->ci % 32 == 0 &&
-                           tap_pairs_enabled();
-  w.vchunks = paired_taps ? 6 * w.cblocks : w.chunks;
+  // at most 64 output channels leave half of the 128-row tile empty. A 3x3 stride-1 layer fills it with gy shifted by one pixel
+  // and computes six taps' columns instead of nine (64 -> 64 3x3 at 56^2, batch 256: 0.74 -> 0.51 ms); the window mode with gy
+  // shifted by one row, which pairs filter row ky with ky - stride (7x7 stride 2: rows 6, 5, 2, 1 instead of seven).
+  const bool narrow = g->co <= 64 && g->co % 32 == 0 && tap_pairs_enabled();
+  const bool paired_taps = narrow && !window && g->ks == 3 && g->stride == 1 && g->pad == 1 && g->ci % 32 == 0;
+  const bool paired_rows = narrow && window && g->ks <= 16 && g->stride < g->ks;
+  w.vchunks = w.chunks;
+  if (paired_taps) {
+    for (int ky = 0, v = 0; ky < 3; ky++) {
+      w.top[v] = (int8_t)(ky * 3 + 1); w.bot[v++] = (int8_t)(ky * 3);
+      w.top[v] = (int8_t)(ky * 3 + 2); w.bot[v++] = -1;
+    }
+    w.shift_x = 1;
+    w.vchunks = 6 * w.cblocks;
+  } else if (paired_rows) {  // from the last filter row up: a row nobody yields yet is loaded and yields the row `stride` above it
+    bool have[16] = {};
+    int v = 0;
+    for (int ky = g->ks - 1; ky >= 0; ky--) {
+      if (have[ky]) continue;
+      w.top[v] = (int8_t)ky; w.bot[v] = (int8_t)(ky - g->stride >= 0 ? ky - g->stride : -1);
+      if (ky - g->stride >= 0) have[ky - g->stride] = true;
+      v++;
+    }
+    w.shift_y = 1;
+    w.vchunks = v * w.cblocks;
+  }
   // tile width: the widest that pads the 32-column chunks (nearly) least (18 chunks of a 64-channel 3x3 layer: 3 x 192 columns,
   // not 3 x 256 with the last tile a quarter full; measured 0.83 -> 0.76 ms there)
   int64_t least = INT64_MAX;
@@ -1688,7 +1715,7 @@ WgPlan plan_wgrad(const OmtConvGeo* g) {
   w.pb = PB;
   int64_t total_blocks = cdiv((int64_t)g->n * g->oh * g->ow, PB);
   if (window) {
-    w.mode = 4 | 8;
+    w.mode = paired_rows ? 4 | 8 | 16 : 4 | 8;
     w.bw = PB; w.bh = 1; w.bn_img = 1;
   } else if (matrix) {
     w.mode = 2 | (g->co % 32 == 0 ? 1 : 0);
@@ -1708,7 +1735,7 @@ WgPlan plan_wgrad(const OmtConvGeo* g) {
     w.mode = g->co % 32 == 0 ? 1 : 0;
   }
   if (w.mode & 4) {
-    w.tiles_x = (int)cdiv(g->ow, w.bw); w.tiles_y = (int)cdiv(g->oh, w.bh);
+    w.tiles_x = (int)cdiv(g->ow, w.bw); w.tiles_y = (int)cdiv(g->oh + w.shift_y, w.bh);  // (a row shift: blocks from row -1)
     total_blocks = (int64_t)w.tiles_x * w.tiles_y * cdiv(g->n, w.bn_img);
   }
   w.total_blocks = (int)total_blocks;
@@ -1794,7 +1821,8 @@ int launch_wgrad(const OmtConvGeo* g, const WgPlan& w, const float* x, const flo
   a.mode = w.mode; a.total_blocks = w.total_blocks;
   a.bw = w.bw; a.bh = w.bh; a.bn = w.bn_img; a.tiles_x = w.tiles_x; a.tiles_y = w.tiles_y; a.cpi = w.cpi;
   a.part = part; a.P = g->n * g->oh * g->ow; a.co = g->co; a.oh = g->oh; a.ow = g->ow; a.ks = g->ks; a.stride = g->stride; a.pad = g->pad;
-  a.cblocks = w.cblocks; a.cpad = w.cpad; a.chunks = w.vchunks; a.out_chunks = w.chunks; a.blocks_per_slice = w.blocks_per_slice;
+  a.cblocks = w.cblocks; a.cpad = w.cpad; a.chunks = w.vchunks; a.out_chunks = w.chunks;
+  memcpy(a.top, w.top, sizeof(a.top)); memcpy(a.bot, w.bot, sizeof(a.bot)); a.shift_x = w.shift_x; a.shift_y = w.shift_y; a.blocks_per_slice = w.blocks_per_slice;
   dim3 grid((unsigned)cdiv(g->co, BM), (unsigned)cdiv(w.vchunks, BN / 32), (unsigned)w.slices);
   if constexpr (PAIR) {
     cudaLaunchConfig_t cfg{};

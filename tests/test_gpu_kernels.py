@@ -264,6 +264,31 @@ def test_weight_gradient_of_narrow_3x3_layers_pairs_taps(capi, shape):
     capi.call("omt_sync")
 
 
+@pytest.mark.parametrize("shape", [(2, 3, 64, 7, 2, 3, 37, 41), (3, 3, 32, 5, 1, 2, 19, 23), (2, 4, 64, 3, 2, 1, 16, 9), (2, 1, 64, 11, 4, 2, 63, 63),
+                                   (2, 3, 64, 3, 1, 0, 12, 40), (1, 2, 32, 4, 3, 0, 31, 10)],
+                         ids=lambda s: "n%d_ci%d_co%d_k%d_s%d_p%d_%dx%d" % s)
+def test_weight_gradient_of_first_layers_pairs_filter_rows(capi, shape):
+    """At most 4 input and at most 64 output channels (network stems): the weight-gradient kernel fills the empty half of its
+    gy tile with gy shifted by one row, so that the x columns of filter row ky also yield row ky - stride; its pixel blocks
+    start one row above the image so that the shifted operand's first row has a partner. Strides 1-4, with and without
+    padding, odd image sizes; per filter row against float64 aten on the CPU."""
+    n, ci, co, ks, s_, p_, h, w_ = shape
+    torch.manual_seed(n + ci + co + ks + h)
+    oh, ow = (h + 2 * p_ - ks) // s_ + 1, (w_ + 2 * p_ - ks) // s_ + 1
+    x, gy = torch.randn(n, ci, h, w_), torch.randn(n, co, oh, ow)
+    wt = torch.zeros(co, ci, ks, ks, dtype=torch.float64)
+    _, _, dw, _ = oracle.aten_conv(x.double(), wt, None, s_, p_, gy.double())
+    before = capi.kernel_counts()
+    got = host(capi.conv_wgrad(dev(x), dev(gy, True), ks, s_, p_, flags=capi.FORCE_TC))
+    after = capi.kernel_counts()
+    pairs = lambda kc: sum(v for k, v in kc.items() if k.endswith("_tap_pairs"))
+    assert pairs(after) == pairs(before) + 1, after
+    assert rel_err(got, dw.float().numpy()) <= TOL
+    for ky in range(ks):
+        assert rel_err(got[:, :, ky], dw[:, :, ky].float().numpy()) <= 2 * TOL, ky
+    capi.call("omt_sync")
+
+
 def test_alexnet_conv1_full_size_per_tensor_vs_aten(capi):
     """AlexNet conv1 at full size (x [16,3,224,224], w [64,3,11,11], stride 4, pad 2; tools/gemm_bench.py:26-38): y, dx, dw
     and db each compared per tensor with aten's convolution and convolution_backward on the CPU, on the library's default
