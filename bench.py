@@ -707,7 +707,7 @@ def main():
         line["rank_param_spread"] = spread
     if args.workload == "resnet50" and world == 1 and not args.no_secondary:
         line["secondary"] = secondary(peaks)
-    if not args.no_cpu_baseline:
+    if not args.no_cpu_baseline and world == 1:  # (multi-GPU runs hold their GPUs while this runs: single-GPU line only)
         # bounded sample of the same workload at its full size: one untimed step, then as many as fit in ~20 s (at least 2)
         cms, csteps, cwarm, cores = cpu_arm(wl, 1, 200, budget_s=20.0)
         line["cpu_baseline"] = {"value": wl.value(cms), "unit": wl.unit, "cores": cores, "kind": "reference", "ms_per_step": cms,
