@@ -394,12 +394,17 @@ class Train:
         return self._g
 
     def e2e_step(self):
-        if self.graph:  # refill the static batch from pinned memory, replay, read the loss back
-            g = self._graphed()
-            self.x.copy_(self.xh, non_blocking=True)
-            self.y.copy_(self.yh, non_blocking=True)
-            return g().item()
         return self._e2e_prefetch()
+
+    def _run(self, x, y):
+        """One step on the device batch (x, y): the eager / compiled step, or a device-to-device copy into the recorded step's
+        static batch followed by its replay."""
+        if self.graph:
+            g = self._graphed()
+            self.x.copy_(x)
+            self.y.copy_(y)
+            return g()
+        return self._step(x, y)
 
     def _e2e_prefetch(self):
         """One step fed from pinned host memory, as a prefetching data loader feeds it: this step's batch was copied to one
@@ -417,7 +422,7 @@ class Train:
         torch.cuda.current_stream().wait_event(pf["ready"][k])
         self._prefetch(1 - k)
         x, y = pf["bufs"][k]
-        loss = self._step(x, y)
+        loss = self._run(x, y)
         pf["freed"][k].record(torch.cuda.current_stream())
         pf["i"] += 1
         return loss.item()  # device->host read of the loss
@@ -453,6 +458,10 @@ class Train:
 
     def roofline(self, ms, peaks):
         # conv GEMMs measured live: two extra steps with the library's per-call CUDA-event timing switched on
+        if self.graph:  # the timed steps were replays: let the eager steps fill the allocator's cache for this stream first
+            for _ in range(2):
+                self._step(self.x, self.y)
+            torch.cuda.synchronize()
         self.capi.conv_timing(True)
         for _ in range(2):
             self._step(self.x, self.y)  # eager even when the timed steps were graph replays: the timing wraps each call
@@ -637,7 +646,7 @@ def main():
     ap.add_argument("--no-secondary", action="store_true", help="resnet50 at N=1: skip the extra conv1 / resnet18 / hbm measurements")
     ap.add_argument("--eager", action="store_true", help="training workloads: call the nn.Module directly instead of through the compile backend")
     ap.add_argument("--compile", action="store_true", help="training workloads: call the model through the compile backend")
-    ap.add_argument("--graph", action="store_true", help="training workloads: replay the whole step as one CUDA graph")
+    ap.add_argument("--graph", action="store_true", help="training workloads on one GPU: replay the whole step as one CUDA graph")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--regions", action="store_true",
                     help="compile the model region by region (compile.compile_regions) instead of as one graph: gradient buckets then "
@@ -661,6 +670,11 @@ def main():
         return run_reference(args, wl)
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
     rank, world = dist_setup(args.gpus)
+    if isinstance(wl, Train) and world > 1 and wl.graph:
+        # data-parallel steps are launched kernel by kernel: a recorded step with its NCCL all-reduces replays correctly
+        # (measured on 2 GPUs), but the process then hung in its teardown
+        wl.graph = False
+        wl.set_api()
     wl.setup_gpu(seed=rank, world=world)
     capi = wl.capi
     peaks = measured_peaks()
