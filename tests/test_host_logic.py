@@ -267,3 +267,24 @@ def test_step_counters_of_all_batch_norm_layers_advance_in_one_op(pkg, monkeypat
     assert seen[0]["step_counters"] == 3 and "aten._foreach_add.Scalar" in targets
     assert [int(v) for k, v in mod.state_dict().items() if "num_batches" in k] == [2, 2, 2]
     assert all(torch.allclose(a, b, rtol=1e-5, atol=1e-6) for a, b in zip(mod.state_dict().values(), ref.state_dict().values()))
+
+
+def test_bench_reference_arm_prints_the_contract_line():
+    """`bench.py --impl reference` needs no GPU: it times the CPU implementation of the workload and prints one JSON line with the
+    same metric, unit and config as the GPU arm, `impl`, a `cpu_baseline` describing the run and an `e2e` that repeats it."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--workload", "plaincnn", "--steps", "2", "--warmup", "3"],
+                         capture_output=True, text=True, timeout=600, cwd=root)
+    assert out.returncode == 0, out.stderr[-2000:]
+    line = json.loads(out.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and line["metric"] == "train_ms_per_step" and line["unit"] == "ms/step"
+    assert line["higher_is_better"] is False and line["n_gpus"] == 1 and line["steps"] == 2 and line["vs_baseline"] is None
+    assert line["config"]["workload"] == "plaincnn_b128_train" and line["data"] == "synthetic"
+    assert line["value"] > 0 and line["value"] == line["ms_per_step"]
+    cb = line["cpu_baseline"]
+    assert cb["kind"] == "reference" and cb["cores"] >= 1 and cb["value"] == line["value"] and "PyTorch CPU" in cb["sample"]
+    assert line["e2e"] == {"value": line["value"], "unit": "ms/step", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
