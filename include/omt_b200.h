@@ -126,6 +126,25 @@ size_t omt_kernel_times(char* buf, size_t n, int reset);
  * workspace == NULL the library takes the scratch from its own caching allocator on `stream`. */
 size_t omt_conv_workspace_bytes(int kind, const OmtConvGeo* g, uint32_t flags);
 
+/* Per-geometry plan overrides and the timing pass that finds them. Replaces the reference's tuning cache and autotune
+ * (csrc/conv.cpp:29-60 conv_plan / g_conv_cache, :116-155 autotune, :243-272 tune_dump / tune_load). The tensor-core
+ * kernels pick their tile width and the weight gradient's split-K slice count from the geometry by fixed rules; an
+ * override replaces that choice for one (pass, geometry): pass 0 forward, 1 input gradient, 2 weight gradient; `tile` =
+ * tile width in columns (64, 128, 256; 192 for the weight gradient; 0 = the rule), `mult` = factor on the rule's slice
+ * count (weight gradient only; 1 = the rule). omt_conv_workspace_bytes and omt_conv_bnstats_groups follow the override.
+ * omt_conv_autotune times the rules and every candidate on zero-filled channels-last operands of the geometry
+ * (allocated from the library's caching allocator; one warm-up call, then about 15 ms of timed calls per candidate,
+ * CUDA events on `stream`, which it synchronises: not inside a stream capture), stores the fastest as the override if it
+ * beats the rules by more than 3 % (else removes any override) and reports the choice. Geometries the tensor-core path
+ * does not take, or where a width would split the reduction over CTAs, are left to the rules (tile 0).
+ * omt_conv_plans_dump writes "pass,n,ci,co,ih,iw,oh,ow,ks,stride,pad=tile,mult\n" lines for all overrides and returns
+ * the bytes needed; omt_conv_plans_load reads such lines (skipping those it cannot use) and returns how many it took. */
+int omt_conv_plan_set(int kind, const OmtConvGeo* g, int32_t tile, double mult);
+int omt_conv_plan_get(int kind, const OmtConvGeo* g, int32_t* tile, double* mult); /* 1 if an override is stored, else 0 */
+int omt_conv_autotune(int kind, const OmtConvGeo* g, int32_t* tile, double* mult, float* best_ms, float* rule_ms, omt_stream_t stream);
+size_t omt_conv_plans_dump(char* buf, size_t n);
+int omt_conv_plans_load(const char* text);
+
 /* y[n,co,oh,ow] = conv(x, w) (+bias)(ReLU). w is [co, ci, ks, ks] contiguous. Replaces gemm_forward
  * (csrc/conv.cpp:70-77) and the kind-0 generated kernel (omarchy_mac_torch/gemm.py:25-42).
  * With OMT_EPI_BNSTATS the epilogue also reduces the values it stores into batch-norm partial statistics, so that the

@@ -72,6 +72,11 @@ SIGNATURES = {
     "omt_kernel_counts": (_SZ, [C.c_char_p, _SZ, _I]),
     "omt_conv_workspace_bytes": (_SZ, [_I, _G, _U]),
     "omt_conv_fwd": (_I, [_G, _A, _P, _P, _A, _P, _U, _P, _SZ, _P]),
+    "omt_conv_plan_set": (_I, [_I, _G, C.c_int32, C.c_double]),
+    "omt_conv_plan_get": (_I, [_I, _G, C.POINTER(C.c_int32), C.POINTER(C.c_double)]),
+    "omt_conv_autotune": (_I, [_I, _G, C.POINTER(C.c_int32), C.POINTER(C.c_double), C.POINTER(C.c_float), C.POINTER(C.c_float), _P]),
+    "omt_conv_plans_dump": (_SZ, [C.c_char_p, _SZ]),
+    "omt_conv_plans_load": (_I, [C.c_char_p]),
     "omt_conv_dgrad": (_I, [_G, _A, _P, _A, _U, _P, _SZ, _P]),
     "omt_conv_wgrad": (_I, [_G, _A, _A, _P, _F, _U, _P, _SZ, _P]),
     "omt_conv_wgrad_noalloc_capacity": (_SZ, []),
@@ -192,6 +197,41 @@ def conv_timing_read(reset=True):
     call("omt_conv_timing_bytes", b)
     call("omt_conv_timing_read", f, m, c, int(reset))
     return {k: (f[i], m[i], c[i], b[i]) for i, k in enumerate(("fwd", "dgrad", "wgrad"))}
+
+
+def conv_autotune(kind, g, stream=None):
+    """Time the planner's rules and every candidate plan for pass `kind` (0 forward, 1 input gradient, 2 weight gradient) of
+    geometry `g`; the fastest becomes the stored override when it beats the rules by more than 3 %. Returns
+    (tile, mult, best_ms, rule_ms); tile 0 and mult 1.0 mean the rules stay."""
+    tile, mult, best, rule = C.c_int32(0), C.c_double(1.0), C.c_float(0), C.c_float(0)
+    call("omt_conv_autotune", int(kind), g, C.byref(tile), C.byref(mult), C.byref(best), C.byref(rule), stream_handle(stream))
+    return tile.value, mult.value, best.value, rule.value
+
+
+def conv_plan_get(kind, g):
+    """(tile, mult) of the stored override for (kind, g), or None."""
+    tile, mult = C.c_int32(0), C.c_double(1.0)
+    have = lib().omt_conv_plan_get(int(kind), g, C.byref(tile), C.byref(mult))
+    return (tile.value, mult.value) if have == 1 else None
+
+
+def conv_plans_dump():
+    """All stored overrides as {"pass,n,ci,co,ih,iw,oh,ow,ks,stride,pad": (tile, mult)}."""
+    n = lib().omt_conv_plans_dump(None, 0)
+    buf = C.create_string_buffer(n + 1)
+    lib().omt_conv_plans_dump(buf, n + 1)
+    out = {}
+    for line in buf.value.decode().splitlines():
+        k, _, v = line.partition("=")
+        t, _, m = v.partition(",")
+        out[k] = (int(t), float(m))
+    return out
+
+
+def conv_plans_load(entries):
+    """Store overrides from a {key: (tile, mult)} mapping as conv_plans_dump returns it; returns how many were taken."""
+    text = "".join(f"{k}={int(v[0])},{float(v[1])!r}\n" for k, v in entries.items())
+    return lib().omt_conv_plans_load(text.encode())
 
 
 def kernel_counts(reset=False):

@@ -85,6 +85,13 @@ inline bool is_nhwc(const OmtAct* a, int c, int h, int w) {
   return (c == 1 || a->sc == 1) && (w == 1 || a->sw == c) && (h == 1 || a->sh == (int64_t)w * c) && a->sn == (int64_t)h * w * c;
 }
 
+// A per-geometry plan override for the tensor-core convolution kernels: `bn` = tile width in columns (0: the planner's
+// rule), `mult` = factor on the weight gradient's split-K slice count (0: the rule). The public entry points install the
+// override stored for their (pass, geometry), if any, in this thread-local for the duration of the call, so that every
+// planning function the call reaches (tile choice, split-K, workspace size) sees the same one.
+struct PlanOverride { int bn; double mult; };
+extern thread_local PlanOverride tl_plan;
+
 // Argument checks every dense-convolution entry point starts with (the reference's conv_kind / NEED rules,
 // csrc/conv.cpp:167-183): a square kernel up to 11, stride 1..4, pad <= ks, consistent output size, GEMM extents below 2^31.
 inline int check_dense(const OmtConvGeo* g, const char* who) {

@@ -2,7 +2,14 @@
 // path selection (tcgen05 tensor-core kernels when the geometry and layout allow, exact-fp32 CUDA-core kernels
 // otherwise), workspace handling, and two small copy helpers.
 #include <algorithm>
+#include <array>
+#include <atomic>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <map>
 #include <mutex>
+#include <string>
 #include <vector>
 
 #include "common.cuh"
@@ -23,6 +30,28 @@ int tc_conv_fwd(const OmtConvGeo* g, const OmtAct* x, const float* w, const floa
 int tc_conv_dgrad(const OmtConvGeo* g, const OmtAct* gy, const float* w, const OmtAct* dx, uint32_t flags, void* ws, cudaStream_t s);
 int tc_conv_wgrad(const OmtConvGeo* g, const OmtAct* x, const OmtAct* gy, float* dw, float scale, void* ws, cudaStream_t s);
 int tc_bnstats_groups(const OmtConvGeo* g, const OmtAct* x, const OmtAct* y);
+
+// ---- per-geometry plan overrides (the reference's tuning cache g_conv_cache, csrc/conv.cpp:29-60, 116-155) ----
+// key: pass (0 forward, 1 input gradient, 2 weight gradient), n, ci, co, ih, iw, oh, ow, ks, stride, pad
+using PlanKey = std::array<int, 11>;
+static std::map<PlanKey, PlanOverride> g_plans;
+static std::mutex g_plans_mu;
+static std::atomic<int> g_plans_count{0};
+static PlanKey plan_key(int kind, const OmtConvGeo* g) {
+  return {kind, g->n, g->ci, g->co, g->ih, g->iw, g->oh, g->ow, g->ks, g->stride, g->pad};
+}
+// installs the override stored for (kind, g) for the lifetime of the object (none stored: the planner's rules)
+struct PlanScope {
+  PlanOverride saved;
+  PlanScope(int kind, const OmtConvGeo* g) : saved(tl_plan) {
+    tl_plan = PlanOverride{0, 0.0};
+    if (!g || g_plans_count.load(std::memory_order_relaxed) == 0) return;
+    std::lock_guard<std::mutex> l(g_plans_mu);
+    auto it = g_plans.find(plan_key(kind, g));
+    if (it != g_plans.end()) tl_plan = it->second;
+  }
+  ~PlanScope() { tl_plan = saved; }
+};
 
 // ---- optional per-call timing of the three passes ----
 static bool g_timing = false;
@@ -197,6 +226,7 @@ static bool dgrad_by_taps_ok(const OmtConvGeo* g, const OmtAct* gy_cl) {
 }
 static int dgrad_by_taps(const OmtConvGeo* g, const OmtAct* gy, const float* w, const OmtAct* dx, omt_stream_t stream) {
   const OmtConvGeo g1 = taps_geo(g);
+  PlanScope plan(1, nullptr);  // the inner 1x1 product is another geometry: the planner's rules
   const int colsp = g1.ci, kk = g->ks * g->ks;
   const size_t P = (size_t)g->n * g->oh * g->ow;
   const size_t wm_floats = ((size_t)g->co * colsp + 63) / 64 * 64;
@@ -226,11 +256,13 @@ size_t omt_conv_workspace_bytes(int kind, const OmtConvGeo* g, uint32_t flags) {
   if (!g || g->groups != 1) return 0;
   size_t simt = kind == 2 ? simt_wgrad_workspace(g) : 0;
   if (flags & OMT_FORCE_SIMT) return simt;
+  PlanScope plan(kind, g);
   return std::max(simt, tc_workspace(kind, g));
 }
 
 int32_t omt_conv_bnstats_groups(const OmtConvGeo* g, const OmtAct* x, const OmtAct* y) {
   if (check_dense(g, "omt_conv_bnstats_groups") || !x || !y || !x->p || !y->p) return 0;
+  PlanScope plan(0, g);
   return tc_bnstats_groups(g, x, y);
 }
 
@@ -243,6 +275,7 @@ int omt_conv_fwd(const OmtConvGeo* g, const OmtAct* x, const float* w, const flo
                  uint32_t flags, void* workspace, size_t workspace_bytes, omt_stream_t stream) {
   int r = check_dense(g, "omt_conv_fwd");
   if (r) return r;
+  PlanScope plan(0, g);
   OMT_REQUIRE(x && y && x->p && y->p && w, "omt_conv_fwd: null pointer");
   OMT_REQUIRE(!(flags & OMT_EPI_BIAS) || bias, "omt_conv_fwd: OMT_EPI_BIAS without a bias pointer");
   OMT_REQUIRE(!(flags & OMT_EPI_BNSTATS) || stats, "omt_conv_fwd: OMT_EPI_BNSTATS without a stats pointer");
@@ -271,6 +304,7 @@ int omt_conv_dgrad(const OmtConvGeo* g, const OmtAct* gy, const float* w, const 
                    size_t workspace_bytes, omt_stream_t stream) {
   int r = check_dense(g, "omt_conv_dgrad");
   if (r) return r;
+  PlanScope plan(1, g);
   OMT_REQUIRE(gy && dx && gy->p && dx->p && w, "omt_conv_dgrad: null pointer");
   bool tc = !(flags & OMT_FORCE_SIMT) && tc_supported(1, g, gy, dx);
   CallTimer timer(1, g, st(stream));
@@ -310,6 +344,7 @@ int omt_conv_wgrad(const OmtConvGeo* g, const OmtAct* x, const OmtAct* gy, float
                    size_t workspace_bytes, omt_stream_t stream) {
   int r = check_dense(g, "omt_conv_wgrad");
   if (r) return r;
+  PlanScope plan(2, g);
   OMT_REQUIRE(x && gy && x->p && gy->p && dw, "omt_conv_wgrad: null pointer");
   bool tc = !(flags & OMT_FORCE_SIMT) && tc_supported(2, g, x, gy);
   CallTimer timer(2, g, st(stream));
@@ -419,6 +454,157 @@ int omt_act_copy(const OmtAct* src, const OmtAct* dst, int32_t n, int32_t c, int
   }
   strided_copy_kernel<<<(unsigned)cdiv(total, 256), 256, 0, st(stream)>>>(view(src), view(dst), n, c, h, w);
   return check_launch("act_strided_copy");
+}
+
+// ---- plan overrides and the timing pass that finds them (reference autotune / tune_dump / tune_load, csrc/conv.cpp:116-155, 243-272) ----
+
+int omt_conv_plan_set(int kind, const OmtConvGeo* g, int32_t tile, double mult) {
+  OMT_REQUIRE(g && kind >= 0 && kind <= 2, "omt_conv_plan_set: bad arguments");
+  OMT_REQUIRE(tile == 0 || tile == 64 || tile == 128 || tile == 256 || (kind == 2 && tile == 192), "omt_conv_plan_set: tile width %d", (int)tile);
+  OMT_REQUIRE(mult >= 0 && mult <= 16 && (kind == 2 || mult == 0 || mult == 1), "omt_conv_plan_set: slice factor %g", mult);
+  std::lock_guard<std::mutex> l(g_plans_mu);
+  if (tile == 0 && (mult == 0 || mult == 1)) g_plans.erase(plan_key(kind, g));
+  else g_plans[plan_key(kind, g)] = PlanOverride{(int)tile, mult == 1 ? 0.0 : mult};
+  g_plans_count.store((int)g_plans.size(), std::memory_order_relaxed);
+  return OMT_OK;
+}
+
+int omt_conv_plan_get(int kind, const OmtConvGeo* g, int32_t* tile, double* mult) {
+  OMT_REQUIRE(g && tile && mult, "omt_conv_plan_get: bad arguments");
+  std::lock_guard<std::mutex> l(g_plans_mu);
+  auto it = g_plans.find(plan_key(kind, g));
+  *tile = it == g_plans.end() ? 0 : it->second.bn;
+  *mult = it == g_plans.end() || it->second.mult == 0 ? 1.0 : it->second.mult;
+  return it == g_plans.end() ? 0 : 1;
+}
+
+size_t omt_conv_plans_dump(char* buf, size_t n) {
+  std::string out;
+  {
+    std::lock_guard<std::mutex> l(g_plans_mu);
+    char line[160];
+    for (auto& kv : g_plans) {
+      int len = 0;
+      for (int i = 0; i < 11; i++) len += snprintf(line + len, sizeof(line) - len, i ? ",%d" : "%d", kv.first[i]);
+      snprintf(line + len, sizeof(line) - len, "=%d,%g\n", kv.second.bn, kv.second.mult == 0 ? 1.0 : kv.second.mult);
+      out += line;
+    }
+  }
+  if (buf && n) {
+    const size_t m = std::min(n - 1, out.size());
+    memcpy(buf, out.data(), m);
+    buf[m] = 0;
+  }
+  return out.size();
+}
+
+int omt_conv_plans_load(const char* text) {
+  OMT_REQUIRE(text, "omt_conv_plans_load: null text");
+  int loaded = 0;
+  const char* p = text;
+  while (*p) {
+    int k[11], tile = 0, used = 0;
+    double mult = 1.0;
+    const int got = sscanf(p, "%d,%d,%d,%d,%d,%d,%d,%d,%d,%d,%d=%d,%lf%n", &k[0], &k[1], &k[2], &k[3], &k[4], &k[5], &k[6], &k[7], &k[8], &k[9], &k[10],
+                           &tile, &mult, &used);
+    if (got == 13) {
+      OmtConvGeo g{k[1], k[2], k[3], k[4], k[5], k[6], k[7], k[8], k[9], k[10], 1};
+      if (k[0] >= 0 && k[0] <= 2 && omt_conv_plan_set(k[0], &g, tile, mult) == OMT_OK) loaded++;
+    }
+    while (*p && *p != '\n') p++;  // entries that do not parse or name a tile this build does not have are skipped
+    if (*p) p++;
+  }
+  return loaded;
+}
+
+int omt_conv_autotune(int kind, const OmtConvGeo* g, int32_t* tile, double* mult, float* best_ms, float* rule_ms, omt_stream_t stream) {
+  int r = check_dense(g, "omt_conv_autotune");
+  if (r) return r;
+  OMT_REQUIRE(kind >= 0 && kind <= 2, "omt_conv_autotune: pass %d", kind);
+  if (tile) *tile = 0;
+  if (mult) *mult = 1.0;
+  if (best_ms) *best_ms = 0.f;
+  if (rule_ms) *rule_ms = 0.f;
+  cudaStream_t s = st(stream);
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  OMT_CUDA(cudaStreamIsCapturing(s, &cap));
+  OMT_REQUIRE(cap == cudaStreamCaptureStatusNone, "omt_conv_autotune: the stream is being captured (the timing pass synchronises)");
+  // channels-last operands filled with zeros (the kernels' time does not depend on the values)
+  const size_t xn = (size_t)g->n * g->ci * g->ih * g->iw, yn = (size_t)g->n * g->co * g->oh * g->ow, wn = (size_t)g->co * g->ci * g->ks * g->ks;
+  struct Buf {
+    void* p = nullptr;
+    ~Buf() { if (p) omt_free(p); }
+  } bx, by, bw;
+  bx.p = omt_malloc(xn * 4, stream); by.p = omt_malloc(yn * 4, stream); bw.p = omt_malloc(wn * 4, stream);
+  OMT_REQUIRE(bx.p && by.p && bw.p, "omt_conv_autotune: out of device memory for the trial operands");
+  OMT_CUDA(cudaMemsetAsync(bx.p, 0, xn * 4, s)); OMT_CUDA(cudaMemsetAsync(by.p, 0, yn * 4, s)); OMT_CUDA(cudaMemsetAsync(bw.p, 0, wn * 4, s));
+  OmtAct ax{(float*)bx.p, (int64_t)g->ih * g->iw * g->ci, 1, (int64_t)g->iw * g->ci, g->ci};
+  OmtAct ay{(float*)by.p, (int64_t)g->oh * g->ow * g->co, 1, (int64_t)g->ow * g->co, g->co};
+  if (!(kind == 0 ? tc_supported(0, g, &ax, &ay) : kind == 1 ? tc_supported(1, g, &ay, &ax) : tc_supported(2, g, &ax, &ay))) return OMT_OK;
+  // candidates: tile widths the geometry can fill; forward / input gradient only where no width splits the reduction over
+  // CTAs (the statistics epilogue and the callers' workspace sizes then do not depend on the choice)
+  std::vector<PlanOverride> cands;
+  if (kind == 2) {
+    const int chunks = g->ks * g->ks * (int)cdiv(g->ci, 32);
+    for (int bn : {64, 128, 192, 256})
+      if (bn / 32 <= 2 * chunks)
+        for (double m : {0.5, 1.0, 2.0}) cands.push_back(PlanOverride{bn, m == 1.0 ? 0.0 : m});
+  } else {
+    const int cols = kind == 0 ? g->co : g->ci;
+    const int64_t rows = kind == 0 ? (int64_t)g->n * g->oh * g->ow : (int64_t)g->n * cdiv(g->ih, g->stride) * cdiv(g->iw, g->stride);
+    if (g->ci <= 4 || cols <= 128 || cdiv(rows, 128) * cdiv(cols, 256) * 2 <= sm_count()) return OMT_OK;  // (<= 128 columns: one width)
+    cands.push_back(PlanOverride{128, 0.0});
+    cands.push_back(PlanOverride{256, 0.0});
+  }
+  cudaEvent_t e0, e1;
+  OMT_CUDA(cudaEventCreate(&e0));
+  if (cudaEventCreate(&e1) != cudaSuccess) { cudaEventDestroy(e0); set_error("omt_conv_autotune: cudaEventCreate failed"); return OMT_ECUDA; }
+  auto run = [&]() -> int {
+    if (kind == 0) return omt_conv_fwd(g, &ax, (const float*)bw.p, nullptr, &ay, nullptr, 0, nullptr, 0, stream);
+    if (kind == 1) return omt_conv_dgrad(g, &ay, (const float*)bw.p, &ax, 0, nullptr, 0, stream);
+    return omt_conv_wgrad(g, &ax, &ay, (float*)bw.p, 1.f, 0, nullptr, 0, stream);
+  };
+  // one warm-up call, one timed call, then up to six more (about 15 ms of timing per candidate, as the reference's pass)
+  auto time_it = [&](float* ms) -> int {
+    int rr = run();
+    if (rr) return rr;
+    float first = 0.f, rest = 0.f;
+    cudaEventRecord(e0, s);
+    rr = run();
+    cudaEventRecord(e1, s);
+    if (rr || cudaEventSynchronize(e1) != cudaSuccess || cudaEventElapsedTime(&first, e0, e1) != cudaSuccess) return rr ? rr : OMT_ECUDA;
+    const int reps = (int)std::max(1.0, std::min(6.0, 15.0 / std::max((double)first, 0.05)));
+    *ms = first;
+    if (reps > 1) {
+      cudaEventRecord(e0, s);
+      for (int i = 0; i < reps && !rr; i++) rr = run();
+      cudaEventRecord(e1, s);
+      if (rr || cudaEventSynchronize(e1) != cudaSuccess || cudaEventElapsedTime(&rest, e0, e1) != cudaSuccess) return rr ? rr : OMT_ECUDA;
+      *ms = std::min(first, rest / reps);
+    }
+    return OMT_OK;
+  };
+  float base = 0.f, best = 0.f;
+  PlanOverride best_plan{0, 0.0};
+  omt_conv_plan_set(kind, g, 0, 0);  // the planner's rules first
+  r = time_it(&base);
+  best = base;
+  for (size_t i = 0; i < cands.size() && !r; i++) {
+    float ms = 0.f;
+    if (omt_conv_plan_set(kind, g, cands[i].bn, cands[i].mult == 0 ? 1.0 : cands[i].mult) != OMT_OK) continue;
+    r = time_it(&ms);
+    if (!r && ms < best) { best = ms; best_plan = cands[i]; }
+  }
+  cudaEventDestroy(e0); cudaEventDestroy(e1);
+  // an override has to pay for itself: within 3 % of the rules' time the rules stay
+  if (r || best > 0.97f * base) best_plan = PlanOverride{0, 0.0};
+  omt_conv_plan_set(kind, g, best_plan.bn, best_plan.mult == 0 ? 1.0 : best_plan.mult);
+  if (r) return r;
+  if (tile) *tile = best_plan.bn;
+  if (mult) *mult = best_plan.mult == 0 ? 1.0 : best_plan.mult;
+  if (best_ms) *best_ms = best_plan.bn || best_plan.mult ? best : base;
+  if (rule_ms) *rule_ms = base;
+  return OMT_OK;
 }
 
 }  // extern "C"

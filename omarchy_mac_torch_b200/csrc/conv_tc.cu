@@ -42,6 +42,8 @@
 
 namespace omt {
 
+thread_local PlanOverride tl_plan{0, 0.0};
+
 namespace {
 
 constexpr int BM = 128;        // output pixels per tile (UMMA M)
@@ -948,6 +950,7 @@ struct TcProblem {  // a convolution of a channels-last activation `a` [n, ih, i
 };
 
 int pick_bn(const TcProblem& p) {
+  if (tl_plan.bn == 64 || tl_plan.bn == 128 || tl_plan.bn == 256) return tl_plan.bn;  // tuned or loaded for this geometry
   if (p.rows <= 64) return 64;
   if (p.rows <= 128) return 128;
   // (128 x 256 tiles with a short reduction use one accumulator per tile and two TMEM buffers, so their epilogue overlaps the
@@ -1719,6 +1722,7 @@ WgPlan plan_wgrad(const OmtConvGeo* g) {
   w.bn = 64;
   for (int bn : {128, 192, 256})  // (a wider tile may pad up to 15 % more: AlexNet conv1's 22 chunks run faster as 3 x 256 than as 11 x 64)
     if (cdiv(w.vchunks, bn / 32) * bn * 100 <= least * 115) w.bn = bn;
+  if (tl_plan.bn == 64 || tl_plan.bn == 128 || tl_plan.bn == 192 || tl_plan.bn == 256) w.bn = tl_plan.bn;  // tuned or loaded
   const int64_t tiles = cdiv(g->co, BM) * cdiv(w.vchunks, w.bn / 32);
   const int per_tile = w.bn / 32;
   // CTA pairs: two co tiles share the x columns, each CTA staging half of them (full tiles only, not the window mode)
@@ -1766,7 +1770,8 @@ WgPlan plan_wgrad(const OmtConvGeo* g) {
   w.total_blocks = (int)total_blocks;
   // one wave of CTAs: a CTA's fixed cost (TMEM allocation, first loads, 128 KB partial tile written and summed later) is
   // worth 5-10 k-blocks, so fewer and longer split-K slices win over finer load balance (measured with 1-4 waves)
-  const int64_t want = std::max<int64_t>(1, sm_count() / tiles);
+  int64_t want = std::max<int64_t>(1, sm_count() / tiles);
+  if (tl_plan.mult > 0) want = std::max<int64_t>(1, (int64_t)(want * tl_plan.mult + 0.5));
   const int64_t slices = std::max<int64_t>(1, std::min<int64_t>(want, total_blocks / 8));
   w.blocks_per_slice = (int)cdiv(total_blocks, slices);
   w.slices = (int)cdiv(total_blocks, w.blocks_per_slice);

@@ -1,11 +1,19 @@
 // aten::convolution / aten::convolution_backward for the device: dense (implicit GEMM: tensor-core or exact-fp32 path,
 // chosen inside libomt_b200.so) and depthwise. Same coverage rules as the reference's conv_kind (csrc/conv.cpp:167-177)
-// and the same op signatures (csrc/conv.cpp:179-237, 285-288); tile planning / autotuning callbacks of the reference
-// (csrc/conv.cpp:29-60, 116-155) have no counterpart because the kernels are compiled ahead of time and pick their
-// tile from the geometry, so the planner/tuning bindings are kept as inert shims.
+// and the same op signatures (csrc/conv.cpp:179-237, 285-288). The reference's planner callback (csrc/conv.cpp:29-60) has
+// no counterpart: the kernels are compiled ahead of time and pick their tile from the geometry. Its tuning pass has
+// (csrc/conv.cpp:116-155): with set_tuning(true, ...) the first use of a (pass, geometry) times the library's candidate
+// plans (omt_conv_autotune) and later calls use the winner; tune_dump / tune_load / tuned_plans move the choices in and out.
 #include "omt.h"
 
+#include <array>
 #include <cstdlib>
+#include <map>
+#include <mutex>
+#include <set>
+#include <string>
+
+#include <cuda_runtime.h>
 
 #include <pybind11/functional.h>
 #include <pybind11/stl.h>
@@ -14,8 +22,29 @@ namespace omt {
 
 int g_fold = 1;
 static int g_cl_mode = 0;  // 0: conv outputs follow the input layout; 1: channels-last whenever co % 4 == 0
-static bool g_tune = true;
+static bool g_tune = false;
 static int g_num_tiles = 0;
+
+// set_tuning(true): the first dense conv call of a (pass, geometry) runs the library's timing pass (csrc/conv.cpp:29-60
+// conv_plan -> autotune on a cache miss). Not while the stream is being captured (the pass synchronises).
+static std::mutex g_tuned_mu;
+static std::set<std::array<int, 11>> g_tuned;
+void maybe_tune(int kind, const OmtConvGeo& g) {
+  if (!g_tune || g.groups != 1) return;
+  const std::array<int, 11> key{kind, g.n, g.ci, g.co, g.ih, g.iw, g.oh, g.ow, g.ks, g.stride, g.pad};
+  {
+    std::lock_guard<std::mutex> l(g_tuned_mu);
+    if (g_tuned.count(key)) return;
+  }
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing((cudaStream_t)cur_stream(), &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) return;
+  int32_t tile = 0;
+  double mult = 1.0;
+  if (omt_conv_plan_get(kind, &g, &tile, &mult) == 0)  // nothing loaded for it
+    check(omt_conv_autotune(kind, &g, nullptr, nullptr, nullptr, nullptr, cur_stream()), "conv tuning pass");
+  std::lock_guard<std::mutex> l(g_tuned_mu);
+  g_tuned.insert(key);
+}
 
 OmtConvGeo conv_geo(int64_t n, int64_t ci, int64_t co, int64_t ih, int64_t iw, int64_t ks, int64_t stride, int64_t pad, int64_t groups) {
   OmtConvGeo g;
@@ -44,6 +73,7 @@ static std::string conv_kind(const Tensor& x, const Tensor& w, IntArrayRef strid
 }
 
 Tensor conv_forward(const Tensor& x, const Tensor& w, const Tensor* bias, const OmtConvGeo& g, bool relu) {
+  maybe_tune(0, g);
   Tensor out = empty_dev({g.n, g.co, g.oh, g.ow}, at::kFloat, prefer_cl(x, g.co));
   out = dense4(out);
   OmtAct ax = act(x), ay = act(out);
@@ -55,6 +85,7 @@ Tensor conv_forward(const Tensor& x, const Tensor& w, const Tensor* bias, const 
 }
 
 Tensor conv_forward_stats(const Tensor& x, const Tensor& w, const Tensor* bias, const OmtConvGeo& g, Tensor& partials, int& groups) {
+  maybe_tune(0, g);  // (before the statistics query below: both follow the stored plan)
   Tensor out = dense4(empty_dev({g.n, g.co, g.oh, g.ow}, at::kFloat, prefer_cl(x, g.co)));
   OmtAct ax = act(x), ay = act(out);
   // OMARCHY_MAC_TORCH_EPILOGUE_STATS=0 leaves the statistics to a separate pass over y (for A/B measurements)
@@ -102,11 +133,13 @@ static std::tuple<Tensor, Tensor, Tensor> convolution_backward_(const Tensor& gy
   if (mask[0]) {
     gx = dense4(empty_dev(x.sizes(), at::kFloat, cl));
     OmtAct adx = act(gx);
+    if (kind == "dense") maybe_tune(1, g);
     if (kind == "dense") check(omt_conv_dgrad(&g, &ag, w.data_ptr<float>(), &adx, 0, nullptr, 0, cur_stream()), "conv input gradient");
     else check(omt_dw_dgrad(&g, &ag, w.data_ptr<float>(), &adx, cur_stream()), "depthwise input gradient");
   }
   if (mask[1]) {
     gw = empty_dev(w.sizes(), at::kFloat);
+    if (kind == "dense") maybe_tune(2, g);
     if (kind == "dense") check(omt_conv_wgrad(&g, &ax, &ag, gw.data_ptr<float>(), 1.f, 0, nullptr, 0, cur_stream()), "conv weight gradient");
     else check(omt_dw_wgrad(&g, &ax, &ag, gw.data_ptr<float>(), 1.f, cur_stream()), "depthwise weight gradient");
   }
@@ -136,6 +169,7 @@ static std::tuple<Tensor, Tensor> conv_backward_acc_dev(const Tensor& gy_, const
   OmtConvGeo g = conv_geo(x.size(0), x.size(1), w.size(0), x.size(2), x.size(3), w.size(2), stride[0], padding[0], 1);
   NEED(gy.size(2) == g.oh && gy.size(3) == g.ow, "grad_output size does not match the geometry");
   OmtAct ag = act(gy), ax = act(x), aacc = act(acc);
+  maybe_tune(1, g);
   int st = omt_conv_dgrad(&g, &ag, w.data_ptr<float>(), &aacc, OMT_EPI_ACCUM, nullptr, 0, cur_stream());
   if (st == OMT_EINVAL) {  // not a tensor-core geometry: plain input gradient, then the add
     Tensor gx = dense4(empty_dev(x.sizes(), at::kFloat, layout4(acc) == 1));
@@ -148,20 +182,55 @@ static std::tuple<Tensor, Tensor> conv_backward_acc_dev(const Tensor& gy_, const
   Tensor gw;
   if (need_w) {
     gw = empty_dev(w.sizes(), at::kFloat);
+    maybe_tune(2, g);
     check(omt_conv_wgrad(&g, &ax, &ag, gw.data_ptr<float>(), 1.f, 0, nullptr, 0, cur_stream()), "conv weight gradient");
   }
   return {acc, gw};
 }
 
 void bind_conv(py::module_& m) {
-  // Inert shims for the reference's generated-kernel planner (csrc/conv.cpp:239-283): kept so code written against the
-  // reference's _native module keeps importing; the CUDA kernels need no runtime source generation or per-shape tuning.
+  // set_conv_planner is an inert shim for the reference's generated-kernel planner (csrc/conv.cpp:239-241): kept so code
+  // written against the reference's _native module keeps importing; the CUDA kernels need no runtime source generation.
   m.def("set_conv_planner", [](py::object) {});
   m.def("set_fold", [](int f) { g_fold = f; });
   m.def("set_tuning", [](bool on, int num_tiles) { g_tune = on; g_num_tiles = num_tiles; });
-  m.def("tune_dump", []() { return std::map<std::string, std::pair<int, double>>(); });
-  m.def("tune_load", [](std::map<std::string, std::pair<int, double>>) {});
-  m.def("tuned_plans", []() { return std::map<std::string, std::string>(); });
+  // geometry key "pass,n,ci,co,ih,iw,oh,ow,ks,stride,pad" -> (tile width in columns, split-K slice factor): csrc/conv.cpp:243-272
+  m.def("tune_dump", []() {
+    std::map<std::string, std::pair<int, double>> r;
+    std::string text(omt_conv_plans_dump(nullptr, 0) + 1, '\0');
+    omt_conv_plans_dump(text.data(), text.size());
+    size_t pos = 0;
+    while (pos < text.size() && text[pos]) {
+      size_t nl = text.find('\n', pos);
+      if (nl == std::string::npos) break;
+      const std::string line = text.substr(pos, nl - pos);
+      const size_t eq = line.find('='), comma = line.find(',', eq == std::string::npos ? 0 : eq);
+      if (eq != std::string::npos && comma != std::string::npos)
+        r[line.substr(0, eq)] = {std::stoi(line.substr(eq + 1, comma - eq - 1)), std::stod(line.substr(comma + 1))};
+      pos = nl + 1;
+    }
+    return r;
+  });
+  m.def("tune_load", [](std::map<std::string, std::pair<int, double>> entries) {
+    std::string text;
+    for (auto& e : entries) text += e.first + "=" + std::to_string(e.second.first) + "," + std::to_string(e.second.second) + "\n";
+    return omt_conv_plans_load(text.c_str());
+  });
+  m.def("tuned_plans", []() {
+    std::map<std::string, std::string> r;
+    std::string text(omt_conv_plans_dump(nullptr, 0) + 1, '\0');
+    omt_conv_plans_dump(text.data(), text.size());
+    size_t pos = 0;
+    while (pos < text.size() && text[pos]) {
+      size_t nl = text.find('\n', pos);
+      if (nl == std::string::npos) break;
+      const std::string line = text.substr(pos, nl - pos);
+      const size_t eq = line.find('=');
+      if (eq != std::string::npos) r[line.substr(0, eq)] = line.substr(eq + 1);
+      pos = nl + 1;
+    }
+    return r;
+  });
   m.def("set_channels_last", [](int mode) { g_cl_mode = mode; }, "0: conv outputs follow the input layout; 1: channels-last when co % 4 == 0");
   m.def("channels_last_mode", []() { return g_cl_mode; });
 }

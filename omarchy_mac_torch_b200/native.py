@@ -34,7 +34,11 @@ torch.utils.rename_privateuse1_backend(DEVICE)
 torch.utils.generate_methods_for_privateuse1_backend(for_tensor=True, for_module=True, for_packed_sequence=True, for_storage=True)
 
 core.set_fold(int(os.environ.get("OMARCHY_MAC_TORCH_FOLD", "1")))
-core.set_tuning(os.environ.get("OMARCHY_MAC_TORCH_TUNE", "1") != "0", 0)
+# OMARCHY_MAC_TORCH_TUNE=1: the first use of a convolution (pass, geometry) times the library's candidate tile plans and keeps
+# the winner (the reference tunes by default, omarchy_mac_torch/native.py:75; here the built-in rules are the default and
+# the timing pass is opt-in, because it synchronises the stream and a step may be under CUDA-graph capture).
+TUNING = os.environ.get("OMARCHY_MAC_TORCH_TUNE", "0") == "1"
+core.set_tuning(TUNING, 4)
 core.set_debug(os.environ.get("OMARCHY_MAC_TORCH_DEBUG", "0") == "1")
 # conv outputs are produced channels-last (the layout the tensor-core kernels read) unless this is set to 0
 core.set_channels_last(int(os.environ.get("OMARCHY_MAC_TORCH_CHANNELS_LAST", "1")))
@@ -141,3 +145,50 @@ class _Fallbacks:
 
 
 FALLBACKS = _Fallbacks()
+
+
+# ---- on-disk cache of the convolution tuning (omarchy_mac_torch/native.py:182-206): read at import and written at exit, only
+# when tuning is on, so that a default run never depends on what an earlier process measured ----
+_TUNE_FILE = os.path.expanduser(os.environ.get("OMARCHY_MAC_TORCH_TUNE_FILE", "~/.cache/omarchy-mac-torch-b200/tuning.json"))
+
+
+def load_tuning(path=None):
+    """Install the plan overrides stored in a tuning file ({"pass,n,ci,co,ih,iw,oh,ow,ks,stride,pad": [tile, mult]}); returns
+    how many the library took."""
+    import json
+    with open(path or _TUNE_FILE) as f:
+        return core.tune_load({k: (int(v[0]), float(v[1])) for k, v in json.load(f).items()})
+
+
+def save_tuning(path=None):
+    """Merge the current plan overrides into the tuning file."""
+    import json
+    path = path or _TUNE_FILE
+    os.makedirs(os.path.dirname(path), exist_ok=True)
+    old = {}
+    try:
+        with open(path) as f:
+            old = json.load(f)
+    except (OSError, ValueError):
+        pass
+    old.update({k: list(v) for k, v in core.tune_dump().items()})
+    with open(path, "w") as f:
+        json.dump(old, f)
+
+
+if TUNING:
+    import atexit
+
+    try:
+        load_tuning()
+    except (OSError, ValueError, TypeError):
+        pass
+
+    def _save_tuning_at_exit():
+        try:
+            save_tuning()
+        except Exception:
+            pass
+
+    atexit.register(_save_tuning_at_exit)
+

@@ -787,3 +787,37 @@ def test_compile_backend(omt):
     ref.eval(); mod.eval()
     with torch.no_grad():
         assert e(torch.compile(mod, backend="omarchy_mac_torch")(x.to(D)), ref(x)) <= 1e-3
+
+
+def test_tuning_pass_through_the_device_ops(omt):
+    """set_tuning(True): the first dense convolution of a (pass, geometry) runs the library's timing pass; results are those of
+    the CPU, later calls reuse the choice, and tune_dump / tune_load carry the choices in the reference's key format."""
+    from omarchy_mac_torch_b200.native import core
+    torch.manual_seed(3)
+    conv = torch.nn.Conv2d(64, 192, 3, padding=1, bias=False)
+    x = torch.randn(16, 64, 28, 28, requires_grad=True)
+    y = conv(x)
+    y.square().sum().backward()
+    want = (y.detach(), x.grad.clone(), conv.weight.grad.clone())
+    before = dict(core.tune_dump())
+    core.set_tuning(True, 4)
+    try:
+        dconv = copy.deepcopy(conv).to(omt.DEVICE)
+        dconv.weight.grad = None
+        for _ in range(2):  # the second pass finds every geometry tuned
+            xd = x.detach().to(omt.DEVICE).requires_grad_(True)
+            yd = dconv(xd)
+            yd.square().sum().backward()
+        assert e(yd, want[0]) <= TOL and e(xd.grad, want[1]) <= TOL
+        assert e(dconv.weight.grad / 2, want[2]) <= TOL
+        dump = core.tune_dump()
+        for k, (tile, mult) in dump.items():
+            f = [int(v) for v in k.split(",")]
+            assert len(f) == 11 and f[0] in (0, 1, 2) and tile in (0, 64, 128, 192, 256) and mult > 0
+        assert core.tune_load(dict(dump)) == len(dump)
+        assert set(core.tuned_plans()) == set(dump)
+    finally:
+        core.set_tuning(False, 4)
+        for k in set(core.tune_dump()) - set(before):
+            core.tune_load({k: (0, 1.0)})
+

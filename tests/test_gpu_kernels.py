@@ -289,6 +289,56 @@ def test_weight_gradient_of_first_layers_pairs_filter_rows(capi, shape):
     capi.call("omt_sync")
 
 
+@pytest.mark.parametrize("shape", [(8, 64, 256, 28, 1, 1), (4, 128, 128, 28, 3, 1), (4, 256, 512, 28, 1, 2), (16, 96, 160, 14, 3, 1)],
+                         ids=lambda s: "n%d_ci%d_co%d_hw%d_k%d_s%d" % s)
+def test_conv_plan_overrides_and_the_tuning_pass(capi, shape):
+    """Every tile width / slice factor the tuning pass may choose gives the same results as the planner's rules (against
+    float64 aten on the CPU), also with a caller-provided workspace of omt_conv_workspace_bytes under the override; then the
+    pass itself: it leaves either no override or one of its candidates, and the results stand."""
+    n, ci, co, hw, ks, s_ = shape
+    p_ = ks // 2
+    torch.manual_seed(sum(shape))
+    x, w = torch.randn(n, ci, hw, hw), torch.randn(co, ci, ks, ks) * (2.0 / (ci * ks * ks)) ** 0.5
+    oh = (hw + 2 * p_ - ks) // s_ + 1
+    gy = torch.randn(n, co, oh, oh)
+    y, dx, dw, _ = oracle.aten_conv(x.double(), w.double(), None, s_, p_, gy.double())
+    y, dx, dw = y.float().numpy(), dx.float().numpy(), dw.float().numpy()
+    xd, wd, gd = dev(x, True), dev(w), dev(gy, True)
+    g = capi.geo(n, ci, co, hw, hw, ks, s_, p_)
+
+    def check_all():
+        assert rel_err(host(capi.conv_fwd(xd, wd, None, s_, p_, flags=capi.FORCE_TC, cl=True)), y) <= TOL
+        assert rel_err(host(capi.conv_dgrad(gd, wd, (hw, hw), s_, p_, flags=capi.FORCE_TC, cl=True)), dx) <= TOL
+        assert rel_err(host(capi.conv_wgrad(xd, gd, ks, s_, p_, flags=capi.FORCE_TC)), dw) <= TOL
+
+    try:
+        for tile in (64, 128, 256):
+            capi.call("omt_conv_plan_set", 0, g, tile, 1.0)
+            capi.call("omt_conv_plan_set", 1, g, tile, 1.0)
+            for wt, mult in ((64, 2.0), (128, 0.5), (192, 1.0), (256, 2.0), (0, 0.5)):
+                capi.call("omt_conv_plan_set", 2, g, wt, mult)
+                check_all()
+            # the caller's workspace, sized under the override
+            nbytes = capi.lib().omt_conv_workspace_bytes(2, g, 0)
+            ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+            got = torch.empty(co, ci, ks, ks, device="cuda")
+            capi.call("omt_conv_wgrad", g, capi.act(xd), capi.act(gd), capi.ptr(got), 1.0, capi.FORCE_TC, capi.ptr(ws), nbytes, capi.stream_handle())
+            assert rel_err(host(got), dw) <= TOL
+        for kind in (0, 1, 2):
+            capi.call("omt_conv_plan_set", kind, g, 0, 1.0)
+        assert capi.conv_plans_dump() == {}
+        for kind in (0, 1, 2):
+            tile, mult, best, rule = capi.conv_autotune(kind, g)
+            assert tile in (0, 64, 128, 192, 256) and mult in (0.5, 1.0, 2.0) and 0 <= best <= rule + 1e-6
+            stored = capi.conv_plan_get(kind, g)
+            assert stored == ((tile, mult) if (tile or mult != 1.0) else None)
+        check_all()
+    finally:
+        for kind in (0, 1, 2):
+            capi.call("omt_conv_plan_set", kind, g, 0, 1.0)
+    capi.call("omt_sync")
+
+
 def test_alexnet_conv1_full_size_per_tensor_vs_aten(capi):
     """AlexNet conv1 at full size (x [16,3,224,224], w [64,3,11,11], stride 4, pad 2; tools/gemm_bench.py:26-38): y, dx, dw
     and db each compared per tensor with aten's convolution and convolution_backward on the CPU, on the library's default

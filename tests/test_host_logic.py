@@ -288,3 +288,33 @@ def test_bench_reference_arm_prints_the_contract_line():
     cb = line["cpu_baseline"]
     assert cb["kind"] == "reference" and cb["cores"] >= 1 and cb["value"] == line["value"] and "PyTorch CPU" in cb["sample"]
     assert line["e2e"] == {"value": line["value"], "unit": "ms/step", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+
+
+def test_conv_plan_overrides_round_trip_without_a_gpu():
+    """The per-geometry plan table behind the tuning pass (set / get / dump / load) is host-side state of the library: stored
+    overrides come back, the text form round-trips, entries naming a tile width this build does not have are skipped, and
+    clearing leaves the table empty."""
+    from omarchy_mac_torch_b200 import capi
+    lib = capi.lib()
+    g1 = capi.geo(256, 128, 128, 28, 28, 3, 1, 1)
+    g2 = capi.geo(256, 64, 256, 56, 56, 1, 1, 0)
+    assert capi.conv_plan_get(2, g1) is None
+    capi.call("omt_conv_plan_set", 2, g1, 192, 0.5)
+    capi.call("omt_conv_plan_set", 0, g2, 128, 1.0)
+    assert capi.conv_plan_get(2, g1) == (192, 0.5) and capi.conv_plan_get(0, g2) == (128, 1.0) and capi.conv_plan_get(1, g2) is None
+    dump = capi.conv_plans_dump()
+    assert dump == {"2,256,128,128,28,28,28,28,3,1,1": (192, 0.5), "0,256,64,256,56,56,56,56,1,1,0": (128, 1.0)}
+    with pytest.raises(capi.OmtError):
+        capi.call("omt_conv_plan_set", 0, g2, 192, 1.0)   # 192 columns exist for the weight gradient only
+    with pytest.raises(capi.OmtError):
+        capi.call("omt_conv_plan_set", 1, g2, 256, 2.0)   # the slice factor belongs to the weight gradient
+    capi.call("omt_conv_plan_set", 2, g1, 0, 1.0)
+    capi.call("omt_conv_plan_set", 0, g2, 0, 0.0)
+    assert capi.conv_plans_dump() == {}
+    took = capi.conv_plans_load({**dump, "1,8,32,32,9,9,9,9,3,1,1": (96, 1.0), "not a key": (64, 1.0)})
+    assert took == 2 and capi.conv_plans_dump() == dump
+    assert lib.omt_conv_plans_load(b"") == 0
+    for k in dump:  # leave the process as it was found
+        f = [int(v) for v in k.split(",")]
+        capi.call("omt_conv_plan_set", f[0], capi.geo(f[1], f[2], f[3], f[4], f[5], f[8], f[9], f[10]), 0, 1.0)
+    assert capi.conv_plans_dump() == {}
